@@ -1,0 +1,221 @@
+/*
+ * leanffn_b200.h -- C ABI of the B200 (sm_100a) LeanFFN / block-sparse linear kernels.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches asynchronously on that stream and returns
+ * an int32 status: 0 = ok, < 0 = rejected argument (nothing was launched), > 0 = CUDA runtime
+ * error code + 1000.  No entry point allocates device memory (scratch is caller-provided)
+ * unless its comment says otherwise; none synchronises the device.
+ *
+ * Device-side waits are bounded: a kernel that gives up on a wait records a non-zero word in
+ * the caller-provided `status_word` (int32 in device memory, may be NULL) and returns.
+ *
+ * The entry points replace, one to one, what the reference (learning-at-home/lean_transformer)
+ * asks of PyTorch/ATen/cuBLAS/Triton on its LeanFFN path.  Each declaration cites the reference
+ * call site it stands in for (file:line relative to the reference project root).
+ */
+#ifndef LEANFFN_B200_H_
+#define LEANFFN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums (plain ints in the ABI) ------------------------------------------------------ */
+
+/* element types */
+#define LEANFFN_F32 0
+#define LEANFFN_BF16 1
+
+/* activations: lean_transformer/utils.py:24-38 (gelu_fused) and the transformers ACT2FN names
+ * the reference re-exports at lean_transformer/utils.py:80 */
+#define LEANFFN_ACT_GELU_TANH 0 /* gelu_fused, gelu_new, gelu_pytorch_tanh: 0.5x(1+tanh(0.79788456 x (1+0.044715 x^2))) */
+#define LEANFFN_ACT_GELU_ERF 1  /* gelu */
+#define LEANFFN_ACT_RELU 2
+#define LEANFFN_ACT_SILU 3      /* silu, swish */
+#define LEANFFN_ACT_TANH 4
+#define LEANFFN_ACT_SIGMOID 5
+#define LEANFFN_ACT_IDENTITY 6  /* linear */
+#define LEANFFN_ACT_COUNT 7
+
+/* GEMM epilogues */
+#define LEANFFN_EPI_STORE 0            /* D = acc [+ bias] */
+#define LEANFFN_EPI_GLU_FWD 1          /* gated: D = pre (acc+bias, [M,2I]), D2 = act(pre[:, :I]) * pre[:, I:] */
+#define LEANFFN_EPI_ACT_FWD 2          /* D = pre (acc+bias), D2 = act(pre) */
+#define LEANFFN_EPI_DROPOUT_RESIDUAL 3 /* D = dropout(acc+bias) + aux */
+#define LEANFFN_EPI_GLU_BWD 4          /* acc = dHid [M,I]; aux = pre [M,2I]; D = dPre [M,2I]; D2 = hid (optional) */
+#define LEANFFN_EPI_ACT_BWD 5          /* acc = dHid [M,N]; aux = pre; D = acc * act'(pre); D2 = act(pre) (optional) */
+
+/* negative status codes */
+#define LEANFFN_OK 0
+#define LEANFFN_ERR_NULL (-1)
+#define LEANFFN_ERR_SHAPE (-2)
+#define LEANFFN_ERR_ALIGN (-3)
+#define LEANFFN_ERR_DTYPE (-4)
+#define LEANFFN_ERR_UNSUPPORTED (-5)
+#define LEANFFN_ERR_DRIVER (-6)   /* could not obtain / call cuTensorMapEncodeTiled */
+#define LEANFFN_ERR_TOO_LARGE (-7)
+
+/* device-side status_word values */
+#define LEANFFN_DEV_OK 0
+#define LEANFFN_DEV_TIMEOUT_PRODUCER 1
+#define LEANFFN_DEV_TIMEOUT_MMA 2
+#define LEANFFN_DEV_TIMEOUT_EPILOGUE 3
+
+int32_t leanffn_abi_version(void);
+const char* leanffn_status_string(int32_t status);
+
+/* ---- row kernels ------------------------------------------------------------------------ */
+
+/* LayerNorm forward over the last dim: y = (x - mean) * rsqrt(var + eps) * gamma + beta, biased
+ * variance, statistics in fp32 (two-pass over registers).  Optionally followed by
+ * y = dropout(y) (Philox mask, see leanffn_dropout) and y += residual.
+ * Replaces F.layer_norm at lean_transformer/ffn.py:184, :200 and :283, torch.dropout_ at :204
+ * and torch.add at :207 (post-LN configuration). x, residual: x_dtype; gamma, beta: param_dtype
+ * (may be NULL = ones / zeros); y: y_dtype. */
+int32_t leanffn_layer_norm_forward(const void* x, int32_t x_dtype, const void* gamma, const void* beta,
+                                   int32_t param_dtype, void* y, int32_t y_dtype, int64_t rows, int64_t cols,
+                                   float eps, float dropout_p, uint64_t seed, uint64_t elem_offset,
+                                   const void* residual, int32_t residual_dtype, void* stream);
+
+/* Scratch (bytes) leanffn_layer_norm_backward needs for its per-block partial sums. */
+size_t leanffn_layer_norm_backward_scratch_bytes(int64_t rows, int64_t cols);
+
+/* LayerNorm backward with statistics recomputed from x (nothing but x is read from the forward):
+ *   dx = rstd * (g - mean(g) - xn * mean(g * xn)) [+ dresidual],  g = dy * gamma,
+ *   dgamma = sum_rows(dy * xn), dbeta = sum_rows(dy).
+ * Replaces torch.autograd.grad over the rematerialised F.layer_norm at
+ * lean_transformer/ffn.py:247-259 and :280-293, and the residual add at :297-300.
+ * dgamma/dbeta are fp32 [cols] (may be NULL together); dx may be NULL. */
+int32_t leanffn_layer_norm_backward(const void* dy, int32_t dy_dtype, const void* x, int32_t x_dtype,
+                                    const void* gamma, int32_t param_dtype, const void* dresidual,
+                                    int32_t dresidual_dtype, void* dx, int32_t dx_dtype, float* dgamma,
+                                    float* dbeta, void* scratch, int64_t rows, int64_t cols, float eps,
+                                    void* stream);
+
+/* hid = act(pre) (gated == 0, pre [rows, inter]) or act(pre[:, :inter]) * pre[:, inter:]
+ * (gated != 0, pre [rows, 2*inter]).  Replaces _LeanFFN._apply_activation,
+ * lean_transformer/ffn.py:138-144 (the first half of the last dim is the gate). */
+int32_t leanffn_activation_forward(const void* pre, void* hid, int32_t dtype, int64_t rows, int64_t inter,
+                                   int32_t gated, int32_t act, void* stream);
+
+/* dpre = d(hid)/d(pre) applied to dhid; optionally also rematerialises hid (hid_out may be NULL).
+ * Replaces torch.autograd.grad(hid_act, pre_activation, ...) at lean_transformer/ffn.py:275
+ * (GELU.backward, lean_transformer/utils.py:33-50). */
+int32_t leanffn_activation_backward(const void* dhid, const void* pre, void* dpre, void* hid_out,
+                                    int32_t dtype, int64_t rows, int64_t inter, int32_t gated, int32_t act,
+                                    void* stream);
+
+/* y[i] = (keep(seed, elem_offset + i) ? x[i] / (1 - p) : 0) [+ residual[i]], i in [0, n); residual may be
+ * NULL.  keep() is a pure function:
+ * Philox4x32-10 with key (seed_lo, seed_hi), counter ((e >> 2) lo, (e >> 2) hi, 0, 0), word e & 3,
+ * keep iff word >= floor(p * 2^32).  The same call with the same (seed, offset) regenerates the
+ * mask, which is how backward reuses the forward's mask.
+ * Replaces torch.dropout_/torch.dropout at lean_transformer/ffn.py:204 and :245 (the reference
+ * restores the RNG state instead, :308-321) and torch.add at :207. */
+int32_t leanffn_dropout(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t n, float p,
+                        uint64_t seed, uint64_t elem_offset, const void* residual, int32_t residual_dtype,
+                        void* stream);
+
+/* mask[i] = keep(seed, elem_offset + i) as uint8; lets a checker inject the very same mask into
+ * another implementation. */
+int32_t leanffn_dropout_mask(uint8_t* mask, int64_t n, float p, uint64_t seed, uint64_t elem_offset,
+                             void* stream);
+
+size_t leanffn_column_sum_scratch_bytes(int64_t rows, int64_t cols);
+/* out[c] = sum_r x[r, c] in fp32, deterministic two-stage reduction.
+ * Replaces grad_output_flat.sum(dim=0) at lean_transformer/blocksparse/linear.py:293-294. */
+int32_t leanffn_column_sum(const void* x, int32_t x_dtype, int64_t ld, float* out, void* scratch,
+                           int64_t rows, int64_t cols, void* stream);
+
+/* y = (y_dtype) x, n elements. Replaces the autocast casts the reference relies on
+ * (torch.cuda.amp.custom_fwd at lean_transformer/ffn.py:147). */
+int32_t leanffn_cast(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t n, void* stream);
+
+/* y[c, r] = x[r, c]; x is [rows, cols] with leading dim ldx, y is [cols, rows] contiguous. */
+int32_t leanffn_transpose(const void* x, int32_t dtype, int64_t ldx, void* y, int64_t rows, int64_t cols,
+                          void* stream);
+
+/* ---- GEMMs ------------------------------------------------------------------------------ */
+
+/* One descriptor serves the dense and the block-sparse products and all fused epilogues.
+ *
+ * D[M,N] = sum over k of A(m,k) * B(n,k), fp32 accumulation.
+ *   a_mn_major == 0: A is stored [M,K] row-major (K contiguous, leading dim lda)
+ *   a_mn_major != 0: A is stored [K,M] row-major (M contiguous)            -- "transposed"
+ *   b_mn_major == 0: B is stored [N,K] row-major (K contiguous)            -- x @ W^T with W [out,in]
+ *   b_mn_major != 0: B is stored [K,N] row-major (N contiguous)
+ * This covers lean_transformer/blocksparse/linear.py:219 (F.linear), :304-305 (wgrad, both
+ * operands MN-major, K = tokens) and :307-308 (dgrad, B MN-major).
+ *
+ * Low-rank term (optional, lean_transformer/blocksparse/linear.py:221-226 and :317-323): after the
+ * main k-loop the kernel continues over a second operand pair A2 (M x K2) / B2 (N x K2), stored with
+ * the same majorness as A / B, accumulating into the same tile.
+ *
+ * Block-sparse modes (lean_transformer/blocksparse/native_backend.py:9-76 and the Triton operator of
+ * lean_transformer/blocksparse/triton_backend.py:18-79).  B is an array of bs_num_blocks weight blocks,
+ * block f a row-major [block(out) x block(in)] matrix at B + f*block*block.  That is the reference's
+ * native tensor [in_features, blocks_per_input, block] (f = j*blocks_per_input + a) as well as its
+ * Triton tensor [1, nnz, block, block] (f = rank of the block in layout.nonzero()).  Which blocks meet
+ * is given by bs_index, a table of int32 PAIRS with bs_nnz pairs per row, and bs_count (int32 per
+ * table row: how many leading pairs are valid; NULL = bs_nnz everywhere):
+ *   bs_mode 0: dense.
+ *   bs_mode 1: forward.  A = x [M, K=in_features], N = out_features.  Table row = output block,
+ *              pair = (weight block f, input block j):  D[:, i] = sum_t x[:, j_t] . W_f_t^T.
+ *   bs_mode 2: dgrad.    A = dy [M, K=out_features], N = in_features.  Table row = input block,
+ *              pair = (weight block f, output block o): D[:, j] = sum_t dy[:, o_t] . W_f_t.
+ *   bs_mode 3: wgrad.    A = dy [tokens(K), out_features] and B = x [tokens(K), in_features], both
+ *              MN-major; D = the weight gradient, M = bs_num_blocks*block rows of N = block columns.
+ *              Table row = weight block f, one pair (output block o, input block j), bs_nnz = 1.
+ * Block-sparse products take LEANFFN_EPI_STORE only.
+ */
+typedef struct leanffn_gemm_desc {
+  int32_t M, N, K;
+  int32_t in_dtype;      /* LEANFFN_BF16: tcgen05 tensor-core path; LEANFFN_F32: SIMT fp32 path */
+  const void* A;
+  int64_t lda;
+  int32_t a_mn_major;
+  int32_t b_mn_major;
+  const void* B;
+  int64_t ldb;
+  /* low-rank continuation (K2 == 0 disables) */
+  const void* A2;
+  const void* B2;
+  int64_t lda2, ldb2;
+  int32_t K2;
+  /* block-sparse */
+  int32_t bs_mode;
+  int32_t bs_block;
+  int32_t bs_nnz;        /* pairs per row of bs_index */
+  int32_t bs_num_blocks; /* number of weight blocks in B (modes 1, 2) or D (mode 3) */
+  const int32_t* bs_index;
+  const int32_t* bs_count;
+  /* epilogue */
+  int32_t epilogue;
+  int32_t act;
+  void* D;
+  int64_t ldd;
+  int32_t d_dtype;
+  void* D2;
+  int64_t ldd2;
+  const void* bias;  /* [N] or NULL */
+  int32_t bias_dtype;
+  const void* aux;   /* residual [M,N] or pre-activation, see epilogue */
+  int64_t ldaux;
+  int32_t aux_dtype;
+  float dropout_p;
+  uint64_t seed;
+  uint64_t elem_offset; /* element index of D[0,0] in the logical dropout stream */
+  int32_t* status_word; /* device int32 or NULL */
+  int32_t force_simt;   /* != 0: run the SIMT kernel whatever the dtype (checker / odd shapes) */
+} leanffn_gemm_desc;
+
+int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEANFFN_B200_H_ */

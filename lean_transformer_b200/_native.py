@@ -1,0 +1,103 @@
+"""ctypes binding of ``libleanffn_b200.so`` (declared in ``include/leanffn_b200.h``).
+
+The library is the only compute path of this package.  If it is missing or does not load, importing
+this module raises: there is no PyTorch / CPU fallback behind it.
+"""
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+from pathlib import Path
+
+LIB_NAME = "libleanffn_b200.so"
+LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
+
+# element types / activations / epilogues: keep in sync with include/leanffn_b200.h
+F32, BF16 = 0, 1
+ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_TANH, ACT_SIGMOID, ACT_IDENTITY = range(7)
+EPI_STORE, EPI_GLU_FWD, EPI_ACT_FWD, EPI_DROPOUT_RESIDUAL, EPI_GLU_BWD, EPI_ACT_BWD = range(6)
+DEV_STATUS_NAMES = {0: "ok", 1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out"}
+
+
+class GemmDesc(ctypes.Structure):
+    """Mirror of ``leanffn_gemm_desc``."""
+
+    _fields_ = [
+        ("M", c_int32), ("N", c_int32), ("K", c_int32), ("in_dtype", c_int32),
+        ("A", c_void_p), ("lda", c_int64), ("a_mn_major", c_int32), ("b_mn_major", c_int32),
+        ("B", c_void_p), ("ldb", c_int64),
+        ("A2", c_void_p), ("B2", c_void_p), ("lda2", c_int64), ("ldb2", c_int64), ("K2", c_int32),
+        ("bs_mode", c_int32), ("bs_block", c_int32), ("bs_nnz", c_int32), ("bs_num_blocks", c_int32),
+        ("bs_index", c_void_p), ("bs_count", c_void_p),
+        ("epilogue", c_int32), ("act", c_int32),
+        ("D", c_void_p), ("ldd", c_int64), ("d_dtype", c_int32),
+        ("D2", c_void_p), ("ldd2", c_int64),
+        ("bias", c_void_p), ("bias_dtype", c_int32),
+        ("aux", c_void_p), ("ldaux", c_int64), ("aux_dtype", c_int32),
+        ("dropout_p", c_float), ("seed", c_uint64), ("elem_offset", c_uint64),
+        ("status_word", c_void_p), ("force_simt", c_int32),
+    ]
+
+
+_SIGNATURES = {
+    "leanffn_abi_version": (c_int32, []),
+    "leanffn_status_string": (c_char_p, [c_int32]),
+    "leanffn_layer_norm_forward": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int64,
+                                             c_int64, c_float, c_float, c_uint64, c_uint64, c_void_p, c_int32,
+                                             c_void_p]),
+    "leanffn_layer_norm_backward_scratch_bytes": (c_size_t, [c_int64, c_int64]),
+    "leanffn_layer_norm_backward": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_int32,
+                                              c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                              c_float, c_void_p]),
+    "leanffn_activation_forward": (c_int32, [c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int32, c_int32, c_void_p]),
+    "leanffn_activation_backward": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,
+                                              c_int32, c_int32, c_void_p]),
+    "leanffn_dropout": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_float, c_uint64, c_uint64, c_void_p,
+                                  c_int32, c_void_p]),
+    "leanffn_dropout_mask": (c_int32, [c_void_p, c_int64, c_float, c_uint64, c_uint64, c_void_p]),
+    "leanffn_column_sum_scratch_bytes": (c_size_t, [c_int64, c_int64]),
+    "leanffn_column_sum": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "leanffn_cast": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_void_p]),
+    "leanffn_transpose": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
+    "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def _load():
+    if not LIB_PATH.exists():
+        raise NativeLibraryError(
+            f"{LIB_PATH} is missing. Build it with `python -m lean_transformer_b200.build` (needs nvcc); "
+            "this package has no fallback path without its CUDA library."
+        )
+    try:
+        lib = ctypes.CDLL(os.fspath(LIB_PATH))
+    except OSError as e:  # pragma: no cover - depends on the machine
+        raise NativeLibraryError(f"could not load {LIB_PATH}: {e}") from e
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:
+            raise NativeLibraryError(f"{LIB_PATH} does not export {name}") from e
+        fn.restype = restype
+        fn.argtypes = argtypes
+    if lib.leanffn_abi_version() != 1:
+        raise NativeLibraryError("libleanffn_b200.so has an unexpected ABI version; rebuild it")
+    return lib
+
+
+lib = _load()
+
+
+def status_string(code: int) -> str:
+    return lib.leanffn_status_string(int(code)).decode()
+
+
+def check(code: int, what: str):
+    """Raise if a C-ABI call reported a non-zero status."""
+    if code != 0:
+        raise RuntimeError(f"{what} failed with status {code}: {status_string(code)}")

@@ -1,0 +1,139 @@
+"""Block-sparse matmul over the reference's native weight layout, computed by the CUDA kernels.
+
+Same call signatures as lean_transformer/blocksparse/native_backend.py:9-76: the weight is
+[in_features, blocks_per_input, block]; input block j and slot a hold a [block(out) x block(in)] matrix
+that feeds output block backward_indices[j, a].  Where the reference materialises every active output
+block ([nnz * block, tokens]) and gathers with embedding_bag, the kernels here walk only the nonzero
+blocks of each output tile.
+"""
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import ops
+from .layout import tables_from_native_indices
+
+_TABLE_CACHE: Dict[tuple, tuple] = {}
+
+
+def _cache_put(key, value):
+    if len(_TABLE_CACHE) > 256:
+        _TABLE_CACHE.clear()
+    _TABLE_CACHE[key] = value
+    return value
+
+
+def backward_indices_from_forward(forward_indices: torch.Tensor, blocks_per_input: int) -> torch.Tensor:
+    """Invert forward_indices: entry f = j * blocks_per_input + a listed under output block i means
+    backward_indices[j, a] = i."""
+    out_blocks, per_row = forward_indices.shape
+    flat = forward_indices.to(torch.int64).flatten()
+    owner = torch.arange(out_blocks, device=forward_indices.device).repeat_interleave(per_row)
+    backward = torch.empty(flat.numel(), dtype=torch.int64, device=forward_indices.device)
+    backward[flat] = owner
+    return backward.view(-1, blocks_per_input)
+
+
+def native_tables(forward_indices: Optional[torch.Tensor], backward_indices: Optional[torch.Tensor],
+                  blocks_per_input: int):
+    """(forward, dgrad, wgrad) pair tables on the indices' device, cached per index tensor."""
+    key = (forward_indices.data_ptr() if forward_indices is not None else 0,
+           backward_indices.data_ptr() if backward_indices is not None else 0, blocks_per_input,
+           str((forward_indices if forward_indices is not None else backward_indices).device))
+    hit = _TABLE_CACHE.get(key)
+    if hit is not None:
+        return hit
+    if backward_indices is None:
+        backward_indices = backward_indices_from_forward(forward_indices, blocks_per_input)
+    if forward_indices is None:
+        in_blocks, per_col = backward_indices.shape
+        out_blocks = int(backward_indices.max().item()) + 1
+        # list, per output block, the flat ids feeding it (ascending)
+        flat_owner = backward_indices.flatten()
+        order = torch.argsort(flat_owner, stable=True)
+        forward_indices = order.view(out_blocks, -1).to(torch.int32)
+    return _cache_put(key, tables_from_native_indices(forward_indices, backward_indices))
+
+
+def _bs_forward(x2d: torch.Tensor, weight: torch.Tensor, fwd_table: torch.Tensor, out_features: int,
+                out: Optional[torch.Tensor] = None, bias=None, a2=None, b2=None,
+                out_dtype: Optional[torch.dtype] = None, count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    block = weight.shape[-1]
+    num_blocks = weight.numel() // (block * block)
+    return ops.gemm(x2d, weight, M=x2d.shape[0], N_=out_features, K=x2d.shape[1], out=out, bias=bias, a2=a2, b2=b2,
+                    out_dtype=out_dtype, bs_mode=1, bs_block=block, bs_nnz=fwd_table.shape[1],
+                    bs_num_blocks=num_blocks, bs_index=fwd_table, bs_count=count)
+
+
+def _bs_dgrad(dy2d: torch.Tensor, weight: torch.Tensor, dgrad_table: torch.Tensor, in_features: int,
+              a2=None, b2=None, count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    block = weight.shape[-1]
+    num_blocks = weight.numel() // (block * block)
+    return ops.gemm(dy2d, weight, M=dy2d.shape[0], N_=in_features, K=dy2d.shape[1], b_mn_major=True, a2=a2, b2=b2,
+                    bs_mode=2, bs_block=block, bs_nnz=dgrad_table.shape[1], bs_num_blocks=num_blocks,
+                    bs_index=dgrad_table, bs_count=count)
+
+
+def _bs_wgrad(dy2d: torch.Tensor, x2d: torch.Tensor, weight_like: torch.Tensor, wgrad_table: torch.Tensor,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    block = weight_like.shape[-1]
+    num_blocks = weight_like.numel() // (block * block)
+    out = torch.empty((num_blocks * block, block), dtype=out_dtype, device=dy2d.device)
+    ops.gemm(dy2d, x2d, a_mn_major=True, b_mn_major=True, M=num_blocks * block, N_=block, K=dy2d.shape[0], out=out,
+             bs_mode=3, bs_block=block, bs_nnz=1, bs_num_blocks=num_blocks, bs_index=wgrad_table)
+    return out.view(weight_like.shape)
+
+
+class _BlocksparseMatmul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, weight, forward_indices):
+        in_features, blocks_per_input, block = weight.shape
+        fwd, dgrad, wgrad = native_tables(forward_indices, None, blocks_per_input)
+        x2d = input.reshape(-1, in_features).contiguous()
+        out_features = forward_indices.shape[0] * block
+        out = _bs_forward(x2d, weight.contiguous(), fwd, out_features)
+        ctx.save_for_backward(input, weight)
+        ctx.tables = (dgrad, wgrad)
+        return out.view(*input.shape[:-1], out_features)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight = ctx.saved_tensors
+        dgrad, wgrad = ctx.tables
+        dy = ops.cast(grad_output.reshape(-1, grad_output.shape[-1]).contiguous(), input.dtype)
+        x2d = input.reshape(-1, input.shape[-1]).contiguous()
+        grad_input = grad_weight = None
+        if ctx.needs_input_grad[0]:
+            grad_input = _bs_dgrad(dy, weight.contiguous(), dgrad, input.shape[-1]).view(input.shape)
+        if ctx.needs_input_grad[1]:
+            grad_weight = _bs_wgrad(dy, x2d, weight, wgrad, weight.dtype)
+        return grad_input, grad_weight, None
+
+
+def blocksparse_matmul(input: torch.Tensor, weight: torch.Tensor, forward_indices: torch.Tensor) -> torch.Tensor:
+    """
+    :param input: tensor [*batch_dims, in_features]
+    :param weight: tensor [in_features, active_blocks_per_input, block_size]
+    :param forward_indices: the first output of get_indices_from_layout(...)
+    :returns: tensor [*batch_dims, out_features]
+    """
+    assert input.shape[-1] == weight.shape[0]
+    return _BlocksparseMatmul.apply(input, weight, forward_indices)
+
+
+def blocksparse_matmul_backward(grad_output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor,
+                                backward_indices: torch.Tensor, input_requires_grad: bool = True,
+                                weight_requires_grad: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Gradients of blocksparse_matmul w.r.t. input and / or weight without autograd."""
+    assert input_requires_grad or weight_requires_grad, "computing backward but none of the inputs requires grad"
+    in_features, blocks_per_input, block = weight.shape
+    _, dgrad, wgrad = native_tables(None, backward_indices, blocks_per_input)
+    dy = grad_output.reshape(-1, grad_output.shape[-1]).contiguous()
+    x2d = input.reshape(-1, input.shape[-1]).contiguous()
+    grad_input = grad_weight = torch.empty(0, device=grad_output.device)
+    if input_requires_grad:
+        grad_input = _bs_dgrad(dy, weight.contiguous(), dgrad, in_features).view(
+            grad_output.shape[:-1] + input.shape[-1:])
+    if weight_requires_grad:
+        grad_weight = _bs_wgrad(dy, x2d, weight, wgrad, weight.dtype)
+    return grad_input, grad_weight

@@ -1,0 +1,213 @@
+// C-ABI GEMM entry point: validates the descriptor, picks the tcgen05 tensor-core kernel when the
+// problem meets its layout rules (bf16 operands, 16-byte aligned pitches, block-sparse blocks that are
+// multiples of 128) and the SIMT kernel otherwise.  There is no host or library fallback: both paths
+// are this library's own device code.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "gemm_common.cuh"
+
+namespace leanffn {
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline size_t esize(int32_t dtype) { return dtype == LEANFFN_BF16 ? 2 : 4; }
+static inline bool pitch16(int64_t ld, int32_t dtype) { return (ld * static_cast<int64_t>(esize(dtype))) % 16 == 0; }
+
+}  // namespace leanffn
+
+using namespace leanffn;
+
+extern "C" int32_t leanffn_abi_version(void) { return 1; }
+
+extern "C" const char* leanffn_status_string(int32_t s) {
+  switch (s) {
+    case LEANFFN_OK: return "ok";
+    case LEANFFN_ERR_NULL: return "null pointer argument";
+    case LEANFFN_ERR_SHAPE: return "invalid shape";
+    case LEANFFN_ERR_ALIGN: return "pointer or pitch not aligned";
+    case LEANFFN_ERR_DTYPE: return "unsupported element type combination";
+    case LEANFFN_ERR_UNSUPPORTED: return "unsupported option";
+    case LEANFFN_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
+    case LEANFFN_ERR_TOO_LARGE: return "size beyond the supported maximum";
+    default: break;
+  }
+  if (s >= 1000) return cudaGetErrorString(static_cast<cudaError_t>(s - 1000));
+  return "unknown status";
+}
+
+extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
+  if (d == nullptr) return LEANFFN_ERR_NULL;
+  if (d->A == nullptr || d->B == nullptr || d->D == nullptr) return LEANFFN_ERR_NULL;
+  if (d->M < 0 || d->N <= 0 || d->K <= 0 || d->K2 < 0) return LEANFFN_ERR_SHAPE;
+  if (d->in_dtype != LEANFFN_F32 && d->in_dtype != LEANFFN_BF16) return LEANFFN_ERR_DTYPE;
+  if (d->d_dtype != LEANFFN_F32 && d->d_dtype != LEANFFN_BF16) return LEANFFN_ERR_DTYPE;
+  if (d->epilogue < LEANFFN_EPI_STORE || d->epilogue > LEANFFN_EPI_ACT_BWD) return LEANFFN_ERR_UNSUPPORTED;
+  if (d->act < 0 || d->act >= LEANFFN_ACT_COUNT) return LEANFFN_ERR_UNSUPPORTED;
+  if (d->bs_mode < 0 || d->bs_mode > 3) return LEANFFN_ERR_UNSUPPORTED;
+  if (!(d->dropout_p >= 0.f && d->dropout_p < 1.f)) return LEANFFN_ERR_UNSUPPORTED;
+  if (d->K2 > 0 && (d->A2 == nullptr || d->B2 == nullptr)) return LEANFFN_ERR_NULL;
+  const int epi = d->epilogue;
+  const bool needs_d2 = epi == LEANFFN_EPI_GLU_FWD || epi == LEANFFN_EPI_ACT_FWD;
+  const bool needs_aux = epi == LEANFFN_EPI_GLU_BWD || epi == LEANFFN_EPI_ACT_BWD;
+  if (needs_d2 && d->D2 == nullptr) return LEANFFN_ERR_NULL;
+  if (needs_aux && d->aux == nullptr) return LEANFFN_ERR_NULL;
+  if (epi == LEANFFN_EPI_GLU_FWD && (d->N % 2 != 0)) return LEANFFN_ERR_SHAPE;
+  if (d->bs_mode != 0) {
+    if (d->bs_index == nullptr) return LEANFFN_ERR_NULL;
+    if (d->bs_block <= 0 || d->bs_nnz <= 0 || d->bs_num_blocks <= 0) return LEANFFN_ERR_SHAPE;
+    if (d->bs_mode == 3) {
+      if (!d->a_mn_major || !d->b_mn_major || d->N != d->bs_block ||
+          d->M != static_cast<int64_t>(d->bs_num_blocks) * d->bs_block || d->K2 != 0 || d->bs_nnz != 1)
+        return LEANFFN_ERR_SHAPE;
+    } else {
+      if (d->a_mn_major || d->N % d->bs_block != 0 || d->K % d->bs_block != 0) return LEANFFN_ERR_SHAPE;
+    }
+    if (epi != LEANFFN_EPI_STORE) return LEANFFN_ERR_UNSUPPORTED;
+  }
+  if (d->M == 0) return LEANFFN_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  EpiParams ep{};
+  ep.kind = epi;
+  ep.act = d->act;
+  ep.M = d->M;
+  ep.N = d->N;
+  ep.D = d->D;
+  ep.ldd = d->ldd;
+  ep.d_dtype = d->d_dtype;
+  ep.D2 = d->D2;
+  ep.ldd2 = d->ldd2;
+  ep.bias = d->bias;
+  ep.bias_dtype = d->bias_dtype;
+  ep.aux = d->aux;
+  ep.ldaux = d->ldaux;
+  ep.aux_dtype = d->aux_dtype;
+  ep.threshold = d->dropout_p > 0.f ? dropout_threshold(d->dropout_p) : 0u;
+  ep.keep_scale = 1.0f / (1.0f - d->dropout_p);
+  ep.seed = d->seed;
+  ep.elem_offset = d->elem_offset;
+
+  // Reduction length seen by the kernels.
+  int64_t k_eff = d->K;
+  if (d->bs_mode == 1 || d->bs_mode == 2) k_eff = static_cast<int64_t>(d->bs_nnz) * d->bs_block;
+
+  // ---- tensor-core path ------------------------------------------------------------------------
+  bool tc = d->in_dtype == LEANFFN_BF16 && !d->force_simt;
+  tc = tc && d->M >= 64 && d->N >= 64 && k_eff >= 32;
+  tc = tc && aligned16(d->A) && aligned16(d->B) && pitch16(d->lda, LEANFFN_BF16) && aligned16(d->D) &&
+       pitch16(d->ldd, d->d_dtype) && d->N % 8 == 0;
+  if (d->bs_mode == 0 || d->bs_mode == 3) tc = tc && pitch16(d->ldb, LEANFFN_BF16);
+  if (d->bs_mode != 0) tc = tc && d->bs_block % 128 == 0;
+  if (d->a_mn_major && !d->b_mn_major) tc = false;  // combination not used by any caller
+  if (d->K2 > 0)
+    tc = tc && aligned16(d->A2) && aligned16(d->B2) && pitch16(d->lda2, LEANFFN_BF16) && pitch16(d->ldb2, LEANFFN_BF16);
+  if (d->bias != nullptr) tc = tc && aligned16(d->bias);
+  if (d->aux != nullptr) tc = tc && aligned16(d->aux) && pitch16(d->ldaux, d->aux_dtype);
+  if (d->D2 != nullptr) tc = tc && aligned16(d->D2) && pitch16(d->ldd2, d->d_dtype);
+  if (needs_d2) tc = tc && d->d_dtype == LEANFFN_BF16;
+  if (epi == LEANFFN_EPI_GLU_FWD) tc = tc && (d->N / 2) % 8 == 0 && d->bs_mode == 0;
+  if (ep.threshold != 0u) tc = tc && d->elem_offset % 4 == 0;
+
+  if (tc) {
+    TcParams p{};
+    p.ep = ep;
+    p.status = d->status_word;
+    p.bs_mode = d->bs_mode;
+    p.bs_block = d->bs_mode ? d->bs_block : 0;
+    p.bs_nnz = d->bs_nnz;
+    p.bs_index = d->bs_index;
+    p.bs_count = d->bs_count;
+    p.glu_split = 0;
+    int block_n = (d->bs_mode != 0 || d->N <= 128) ? 128 : 256;
+    int64_t n_tiles_n;
+    if (epi == LEANFFN_EPI_GLU_FWD) {
+      block_n = 256;
+      p.glu_split = d->N / 2;
+      n_tiles_n = (p.glu_split + 127) / 128;
+    } else {
+      n_tiles_n = (d->N + block_n - 1) / block_n;
+    }
+    p.num_m_blocks = static_cast<int32_t>((d->M + 127) / 128);
+    p.num_n_blocks = static_cast<int32_t>(n_tiles_n);
+    p.num_k_blocks = static_cast<int32_t>((k_eff + 63) / 64);
+    p.num_k2_blocks = static_cast<int32_t>((d->K2 + 63) / 64);
+    TcOperand A{}, B{}, A2{}, B2{};
+    A.ptr = d->A;
+    A.ld = d->lda;
+    B.ptr = d->B;
+    B.ld = d->ldb;
+    if (d->bs_mode == 0) {
+      if (d->a_mn_major) A.rows = d->K, A.cols = d->M; else A.rows = d->M, A.cols = d->K;
+      if (d->b_mn_major) B.rows = d->K, B.cols = d->N; else B.rows = d->N, B.cols = d->K;
+    } else if (d->bs_mode == 1 || d->bs_mode == 2) {
+      // A: activations [M, K]; B: the weight blocks seen as one [(num_blocks * block), block] matrix
+      A.rows = d->M, A.cols = d->K;
+      B.rows = static_cast<int64_t>(d->bs_num_blocks) * d->bs_block;
+      B.cols = d->bs_block;
+      B.ld = d->bs_block;
+    } else {
+      A.rows = d->K, A.cols = d->lda;  // dy [tokens, out_features]
+      B.rows = d->K, B.cols = d->ldb;  // x  [tokens, in_features]
+    }
+    if (d->K2 > 0) {
+      A2.ptr = d->A2, A2.ld = d->lda2;
+      B2.ptr = d->B2, B2.ld = d->ldb2;
+      if (d->a_mn_major) A2.rows = d->K2, A2.cols = d->M; else A2.rows = d->M, A2.cols = d->K2;
+      if (d->b_mn_major) B2.rows = d->K2, B2.cols = d->N; else B2.rows = d->N, B2.cols = d->K2;
+    }
+    cudaError_t ce;
+    return gemm_tcgen05(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
+                        d->K2 > 0 ? &B2 : nullptr, p, block_n, st, &ce);
+  }
+
+  // ---- SIMT path ---------------------------------------------------------------------------------
+  SimtOperands o{};
+  o.A = d->A;
+  o.B = d->B;
+  o.lda = d->lda;
+  o.ldb = d->ldb;
+  o.K = static_cast<int32_t>(k_eff);
+  if (d->a_mn_major) o.a_sm = 1, o.a_sk = d->lda; else o.a_sm = d->lda, o.a_sk = 1;
+  if (d->b_mn_major) o.b_sn = 1, o.b_sk = d->ldb; else o.b_sn = d->ldb, o.b_sk = 1;
+  o.A2 = d->K2 > 0 ? d->A2 : nullptr;
+  o.B2 = d->K2 > 0 ? d->B2 : nullptr;
+  o.K2 = d->K2;
+  if (d->a_mn_major) o.a2_sm = 1, o.a2_sk = d->lda2; else o.a2_sm = d->lda2, o.a2_sk = 1;
+  if (d->b_mn_major) o.b2_sn = 1, o.b2_sk = d->ldb2; else o.b2_sn = d->ldb2, o.b2_sk = 1;
+  o.bs_mode = d->bs_mode;
+  o.bs_block = d->bs_block;
+  o.bs_nnz = d->bs_nnz;
+  o.bs_index = d->bs_index;
+  o.bs_count = d->bs_count;
+
+  cudaError_t e;
+  if (epi == LEANFFN_EPI_STORE || epi == LEANFFN_EPI_DROPOUT_RESIDUAL) {
+    e = gemm_simt(o, ep, d->in_dtype, st);
+    return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+  }
+  // Activation epilogues: the product is stored first, the activation runs as a second pass.
+  EpiParams plain = ep;
+  plain.kind = LEANFFN_EPI_STORE;
+  if (epi == LEANFFN_EPI_GLU_FWD || epi == LEANFFN_EPI_ACT_FWD) {
+    const bool gated = epi == LEANFFN_EPI_GLU_FWD;
+    const int64_t inter = gated ? d->N / 2 : d->N;
+    if (d->ldd != d->N || d->ldd2 != inter || inter % 4 != 0) return LEANFFN_ERR_UNSUPPORTED;
+    e = gemm_simt(o, plain, d->in_dtype, st);
+    if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+    return launch_act_fwd(d->D, d->D2, d->d_dtype, d->M, inter, gated ? 1 : 0, d->act, st);
+  }
+  {
+    const bool gated = epi == LEANFFN_EPI_GLU_BWD;
+    const int64_t inter = d->N;
+    const int64_t ldpre = gated ? 2 * inter : inter;
+    if (d->ldd != ldpre || d->ldaux != ldpre || d->aux_dtype != d->d_dtype || inter % 4 != 0)
+      return LEANFFN_ERR_UNSUPPORTED;
+    if (d->D2 != nullptr && d->ldd2 != inter) return LEANFFN_ERR_UNSUPPORTED;
+    // dHid lands in the linear half of dPre (gated) or in dPre itself, then is transformed in place.
+    plain.D = static_cast<char*>(d->D) + (gated ? inter * esize(d->d_dtype) : 0);
+    plain.bias = nullptr;
+    e = gemm_simt(o, plain, d->in_dtype, st);
+    if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+    return launch_act_bwd(plain.D, ldpre, d->aux, d->D, d->D2, d->d_dtype, d->M, inter, gated ? 1 : 0, d->act, st);
+  }
+}

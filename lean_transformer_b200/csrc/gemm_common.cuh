@@ -1,0 +1,99 @@
+// Pieces shared by the SIMT and the tcgen05 GEMM kernels: the epilogue parameter block and the
+// per-element / per-run epilogue math (bias, gated activation forward and backward, dropout,
+// residual).
+#pragma once
+#include "math.cuh"
+
+namespace leanffn {
+
+struct EpiParams {
+  int32_t kind;  // LEANFFN_EPI_*
+  int32_t act;
+  int32_t M, N;  // logical extent of the accumulator matrix
+  void* D;
+  int64_t ldd;
+  int32_t d_dtype;
+  void* D2;
+  int64_t ldd2;
+  const void* bias;
+  int32_t bias_dtype;
+  const void* aux;
+  int64_t ldaux;
+  int32_t aux_dtype;
+  uint32_t threshold;  // 0: no dropout
+  float keep_scale;
+  uint64_t seed;
+  uint64_t elem_offset;
+};
+
+__device__ __forceinline__ float load_any(const void* p, int32_t dtype, int64_t i) {
+  return dtype == LEANFFN_BF16 ? __bfloat162float(static_cast<const bf16*>(p)[i]) : static_cast<const float*>(p)[i];
+}
+__device__ __forceinline__ void store_any(void* p, int32_t dtype, int64_t i, float v) {
+  if (dtype == LEANFFN_BF16)
+    static_cast<bf16*>(p)[i] = __float2bfloat16_rn(v);
+  else
+    static_cast<float*>(p)[i] = v;
+}
+
+// Scalar epilogue for the kinds the SIMT kernel fuses (STORE, DROPOUT_RESIDUAL).
+__device__ __forceinline__ void epilogue_scalar(const EpiParams& p, int64_t row, int64_t col, float acc) {
+  if (p.bias != nullptr) acc += load_any(p.bias, p.bias_dtype, col);
+  if (p.kind == LEANFFN_EPI_DROPOUT_RESIDUAL) {
+    if (p.threshold != 0u)
+      acc = dropout_keep1(p.elem_offset + static_cast<uint64_t>(row) * p.N + col, p.seed, p.threshold)
+                ? acc * p.keep_scale
+                : 0.f;
+    if (p.aux != nullptr) acc += load_any(p.aux, p.aux_dtype, row * p.ldaux + col);
+  }
+  store_any(p.D, p.d_dtype, row * p.ldd + col, acc);
+}
+
+// ---- operand / parameter blocks shared between the entry point and the kernels ------------------
+struct SimtOperands {
+  const void* A;
+  const void* B;
+  int64_t a_sm, a_sk;  // element strides of A over (m, k)
+  int64_t b_sn, b_sk;
+  int32_t K;
+  // low-rank continuation
+  const void* A2;
+  const void* B2;
+  int64_t a2_sm, a2_sk, b2_sn, b2_sk;
+  int32_t K2;
+  // block-sparse
+  int32_t bs_mode, bs_block, bs_nnz;
+  const int32_t* bs_index;  // int32 pairs
+  const int32_t* bs_count;  // entries per table row, or nullptr (= bs_nnz everywhere)
+  int64_t lda, ldb;
+};
+
+struct TcParams {
+  int32_t num_m_blocks, num_n_blocks;
+  int32_t num_k_blocks;   // main reduction, in 64-element units (dense: ceil(K/64); sparse: nnz * block/64)
+  int32_t num_k2_blocks;  // low-rank continuation
+  int32_t bs_mode, bs_block, bs_nnz;
+  const int32_t* bs_index;  // int32 pairs, see include/leanffn_b200.h
+  const int32_t* bs_count;  // entries per table row, or nullptr
+  int32_t glu_split;  // > 0: B rows [n, n+128) and [glu_split + n, ...) form one 256-wide tile
+  int32_t* status;
+  EpiParams ep;
+};
+
+struct TcOperand {
+  const void* ptr;
+  int64_t rows;  // extent of the matrix as stored (row-major [rows, cols])
+  int64_t cols;
+  int64_t ld;
+};
+
+int sm_count();
+cudaError_t gemm_simt(const SimtOperands& o, const EpiParams& ep, int32_t in_dtype, cudaStream_t st);
+int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
+                     const TcOperand* B2, TcParams p, int block_n, cudaStream_t st, cudaError_t* cuda_err);
+int32_t launch_act_fwd(const void* pre, void* hid, int32_t dtype, int64_t rows, int64_t inter, int32_t gated,
+                       int32_t act, cudaStream_t st);
+int32_t launch_act_bwd(const void* dhid, int64_t ld_dhid, const void* pre, void* dpre, void* hid_out, int32_t dtype,
+                       int64_t rows, int64_t inter, int32_t gated, int32_t act, cudaStream_t st);
+
+}  // namespace leanffn

@@ -1,0 +1,582 @@
+// bf16 GEMM on the Blackwell tensor cores: TMA (cp.async.bulk.tensor, no multicast) stages 128-byte
+// swizzled operand tiles in shared memory, one elected thread issues tcgen05.mma with the fp32
+// accumulator in tensor memory (TMEM), and four epilogue warps read the accumulator back with
+// tcgen05.ld and apply the fused epilogue (bias / gated activation forward and backward / dropout /
+// residual) while the next tile's MMAs already run into the other TMEM accumulator stage.
+//
+// One persistent CTA per SM walks a static, M-grouped tile order.  Warp roles:
+//   warp 0       TMA producer (one elected lane)
+//   warp 1       TMEM allocation + MMA issue (one elected lane)
+//   warps 2..5   epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
+//
+// Operand majorness: a K-major operand is a [rows, K] row-major matrix (TMA box 64 K-elements x 128
+// rows); an MN-major operand is a [K, rows] row-major matrix (TMA boxes of 64 rows-elements x 64
+// K-rows, one per 64 operand rows).  Both land in the canonical 128B-swizzle UMMA layouts.
+//
+// Every mbarrier wait is bounded; a role that gives up records a code in the status word, raises a
+// CTA-wide abort flag, and all roles drain and free TMEM before returning.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+namespace leanffn {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;
+constexpr int UMMA_K = 16;
+constexpr int TC_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr uint32_t A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB
+constexpr uint32_t CHUNK_BYTES = 64 * BLOCK_K * 2;         // one MN-major 64 x 64 box, 8 KiB
+
+template <int BLOCK_N>
+struct TcConfig {
+  static constexpr uint32_t B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
+  static constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator stages
+  static constexpr uint32_t BAR_BYTES = 256;
+  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void report(int32_t* status, int32_t code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+// ---- epilogue on one 32-column run of one accumulator row --------------------------------------
+__device__ __forceinline__ void store_run_bf16(bf16* dst, const float (&v)[32], int ncols_valid) {
+  // ncols_valid is a multiple of 8
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    if (q * 8 < ncols_valid) {
+      uint4 w;
+      w.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+      w.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+      w.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+      w.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+      *reinterpret_cast<uint4*>(dst + q * 8) = w;
+    }
+  }
+}
+__device__ __forceinline__ void store_run_f32(float* dst, const float (&v)[32], int ncols_valid) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    if (q * 4 < ncols_valid)
+      *reinterpret_cast<float4*>(dst + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+}
+__device__ __forceinline__ void store_run(void* base, int32_t dtype, int64_t elem, const float (&v)[32], int nvalid) {
+  if (dtype == LEANFFN_BF16)
+    store_run_bf16(static_cast<bf16*>(base) + elem, v, nvalid);
+  else
+    store_run_f32(static_cast<float*>(base) + elem, v, nvalid);
+}
+__device__ __forceinline__ void load_run(const void* base, int32_t dtype, int64_t elem, float (&v)[32], int nvalid) {
+  if (dtype == LEANFFN_BF16) {
+    const bf16* p = static_cast<const bf16*>(base) + elem;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (q * 8 < nvalid) {
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(p + q * 8));
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u[h]);
+          v[q * 8 + 2 * h] = __low2float(b);
+          v[q * 8 + 2 * h + 1] = __high2float(b);
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 8; ++h) v[q * 8 + h] = 0.f;
+      }
+    }
+  } else {
+    const float* p = static_cast<const float*>(base) + elem;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (q * 4 < nvalid) {
+        const float4 w = __ldg(reinterpret_cast<const float4*>(p + q * 4));
+        v[q * 4] = w.x, v[q * 4 + 1] = w.y, v[q * 4 + 2] = w.z, v[q * 4 + 3] = w.w;
+      } else {
+        v[q * 4] = v[q * 4 + 1] = v[q * 4 + 2] = v[q * 4 + 3] = 0.f;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void add_bias(const EpiParams& ep, int64_t col, float (&v)[32], int nvalid) {
+  if (ep.bias == nullptr) return;
+  float b[32];
+  load_run(ep.bias, ep.bias_dtype, col, b, nvalid);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] += b[j];
+}
+__device__ __forceinline__ void as_f32(const uint32_t (&r)[32], float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+
+template <bool A_MN, bool B_MN, int BLOCK_N>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                    const TcParams p) {
+  using Cfg = TcConfig<BLOCK_N>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then tmem ptr, abort
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t abort_slot = tmem_slot + 4;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + 8u * (2 * STAGES + 4));
+  volatile uint32_t* abort_ptr = tmem_slot_ptr + 1;
+  (void)abort_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 4);
+    }
+    *abort_ptr = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    if (p.num_k2_blocks > 0) {
+      prefetch_tmap(&tmA2);
+      prefetch_tmap(&tmB2);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int kpb = p.bs_block > 0 ? p.bs_block / BLOCK_K : 1;  // k-blocks per sparse block
+  const int sub = p.bs_block > 0 ? p.bs_block / BLOCK_N : 1;  // tiles per sparse block along N (and M for wgrad)
+  // main k-blocks of a tile: fixed for dense / wgrad, per table row for block-sparse forward / dgrad
+  auto main_k_blocks = [&](int n_blk) {
+    if ((p.bs_mode == 1 || p.bs_mode == 2) && p.bs_count != nullptr) return __ldg(p.bs_count + n_blk / sub) * kpb;
+    return p.num_k_blocks;
+  };
+  const int group_size = GROUP_M * p.num_n_blocks;
+  auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
+    const int group = tile / group_size;
+    const int first_m = group * GROUP_M;
+    const int gm = min(p.num_m_blocks - first_m, GROUP_M);
+    const int in_group = tile - group * group_size;
+    m_blk = first_m + in_group % gm;
+    n_blk = in_group / gm;
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------- TMA producer --------------------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(tile, m_blk, n_blk);
+      const int kb_main = main_k_blocks(n_blk);
+      const int kb_total = kb_main + p.num_k2_blocks;
+      for (int kb = 0; kb < kb_total; ++kb) {
+        if (*abort_ptr != 0 || !mbar_wait_bounded(empty_bar(stage), phase ^ 1u)) {
+          report(p.status, LEANFFN_DEV_TIMEOUT_PRODUCER);
+          *abort_ptr = 1;
+          ok = false;
+          break;
+        }
+        const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+        const uint32_t sb = sa + A_STAGE_BYTES;
+        const uint32_t bar = full_bar(stage);
+        mbar_arrive_expect_tx(bar, Cfg::STAGE_BYTES);
+        const bool second = kb >= kb_main;
+        const CUtensorMap* ma = second ? &tmA2 : &tmA;
+        const CUtensorMap* mb = second ? &tmB2 : &tmB;
+        // coordinates (elements): a_k / b_k along the reduction axis, a_r / b_r along rows
+        int a_k, a_r, b_k, b_r;
+        if (second) {
+          const int k2 = kb - kb_main;
+          a_k = b_k = k2 * BLOCK_K;
+          a_r = m_blk * BLOCK_M;
+          b_r = n_blk * BLOCK_N;
+        } else if (p.bs_mode == 0) {
+          a_k = b_k = kb * BLOCK_K;
+          a_r = m_blk * BLOCK_M;
+          b_r = n_blk * BLOCK_N;
+        } else if (p.bs_mode == 1) {
+          // table row = output block; entry = (weight block f, input block j)
+          const int t = kb / kpb, kk = kb - t * kpb;
+          const int2 e = __ldg(reinterpret_cast<const int2*>(p.bs_index) + (n_blk / sub) * p.bs_nnz + t);
+          a_k = e.y * p.bs_block + kk * BLOCK_K;
+          a_r = m_blk * BLOCK_M;
+          b_k = kk * BLOCK_K;
+          b_r = e.x * p.bs_block + (n_blk % sub) * BLOCK_N;
+        } else if (p.bs_mode == 2) {
+          // table row = input block; entry = (weight block f, output block o); B is read MN-major
+          const int t = kb / kpb, kk = kb - t * kpb;
+          const int2 e = __ldg(reinterpret_cast<const int2*>(p.bs_index) + (n_blk / sub) * p.bs_nnz + t);
+          a_k = e.y * p.bs_block + kk * BLOCK_K;
+          a_r = m_blk * BLOCK_M;
+          b_k = e.x * p.bs_block + kk * BLOCK_K;
+          b_r = (n_blk % sub) * BLOCK_N;
+        } else {
+          // table row = weight block f; entry = (output block o, input block j)
+          const int2 e = __ldg(reinterpret_cast<const int2*>(p.bs_index) + m_blk / sub);
+          a_k = b_k = kb * BLOCK_K;
+          a_r = e.x * p.bs_block + (m_blk % sub) * BLOCK_M;
+          b_r = e.y * p.bs_block + n_blk * BLOCK_N;
+        }
+        if constexpr (A_MN) {
+#pragma unroll
+          for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sa + c * CHUNK_BYTES, ma, bar, a_r + c * 64, a_k);
+        } else {
+          tma_load_2d(sa, ma, bar, a_k, a_r);
+        }
+        if constexpr (B_MN) {
+#pragma unroll
+          for (int c = 0; c < BLOCK_N / 64; ++c) tma_load_2d(sb + c * CHUNK_BYTES, mb, bar, b_r + c * 64, b_k);
+        } else {
+          if (p.glu_split > 0) {
+            // 256-wide tile = 128 gate rows + the matching 128 linear rows of the gated weight
+            tma_load_2d(sb, mb, bar, b_k, n_blk * 128);
+            tma_load_2d(sb + 128 * BLOCK_K * 2, mb, bar, b_k, p.glu_split + n_blk * 128);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BLOCK_N / 128; ++c)
+              tma_load_2d(sb + c * 128 * BLOCK_K * 2, mb, bar, b_k, b_r + c * 128);
+          }
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------- MMA issuer ----------------------------------------------
+    constexpr uint32_t idesc = make_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
+    constexpr uint64_t a_hi = A_MN ? make_smem_desc_hi(CHUNK_BYTES, 1024) : make_smem_desc_hi(16, 1024);
+    constexpr uint64_t b_hi = B_MN ? make_smem_desc_hi(CHUNK_BYTES, 1024) : make_smem_desc_hi(16, 1024);
+    constexpr uint32_t a_kstep = A_MN ? 2048u : 32u;  // bytes per UMMA_K step inside a stage
+    constexpr uint32_t b_kstep = B_MN ? 2048u : 32u;
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc_stage = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (*abort_ptr != 0 || !mbar_wait_bounded(tempty_bar(acc_stage), acc_phase ^ 1u)) {
+        report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
+        *abort_ptr = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
+      int m_blk, n_blk;
+      tile_coords(tile, m_blk, n_blk);
+      const int kb_total = main_k_blocks(n_blk) + p.num_k2_blocks;
+      for (int kb = 0; kb < kb_total; ++kb) {
+        if (*abort_ptr != 0 || !mbar_wait_bounded(full_bar(stage), phase)) {
+          report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
+          *abort_ptr = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
+        const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+          const uint64_t da = make_smem_desc(sa + k * a_kstep, a_hi);
+          const uint64_t db = make_smem_desc(sb + k * b_kstep, b_hi);
+          umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok) break;
+      umma_commit(tfull_bar(acc_stage));  // accumulator complete
+      if (++acc_stage == 2) {
+        acc_stage = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------- epilogue ------------------------------------------------
+    const EpiParams& ep = p.ep;
+    const int quarter = warp & 3;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    int acc_stage = 0;
+    uint32_t acc_phase = 0;
+    const bool glu_fwd = ep.kind == LEANFFN_EPI_GLU_FWD;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(tile, m_blk, n_blk);
+      if (*abort_ptr != 0 || !mbar_wait_bounded(tfull_bar(acc_stage), acc_phase)) {
+        report(p.status, LEANFFN_DEV_TIMEOUT_EPILOGUE);
+        *abort_ptr = 1;
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = static_cast<int64_t>(m_blk) * BLOCK_M + quarter * 32 + lane;
+      const bool row_ok = row < ep.M;
+      const bool acc_valid = main_k_blocks(n_blk) + p.num_k2_blocks > 0;  // empty reduction: acc is all zeros
+      const uint32_t t_acc = tmem_base + lane_addr + acc_stage * BLOCK_N;
+      if (glu_fwd) {
+        // columns [0,128): gate, [128,256): linear half; output feature j = n_blk*128 + c
+        if constexpr (BLOCK_N == 256) {
+          const int inter = p.glu_split;
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 32) {
+            uint32_t rg[32], rl[32];
+            __syncwarp();
+            tmem_ld_32x32(t_acc + c, rg);
+            tmem_ld_32x32(t_acc + 128 + c, rl);
+            tmem_ld_wait();
+            const int64_t j = static_cast<int64_t>(n_blk) * 128 + c;
+            const int nvalid = static_cast<int>(inter - j < 32 ? inter - j : 32);
+            if (row_ok && nvalid > 0) {
+              float g[32], l[32], h[32];
+              as_f32(rg, g);
+              as_f32(rl, l);
+              add_bias(ep, j, g, nvalid);
+              add_bias(ep, inter + j, l, nvalid);
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                g[q] = bf16_round(g[q]);
+                l[q] = bf16_round(l[q]);
+                h[q] = bf16_round(act_fwd<true>(ep.act, g[q])) * l[q];
+              }
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + j, g, nvalid);
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + inter + j, l, nvalid);
+              store_run(ep.D2, ep.d_dtype, row * ep.ldd2 + j, h, nvalid);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N; c += 32) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(t_acc + c, r);
+          tmem_ld_wait();
+          const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + c;
+          const int nvalid = static_cast<int>(ep.N - col < 32 ? ep.N - col : 32);
+          if (!row_ok || nvalid <= 0) continue;
+          float v[32];
+          as_f32(r, v);
+          if (!acc_valid) {
+#pragma unroll
+            for (int q = 0; q < 32; ++q) v[q] = 0.f;
+          }
+          switch (ep.kind) {
+            case LEANFFN_EPI_STORE: {
+              add_bias(ep, col, v, nvalid);
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + col, v, nvalid);
+              break;
+            }
+            case LEANFFN_EPI_ACT_FWD: {
+              add_bias(ep, col, v, nvalid);
+              float h[32];
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                v[q] = bf16_round(v[q]);
+                h[q] = act_fwd<true>(ep.act, v[q]);
+              }
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + col, v, nvalid);
+              store_run(ep.D2, ep.d_dtype, row * ep.ldd2 + col, h, nvalid);
+              break;
+            }
+            case LEANFFN_EPI_DROPOUT_RESIDUAL: {
+              add_bias(ep, col, v, nvalid);
+              if (ep.threshold != 0u) {
+                const uint64_t e0 = ep.elem_offset + static_cast<uint64_t>(row) * ep.N + col;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  bool keep[4];
+                  dropout_keep4((e0 >> 2) + q, ep.seed, ep.threshold, keep);
+#pragma unroll
+                  for (int h = 0; h < 4; ++h) v[q * 4 + h] = keep[h] ? v[q * 4 + h] * ep.keep_scale : 0.f;
+                }
+              }
+              if (ep.aux != nullptr) {
+                float a[32];
+                load_run(ep.aux, ep.aux_dtype, row * ep.ldaux + col, a, nvalid);
+#pragma unroll
+                for (int q = 0; q < 32; ++q) v[q] += a[q];
+              }
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + col, v, nvalid);
+              break;
+            }
+            case LEANFFN_EPI_GLU_BWD: {
+              // v = dHid[row, col..]; aux = pre [M, 2N]; D = dPre [M, 2N]; D2 = hid [M, N] (optional)
+              float g[32], l[32], dl[32];
+              load_run(ep.aux, ep.aux_dtype, row * ep.ldaux + col, g, nvalid);
+              load_run(ep.aux, ep.aux_dtype, row * ep.ldaux + ep.N + col, l, nvalid);
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                float y, d;
+                act_fwd_bwd<true>(ep.act, g[q], y, d);
+                y = bf16_round(y);
+                dl[q] = v[q] * y;        // d/d(linear half)
+                g[q] = v[q] * l[q] * d;  // d/d(gate)
+                l[q] = y * l[q];         // rematerialised hid
+              }
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + col, g, nvalid);
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl, nvalid);
+              if (ep.D2 != nullptr) store_run(ep.D2, ep.d_dtype, row * ep.ldd2 + col, l, nvalid);
+              break;
+            }
+            case LEANFFN_EPI_ACT_BWD: {
+              float g[32], h[32];
+              load_run(ep.aux, ep.aux_dtype, row * ep.ldaux + col, g, nvalid);
+#pragma unroll
+              for (int q = 0; q < 32; ++q) {
+                float y, d;
+                act_fwd_bwd<true>(ep.act, g[q], y, d);
+                v[q] *= d;
+                h[q] = y;
+              }
+              store_run(ep.D, ep.d_dtype, row * ep.ldd + col, v, nvalid);
+              if (ep.D2 != nullptr) store_run(ep.D2, ep.d_dtype, row * ep.ldd2 + col, h, nvalid);
+              break;
+            }
+            default:
+              break;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc_stage));
+      if (++acc_stage == 2) {
+        acc_stage = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ------------------------------- teardown ------------------------------------------------------
+  __syncwarp();
+  if (*abort_ptr != 0) {
+    // let copies that may still be in flight land before shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements);
+// box = box_cols (inner, 64 elements = 128 bytes) x box_rows, 128-byte swizzle, zero fill out of bounds.
+static bool make_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_cols,
+                      uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool A_MN, bool B_MN, int BLOCK_N>
+static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2,
+                               const CUtensorMap& b2, const TcParams& p, cudaStream_t st) {
+  using Cfg = TcConfig<BLOCK_N>;
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, BLOCK_N>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, a2, b2, p);
+  return cudaGetLastError();
+}
+
+// Returns LEANFFN_OK, or a negative code when the problem does not fit the tensor-core kernel's
+// constraints (the caller then uses the SIMT kernel).
+int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
+                     const TcOperand* B2, TcParams p, int block_n, cudaStream_t st, cudaError_t* cuda_err) {
+  *cuda_err = cudaSuccess;
+  CUtensorMap ta, tb, ta2, tb2;
+  auto encode = [&](CUtensorMap* m, const TcOperand& o, bool mn) {
+    return make_tmap(m, o.ptr, o.rows, o.cols, o.ld, 64, mn ? 64 : 128);
+  };
+  if (!encode(&ta, A, a_mn) || !encode(&tb, B, b_mn)) return LEANFFN_ERR_DRIVER;
+  if (A2 != nullptr && B2 != nullptr) {
+    if (!encode(&ta2, *A2, a_mn) || !encode(&tb2, *B2, b_mn)) return LEANFFN_ERR_DRIVER;
+  } else {
+    ta2 = ta;
+    tb2 = tb;
+  }
+  cudaError_t e;
+#define TC_GO(AM, BM, BN) e = tc_launch_t<AM, BM, BN>(ta, tb, ta2, tb2, p, st)
+  if (block_n == 256) {
+    if (!a_mn && !b_mn) TC_GO(false, false, 256);
+    else if (!a_mn && b_mn) TC_GO(false, true, 256);
+    else if (a_mn && b_mn) TC_GO(true, true, 256);
+    else return LEANFFN_ERR_UNSUPPORTED;
+  } else {
+    if (!a_mn && !b_mn) TC_GO(false, false, 128);
+    else if (!a_mn && b_mn) TC_GO(false, true, 128);
+    else if (a_mn && b_mn) TC_GO(true, true, 128);
+    else return LEANFFN_ERR_UNSUPPORTED;
+  }
+#undef TC_GO
+  *cuda_err = e;
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+}
+
+}  // namespace leanffn

@@ -1,0 +1,378 @@
+"""LeanFFN on sm_100a kernels: same module API and the same memory-lean contract as the reference's
+``lean_transformer/ffn.py`` (LeanFFN :14-132, _LeanFFN :135-321).
+
+Forward: pre-LayerNorm -> input Linear (gated variants double the width) -> activation -> output Linear ->
+[post-LayerNorm] -> dropout -> + residual.  Only ``input`` and ``pre_activation`` (plus the small low-rank
+hiddens and the post-LN input when used) are kept for backward; the LayerNorm output and the activation
+are rematerialised there.  The kernel schedule in bf16 is
+
+  forward   LN kernel | GEMM1 (epilogue: bias + gated activation, writes pre_activation and hid)
+            | GEMM2 (epilogue: bias + dropout + residual)
+  backward  dropout(dY) | column sums | dgrad2 (epilogue: activation backward, writes dPre and rematerialised
+            hid) | wgrad2 | LN kernel (remat) | wgrad1 | dgrad1 | LN backward (+ residual gradient)
+
+Dropout masks are a pure function of (seed, offset, element index), so backward regenerates the forward's
+mask from two integers instead of restoring RNG state (reference: ffn.py:243-245, :308-321).
+"""
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import _native as N
+from . import ops
+from .blocksparse.linear import (GeneralizedLinear, TritonMatmulForLinearLayer, _GeneralizedLinear, _kind,
+                                 cast_cached, linear_backward_core, linear_forward_core, resolve_compute_dtype)
+from .utils import ACT2FN, resolve_activation
+
+
+def next_dropout_stream(device: torch.device, numel: int):
+    """(seed, element offset) for a dropout mask of ``numel`` elements, taken from (and advancing) torch's CUDA
+    generator of ``device`` so torch.manual_seed and torch.utils.checkpoint's RNG stashing govern it."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    gen = torch.cuda.default_generators[index]
+    seed, offset = gen.initial_seed(), gen.get_offset()
+    gen.set_offset(offset + 4 * ((numel + 15) // 16))  # offsets move in multiples of 4, one unit per 4 elements
+    return seed & 0xFFFFFFFFFFFFFFFF, 4 * offset
+
+
+class LeanFFN(nn.Module):
+    """
+    A transformer FFN module that doesn't hog your GPU memory, computed by hand-written CUDA kernels.
+
+    :param hidden_size: base hidden size of the transformer
+    :param intermediate_size: a (typically larger) hidden dimension where activation is applied
+    :param activation: a nonlinearity from ``ACT2FN`` (or an equivalent torch / transformers callable)
+    :param gated: use gated activations (https://arxiv.org/abs/2002.05202); the input projection is 2x wide
+    :param layer_norm_eps: see torch.nn.functional.layer_norm
+    :param post_layer_norm: additional layer norm on the projected outputs before dropout and the residual
+    :param dropout: hidden dropout probability, applied to the output projection (before adding residual)
+    :param residual: if True, adds the original layer input to the final layer output
+    :param ffn_custom_grad: if True (default), use the memory-lean hand-written backward
+    :param i2h_proj: custom *first* linear layer (hidden_size -> intermediate_size or 2x intermediate_size)
+    :param h2o_proj: custom *second* linear layer (intermediate_size -> hidden_size)
+    """
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation=ACT2FN["gelu_fused"],
+                 gated: bool = False, layer_norm_eps: float = 1e-12, dropout: float = 0.0,
+                 post_layer_norm: bool = False, i2h_proj: Optional[nn.Linear] = None,
+                 h2o_proj: Optional[nn.Linear] = None, residual: bool = True, ffn_custom_grad: bool = True):
+        super().__init__()
+        i2h_out_features = intermediate_size * 2 if gated else intermediate_size
+        self.i2h_proj = nn.Linear(hidden_size, i2h_out_features) if i2h_proj is None else i2h_proj
+        self.h2o_proj = nn.Linear(intermediate_size, hidden_size) if h2o_proj is None else h2o_proj
+        if ffn_custom_grad:
+            assert type(self.i2h_proj) in (nn.Linear, GeneralizedLinear), \
+                "custom grad supports only nn.Linear and GeneralizedLinear"
+            assert type(self.h2o_proj) in (nn.Linear, GeneralizedLinear), \
+                "custom grad supports only nn.Linear and GeneralizedLinear"
+        assert self.i2h_proj.in_features == self.h2o_proj.out_features == hidden_size
+        assert self.i2h_proj.out_features == i2h_out_features and self.h2o_proj.in_features == intermediate_size
+        self.pre_layer_norm = nn.LayerNorm(hidden_size, eps=layer_norm_eps)
+        self.post_layer_norm = nn.LayerNorm(hidden_size, eps=layer_norm_eps) if post_layer_norm else None
+        self.activation = activation
+        self.gated = gated
+        self.dropout = dropout
+        self.residual = residual
+        self.ffn_custom_grad = ffn_custom_grad
+        resolve_activation(activation)  # fail at construction for activations without a kernel
+
+    def forward(self, input):
+        return self._forward_custom(input) if self.ffn_custom_grad else self._forward_pytorch(input)
+
+    def _forward_pytorch(self, input):
+        """Plain-autograd twin (``ffn_custom_grad=False``): every stage is its own differentiable op and
+        keeps its own activations, like the reference's ffn.py:69-85."""
+        input_2d = input.reshape(-1, input.shape[-1])
+        ln = self.pre_layer_norm
+        input_ln = _LayerNormFunction.apply(input_2d, ln.weight, ln.bias, ln.eps)
+        pre_activation = self._apply_proj(self.i2h_proj, input_ln)
+        hid_act = _ActivationStage.apply(pre_activation, resolve_activation(self.activation), self.gated)
+        out = self._apply_proj(self.h2o_proj, hid_act)
+        if self.post_layer_norm is not None:
+            pln = self.post_layer_norm
+            out = _LayerNormFunction.apply(out, pln.weight, pln.bias, pln.eps)
+        if self.dropout and self.training:
+            out = _DropoutFunction.apply(out, self.dropout)
+        if self.residual:
+            out = out + input_2d.to(out.dtype)
+        return out.view(*input.shape)
+
+    @staticmethod
+    def _apply_proj(proj, x):
+        if isinstance(proj, GeneralizedLinear):
+            return proj(x)
+        return _GeneralizedLinear.apply(x, proj.weight, proj.bias, None, None, None, None, None)
+
+    def _forward_custom(self, input):
+        post_ln_weight = post_ln_bias = None
+        if self.post_layer_norm is not None:
+            post_ln_weight, post_ln_bias = self.post_layer_norm.weight, self.post_layer_norm.bias
+        i2h = _projection_args(self.i2h_proj)
+        h2o = _projection_args(self.h2o_proj)
+        return _LeanFFN.apply(
+            input, self.pre_layer_norm.weight, self.pre_layer_norm.bias,
+            self.i2h_proj.weight, self.i2h_proj.bias, *i2h,
+            self.h2o_proj.weight, self.h2o_proj.bias, *h2o,
+            post_ln_weight, post_ln_bias, self.activation, self.gated, self.dropout, self.training,
+            self.pre_layer_norm.eps, self.residual,
+        )
+
+
+def _projection_args(proj):
+    """(lowrank_first, lowrank_second, forward_indices, backward_indices, matmul_op) of a projection."""
+    if isinstance(proj, GeneralizedLinear):
+        first, second = proj.get_combined_lowrank_components()
+        return first, second, proj.matrix.forward_indices, proj.matrix.backward_indices, proj.matrix.matmul_op
+    return None, None, None, None, None
+
+
+class _LeanFFN(torch.autograd.Function):
+    """Autograd function for the transformer FFN with the reference's 25-argument signature."""
+
+    @staticmethod
+    def _apply_activation(pre_activation: torch.Tensor, activation, gated: bool):
+        flat = pre_activation.reshape(-1, pre_activation.shape[-1]).contiguous()
+        hid = ops.activation_forward(flat, gated, resolve_activation(activation))
+        return hid.view(*pre_activation.shape[:-1], hid.shape[-1])
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, input, ln_weight, ln_bias,
+                i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices,
+                i2h_backward_indices, i2h_matmul_op,
+                h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
+                h2o_backward_indices, h2o_matmul_op,
+                post_ln_weight, post_ln_bias, activation, gated: bool, dropout: float, training: bool,
+                ln_eps: float, residual: bool):
+        if not input.is_cuda:
+            raise RuntimeError("LeanFFN (lean_transformer_b200) needs CUDA tensors: its only implementation is "
+                               "the sm_100a kernel library; there is no CPU path")
+        act = resolve_activation(activation)
+        cdt = resolve_compute_dtype(input)
+        ctx._dropout, ctx._training, ctx._ln_eps = dropout, training, ln_eps
+        ctx._act, ctx._gated, ctx._residual, ctx._cdt = act, gated, residual, cdt
+        ctx._i2h_matmul_op, ctx._h2o_matmul_op = i2h_matmul_op, h2o_matmul_op
+        ctx._use_post_ln = post_ln_weight is not None
+        ctx._dropout_stream = None
+
+        hidden = input.shape[-1]
+        input_2d = input.reshape(-1, hidden)
+        if not input_2d.is_contiguous():
+            input_2d = input_2d.contiguous()
+        tokens = input_2d.shape[0]
+        i2h_dense = _kind(i2h_weight, i2h_forward_indices, i2h_backward_indices, i2h_matmul_op) == "dense"
+        h2o_dense = _kind(h2o_weight, h2o_forward_indices, h2o_backward_indices, h2o_matmul_op) == "dense"
+        out_features1 = i2h_bias.shape[0] if i2h_bias is not None else _out_features(
+            i2h_weight, i2h_forward_indices, i2h_matmul_op)
+        inter = out_features1 // 2 if gated else out_features1
+
+        input_ln = ops.layer_norm_forward(input_2d, ln_weight, ln_bias, ln_eps, cdt)
+
+        pre_activation = torch.empty((tokens, out_features1), dtype=cdt, device=input.device)
+        if i2h_dense:
+            hid_act = torch.empty((tokens, inter), dtype=cdt, device=input.device)
+            _, i2h_lowrank_hid = linear_forward_core(
+                input_ln, i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, None, None, None, cdt,
+                epilogue=N.EPI_GLU_FWD if gated else N.EPI_ACT_FWD, act=act, out=pre_activation, out2=hid_act)
+        else:
+            _, i2h_lowrank_hid = linear_forward_core(
+                input_ln, i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices,
+                i2h_backward_indices, i2h_matmul_op, cdt, out=pre_activation)
+            hid_act = ops.activation_forward(pre_activation, gated, act)
+        del input_ln
+
+        use_dropout = bool(training and dropout)
+        seed = offset = 0
+        if use_dropout:
+            seed, offset = next_dropout_stream(input.device, tokens * hidden)
+            ctx._dropout_stream = (seed, offset)
+        post_ln_input = None
+        if ctx._use_post_ln or not h2o_dense:
+            out, h2o_lowrank_hid = linear_forward_core(
+                hid_act, h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
+                h2o_backward_indices, h2o_matmul_op, cdt)
+            if ctx._use_post_ln:
+                post_ln_input = out
+                out = ops.layer_norm_forward(post_ln_input, post_ln_weight, post_ln_bias, ln_eps, cdt,
+                                             dropout_p=dropout if use_dropout else 0.0, seed=seed,
+                                             elem_offset=offset, residual=input_2d if residual else None)
+            elif use_dropout or residual:
+                out = _dropout_residual(out, dropout if use_dropout else 0.0, seed, offset,
+                                        input_2d if residual else None)
+        else:
+            out, h2o_lowrank_hid = linear_forward_core(
+                hid_act, h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, None, None, None, cdt,
+                epilogue=N.EPI_DROPOUT_RESIDUAL, aux=input_2d if residual else None,
+                dropout_p=dropout if use_dropout else 0.0, seed=seed, elem_offset=offset)
+        del hid_act
+
+        ctx.save_for_backward(
+            input, pre_activation, ln_weight, ln_bias, post_ln_input, post_ln_weight, post_ln_bias,
+            i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices,
+            i2h_backward_indices,
+            h2o_lowrank_hid, h2o_weight, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
+            h2o_backward_indices, i2h_bias, h2o_bias)
+        return out.view(*input.shape)
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        (input, pre_activation, ln_weight, ln_bias, post_ln_input, post_ln_weight, post_ln_bias,
+         i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices,
+         i2h_backward_indices,
+         h2o_lowrank_hid, h2o_weight, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
+         h2o_backward_indices, i2h_bias, h2o_bias) = ctx.saved_tensors
+        cdt, act, gated = ctx._cdt, ctx._act, ctx._gated
+        needs = ctx.needs_input_grad
+        hidden = input.shape[-1]
+        input_2d = input.reshape(-1, hidden)
+        if not input_2d.is_contiguous():
+            input_2d = input_2d.contiguous()
+        grad_output_2d = grad_output.reshape(-1, hidden)
+        if not grad_output_2d.is_contiguous():
+            grad_output_2d = grad_output_2d.contiguous()
+        grad_post_ln_weight = grad_post_ln_bias = None
+
+        # backward(... -> post_norm -> dropout -> residual)
+        grad_residual_2d = ops.cast(grad_output_2d, cdt) if ctx._residual else None
+        if ctx._dropout_stream is not None:
+            seed, offset = ctx._dropout_stream
+            grad_h2o_out = ops.dropout(grad_output_2d, ctx._dropout, seed, offset, out_dtype=cdt)
+        else:
+            grad_h2o_out = ops.cast(grad_output_2d, cdt)
+        if ctx._use_post_ln:
+            need_post = bool(needs[17] or needs[18])
+            grad_h2o_out, grad_post_ln_weight, grad_post_ln_bias = ops.layer_norm_backward(
+                grad_h2o_out, post_ln_input, post_ln_weight, ctx._ln_eps, None, cdt, need_param_grads=need_post)
+
+        # backward(... -> nonlinearity -> linear_h2o -> ...): dgrad2 rematerialises the activation
+        h2o_dense = _kind(h2o_weight, h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op) == "dense"
+        h2o_needs = [True, needs[10], needs[11], needs[12], needs[13]]
+        tokens = input_2d.shape[0]
+        inter = pre_activation.shape[1] // 2 if gated else pre_activation.shape[1]
+        need_hid = bool(needs[10] or needs[12])  # hid_act feeds the weight and first-low-rank gradients
+        if h2o_dense:
+            grad_pre = torch.empty_like(pre_activation)
+            hid_act = torch.empty((tokens, inter), dtype=cdt, device=input.device) if need_hid else None
+            grad_h2o_bias = ops.column_sum(grad_h2o_out) if needs[11] else None
+            grad_lowrank_hid = a2 = b2 = None
+            if h2o_lowrank_first is not None:
+                grad_lowrank_hid = ops.gemm(grad_h2o_out, cast_cached(h2o_lowrank_second, cdt), b_mn_major=True)
+                a2, b2 = grad_lowrank_hid, cast_cached(h2o_lowrank_first, cdt)
+            # the dgrad epilogue applies the activation backward and rematerialises hid_act, which the
+            # weight gradients below then consume
+            ops.gemm(grad_h2o_out, cast_cached(h2o_weight, cdt), b_mn_major=True, a2=a2, b2=b2,
+                     epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=act, aux=pre_activation,
+                     out=grad_pre, out2=hid_act)
+            grad_h2o_weight = grad_h2o_lowrank_first = grad_h2o_lowrank_second = None
+            if needs[10]:
+                grad_h2o_weight = ops.gemm(grad_h2o_out, hid_act, a_mn_major=True, b_mn_major=True,
+                                           out_dtype=h2o_weight.dtype)
+            if h2o_lowrank_first is not None and needs[13]:
+                grad_h2o_lowrank_second = ops.gemm(grad_h2o_out, h2o_lowrank_hid, a_mn_major=True, b_mn_major=True,
+                                                   out_dtype=h2o_lowrank_second.dtype)
+            if h2o_lowrank_first is not None and needs[12]:
+                grad_h2o_lowrank_first = ops.gemm(grad_lowrank_hid, hid_act, a_mn_major=True, b_mn_major=True,
+                                                  out_dtype=h2o_lowrank_first.dtype)
+        else:
+            hid_act = ops.activation_forward(pre_activation, gated, act)
+            (grad_hid_act, grad_h2o_weight, grad_h2o_bias, grad_h2o_lowrank_first,
+             grad_h2o_lowrank_second) = linear_backward_core(
+                grad_h2o_out, hid_act, h2o_lowrank_hid, h2o_weight, h2o_lowrank_first, h2o_lowrank_second,
+                h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op, h2o_needs, cdt)
+            grad_pre, _ = ops.activation_backward(grad_hid_act, pre_activation, gated, act)
+            del grad_hid_act
+        del hid_act, grad_h2o_out
+
+        # backward(... -> input_layernorm -> linear_i2h -> ...)
+        need_input_side = bool(needs[0] or needs[1] or needs[2])
+        i2h_needs = [need_input_side, needs[3], needs[4], needs[5], needs[6]]
+        input_ln = None
+        if needs[3] or needs[5]:
+            input_ln = ops.layer_norm_forward(input_2d, ln_weight, ln_bias, ctx._ln_eps, cdt)  # rematerialise
+        (grad_input_ln, grad_i2h_weight, grad_i2h_bias, grad_i2h_lowrank_first,
+         grad_i2h_lowrank_second) = linear_backward_core(
+            grad_pre, input_ln, i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second,
+            i2h_forward_indices, i2h_backward_indices, ctx._i2h_matmul_op, i2h_needs, cdt)
+        del grad_pre, input_ln
+
+        grad_input = grad_ln_weight = grad_ln_bias = None
+        if need_input_side:
+            grad_input, grad_ln_weight, grad_ln_bias = ops.layer_norm_backward(
+                grad_input_ln, input_2d, ln_weight, ctx._ln_eps, grad_residual_2d, input.dtype,
+                need_dx=bool(needs[0]), need_param_grads=bool(needs[1] or needs[2]))
+            if grad_input is not None:
+                grad_input = grad_input.view(*input.shape)
+
+        def only(flag, value):
+            return value if flag else None
+
+        return (only(needs[0], grad_input), only(needs[1], grad_ln_weight), only(needs[2], grad_ln_bias),
+                only(needs[3], grad_i2h_weight), only(needs[4], grad_i2h_bias),
+                only(needs[5], grad_i2h_lowrank_first), only(needs[6], grad_i2h_lowrank_second), None, None, None,
+                only(needs[10], grad_h2o_weight), only(needs[11], grad_h2o_bias),
+                only(needs[12], grad_h2o_lowrank_first), only(needs[13], grad_h2o_lowrank_second), None, None, None,
+                only(needs[17], grad_post_ln_weight), only(needs[18], grad_post_ln_bias),
+                None, None, None, None, None, None)
+
+
+def _out_features(weight, forward_indices, matmul_op):
+    if matmul_op is not None:
+        return matmul_op.out_features
+    if forward_indices is not None:
+        return forward_indices.shape[0] * weight.shape[-1]
+    return weight.shape[0]
+
+
+def _dropout_residual(out, p, seed, offset, residual):
+    """out = dropout(out) + residual as one elementwise kernel, for the configurations where the output GEMM
+    cannot fuse it (block-sparse output projection)."""
+    return ops.dropout(out, p, seed, offset, residual=residual)
+
+
+# ---- stages of the plain-autograd twin ---------------------------------------------------------------
+class _LayerNormFunction(torch.autograd.Function):
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, x, weight, bias, eps):
+        cdt = resolve_compute_dtype(x)
+        ctx.save_for_backward(x, weight)
+        ctx.eps, ctx.cdt = eps, cdt
+        return ops.layer_norm_forward(x.contiguous(), weight, bias, eps, cdt)
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad):
+        x, weight = ctx.saved_tensors
+        need_params = bool(ctx.needs_input_grad[1] or ctx.needs_input_grad[2])
+        dx, dg, db = ops.layer_norm_backward(ops.cast(grad.contiguous(), ctx.cdt), x.contiguous(), weight, ctx.eps,
+                                             None, x.dtype, need_dx=ctx.needs_input_grad[0],
+                                             need_param_grads=need_params)
+        return dx, dg, db, None
+
+
+class _ActivationStage(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pre, act: int, gated: bool):
+        ctx.save_for_backward(pre)
+        ctx.act, ctx.gated = act, gated
+        return ops.activation_forward(pre.contiguous(), gated, act)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (pre,) = ctx.saved_tensors
+        dpre, _ = ops.activation_backward(ops.cast(grad.contiguous(), pre.dtype), pre.contiguous(), ctx.gated, ctx.act)
+        return dpre, None, None
+
+
+class _DropoutFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p: float):
+        ctx.p = p
+        ctx.stream = next_dropout_stream(x.device, x.numel())
+        return ops.dropout(x.contiguous(), p, *ctx.stream)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return ops.dropout(grad.contiguous(), ctx.p, *ctx.stream), None

@@ -1,0 +1,245 @@
+"""Tensor-level wrappers over the C ABI: they take CUDA ``torch.Tensor``s, allocate outputs and
+scratch through torch's caching allocator, and launch on torch's current stream.  PyTorch is used for
+device memory and streams only; every computation is a kernel of ``libleanffn_b200.so``.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _native as N
+
+_DTYPES = {torch.float32: N.F32, torch.bfloat16: N.BF16}
+_status_words = {}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}: the kernels take float32 and bfloat16") from None
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "lean_transformer_b200 runs on CUDA tensors only (sm_100a kernels); got a tensor on "
+                f"{t.device}. There is no CPU path."
+            )
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def status_word(device) -> torch.Tensor:
+    """int32 device word that kernels write when a bounded wait gives up."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status_words[key]
+
+
+def check_device_status(device=None):
+    """Synchronising check of the device-side status word; raises if a kernel reported a timeout."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = status_word(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"device-side status {code}: {N.DEV_STATUS_NAMES.get(code, 'unknown')}")
+
+
+# ---- row kernels ----------------------------------------------------------------------------------
+def layer_norm_forward(x: torch.Tensor, gamma: Optional[torch.Tensor], beta: Optional[torch.Tensor], eps: float,
+                       out_dtype: torch.dtype, dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0,
+                       residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(x, gamma, beta, residual)
+    assert x.dim() == 2 and x.is_contiguous()
+    rows, cols = x.shape
+    y = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+    if gamma is not None:
+        assert gamma.is_contiguous() and gamma.numel() == cols
+        assert beta is None or (beta.dtype == gamma.dtype and beta.is_contiguous())
+    if residual is not None:
+        assert residual.shape == x.shape and residual.is_contiguous()
+    pdt = _dt(gamma) if gamma is not None else (_dt(beta) if beta is not None else N.F32)
+    N.check(N.lib.leanffn_layer_norm_forward(
+        _ptr(x), _dt(x), _ptr(gamma), _ptr(beta), pdt, _ptr(y), _dt(y), rows, cols, float(eps), float(dropout_p),
+        int(seed), int(elem_offset), _ptr(residual), _dt(residual) if residual is not None else 0, _stream(x)),
+        "leanffn_layer_norm_forward")
+    return y
+
+
+def layer_norm_backward(dy: torch.Tensor, x: torch.Tensor, gamma: Optional[torch.Tensor], eps: float,
+                        dresidual: Optional[torch.Tensor], dx_dtype: Optional[torch.dtype], need_dx: bool = True,
+                        need_param_grads: bool = True
+                        ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]:
+    _require_cuda(dy, x, gamma, dresidual)
+    assert dy.dim() == 2 and dy.is_contiguous() and x.is_contiguous() and dy.shape == x.shape
+    rows, cols = x.shape
+    dx = torch.empty((rows, cols), dtype=dx_dtype or x.dtype, device=x.device) if need_dx else None
+    dgamma = dbeta = scratch = None
+    if need_param_grads:
+        dgb = torch.empty((2, cols), dtype=torch.float32, device=x.device)
+        dgamma, dbeta = dgb[0], dgb[1]
+        nbytes = N.lib.leanffn_layer_norm_backward_scratch_bytes(rows, cols)
+        scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=x.device)
+    if dresidual is not None:
+        assert dresidual.shape == x.shape and dresidual.is_contiguous()
+    N.check(N.lib.leanffn_layer_norm_backward(
+        _ptr(dy), _dt(dy), _ptr(x), _dt(x), _ptr(gamma), _dt(gamma) if gamma is not None else N.F32,
+        _ptr(dresidual), _dt(dresidual) if dresidual is not None else 0, _ptr(dx), _dt(dx) if dx is not None else 0,
+        _ptr(dgamma), _ptr(dbeta), _ptr(scratch), rows, cols, float(eps), _stream(x)),
+        "leanffn_layer_norm_backward")
+    return dx, dgamma, dbeta
+
+
+def activation_forward(pre: torch.Tensor, gated: bool, act: int) -> torch.Tensor:
+    _require_cuda(pre)
+    assert pre.dim() == 2 and pre.is_contiguous()
+    rows = pre.shape[0]
+    inter = pre.shape[1] // 2 if gated else pre.shape[1]
+    hid = torch.empty((rows, inter), dtype=pre.dtype, device=pre.device)
+    N.check(N.lib.leanffn_activation_forward(_ptr(pre), _ptr(hid), _dt(pre), rows, inter, int(gated), act,
+                                             _stream(pre)), "leanffn_activation_forward")
+    return hid
+
+
+def activation_backward(dhid: torch.Tensor, pre: torch.Tensor, gated: bool, act: int, want_hid: bool = False):
+    _require_cuda(dhid, pre)
+    assert pre.dim() == 2 and pre.is_contiguous() and dhid.is_contiguous() and dhid.dtype == pre.dtype
+    rows = pre.shape[0]
+    inter = pre.shape[1] // 2 if gated else pre.shape[1]
+    assert dhid.shape == (rows, inter)
+    dpre = torch.empty_like(pre)
+    hid = torch.empty_like(dhid) if want_hid else None
+    N.check(N.lib.leanffn_activation_backward(_ptr(dhid), _ptr(pre), _ptr(dpre), _ptr(hid), _dt(pre), rows, inter,
+                                              int(gated), act, _stream(pre)), "leanffn_activation_backward")
+    return dpre, hid
+
+
+def dropout(x: torch.Tensor, p: float, seed: int, elem_offset: int, out_dtype: Optional[torch.dtype] = None,
+            residual: Optional[torch.Tensor] = None):
+    """y = dropout(x) [+ residual]; p == 0 makes it a cast (+ add)."""
+    _require_cuda(x, residual)
+    assert x.is_contiguous()
+    y = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    if residual is not None:
+        assert residual.is_contiguous() and residual.numel() == x.numel()
+    N.check(N.lib.leanffn_dropout(_ptr(x), _dt(x), _ptr(y), _dt(y), x.numel(), float(p), int(seed), int(elem_offset),
+                                  _ptr(residual), _dt(residual) if residual is not None else 0, _stream(x)),
+            "leanffn_dropout")
+    return y
+
+
+def dropout_mask(numel: int, p: float, seed: int, elem_offset: int, device) -> torch.Tensor:
+    mask = torch.empty(numel, dtype=torch.uint8, device=device)
+    _require_cuda(mask)
+    N.check(N.lib.leanffn_dropout_mask(_ptr(mask), numel, float(p), int(seed), int(elem_offset), _stream(mask)),
+            "leanffn_dropout_mask")
+    return mask
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    _require_cuda(x)
+    x = x.contiguous()
+    y = torch.empty(x.shape, dtype=dtype, device=x.device)
+    N.check(N.lib.leanffn_cast(_ptr(x), _dt(x), _ptr(y), _dt(y), x.numel(), _stream(x)), "leanffn_cast")
+    return y
+
+
+def column_sum(x: torch.Tensor) -> torch.Tensor:
+    _require_cuda(x)
+    assert x.dim() == 2 and x.stride(1) == 1
+    rows, cols = x.shape
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    nbytes = N.lib.leanffn_column_sum_scratch_bytes(rows, cols)
+    scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=x.device)
+    N.check(N.lib.leanffn_column_sum(_ptr(x), _dt(x), x.stride(0), _ptr(out), _ptr(scratch), rows, cols, _stream(x)),
+            "leanffn_column_sum")
+    return out
+
+
+def transpose(x: torch.Tensor) -> torch.Tensor:
+    _require_cuda(x)
+    assert x.dim() == 2 and x.stride(1) == 1
+    rows, cols = x.shape
+    y = torch.empty((cols, rows), dtype=x.dtype, device=x.device)
+    N.check(N.lib.leanffn_transpose(_ptr(x), _dt(x), x.stride(0), _ptr(y), rows, cols, _stream(x)),
+            "leanffn_transpose")
+    return y
+
+
+# ---- GEMM -----------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
+         M: Optional[int] = None, N_: Optional[int] = None, K: Optional[int] = None,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+         bias: Optional[torch.Tensor] = None, epilogue: int = N.EPI_STORE, act: int = 0,
+         out2: Optional[torch.Tensor] = None, aux: Optional[torch.Tensor] = None,
+         a2: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None,
+         dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0,
+         bs_mode: int = 0, bs_block: int = 0, bs_nnz: int = 0, bs_num_blocks: int = 0,
+         bs_index: Optional[torch.Tensor] = None, bs_count: Optional[torch.Tensor] = None,
+         force_simt: bool = False) -> torch.Tensor:
+    """D = A(m,k) . B(n,k) with the fused epilogues of ``leanffn_gemm`` (see include/leanffn_b200.h).
+
+    Dense operands are 2-D with unit inner stride: a K-major A is [M, K], an MN-major A is [K, M];
+    a K-major B is [N, K] (so D = A @ B.T), an MN-major B is [K, N].
+    """
+    _require_cuda(a, b, out, bias, out2, aux, a2, b2, bs_index, bs_count)
+    assert a.dim() == 2 and a.stride(1) == 1 and a.dtype == b.dtype
+    d = N.GemmDesc()
+    if bs_mode == 0:
+        assert b.dim() == 2 and b.stride(1) == 1
+        m, k = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
+        n, kb = (b.shape[1], b.shape[0]) if b_mn_major else b.shape
+        assert k == kb, f"reduction mismatch: {k} vs {kb}"
+        d.ldb = b.stride(0)
+    else:
+        assert b.is_contiguous() and M is not None and N_ is not None and K is not None
+        m, n, k = M, N_, K
+        assert bs_index is not None and bs_index.dtype == torch.int32 and bs_index.is_contiguous()
+        d.ldb = b.stride(0) if bs_mode == 3 else bs_block
+    d.M, d.N, d.K = int(m), int(n), int(k)
+    d.in_dtype = _dt(a)
+    d.A, d.lda = _ptr(a), a.stride(0)
+    d.B = _ptr(b)
+    d.a_mn_major, d.b_mn_major = int(a_mn_major), int(b_mn_major)
+    if a2 is not None:
+        assert b2 is not None and a2.stride(1) == 1 and b2.stride(1) == 1 and a2.dtype == a.dtype == b2.dtype
+        d.A2, d.B2, d.lda2, d.ldb2 = _ptr(a2), _ptr(b2), a2.stride(0), b2.stride(0)
+        d.K2 = a2.shape[0] if a_mn_major else a2.shape[1]
+    d.bs_mode, d.bs_block, d.bs_nnz, d.bs_num_blocks = bs_mode, bs_block, bs_nnz, bs_num_blocks
+    d.bs_index = _ptr(bs_index)
+    if bs_count is not None:
+        assert bs_count.dtype == torch.int32 and bs_count.is_contiguous()
+        d.bs_count = _ptr(bs_count)
+    d.epilogue, d.act = epilogue, act
+    if out is None:
+        cols = 2 * n if epilogue == N.EPI_GLU_BWD else n
+        out = torch.empty((m, cols), dtype=out_dtype or a.dtype, device=a.device)
+    assert out.stride(-1) == 1
+    d.D, d.ldd, d.d_dtype = _ptr(out), out.stride(0) if out.dim() == 2 else n, _dt(out)
+    if out2 is not None:
+        assert out2.dtype == out.dtype and out2.stride(1) == 1
+        d.D2, d.ldd2 = _ptr(out2), out2.stride(0)
+    if bias is not None:
+        assert bias.is_contiguous()
+        d.bias, d.bias_dtype = _ptr(bias), _dt(bias)
+    if aux is not None:
+        assert aux.stride(1) == 1
+        d.aux, d.ldaux, d.aux_dtype = _ptr(aux), aux.stride(0), _dt(aux)
+    d.dropout_p, d.seed, d.elem_offset = float(dropout_p), int(seed), int(elem_offset)
+    d.status_word = _ptr(status_word(a.device))
+    d.force_simt = int(force_simt)
+    N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
+    return out
