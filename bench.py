@@ -1,0 +1,392 @@
+"""LeanFFN forward+backward throughput (tokens/s) on 1/2/4/8 B200s.
+
+    python bench.py --gpus 1 --steps K --warmup W                  # this repository's CUDA path
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...                            # CPU baseline arm (host cores)
+
+One JSON line is printed by rank 0.  Workloads (synthetic data, random-init weights of the named shape):
+  dense_bf16_h8192   hidden 8192, intermediate 32768, GeGLU, bf16, 65536 tokens in total, no dropout; tokens are
+                     partitioned across the N ranks and weight gradients are all-reduced (default: it is the
+                     configuration the 1/2/4/8-GPU metric is quoted on and it fits one GPU)
+  mixed_bf16_h1024   hidden 1024, intermediate 4096, GeGLU, 16 x 1024 tokens per rank, fp32 parameters and
+                     residual stream with bf16 compute, dropout 0.1
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    "dense_bf16_h8192": dict(hidden=8192, inter=32768, total_tokens=65536, scaling="strong", dropout=0.0, mixed=False),
+    "mixed_bf16_h1024": dict(hidden=1024, inter=4096, tokens_per_rank=16384, scaling="weak", dropout=0.1, mixed=True),
+}
+
+
+def flops_per_token(hidden, inter):
+    return 18.0 * hidden * inter  # gated FFN: forward 6*H*I, backward 12*H*I
+
+
+def load_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return dict(bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"], hbm=d["hbm_gbs"], source="measured")
+    return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clock, reasons = [], None, set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6 or not parts[0].isdigit():
+                continue
+            clocks.append(int(parts[0]))
+            max_clock = int(parts[1]) if parts[1].isdigit() else max_clock
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return dict(sm_mhz=clocks[len(clocks) // 2] if clocks else None, sm_max_mhz=max_clock, reasons=sorted(reasons),
+                    samples=len(clocks))
+
+
+# ------------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the oracle (a CPU restatement of the reference's algorithm) on host cores
+# ------------------------------------------------------------------------------------------------------
+def cpu_step_time(hidden, inter, sample_tokens, steps, warmup, threads):
+    from oracle import leanffn_oracle as O
+
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(0)
+    rn = lambda *s: torch.randn(*s, generator=gen)  # noqa: E731
+    params = dict(ln_weight=torch.ones(hidden), ln_bias=torch.zeros(hidden), i2h_weight=0.02 * rn(2 * inter, hidden),
+                  i2h_bias=torch.zeros(2 * inter), h2o_weight=0.02 * rn(hidden, inter), h2o_bias=torch.zeros(hidden))
+    x, g = rn(sample_tokens, hidden), rn(sample_tokens, hidden)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.leanffn_step(x, g, params, gated=True)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def host_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args, wl, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    hidden, inter = wl["hidden"], wl["inter"]
+    threads = host_threads()
+    sample = 512 if hidden >= 4096 else 4096
+    step_s = cpu_step_time(hidden, inter, sample, args.steps, args.warmup, threads)
+    value = sample / step_s
+    sample_desc = (f"{sample} tokens of the {name} workload per step (fp32, GeGLU, hidden {hidden}, intermediate {inter}), "
+                   f"median of {args.steps} steps after {args.warmup} warm-up")
+    line = dict(impl="reference", metric="LeanFFN fwd+bwd tokens/sec", value=value, unit="tokens/s", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, ms_per_step=step_s * 1e3, higher_is_better=True,
+                scaling=wl["scaling"], vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=name, hidden=hidden, intermediate=inter, gated=True, sample_tokens=sample,
+                            parallelism="host cores only"),
+                cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=sample_desc),
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gflops=value * flops_per_token(hidden, inter) / 1e9)
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------
+# this repository's arm
+# ------------------------------------------------------------------------------------------------------
+def build_module(wl, device):
+    import lean_transformer_b200 as L
+
+    torch.manual_seed(0)
+    ffn = L.LeanFFN(wl["hidden"], wl["inter"], gated=True, dropout=wl["dropout"])
+    with torch.no_grad():
+        for proj in (ffn.i2h_proj, ffn.h2o_proj):
+            proj.bias.zero_()
+    ffn = ffn.to(device)
+    with torch.no_grad():  # weights ~ N(0, 0.02), generated on the device (identical on every rank: same seed)
+        gen = torch.Generator(device=device).manual_seed(0)
+        for proj in (ffn.i2h_proj, ffn.h2o_proj):
+            proj.weight.normal_(0.0, 0.02, generator=gen)
+    if not wl["mixed"]:
+        ffn = ffn.bfloat16()
+    return ffn.train()
+
+
+def run_ours(args, wl, name):
+    import torch.distributed as dist
+
+    import lean_transformer_b200 as L
+    from lean_transformer_b200 import dist as ldist
+    from lean_transformer_b200 import ffn as lffn
+    from lean_transformer_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    hidden, inter = wl["hidden"], wl["inter"]
+    if wl["scaling"] == "strong":
+        start, tokens = ldist.shard_tokens(wl["total_tokens"], world, rank)
+        total_tokens = wl["total_tokens"]
+    else:
+        tokens = wl["tokens_per_rank"]
+        total_tokens = tokens * world
+    in_dtype = torch.float32 if wl["mixed"] else torch.bfloat16
+    ffn = build_module(wl, device)
+    params = [p for p in ffn.parameters()]
+    gen = torch.Generator(device=device).manual_seed(1000 + rank)
+    x_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(in_dtype)
+    g_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(torch.bfloat16)
+    sync = ldist.GradSync(wire_dtype=torch.bfloat16) if world > 1 else None
+    if world > 1:
+        lffn.set_grad_ready_hook(sync.reduce)
+        ops.set_max_ctas(max(1, torch.cuda.get_device_properties(device).multi_processor_count - args.comm_sms))
+
+    def step(x, g):
+        for p in params:
+            p.grad = None
+        x = x.requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=wl["mixed"]):
+            out = ffn(x)
+        out.backward(g)
+        if sync is not None:
+            sync.finish()
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing (value) ---------------------------------------------------------------
+    for _ in range(args.warmup):
+        step(x_dev.detach(), g_dev)
+    L.check_device_status(device)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    launches0 = ops.launch_count
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ops.GemmTimer() as timer:
+        t_start.record()
+        for _ in range(args.steps):
+            step(x_dev.detach(), g_dev)
+        t_end.record()
+        barrier()
+    elapsed = torch.tensor([t_start.elapsed_time(t_end) * 1e-3], device=device, dtype=torch.float64)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = ops.launch_count - launches0
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    seconds = float(elapsed.item())
+    gemm_flops, gemm_seconds, gemm_launches = timer.summary()
+    L.check_device_status(device)
+
+    # ---- end-to-end through the module API with host buffers (e2e) --------------------------------------
+    x_host = x_dev.detach().cpu().pin_memory()
+    g_host = g_dev.cpu().pin_memory()
+    copy_stream = torch.cuda.Stream(device)
+    bufs = [(torch.empty_like(x_dev), torch.empty_like(g_dev)) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def upload(i):
+        slot = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[slot])
+            bufs[slot][0].copy_(x_host, non_blocking=True)
+            bufs[slot][1].copy_(g_host, non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    def e2e_loop(n):
+        losses = []
+        main = torch.cuda.current_stream(device)
+        for slot in range(2):
+            consumed[slot].record(main)
+        upload(0)
+        for i in range(n):
+            slot = i % 2
+            if i + 1 < n:
+                upload(i + 1)  # the next step's inputs cross PCIe while this step computes
+            main.wait_event(ready[slot])
+            xb, gb = bufs[slot]
+            out = step(xb.detach(), gb)
+            loss = torch.dot(out.detach().reshape(-1), gb.reshape(-1))  # loss = sum(out * g)
+            consumed[slot].record(main)
+            losses.append(float(loss.item()))  # device -> host read of the step's result
+        return losses
+
+    e2e_loop(min(2, args.warmup))
+    barrier()
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    losses = e2e_loop(args.steps)
+    e_end.record()
+    barrier()
+    e_elapsed = torch.tensor([e_start.elapsed_time(e_end) * 1e-3], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e_elapsed, op=dist.ReduceOp.MAX)
+    e_seconds = float(e_elapsed.item())
+    L.check_device_status(device)
+
+    extra = {}
+    if rank == 0 and world == 1 and args.extra_workload and args.extra_workload != name:
+        extra[args.extra_workload] = quick_measure(WORKLOADS[args.extra_workload], device, args)
+
+    if world > 1:
+        lffn.set_grad_ready_hook(None)
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    peaks = load_peaks()
+    tokens_per_s = total_tokens * args.steps / seconds
+    tflops = tokens_per_s * flops_per_token(hidden, inter) / 1e12
+    achieved = gemm_flops / gemm_seconds / 1e12 if gemm_seconds > 0 else None
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        threads = host_threads()
+        sample = 512 if hidden >= 4096 else 4096
+        cpu_s = cpu_step_time(hidden, inter, sample, 3, 1, threads)
+        cpu = dict(value=sample / cpu_s, unit="tokens/s", cores=threads, kind="port",
+                   sample=f"{sample} tokens of the {name} workload per step in fp32 on the host cores "
+                          f"(CPU restatement of the reference's LeanFFN), median of 3 steps after 1 warm-up")
+    line = dict(
+        metric="LeanFFN fwd+bwd tokens/sec", value=tokens_per_s, unit="tokens/s", n_gpus=world, steps=args.steps,
+        warmup=args.warmup, ms_per_step=seconds / args.steps * 1e3, higher_is_better=True, scaling=wl["scaling"],
+        vs_baseline=None, dtype="bf16", data="synthetic",
+        config=dict(workload=name, hidden=hidden, intermediate=inter, gated=True, activation="gelu_fused",
+                    dropout=wl["dropout"], total_tokens=total_tokens, tokens_per_gpu=tokens,
+                    parameters="fp32 masters + bf16 compute (autocast)" if wl["mixed"] else "bf16",
+                    parallelism=f"dp{world} token partition" + (", bf16 gradient all-reduce overlapped with backward"
+                                                                 if world > 1 else ""),
+                    l2="inputs and activations exceed the 126 MB L2 (no flush needed)",
+                    step="forward + backward" + (" + gradient all-reduce" if world > 1 else "")),
+        tflops=tflops, pct_of_bf16_peak_measured_burst=100.0 * tflops / world / peaks["bf16"],
+        pct_of_bf16_peak_datasheet=100.0 * tflops / world / 2250.0,
+        roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
+                      frac=(achieved / peaks["bf16_sustained"]) if achieved else None, traffic=None,
+                      kernel="gemm_tcgen05_kernel (all GEMM launches of the timed region)", launches=gemm_launches,
+                      peak_source=f"bf16_tflops_sustained of {peaks['source']} peaks (kernel timed inside a long step)"),
+        cpu_baseline=cpu,
+        e2e=dict(value=total_tokens * args.steps / e_seconds, unit="tokens/s",
+                 h2d_bytes_per_step=(x_host.numel() * x_host.element_size() + g_host.numel() * g_host.element_size()) * world,
+                 d2h_bytes_per_step=2 * world, ms_per_step=e_seconds / args.steps * 1e3,
+                 api="LeanFFN.forward / Tensor.backward with pinned host inputs, double-buffered uploads",
+                 last_loss=losses[-1] if losses else None),
+        gpu_launches=launches, clocks=clocks)
+    if extra:
+        line["other_workloads"] = extra
+    print(json.dumps(line), flush=True)
+
+
+def quick_measure(wl, device, args):
+    """Device-resident fwd+bwd rate of a second workload on one GPU (reported next to the headline)."""
+    import lean_transformer_b200 as L
+
+    ffn = build_module(wl, device)
+    tokens, hidden = wl.get("tokens_per_rank") or wl["total_tokens"], wl["hidden"]
+    x = torch.randn(tokens, hidden, device=device).to(torch.float32 if wl["mixed"] else torch.bfloat16)
+    g = torch.randn(tokens, hidden, device=device).to(torch.bfloat16)
+    params = list(ffn.parameters())
+
+    def step():
+        for p in params:
+            p.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=wl["mixed"]):
+            out = ffn(x.detach().requires_grad_(True))
+        out.backward(g)
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    n = 50
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    L.check_device_status(device)
+    s = a.elapsed_time(b) * 1e-3 / n
+    return dict(tokens_per_s=tokens / s, ms_per_step=s * 1e3, tflops=tokens / s * flops_per_token(hidden, wl["inter"]) / 1e12,
+                config=dict(hidden=hidden, intermediate=wl["inter"], tokens=tokens, dropout=wl["dropout"],
+                            parameters="fp32 masters + bf16 compute" if wl["mixed"] else "bf16"))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="dense_bf16_h8192")
+    ap.add_argument("--extra-workload", default="mixed_bf16_h1024")
+    ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to NCCL while GEMMs run (N > 1)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, wl, args.workload)
+    else:
+        run_ours(args, wl, args.workload)
+
+
+if __name__ == "__main__":
+    main()

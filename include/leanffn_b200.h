@@ -211,6 +211,8 @@ typedef struct leanffn_gemm_desc {
   uint64_t elem_offset; /* element index of D[0,0] in the logical dropout stream */
   int32_t* status_word; /* device int32 or NULL */
   int32_t force_simt;   /* != 0: run the SIMT kernel whatever the dtype (checker / odd shapes) */
+  int32_t max_ctas;     /* > 0: cap on the persistent grid of the tensor-core kernel (leave SMs to a
+                           concurrently running collective); 0 = one CTA per SM */
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);

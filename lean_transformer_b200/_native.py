@@ -34,7 +34,7 @@ class GemmDesc(ctypes.Structure):
         ("bias", c_void_p), ("bias_dtype", c_int32),
         ("aux", c_void_p), ("ldaux", c_int64), ("aux_dtype", c_int32),
         ("dropout_p", c_float), ("seed", c_uint64), ("elem_offset", c_uint64),
-        ("status_word", c_void_p), ("force_simt", c_int32),
+        ("status_word", c_void_p), ("force_simt", c_int32), ("max_ctas", c_int32),
     ]
 
 

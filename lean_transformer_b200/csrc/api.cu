@@ -118,6 +118,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     p.bs_index = d->bs_index;
     p.bs_count = d->bs_count;
     p.glu_split = 0;
+    p.max_ctas = d->max_ctas;
     int block_n = (d->bs_mode != 0 || d->N <= 128) ? 128 : 256;
     int64_t n_tiles_n;
     if (epi == LEANFFN_EPI_GLU_FWD) {

@@ -76,6 +76,7 @@ struct TcParams {
   const int32_t* bs_index;  // int32 pairs, see include/leanffn_b200.h
   const int32_t* bs_count;  // entries per table row, or nullptr
   int32_t glu_split;  // > 0: B rows [n, n+128) and [glu_split + n, ...) form one 256-wide tile
+  int32_t max_ctas;   // > 0: cap on the persistent grid
   int32_t* status;
   EpiParams ep;
 };

@@ -540,7 +540,8 @@ static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const
     configured[dev] = true;
   }
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   kern<<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, a2, b2, p);
   return cudaGetLastError();
 }

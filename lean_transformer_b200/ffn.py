@@ -26,6 +26,27 @@ from .blocksparse.linear import (GeneralizedLinear, TritonMatmulForLinearLayer, 
 from .utils import ACT2FN, resolve_activation
 
 
+# Optional callback ``fn(name, grad)`` invoked inside the backward as soon as a parameter gradient exists
+# (names: "h2o_weight", "h2o_bias", "i2h_weight", ...).  A data-parallel trainer uses it to start the
+# all-reduce of the output projection's gradients while the input projection's are still being computed
+# (see lean_transformer_b200.dist.GradSync); autograd hooks would only fire after the whole backward.
+_grad_ready_hook = None
+
+
+def set_grad_ready_hook(fn):
+    """Install (or clear, with None) the gradient-ready callback; returns the previous one."""
+    global _grad_ready_hook
+    previous, _grad_ready_hook = _grad_ready_hook, fn
+    return previous
+
+
+def _notify(**grads):
+    if _grad_ready_hook is not None:
+        for name, grad in grads.items():
+            if grad is not None:
+                _grad_ready_hook(name, grad)
+
+
 def next_dropout_stream(device: torch.device, numel: int):
     """(seed, element offset) for a dropout mask of ``numel`` elements, taken from (and advancing) torch's CUDA
     generator of ``device`` so torch.manual_seed and torch.utils.checkpoint's RNG stashing govern it."""
@@ -284,6 +305,10 @@ class _LeanFFN(torch.autograd.Function):
             grad_pre, _ = ops.activation_backward(grad_hid_act, pre_activation, gated, act)
             del grad_hid_act
         del hid_act, grad_h2o_out
+        _notify(h2o_weight=only_if(needs[10], grad_h2o_weight), h2o_bias=only_if(needs[11], grad_h2o_bias),
+                h2o_lowrank_first=only_if(needs[12], grad_h2o_lowrank_first),
+                h2o_lowrank_second=only_if(needs[13], grad_h2o_lowrank_second),
+                post_ln_weight=grad_post_ln_weight, post_ln_bias=grad_post_ln_bias)
 
         # backward(... -> input_layernorm -> linear_i2h -> ...)
         need_input_side = bool(needs[0] or needs[1] or needs[2])
@@ -296,6 +321,8 @@ class _LeanFFN(torch.autograd.Function):
             grad_pre, input_ln, i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second,
             i2h_forward_indices, i2h_backward_indices, ctx._i2h_matmul_op, i2h_needs, cdt)
         del grad_pre, input_ln
+        _notify(i2h_weight=grad_i2h_weight, i2h_bias=grad_i2h_bias, i2h_lowrank_first=grad_i2h_lowrank_first,
+                i2h_lowrank_second=grad_i2h_lowrank_second)
 
         grad_input = grad_ln_weight = grad_ln_bias = None
         if need_input_side:
@@ -304,9 +331,8 @@ class _LeanFFN(torch.autograd.Function):
                 need_dx=bool(needs[0]), need_param_grads=bool(needs[1] or needs[2]))
             if grad_input is not None:
                 grad_input = grad_input.view(*input.shape)
-
-        def only(flag, value):
-            return value if flag else None
+            _notify(ln_weight=grad_ln_weight, ln_bias=grad_ln_bias)
+        only = only_if
 
         return (only(needs[0], grad_input), only(needs[1], grad_ln_weight), only(needs[2], grad_ln_bias),
                 only(needs[3], grad_i2h_weight), only(needs[4], grad_i2h_bias),
@@ -315,6 +341,10 @@ class _LeanFFN(torch.autograd.Function):
                 only(needs[12], grad_h2o_lowrank_first), only(needs[13], grad_h2o_lowrank_second), None, None, None,
                 only(needs[17], grad_post_ln_weight), only(needs[18], grad_post_ln_bias),
                 None, None, None, None, None, None)
+
+
+def only_if(flag, value):
+    return value if flag else None
 
 
 def _out_features(weight, forward_indices, matmul_op):

@@ -11,6 +11,42 @@ from . import _native as N
 _DTYPES = {torch.float32: N.F32, torch.bfloat16: N.BF16}
 _status_words = {}
 
+# Bookkeeping for benchmarks: kernels launched by this package, an optional per-GEMM CUDA-event timer and the
+# persistent-grid cap used while a collective shares the GPU.
+launch_count = 0
+_gemm_timer = None
+_max_ctas = 0
+
+
+def set_max_ctas(n: int):
+    """Cap the tensor-core GEMM's persistent grid at ``n`` CTAs (0 = one per SM)."""
+    global _max_ctas
+    _max_ctas = int(n)
+
+
+class GemmTimer:
+    """Records a CUDA-event pair around every GEMM launch on the launching stream, with the launch's
+    algorithmic FLOPs (2 * M * N * K_effective), so a benchmark can report the kernel's achieved rate."""
+
+    def __init__(self):
+        self.records = []
+
+    def __enter__(self):
+        global _gemm_timer
+        _gemm_timer = self
+        return self
+
+    def __exit__(self, *exc):
+        global _gemm_timer
+        _gemm_timer = None
+
+    def summary(self):
+        """(total_flops, total_seconds, launches) after a device synchronisation."""
+        flops = sum(r[2] for r in self.records)
+        seconds = sum(r[0].elapsed_time(r[1]) for r in self.records) * 1e-3
+        return flops, seconds, len(self.records)
+
+
 
 def _dt(t: torch.Tensor) -> int:
     try:
@@ -26,6 +62,11 @@ def _require_cuda(*tensors):
                 "lean_transformer_b200 runs on CUDA tensors only (sm_100a kernels); got a tensor on "
                 f"{t.device}. There is no CPU path."
             )
+
+
+def _count(n: int = 1):
+    global launch_count
+    launch_count += n
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -74,6 +115,7 @@ def layer_norm_forward(x: torch.Tensor, gamma: Optional[torch.Tensor], beta: Opt
         _ptr(x), _dt(x), _ptr(gamma), _ptr(beta), pdt, _ptr(y), _dt(y), rows, cols, float(eps), float(dropout_p),
         int(seed), int(elem_offset), _ptr(residual), _dt(residual) if residual is not None else 0, _stream(x)),
         "leanffn_layer_norm_forward")
+    _count()
     return y
 
 
@@ -98,6 +140,7 @@ def layer_norm_backward(dy: torch.Tensor, x: torch.Tensor, gamma: Optional[torch
         _ptr(dresidual), _dt(dresidual) if dresidual is not None else 0, _ptr(dx), _dt(dx) if dx is not None else 0,
         _ptr(dgamma), _ptr(dbeta), _ptr(scratch), rows, cols, float(eps), _stream(x)),
         "leanffn_layer_norm_backward")
+    _count(3 if need_param_grads else 1)
     return dx, dgamma, dbeta
 
 
@@ -109,6 +152,7 @@ def activation_forward(pre: torch.Tensor, gated: bool, act: int) -> torch.Tensor
     hid = torch.empty((rows, inter), dtype=pre.dtype, device=pre.device)
     N.check(N.lib.leanffn_activation_forward(_ptr(pre), _ptr(hid), _dt(pre), rows, inter, int(gated), act,
                                              _stream(pre)), "leanffn_activation_forward")
+    _count()
     return hid
 
 
@@ -122,6 +166,7 @@ def activation_backward(dhid: torch.Tensor, pre: torch.Tensor, gated: bool, act:
     hid = torch.empty_like(dhid) if want_hid else None
     N.check(N.lib.leanffn_activation_backward(_ptr(dhid), _ptr(pre), _ptr(dpre), _ptr(hid), _dt(pre), rows, inter,
                                               int(gated), act, _stream(pre)), "leanffn_activation_backward")
+    _count()
     return dpre, hid
 
 
@@ -136,6 +181,7 @@ def dropout(x: torch.Tensor, p: float, seed: int, elem_offset: int, out_dtype: O
     N.check(N.lib.leanffn_dropout(_ptr(x), _dt(x), _ptr(y), _dt(y), x.numel(), float(p), int(seed), int(elem_offset),
                                   _ptr(residual), _dt(residual) if residual is not None else 0, _stream(x)),
             "leanffn_dropout")
+    _count()
     return y
 
 
@@ -154,6 +200,7 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     x = x.contiguous()
     y = torch.empty(x.shape, dtype=dtype, device=x.device)
     N.check(N.lib.leanffn_cast(_ptr(x), _dt(x), _ptr(y), _dt(y), x.numel(), _stream(x)), "leanffn_cast")
+    _count()
     return y
 
 
@@ -166,6 +213,7 @@ def column_sum(x: torch.Tensor) -> torch.Tensor:
     scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=x.device)
     N.check(N.lib.leanffn_column_sum(_ptr(x), _dt(x), x.stride(0), _ptr(out), _ptr(scratch), rows, cols, _stream(x)),
             "leanffn_column_sum")
+    _count(2)
     return out
 
 
@@ -241,5 +289,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     d.dropout_p, d.seed, d.elem_offset = float(dropout_p), int(seed), int(elem_offset)
     d.status_word = _ptr(status_word(a.device))
     d.force_simt = int(force_simt)
+    d.max_ctas = _max_ctas
+    global launch_count
+    launch_count += 1
+    if _gemm_timer is not None:
+        k_eff = bs_nnz * bs_block if bs_mode in (1, 2) else k
+        flops = 2.0 * m * n * (k_eff + (d.K2 or 0))
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
+        end.record()
+        _gemm_timer.records.append((start, end, flops))
+        return out
     N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
     return out

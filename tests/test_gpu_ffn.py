@@ -1,0 +1,281 @@
+"""LeanFFN / GeneralizedLinear through the public module API against the CPU oracle (needs a B200).
+
+Tolerances: fp32 mode rtol = atol = 1e-4; bf16 mode rtol 2e-2 / atol 1e-2.  Outputs and input gradients are
+checked elementwise with exactly those numbers.  Parameter gradients are sums over all tokens; for them the
+absolute floor is scaled by the gradient tensor's RMS (see conftest.assert_close), because the rounding noise
+of a sum of thousands of bf16 products does not shrink for the elements that happen to cancel to ~0.
+"""
+import pytest
+import torch
+
+from conftest import (BF16_ATOL, BF16_RTOL, FP32_ATOL, FP32_RTOL, assert_close, golden_ffn_case, load_golden)
+from helpers import make_ffn, random_params, run_step
+from oracle import leanffn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None):
+    assert_close(out, ref_out, rtol, atol, "out")
+    assert_close(grads["input"], ref_grads["input"], rtol, atol, "grad_input")
+    n = 0
+    for key, ref in ref_grads.items():
+        if key == "input" or ref is None:
+            continue
+        assert grads.get(key) is not None, f"no gradient for {key}"
+        assert_close(grads[key], ref, param_rtol or rtol, atol, f"grad_{key}", scale_atol=True)
+        n += 1
+    return n
+
+
+# ---- golden vectors produced by the reference -----------------------------------------------------
+@pytest.mark.parametrize("name", ["ffn_dense_plain", "ffn_gated_postln", "ffn_pixelfly_lowrank"])
+@pytest.mark.parametrize("custom_grad", [True, False])
+def test_golden_fp32(cuda_device, name, custom_grad):
+    x, g, params, expected, meta = golden_ffn_case(name, dtype=torch.float32)
+    ffn = make_ffn(params, gated=bool(meta["gated"]), residual=bool(meta["residual"]), custom_grad=custom_grad)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device))
+    ref = {k: v for k, v in expected.items() if k != "out"}
+    assert _check(out, grads, expected["out"], ref, FP32_RTOL, FP32_ATOL) >= 6
+
+
+def test_golden_dropout_mask_fp32(cuda_device):
+    """The reference run with the Philox mask injected: our kernels regenerate that mask from (seed, offset)."""
+    x, g, params, expected, meta = golden_ffn_case("ffn_dropout_mask", dtype=torch.float32)
+    ffn = make_ffn(params, gated=True, dropout=meta["dropout"]).train()
+    gen = torch.cuda.default_generators[cuda_device.index]
+    gen.manual_seed(meta["seed"])
+    gen.set_offset(meta["offset"] // 4)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device))
+    ref = {k: v for k, v in expected.items() if k != "out"}
+    _check(out, grads, expected["out"], ref, FP32_RTOL, FP32_ATOL)
+    assert gen.get_offset() > meta["offset"] // 4  # the stream advanced
+
+
+# ---- seeded configurations against the oracle ------------------------------------------------------
+@pytest.mark.parametrize("hidden,inter,gated,post_ln,residual,act", [
+    (32, 128, False, False, True, "gelu_fused"), (64, 96, True, True, False, "silu"),
+    (100, 60, True, False, True, "relu"), (256, 512, False, True, True, "gelu"),
+    (768, 3072, True, False, True, "gelu_fused")])
+def test_fp32_mode_vs_oracle(cuda_device, hidden, inter, gated, post_ln, residual, act):
+    tokens = 4096 if hidden == 768 else 515  # config 1 at full size: 8 x 512 tokens, eps 1e-12
+    params = random_params(hidden, inter, gated, seed=0, post_ln=post_ln, bias_std=0.0 if hidden == 768 else 0.1)
+    torch.manual_seed(0)
+    x, g = torch.randn(tokens, hidden), torch.randn(tokens, hidden)
+    names = {"gelu_fused": "gelu_tanh", "gelu": "gelu_erf"}
+    kw = dict(activation=names.get(act, act), gated=gated, residual=residual)
+    p64 = {k: v.double() for k, v in params.items()}
+    ref_out, ref_grads = O.leanffn_step(x.double(), g.double(), p64, **kw)
+    ffn = make_ffn(params, gated=gated, residual=residual, activation=act)
+    out, grads = run_step(ffn, x.view(1, tokens, hidden).to(cuda_device), g.view(1, tokens, hidden).to(cuda_device))
+    _check(out.view(tokens, hidden), {k: (v.view(tokens, hidden) if k == "input" else v) for k, v in grads.items()},
+           ref_out, ref_grads, FP32_RTOL, FP32_ATOL)
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,p", [(16384, 1024, 4096, 0.1), (1000, 512, 1024, 0.0), (2048, 768, 3072, 0.0)])
+def test_bf16_autocast_vs_oracle(cuda_device, tokens, hidden, inter, p):
+    """Config 2 at full size (16 x 1024 tokens, hidden 1024, GeGLU, dropout 0.1 with the seeded Philox mask):
+    fp32 parameters and residual stream, bf16 tensor-core compute, against the fp32 oracle with the same mask."""
+    params = random_params(hidden, inter, True, seed=0)
+    torch.manual_seed(0)
+    x, g = torch.randn(tokens, hidden), torch.randn(tokens, hidden)
+    seed, offset = 0, 0
+    keep = torch.from_numpy(O.dropout_keep_mask(tokens * hidden, p, seed, offset)).view(tokens, hidden) if p else None
+    ref_out, ref_grads = O.leanffn_step(x, g, params, gated=True, dropout_p=p, keep_mask=keep)
+    ffn = make_ffn(params, gated=True, dropout=p).train()
+    gen = torch.cuda.default_generators[cuda_device.index]
+    gen.manual_seed(seed)
+    gen.set_offset(offset)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device), autocast=True)
+    assert out.dtype == torch.bfloat16 and grads["input"].dtype == torch.float32
+    assert grads["i2h_weight"].dtype == torch.float32
+    _check(out, grads, ref_out, ref_grads, BF16_RTOL, BF16_ATOL)
+
+
+def test_pure_bf16_model_vs_oracle(cuda_device):
+    params = random_params(512, 1024, True, seed=3, bias_std=0.05)
+    torch.manual_seed(3)
+    x, g = torch.randn(700, 512).bfloat16(), torch.randn(700, 512).bfloat16()
+    p_b = {k: v.bfloat16() for k, v in params.items()}
+    ref_out, ref_grads = O.leanffn_step(x.float(), g.float(), {k: v.float() for k, v in p_b.items()}, gated=True)
+    ffn = make_ffn(p_b, gated=True, dtype=torch.bfloat16)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device))
+    _check(out, grads, ref_out, ref_grads, BF16_RTOL, BF16_ATOL)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, "autocast"])
+def test_pixelfly_lowrank_ffn_vs_oracle(cuda_device, dtype):
+    """Config 3 at reduced token count: both projections block-sparse (pixelfly, block 128) with a rank-128
+    low-rank term, GeGLU.  Widths are scaled down 4x for the fp32 run so the CPU oracle stays in seconds."""
+    from lean_transformer_b200.blocksparse import layout as LY
+    hidden, inter, tokens, bs, rank = (1024, 4096, 384, 128, 128) if dtype == "autocast" else (512, 1024, 200, 64, 16)
+    gen = torch.Generator().manual_seed(0)
+    rn = lambda *s: torch.randn(*s, generator=gen)  # noqa: E731
+    params = dict(ln_weight=1 + 0.1 * rn(hidden), ln_bias=0.1 * rn(hidden))
+    for prefix, fin, fout in (("i2h", hidden, 2 * inter), ("h2o", inter, hidden)):
+        fwd, bwd = LY.get_indices_from_layout(LY.get_blocksparse_layout(fout, fin, f"pixelfly(block_size={bs})"))
+        params.update({f"{prefix}_weight": 0.02 * rn(fin, bwd.shape[1], bs), f"{prefix}_bias": 0.02 * rn(fout),
+                       f"{prefix}_lowrank_first": 0.02 * rn(rank, fin), f"{prefix}_lowrank_second": 0.02 * rn(fout, rank),
+                       f"{prefix}_forward_indices": fwd, f"{prefix}_backward_indices": bwd})
+    x, g = rn(tokens, hidden), rn(tokens, hidden)
+    ref_out, ref_grads = O.leanffn_step(x.double(), g.double(),
+                                        {k: (v.double() if v.is_floating_point() else v) for k, v in params.items()},
+                                        gated=True)
+    ffn = make_ffn(params, gated=True)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device), autocast=dtype == "autocast")
+    rtol, atol = (BF16_RTOL, BF16_ATOL) if dtype == "autocast" else (FP32_RTOL, FP32_ATOL)
+    assert _check(out, grads, ref_out, ref_grads, rtol, atol) >= 10
+
+
+# ---- behaviours the reference's own tests pin --------------------------------------------------------
+def test_stacked_layers_and_custom_vs_plain_autograd(cuda_device):
+    """tests/test_ffn.py pattern: the same module applied 4 times; custom backward == plain-autograd twin."""
+    torch.manual_seed(0)
+    params = random_params(32, 128, True, seed=1, std=0.2, post_ln=True, bias_std=0.1)
+    custom = make_ffn(params, gated=True, custom_grad=True)
+    plain = make_ffn(params, gated=True, custom_grad=False)
+    x = torch.rand(4, 128, 32, device=cuda_device)
+    results = []
+    for ffn in (custom, plain):
+        inp = x.clone().requires_grad_()
+        out = inp
+        for _ in range(4):
+            out = ffn(out)
+        obj = (out * (out + 1)).square().mean()
+        grads = torch.autograd.grad(obj, [inp] + list(ffn.parameters()))
+        results.append((out, grads))
+    assert_close(results[0][0], results[1][0], 1e-5, 1e-6, "stacked out")
+    for a, b in zip(results[0][1], results[1][1]):
+        assert_close(a, b, 1e-4, 1e-5, "stacked grads")
+    # and against the oracle applied four times
+    p64 = {k: v.double() for k, v in params.items()}
+    ref = x.double().cpu()
+    for _ in range(4):
+        ref, _ = O.leanffn_forward(ref, p64, gated=True)
+    assert_close(results[0][0], ref, FP32_RTOL, FP32_ATOL, "stacked out vs oracle")
+
+
+def test_dropout_semantics(cuda_device):
+    """tests/test_ffn.py::test_ffn_dropout: two runs agree iff dropout == 0; plus: backward reuses the forward's
+    mask, eval mode disables dropout, and reseeding reproduces the run."""
+    torch.manual_seed(0)
+    x = torch.rand(4, 128, 32, device=cuda_device, requires_grad=True)
+    for p in (0.0, 0.5):
+        ffn = make_ffn(random_params(32, 128, True, seed=2, std=0.2, post_ln=True), gated=True, dropout=p).train()
+        runs = []
+        for _ in range(2):
+            out = x
+            for _ in range(4):
+                out = ffn(out)
+            (g,) = torch.autograd.grad(out.norm(), x)
+            runs.append((out.detach(), g))
+        same = torch.allclose(runs[0][0], runs[1][0], rtol=1e-3, atol=1e-5)
+        assert same == (p == 0) and torch.allclose(runs[0][1], runs[1][1], rtol=1e-3, atol=1e-5) == (p == 0)
+    torch.manual_seed(123)
+    a = ffn(x).detach()
+    torch.manual_seed(123)
+    b = ffn(x).detach()
+    assert torch.equal(a, b)
+    ffn.eval()
+    assert torch.equal(ffn(x), ffn(x))
+    # gradient w.r.t. the output projection bias is exactly the (masked, rescaled) upstream gradient summed
+    ffn = make_ffn(random_params(32, 128, False, seed=2), gated=False, dropout=0.5, residual=False).train()
+    out = ffn(x.detach())
+    out.sum().backward()
+    kept = (out.detach().reshape(-1, 32) != 0).float()  # dropped entries are exactly 0 (no residual)
+    assert_close(ffn.h2o_proj.bias.grad, kept.sum(0) * 2.0, 1e-5, 1e-5, "mask reused in backward")
+
+
+def test_gradient_checkpointing_recomputes_same_mask(cuda_device):
+    from torch.utils.checkpoint import checkpoint
+    torch.manual_seed(5)
+    ffn = make_ffn(random_params(64, 128, True, seed=5, std=0.2), gated=True, dropout=0.3).train()
+    x = torch.randn(2, 50, 64, device=cuda_device, requires_grad=True)
+    torch.manual_seed(9)
+    out = ffn(x)
+    (g_plain,) = torch.autograd.grad(out.square().sum(), x)
+    torch.manual_seed(9)
+    out_ck = checkpoint(ffn, x, use_reentrant=False, preserve_rng_state=True)
+    (g_ck,) = torch.autograd.grad(out_ck.square().sum(), x)
+    assert torch.equal(out, out_ck) and torch.equal(g_plain, g_ck)
+
+
+def test_run_to_run_determinism_and_needs_input_grad(cuda_device):
+    params = random_params(512, 1024, True, seed=7)
+    ffn = make_ffn(params, gated=True)
+    torch.manual_seed(7)
+    x, g = torch.randn(1000, 512, device=cuda_device), torch.randn(1000, 512, device=cuda_device)
+    o1, g1 = run_step(ffn, x, g, autocast=True)
+    o2, g2 = run_step(ffn, x, g, autocast=True)
+    assert torch.equal(o1, o2) and all(torch.equal(g1[k], g2[k]) for k in g1)
+    # frozen parameters and a non-differentiable input get no gradient and do not break the backward
+    for p in ffn.i2h_proj.parameters():
+        p.requires_grad_(False)
+    ffn.zero_grad(set_to_none=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ffn(x).float().sum().backward()
+    assert ffn.i2h_proj.weight.grad is None and ffn.h2o_proj.weight.grad is not None
+
+
+def test_generalized_linear_golden_and_variants(cuda_device):
+    """tests/test_linear.py: reference outputs for pixelfly(8) + shared low rank + adapter, fp32 mode."""
+    from lean_transformer_b200.blocksparse.linear import GeneralizedLinear, GeneralizedMatrix, _GeneralizedLinear
+    b = {k: torch.from_numpy(v) for k, v in load_golden("linear_pixelfly_lowrank").items()}
+    lin = GeneralizedLinear(GeneralizedMatrix(64, 64, "pixelfly(block_size=8)", b["lowrank_first"].shape[0]), 0)
+    with torch.no_grad():
+        lin.matrix.weight.copy_(b["weight"]); lin.bias.copy_(b["bias"])
+        lin.matrix.lowrank_first.copy_(b["lowrank_first"]); lin.matrix.lowrank_second.copy_(b["lowrank_second"])
+    lin = lin.to(cuda_device)
+    x = b["x"].float().to(cuda_device).requires_grad_()
+    out = lin(x)
+    (out * b["g"].float().to(cuda_device)).sum().backward()
+    assert_close(out, b["out"], FP32_RTOL, FP32_ATOL, "out")
+    assert_close(x.grad, b["grad_input"], FP32_RTOL, FP32_ATOL, "dx")
+    assert_close(lin.matrix.weight.grad, b["grad_weight"], FP32_RTOL, FP32_ATOL, "dw")
+    assert_close(lin.bias.grad, b["grad_bias"], FP32_RTOL, FP32_ATOL, "db")
+    assert_close(lin.matrix.lowrank_first.grad, b["grad_lowrank_first"], FP32_RTOL, FP32_ATOL, "dL1")
+    assert_close(lin.matrix.lowrank_second.grad, b["grad_lowrank_second"], FP32_RTOL, FP32_ATOL, "dL2")
+    # functional form with 7 positional arguments (tests/test_linear.py::test_semishared_linear_naive)
+    torch.manual_seed(1337)
+    inp = torch.randn(3, 15, 256, device=cuda_device, requires_grad=True)
+    w = torch.randn(512, 256, device=cuda_device, requires_grad=True)
+    a1 = torch.randn(64, 256, device=cuda_device, requires_grad=True)
+    a2 = torch.randn(512, 64, device=cuda_device, requires_grad=True)
+    bias = torch.randn(512, device=cuda_device, requires_grad=True)
+    d = torch.randn(3, 15, 512, device=cuda_device)
+    out = _GeneralizedLinear.apply(inp, w, bias, a1, a2, None, None)
+    (out * d).sum().backward()
+    ref, hid = O.linear_forward(inp.detach().double().cpu(), w.detach().double().cpu(), bias.detach().double().cpu(),
+                                a1.detach().double().cpu(), a2.detach().double().cpu())
+    rg = O.linear_backward(d.double().cpu(), inp.detach().double().cpu(), hid, w.detach().double().cpu(),
+                           a1.detach().double().cpu(), a2.detach().double().cpu())
+    assert_close(out, ref, 1e-3, 1e-3, "functional out")
+    for t, key in ((inp, "input"), (w, "weight"), (bias, "bias"), (a1, "lowrank_first"), (a2, "lowrank_second")):
+        assert_close(t.grad, rg[key], 1e-3, 1e-3, key, scale_atol=True)
+
+
+def test_full_size_config5_properties(cuda_device):
+    """Config 5 shapes (hidden 8192, intermediate 32768, GeGLU, bf16) on one GPU: too large for the CPU oracle
+    end to end, so it is checked through size-independent properties:
+      * tokens are independent: 48 sampled rows of the 8192-token forward equal the oracle on those rows;
+      * parameter gradients are sums over tokens: grads(all tokens) == grads(first half) + grads(second half)."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 60 * 2**30:
+        pytest.skip("needs ~60 GB of free device memory")
+    hidden, inter, tokens = 8192, 32768, 8192
+    params = random_params(hidden, inter, True, seed=0)
+    ffn = make_ffn(params, gated=True)
+    torch.manual_seed(0)
+    x, g = torch.randn(tokens, hidden), torch.randn(tokens, hidden)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device), autocast=True)
+    rows = torch.randperm(tokens, generator=torch.Generator().manual_seed(1))[:48]
+    ref_rows, _ = O.leanffn_forward(x[rows], params, gated=True)
+    assert_close(out[rows.to(cuda_device)], ref_rows, BF16_RTOL, BF16_ATOL, "sampled rows of the forward")
+    full = {k: v.clone() for k, v in grads.items() if k != "input"}
+    halves = []
+    for sl in (slice(0, tokens // 2), slice(tokens // 2, tokens)):
+        _, gh = run_step(ffn, x[sl].to(cuda_device), g[sl].to(cuda_device), autocast=True)
+        halves.append({k: v.clone() for k, v in gh.items()})
+    assert_close(torch.cat([halves[0]["input"], halves[1]["input"]]), grads["input"], 0, 0, "dX is per token")
+    for k, v in full.items():
+        assert_close(halves[0][k] + halves[1][k], v, 1e-3, 1e-3, f"additivity of grad_{k}", scale_atol=True)
