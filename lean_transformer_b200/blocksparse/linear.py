@@ -7,6 +7,7 @@ state dicts are interchangeable.  The arithmetic is one GEMM launch per product:
 rides in the main kernel's k-loop as a continuation and the bias in its epilogue.
 """
 import math
+import weakref
 from itertools import zip_longest
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -34,24 +35,29 @@ def resolve_compute_dtype(input: torch.Tensor) -> torch.dtype:
     raise TypeError(f"unsupported input dtype {input.dtype}")
 
 
-_CAST_CACHE: Dict[tuple, tuple] = {}
+_CAST_CACHE: Dict[int, tuple] = {}
 
 
 def cast_cached(t: Optional[torch.Tensor], dtype: torch.dtype) -> Optional[torch.Tensor]:
-    """``t`` as a contiguous tensor of ``dtype``; conversions are remembered until ``t`` is modified in place
-    (version counter) or replaced, so a weight is converted once per optimizer step, not once per use."""
+    """``t`` as a contiguous tensor of ``dtype``; conversions are remembered per tensor OBJECT until it is
+    modified in place (version counter), re-pointed at other storage, or garbage collected, so a weight is
+    converted once per optimizer step, not once per use."""
     if t is None:
         return None
     if t.dtype == dtype and t.is_contiguous():
         return t.detach()
-    key = (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype, dtype, str(t.device))
+    key = id(t)
     hit = _CAST_CACHE.get(key)
-    if hit is not None and hit[0] == t._version:
-        return hit[1]
-    if len(_CAST_CACHE) > 512:
-        _CAST_CACHE.clear()
+    if hit is not None:
+        ref, version, data_ptr, target, converted = hit
+        if ref() is t and version == t._version and data_ptr == t.data_ptr() and target == dtype:
+            return converted
     converted = ops.cast(t.detach().contiguous(), dtype)
-    _CAST_CACHE[key] = (t._version, converted)
+    try:
+        ref = weakref.ref(t, lambda _r, _k=key: _CAST_CACHE.pop(_k, None))
+    except TypeError:
+        return converted
+    _CAST_CACHE[key] = (ref, t._version, t.data_ptr(), dtype, converted)
     return converted
 
 

@@ -6,6 +6,7 @@ that feeds output block backward_indices[j, a].  Where the reference materialise
 block ([nnz * block, tokens]) and gathers with embedding_bag, the kernels here walk only the nonzero
 blocks of each output tile.
 """
+import weakref
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -14,13 +15,6 @@ from .. import ops
 from .layout import tables_from_native_indices
 
 _TABLE_CACHE: Dict[tuple, tuple] = {}
-
-
-def _cache_put(key, value):
-    if len(_TABLE_CACHE) > 256:
-        _TABLE_CACHE.clear()
-    _TABLE_CACHE[key] = value
-    return value
 
 
 def backward_indices_from_forward(forward_indices: torch.Tensor, blocks_per_input: int) -> torch.Tensor:
@@ -36,23 +30,29 @@ def backward_indices_from_forward(forward_indices: torch.Tensor, blocks_per_inpu
 
 def native_tables(forward_indices: Optional[torch.Tensor], backward_indices: Optional[torch.Tensor],
                   blocks_per_input: int):
-    """(forward, dgrad, wgrad) pair tables on the indices' device, cached per index tensor."""
-    key = (forward_indices.data_ptr() if forward_indices is not None else 0,
-           backward_indices.data_ptr() if backward_indices is not None else 0, blocks_per_input,
-           str((forward_indices if forward_indices is not None else backward_indices).device))
+    """(forward, dgrad, wgrad) pair tables on the indices' device.  Cached per index-tensor OBJECT (module
+    buffers live as long as their module); the entry is dropped when the tensor is collected and ignored if
+    the tensor was modified in place or re-pointed."""
+    anchor = forward_indices if forward_indices is not None else backward_indices
+    other = backward_indices if forward_indices is not None else None
+    key = (id(anchor), id(other) if other is not None else 0, blocks_per_input)
+    stamp = (anchor._version, anchor.data_ptr(), other._version if other is not None else 0,
+             other.data_ptr() if other is not None else 0)
     hit = _TABLE_CACHE.get(key)
-    if hit is not None:
-        return hit
+    if hit is not None and hit[0]() is anchor and (other is None or hit[1]() is other) and hit[2] == stamp:
+        return hit[3]
     if backward_indices is None:
         backward_indices = backward_indices_from_forward(forward_indices, blocks_per_input)
     if forward_indices is None:
         in_blocks, per_col = backward_indices.shape
         out_blocks = int(backward_indices.max().item()) + 1
-        # list, per output block, the flat ids feeding it (ascending)
-        flat_owner = backward_indices.flatten()
-        order = torch.argsort(flat_owner, stable=True)
+        order = torch.argsort(backward_indices.flatten(), stable=True)  # flat ids grouped by owning output block
         forward_indices = order.view(out_blocks, -1).to(torch.int32)
-    return _cache_put(key, tables_from_native_indices(forward_indices, backward_indices))
+    tables = tables_from_native_indices(forward_indices, backward_indices)
+    drop = lambda _r, _k=key: _TABLE_CACHE.pop(_k, None)  # noqa: E731
+    _TABLE_CACHE[key] = (weakref.ref(anchor, drop), weakref.ref(other, drop) if other is not None else None, stamp,
+                         tables)
+    return tables
 
 
 def _bs_forward(x2d: torch.Tensor, weight: torch.Tensor, fwd_table: torch.Tensor, out_features: int,

@@ -37,8 +37,8 @@ extern "C" const char* leanffn_status_string(int32_t s) {
 
 extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   if (d == nullptr) return LEANFFN_ERR_NULL;
-  if (d->A == nullptr || d->B == nullptr || d->D == nullptr) return LEANFFN_ERR_NULL;
   if (d->M < 0 || d->N <= 0 || d->K <= 0 || d->K2 < 0) return LEANFFN_ERR_SHAPE;
+  if (d->M > 0 && (d->A == nullptr || d->B == nullptr || d->D == nullptr)) return LEANFFN_ERR_NULL;
   if (d->in_dtype != LEANFFN_F32 && d->in_dtype != LEANFFN_BF16) return LEANFFN_ERR_DTYPE;
   if (d->d_dtype != LEANFFN_F32 && d->d_dtype != LEANFFN_BF16) return LEANFFN_ERR_DTYPE;
   if (d->epilogue < LEANFFN_EPI_STORE || d->epilogue > LEANFFN_EPI_ACT_BWD) return LEANFFN_ERR_UNSUPPORTED;

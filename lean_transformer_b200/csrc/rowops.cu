@@ -674,8 +674,8 @@ extern "C" int32_t leanffn_layer_norm_forward(const void* x, int32_t x_dtype, co
                                               int64_t cols, float eps, float dropout_p, uint64_t seed,
                                               uint64_t elem_offset, const void* residual, int32_t residual_dtype,
                                               void* stream) {
-  if (x == nullptr || y == nullptr) return LEANFFN_ERR_NULL;
   if (rows < 0 || cols <= 0 || cols > 0x7fffffff) return LEANFFN_ERR_SHAPE;
+  if (rows > 0 && (x == nullptr || y == nullptr)) return LEANFFN_ERR_NULL;
   if (!dtype_ok(x_dtype) || !dtype_ok(param_dtype) || !dtype_ok(y_dtype)) return LEANFFN_ERR_DTYPE;
   if (residual != nullptr && !dtype_ok(residual_dtype)) return LEANFFN_ERR_DTYPE;
   if (!(dropout_p >= 0.f && dropout_p < 1.f)) return LEANFFN_ERR_UNSUPPORTED;

@@ -37,23 +37,42 @@ def golden_ffn_case(name: str, dtype=torch.float64):
     return conv(blob["x"]), conv(blob["g"]), params, expected, meta
 
 
-def assert_close(got: torch.Tensor, ref: torch.Tensor, rtol: float, atol: float, what: str = "", scale_atol=False):
-    """|got - ref| <= atol' + rtol * |ref| elementwise.  With ``scale_atol`` (used for gradients that sum
-    over thousands of tokens) atol' = atol * max(1, rms(ref)): the absolute floor follows the size of the
-    sums, whose rounding noise grows with the number and magnitude of the terms, not with the individual
-    element that happens to be near zero."""
+def assert_close(got: torch.Tensor, ref: torch.Tensor, rtol: float, atol: float, what: str = "", scale_atol=False,
+                 branch: torch.Tensor = None, outlier_frac: float = 0.0):
+    """|got - ref| <= atol * max(1, S) + rtol * max(|ref|, |branch|, S), elementwise.
+
+    With S = 0 and no branch this is torch.allclose's rule.  The two extensions judge an element at the scale
+    of the computation that produced it rather than at the size it happens to end up with:
+
+    ``scale_atol``: S = rms of the GEMM-produced tensor (``branch`` if given, else ``ref``).  A matrix product
+    accumulates hundreds to tens of thousands of products; its rounding noise is proportional to the rms of
+    the accumulated sums, also for the elements whose terms cancel to ~0.
+
+    ``branch``: where a residual is added exactly (out = x + branch, dx = g + branch'), the reference value of
+    the computed branch; an output that cancels against the residual is judged at the branch's size.
+
+    ``outlier_frac`` (bf16 only): rounding noise is random, so among millions of elements a few land beyond any
+    fixed multiple of its standard deviation.  Up to this fraction may exceed the bound; none may exceed 4x."""
     got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
-    floor = atol * max(1.0, float(ref.pow(2).mean().sqrt())) if scale_atol else atol
+    mag = ref.abs()
+    produced = ref
+    if branch is not None:
+        produced = branch.detach().double().cpu().reshape(ref.shape)
+        mag = torch.maximum(mag, produced.abs())
+    S = float(produced.pow(2).mean().sqrt()) if scale_atol and produced.numel() else 0.0
     err = (got - ref).abs()
-    bound = floor + rtol * ref.abs()
+    bound = atol * max(1.0, S) + rtol * mag.clamp_min(S)
     bad = err > bound
+    if outlier_frac > 0 and int(bad.sum()) <= outlier_frac * bad.numel() and not (err > 4 * bound).any():
+        return
     if bad.any():
         worst = int((err - bound).argmax())
         raise AssertionError(
-            f"{what}: {int(bad.sum())}/{bad.numel()} elements out of tolerance (rtol {rtol}, atol {floor:.3g}); "
-            f"worst |err| {float(err.flatten()[worst]):.4g} at ref {float(ref.flatten()[worst]):.4g}; "
-            f"max |err| {float(err.max()):.4g}, max |ref| {float(ref.abs().max()):.4g}")
+            f"{what}: {int(bad.sum())}/{bad.numel()} elements out of tolerance (rtol {rtol}, atol {atol}, S {S:.3g}); "
+            f"worst |err| {float(err.flatten()[worst]):.4g} at ref {float(ref.flatten()[worst]):.4g} "
+            f"(bound {float(bound.flatten()[worst]):.4g}); max |err| {float(err.max()):.4g}, "
+            f"max |ref| {float(ref.abs().max()):.4g}")
 
 
 @pytest.fixture

@@ -54,6 +54,8 @@ def test_argument_validation_without_gpu():
 
     assert N.lib.leanffn_gemm(None, None) == -1
     d = N.GemmDesc()
+    assert N.lib.leanffn_gemm(ctypes.byref(d), None) == -2  # empty shape
+    d.M = d.N = d.K = 8
     assert N.lib.leanffn_gemm(ctypes.byref(d), None) == -1  # null operands
     assert N.lib.leanffn_layer_norm_forward(None, 0, None, None, 0, None, 0, 4, 4, 1e-5, 0.0, 0, 0, None, 0, None) == -1
     assert N.lib.leanffn_dropout(1, 0, 1, 0, 16, 1.5, 0, 0, None, 0, None) == -5  # p out of range
