@@ -5,6 +5,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "gemm_common.cuh"
 
 namespace leanffn {
@@ -155,6 +158,23 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
       B2.ptr = d->B2, B2.ld = d->ldb2;
       if (d->a_mn_major) A2.rows = d->K2, A2.cols = d->M; else A2.rows = d->M, A2.cols = d->K2;
       if (d->b_mn_major) B2.rows = d->K2, B2.cols = d->N; else B2.rows = d->N, B2.cols = d->K2;
+    }
+    // Dense products with at least one full 256 x 256 tile can run on CTA pairs (cta_group::2).  Under the
+    // 1 kW power cap of long runs the one-CTA kernel sustains the higher rate, so it is the default;
+    // LEANFFN_GEMM_KERNEL=pair selects the CTA-pair kernel (it wins on short, cool bursts).
+    static const bool pair_enabled = []() {
+      const char* v = getenv("LEANFFN_GEMM_KERNEL");
+      return v != nullptr && strcmp(v, "pair") == 0;
+    }();
+    static const int pair_tune = []() {
+      const char* v = getenv("LEANFFN_PAIR_TUNE");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    p.tune = pair_tune;
+    if (pair_enabled && d->bs_mode == 0 && block_n == 256 && d->M > 128) {
+      p.num_m_blocks = static_cast<int32_t>((d->M + 255) / 256);
+      return gemm_tcgen05_pair(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
+                               d->K2 > 0 ? &B2 : nullptr, p, st);
     }
     cudaError_t ce;
     return gemm_tcgen05(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,

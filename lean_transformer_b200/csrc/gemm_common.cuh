@@ -77,6 +77,7 @@ struct TcParams {
   const int32_t* bs_count;  // entries per table row, or nullptr
   int32_t glu_split;  // > 0: B rows [n, n+128) and [glu_split + n, ...) form one 256-wide tile
   int32_t max_ctas;   // > 0: cap on the persistent grid
+  int32_t tune;       // experiment knobs of the CTA-pair kernel: bits 0-3 stages (0 = default), bit 4 spin-wait
   int32_t* status;
   EpiParams ep;
 };
@@ -92,6 +93,9 @@ int sm_count();
 cudaError_t gemm_simt(const SimtOperands& o, const EpiParams& ep, int32_t in_dtype, cudaStream_t st);
 int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
                      const TcOperand* B2, TcParams p, int block_n, cudaStream_t st, cudaError_t* cuda_err);
+// CTA-pair (cta_group::2) kernel for dense products; tile counts in p are in 256 x 256 tiles.
+int32_t gemm_tcgen05_pair(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
+                          const TcOperand* B2, TcParams p, cudaStream_t st);
 int32_t launch_act_fwd(const void* pre, void* hid, int32_t dtype, int64_t rows, int64_t inter, int32_t gated,
                        int32_t act, cudaStream_t st);
 int32_t launch_act_bwd(const void* dhid, int64_t ld_dhid, const void* pre, void* dpre, void* hid_out, int32_t dtype,
