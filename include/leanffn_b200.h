@@ -131,6 +131,25 @@ size_t leanffn_column_sum_scratch_bytes(int64_t rows, int64_t cols);
 int32_t leanffn_column_sum(const void* x, int32_t x_dtype, int64_t ld, float* out, void* scratch,
                            int64_t rows, int64_t cols, void* stream);
 
+/* Same result as leanffn_column_sum, for callers that cannot hand over scratch memory: a host that drives
+ * this library through the C ABI alone has no tensor allocator behind it, and a serving or training process
+ * that has given the whole device to its own pool (or that must not stall on the implicit synchronisation of
+ * cudaMalloc / cudaFree in its steady state) cannot allocate at call time.  The partial sums go to a fixed
+ * 1 MiB array inside the library image instead; every GPU that loads the library holds that array until the
+ * process exits.  The call allocates and frees nothing.
+ * Limit: any number of rows, at most 65536 columns (wider inputs, or a GPU so large that its partial sums
+ * exceed leanffn_column_sum_static_capacity() = 262144 floats, are rejected with LEANFFN_ERR_TOO_LARGE and
+ * nothing is launched).
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  All calls on a device share the one array:
+ * calls that may overlap on the GPU (different streams without ordering) race on it and must be serialised
+ * by the caller.  The array keeps whatever the last call left; each call overwrites every partial it reads,
+ * so no clearing is needed.
+ * No counterpart in the reference: it has no C ABI and allocates through PyTorch everywhere. */
+int64_t leanffn_column_sum_static_capacity(void);
+int32_t leanffn_column_sum_static(const void* x, int32_t x_dtype, int64_t ld, float* out, int64_t rows,
+                                  int64_t cols, void* stream);
+
 /* y = (y_dtype) x, n elements. Replaces the autocast casts the reference relies on
  * (torch.cuda.amp.custom_fwd at lean_transformer/ffn.py:147). */
 int32_t leanffn_cast(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t n, void* stream);

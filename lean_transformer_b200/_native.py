@@ -56,6 +56,8 @@ _SIGNATURES = {
     "leanffn_dropout_mask": (c_int32, [c_void_p, c_int64, c_float, c_uint64, c_uint64, c_void_p]),
     "leanffn_column_sum_scratch_bytes": (c_size_t, [c_int64, c_int64]),
     "leanffn_column_sum": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "leanffn_column_sum_static_capacity": (c_int64, []),
+    "leanffn_column_sum_static": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "leanffn_cast": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_void_p]),
     "leanffn_transpose": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),

@@ -860,6 +860,49 @@ extern "C" int32_t leanffn_column_sum(const void* x, int32_t x_dtype, int64_t ld
   return colsum_launch<float>(static_cast<const float*>(x), ld, out, static_cast<float*>(scratch), rows, cols, st);
 }
 
+// ---- column sum without any allocation --------------------------------------------------------------------
+// Scratch for leanffn_column_sum_static lives in the library image: 1 MiB per GPU that loads the library, held
+// until the process exits.  In host code the array's name is only a handle; the device address is looked up once
+// per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+constexpr int64_t STATIC_SCRATCH_FLOATS = 1 << 18;
+constexpr int64_t STATIC_MAX_COLS = 65536;
+static __device__ __align__(256) float g_colsum_static_scratch[STATIC_SCRATCH_FLOATS];
+static float* g_colsum_static_ptr[64] = {nullptr};
+
+extern "C" int64_t leanffn_column_sum_static_capacity(void) { return STATIC_SCRATCH_FLOATS; }
+
+extern "C" int32_t leanffn_column_sum_static(const void* x, int32_t x_dtype, int64_t ld, float* out, int64_t rows,
+                                             int64_t cols, void* stream) {
+  if (rows < 0 || cols <= 0 || ld < cols) return LEANFFN_ERR_SHAPE;
+  if (out == nullptr || (rows > 0 && x == nullptr)) return LEANFFN_ERR_NULL;
+  if (!dtype_ok(x_dtype)) return LEANFFN_ERR_DTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    cudaMemsetAsync(out, 0, sizeof(float) * cols, st);
+    return launch_status();
+  }
+  if (cols > STATIC_MAX_COLS) return LEANFFN_ERR_TOO_LARGE;
+  const int64_t chunks = colsum_chunks(rows, cols);
+  if (chunks > 1 && chunks * cols > STATIC_SCRATCH_FLOATS) return LEANFFN_ERR_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+  if (dev < 0 || dev >= 64) return LEANFFN_ERR_UNSUPPORTED;
+  if (g_colsum_static_ptr[dev] == nullptr) {
+    // first call on this device (it is the current device): resolve the symbol's device address
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_colsum_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return 1000 + static_cast<int32_t>(e);
+    g_colsum_static_ptr[dev] = ptr;
+  }
+  float* scratch = g_colsum_static_ptr[dev];
+  // Every partial the second stage reads is written by the first stage of the same call, so nothing left in
+  // the array by an earlier call is ever consumed and nothing needs clearing.
+  if (x_dtype == LEANFFN_BF16)
+    return colsum_launch<bf16>(static_cast<const bf16*>(x), ld, out, scratch, rows, cols, st);
+  return colsum_launch<float>(static_cast<const float*>(x), ld, out, scratch, rows, cols, st);
+}
+
 extern "C" int32_t leanffn_cast(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t n, void* stream) {
   return leanffn_dropout(x, x_dtype, y, y_dtype, n, 0.f, 0, 0, nullptr, 0, stream);
 }
