@@ -1,0 +1,100 @@
+"""Token partition + gradient all-reduce on 2 CPU ranks (gloo): the multi-GPU host logic without GPUs.
+
+Each rank computes the gradients of its token shard with the CPU oracle (a stand-in for the CUDA backward, which
+produces the same quantities), hands them to GradSync in the order the backward produces them, and the reduced
+result must equal the full-batch gradients.  Failure handling is exercised on the host: a rank that raises
+before the collective must surface as an error on the other rank instead of a hang.
+"""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _problem():
+    from helpers import random_params
+    params = random_params(32, 64, True, seed=0, std=0.2, bias_std=0.1, dtype=torch.float64)
+    gen = torch.Generator().manual_seed(1)
+    x = torch.randn(50, 32, generator=gen, dtype=torch.float64)  # 50 tokens: uneven over 4 ranks, even over 2
+    g = torch.randn(50, 32, generator=gen, dtype=torch.float64)
+    return params, x, g
+
+
+def _worker(rank, world, port, mode, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=20))
+    try:
+        from lean_transformer_b200 import dist as ldist
+        from oracle import leanffn_oracle as O
+        params, x, g = _problem()
+        start, count = ldist.shard_tokens(x.shape[0], world, rank)
+        if mode == "raise" and rank == 1:
+            raise RuntimeError("injected failure before the collective")
+        _, grads = O.leanffn_step(x[start:start + count], g[start:start + count], params, gated=True)
+        sync = ldist.GradSync(wire_dtype=torch.float32 if mode == "wire" else None)
+        order = ["h2o_weight", "h2o_bias", "i2h_weight", "i2h_bias", "ln_weight", "ln_bias"]  # backward's order
+        for name in order:
+            sync.reduce(name, grads[name])
+        assert sync.finish() == len(order) and sync.reduced_names == order
+        torch.save({k: grads[k] for k in order}, os.path.join(result_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["plain", "wire"])
+def test_token_partition_and_gradient_allreduce(tmp_path, mode):
+    from lean_transformer_b200 import dist as ldist
+    from oracle import leanffn_oracle as O
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), mode, str(tmp_path)), nprocs=world, join=True)
+    params, x, g = _problem()
+    _, full = O.leanffn_step(x, g, params, gated=True)
+    for rank in range(world):
+        got = torch.load(tmp_path / f"rank{rank}.pt")
+        for name, value in got.items():
+            tol = 1e-5 if mode == "wire" else 1e-12  # fp32 wire format rounds once
+            assert torch.allclose(value, full[name], rtol=tol, atol=tol), (rank, name)
+
+
+def test_shard_tokens_covers_everything():
+    from lean_transformer_b200 import dist as ldist
+    for total, world in [(65536, 8), (50, 4), (7, 8), (0, 2)]:
+        spans = [ldist.shard_tokens(total, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and sum(c for _, c in spans) == total
+        assert all(spans[i][0] + spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+        assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
+    with pytest.raises(ValueError):
+        ldist.shard_tokens(8, 2, 2)
+
+
+def test_failed_rank_surfaces_as_error_not_hang(tmp_path):
+    """A rank that dies before the collective: the job ends with an exception within the group timeout."""
+    with pytest.raises(Exception):
+        mp.spawn(_worker, args=(2, _free_port(), "raise", str(tmp_path)), nprocs=2, join=True)
+
+
+def test_dropout_mask_is_partition_invariant():
+    """With elem_offset = first_row * hidden, a rank's mask equals the matching rows of the global mask."""
+    from lean_transformer_b200 import dist as ldist
+    from oracle import leanffn_oracle as O
+    tokens, hidden, p, seed = 37, 24, 0.3, 11
+    full = O.dropout_keep_mask(tokens * hidden, p, seed, 0).reshape(tokens, hidden)
+    for rank in range(4):
+        start, count = ldist.shard_tokens(tokens, 4, rank)
+        part = O.dropout_keep_mask(count * hidden, p, seed, start * hidden).reshape(count, hidden)
+        assert (part == full[start:start + count]).all()
