@@ -196,7 +196,11 @@ def run_ours(args, wl, name):
         lffn.set_grad_ready_hook(sync.reduce)
         ops.set_max_ctas(max(1, torch.cuda.get_device_properties(device).multi_processor_count - args.comm_sms))
 
+    from lean_transformer_b200.blocksparse.linear import clear_cast_cache
+
     def step(x, g):
+        if wl["mixed"]:
+            clear_cast_cache()  # a real step updates the fp32 masters, so their bf16 copies are rebuilt every step
         for p in params:
             p.grad = None
         x = x.requires_grad_(True)
@@ -236,6 +240,15 @@ def run_ours(args, wl, name):
     seconds = float(elapsed.item())
     gemm_flops, gemm_seconds, gemm_launches = timer.summary()
     L.check_device_status(device)
+
+    if args.skip_e2e:
+        if rank == 0:
+            print(json.dumps(dict(profiling_run=True, workload=name, tokens=total_tokens, ms_per_step=seconds / args.steps * 1e3,
+                                  gemm_tflops=gemm_flops / gemm_seconds / 1e12 if gemm_seconds else None)), flush=True)
+        if world > 1:
+            lffn.set_grad_ready_hook(None)
+            dist.destroy_process_group()
+        return
 
     # ---- end-to-end through the module API with host buffers (e2e) --------------------------------------
     x_host = x_dev.detach().cpu().pin_memory()
@@ -345,7 +358,11 @@ def quick_measure(wl, device, args):
     g = torch.randn(tokens, hidden, device=device).to(torch.bfloat16)
     params = list(ffn.parameters())
 
+    from lean_transformer_b200.blocksparse.linear import clear_cast_cache
+
     def step():
+        if wl["mixed"]:
+            clear_cast_cache()
         for p in params:
             p.grad = None
         with torch.autocast("cuda", dtype=torch.bfloat16, enabled=wl["mixed"]):
@@ -379,9 +396,14 @@ def main():
     ap.add_argument("--extra-workload", default="mixed_bf16_h1024")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to NCCL while GEMMs run (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override the workload's token count (smaller cases for ncu captures; not a bench number)")
+    ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.tokens:
+        wl["total_tokens" if "total_tokens" in wl else "tokens_per_rank"] = args.tokens
     if args.impl == "reference":
         run_reference_arm(args, wl, args.workload)
     else:

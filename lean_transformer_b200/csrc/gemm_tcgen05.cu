@@ -7,7 +7,8 @@
 // One persistent CTA per SM walks a static, M-grouped tile order.  Warp roles:
 //   warp 0       TMA producer (one elected lane)
 //   warp 1       TMEM allocation + MMA issue (one elected lane)
-//   warps 2..5   epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31
+//   warps 2..9   epilogue; warp w owns TMEM lanes 32*(w%4) .. 32*(w%4)+31, two warps per lane quarter
+//                split the tile's 32-column blocks
 //
 // Operand majorness: a K-major operand is a [rows, K] row-major matrix (TMA box 64 K-elements x 128
 // rows); an MN-major operand is a [K, rows] row-major matrix (TMA boxes of 64 rows-elements x 64
@@ -28,7 +29,8 @@ namespace leanffn {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;
 constexpr int UMMA_K = 16;
-constexpr int TC_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int TC_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int GROUP_M = 16;
 constexpr uint32_t A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB
 constexpr uint32_t CHUNK_BYTES = 64 * BLOCK_K * 2;         // one MN-major 64 x 64 box, 8 KiB
@@ -40,7 +42,8 @@ struct TcConfig {
   static constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
   static constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator stages
   static constexpr uint32_t BAR_BYTES = 256;
-  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr uint32_t PATCH_BYTES = EPI_WARPS * EPI_PATCH_FLOATS * 4;  // epilogue transposition patches
+  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + PATCH_BYTES + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void report(int32_t* status, int32_t code) {
@@ -79,7 +82,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 4);
+      mbar_init(tempty_bar(s), EPI_WARPS);
     }
     *abort_ptr = 0;
     fence_mbar_init();
@@ -258,6 +261,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const EpiParams& ep = p.ep;
     const int quarter = warp & 3;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    float* patch = reinterpret_cast<float*>(smem_gen + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES) +
+                   (warp - 2) * EPI_PATCH_FLOATS;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -269,11 +274,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       tc_fence_after();
-      const int64_t row = static_cast<int64_t>(m_blk) * BLOCK_M + quarter * 32 + lane;
-      const bool row_ok = row < ep.M;
+      const int64_t row0 = static_cast<int64_t>(m_blk) * BLOCK_M + quarter * 32;
       const bool acc_valid = main_k_blocks(n_blk) + p.num_k2_blocks > 0;  // empty reduction: acc is all zeros
       const uint32_t t_acc = tmem_base + lane_addr + acc_stage * BLOCK_N;
-      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row, row_ok, n_blk, acc_valid);
+      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, (warp - 2) >> 2, 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc_stage));

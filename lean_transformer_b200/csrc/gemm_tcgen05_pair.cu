@@ -4,13 +4,13 @@
 // L2 -> shared memory once per pair instead of once per SM.  Per 64-deep k-block a CTA moves 32 KiB for
 // 512 tensor-core clocks (64 B/clk/SM), against 96 B/clk/SM for the one-CTA 128 x 256 kernel.
 //
-// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation (+ MMA issue in the leader CTA,
-// rank 0 of the pair), warps 2..5 = epilogue of the CTA's own 128 accumulator rows.
+// Roles per CTA (320 threads): warp 0 = TMA producer, warp 1 = TMEM allocation (+ MMA issue in the leader CTA,
+// rank 0 of the pair), warps 2..9 = epilogue of the CTA's own 128 accumulator rows.
 // Synchronisation:
 //   full[s]    (leader's shared memory)  both CTAs' TMA bytes are credited to it; the leader's MMA thread waits
 //   empty[s]   (each CTA)                the leader's tcgen05.commit arrives on both CTAs' barriers
 //   tfull[a]   (each CTA)                accumulator stage a complete: commit arrives on both
-//   tempty[a]  (leader's shared memory)  8 arrivals: the 4 epilogue warps of each CTA
+//   tempty[a]  (leader's shared memory)  16 arrivals: the 8 epilogue warps of each CTA
 // Every wait is bounded; a role that gives up records a code, raises the pair-wide abort flags and all roles
 // drain, meet at the closing cluster barrier and free TMEM.
 #include <cuda.h>
@@ -31,15 +31,17 @@ constexpr int BLOCK_M = 256;       // per pair; 128 per CTA
 constexpr int BLOCK_N = 256;       // per pair; each CTA stages 128 rows of B
 constexpr int BLOCK_K = 64;
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int GROUP_M = 8;         // 8 x 256 rows share a sweep over N (L2 reuse of the A panels)
-constexpr int MAX_STAGES = 7;
+constexpr int MAX_STAGES = 6;
 constexpr uint32_t A_BYTES = 128 * BLOCK_K * 2;          // 16 KiB
 constexpr uint32_t B_BYTES = 128 * BLOCK_K * 2;          // 16 KiB (this CTA's half)
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;      // 32 KiB
 constexpr uint32_t CHUNK_BYTES = 64 * BLOCK_K * 2;       // one MN-major 64 x 64 box
 constexpr uint32_t TMEM_COLS = 512;                      // two 256-column accumulator stages
-constexpr uint32_t SMEM_BYTES = MAX_STAGES * STAGE_BYTES + 256 + 1024;
+constexpr uint32_t PATCH_BYTES = EPI_WARPS * EPI_PATCH_FLOATS * 4;
+constexpr uint32_t SMEM_BYTES = MAX_STAGES * STAGE_BYTES + 256 + PATCH_BYTES + 1024;
 
 }  // namespace pair
 
@@ -91,7 +93,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 8);  // 4 epilogue warps x 2 CTAs (used in the leader only)
+      mbar_init(tempty_bar(s), 2 * EPI_WARPS);  // every epilogue warp of both CTAs (used in the leader only)
     }
     *abort_ptr = 0;
     fence_mbar_init();
@@ -246,6 +248,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const int quarter = warp & 3;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t leader_tempty0 = map_to_cta(tempty_bar(0), 0);
+    float* patch = reinterpret_cast<float*>(smem_gen + STAGES_ALLOC * STAGE_BYTES + 256) + (warp - 2) * EPI_PATCH_FLOATS;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     long long w_tfull = 0, t_begin = clock64();
@@ -259,9 +262,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       }
       if (prof) w_tfull += clock64() - tw;
       tc_fence_after();
-      const int64_t row = static_cast<int64_t>(m_blk) * BLOCK_M + rank * 128 + quarter * 32 + lane;
+      const int64_t row0 = static_cast<int64_t>(m_blk) * BLOCK_M + rank * 128 + quarter * 32;
       const uint32_t t_acc = tmem_base + lane_addr + acc_stage * BLOCK_N;
-      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row, row < ep.M && !skip_store, n_blk, true);
+      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, true, patch, lane, (warp - 2) >> 2, 2, skip_store);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8u * acc_stage);
