@@ -176,6 +176,21 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
       return gemm_tcgen05_pair(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
                                d->K2 > 0 ? &B2 : nullptr, p, st);
     }
+    // Long reductions run 256 x 256 tiles per CTA (two accumulator sub-tiles sharing each B stage): a third less
+    // operand traffic per flop; the exposed epilogue is a few percent of such a tile.  LEANFFN_GEMM_TILE=128 / 256
+    // forces one or the other.
+    static const int tile_override = []() {
+      const char* v = getenv("LEANFFN_GEMM_TILE");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    p.m_subtiles = 1;
+    if (d->bs_mode == 0 && block_n == 256 && d->M >= 256) {
+      const int64_t k_total = k_eff + d->K2;
+      if (tile_override == 256 || (tile_override == 0 && k_total >= 4096)) {
+        p.m_subtiles = 2;
+        p.num_m_blocks = static_cast<int32_t>((d->M + 255) / 256);
+      }
+    }
     cudaError_t ce;
     return gemm_tcgen05(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
                         d->K2 > 0 ? &B2 : nullptr, p, block_n, st, &ce);

@@ -35,12 +35,18 @@ constexpr int GROUP_M = 16;
 constexpr uint32_t A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB
 constexpr uint32_t CHUNK_BYTES = 64 * BLOCK_K * 2;         // one MN-major 64 x 64 box, 8 KiB
 
-template <int BLOCK_N>
+// MT = number of 128-row accumulator sub-tiles per CTA tile.  MT == 1: 128 x BLOCK_N tile, two TMEM accumulator
+// stages (the epilogue of one tile overlaps the MMAs of the next).  MT == 2: 256 x 256 tile, both sub-tiles share
+// every B stage (a third less L2 -> shared traffic per flop), all 512 TMEM columns hold ONE tile, so the epilogue
+// is exposed; used for long reductions only, where it is a few percent of the tile time.
+template <int BLOCK_N, int MT = 1>
 struct TcConfig {
+  static constexpr uint32_t A_BYTES = MT * A_STAGE_BYTES;
   static constexpr uint32_t B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
-  static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = BLOCK_N == 256 ? 4 : 6;
-  static constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator stages
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = MT == 2 ? 3 : (BLOCK_N == 256 ? 4 : 6);
+  static constexpr int ACC_STAGES = MT == 2 ? 1 : 2;
+  static constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator stages, or the two sub-tiles of one tile
   static constexpr uint32_t BAR_BYTES = 256;
   static constexpr uint32_t PATCH_BYTES = EPI_WARPS * EPI_PATCH_FLOATS * 4;  // epilogue transposition patches
   static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + PATCH_BYTES + 1024;  // + alignment slack
@@ -50,13 +56,15 @@ __device__ __forceinline__ void report(int32_t* status, int32_t code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
-template <bool A_MN, bool B_MN, int BLOCK_N>
+template <bool A_MN, bool B_MN, int BLOCK_N, int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                     const TcParams p) {
-  using Cfg = TcConfig<BLOCK_N>;
+  using Cfg = TcConfig<BLOCK_N, MT>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int ACC_STAGES = Cfg::ACC_STAGES;
+  constexpr int TILE_M = BLOCK_M * MT;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
@@ -138,7 +146,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           break;
         }
         const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-        const uint32_t sb = sa + A_STAGE_BYTES;
+        const uint32_t sb = sa + Cfg::A_BYTES;
         const uint32_t bar = full_bar(stage);
         mbar_arrive_expect_tx(bar, Cfg::STAGE_BYTES);
         const bool second = kb >= kb_main;
@@ -149,18 +157,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (second) {
           const int k2 = kb - kb_main;
           a_k = b_k = k2 * BLOCK_K;
-          a_r = m_blk * BLOCK_M;
+          a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
         } else if (p.bs_mode == 0) {
           a_k = b_k = kb * BLOCK_K;
-          a_r = m_blk * BLOCK_M;
+          a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
         } else if (p.bs_mode == 1) {
           // table row = output block; entry = (weight block f, input block j)
           const int t = kb / kpb, kk = kb - t * kpb;
           const int2 e = __ldg(reinterpret_cast<const int2*>(p.bs_index) + (n_blk / sub) * p.bs_nnz + t);
           a_k = e.y * p.bs_block + kk * BLOCK_K;
-          a_r = m_blk * BLOCK_M;
+          a_r = m_blk * TILE_M;
           b_k = kk * BLOCK_K;
           b_r = e.x * p.bs_block + (n_blk % sub) * BLOCK_N;
         } else if (p.bs_mode == 2) {
@@ -168,7 +176,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int t = kb / kpb, kk = kb - t * kpb;
           const int2 e = __ldg(reinterpret_cast<const int2*>(p.bs_index) + (n_blk / sub) * p.bs_nnz + t);
           a_k = e.y * p.bs_block + kk * BLOCK_K;
-          a_r = m_blk * BLOCK_M;
+          a_r = m_blk * TILE_M;
           b_k = e.x * p.bs_block + kk * BLOCK_K;
           b_r = (n_blk % sub) * BLOCK_N;
         } else {
@@ -180,9 +188,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if constexpr (A_MN) {
 #pragma unroll
-          for (int c = 0; c < BLOCK_M / 64; ++c) tma_load_2d(sa + c * CHUNK_BYTES, ma, bar, a_r + c * 64, a_k);
+          for (int c = 0; c < TILE_M / 64; ++c) tma_load_2d(sa + c * CHUNK_BYTES, ma, bar, a_r + c * 64, a_k);
         } else {
-          tma_load_2d(sa, ma, bar, a_k, a_r);
+#pragma unroll
+          for (int t = 0; t < MT; ++t) tma_load_2d(sa + t * A_STAGE_BYTES, ma, bar, a_k, a_r + t * BLOCK_M);
         }
         if constexpr (B_MN) {
 #pragma unroll
@@ -223,7 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
+      const uint32_t d_tmem = tmem_base + (MT == 2 ? 0 : acc_stage * BLOCK_N);
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
       const int kb_total = main_k_blocks(n_blk) + p.num_k2_blocks;
@@ -236,12 +245,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tc_fence_after();
         const uint32_t sa = smem_base + stage * Cfg::STAGE_BYTES;
-        const uint32_t sb = sa + A_STAGE_BYTES;
+        const uint32_t sb = sa + Cfg::A_BYTES;
 #pragma unroll
         for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-          const uint64_t da = make_smem_desc(sa + k * a_kstep, a_hi);
           const uint64_t db = make_smem_desc(sb + k * b_kstep, b_hi);
-          umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {  // the sub-tiles read the same B stage
+            const uint64_t da = make_smem_desc(sa + t * A_STAGE_BYTES + k * a_kstep, a_hi);
+            umma_bf16(d_tmem + t * BLOCK_N, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
         }
         umma_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
         if (++stage == STAGES) {
@@ -251,7 +263,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) break;
       umma_commit(tfull_bar(acc_stage));  // accumulator complete
-      if (++acc_stage == 2) {
+      if (++acc_stage == ACC_STAGES) {
         acc_stage = 0;
         acc_phase ^= 1u;
       }
@@ -274,14 +286,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       tc_fence_after();
-      const int64_t row0 = static_cast<int64_t>(m_blk) * BLOCK_M + quarter * 32;
       const bool acc_valid = main_k_blocks(n_blk) + p.num_k2_blocks > 0;  // empty reduction: acc is all zeros
-      const uint32_t t_acc = tmem_base + lane_addr + acc_stage * BLOCK_N;
-      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, (warp - 2) >> 2, 2);
+#pragma unroll 1
+      for (int t = 0; t < MT; ++t) {
+        const int64_t row0 = static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32;
+        const uint32_t t_acc = tmem_base + lane_addr + (MT == 2 ? t : acc_stage) * BLOCK_N;
+        epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, (warp - 2) >> 2, 2);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc_stage));
-      if (++acc_stage == 2) {
+      if (++acc_stage == ACC_STAGES) {
         acc_stage = 0;
         acc_phase ^= 1u;
       }
@@ -336,11 +351,11 @@ bool make_tmap_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t co
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int BLOCK_N>
+template <bool A_MN, bool B_MN, int BLOCK_N, int MT>
 static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2,
                                const CUtensorMap& b2, const TcParams& p, cudaStream_t st) {
-  using Cfg = TcConfig<BLOCK_N>;
-  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, BLOCK_N>;
+  using Cfg = TcConfig<BLOCK_N, MT>;
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, BLOCK_N, MT>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -373,8 +388,13 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
     tb2 = tb;
   }
   cudaError_t e;
-#define TC_GO(AM, BM, BN) e = tc_launch_t<AM, BM, BN>(ta, tb, ta2, tb2, p, st)
-  if (block_n == 256) {
+#define TC_GO(AM, BM, BN) e = tc_launch_t<AM, BM, BN, 1>(ta, tb, ta2, tb2, p, st)
+  if (block_n == 256 && p.m_subtiles == 2) {
+    if (!a_mn && !b_mn) e = tc_launch_t<false, false, 256, 2>(ta, tb, ta2, tb2, p, st);
+    else if (!a_mn && b_mn) e = tc_launch_t<false, true, 256, 2>(ta, tb, ta2, tb2, p, st);
+    else if (a_mn && b_mn) e = tc_launch_t<true, true, 256, 2>(ta, tb, ta2, tb2, p, st);
+    else return LEANFFN_ERR_UNSUPPORTED;
+  } else if (block_n == 256) {
     if (!a_mn && !b_mn) TC_GO(false, false, 256);
     else if (!a_mn && b_mn) TC_GO(false, true, 256);
     else if (a_mn && b_mn) TC_GO(true, true, 256);
