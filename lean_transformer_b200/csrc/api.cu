@@ -183,12 +183,26 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
       const char* v = getenv("LEANFFN_GEMM_TILE");
       return v != nullptr ? atoi(v) : 0;
     }();
+    static const int group_override = []() {
+      const char* v = getenv("LEANFFN_GROUP_M");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    p.group_m = group_override;
     p.m_subtiles = 1;
     if (d->bs_mode == 0 && block_n == 256 && d->M >= 256) {
       const int64_t k_total = k_eff + d->K2;
-      if (tile_override == 256 || (tile_override == 0 && k_total >= 4096)) {
+      // wave efficiency of a persistent grid: tiles / (waves * SMs); the larger tile must not quantise worse
+      const int sms = sm_count();
+      auto wave_eff = [sms](int64_t tiles) {
+        return static_cast<double>(tiles) / static_cast<double>(((tiles + sms - 1) / sms) * sms);
+      };
+      const int64_t tiles128 = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
+      const int64_t tiles256 = ((d->M + 255) / 256) * static_cast<int64_t>(p.num_n_blocks);
+      const bool pays = k_total >= 4096 && wave_eff(tiles256) >= wave_eff(tiles128) - 0.05;
+      if (tile_override == 256 || (tile_override == 0 && pays)) {
         p.m_subtiles = 2;
         p.num_m_blocks = static_cast<int32_t>((d->M + 255) / 256);
+        if (p.group_m == 0) p.group_m = 8;  // 8 x 256 rows per sweep: measured best for the 256 x 256 tiles
       }
     }
     cudaError_t ce;

@@ -77,6 +77,7 @@ struct TcParams {
   const int32_t* bs_count;  // entries per table row, or nullptr
   int32_t glu_split;  // > 0: B rows [n, n+128) and [glu_split + n, ...) form one 256-wide tile
   int32_t max_ctas;   // > 0: cap on the persistent grid
+  int32_t group_m;    // M-tiles that share one sweep over N in the tile order (0 = kernel default)
   int32_t m_subtiles; // one-CTA kernel: 1 = 128-row tiles (two accumulator stages), 2 = 256 x 256 tiles
   int32_t tune;       // experiment knobs of the CTA-pair kernel: bits 0-3 stages (0 = default), bit 4 spin-wait
   int32_t* status;
