@@ -28,10 +28,20 @@ sys.path.insert(0, str(ROOT))
 WORKLOADS = {
     "dense_bf16_h8192": dict(hidden=8192, inter=32768, total_tokens=65536, scaling="strong", dropout=0.0, mixed=False),
     "mixed_bf16_h1024": dict(hidden=1024, inter=4096, tokens_per_rank=16384, scaling="weak", dropout=0.1, mixed=True),
+    "pixelfly_bf16_h4096": dict(hidden=4096, inter=16384, tokens_per_rank=65536, scaling="weak", dropout=0.0, mixed=False,
+                                layout="pixelfly(block_size=128)", lowrank=128),
 }
 
 
-def flops_per_token(hidden, inter):
+def flops_per_token(hidden, inter, wl=None):
+    if wl is not None and wl.get("layout"):
+        # block-sparse + low rank: 6 * (nonzero weights of both projections + rank * (in + out) of both)
+        import math
+        block, rank = 128, wl["lowrank"]
+        m1, m2 = min(2 * inter, hidden) // block, min(inter, hidden) // block
+        per_row1, per_row2 = (int(math.log2(m1)) + 1) * (hidden // block) // m1, (int(math.log2(m2)) + 1) * (inter // block) // m2
+        nnz1, nnz2 = per_row1 * (2 * inter // block), per_row2 * (hidden // block)
+        return 6.0 * ((nnz1 + nnz2) * block * block + rank * (hidden + 2 * inter) + rank * (inter + hidden))
     return 18.0 * hidden * inter  # gated FFN: forward 6*H*I, backward 12*H*I
 
 
@@ -91,14 +101,25 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------------
 # CPU baseline / reference arm: the oracle (a CPU restatement of the reference's algorithm) on host cores
 # ------------------------------------------------------------------------------------------------------
-def cpu_step_time(hidden, inter, sample_tokens, steps, warmup, threads):
+def cpu_step_time(hidden, inter, sample_tokens, steps, warmup, threads, wl=None):
     from oracle import leanffn_oracle as O
 
     torch.set_num_threads(threads)
     gen = torch.Generator().manual_seed(0)
     rn = lambda *s: torch.randn(*s, generator=gen)  # noqa: E731
-    params = dict(ln_weight=torch.ones(hidden), ln_bias=torch.zeros(hidden), i2h_weight=0.02 * rn(2 * inter, hidden),
-                  i2h_bias=torch.zeros(2 * inter), h2o_weight=0.02 * rn(hidden, inter), h2o_bias=torch.zeros(hidden))
+    params = dict(ln_weight=torch.ones(hidden), ln_bias=torch.zeros(hidden), i2h_bias=torch.zeros(2 * inter),
+                  h2o_bias=torch.zeros(hidden))
+    if wl is not None and wl.get("layout"):
+        from lean_transformer_b200.blocksparse import layout as LY
+        for prefix, fin, fout in (("i2h", hidden, 2 * inter), ("h2o", inter, hidden)):
+            fwd, bwd = LY.get_indices_from_layout(LY.get_blocksparse_layout(fout, fin, wl["layout"]))
+            block = fin // bwd.shape[0]
+            params.update({f"{prefix}_weight": 0.02 * rn(fin, bwd.shape[1], block),
+                           f"{prefix}_lowrank_first": 0.02 * rn(wl["lowrank"], fin),
+                           f"{prefix}_lowrank_second": 0.02 * rn(fout, wl["lowrank"]),
+                           f"{prefix}_forward_indices": fwd, f"{prefix}_backward_indices": bwd})
+    else:
+        params.update(i2h_weight=0.02 * rn(2 * inter, hidden), h2o_weight=0.02 * rn(hidden, inter))
     x, g = rn(sample_tokens, hidden), rn(sample_tokens, hidden)
     times = []
     for i in range(warmup + steps):
@@ -124,7 +145,7 @@ def run_reference_arm(args, wl, name):
     hidden, inter = wl["hidden"], wl["inter"]
     threads = host_threads()
     sample = 512 if hidden >= 4096 else 4096
-    step_s = cpu_step_time(hidden, inter, sample, args.steps, args.warmup, threads)
+    step_s = cpu_step_time(hidden, inter, sample, args.steps, args.warmup, threads, wl)
     value = sample / step_s
     sample_desc = (f"{sample} tokens of the {name} workload per step (fp32, GeGLU, hidden {hidden}, intermediate {inter}), "
                    f"median of {args.steps} steps after {args.warmup} warm-up")
@@ -135,7 +156,7 @@ def run_reference_arm(args, wl, name):
                             parallelism="host cores only"),
                 cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=sample_desc),
                 e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
-                gflops=value * flops_per_token(hidden, inter) / 1e9)
+                gflops=value * flops_per_token(hidden, inter, wl) / 1e9)
     print(json.dumps(line), flush=True)
 
 
@@ -146,7 +167,12 @@ def build_module(wl, device):
     import lean_transformer_b200 as L
 
     torch.manual_seed(0)
-    ffn = L.LeanFFN(wl["hidden"], wl["inter"], gated=True, dropout=wl["dropout"])
+    i2h = h2o = None
+    if wl.get("layout"):
+        from lean_transformer_b200.blocksparse.linear import GeneralizedLinear, GeneralizedMatrix
+        i2h = GeneralizedLinear(GeneralizedMatrix(wl["hidden"], 2 * wl["inter"], wl["layout"], wl["lowrank"]))
+        h2o = GeneralizedLinear(GeneralizedMatrix(wl["inter"], wl["hidden"], wl["layout"], wl["lowrank"]))
+    ffn = L.LeanFFN(wl["hidden"], wl["inter"], gated=True, dropout=wl["dropout"], i2h_proj=i2h, h2o_proj=h2o)
     with torch.no_grad():
         for proj in (ffn.i2h_proj, ffn.h2o_proj):
             proj.bias.zero_()
@@ -155,6 +181,9 @@ def build_module(wl, device):
         gen = torch.Generator(device=device).manual_seed(0)
         for proj in (ffn.i2h_proj, ffn.h2o_proj):
             proj.weight.normal_(0.0, 0.02, generator=gen)
+            if wl.get("layout"):
+                proj.matrix.lowrank_first.normal_(0.0, 0.02, generator=gen)
+                proj.matrix.lowrank_second.normal_(0.0, 0.02, generator=gen)
     if not wl["mixed"]:
         ffn = ffn.bfloat16()
     return ffn.train()
@@ -309,13 +338,13 @@ def run_ours(args, wl, name):
 
     peaks = load_peaks()
     tokens_per_s = total_tokens * args.steps / seconds
-    tflops = tokens_per_s * flops_per_token(hidden, inter) / 1e12
+    tflops = tokens_per_s * flops_per_token(hidden, inter, wl) / 1e12
     achieved = gemm_flops / gemm_seconds / 1e12 if gemm_seconds > 0 else None
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = host_threads()
         sample = 512 if hidden >= 4096 else 4096
-        cpu_s = cpu_step_time(hidden, inter, sample, 3, 1, threads)
+        cpu_s = cpu_step_time(hidden, inter, sample, 3, 1, threads, wl)
         cpu = dict(value=sample / cpu_s, unit="tokens/s", cores=threads, kind="port",
                    sample=f"{sample} tokens of the {name} workload per step in fp32 on the host cores "
                           f"(CPU restatement of the reference's LeanFFN), median of 3 steps after 1 warm-up")
@@ -381,7 +410,7 @@ def quick_measure(wl, device, args):
     torch.cuda.synchronize()
     L.check_device_status(device)
     s = a.elapsed_time(b) * 1e-3 / n
-    return dict(tokens_per_s=tokens / s, ms_per_step=s * 1e3, tflops=tokens / s * flops_per_token(hidden, wl["inter"]) / 1e12,
+    return dict(tokens_per_s=tokens / s, ms_per_step=s * 1e3, tflops=tokens / s * flops_per_token(hidden, wl["inter"], wl) / 1e12,
                 config=dict(hidden=hidden, intermediate=wl["inter"], tokens=tokens, dropout=wl["dropout"],
                             parameters="fp32 masters + bf16 compute" if wl["mixed"] else "bf16"))
 

@@ -105,7 +105,8 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   if (d->K2 > 0)
     tc = tc && aligned16(d->A2) && aligned16(d->B2) && pitch16(d->lda2, LEANFFN_BF16) && pitch16(d->ldb2, LEANFFN_BF16);
   if (d->bias != nullptr) tc = tc && aligned16(d->bias);
-  if (d->aux != nullptr) tc = tc && aligned16(d->aux) && pitch16(d->ldaux, d->aux_dtype);
+  if (d->aux != nullptr) tc = tc && aligned16(d->aux) && pitch16(d->ldaux, d->aux_dtype) &&
+              (d->aux_dtype == LEANFFN_BF16 || epi == LEANFFN_EPI_DROPOUT_RESIDUAL);
   if (d->D2 != nullptr) tc = tc && aligned16(d->D2) && pitch16(d->ldd2, d->d_dtype);
   if (needs_d2) tc = tc && d->d_dtype == LEANFFN_BF16;
   if (epi == LEANFFN_EPI_GLU_FWD) tc = tc && (d->N / 2) % 8 == 0 && d->bs_mode == 0;

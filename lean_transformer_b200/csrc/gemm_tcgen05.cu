@@ -412,3 +412,5 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
 }
 
 }  // namespace leanffn
+
+

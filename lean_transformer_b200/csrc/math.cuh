@@ -147,6 +147,38 @@ __device__ __forceinline__ float act_fwd(int act, float x) {
   }
 }
 
+// Compile-time selected variants for the GEMM epilogues: ACT >= 0 inlines exactly one activation (small code, the
+// hot loops stay in the instruction cache); ACT < 0 falls back to the run-time switch.
+template <int ACT, bool FAST>
+__device__ __forceinline__ float act_fwd_t(int act, float x) {
+  if constexpr (ACT == LEANFFN_ACT_GELU_TANH) {
+    return 0.5f * x * (1.0f + tanh_f<FAST>(0.79788456f * x * (1.0f + 0.044715f * x * x)));
+  } else if constexpr (ACT == LEANFFN_ACT_SILU) {
+    return x * sigmoid_f<FAST>(x);
+  } else if constexpr (ACT == LEANFFN_ACT_RELU) {
+    return x > 0.0f ? x : 0.0f;
+  } else {
+    return act_fwd<FAST>(act, x);
+  }
+}
+template <int ACT, bool FAST>
+__device__ __forceinline__ void act_fwd_bwd_t(int act, float x, float& y, float& d) {
+  if constexpr (ACT == LEANFFN_ACT_GELU_TANH) {
+    const float t = tanh_f<FAST>(0.79788456f * x * (1.0f + 0.044715f * x * x));
+    y = 0.5f * x * (1.0f + t);
+    d = 0.5f * x * ((1.0f - t * t) * (0.79788456f + 0.1070322243f * x * x)) + 0.5f * (1.0f + t);
+  } else if constexpr (ACT == LEANFFN_ACT_SILU) {
+    const float s = sigmoid_f<FAST>(x);
+    y = x * s;
+    d = s * (1.0f + x * (1.0f - s));
+  } else if constexpr (ACT == LEANFFN_ACT_RELU) {
+    y = x > 0.0f ? x : 0.0f;
+    d = x > 0.0f ? 1.0f : 0.0f;
+  } else {
+    act_fwd_bwd<FAST>(act, x, y, d);
+  }
+}
+
 // ---- Philox4x32-10 ----------------------------------------------------------------------------
 // Counter (g lo, g hi, 0, 0) with g = element_index >> 2, key (seed lo, seed hi); element e uses
 // output word e & 3.

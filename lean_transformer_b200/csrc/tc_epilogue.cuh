@@ -1,8 +1,12 @@
 // Epilogue of the tcgen05 GEMM kernels.  A warp reads a 32-row x 32-column block of the fp32 accumulator from
-// tensor memory (tcgen05.ld gives lane i the 32 columns of row i), transposes it through a private shared-memory
-// patch so that four neighbouring lanes own 32 consecutive bytes-or-more of ONE output row, and then applies the
-// fused epilogue with fully used 32-byte sectors on every global load and store:
+// tensor memory (tcgen05.ld gives lane i the 32 columns of row i), adds the bias, rounds to bf16 and transposes the
+// block through a private shared-memory patch so that four neighbouring lanes own 64 consecutive bytes of ONE
+// output row; the fused epilogue then runs with fully used 32-byte sectors on every global load and store:
 //   lane l, step i (0..3):  row = 8*i + l/4,  columns (l%4)*8 .. +7 of the block.
+// The patch is exchanged as packed bf16 in 16-byte pieces (4 vector stores + 4 vector loads per lane and block):
+// the main loop's TMA writes and tensor-core operand reads keep shared memory busy, so the epilogue has to be
+// frugal with it.  Every intermediate of the fused block is a bf16 tensor in the unfused formulation, hence the
+// early rounding changes no result.  Plain fp32 outputs (weight gradients into fp32 masters) keep an fp32 exchange.
 // Shared by the one-CTA and the CTA-pair kernels; EPI_WARPS warps split the column blocks of a tile.
 #pragma once
 #include "gemm_common.cuh"
@@ -10,7 +14,8 @@
 
 namespace leanffn {
 
-constexpr int EPI_PATCH_FLOATS = 32 * 33;  // per-warp transposition patch (row pitch 33: conflict-free)
+constexpr int EPI_PATCH_FLOATS = 32 * 33;  // per-warp patch: fp32 exchange uses row pitch 33 (conflict-free);
+                                           // the bf16 exchange uses its first 2 KiB
 
 __device__ __forceinline__ void load8(const void* base, int32_t dtype, int64_t elem, float (&v)[8]) {
   if (dtype == LEANFFN_BF16) {
@@ -43,6 +48,73 @@ __device__ __forceinline__ void store8(void* base, int32_t dtype, int64_t elem, 
   }
 }
 
+__device__ __forceinline__ void unpack8(const uint4& w, float (&v)[8]) {
+  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u[h]);
+    v[2 * h] = __low2float(b);
+    v[2 * h + 1] = __high2float(b);
+  }
+}
+__device__ __forceinline__ void store_packed8(void* base, int32_t dtype, int64_t elem, const uint4& w) {
+  if (dtype == LEANFFN_BF16) {
+    *reinterpret_cast<uint4*>(static_cast<bf16*>(base) + elem) = w;
+  } else {
+    float v[8];
+    unpack8(w, v);
+    store8(base, dtype, elem, v);
+  }
+}
+
+// Bias of the 32 columns first .. first+31 (same for every lane: broadcast loads).  Columns at or beyond `limit`
+// read as 0; limit and first are multiples of 8.
+__device__ __forceinline__ void load_bias32(const void* bias, int32_t dtype, int64_t first, int64_t limit,
+                                            float (&b)[32]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (bias != nullptr && first + 8 * c < limit) load8(bias, dtype, first + 8 * c, t);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) b[8 * c + q] = t[q];
+  }
+}
+
+// Byte offset of 16-byte piece `chunk` (8 bf16 columns) of `row` inside the bf16 patch.  Row pitch 64 B with the
+// piece index XOR-ed by bits 1-2 of the row: both the row-wise vector stores (8 lanes = 8 rows, one piece) and the
+// transposed vector loads (8 lanes = 2 rows x 4 pieces) touch 8 distinct 16-byte bank groups.
+__device__ __forceinline__ uint32_t patch_offset(int row, int chunk) {
+  return static_cast<uint32_t>(row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4));
+}
+
+// TMEM block (lane = row) + bias, rounded to bf16 ->  w[i] = 8 packed values of (row 8*i + lane/4,
+// columns (lane%4)*8 .. +7) of the block.
+__device__ __forceinline__ void load_block_bf16(uint32_t taddr, float* patch, int lane, bool valid,
+                                                const float (&bias)[32], uint4 (&w)[4]) {
+  uint32_t r[32];
+  __syncwarp();
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+  char* base = reinterpret_cast<char*>(patch);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float f[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] = (valid ? __uint_as_float(r[8 * c + q]) : 0.f) + bias[8 * c + q];
+    uint4 p;
+    p.x = pack_bf16x2(f[0], f[1]);
+    p.y = pack_bf16x2(f[2], f[3]);
+    p.z = pack_bf16x2(f[4], f[5]);
+    p.w = pack_bf16x2(f[6], f[7]);
+    *reinterpret_cast<uint4*>(base + patch_offset(lane, c)) = p;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    w[i] = *reinterpret_cast<const uint4*>(base + patch_offset(8 * i + (lane >> 2), lane & 3));
+  __syncwarp();
+}
+
 // TMEM block (lane = row) -> v[i][j] = element (row 8*i + lane/4, column (lane%4)*8 + j) of the block.
 __device__ __forceinline__ void load_block_transposed(uint32_t taddr, float* patch, int lane, bool valid,
                                                       float (&v)[4][8]) {
@@ -60,85 +132,194 @@ __device__ __forceinline__ void load_block_transposed(uint32_t taddr, float* pat
   __syncwarp();
 }
 
+// Activation on 8 values.  ACT >= 0: one inlined activation.  ACT < 0: the run-time switch lives in ONE
+// out-of-line copy, so rarely used activations do not bloat (and evict) the hot epilogue code.
+static __device__ __noinline__ void act_fwd8_generic(int act, float* x) {
+  for (int q = 0; q < 8; ++q) x[q] = act_fwd<true>(act, x[q]);
+}
+static __device__ __noinline__ void act_fwd_bwd8_generic(int act, float* x, float* d) {
+  for (int q = 0; q < 8; ++q) {
+    float y, dd;
+    act_fwd_bwd<true>(act, x[q], y, dd);
+    x[q] = y, d[q] = dd;
+  }
+}
+template <int ACT>
+__device__ __forceinline__ void act_fwd8(int act, const float (&x)[8], float (&y)[8]) {
+  if constexpr (ACT >= 0) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) y[q] = act_fwd_t<ACT, true>(act, x[q]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) y[q] = x[q];
+    act_fwd8_generic(act, y);
+  }
+}
+template <int ACT>
+__device__ __forceinline__ void act_fwd_bwd8(int act, const float (&x)[8], float (&y)[8], float (&d)[8]) {
+  if constexpr (ACT >= 0) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) act_fwd_bwd_t<ACT, true>(act, x[q], y[q], d[q]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) y[q] = x[q];
+    act_fwd_bwd8_generic(act, y, d);
+  }
+}
+
 // One warp's share of a 128-row accumulator tile: TMEM lanes [quarter*32, +32), column blocks
 // block_begin, block_begin + block_step, ...  t_acc = TMEM address of (lane quarter*32, first column of the tile);
 // row0 = global row of TMEM lane quarter*32; n_blk = tile index along N (gated forward: along the
-// intermediate dimension).
-template <int BLOCK_N>
-__device__ __forceinline__ void epilogue_tile(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
-                                              int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
-                                              int block_step, bool skip_store = false) {
+// intermediate dimension).  KIND / ACT are compile-time so that each launch runs a small, cache-resident loop.
+template <int BLOCK_N, int KIND, int ACT>
+__device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
+                                                int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
+                                                int block_step, bool skip_store) {
   const int sub_row = lane >> 2;        // + 8*i
   const int sub_col = (lane & 3) * 8;   // within the 32-column block
-  if (ep.kind == LEANFFN_EPI_GLU_FWD) {
+  if constexpr (KIND == LEANFFN_EPI_GLU_FWD) {
     if constexpr (BLOCK_N == 256) {
       // tile columns [0,128): gate, [128,256): linear half; output feature j = n_blk*128 + column
       const int inter = glu_split;
 #pragma unroll 1
       for (int blk = block_begin; blk < 4; blk += block_step) {
-        float g[4][8], l[4][8];
-        load_block_transposed(t_acc + blk * 32, patch, lane, acc_valid, g);
-        load_block_transposed(t_acc + 128 + blk * 32, patch, lane, acc_valid, l);
-        const int64_t j = static_cast<int64_t>(n_blk) * 128 + blk * 32 + sub_col;
-        if (j >= inter || skip_store) continue;
-        float bg[8] = {0, 0, 0, 0, 0, 0, 0, 0}, bl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (ep.bias != nullptr) {
-          load8(ep.bias, ep.bias_dtype, j, bg);
-          load8(ep.bias, ep.bias_dtype, inter + j, bl);
+        const int64_t j0 = static_cast<int64_t>(n_blk) * 128 + blk * 32;
+        const int64_t j = j0 + sub_col;
+        const bool live = j < inter && !skip_store;
+        uint4 g[4], l[4];
+        {
+          float bias[32];
+          load_bias32(ep.bias, ep.bias_dtype, j0, inter, bias);
+          load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, g);
         }
+        {
+          float bias[32];
+          load_bias32(ep.bias, ep.bias_dtype, inter + j0, 2 * static_cast<int64_t>(inter), bias);
+          load_block_bf16(t_acc + 128 + blk * 32, patch, lane, acc_valid, bias, l);
+        }
+        if (!live) continue;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int64_t row = row0 + 8 * i + sub_row;
           if (row >= ep.M) continue;
-          float h[8];
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + j, g[i]);
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + inter + j, l[i]);
+          float gf[8], lf[8], h[8];
+          unpack8(g[i], gf);
+          unpack8(l[i], lf);
+          act_fwd8<ACT>(ep.act, gf, h);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            g[i][q] = bf16_round(g[i][q] + bg[q]);
-            l[i][q] = bf16_round(l[i][q] + bl[q]);
-            h[q] = bf16_round(act_fwd<true>(ep.act, g[i][q])) * l[i][q];
-          }
-          store8(ep.D, ep.d_dtype, row * ep.ldd + j, g[i]);
-          store8(ep.D, ep.d_dtype, row * ep.ldd + inter + j, l[i]);
+          for (int q = 0; q < 8; ++q) h[q] = bf16_round(h[q]) * lf[q];
           store8(ep.D2, ep.d_dtype, row * ep.ldd2 + j, h);
         }
       }
     }
     return;
-  }
+  } else if constexpr (KIND == LEANFFN_EPI_STORE) {
+    if (ep.d_dtype != LEANFFN_BF16) {
+      // full-precision output: fp32 exchange
 #pragma unroll 1
-  for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
-    float v[4][8];
-    load_block_transposed(t_acc + blk * 32, patch, lane, acc_valid, v);
-    const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32 + sub_col;
-    if (col >= ep.N || skip_store) continue;
-    float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (ep.bias != nullptr) load8(ep.bias, ep.bias_dtype, col, b);
+      for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
+        const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32 + sub_col;
+        const bool live = col < ep.N && !skip_store;
+        float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (live && ep.bias != nullptr) load8(ep.bias, ep.bias_dtype, col, b);
+        float v[4][8];
+        load_block_transposed(t_acc + blk * 32, patch, lane, acc_valid, v);
+        if (!live) continue;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int64_t row = row0 + 8 * i + sub_row;
-      if (row >= ep.M) continue;
-      float(&x)[8] = v[i];
-      switch (ep.kind) {
-        case LEANFFN_EPI_STORE: {
+        for (int i = 0; i < 4; ++i) {
+          const int64_t row = row0 + 8 * i + sub_row;
+          if (row >= ep.M) continue;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) x[q] += b[q];
-          store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
-          break;
+          for (int q = 0; q < 8; ++q) v[i][q] += b[q];
+          store8(ep.D, ep.d_dtype, row * ep.ldd + col, v[i]);
         }
-        case LEANFFN_EPI_ACT_FWD: {
-          float h[8];
+      }
+      return;
+    }
+#pragma unroll 1
+    for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
+      const int64_t col0 = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
+      const int64_t col = col0 + sub_col;
+      const bool live = col < ep.N && !skip_store;
+      uint4 w[4];
+      {
+        float bias[32];
+        load_bias32(ep.bias, ep.bias_dtype, col0, ep.N, bias);
+        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w);
+      }
+      if (!live) continue;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            x[q] = bf16_round(x[q] + b[q]);
-            h[q] = act_fwd<true>(ep.act, x[q]);
+      for (int i = 0; i < 4; ++i) {
+        const int64_t row = row0 + 8 * i + sub_row;
+        if (row < ep.M) store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, w[i]);
+      }
+    }
+  } else {
+    // The residual / pre-activation rows (bf16) of a block are requested one block ahead and stay packed in
+    // registers until used: the loads of block b+1 are in flight while block b is read from tensor memory,
+    // computed and stored, which doubles the bytes in flight per warp.
+    constexpr bool HAS_AUX =
+        KIND == LEANFFN_EPI_DROPOUT_RESIDUAL || KIND == LEANFFN_EPI_GLU_BWD || KIND == LEANFFN_EPI_ACT_BWD;
+    constexpr int NUM_BLOCKS = BLOCK_N / 32;
+    uint4 n0[4], n1[4];
+    auto request_aux = [&](int blk) {
+      const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32 + sub_col;
+      const bool live = col < ep.N && !skip_store && ep.aux != nullptr;
+      const bf16* aux = static_cast<const bf16*>(ep.aux);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t row = row0 + 8 * i + sub_row;
+        const bool ok = live && row < ep.M;
+        n0[i] = n1[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (ok) {
+          if (KIND == LEANFFN_EPI_DROPOUT_RESIDUAL && ep.aux_dtype == LEANFFN_F32) {
+            // fp32 residual: the 8 columns fill both register sets (n0: columns 0-3, n1: columns 4-7)
+            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(ep.aux) + row * ep.ldaux + col);
+            n0[i] = __ldg(src);
+            n1[i] = __ldg(src + 1);
+          } else {
+            n0[i] = __ldg(reinterpret_cast<const uint4*>(aux + row * ep.ldaux + col));
+            if constexpr (KIND == LEANFFN_EPI_GLU_BWD)
+              n1[i] = __ldg(reinterpret_cast<const uint4*>(aux + row * ep.ldaux + ep.N + col));
           }
-          store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
-          store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, h);
-          break;
         }
-        case LEANFFN_EPI_DROPOUT_RESIDUAL: {
+      }
+    };
+    if constexpr (HAS_AUX) {
+      if (block_begin < NUM_BLOCKS) request_aux(block_begin);
+    }
+#pragma unroll 1
+    for (int blk = block_begin; blk < NUM_BLOCKS; blk += block_step) {
+      const int64_t col0 = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
+      const int64_t col = col0 + sub_col;
+      const bool live = col < ep.N && !skip_store;
+      uint4 c0[4], c1[4];
+      if constexpr (HAS_AUX) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) x[q] += b[q];
+        for (int i = 0; i < 4; ++i) c0[i] = n0[i], c1[i] = n1[i];
+        if (blk + block_step < NUM_BLOCKS) request_aux(blk + block_step);
+      }
+      uint4 w[4];
+      {
+        float bias[32];
+        load_bias32(ep.bias, ep.bias_dtype, col0, ep.N, bias);
+        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w);
+      }
+      if (!live) continue;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t row = row0 + 8 * i + sub_row;
+        if (row >= ep.M) continue;
+        float x[8];
+        unpack8(w[i], x);
+        if constexpr (KIND == LEANFFN_EPI_ACT_FWD) {
+          float h[8];
+          act_fwd8<ACT>(ep.act, x, h);
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, w[i]);
+          store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, h);
+        } else if constexpr (KIND == LEANFFN_EPI_DROPOUT_RESIDUAL) {
           if (ep.threshold != 0u) {
             const uint64_t e0 = ep.elem_offset + static_cast<uint64_t>(row) * ep.N + col;
 #pragma unroll
@@ -149,53 +330,79 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams& ep, int glu_split
               for (int h = 0; h < 4; ++h) x[q * 4 + h] = keep[h] ? x[q * 4 + h] * ep.keep_scale : 0.f;
             }
           }
-          if (ep.aux != nullptr) {
-            float a[8];
-            load8(ep.aux, ep.aux_dtype, row * ep.ldaux + col, a);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) x[q] += a[q];
+          float res[8];
+          if (ep.aux_dtype == LEANFFN_F32) {
+            res[0] = __uint_as_float(c0[i].x), res[1] = __uint_as_float(c0[i].y);
+            res[2] = __uint_as_float(c0[i].z), res[3] = __uint_as_float(c0[i].w);
+            res[4] = __uint_as_float(c1[i].x), res[5] = __uint_as_float(c1[i].y);
+            res[6] = __uint_as_float(c1[i].z), res[7] = __uint_as_float(c1[i].w);
+          } else {
+            unpack8(c0[i], res);
           }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) x[q] += res[q];
           store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
-          break;
-        }
-        case LEANFFN_EPI_GLU_BWD: {
-          // x = dHid[row, col..]; aux = pre [M, 2N]; D = dPre [M, 2N]; D2 = hid [M, N] (optional)
-          float g[8], l[8], dl[8];
-          load8(ep.aux, ep.aux_dtype, row * ep.ldaux + col, g);
-          load8(ep.aux, ep.aux_dtype, row * ep.ldaux + ep.N + col, l);
+        } else if constexpr (KIND == LEANFFN_EPI_GLU_BWD) {
+          // x = dHid[row, col..]; aux = pre [M, 2N] (a0 gate, a1 linear); D = dPre [M, 2N]; D2 = hid [M, N] (optional)
+          float gate[8], lin[8], y[8], d[8], dl[8];
+          unpack8(c0[i], gate);
+          unpack8(c1[i], lin);
+          act_fwd_bwd8<ACT>(ep.act, gate, y, d);
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            float y, d;
-            act_fwd_bwd<true>(ep.act, g[q], y, d);
-            y = bf16_round(y);
-            dl[q] = x[q] * y;        // d/d(linear half)
-            g[q] = x[q] * l[q] * d;  // d/d(gate)
-            l[q] = y * l[q];         // rematerialised hid
+            y[q] = bf16_round(y[q]);
+            dl[q] = x[q] * y[q];          // d/d(linear half)
+            d[q] = x[q] * lin[q] * d[q];  // d/d(gate)
+            y[q] = y[q] * lin[q];         // rematerialised hid
           }
-          store8(ep.D, ep.d_dtype, row * ep.ldd + col, g);
+          store8(ep.D, ep.d_dtype, row * ep.ldd + col, d);
           store8(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl);
-          if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, l);
-          break;
-        }
-        case LEANFFN_EPI_ACT_BWD: {
-          float g[8], h[8];
-          load8(ep.aux, ep.aux_dtype, row * ep.ldaux + col, g);
+          if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, y);
+        } else if constexpr (KIND == LEANFFN_EPI_ACT_BWD) {
+          float pre[8], y[8], d[8];
+          unpack8(c0[i], pre);
+          act_fwd_bwd8<ACT>(ep.act, pre, y, d);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float y, d;
-            act_fwd_bwd<true>(ep.act, g[q], y, d);
-            x[q] *= d;
-            h[q] = y;
-          }
+          for (int q = 0; q < 8; ++q) x[q] *= d[q];
           store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
-          if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, h);
-          break;
+          if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, y);
         }
-        default:
-          break;
       }
     }
   }
+}
+
+template <int BLOCK_N, int KIND>
+__device__ __forceinline__ void epilogue_tile_act(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
+                                                  int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
+                                                  int block_step, bool skip_store) {
+  // gelu_fused and silu get their own inlined loops; everything else shares the out-of-line switch
+  if (ep.act == LEANFFN_ACT_GELU_TANH)
+    epilogue_tile_t<BLOCK_N, KIND, LEANFFN_ACT_GELU_TANH>(ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane,
+                                                          block_begin, block_step, skip_store);
+  else if (ep.act == LEANFFN_ACT_SILU)
+    epilogue_tile_t<BLOCK_N, KIND, LEANFFN_ACT_SILU>(ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane,
+                                                     block_begin, block_step, skip_store);
+  else
+    epilogue_tile_t<BLOCK_N, KIND, -1>(ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, block_begin,
+                                       block_step, skip_store);
+}
+
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_tile(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
+                                              int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
+                                              int block_step, bool skip_store = false) {
+#define LEANFFN_EPI_ARGS ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, block_begin, block_step, skip_store
+  switch (ep.kind) {
+    case LEANFFN_EPI_STORE: epilogue_tile_t<BLOCK_N, LEANFFN_EPI_STORE, -1>(LEANFFN_EPI_ARGS); break;
+    case LEANFFN_EPI_DROPOUT_RESIDUAL: epilogue_tile_t<BLOCK_N, LEANFFN_EPI_DROPOUT_RESIDUAL, -1>(LEANFFN_EPI_ARGS); break;
+    case LEANFFN_EPI_GLU_FWD: epilogue_tile_act<BLOCK_N, LEANFFN_EPI_GLU_FWD>(LEANFFN_EPI_ARGS); break;
+    case LEANFFN_EPI_ACT_FWD: epilogue_tile_act<BLOCK_N, LEANFFN_EPI_ACT_FWD>(LEANFFN_EPI_ARGS); break;
+    case LEANFFN_EPI_GLU_BWD: epilogue_tile_act<BLOCK_N, LEANFFN_EPI_GLU_BWD>(LEANFFN_EPI_ARGS); break;
+    case LEANFFN_EPI_ACT_BWD: epilogue_tile_act<BLOCK_N, LEANFFN_EPI_ACT_BWD>(LEANFFN_EPI_ARGS); break;
+    default: break;
+  }
+#undef LEANFFN_EPI_ARGS
 }
 
 }  // namespace leanffn
