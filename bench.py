@@ -45,6 +45,12 @@ def flops_per_token(hidden, inter, wl=None):
     return 18.0 * hidden * inter  # gated FFN: forward 6*H*I, backward 12*H*I
 
 
+# DRAM bytes (read + written) per GEMM launch and per token of the GPU's shard, from one `ncu --set full` capture of the
+# six GEMMs of a step at 8192 tokens (profiles/gemm_tcgen05_dense_bf16_h8192_tokens8192.md): 37.45 GB over 6 launches.
+# Operand re-reads and activation traffic both grow with the token count, so the figure is scaled by tokens.
+GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH = {"dense_bf16_h8192": 37.45e9 / 6 / 8192}
+
+
 def load_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -362,7 +368,10 @@ def run_ours(args, wl, name):
         tflops=tflops, pct_of_bf16_peak_measured_burst=100.0 * tflops / world / peaks["bf16"],
         pct_of_bf16_peak_datasheet=100.0 * tflops / world / 2250.0,
         roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
-                      frac=(achieved / peaks["bf16_sustained"]) if achieved else None, traffic=None,
+                      frac=(achieved / peaks["bf16_sustained"]) if achieved else None,
+                      traffic=(GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH[name] * tokens
+                               if name in GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH else None),
+                      traffic_unit="bytes per launch (ncu dram read + write of a smaller capture, scaled by tokens)",
                       kernel="gemm_tcgen05_kernel (all GEMM launches of the timed region)", launches=gemm_launches,
                       peak_source=f"bf16_tflops_sustained of {peaks['source']} peaks (kernel timed inside a long step)"),
         cpu_baseline=cpu,
