@@ -103,11 +103,13 @@ def linear_forward_core(x2d, weight, bias, lowrank_first, lowrank_second, forwar
 
 def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_second, forward_indices,
                          backward_indices, matmul_op, needs_input_grad, cdt, *, dgrad_epilogue=N.EPI_STORE, act=0,
-                         dgrad_aux=None, dgrad_out=None, dgrad_out2=None, bias_dtype=None):
+                         dgrad_aux=None, dgrad_out=None, dgrad_out2=None, bias_dtype=None, on_param_grads=None):
     """Gradients of linear_forward_core in the reference's order
     (input, weight, bias, lowrank_first, lowrank_second); ``x2d`` / ``dy2d`` are in the compute dtype.
     Weight-like gradients come back in their parameter's dtype.  The input gradient may carry a fused
-    activation-backward epilogue (dense W only)."""
+    activation-backward epilogue (dense W only).  ``on_param_grads(weight, bias, lowrank_first, lowrank_second)``
+    is called once the parameter gradients are launched and before the input gradient is, so a data-parallel
+    caller can start their reduction underneath the input-gradient product."""
     kind = _kind(weight, forward_indices, backward_indices, matmul_op)
     need_x, need_w, need_b, need_l1, need_l2 = (list(needs_input_grad) + [False] * 5)[:5]
     grad_input = grad_weight = grad_bias = grad_l1 = grad_l2 = None
@@ -135,6 +137,8 @@ def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_
             grad_weight = _bs_wgrad(dy2d, x2d, weight, tables[2], weight.dtype)
         else:
             grad_weight = _bs_wgrad(dy2d, x2d, weight, matmul_op._tables(dy2d.device)[4], weight.dtype)
+    if on_param_grads is not None:
+        on_param_grads(grad_weight, grad_bias, grad_l1, grad_l2)
     if need_x:
         w = cast_cached(weight, cdt)
         a2, b2 = (grad_lowrank_hid, l1) if has_lowrank else (None, None)

@@ -319,10 +319,10 @@ class _LeanFFN(torch.autograd.Function):
         (grad_input_ln, grad_i2h_weight, grad_i2h_bias, grad_i2h_lowrank_first,
          grad_i2h_lowrank_second) = linear_backward_core(
             grad_pre, input_ln, i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second,
-            i2h_forward_indices, i2h_backward_indices, ctx._i2h_matmul_op, i2h_needs, cdt)
+            i2h_forward_indices, i2h_backward_indices, ctx._i2h_matmul_op, i2h_needs, cdt,
+            on_param_grads=lambda w, b, l1, l2: _notify(i2h_weight=w, i2h_bias=b, i2h_lowrank_first=l1,
+                                                        i2h_lowrank_second=l2))
         del grad_pre, input_ln
-        _notify(i2h_weight=grad_i2h_weight, i2h_bias=grad_i2h_bias, i2h_lowrank_first=grad_i2h_lowrank_first,
-                i2h_lowrank_second=grad_i2h_lowrank_second)
 
         grad_input = grad_ln_weight = grad_ln_bias = None
         if need_input_side:
