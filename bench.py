@@ -226,9 +226,24 @@ def run_ours(args, wl, name):
     gen = torch.Generator(device=device).manual_seed(1000 + rank)
     x_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(in_dtype)
     g_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(torch.bfloat16)
-    sync = ldist.GradSync(wire_dtype=torch.bfloat16, comm_sms=args.comm_sms, measure_tail=True) if world > 1 else None
+    sync = (ldist.GradSync(wire_dtype=torch.bfloat16, comm_sms=args.comm_sms if args.grad_exchange == "nccl" else None,
+                           measure_tail=True, params=params) if world > 1 else None)
+    reducer = None
+    exchange_note = args.grad_exchange
     if world > 1:
         lffn.set_grad_ready_hook(sync.reduce)
+        if args.grad_exchange == "fused" and not wl.get("layout"):
+            # the two dense weight gradients are reduce-scattered inside their GEMMs; NCCL keeps the small tensors
+            from lean_transformer_b200.blocksparse.linear import set_weight_grad_reducer
+            try:
+                reducer = ldist.ScatteredGradReducer({"i2h_weight": ffn.i2h_proj.weight, "h2o_weight": ffn.h2o_proj.weight})
+                set_weight_grad_reducer(reducer)
+            except Exception as e:  # no peer-mapped memory on this machine: every gradient goes through NCCL
+                exchange_note = f"nccl (peer-mapped buffer unavailable: {type(e).__name__})"
+                sync.comm_sms = args.comm_sms
+        elif args.grad_exchange == "fused":
+            exchange_note = "nccl (block-sparse weights)"
+            sync.comm_sms = args.comm_sms
 
     from lean_transformer_b200.blocksparse.linear import clear_cast_cache
 
@@ -237,12 +252,16 @@ def run_ours(args, wl, name):
             clear_cast_cache()  # a real step updates the fp32 masters, so their bf16 copies are rebuilt every step
         for p in params:
             p.grad = None
+        if reducer is not None:
+            reducer.begin_step()
         x = x.requires_grad_(True)
         with torch.autocast("cuda", dtype=torch.bfloat16, enabled=wl["mixed"]):
             out = ffn(x)
         out.backward(g)
         if sync is not None:
             sync.finish()
+        if reducer is not None:
+            reducer.finish()
         return out
 
     def barrier():
@@ -283,10 +302,12 @@ def run_ours(args, wl, name):
     if args.skip_e2e:
         if rank == 0:
             print(json.dumps(dict(profiling_run=True, workload=name, tokens=total_tokens, ms_per_step=seconds / args.steps * 1e3,
-                                  exposed_allreduce_ms=exposed_ms, comm_sms=args.comm_sms,
+                                  exposed_allreduce_ms=exposed_ms, comm_sms=args.comm_sms, grad_exchange=exchange_note,
                                   gemm_tflops=gemm_flops / gemm_seconds / 1e12 if gemm_seconds else None)), flush=True)
         if world > 1:
             lffn.set_grad_ready_hook(None)
+            if reducer is not None:
+                set_weight_grad_reducer(None)
             dist.destroy_process_group()
         return
 
@@ -343,6 +364,8 @@ def run_ours(args, wl, name):
 
     if world > 1:
         lffn.set_grad_ready_hook(None)
+        if reducer is not None:
+            set_weight_grad_reducer(None)
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -366,8 +389,10 @@ def run_ours(args, wl, name):
         config=dict(workload=name, hidden=hidden, intermediate=inter, gated=True, activation="gelu_fused",
                     dropout=wl["dropout"], total_tokens=total_tokens, tokens_per_gpu=tokens,
                     parameters="fp32 masters + bf16 compute (autocast)" if wl["mixed"] else "bf16",
-                    parallelism=f"dp{world} token partition" + (", bf16 gradient all-reduce overlapped with backward"
-                                                                 if world > 1 else ""),
+                    parallelism=f"dp{world} token partition" + (
+                        "" if world == 1 else ", weight gradients reduce-scattered inside their GEMMs (NVLink peer atomics) "
+                        "+ copy-engine all-gather, NCCL for the small tensors" if reducer is not None
+                        else ", bf16 gradient all-reduce (NCCL) overlapped with backward"),
                     l2="inputs and activations exceed the 126 MB L2 (no flush needed)",
                     step="forward + backward" + (" + gradient all-reduce" if world > 1 else "")),
         tflops=tflops, pct_of_bf16_peak_measured_burst=100.0 * tflops / world / peaks["bf16"],
@@ -388,6 +413,7 @@ def run_ours(args, wl, name):
         gpu_launches=launches, clocks=clocks)
     if world > 1:
         line["comm"] = dict(exposed_allreduce_ms_per_step=exposed_ms, sms_left_to_nccl=args.comm_sms,
+                            grad_exchange=exchange_note,
                             note="time the compute stream of rank 0 waited for gradient all-reduces after its last kernel")
     if extra:
         line["other_workloads"] = extra
@@ -441,6 +467,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="dense_bf16_h8192")
     ap.add_argument("--extra-workload", default="mixed_bf16_h1024")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to NCCL while GEMMs run (N > 1)")
+    ap.add_argument("--grad-exchange", choices=("nccl", "fused"), default="fused",
+                    help="N > 1: all-reduce every gradient with NCCL, or reduce-scatter the dense weight gradients inside "
+                         "their GEMMs (peer atomics over NVLink + copy-engine hand-out) and keep NCCL for the small ones")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the workload's token count (smaller cases for ncu captures; not a bench number)")

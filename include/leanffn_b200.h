@@ -232,9 +232,26 @@ typedef struct leanffn_gemm_desc {
   int32_t force_simt;   /* != 0: run the SIMT kernel whatever the dtype (checker / odd shapes) */
   int32_t max_ctas;     /* > 0: cap on the persistent grid of the tensor-core kernel (leave SMs to a
                            concurrently running collective); 0 = one CTA per SM */
+  /* Reduce-scatter fused into the epilogue (data-parallel weight gradients; no counterpart in the reference, which
+   * has no distributed code).  scatter_world = W > 0 (at most 8): the result is not stored to D; element (r, c) is
+   * ADDED (relaxed atomic add at system scope) to scatter_D[(r >> scatter_block_shift) % W] + r*ldd + c, where
+   * scatter_D[k] is the address of the SAME [M, ldd] matrix in the memory of rank k (peer-mapped over NVLink; entry
+   * [own rank] is local).  After every rank has run its product and the ranks have synchronised, rank k holds the
+   * sum over ranks of the row blocks it owns (blocks of 2^scatter_block_shift rows, dealt round-robin); the other
+   * rows of its replica are untouched.  The caller zeroes the owned blocks before the first contribution can
+   * arrive.  Tensor-core path with LEANFFN_EPI_STORE, no bias, scatter_block_shift >= 7 only. */
+  int32_t scatter_world;
+  int32_t scatter_block_shift;
+  void* scatter_D[8];
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
+
+/* Strided device-to-device copy of `height` pieces of `width_bytes` (cudaMemcpy2DAsync; between two GPUs with peer
+ * access it runs on a copy engine and occupies no SM).  Used to hand the reduced row blocks of a scattered weight
+ * gradient to the other ranks.  No counterpart in the reference. */
+int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const void* src, uint64_t src_pitch_bytes,
+                        uint64_t width_bytes, uint64_t height, void* stream);
 
 #ifdef __cplusplus
 }

@@ -35,6 +35,7 @@ class GemmDesc(ctypes.Structure):
         ("aux", c_void_p), ("ldaux", c_int64), ("aux_dtype", c_int32),
         ("dropout_p", c_float), ("seed", c_uint64), ("elem_offset", c_uint64),
         ("status_word", c_void_p), ("force_simt", c_int32), ("max_ctas", c_int32),
+        ("scatter_world", c_int32), ("scatter_block_shift", c_int32), ("scatter_D", c_void_p * 8),
     ]
 
 
@@ -60,6 +61,7 @@ _SIGNATURES = {
     "leanffn_column_sum_static": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "leanffn_cast": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_void_p]),
     "leanffn_transpose": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
+    "leanffn_copy_2d": (c_int32, [c_void_p, c_uint64, c_void_p, c_uint64, c_uint64, c_uint64, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
 }
 

@@ -101,6 +101,30 @@ def linear_forward_core(x2d, weight, bias, lowrank_first, lowrank_second, forwar
     return out, lowrank_hid
 
 
+_weight_grad_reducer = None
+
+
+def set_weight_grad_reducer(reducer):
+    """Install (or remove, with None) a ``dist.ScatteredGradReducer``: dense weight-gradient GEMMs of weights it
+    has registered add their tiles into the owning rank's replica instead of storing them, and the gradient
+    returned to autograd for such a weight is None (the reducer delivers the sum)."""
+    global _weight_grad_reducer
+    previous, _weight_grad_reducer = _weight_grad_reducer, reducer
+    return previous
+
+
+def dense_weight_grad(dy2d, x2d, weight):
+    """dW = dyT . x for a dense weight (linear.py:304-305 of the reference), through the installed reducer if any."""
+    reducer = _weight_grad_reducer
+    target = reducer.target(weight) if reducer is not None else None
+    if target is None:
+        return ops.gemm(dy2d, x2d, a_mn_major=True, b_mn_major=True, out_dtype=weight.dtype)
+    out, scatter = target
+    ops.gemm(dy2d, x2d, a_mn_major=True, b_mn_major=True, out=out, scatter=scatter)
+    reducer.gradient_launched(weight)
+    return None
+
+
 def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_second, forward_indices,
                          backward_indices, matmul_op, needs_input_grad, cdt, *, dgrad_epilogue=N.EPI_STORE, act=0,
                          dgrad_aux=None, dgrad_out=None, dgrad_out2=None, bias_dtype=None, on_param_grads=None):
@@ -109,7 +133,8 @@ def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_
     Weight-like gradients come back in their parameter's dtype.  The input gradient may carry a fused
     activation-backward epilogue (dense W only).  ``on_param_grads(weight, bias, lowrank_first, lowrank_second)``
     is called once the parameter gradients are launched and before the input gradient is, so a data-parallel
-    caller can start their reduction underneath the input-gradient product."""
+    caller can start their reduction underneath the input-gradient product; it returns the four values to hand
+    back (None for a gradient it has taken over)."""
     kind = _kind(weight, forward_indices, backward_indices, matmul_op)
     need_x, need_w, need_b, need_l1, need_l2 = (list(needs_input_grad) + [False] * 5)[:5]
     grad_input = grad_weight = grad_bias = grad_l1 = grad_l2 = None
@@ -132,13 +157,13 @@ def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_
         tables = native_tables(forward_indices, backward_indices, weight.shape[1])
     if need_w:
         if kind == "dense":
-            grad_weight = ops.gemm(dy2d, x2d, a_mn_major=True, b_mn_major=True, out_dtype=weight.dtype)
+            grad_weight = dense_weight_grad(dy2d, x2d, weight)
         elif kind == "native":
             grad_weight = _bs_wgrad(dy2d, x2d, weight, tables[2], weight.dtype)
         else:
             grad_weight = _bs_wgrad(dy2d, x2d, weight, matmul_op._tables(dy2d.device)[4], weight.dtype)
     if on_param_grads is not None:
-        on_param_grads(grad_weight, grad_bias, grad_l1, grad_l2)
+        grad_weight, grad_bias, grad_l1, grad_l2 = on_param_grads(grad_weight, grad_bias, grad_l1, grad_l2)
     if need_x:
         w = cast_cached(weight, cdt)
         a2, b2 = (grad_lowrank_hid, l1) if has_lowrank else (None, None)

@@ -67,6 +67,15 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     }
     if (epi != LEANFFN_EPI_STORE) return LEANFFN_ERR_UNSUPPORTED;
   }
+  if (d->scatter_world != 0) {
+    if (d->scatter_world < 0 || d->scatter_world > 8) return LEANFFN_ERR_TOO_LARGE;
+    if (epi != LEANFFN_EPI_STORE || d->bias != nullptr || d->scatter_block_shift < 7 || d->scatter_block_shift > 30)
+      return LEANFFN_ERR_UNSUPPORTED;
+    for (int k = 0; k < d->scatter_world; ++k) {
+      if (d->scatter_D[k] == nullptr) return LEANFFN_ERR_NULL;
+      if (!aligned16(d->scatter_D[k])) return LEANFFN_ERR_ALIGN;
+    }
+  }
   if (d->M == 0) return LEANFFN_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -89,6 +98,9 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   ep.keep_scale = 1.0f / (1.0f - d->dropout_p);
   ep.seed = d->seed;
   ep.elem_offset = d->elem_offset;
+  ep.scatter_world = d->scatter_world;
+  ep.scatter_shift = d->scatter_block_shift;
+  for (int k = 0; k < 8; ++k) ep.scatter_D[k] = k < d->scatter_world ? d->scatter_D[k] : nullptr;
 
   // Reduction length seen by the kernels.
   int64_t k_eff = d->K;
@@ -172,7 +184,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
       return v != nullptr ? atoi(v) : 0;
     }();
     p.tune = pair_tune;
-    if (pair_enabled && d->bs_mode == 0 && block_n == 256 && d->M > 128) {
+    if (pair_enabled && d->bs_mode == 0 && block_n == 256 && d->M > 128 && d->scatter_world == 0) {
       p.num_m_blocks = static_cast<int32_t>((d->M + 255) / 256);
       return gemm_tcgen05_pair(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
                                d->K2 > 0 ? &B2 : nullptr, p, st);
@@ -212,6 +224,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   }
 
   // ---- SIMT path ---------------------------------------------------------------------------------
+  if (d->scatter_world != 0) return LEANFFN_ERR_UNSUPPORTED;  // the scattered reduction exists in the tensor-core kernel only
   SimtOperands o{};
   o.A = d->A;
   o.B = d->B;
@@ -261,4 +274,14 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
     return launch_act_bwd(plain.D, ldpre, d->aux, d->D, d->D2, d->d_dtype, d->M, inter, gated ? 1 : 0, d->act, st);
   }
+}
+
+extern "C" int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const void* src, uint64_t src_pitch_bytes,
+                                   uint64_t width_bytes, uint64_t height, void* stream) {
+  if (width_bytes == 0 || height == 0) return LEANFFN_OK;
+  if (dst == nullptr || src == nullptr) return LEANFFN_ERR_NULL;
+  if (dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes) return LEANFFN_ERR_SHAPE;
+  const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch_bytes, src, src_pitch_bytes, width_bytes, height,
+                                          cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }

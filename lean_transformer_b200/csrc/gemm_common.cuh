@@ -24,6 +24,10 @@ struct EpiParams {
   float keep_scale;
   uint64_t seed;
   uint64_t elem_offset;
+  // reduce-scatter of the result into peer replicas (scatter_world == 0: plain store to D)
+  int32_t scatter_world;
+  int32_t scatter_shift;
+  void* scatter_D[8];
 };
 
 __device__ __forceinline__ float load_any(const void* p, int32_t dtype, int64_t i) {

@@ -302,6 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         acc_phase ^= 1u;
       }
     }
+    if (ep.scatter_world > 0) __threadfence_system();  // contributions to peer replicas are out before the kernel ends
   }
 
   // ------------------------------- teardown ------------------------------------------------------

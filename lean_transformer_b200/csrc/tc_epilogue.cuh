@@ -67,6 +67,27 @@ __device__ __forceinline__ void store_packed8(void* base, int32_t dtype, int64_t
   }
 }
 
+// Atomic add (relaxed, system scope: the target may be another GPU's memory) of 8 consecutive elements.
+__device__ __forceinline__ void red_add_packed8(void* base, int64_t elem, const uint4& w) {
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(static_cast<bf16*>(base) + elem),
+               "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w)
+               : "memory");
+}
+__device__ __forceinline__ void red_add_f32x8(void* base, int64_t elem, const float (&v)[8]) {
+  float* p = static_cast<float*>(base) + elem;
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]),
+               "f"(v[3])
+               : "memory");
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p + 4), "f"(v[4]), "f"(v[5]), "f"(v[6]),
+               "f"(v[7])
+               : "memory");
+}
+// Replica that owns `row` when the result is scattered over ranks (row blocks dealt round-robin).
+__device__ __forceinline__ void* scatter_target(const EpiParams& ep, int64_t row) {
+  const uint32_t owner = (static_cast<uint32_t>(row) >> ep.scatter_shift) % static_cast<uint32_t>(ep.scatter_world);
+  return ep.scatter_D[owner];
+}
+
 // Bias of the 32 columns first .. first+31 (same for every lane: broadcast loads).  Columns at or beyond `limit`
 // read as 0; limit and first are multiples of 8.
 __device__ __forceinline__ void load_bias32(const void* bias, int32_t dtype, int64_t first, int64_t limit,
@@ -233,7 +254,10 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           if (row >= ep.M) continue;
 #pragma unroll
           for (int q = 0; q < 8; ++q) v[i][q] += b[q];
-          store8(ep.D, ep.d_dtype, row * ep.ldd + col, v[i]);
+          if (ep.scatter_world > 0)
+            red_add_f32x8(scatter_target(ep, row), row * ep.ldd + col, v[i]);
+          else
+            store8(ep.D, ep.d_dtype, row * ep.ldd + col, v[i]);
         }
       }
       return;
@@ -253,7 +277,11 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int64_t row = row0 + 8 * i + sub_row;
-        if (row < ep.M) store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, w[i]);
+        if (row >= ep.M) continue;
+        if (ep.scatter_world > 0)
+          red_add_packed8(scatter_target(ep, row), row * ep.ldd + col, w[i]);
+        else
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, w[i]);
       }
     }
   } else {

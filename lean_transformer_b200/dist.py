@@ -27,7 +27,15 @@ class GradSync:
 
     ``reduce(name, grad)`` starts an in-place all-reduce (optionally through a lower-precision wire copy) and
     returns immediately; ``finish()`` blocks the current stream until every started reduction has landed and
-    returns how many tensors were reduced.  Usable as the callback of ``ffn.set_grad_ready_hook``.
+    returns how many tensors were reduced.
+
+    As the callback of ``ffn.set_grad_ready_hook`` it is called as ``reduce(name, grad, param)`` from inside the
+    backward.  Autograd would cast or copy the returned gradient on the compute stream while the reduction is still
+    in flight on NCCL's stream, so in this mode the synchroniser TAKES the gradient (returns True, the backward
+    hands None to autograd) and ``finish()`` stores the reduced tensor into ``.grad`` of the parameter, which it
+    finds among ``params`` by storage address.  Gradients of tensors that are not in ``params`` (e.g. the
+    concatenation of a shared low-rank factor and an adapter) are left to autograd, unreduced, and their names are
+    collected in ``unclaimed``; reduce those after the backward (``all_reduce_module_gradients``).
 
     ``comm_sms``: the tensor-core GEMMs are persistent kernels holding one CTA on every SM until they end, so a
     collective started meanwhile would find no SM to run on.  With ``comm_sms`` set, the GEMM grid is capped at
@@ -39,7 +47,7 @@ class GradSync:
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, wire_dtype: Optional[torch.dtype] = None,
-                 average: bool = False, comm_sms: Optional[int] = None, measure_tail: bool = False):
+                 average: bool = False, comm_sms: Optional[int] = None, measure_tail: bool = False, params=None):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.group = group
@@ -48,6 +56,8 @@ class GradSync:
         self.average = average
         self.comm_sms = comm_sms
         self.measure_tail = measure_tail
+        self._owners = {p.data_ptr(): p for p in params} if params is not None else {}
+        self.unclaimed: List[str] = []
         self._tail_events: List[tuple] = []
         self._pending: List[tuple] = []
         self.reduced_names: List[str] = []
@@ -62,10 +72,16 @@ class GradSync:
         else:
             ops.set_max_ctas(0)
 
-    def reduce(self, name: str, grad: torch.Tensor):
+    def reduce(self, name: str, grad: torch.Tensor, param: Optional[torch.Tensor] = None) -> bool:
+        owner = None
+        if param is not None:  # called from inside a backward
+            owner = self._owners.get(param.data_ptr())
+            if owner is None or owner.shape != grad.shape:
+                self.unclaimed.append(name)
+                return False
         if self.world_size == 1:
             self.reduced_names.append(name)
-            return
+            return False
         wire = grad
         if self.wire_dtype is not None and grad.dtype != self.wire_dtype:
             wire = grad.to(self.wire_dtype)
@@ -74,7 +90,8 @@ class GradSync:
         work = dist.all_reduce(wire, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         if not self._pending and grad.is_cuda:
             self._cap_gemm_grid(True)
-        self._pending.append((name, grad, wire, work))
+        self._pending.append((name, grad, wire, work, owner))
+        return owner is not None
 
     __call__ = reduce
 
@@ -84,12 +101,21 @@ class GradSync:
         if timed:
             before, after = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             before.record()
-        for name, grad, wire, work in self._pending:
+        for name, grad, wire, work, owner in self._pending:
             work.wait()
-            if wire is not grad:
-                grad.copy_(wire)
-            if self.average:
-                grad.div_(self.world_size)
+            if owner is None:
+                if wire is not grad:
+                    grad.copy_(wire)
+                if self.average:
+                    grad.div_(self.world_size)
+            else:
+                result = wire if wire.dtype == owner.dtype else wire.to(owner.dtype)
+                if self.average:
+                    result = result.div_(self.world_size)
+                if owner.grad is None:
+                    owner.grad = result
+                else:
+                    owner.grad.add_(result)
             self.reduced_names.append(name)
             done += 1
         if timed:
@@ -106,6 +132,148 @@ class GradSync:
         out = [a.elapsed_time(b) for a, b in self._tail_events]
         self._tail_events.clear()
         return out
+
+
+def owned_row_blocks(rows: int, world_size: int, rank: int, block_shift: int) -> range:
+    """Indices of the ``2**block_shift``-row blocks of a ``rows``-row matrix that ``rank`` owns when the blocks are
+    dealt round-robin (the ownership rule of ``leanffn_gemm``'s ``scatter_world`` mode)."""
+    blocks = (rows + (1 << block_shift) - 1) >> block_shift
+    return range(rank, blocks, world_size)
+
+
+class ScatteredGradReducer:
+    """Sum of dense weight gradients over the ranks, with the reduce-scatter half fused into the GEMM that
+    produces the gradient.
+
+    Every registered weight gets a slice of one symmetric (peer-mapped) buffer.  The weight-gradient GEMM does not
+    store its tiles: its epilogue adds each tile straight into the replica of the rank that owns the tile's row
+    block (``red.add`` over NVLink, 256-row blocks dealt round-robin so that all links carry traffic at any
+    moment).  When a GEMM has finished on every rank, each rank holds the complete sum of its own blocks and hands
+    them to the other ranks with copy-engine copies, which occupy no SM and run underneath the next GEMMs.
+    Per step::
+
+        reducer.begin_step()          # zero the owned blocks, synchronise the ranks
+        out = ffn(x); out.backward(g) # weight gradients of registered weights come back as None
+        reducer.finish()              # waits for the exchange; sets param.grad to the summed gradient
+
+    Summation order across ranks is not fixed, so results are not bit-reproducible (bf16 gradients are also
+    accumulated in bf16 at the owner).  Micro-batch accumulation: call ``begin_step`` once, run several
+    backwards, then ``finish`` — every backward adds into the same blocks.
+    """
+
+    BLOCK_SHIFT = 8  # 256 rows: the tile height of the weight-gradient GEMM
+
+    def __init__(self, weights: Dict[str, torch.Tensor], group: Optional[dist.ProcessGroup] = None,
+                 spare_sms: int = 4):
+        import torch.distributed._symmetric_memory as symm
+
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world_size, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world_size > 8:
+            raise ValueError("the fused reduce-scatter addresses at most 8 replicas (one NVLink domain)")
+        block_rows = 1 << self.BLOCK_SHIFT
+        self._slices: Dict[str, tuple] = {}
+        self._by_storage: Dict[int, str] = {}
+        self._params: Dict[str, torch.Tensor] = {}
+        offset = 0
+        device = None
+        for name, w in weights.items():
+            if w.dim() != 2 or not w.is_cuda or not w.is_contiguous():
+                raise ValueError(f"{name}: dense, contiguous 2-D CUDA weights only")
+            if w.shape[0] % block_rows != 0:
+                raise ValueError(f"{name}: {w.shape[0]} rows are not a multiple of {block_rows}")
+            device = w.device
+            nbytes = w.numel() * w.element_size()
+            self._slices[name] = (offset, tuple(w.shape), w.dtype)
+            self._by_storage[w.data_ptr()] = name
+            self._params[name] = w
+            offset += (nbytes + 255) // 256 * 256
+        self._buffer = symm.empty(offset, dtype=torch.uint8, device=device)
+        self._handle = symm.rendezvous(self._buffer, self.group.group_name)
+        self._peer_bases = [int(p) for p in self._handle.buffer_ptrs]
+        self._views = {name: self._buffer[off:off + torch.Size(shape).numel() * dt.itemsize]
+                       .view(dt).view(shape) for name, (off, shape, dt) in self._slices.items()}
+        self._side = torch.cuda.Stream(device)
+        self._done: List[torch.cuda.Event] = []
+        self._capped = False
+        self._sms = torch.cuda.get_device_properties(device).multi_processor_count
+        self._spare_sms = max(1, int(spare_sms))
+        self._buffer.zero_()
+        self._handle.barrier(channel=0)
+
+    def gradient(self, name: str) -> torch.Tensor:
+        """This rank's replica of the summed gradient (valid after ``finish``)."""
+        return self._views[name]
+
+    def begin_step(self):
+        """Zero the row blocks this rank owns and synchronise: no contribution may arrive before that."""
+        block_rows = 1 << self.BLOCK_SHIFT
+        for name, view in self._views.items():
+            rows, cols = view.shape
+            if rows % (block_rows * self.world_size) == 0:
+                view.view(rows // (block_rows * self.world_size), self.world_size, block_rows * cols)[:, self.rank].zero_()
+            else:
+                view.zero_()
+        self._handle.barrier(channel=0)
+
+    def target(self, weight: torch.Tensor):
+        """``(out, scatter)`` arguments of ``ops.gemm`` for the gradient of ``weight``, or None if not registered."""
+        name = self._by_storage.get(weight.data_ptr())
+        if name is None:
+            return None
+        offset = self._slices[name][0]
+        return self._views[name], ([base + offset for base in self._peer_bases], self.BLOCK_SHIFT)
+
+    def gradient_launched(self, weight: torch.Tensor):
+        """Called right after the scattering GEMM of ``weight`` was enqueued on the current stream: queues, on a side
+        stream, rank synchronisation -> copy-engine hand-out of the owned blocks -> rank synchronisation."""
+        from . import ops
+
+        name = self._by_storage[weight.data_ptr()]
+        offset, (rows, cols), dtype = self._slices[name]
+        if not self._capped:
+            # the synchronisation kernels of the side stream (and NCCL's for the small tensors) need an SM while
+            # persistent GEMMs hold the others
+            ops.set_max_ctas(self._sms - self._spare_sms)
+            self._capped = True
+        ready = torch.cuda.Event()
+        ready.record()
+        self._side.wait_event(ready)
+        block_bytes = (1 << self.BLOCK_SHIFT) * cols * dtype.itemsize
+        owned = owned_row_blocks(rows, self.world_size, self.rank, self.BLOCK_SHIFT)
+        with torch.cuda.stream(self._side):
+            self._handle.barrier(channel=1)  # every rank's contributions have landed
+            if len(owned) > 0:
+                start = offset + self.rank * block_bytes
+                pitch = self.world_size * block_bytes
+                for shift in range(1, self.world_size):
+                    peer = (self.rank + shift) % self.world_size
+                    ops.copy_2d(self._peer_bases[peer] + start, pitch, self._peer_bases[self.rank] + start, pitch,
+                                block_bytes, len(owned), self._side)
+            self._handle.barrier(channel=1)  # every rank's blocks have arrived here
+            done = torch.cuda.Event()
+            done.record()
+        self._done.append(done)
+
+    def finish(self) -> int:
+        """Make the current stream wait for the exchanges started since ``begin_step``; point ``param.grad`` of
+        every registered parameter at its summed gradient.  Returns the number of exchanges waited for."""
+        from . import ops
+
+        current = torch.cuda.current_stream()
+        for event in self._done:
+            current.wait_event(event)
+        count = len(self._done)
+        self._done.clear()
+        if self._capped:
+            ops.set_max_ctas(0)
+            self._capped = False
+        for name, w in self._params.items():
+            if isinstance(w, torch.nn.Parameter) or w.requires_grad:
+                w.grad = self._views[name]
+        return count
 
 
 def all_reduce_module_gradients(module: torch.nn.Module, group=None, wire_dtype=None) -> int:

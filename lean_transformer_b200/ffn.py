@@ -22,14 +22,18 @@ import torch.nn as nn
 from . import _native as N
 from . import ops
 from .blocksparse.linear import (GeneralizedLinear, TritonMatmulForLinearLayer, _GeneralizedLinear, _kind,
-                                 cast_cached, linear_backward_core, linear_forward_core, resolve_compute_dtype)
+                                 cast_cached, dense_weight_grad, linear_backward_core, linear_forward_core,
+                                 resolve_compute_dtype)
 from .utils import ACT2FN, resolve_activation
 
 
-# Optional callback ``fn(name, grad)`` invoked inside the backward as soon as a parameter gradient exists
-# (names: "h2o_weight", "h2o_bias", "i2h_weight", ...).  A data-parallel trainer uses it to start the
-# all-reduce of the output projection's gradients while the input projection's are still being computed
-# (see lean_transformer_b200.dist.GradSync); autograd hooks would only fire after the whole backward.
+# Optional callback ``fn(name, grad, param) -> bool`` invoked inside the backward as soon as a parameter gradient
+# exists (names: "h2o_weight", "h2o_bias", "i2h_weight", ...; ``param`` is the tensor the gradient belongs to).  A
+# data-parallel trainer uses it to start the all-reduce of the output projection's gradients while the input
+# projection's are still being computed (see lean_transformer_b200.dist.GradSync); autograd hooks would only fire
+# after the whole backward.  A callback that returns True has TAKEN the gradient: the backward then returns None
+# for that parameter and the callback's owner delivers ``param.grad`` itself.  This matters because autograd may
+# cast or copy a returned gradient on the compute stream while an asynchronous reduction is still writing it.
 _grad_ready_hook = None
 
 
@@ -40,11 +44,11 @@ def set_grad_ready_hook(fn):
     return previous
 
 
-def _notify(**grads):
-    if _grad_ready_hook is not None:
-        for name, grad in grads.items():
-            if grad is not None:
-                _grad_ready_hook(name, grad)
+def _offer(name, grad, param):
+    """Hand a finished gradient to the callback; returns what the backward passes on to autograd."""
+    if grad is None or _grad_ready_hook is None:
+        return grad
+    return None if _grad_ready_hook(name, grad, param) is True else grad
 
 
 def next_dropout_stream(device: torch.device, numel: int):
@@ -288,8 +292,7 @@ class _LeanFFN(torch.autograd.Function):
                      out=grad_pre, out2=hid_act)
             grad_h2o_weight = grad_h2o_lowrank_first = grad_h2o_lowrank_second = None
             if needs[10]:
-                grad_h2o_weight = ops.gemm(grad_h2o_out, hid_act, a_mn_major=True, b_mn_major=True,
-                                           out_dtype=h2o_weight.dtype)
+                grad_h2o_weight = dense_weight_grad(grad_h2o_out, hid_act, h2o_weight)
             if h2o_lowrank_first is not None and needs[13]:
                 grad_h2o_lowrank_second = ops.gemm(grad_h2o_out, h2o_lowrank_hid, a_mn_major=True, b_mn_major=True,
                                                    out_dtype=h2o_lowrank_second.dtype)
@@ -305,10 +308,14 @@ class _LeanFFN(torch.autograd.Function):
             grad_pre, _ = ops.activation_backward(grad_hid_act, pre_activation, gated, act)
             del grad_hid_act
         del hid_act, grad_h2o_out
-        _notify(h2o_weight=only_if(needs[10], grad_h2o_weight), h2o_bias=only_if(needs[11], grad_h2o_bias),
-                h2o_lowrank_first=only_if(needs[12], grad_h2o_lowrank_first),
-                h2o_lowrank_second=only_if(needs[13], grad_h2o_lowrank_second),
-                post_ln_weight=grad_post_ln_weight, post_ln_bias=grad_post_ln_bias)
+        grad_h2o_weight = _offer("h2o_weight", only_if(needs[10], grad_h2o_weight), h2o_weight)
+        grad_h2o_bias = _offer("h2o_bias", only_if(needs[11], grad_h2o_bias), h2o_bias)
+        grad_h2o_lowrank_first = _offer("h2o_lowrank_first", only_if(needs[12], grad_h2o_lowrank_first),
+                                        h2o_lowrank_first)
+        grad_h2o_lowrank_second = _offer("h2o_lowrank_second", only_if(needs[13], grad_h2o_lowrank_second),
+                                         h2o_lowrank_second)
+        grad_post_ln_weight = _offer("post_ln_weight", grad_post_ln_weight, post_ln_weight)
+        grad_post_ln_bias = _offer("post_ln_bias", grad_post_ln_bias, post_ln_bias)
 
         # backward(... -> input_layernorm -> linear_i2h -> ...)
         need_input_side = bool(needs[0] or needs[1] or needs[2])
@@ -320,8 +327,9 @@ class _LeanFFN(torch.autograd.Function):
          grad_i2h_lowrank_second) = linear_backward_core(
             grad_pre, input_ln, i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second,
             i2h_forward_indices, i2h_backward_indices, ctx._i2h_matmul_op, i2h_needs, cdt,
-            on_param_grads=lambda w, b, l1, l2: _notify(i2h_weight=w, i2h_bias=b, i2h_lowrank_first=l1,
-                                                        i2h_lowrank_second=l2))
+            on_param_grads=lambda w, b, l1, l2: (_offer("i2h_weight", w, i2h_weight), _offer("i2h_bias", b, i2h_bias),
+                                                 _offer("i2h_lowrank_first", l1, i2h_lowrank_first),
+                                                 _offer("i2h_lowrank_second", l2, i2h_lowrank_second)))
         del grad_pre, input_ln
 
         grad_input = grad_ln_weight = grad_ln_bias = None
@@ -331,7 +339,8 @@ class _LeanFFN(torch.autograd.Function):
                 need_dx=bool(needs[0]), need_param_grads=bool(needs[1] or needs[2]))
             if grad_input is not None:
                 grad_input = grad_input.view(*input.shape)
-            _notify(ln_weight=grad_ln_weight, ln_bias=grad_ln_bias)
+            grad_ln_weight = _offer("ln_weight", grad_ln_weight, ln_weight)
+            grad_ln_bias = _offer("ln_bias", grad_ln_bias, ln_bias)
         only = only_if
 
         return (only(needs[0], grad_input), only(needs[1], grad_ln_weight), only(needs[2], grad_ln_bias),

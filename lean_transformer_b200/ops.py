@@ -237,11 +237,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0,
          bs_mode: int = 0, bs_block: int = 0, bs_nnz: int = 0, bs_num_blocks: int = 0,
          bs_index: Optional[torch.Tensor] = None, bs_count: Optional[torch.Tensor] = None,
-         force_simt: bool = False) -> torch.Tensor:
+         force_simt: bool = False, scatter=None) -> torch.Tensor:
     """D = A(m,k) . B(n,k) with the fused epilogues of ``leanffn_gemm`` (see include/leanffn_b200.h).
 
     Dense operands are 2-D with unit inner stride: a K-major A is [M, K], an MN-major A is [K, M];
     a K-major B is [N, K] (so D = A @ B.T), an MN-major B is [K, N].
+
+    ``scatter = (replica_addresses, block_shift)``: instead of being stored, the result is added into the replica
+    of ``out`` that owns each row block (``out`` is this rank's replica; see ``scatter_world`` in the header).
     """
     _require_cuda(a, b, out, bias, out2, aux, a2, b2, bs_index, bs_count)
     assert a.dim() == 2 and a.stride(1) == 1 and a.dtype == b.dtype
@@ -290,6 +293,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     d.status_word = _ptr(status_word(a.device))
     d.force_simt = int(force_simt)
     d.max_ctas = _max_ctas
+    if scatter is not None:
+        addresses, shift = scatter
+        assert 1 <= len(addresses) <= 8 and epilogue == N.EPI_STORE and bias is None and out.dim() == 2
+        d.scatter_world, d.scatter_block_shift = len(addresses), int(shift)
+        for i, address in enumerate(addresses):
+            d.scatter_D[i] = int(address)
     global launch_count
     launch_count += 1
     if _gemm_timer is not None:
@@ -303,3 +312,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
         return out
     N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
     return out
+
+
+def copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width_bytes: int, height: int, stream=None):
+    """Strided device-to-device copy by raw addresses (``leanffn_copy_2d``); with peer addresses it runs on a copy
+    engine.  ``stream``: a ``torch.cuda.Stream`` (default: the current one)."""
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    N.check(N.lib.leanffn_copy_2d(int(dst_ptr), int(dst_pitch), int(src_ptr), int(src_pitch), int(width_bytes),
+                                  int(height), handle), "leanffn_copy_2d")

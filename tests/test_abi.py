@@ -45,6 +45,7 @@ def test_descriptor_layout_matches_header():
         first = names[0].split()[-1].lstrip("*")
         fields.append(first)
         fields.extend(n.strip().lstrip("*") for n in names[1:])
+    fields = [re.sub(r"\[\d+\]$", "", f) for f in fields]  # array members: name[8] -> name
     assert fields == [f[0] for f in _native.GemmDesc._fields_]
 
 
