@@ -141,6 +141,17 @@ def owned_row_blocks(rows: int, world_size: int, rank: int, block_shift: int) ->
     return range(rank, blocks, world_size)
 
 
+def handout_plan(rows: int, cols: int, itemsize: int, world_size: int, rank: int, block_shift: int):
+    """Strided copy that covers exactly the row blocks ``rank`` owns in a row-major ``[rows, cols]`` matrix:
+    ``(start_byte, pitch_bytes, width_bytes, height)`` for ``leanffn_copy_2d`` (same layout at source and
+    destination).  ``rows`` must be a multiple of the block height."""
+    block_rows = 1 << block_shift
+    if rows % block_rows != 0:
+        raise ValueError(f"{rows} rows are not a multiple of {block_rows}")
+    block_bytes = block_rows * cols * itemsize
+    return rank * block_bytes, world_size * block_bytes, block_bytes, len(owned_row_blocks(rows, world_size, rank, block_shift))
+
+
 class ScatteredGradReducer:
     """Sum of dense weight gradients over the ranks, with the reduce-scatter half fused into the GEMM that
     produces the gradient.
@@ -241,17 +252,15 @@ class ScatteredGradReducer:
         ready = torch.cuda.Event()
         ready.record()
         self._side.wait_event(ready)
-        block_bytes = (1 << self.BLOCK_SHIFT) * cols * dtype.itemsize
-        owned = owned_row_blocks(rows, self.world_size, self.rank, self.BLOCK_SHIFT)
+        first, pitch, width, height = handout_plan(rows, cols, dtype.itemsize, self.world_size, self.rank, self.BLOCK_SHIFT)
         with torch.cuda.stream(self._side):
             self._handle.barrier(channel=1)  # every rank's contributions have landed
-            if len(owned) > 0:
-                start = offset + self.rank * block_bytes
-                pitch = self.world_size * block_bytes
+            if height > 0:
+                start = offset + first
                 for shift in range(1, self.world_size):
                     peer = (self.rank + shift) % self.world_size
                     ops.copy_2d(self._peer_bases[peer] + start, pitch, self._peer_bases[self.rank] + start, pitch,
-                                block_bytes, len(owned), self._side)
+                                width, height, self._side)
             self._handle.barrier(channel=1)  # every rank's blocks have arrived here
             done = torch.cuda.Event()
             done.record()

@@ -98,3 +98,34 @@ def test_dropout_mask_is_partition_invariant():
         start, count = ldist.shard_tokens(tokens, 4, rank)
         part = O.dropout_keep_mask(count * hidden, p, seed, start * hidden).reshape(count, hidden)
         assert (part == full[start:start + count]).all()
+
+
+@pytest.mark.parametrize("world,rows,cols", [(2, 512, 24), (4, 1024, 8), (8, 2048, 16), (8, 768, 8), (3, 1280, 4)])
+def test_scattered_reduction_plan_sums_every_row_once(world, rows, cols):
+    """Host logic of the fused reduce-scatter: emulate, with numpy, the epilogue's ownership rule (row blocks dealt
+    round-robin), then the strided hand-out copies; every replica must end up holding the sum over ranks."""
+    import numpy as np
+    from lean_transformer_b200 import dist as ldist
+    shift = ldist.ScatteredGradReducer.BLOCK_SHIFT
+    rng = np.random.default_rng(0)
+    contributions = rng.integers(-8, 8, size=(world, rows, cols)).astype(np.float32)
+    replicas = np.full((world, rows, cols), np.nan, dtype=np.float32)
+    for rank in range(world):  # begin_step: owned blocks are zeroed
+        for b in ldist.owned_row_blocks(rows, world, rank, shift):
+            replicas[rank, b << shift:(b + 1) << shift] = 0
+    for rank in range(world):  # the GEMM epilogue of every rank: add each row into its owner's replica
+        for r in range(rows):
+            owner = (r >> shift) % world
+            replicas[owner, r] += contributions[rank, r]
+    flat = replicas.reshape(world, -1).view(np.uint8)
+    for rank in range(world):  # hand-out: strided copy of the owned blocks to every other replica
+        start, pitch, width, height = ldist.handout_plan(rows, cols, 4, world, rank, shift)
+        for peer in range(world):
+            if peer == rank:
+                continue
+            for h in range(height):
+                lo = start + h * pitch
+                flat[peer, lo:lo + width] = flat[rank, lo:lo + width]
+    total = contributions.sum(0)
+    for rank in range(world):
+        assert np.array_equal(replicas[rank], total), rank
