@@ -35,20 +35,22 @@ constexpr int GROUP_M = 16;
 constexpr uint32_t A_STAGE_BYTES = BLOCK_M * BLOCK_K * 2;  // 16 KiB
 constexpr uint32_t CHUNK_BYTES = 64 * BLOCK_K * 2;         // one MN-major 64 x 64 box, 8 KiB
 
-// MT = number of 128-row accumulator sub-tiles per CTA tile.  MT == 1: 128 x BLOCK_N tile, two TMEM accumulator
-// stages (the epilogue of one tile overlaps the MMAs of the next).  MT == 2: 256 x 256 tile, both sub-tiles share
-// every B stage (a third less L2 -> shared traffic per flop), all 512 TMEM columns hold ONE tile, so the epilogue
-// is exposed; used for long reductions only, where it is a few percent of the tile time.
+// MT = number of 128-row accumulator sub-tiles per CTA tile; both sub-tiles share every B stage, which cuts the
+// L2 -> shared-memory traffic per flop (by a third for 256-wide tiles, a quarter for 128-wide ones).
+//   <256, 1>: 128 x 256 tile, two TMEM accumulator stages (the epilogue of one tile overlaps the MMAs of the next).
+//   <256, 2>: 256 x 256 tile; all 512 TMEM columns hold ONE tile, so the epilogue is exposed: long reductions only.
+//   <128, 1>: 128 x 128 tile (narrow N, weight-gradient blocks of block-sparse layers), two accumulator stages.
+//   <128, 2>: 256 x 128 tile, two accumulator stages of two sub-tiles (512 columns): block-sparse forward / dgrad.
 template <int BLOCK_N, int MT = 1>
 struct TcConfig {
   static constexpr uint32_t A_BYTES = MT * A_STAGE_BYTES;
   static constexpr uint32_t B_STAGE_BYTES = BLOCK_N * BLOCK_K * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = MT == 2 ? 3 : (BLOCK_N == 256 ? 4 : 6);
-  static constexpr int ACC_STAGES = MT == 2 ? 1 : 2;
-  static constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator stages, or the two sub-tiles of one tile
+  static constexpr int ACC_STAGES = (MT * BLOCK_N == 512) ? 1 : 2;
+  static constexpr uint32_t TMEM_COLS = ACC_STAGES * MT * BLOCK_N;
   static constexpr uint32_t BAR_BYTES = 256;
   static constexpr uint32_t PATCH_BYTES = EPI_WARPS * EPI_PATCH_FLOATS * 4;  // epilogue transposition patches
+  static constexpr int STAGES = (227 * 1024 - 1024 - BAR_BYTES - PATCH_BYTES) / STAGE_BYTES;  // 6 / 4 / 4 / 3
   static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + PATCH_BYTES + 1024;  // + alignment slack
 };
 
@@ -233,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + (MT == 2 ? 0 : acc_stage * BLOCK_N);
+      const uint32_t d_tmem = tmem_base + acc_stage * (MT * BLOCK_N);
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
       const int kb_total = main_k_blocks(n_blk) + p.num_k2_blocks;
@@ -291,7 +293,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll 1
       for (int t = 0; t < MT; ++t) {
         const int64_t row0 = static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32;
-        const uint32_t t_acc = tmem_base + lane_addr + (MT == 2 ? t : acc_stage) * BLOCK_N;
+        const uint32_t t_acc = tmem_base + lane_addr + (acc_stage * MT + t) * BLOCK_N;
         epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, (warp - 2) >> 2, 2);
       }
       tc_fence_before();
@@ -391,7 +393,11 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
   }
   cudaError_t e;
 #define TC_GO(AM, BM, BN) e = tc_launch_t<AM, BM, BN, 1>(ta, tb, ta2, tb2, p, st)
-  if (block_n == 256 && p.m_subtiles == 2) {
+  if (block_n == 128 && p.m_subtiles == 2) {
+    if (!a_mn && !b_mn) e = tc_launch_t<false, false, 128, 2>(ta, tb, ta2, tb2, p, st);
+    else if (!a_mn && b_mn) e = tc_launch_t<false, true, 128, 2>(ta, tb, ta2, tb2, p, st);
+    else return LEANFFN_ERR_UNSUPPORTED;
+  } else if (block_n == 256 && p.m_subtiles == 2) {
     if (!a_mn && !b_mn) e = tc_launch_t<false, false, 256, 2>(ta, tb, ta2, tb2, p, st);
     else if (!a_mn && b_mn) e = tc_launch_t<false, true, 256, 2>(ta, tb, ta2, tb2, p, st);
     else if (a_mn && b_mn) e = tc_launch_t<true, true, 256, 2>(ta, tb, ta2, tb2, p, st);

@@ -51,14 +51,36 @@ def _offer(name, grad, param):
     return None if _grad_ready_hook(name, grad, param) is True else grad
 
 
-def next_dropout_stream(device: torch.device, numel: int):
-    """(seed, element offset) for a dropout mask of ``numel`` elements, taken from (and advancing) torch's CUDA
-    generator of ``device`` so torch.manual_seed and torch.utils.checkpoint's RNG stashing govern it."""
+_token_window = None
+
+
+def set_token_window(first_token: Optional[int], total_tokens: Optional[int] = None):
+    """Token-partitioned data parallelism: declare that the rows this process feeds to LeanFFN are tokens
+    ``[first_token, first_token + rows)`` of a global batch of ``total_tokens``.  Dropout masks are then drawn at
+    the GLOBAL element index and the generator advances by the global size, so with equal seeds the union of the
+    ranks' masks equals the single-process mask of the whole batch (partition-invariant training).  ``None``
+    clears the window.  Returns the previous window."""
+    global _token_window
+    previous = _token_window
+    _token_window = None if first_token is None else (int(first_token), int(total_tokens))
+    return previous
+
+
+def next_dropout_stream(device: torch.device, numel: int, row_elems: Optional[int] = None):
+    """(seed, element offset) for a dropout mask of ``numel`` elements (rows of ``row_elems``), taken from (and
+    advancing) torch's CUDA generator of ``device`` so torch.manual_seed and torch.utils.checkpoint's RNG stashing
+    govern it."""
     index = device.index if device.index is not None else torch.cuda.current_device()
     gen = torch.cuda.default_generators[index]
     seed, offset = gen.initial_seed(), gen.get_offset()
+    shift = 0
+    if _token_window is not None and row_elems:
+        first, total = _token_window
+        if first * row_elems + numel > total * row_elems:
+            raise ValueError(f"token window [{first}, +{numel // row_elems}) exceeds the declared {total} tokens")
+        shift, numel = first * row_elems, total * row_elems
     gen.set_offset(offset + 4 * ((numel + 15) // 16))  # offsets move in multiples of 4, one unit per 4 elements
-    return seed & 0xFFFFFFFFFFFFFFFF, 4 * offset
+    return seed & 0xFFFFFFFFFFFFFFFF, 4 * offset + shift
 
 
 class LeanFFN(nn.Module):
@@ -210,7 +232,7 @@ class _LeanFFN(torch.autograd.Function):
         use_dropout = bool(training and dropout)
         seed = offset = 0
         if use_dropout:
-            seed, offset = next_dropout_stream(input.device, tokens * hidden)
+            seed, offset = next_dropout_stream(input.device, tokens * hidden, hidden)
             ctx._dropout_stream = (seed, offset)
         post_ln_input = None
         if ctx._use_post_ln or not h2o_dense:
@@ -409,7 +431,7 @@ class _DropoutFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, p: float):
         ctx.p = p
-        ctx.stream = next_dropout_stream(x.device, x.numel())
+        ctx.stream = next_dropout_stream(x.device, x.numel(), x.shape[-1])
         return ops.dropout(x.contiguous(), p, *ctx.stream)
 
     @staticmethod

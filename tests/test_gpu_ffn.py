@@ -195,6 +195,32 @@ def test_dropout_semantics(cuda_device):
     assert_close(ffn.h2o_proj.bias.grad, kept.sum(0) * 2.0, 1e-5, 1e-5, "mask reused in backward")
 
 
+def test_token_window_makes_dropout_partition_invariant(cuda_device):
+    """Two token shards run with ``set_token_window`` and the whole batch's seed reproduce the whole-batch result
+    (same dropout mask at the same global element), and the generator ends in the same state."""
+    from lean_transformer_b200 import ffn as lffn
+    ffn = make_ffn(random_params(64, 128, True, seed=7, std=0.2), gated=True, dropout=0.4).train()
+    x = torch.randn(96, 64, device=cuda_device)
+    torch.manual_seed(21)
+    whole = ffn(x).detach()
+    after_whole = torch.cuda.default_generators[x.device.index or 0].get_offset()
+    for first, count in ((0, 40), (40, 56)):
+        torch.manual_seed(21)
+        previous = lffn.set_token_window(first, 96)
+        try:
+            part = ffn(x[first:first + count]).detach()
+        finally:
+            lffn.set_token_window(*previous) if previous is not None else lffn.set_token_window(None)
+        assert torch.cuda.default_generators[x.device.index or 0].get_offset() == after_whole
+        assert_close(part, whole[first:first + count], FP32_RTOL, FP32_ATOL, f"shard at {first}")
+    with pytest.raises(ValueError):
+        lffn.set_token_window(90, 96)
+        try:
+            ffn(x[:10])
+        finally:
+            lffn.set_token_window(None)
+
+
 def test_gradient_checkpointing_recomputes_same_mask(cuda_device):
     from torch.utils.checkpoint import checkpoint
     torch.manual_seed(5)
