@@ -189,7 +189,13 @@ int32_t leanffn_transpose(const void* x, int32_t dtype, int64_t ldx, void* y, in
  *   bs_mode 3: wgrad.    A = dy [tokens(K), out_features] and B = x [tokens(K), in_features], both
  *              MN-major; D = the weight gradient, M = bs_num_blocks*block rows of N = block columns.
  *              Table row = weight block f, one pair (output block o, input block j), bs_nnz = 1.
- * Block-sparse products take LEANFFN_EPI_STORE only.
+ * Block-sparse products take LEANFFN_EPI_STORE; the input-gradient mode (2) also takes LEANFFN_EPI_GLU_BWD and
+ * LEANFFN_EPI_ACT_BWD (the epilogue reads the dense pre-activation tensor, which the sparsity does not touch); the
+ * forward mode (1) also takes LEANFFN_EPI_DROPOUT_RESIDUAL and, for bf16 with bs_block == 128 and N/2 a multiple
+ * of 128, LEANFFN_EPI_GLU_FWD.  For the latter the CALLER guarantees that table rows i and i + N/(2*bs_block)
+ * (a gate block and its linear partner) list the same input blocks in the same order and have equal bs_count:
+ * one activation tile then meets the weight blocks of both halves (true for pixelfly layouts, whose pattern
+ * repeats along the output dimension).
  */
 typedef struct leanffn_gemm_desc {
   int32_t M, N, K;

@@ -18,7 +18,7 @@ from .. import _native as N
 from .. import ops
 from ..utils import pad_to_multiple
 from .layout import get_blocksparse_layout, get_indices_from_layout
-from .native_backend import _bs_dgrad, _bs_forward, _bs_wgrad, native_tables
+from .native_backend import _bs_dgrad, _bs_forward, _bs_wgrad, gate_and_linear_blocks_pair_up, native_tables
 from .triton_backend import TRITON_PAD_TO, TritonMatmulForLinearLayer
 
 
@@ -77,8 +77,8 @@ def _kind(weight: torch.Tensor, forward_indices, backward_indices, matmul_op) ->
 def linear_forward_core(x2d, weight, bias, lowrank_first, lowrank_second, forward_indices, backward_indices,
                         matmul_op, cdt, *, epilogue=N.EPI_STORE, act=0, out=None, out2=None, aux=None,
                         dropout_p=0.0, seed=0, elem_offset=0, out_dtype=None):
-    """output = x @ W^T (+ low rank) (+ bias) with an optional fused epilogue (dense W only).
-    Returns (output, lowrank_hid)."""
+    """output = x @ W^T (+ low rank) (+ bias) with an optional fused epilogue (block-sparse weights: dropout +
+    residual always, the gated activation if ``can_fuse_gated_forward`` says so).  Returns (output, lowrank_hid)."""
     kind = _kind(weight, forward_indices, backward_indices, matmul_op)
     w = cast_cached(weight, cdt)
     lowrank_hid = a2 = b2 = None
@@ -89,16 +89,33 @@ def linear_forward_core(x2d, weight, bias, lowrank_first, lowrank_second, forwar
         out = ops.gemm(x2d, w, bias=bias, a2=a2, b2=b2, epilogue=epilogue, act=act, out=out, out2=out2, aux=aux,
                        dropout_p=dropout_p, seed=seed, elem_offset=elem_offset, out_dtype=out_dtype)
     else:
-        assert epilogue == N.EPI_STORE, "block-sparse products take the plain epilogue"
+        assert epilogue in (N.EPI_STORE, N.EPI_GLU_FWD, N.EPI_DROPOUT_RESIDUAL)
+        fused = {}
+        if epilogue != N.EPI_STORE:
+            fused = dict(epilogue=epilogue, act=act, out2=out2, aux=aux, dropout_p=dropout_p, seed=seed,
+                         elem_offset=elem_offset)
         if kind == "native":
             fwd, _, _ = native_tables(forward_indices, backward_indices, weight.shape[1])
             out_features = fwd.shape[0] * weight.shape[-1]
-            out = _bs_forward(x2d, w, fwd, out_features, out=out, bias=bias, a2=a2, b2=b2, out_dtype=out_dtype)
+            out = _bs_forward(x2d, w, fwd, out_features, out=out, bias=bias, a2=a2, b2=b2, out_dtype=out_dtype, **fused)
         else:
             fwd, fwd_count, _, _, _ = matmul_op._tables(x2d.device)
             out = _bs_forward(x2d, w, fwd, matmul_op.out_features, out=out, bias=bias, a2=a2, b2=b2,
-                              out_dtype=out_dtype, count=fwd_count)
+                              out_dtype=out_dtype, count=fwd_count, **fused)
     return out, lowrank_hid
+
+
+def can_fuse_gated_forward(weight, forward_indices, backward_indices, matmul_op, cdt) -> bool:
+    """Whether the block-sparse forward product of a gated input projection can carry the activation in its
+    epilogue: bf16 tensor-core path, 128-wide blocks, gate and linear blocks reading the same input blocks."""
+    kind = _kind(weight, forward_indices, backward_indices, matmul_op)
+    if kind == "dense" or cdt != torch.bfloat16 or weight.shape[-1] != 128:
+        return False
+    if kind == "native":
+        fwd, _, _ = native_tables(forward_indices, backward_indices, weight.shape[1])
+        return fwd.shape[0] % 2 == 0 and gate_and_linear_blocks_pair_up(fwd)
+    fwd, fwd_count, _, _, _ = matmul_op._tables(weight.device)
+    return fwd.shape[0] % 2 == 0 and gate_and_linear_blocks_pair_up(fwd, fwd_count)
 
 
 _weight_grad_reducer = None
@@ -125,13 +142,36 @@ def dense_weight_grad(dy2d, x2d, weight):
     return None
 
 
+def weight_grad(kind, dy2d, x2d, weight, forward_indices, backward_indices, matmul_op):
+    """dW in the weight's own storage format for a dense, native block-sparse or triton-ordered weight."""
+    if kind == "dense":
+        return dense_weight_grad(dy2d, x2d, weight)
+    if kind == "native":
+        tables = native_tables(forward_indices, backward_indices, weight.shape[1])
+        return _bs_wgrad(dy2d, x2d, weight, tables[2], weight.dtype)
+    return _bs_wgrad(dy2d, x2d, weight, matmul_op._tables(dy2d.device)[4], weight.dtype)
+
+
+def input_grad(kind, dy2d, weight, forward_indices, backward_indices, matmul_op, cdt, a2=None, b2=None, **epilogue):
+    """dX = dY . W (+ low-rank continuation a2 . b2) for any weight kind; ``epilogue`` forwards the fused
+    activation-backward arguments of ``ops.gemm`` (epilogue, act, aux, out, out2)."""
+    w = cast_cached(weight, cdt)
+    if kind == "dense":
+        return ops.gemm(dy2d, w, b_mn_major=True, a2=a2, b2=b2, **epilogue)
+    if kind == "native":
+        tables = native_tables(forward_indices, backward_indices, weight.shape[1])
+        return _bs_dgrad(dy2d, w, tables[1], weight.shape[0], a2=a2, b2=b2, **epilogue)
+    t = matmul_op._tables(dy2d.device)
+    return _bs_dgrad(dy2d, w, t[2], matmul_op.in_features, a2=a2, b2=b2, count=t[3], **epilogue)
+
+
 def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_second, forward_indices,
                          backward_indices, matmul_op, needs_input_grad, cdt, *, dgrad_epilogue=N.EPI_STORE, act=0,
                          dgrad_aux=None, dgrad_out=None, dgrad_out2=None, bias_dtype=None, on_param_grads=None):
     """Gradients of linear_forward_core in the reference's order
     (input, weight, bias, lowrank_first, lowrank_second); ``x2d`` / ``dy2d`` are in the compute dtype.
     Weight-like gradients come back in their parameter's dtype.  The input gradient may carry a fused
-    activation-backward epilogue (dense W only).  ``on_param_grads(weight, bias, lowrank_first, lowrank_second)``
+    activation-backward epilogue.  ``on_param_grads(weight, bias, lowrank_first, lowrank_second)``
     is called once the parameter gradients are launched and before the input gradient is, so a data-parallel
     caller can start their reduction underneath the input-gradient product; it returns the four values to hand
     back (None for a gradient it has taken over)."""
@@ -152,31 +192,17 @@ def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_
         grad_bias = ops.column_sum(dy2d)
         if bias_dtype is not None and bias_dtype != torch.float32:
             grad_bias = ops.cast(grad_bias, bias_dtype)
-    tables = None
-    if kind == "native":
-        tables = native_tables(forward_indices, backward_indices, weight.shape[1])
     if need_w:
-        if kind == "dense":
-            grad_weight = dense_weight_grad(dy2d, x2d, weight)
-        elif kind == "native":
-            grad_weight = _bs_wgrad(dy2d, x2d, weight, tables[2], weight.dtype)
-        else:
-            grad_weight = _bs_wgrad(dy2d, x2d, weight, matmul_op._tables(dy2d.device)[4], weight.dtype)
+        grad_weight = weight_grad(kind, dy2d, x2d, weight, forward_indices, backward_indices, matmul_op)
     if on_param_grads is not None:
         grad_weight, grad_bias, grad_l1, grad_l2 = on_param_grads(grad_weight, grad_bias, grad_l1, grad_l2)
     if need_x:
-        w = cast_cached(weight, cdt)
         a2, b2 = (grad_lowrank_hid, l1) if has_lowrank else (None, None)
-        if kind == "dense":
-            grad_input = ops.gemm(dy2d, w, b_mn_major=True, a2=a2, b2=b2, epilogue=dgrad_epilogue, act=act,
-                                  aux=dgrad_aux, out=dgrad_out, out2=dgrad_out2)
-        else:
-            assert dgrad_epilogue == N.EPI_STORE
-            if kind == "native":
-                grad_input = _bs_dgrad(dy2d, w, tables[1], weight.shape[0], a2=a2, b2=b2)
-            else:
-                t = matmul_op._tables(dy2d.device)
-                grad_input = _bs_dgrad(dy2d, w, t[2], matmul_op.in_features, a2=a2, b2=b2, count=t[3])
+        epilogue = {}
+        if dgrad_epilogue != N.EPI_STORE:
+            epilogue = dict(epilogue=dgrad_epilogue, act=act, aux=dgrad_aux, out=dgrad_out, out2=dgrad_out2)
+        grad_input = input_grad(kind, dy2d, weight, forward_indices, backward_indices, matmul_op, cdt, a2=a2, b2=b2,
+                                **epilogue)
     return grad_input, grad_weight, grad_bias, grad_l1, grad_l2
 
 

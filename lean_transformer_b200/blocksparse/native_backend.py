@@ -57,21 +57,38 @@ def native_tables(forward_indices: Optional[torch.Tensor], backward_indices: Opt
 
 def _bs_forward(x2d: torch.Tensor, weight: torch.Tensor, fwd_table: torch.Tensor, out_features: int,
                 out: Optional[torch.Tensor] = None, bias=None, a2=None, b2=None,
-                out_dtype: Optional[torch.dtype] = None, count: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out_dtype: Optional[torch.dtype] = None, count: Optional[torch.Tensor] = None, **epilogue) -> torch.Tensor:
+    """Y = X . W^T over the nonzero blocks; ``epilogue`` forwards fused-epilogue arguments of ``ops.gemm``."""
     block = weight.shape[-1]
     num_blocks = weight.numel() // (block * block)
     return ops.gemm(x2d, weight, M=x2d.shape[0], N_=out_features, K=x2d.shape[1], out=out, bias=bias, a2=a2, b2=b2,
                     out_dtype=out_dtype, bs_mode=1, bs_block=block, bs_nnz=fwd_table.shape[1],
-                    bs_num_blocks=num_blocks, bs_index=fwd_table, bs_count=count)
+                    bs_num_blocks=num_blocks, bs_index=fwd_table, bs_count=count, **epilogue)
+
+
+def gate_and_linear_blocks_pair_up(fwd_table: torch.Tensor, count: Optional[torch.Tensor] = None) -> bool:
+    """True if output blocks i and i + half (a gate block and its linear partner of a gated projection) read the
+    same input blocks in the same order: the condition under which the gated activation can be fused into the
+    block-sparse forward product.  The answer is remembered on the (cached, immutable) table tensor."""
+    cached = getattr(fwd_table, "_leanffn_pairs_up", None)
+    if cached is None:
+        rows = fwd_table.shape[0]
+        cached = rows % 2 == 0 and bool(torch.equal(fwd_table[:rows // 2, :, 1], fwd_table[rows // 2:, :, 1]))
+        if cached and count is not None:
+            cached = bool(torch.equal(count[:rows // 2], count[rows // 2:]))
+        fwd_table._leanffn_pairs_up = cached
+    return cached
 
 
 def _bs_dgrad(dy2d: torch.Tensor, weight: torch.Tensor, dgrad_table: torch.Tensor, in_features: int,
-              a2=None, b2=None, count: Optional[torch.Tensor] = None) -> torch.Tensor:
+              a2=None, b2=None, count: Optional[torch.Tensor] = None, **epilogue) -> torch.Tensor:
+    """dX = dY . W over the nonzero blocks; ``epilogue`` = the activation-backward arguments of ``ops.gemm``
+    (epilogue, act, aux, out, out2) when the product feeds an activation's backward directly."""
     block = weight.shape[-1]
     num_blocks = weight.numel() // (block * block)
     return ops.gemm(dy2d, weight, M=dy2d.shape[0], N_=in_features, K=dy2d.shape[1], b_mn_major=True, a2=a2, b2=b2,
                     bs_mode=2, bs_block=block, bs_nnz=dgrad_table.shape[1], bs_num_blocks=num_blocks,
-                    bs_index=dgrad_table, bs_count=count)
+                    bs_index=dgrad_table, bs_count=count, **epilogue)
 
 
 def _bs_wgrad(dy2d: torch.Tensor, x2d: torch.Tensor, weight_like: torch.Tensor, wgrad_table: torch.Tensor,

@@ -65,7 +65,13 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     } else {
       if (d->a_mn_major || d->N % d->bs_block != 0 || d->K % d->bs_block != 0) return LEANFFN_ERR_SHAPE;
     }
-    if (epi != LEANFFN_EPI_STORE) return LEANFFN_ERR_UNSUPPORTED;
+    const bool bwd_epilogue = epi == LEANFFN_EPI_GLU_BWD || epi == LEANFFN_EPI_ACT_BWD;
+    const bool fwd_epilogue = epi == LEANFFN_EPI_DROPOUT_RESIDUAL || epi == LEANFFN_EPI_GLU_FWD;
+    if (epi != LEANFFN_EPI_STORE && !(d->bs_mode == 2 && bwd_epilogue) && !(d->bs_mode == 1 && fwd_epilogue))
+      return LEANFFN_ERR_UNSUPPORTED;
+    // gated forward: one tile = a gate block and its linear partner, which must share their input blocks
+    if (epi == LEANFFN_EPI_GLU_FWD && (d->bs_block != 128 || (d->N / 2) % 128 != 0 || d->in_dtype != LEANFFN_BF16))
+      return LEANFFN_ERR_UNSUPPORTED;
   }
   if (d->scatter_world != 0) {
     if (d->scatter_world < 0 || d->scatter_world > 8) return LEANFFN_ERR_TOO_LARGE;
@@ -121,7 +127,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
               (d->aux_dtype == LEANFFN_BF16 || epi == LEANFFN_EPI_DROPOUT_RESIDUAL);
   if (d->D2 != nullptr) tc = tc && aligned16(d->D2) && pitch16(d->ldd2, d->d_dtype);
   if (needs_d2) tc = tc && d->d_dtype == LEANFFN_BF16;
-  if (epi == LEANFFN_EPI_GLU_FWD) tc = tc && (d->N / 2) % 8 == 0 && d->bs_mode == 0;
+  if (epi == LEANFFN_EPI_GLU_FWD) tc = tc && (d->N / 2) % 8 == 0 && (d->bs_mode == 0 || d->bs_mode == 1);
   if (ep.threshold != 0u) tc = tc && d->elem_offset % 4 == 0;
 
   if (tc) {

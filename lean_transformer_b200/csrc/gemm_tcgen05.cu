@@ -114,10 +114,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   const int kpb = p.bs_block > 0 ? p.bs_block / BLOCK_K : 1;  // k-blocks per sparse block
-  const int sub = p.bs_block > 0 ? p.bs_block / BLOCK_N : 1;  // tiles per sparse block along N (and M for wgrad)
+  const int sub = p.bs_block >= BLOCK_N ? p.bs_block / BLOCK_N : 1;  // tiles per sparse block along N (and M for wgrad)
   // main k-blocks of a tile: fixed for dense / wgrad, per table row for block-sparse forward / dgrad
   auto main_k_blocks = [&](int n_blk) {
-    if ((p.bs_mode == 1 || p.bs_mode == 2) && p.bs_count != nullptr) return __ldg(p.bs_count + n_blk / sub) * kpb;
+    if ((p.bs_mode == 1 || p.bs_mode == 2) && p.bs_count != nullptr)
+      return __ldg(p.bs_count + (p.glu_split > 0 ? n_blk : n_blk / sub)) * kpb;
     return p.num_k_blocks;
   };
   const int group_m = p.group_m > 0 ? p.group_m : GROUP_M;
@@ -156,16 +157,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const CUtensorMap* ma = second ? &tmA2 : &tmA;
         const CUtensorMap* mb = second ? &tmB2 : &tmB;
         // coordinates (elements): a_k / b_k along the reduction axis, a_r / b_r along rows
-        int a_k, a_r, b_k, b_r;
+        // gated forward: the 256-wide tile is 128 gate rows (from b_r) + the matching 128 linear rows (from b_r2)
+        int a_k, a_r, b_k, b_r, b_r2 = 0;
         if (second) {
           const int k2 = kb - kb_main;
           a_k = b_k = k2 * BLOCK_K;
           a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
+          if (p.glu_split > 0) b_r = n_blk * 128, b_r2 = p.glu_split + n_blk * 128;
         } else if (p.bs_mode == 0) {
           a_k = b_k = kb * BLOCK_K;
           a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
+          if (p.glu_split > 0) b_r = n_blk * 128, b_r2 = p.glu_split + n_blk * 128;
+        } else if (p.bs_mode == 1 && p.glu_split > 0) {
+          // gated block-sparse forward (128-wide blocks): table rows n_blk (gate) and n_blk + I/128 (linear) list the
+          // same input blocks, so one A tile meets the weight blocks of both halves
+          const int t = kb / kpb, kk = kb - t * kpb;
+          const int2* table = reinterpret_cast<const int2*>(p.bs_index);
+          const int2 e = __ldg(table + n_blk * p.bs_nnz + t);
+          const int2 e2 = __ldg(table + (n_blk + p.glu_split / p.bs_block) * p.bs_nnz + t);
+          a_k = e.y * p.bs_block + kk * BLOCK_K;
+          a_r = m_blk * TILE_M;
+          b_k = kk * BLOCK_K;
+          b_r = e.x * p.bs_block;
+          b_r2 = e2.x * p.bs_block;
         } else if (p.bs_mode == 1) {
           // table row = output block; entry = (weight block f, input block j)
           const int t = kb / kpb, kk = kb - t * kpb;
@@ -201,9 +217,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int c = 0; c < BLOCK_N / 64; ++c) tma_load_2d(sb + c * CHUNK_BYTES, mb, bar, b_r + c * 64, b_k);
         } else {
           if (p.glu_split > 0) {
-            // 256-wide tile = 128 gate rows + the matching 128 linear rows of the gated weight
-            tma_load_2d(sb, mb, bar, b_k, n_blk * 128);
-            tma_load_2d(sb + 128 * BLOCK_K * 2, mb, bar, b_k, p.glu_split + n_blk * 128);
+            tma_load_2d(sb, mb, bar, b_k, b_r);
+            tma_load_2d(sb + 128 * BLOCK_K * 2, mb, bar, b_k, b_r2);
           } else {
 #pragma unroll
             for (int c = 0; c < BLOCK_N / 128; ++c)

@@ -22,7 +22,8 @@ import torch.nn as nn
 from . import _native as N
 from . import ops
 from .blocksparse.linear import (GeneralizedLinear, TritonMatmulForLinearLayer, _GeneralizedLinear, _kind,
-                                 cast_cached, dense_weight_grad, linear_backward_core, linear_forward_core,
+                                 can_fuse_gated_forward, cast_cached, input_grad, linear_backward_core, linear_forward_core,
+                                 weight_grad,
                                  resolve_compute_dtype)
 from .utils import ACT2FN, resolve_activation
 
@@ -209,7 +210,6 @@ class _LeanFFN(torch.autograd.Function):
             input_2d = input_2d.contiguous()
         tokens = input_2d.shape[0]
         i2h_dense = _kind(i2h_weight, i2h_forward_indices, i2h_backward_indices, i2h_matmul_op) == "dense"
-        h2o_dense = _kind(h2o_weight, h2o_forward_indices, h2o_backward_indices, h2o_matmul_op) == "dense"
         out_features1 = i2h_bias.shape[0] if i2h_bias is not None else _out_features(
             i2h_weight, i2h_forward_indices, i2h_matmul_op)
         inter = out_features1 // 2 if gated else out_features1
@@ -217,10 +217,13 @@ class _LeanFFN(torch.autograd.Function):
         input_ln = ops.layer_norm_forward(input_2d, ln_weight, ln_bias, ln_eps, cdt)
 
         pre_activation = torch.empty((tokens, out_features1), dtype=cdt, device=input.device)
-        if i2h_dense:
+        i2h_fused = i2h_dense or (gated and can_fuse_gated_forward(i2h_weight, i2h_forward_indices,
+                                                                   i2h_backward_indices, i2h_matmul_op, cdt))
+        if i2h_fused:
             hid_act = torch.empty((tokens, inter), dtype=cdt, device=input.device)
             _, i2h_lowrank_hid = linear_forward_core(
-                input_ln, i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, None, None, None, cdt,
+                input_ln, i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices,
+                i2h_backward_indices, i2h_matmul_op, cdt,
                 epilogue=N.EPI_GLU_FWD if gated else N.EPI_ACT_FWD, act=act, out=pre_activation, out2=hid_act)
         else:
             _, i2h_lowrank_hid = linear_forward_core(
@@ -235,21 +238,18 @@ class _LeanFFN(torch.autograd.Function):
             seed, offset = next_dropout_stream(input.device, tokens * hidden, hidden)
             ctx._dropout_stream = (seed, offset)
         post_ln_input = None
-        if ctx._use_post_ln or not h2o_dense:
-            out, h2o_lowrank_hid = linear_forward_core(
+        if ctx._use_post_ln:
+            post_ln_input, h2o_lowrank_hid = linear_forward_core(
                 hid_act, h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
                 h2o_backward_indices, h2o_matmul_op, cdt)
-            if ctx._use_post_ln:
-                post_ln_input = out
-                out = ops.layer_norm_forward(post_ln_input, post_ln_weight, post_ln_bias, ln_eps, cdt,
-                                             dropout_p=dropout if use_dropout else 0.0, seed=seed,
-                                             elem_offset=offset, residual=input_2d if residual else None)
-            elif use_dropout or residual:
-                out = _dropout_residual(out, dropout if use_dropout else 0.0, seed, offset,
-                                        input_2d if residual else None)
+            out = ops.layer_norm_forward(post_ln_input, post_ln_weight, post_ln_bias, ln_eps, cdt,
+                                         dropout_p=dropout if use_dropout else 0.0, seed=seed,
+                                         elem_offset=offset, residual=input_2d if residual else None)
         else:
+            # dense or block-sparse: bias, dropout and the residual add ride in the product's epilogue
             out, h2o_lowrank_hid = linear_forward_core(
-                hid_act, h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, None, None, None, cdt,
+                hid_act, h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
+                h2o_backward_indices, h2o_matmul_op, cdt,
                 epilogue=N.EPI_DROPOUT_RESIDUAL, aux=input_2d if residual else None,
                 dropout_p=dropout if use_dropout else 0.0, seed=seed, elem_offset=offset)
         del hid_act
@@ -294,41 +294,32 @@ class _LeanFFN(torch.autograd.Function):
                 grad_h2o_out, post_ln_input, post_ln_weight, ctx._ln_eps, None, cdt, need_param_grads=need_post)
 
         # backward(... -> nonlinearity -> linear_h2o -> ...): dgrad2 rematerialises the activation
-        h2o_dense = _kind(h2o_weight, h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op) == "dense"
-        h2o_needs = [True, needs[10], needs[11], needs[12], needs[13]]
+        h2o_kind = _kind(h2o_weight, h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op)
         tokens = input_2d.shape[0]
         inter = pre_activation.shape[1] // 2 if gated else pre_activation.shape[1]
         need_hid = bool(needs[10] or needs[12])  # hid_act feeds the weight and first-low-rank gradients
-        if h2o_dense:
-            grad_pre = torch.empty_like(pre_activation)
-            hid_act = torch.empty((tokens, inter), dtype=cdt, device=input.device) if need_hid else None
-            grad_h2o_bias = ops.column_sum(grad_h2o_out) if needs[11] else None
-            grad_lowrank_hid = a2 = b2 = None
-            if h2o_lowrank_first is not None:
-                grad_lowrank_hid = ops.gemm(grad_h2o_out, cast_cached(h2o_lowrank_second, cdt), b_mn_major=True)
-                a2, b2 = grad_lowrank_hid, cast_cached(h2o_lowrank_first, cdt)
-            # the dgrad epilogue applies the activation backward and rematerialises hid_act, which the
-            # weight gradients below then consume
-            ops.gemm(grad_h2o_out, cast_cached(h2o_weight, cdt), b_mn_major=True, a2=a2, b2=b2,
-                     epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=act, aux=pre_activation,
-                     out=grad_pre, out2=hid_act)
-            grad_h2o_weight = grad_h2o_lowrank_first = grad_h2o_lowrank_second = None
-            if needs[10]:
-                grad_h2o_weight = dense_weight_grad(grad_h2o_out, hid_act, h2o_weight)
-            if h2o_lowrank_first is not None and needs[13]:
-                grad_h2o_lowrank_second = ops.gemm(grad_h2o_out, h2o_lowrank_hid, a_mn_major=True, b_mn_major=True,
-                                                   out_dtype=h2o_lowrank_second.dtype)
-            if h2o_lowrank_first is not None and needs[12]:
-                grad_h2o_lowrank_first = ops.gemm(grad_lowrank_hid, hid_act, a_mn_major=True, b_mn_major=True,
-                                                  out_dtype=h2o_lowrank_first.dtype)
-        else:
-            hid_act = ops.activation_forward(pre_activation, gated, act)
-            (grad_hid_act, grad_h2o_weight, grad_h2o_bias, grad_h2o_lowrank_first,
-             grad_h2o_lowrank_second) = linear_backward_core(
-                grad_h2o_out, hid_act, h2o_lowrank_hid, h2o_weight, h2o_lowrank_first, h2o_lowrank_second,
-                h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op, h2o_needs, cdt)
-            grad_pre, _ = ops.activation_backward(grad_hid_act, pre_activation, gated, act)
-            del grad_hid_act
+        grad_pre = torch.empty_like(pre_activation)
+        hid_act = torch.empty((tokens, inter), dtype=cdt, device=input.device) if need_hid else None
+        grad_h2o_bias = ops.column_sum(grad_h2o_out) if needs[11] else None
+        grad_lowrank_hid = a2 = b2 = None
+        if h2o_lowrank_first is not None:
+            grad_lowrank_hid = ops.gemm(grad_h2o_out, cast_cached(h2o_lowrank_second, cdt), b_mn_major=True)
+            a2, b2 = grad_lowrank_hid, cast_cached(h2o_lowrank_first, cdt)
+        # the input-gradient epilogue (dense or block-sparse weight alike) applies the activation backward and
+        # rematerialises hid_act, which the weight gradients below then consume
+        input_grad(h2o_kind, grad_h2o_out, h2o_weight, h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op,
+                   cdt, a2=a2, b2=b2, epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=act,
+                   aux=pre_activation, out=grad_pre, out2=hid_act)
+        grad_h2o_weight = grad_h2o_lowrank_first = grad_h2o_lowrank_second = None
+        if needs[10]:
+            grad_h2o_weight = weight_grad(h2o_kind, grad_h2o_out, hid_act, h2o_weight, h2o_forward_indices,
+                                          h2o_backward_indices, ctx._h2o_matmul_op)
+        if h2o_lowrank_first is not None and needs[13]:
+            grad_h2o_lowrank_second = ops.gemm(grad_h2o_out, h2o_lowrank_hid, a_mn_major=True, b_mn_major=True,
+                                               out_dtype=h2o_lowrank_second.dtype)
+        if h2o_lowrank_first is not None and needs[12]:
+            grad_h2o_lowrank_first = ops.gemm(grad_lowrank_hid, hid_act, a_mn_major=True, b_mn_major=True,
+                                              out_dtype=h2o_lowrank_first.dtype)
         del hid_act, grad_h2o_out
         grad_h2o_weight = _offer("h2o_weight", only_if(needs[10], grad_h2o_weight), h2o_weight)
         grad_h2o_bias = _offer("h2o_bias", only_if(needs[11], grad_h2o_bias), h2o_bias)

@@ -286,6 +286,52 @@ def test_blocksparse_native_vs_oracle(cuda_device, in_f, out_f, bs, dtype):
     _ops.check_device_status(cuda_device)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_blocksparse_fused_epilogues_match_unfused(cuda_device, dtype):
+    """Block-sparse products with the gated activation (forward), dropout + residual (forward) and the activation
+    backward (input gradient) in their epilogues against the same product followed by the stand-alone kernels."""
+    from lean_transformer_b200 import _native as N, ops
+    from lean_transformer_b200.blocksparse import layout as LY
+    from lean_transformer_b200.blocksparse.native_backend import (_bs_dgrad, _bs_forward, gate_and_linear_blocks_pair_up,
+                                                                  native_tables)
+    torch.manual_seed(3)
+    bs, hidden, inter, tokens = 128, 512, 2048, 400
+    fwd1, bwd1 = LY.get_indices_from_layout(LY.get_blocksparse_layout(2 * inter, hidden, f"pixelfly(block_size={bs})"))
+    fwd2, bwd2 = LY.get_indices_from_layout(LY.get_blocksparse_layout(hidden, inter, f"pixelfly(block_size={bs})"))
+    fwd1, bwd1, fwd2, bwd2 = (t.to(cuda_device) for t in (fwd1, bwd1, fwd2, bwd2))
+    w1 = (torch.randn(hidden, bwd1.shape[1], bs, device=cuda_device) * 0.05).to(dtype)
+    w2 = (torch.randn(inter, bwd2.shape[1], bs, device=cuda_device) * 0.05).to(dtype)
+    b1 = torch.randn(2 * inter, device=cuda_device) * 0.1
+    x = torch.randn(tokens, hidden, device=cuda_device).to(dtype)
+    t1, t2 = native_tables(fwd1, bwd1, w1.shape[1]), native_tables(fwd2, bwd2, w2.shape[1])
+    assert gate_and_linear_blocks_pair_up(t1[0])
+
+    pre_ref = _bs_forward(x, w1, t1[0], 2 * inter, bias=b1)
+    hid_ref = ops.activation_forward(pre_ref, True, 0)
+    if dtype == torch.bfloat16:  # fp32 runs on the SIMT kernel, which applies the activation as a second pass anyway
+        pre, hid = torch.empty_like(pre_ref), torch.empty_like(hid_ref)
+        _bs_forward(x, w1, t1[0], 2 * inter, out=pre, bias=b1, epilogue=N.EPI_GLU_FWD, act=0, out2=hid)
+        assert torch.equal(pre, pre_ref) and torch.equal(hid, hid_ref)
+
+    res = torch.randn(tokens, hidden, device=cuda_device).to(dtype)
+    plain = _bs_forward(hid_ref, w2, t2[0], hidden)
+    want = ops.dropout(plain, 0.25, 11, 64, residual=res)
+    got = _bs_forward(hid_ref, w2, t2[0], hidden, epilogue=N.EPI_DROPOUT_RESIDUAL, aux=res, dropout_p=0.25, seed=11,
+                      elem_offset=64)
+    rtol, atol = (BF16_RTOL, BF16_ATOL) if dtype == torch.bfloat16 else (FP32_RTOL, FP32_ATOL)
+    assert_close(got, want.double().cpu(), rtol, atol, "dropout + residual in the sparse forward")
+    assert torch.equal(got == res, want == res)  # same elements dropped
+
+    dy = torch.randn(tokens, hidden, device=cuda_device).to(dtype)
+    dhid = _bs_dgrad(dy, w2, t2[1], inter)
+    dpre_ref, hid_again = ops.activation_backward(dhid, pre_ref, True, 0, want_hid=True)
+    dpre, hid2 = torch.empty_like(pre_ref), torch.empty_like(hid_ref)
+    _bs_dgrad(dy, w2, t2[1], inter, epilogue=N.EPI_GLU_BWD, act=0, aux=pre_ref, out=dpre, out2=hid2)
+    assert torch.equal(hid2, hid_ref)
+    assert_close(dpre, dpre_ref.double().cpu(), rtol, atol, "activation backward in the sparse input gradient")
+    ops.check_device_status(cuda_device)
+
+
 @pytest.mark.parametrize("bs,dtype", [(16, torch.float32), (128, torch.bfloat16)])
 def test_row_major_block_order_operator(cuda_device, bs, dtype):
     """The 'triton' weight order ([1, nnz, bs, bs] in layout.nonzero() order) with an UNBALANCED layout,
