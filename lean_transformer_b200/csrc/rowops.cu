@@ -48,6 +48,27 @@ __device__ __forceinline__ float row_sum(float v, float* smem, int row_in_block,
   return v;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Pair of sums over the WPR warps of one row with ONE block barrier: callers alternate between two shared buffers
+// (`parity`), so a buffer is rewritten only after a later barrier has seen every reader leave it.
+template <int WPR>
+__device__ __forceinline__ float2 row_sum_pair(float a, float b, float2* buffers, int buffer_len, int& parity,
+                                               int row_in_block, int warp_in_row, int lane) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  if constexpr (WPR > 1) {
+    float2* buf = buffers + parity * buffer_len + row_in_block * WPR;
+    parity ^= 1;
+    if (lane == 0) buf[warp_in_row] = make_float2(a, b);
+    __syncthreads();
+    const float2 t = lane < WPR ? buf[lane] : make_float2(0.f, 0.f);
+    a = warp_sum(t.x);
+    b = warp_sum(t.y);
+  }
+  return make_float2(a, b);
+}
+
 constexpr int LN_THREADS = 256;
 
 // ---- LayerNorm forward ---------------------------------------------------------------------
@@ -174,13 +195,19 @@ ln_fwd_generic_kernel(const TX* __restrict__ x, const TP* __restrict__ gamma, co
 // Partial dgamma / dbeta of the rows a (block, row-slot) pair visits go to
 // part[(blockIdx.x * ROWS_PER_BLOCK + row_in_block) * 2 * cols + {0, cols} + c]; a column-sum pass
 // finishes them.
+// Wide rows are spread over up to 32 warps (1024 threads) so that a thread keeps few values and the SM many warps:
+// the kernel is a chain of load -> four row reductions -> store per row, and only other warps hide that latency.
+__host__ __device__ constexpr int ln_bwd_threads(int wpr) { return wpr > LN_THREADS / 32 ? wpr * 32 : LN_THREADS; }
+
 template <typename TD, typename TX, typename TP, typename TR, typename TO, int VPT, int WPR>
-__global__ void __launch_bounds__(LN_THREADS)
+__global__ void __launch_bounds__(ln_bwd_threads(WPR))
 ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __restrict__ gamma,
               const TR* __restrict__ dres, TO* __restrict__ dx, float* __restrict__ part, int64_t rows, int cols,
               float eps) {
-  constexpr int ROWS_PER_BLOCK = (LN_THREADS / 32) / WPR;
-  __shared__ float red[LN_THREADS / 32];
+  constexpr int THREADS = ln_bwd_threads(WPR);
+  constexpr int ROWS_PER_BLOCK = (THREADS / 32) / WPR;
+  __shared__ float2 red[2 * (THREADS / 32)];
+  int parity = 0;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int row_in_block = warp / WPR;
@@ -199,7 +226,24 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
     const int64_t row = row0 + row_in_block;
     const bool row_ok = row < rows;
     float v[VPT][4], d[VPT][4];
+    Vec4<TR> res[VPT];  // residual gradient, requested together with x and dy (one memory round trip per row)
     float s = 0.f;
+    {
+      // the row this thread visits next goes to L2 now: a block works on one row at a time, so nothing else
+      // hides the DRAM latency of its loads
+      const int64_t next = row + static_cast<int64_t>(gridDim.x) * ROWS_PER_BLOCK;
+      if (next < rows) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int c = (t_in_row + i * 32 * WPR) * 4;
+          if (c < cols) {
+            prefetch_l2(x + next * cols + c);
+            prefetch_l2(dy + next * cols + c);
+            if (dres != nullptr && dx != nullptr) prefetch_l2(dres + next * cols + c);
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = (t_in_row + i * 32 * WPR) * 4;
@@ -210,13 +254,14 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
         Vec4<TD> qd;
         qd.load(dy + row * cols + c);
         qd.get(d[i]);
+        if (dres != nullptr && dx != nullptr) res[i].load(dres + row * cols + c);
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[i][j] = d[i][j] = 0.f;
       }
       s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
     }
-    const float mean = row_sum<WPR>(s, red, row_in_block, warp_in_row, lane) * inv_cols;
+    const float mean = row_sum_pair<WPR>(s, 0.f, red, THREADS / 32, parity, row_in_block, warp_in_row, lane).x * inv_cols;
     float s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -229,7 +274,8 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
         }
       }
     }
-    const float rstd = rsqrtf(row_sum<WPR>(s2, red, row_in_block, warp_in_row, lane) * inv_cols + eps);
+    const float rstd =
+        rsqrtf(row_sum_pair<WPR>(s2, 0.f, red, THREADS / 32, parity, row_in_block, warp_in_row, lane).x * inv_cols + eps);
     // v <- normalised x, d stays dy; g = dy * gamma
     float sg = 0.f, sgx = 0.f;
 #pragma unroll
@@ -252,8 +298,8 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
         sgx += d[i][j] * xn;
       }
     }
-    const float mg = row_sum<WPR>(sg, red, row_in_block, warp_in_row, lane) * inv_cols;
-    const float mgx = row_sum<WPR>(sgx, red, row_in_block, warp_in_row, lane) * inv_cols;
+    const float2 sums = row_sum_pair<WPR>(sg, sgx, red, THREADS / 32, parity, row_in_block, warp_in_row, lane);
+    const float mg = sums.x * inv_cols, mgx = sums.y * inv_cols;
     if (dx != nullptr) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
@@ -263,10 +309,8 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
 #pragma unroll
           for (int j = 0; j < 4; ++j) o[j] = rstd * (d[i][j] - mg - v[i][j] * mgx);
           if (dres != nullptr) {
-            Vec4<TR> q;
             float r[4];
-            q.load(dres + row * cols + c);
-            q.get(r);
+            res[i].get(r);
 #pragma unroll
             for (int j = 0; j < 4; ++j) o[j] += r[j];
           }
@@ -604,12 +648,15 @@ static LnBwdPlan ln_bwd_plan(int64_t rows, int64_t cols) {
     else if (cols <= 512) p.vpt = 4, p.wpr = 1;
     else if (cols <= 1024) p.vpt = 2, p.wpr = 4;
     else if (cols <= 2048) p.vpt = 2, p.wpr = 8;
-    else if (cols <= 4096) p.vpt = 4, p.wpr = 8;
-    else if (cols <= 8192) p.vpt = 8, p.wpr = 8;
+    else if (cols <= 4096) p.vpt = 2, p.wpr = 16;
+    else if (cols <= 8192) p.vpt = 2, p.wpr = 32;
     else p.vpt = 16, p.wpr = 8;
-    const int rpb = (LN_THREADS / 32) / p.wpr;
+    const int threads = ln_bwd_threads(p.wpr);
+    const int rpb = (threads / 32) / p.wpr;
     int64_t blocks = (rows + rpb - 1) / rpb;
-    const int64_t cap = static_cast<int64_t>(sms) * 2;
+    // co-resident blocks per SM: the 2-vector variants use 64 registers per thread
+    const int per_sm = p.vpt <= 2 ? 1024 / threads : 2;
+    const int64_t cap = static_cast<int64_t>(sms) * per_sm;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     p.blocks = blocks;
@@ -638,15 +685,15 @@ static int32_t ln_bwd_dispatch(const void* dy, const void* x, const void* gamma,
   const unsigned grid = static_cast<unsigned>(plan.blocks);
 #define LN_BWD_CASE(VPT, WPR)                                                                                  \
   if (plan.vpt == VPT && plan.wpr == WPR)                                                                      \
-    ln_bwd_kernel<TD, TX, TP, TR, TO, VPT, WPR><<<grid, LN_THREADS, 0, st>>>(dyp, xp, gp, rp, dxp, part, rows, \
-                                                                            c, eps);
+    ln_bwd_kernel<TD, TX, TP, TR, TO, VPT, WPR><<<grid, ln_bwd_threads(WPR), 0, st>>>(dyp, xp, gp, rp, dxp, part, \
+                                                                                     rows, c, eps);
   LN_BWD_CASE(1, 1)
   else LN_BWD_CASE(2, 1)
   else LN_BWD_CASE(4, 1)
   else LN_BWD_CASE(2, 4)
   else LN_BWD_CASE(2, 8)
-  else LN_BWD_CASE(4, 8)
-  else LN_BWD_CASE(8, 8)
+  else LN_BWD_CASE(2, 16)
+  else LN_BWD_CASE(2, 32)
   else LN_BWD_CASE(16, 8)
   else ln_bwd_generic_kernel<TD, TX, TP, TR, TO><<<grid, LN_THREADS, 0, st>>>(dyp, xp, gp, rp, dxp, part, rows, c, eps);
 #undef LN_BWD_CASE
