@@ -332,6 +332,53 @@ def test_blocksparse_fused_epilogues_match_unfused(cuda_device, dtype):
     ops.check_device_status(cuda_device)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_gemm_scatter_epilogue_on_one_gpu(ops, cuda_device, out_dtype, world):
+    """The reduce-scatter epilogue with every "replica" in this GPU's memory: two products are added into the
+    replicas; each replica must hold the sum of both in the 256-row blocks it owns and stay untouched elsewhere."""
+    from lean_transformer_b200 import dist as ldist
+    torch.manual_seed(world)
+    M, N, K, shift = 1024 + 128, 384, 512, 8
+    a = [torch.randn(K, M, device=cuda_device).bfloat16() for _ in range(2)]   # weight-gradient form: both MN-major
+    b = [torch.randn(K, N, device=cuda_device).bfloat16() for _ in range(2)]
+    replicas = [torch.full((M, N), 7.0, device=cuda_device, dtype=out_dtype) for _ in range(world)]
+    for rank, rep in enumerate(replicas):  # what begin_step does: zero the owned blocks
+        for blk in ldist.owned_row_blocks(M, world, rank, shift):
+            rep[blk << shift:(blk + 1) << shift] = 0
+    addresses = [r.data_ptr() for r in replicas]
+    for i in range(2):
+        ops.gemm(a[i], b[i], a_mn_major=True, b_mn_major=True, out=replicas[0], scatter=(addresses, shift))
+    torch.cuda.synchronize()
+    total = sum(a[i].double().t() @ b[i].double() for i in range(2)).cpu()
+    for rank, rep in enumerate(replicas):
+        owned = torch.zeros(M, dtype=torch.bool)
+        for blk in ldist.owned_row_blocks(M, world, rank, shift):
+            owned[blk << shift:(blk + 1) << shift] = True
+        got = rep.double().cpu()
+        assert torch.equal(got[~owned], torch.full_like(got[~owned], 7.0)), "rows of other owners were touched"
+        assert_close(got[owned], total[owned], BF16_RTOL, BF16_ATOL, f"replica {rank}", scale_atol=True)
+    # scattered products exist on the tensor-core path only
+    with pytest.raises(Exception):
+        ops.gemm(a[0].float(), b[0].float(), a_mn_major=True, b_mn_major=True, out=replicas[0].float(),
+                 scatter=(addresses, shift))
+    ops.check_device_status(cuda_device)
+
+
+def test_copy_2d_moves_owned_blocks(ops, cuda_device):
+    from lean_transformer_b200 import dist as ldist
+    rows, cols, world, rank, shift = 2048, 24, 4, 1, 8
+    src = torch.randn(rows, cols, device=cuda_device)
+    dst = torch.zeros_like(src)
+    start, pitch, width, height = ldist.handout_plan(rows, cols, 4, world, rank, shift)
+    ops.copy_2d(dst.data_ptr() + start, pitch, src.data_ptr() + start, pitch, width, height)
+    torch.cuda.synchronize()
+    owned = torch.zeros(rows, dtype=torch.bool)
+    for blk in ldist.owned_row_blocks(rows, world, rank, shift):
+        owned[blk << shift:(blk + 1) << shift] = True
+    assert torch.equal(dst.cpu()[owned], src.cpu()[owned]) and not dst.cpu()[~owned].any()
+
+
 @pytest.mark.parametrize("bs,dtype", [(16, torch.float32), (128, torch.bfloat16)])
 def test_row_major_block_order_operator(cuda_device, bs, dtype):
     """The 'triton' weight order ([1, nnz, bs, bs] in layout.nonzero() order) with an UNBALANCED layout,
