@@ -221,4 +221,7 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LEAN_REFERENCE_ROOT", "/root/reference"))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LEAN_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: make_golden.py <checkout of learning-at-home/lean_transformer>  (or set LEAN_REFERENCE_ROOT)")
+    main(root)
