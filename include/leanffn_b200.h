@@ -249,6 +249,10 @@ typedef struct leanffn_gemm_desc {
   int32_t scatter_world;
   int32_t scatter_block_shift;
   void* scatter_D[8];
+  /* bs_mode 3 with bs_block == 128 only: != 0 asserts that weight blocks 2i and 2i+1 read the same input block
+   * (equal second entries of their table rows; bs_num_blocks even), as in the reference's native order with an
+   * even number of blocks per input block.  One CTA then computes both blocks from one tile of x. */
+  int32_t bs_wgrad_pairs;
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);

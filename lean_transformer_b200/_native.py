@@ -36,6 +36,7 @@ class GemmDesc(ctypes.Structure):
         ("dropout_p", c_float), ("seed", c_uint64), ("elem_offset", c_uint64),
         ("status_word", c_void_p), ("force_simt", c_int32), ("max_ctas", c_int32),
         ("scatter_world", c_int32), ("scatter_block_shift", c_int32), ("scatter_D", c_void_p * 8),
+        ("bs_wgrad_pairs", c_int32),
     ]
 
 

@@ -91,13 +91,26 @@ def _bs_dgrad(dy2d: torch.Tensor, weight: torch.Tensor, dgrad_table: torch.Tenso
                     bs_index=dgrad_table, bs_count=count, **epilogue)
 
 
+def weight_blocks_pair_up(wgrad_table: torch.Tensor) -> bool:
+    """True if weight blocks 2i and 2i+1 always read the same input block (native order with an even number of
+    blocks per input block): one CTA can then produce both gradients from one tile of x.  Remembered on the
+    (cached, immutable) table tensor."""
+    cached = getattr(wgrad_table, "_leanffn_pairs_up", None)
+    if cached is None:
+        flat = wgrad_table.reshape(-1, 2)
+        cached = flat.shape[0] % 2 == 0 and bool(torch.equal(flat[0::2, 1], flat[1::2, 1]))
+        wgrad_table._leanffn_pairs_up = cached
+    return cached
+
+
 def _bs_wgrad(dy2d: torch.Tensor, x2d: torch.Tensor, weight_like: torch.Tensor, wgrad_table: torch.Tensor,
               out_dtype: torch.dtype) -> torch.Tensor:
     block = weight_like.shape[-1]
     num_blocks = weight_like.numel() // (block * block)
     out = torch.empty((num_blocks * block, block), dtype=out_dtype, device=dy2d.device)
+    pairs = block == 128 and dy2d.dtype == torch.bfloat16 and weight_blocks_pair_up(wgrad_table)
     ops.gemm(dy2d, x2d, a_mn_major=True, b_mn_major=True, M=num_blocks * block, N_=block, K=dy2d.shape[0], out=out,
-             bs_mode=3, bs_block=block, bs_nnz=1, bs_num_blocks=num_blocks, bs_index=wgrad_table)
+             bs_mode=3, bs_block=block, bs_nnz=1, bs_num_blocks=num_blocks, bs_index=wgrad_table, bs_wgrad_pairs=pairs)
     return out.view(weight_like.shape)
 
 

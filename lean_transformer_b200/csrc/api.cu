@@ -239,6 +239,11 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
         if (p.group_m == 0) p.group_m = 8;
       }
     }
+    if (d->bs_mode == 3 && d->bs_wgrad_pairs != 0 && d->bs_block == 128 && d->bs_num_blocks % 2 == 0 &&
+        tile_override != 128) {
+      p.m_subtiles = 2;  // 256 x 128 tile = two weight blocks that share their x tile
+      p.num_m_blocks = d->bs_num_blocks / 2;
+    }
     cudaError_t ce;
     return gemm_tcgen05(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
                         d->K2 > 0 ? &B2 : nullptr, p, block_n, st, &ce);

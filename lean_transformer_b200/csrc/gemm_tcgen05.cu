@@ -158,7 +158,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const CUtensorMap* mb = second ? &tmB2 : &tmB;
         // coordinates (elements): a_k / b_k along the reduction axis, a_r / b_r along rows
         // gated forward: the 256-wide tile is 128 gate rows (from b_r) + the matching 128 linear rows (from b_r2)
-        int a_k, a_r, b_k, b_r, b_r2 = 0;
+        int a_k, a_r, b_k, b_r, b_r2 = 0, a_r1 = -1;
         if (second) {
           const int k2 = kb - kb_main;
           a_k = b_k = k2 * BLOCK_K;
@@ -198,6 +198,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           a_r = m_blk * TILE_M;
           b_k = e.x * p.bs_block + kk * BLOCK_K;
           b_r = (n_blk % sub) * BLOCK_N;
+        } else if (MT == 2) {
+          // weight gradient, two 128-wide weight blocks per CTA: blocks 2*m_blk and 2*m_blk + 1 read the same
+          // input block (the caller's guarantee), so both sub-tiles share the x stage
+          const int2* table = reinterpret_cast<const int2*>(p.bs_index);
+          const int2 e = __ldg(table + 2 * m_blk);
+          const int2 e1 = __ldg(table + 2 * m_blk + 1);
+          a_k = b_k = kb * BLOCK_K;
+          a_r = e.x * p.bs_block;
+          a_r1 = e1.x * p.bs_block;
+          b_r = e.y * p.bs_block + n_blk * BLOCK_N;
         } else {
           // table row = weight block f; entry = (output block o, input block j)
           const int2 e = __ldg(reinterpret_cast<const int2*>(p.bs_index) + m_blk / sub);
@@ -206,8 +216,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           b_r = e.y * p.bs_block + n_blk * BLOCK_N;
         }
         if constexpr (A_MN) {
+          if (a_r1 < 0) a_r1 = a_r + BLOCK_M;  // second sub-tile: the next 128 rows unless set above
 #pragma unroll
-          for (int c = 0; c < TILE_M / 64; ++c) tma_load_2d(sa + c * CHUNK_BYTES, ma, bar, a_r + c * 64, a_k);
+          for (int c = 0; c < TILE_M / 64; ++c)
+            tma_load_2d(sa + c * CHUNK_BYTES, ma, bar, (c < 2 ? a_r : a_r1 - BLOCK_M) + c * 64, a_k);
         } else {
 #pragma unroll
           for (int t = 0; t < MT; ++t) tma_load_2d(sa + t * A_STAGE_BYTES, ma, bar, a_k, a_r + t * BLOCK_M);
@@ -411,6 +423,7 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
   if (block_n == 128 && p.m_subtiles == 2) {
     if (!a_mn && !b_mn) e = tc_launch_t<false, false, 128, 2>(ta, tb, ta2, tb2, p, st);
     else if (!a_mn && b_mn) e = tc_launch_t<false, true, 128, 2>(ta, tb, ta2, tb2, p, st);
+    else if (a_mn && b_mn) e = tc_launch_t<true, true, 128, 2>(ta, tb, ta2, tb2, p, st);
     else return LEANFFN_ERR_UNSUPPORTED;
   } else if (block_n == 256 && p.m_subtiles == 2) {
     if (!a_mn && !b_mn) e = tc_launch_t<false, false, 256, 2>(ta, tb, ta2, tb2, p, st);

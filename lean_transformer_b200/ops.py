@@ -237,7 +237,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0,
          bs_mode: int = 0, bs_block: int = 0, bs_nnz: int = 0, bs_num_blocks: int = 0,
          bs_index: Optional[torch.Tensor] = None, bs_count: Optional[torch.Tensor] = None,
-         force_simt: bool = False, scatter=None) -> torch.Tensor:
+         force_simt: bool = False, scatter=None, bs_wgrad_pairs: bool = False) -> torch.Tensor:
     """D = A(m,k) . B(n,k) with the fused epilogues of ``leanffn_gemm`` (see include/leanffn_b200.h).
 
     Dense operands are 2-D with unit inner stride: a K-major A is [M, K], an MN-major A is [K, M];
@@ -293,6 +293,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     d.status_word = _ptr(status_word(a.device))
     d.force_simt = int(force_simt)
     d.max_ctas = _max_ctas
+    d.bs_wgrad_pairs = int(bs_wgrad_pairs)
     if scatter is not None:
         addresses, shift = scatter
         assert 1 <= len(addresses) <= 8 and epilogue == N.EPI_STORE and bias is None and out.dim() == 2
