@@ -185,11 +185,6 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
       const char* v = getenv("LEANFFN_GEMM_KERNEL");
       return v != nullptr && strcmp(v, "pair") == 0;
     }();
-    static const int pair_tune = []() {
-      const char* v = getenv("LEANFFN_PAIR_TUNE");
-      return v != nullptr ? atoi(v) : 0;
-    }();
-    p.tune = pair_tune;
     if (pair_enabled && d->bs_mode == 0 && block_n == 256 && d->M > 128 && d->scatter_world == 0) {
       p.num_m_blocks = static_cast<int32_t>((d->M + 255) / 256);
       return gemm_tcgen05_pair(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,

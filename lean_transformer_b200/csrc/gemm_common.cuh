@@ -83,7 +83,6 @@ struct TcParams {
   int32_t max_ctas;   // > 0: cap on the persistent grid
   int32_t group_m;    // M-tiles that share one sweep over N in the tile order (0 = kernel default)
   int32_t m_subtiles; // one-CTA kernel: 1 = 128-row tiles (two accumulator stages), 2 = 256 x 256 tiles
-  int32_t tune;       // experiment knobs of the CTA-pair kernel: bits 0-3 stages (0 = default), bit 4 spin-wait
   int32_t* status;
   EpiParams ep;
 };

@@ -57,11 +57,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
   constexpr int STAGES_ALLOC = MAX_STAGES;
-  const int STAGES = (p.tune & 15) ? (p.tune & 15) : 6;
-  const bool spin = (p.tune & 16) != 0;
-  const bool prof = (p.tune & 256) != 0;       // probe: per-role wait-cycle counters printed by the first pair
-  const bool skip_store = (p.tune & 32) != 0;  // probe: epilogue reads TMEM but stores nothing
-  const bool skip_load = (p.tune & 64) != 0;   // probe: no TMA loads, MMAs run on whatever shared memory holds
+  constexpr int STAGES = MAX_STAGES;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES_ALLOC * STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -134,7 +130,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    long long w_empty = 0, t_begin = clock64();
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
@@ -143,25 +138,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int b_r = p.glu_split > 0 ? (leader ? n_blk * 128 : p.glu_split + n_blk * 128)
                                       : n_blk * BLOCK_N + static_cast<int>(rank) * 128;
       for (int kb = 0; kb < kb_total; ++kb) {
-        const long long tw = prof ? clock64() : 0;
-        if (*abort_ptr != 0 || !(spin ? mbar_spin_bounded(empty_bar(stage), phase ^ 1u)
-                                      : mbar_wait_bounded(empty_bar(stage), phase ^ 1u))) {
+        if (*abort_ptr != 0 || !mbar_wait_bounded(empty_bar(stage), phase ^ 1u)) {
           raise_abort(LEANFFN_DEV_TIMEOUT_PRODUCER);
           ok = false;
           break;
         }
-        if (prof) w_empty += clock64() - tw;
         const uint32_t sa = smem_base + stage * STAGE_BYTES;
         const uint32_t sb = sa + A_BYTES;
         const uint32_t bar = leader_full0 + 8u * stage;  // the leader's full barrier, cluster-window address
-        if (skip_load) {
-          if (leader) mbar_arrive(full_bar(stage));
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          continue;
-        }
         if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
         const bool second = kb >= p.num_k_blocks;
         const CUtensorMap* ma = second ? &tmA2 : &tmA;
@@ -185,8 +169,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
       }
     }
-    if (prof && blockIdx.x < 2)
-      printf("cta %d producer: total %lld cycles, waiting for free stages %lld\n", blockIdx.x, clock64() - t_begin, w_empty);
   } else if (warp == 1 && lane == 0 && leader) {
     // ------------------------------- MMA issuer (leader CTA only) --------------------------------
     constexpr uint32_t idesc = make_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
@@ -199,24 +181,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    long long w_full = 0, w_tempty = 0, t_begin = clock64();
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-      const long long t0 = prof ? clock64() : 0;
       if (*abort_ptr != 0 || !mbar_wait_bounded(tempty_bar(acc_stage), acc_phase ^ 1u)) {
         raise_abort(LEANFFN_DEV_TIMEOUT_MMA);
         break;
       }
-      if (prof) w_tempty += clock64() - t0;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc_stage * BLOCK_N;
       for (int kb = 0; kb < kb_total; ++kb) {
-        const long long tw = prof ? clock64() : 0;
-        if (*abort_ptr != 0 || !(spin ? mbar_spin_bounded(full_bar(stage), phase) : mbar_wait_bounded(full_bar(stage), phase))) {
+        if (*abort_ptr != 0 || !mbar_wait_bounded(full_bar(stage), phase)) {
           raise_abort(LEANFFN_DEV_TIMEOUT_MMA);
           ok = false;
           break;
         }
-        if (prof) w_full += clock64() - tw;
         tc_fence_after();
         const uint32_t sa = smem_base + stage * STAGE_BYTES;
         const uint32_t sb = sa + A_BYTES;
@@ -239,9 +216,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         acc_phase ^= 1u;
       }
     }
-    if (prof && blockIdx.x < 2)
-      printf("cta %d mma: total %lld cycles, waiting for operands %lld, waiting for a free accumulator %lld\n",
-             blockIdx.x, clock64() - t_begin, w_full, w_tempty);
   } else if (warp >= 2) {
     // ------------------------------- epilogue (both CTAs, own 128 rows) ---------------------------
     const EpiParams& ep = p.ep;
@@ -251,20 +225,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     float* patch = reinterpret_cast<float*>(smem_gen + STAGES_ALLOC * STAGE_BYTES + 256) + (warp - 2) * EPI_PATCH_FLOATS;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
-    long long w_tfull = 0, t_begin = clock64();
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
-      const long long tw = prof ? clock64() : 0;
       if (*abort_ptr != 0 || !mbar_wait_bounded(tfull_bar(acc_stage), acc_phase)) {
         if (lane == 0) raise_abort(LEANFFN_DEV_TIMEOUT_EPILOGUE);
         break;
       }
-      if (prof) w_tfull += clock64() - tw;
       tc_fence_after();
       const int64_t row0 = static_cast<int64_t>(m_blk) * BLOCK_M + rank * 128 + quarter * 32;
       const uint32_t t_acc = tmem_base + lane_addr + acc_stage * BLOCK_N;
-      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, true, patch, lane, (warp - 2) >> 2, 2, skip_store);
+      epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, true, patch, lane, (warp - 2) >> 2, 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8u * acc_stage);
@@ -273,9 +244,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         acc_phase ^= 1u;
       }
     }
-    if (prof && blockIdx.x < 2 && warp == 2 && lane == 0)
-      printf("cta %d epilogue warp: total %lld cycles, waiting for accumulators %lld\n", blockIdx.x,
-             clock64() - t_begin, w_tfull);
   }
 
   // ------------------------------- teardown ------------------------------------------------------

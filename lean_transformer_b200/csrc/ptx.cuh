@@ -53,32 +53,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Non-suspending poll of an mbarrier phase (mbarrier.test_wait): lower wake-up latency than try_wait, at the
-// cost of issue slots; used by the single producer / MMA threads whose latency is on the critical path.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred P;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_test_wait(bar, parity)) return true;
-    if (clock64() - t0 > 2000000000LL) return false;
-  }
-}
-
 // Bounded wait: gives up after ~WAIT_LIMIT_CYCLES SM clocks (about a second) and returns false.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {

@@ -195,7 +195,7 @@ __device__ __forceinline__ void act_fwd_bwd8(int act, const float (&x)[8], float
 template <int BLOCK_N, int KIND, int ACT>
 __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
                                                 int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
-                                                int block_step, bool skip_store) {
+                                                int block_step) {
   const int sub_row = lane >> 2;        // + 8*i
   const int sub_col = (lane & 3) * 8;   // within the 32-column block
   if constexpr (KIND == LEANFFN_EPI_GLU_FWD) {
@@ -206,7 +206,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       for (int blk = block_begin; blk < 4; blk += block_step) {
         const int64_t j0 = static_cast<int64_t>(n_blk) * 128 + blk * 32;
         const int64_t j = j0 + sub_col;
-        const bool live = j < inter && !skip_store;
+        const bool live = j < inter;
         uint4 g[4], l[4];
         {
           float bias[32];
@@ -242,7 +242,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
 #pragma unroll 1
       for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
         const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32 + sub_col;
-        const bool live = col < ep.N && !skip_store;
+        const bool live = col < ep.N;
         float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (live && ep.bias != nullptr) load8(ep.bias, ep.bias_dtype, col, b);
         float v[4][8];
@@ -266,7 +266,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
     for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
       const int64_t col0 = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
       const int64_t col = col0 + sub_col;
-      const bool live = col < ep.N && !skip_store;
+      const bool live = col < ep.N;
       uint4 w[4];
       {
         float bias[32];
@@ -294,7 +294,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
     uint4 n0[4], n1[4];
     auto request_aux = [&](int blk) {
       const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32 + sub_col;
-      const bool live = col < ep.N && !skip_store && ep.aux != nullptr;
+      const bool live = col < ep.N && ep.aux != nullptr;
       const bf16* aux = static_cast<const bf16*>(ep.aux);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -322,7 +322,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
     for (int blk = block_begin; blk < NUM_BLOCKS; blk += block_step) {
       const int64_t col0 = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
       const int64_t col = col0 + sub_col;
-      const bool live = col < ep.N && !skip_store;
+      const bool live = col < ep.N;
       uint4 c0[4], c1[4];
       if constexpr (HAS_AUX) {
 #pragma unroll
@@ -403,24 +403,24 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
 template <int BLOCK_N, int KIND>
 __device__ __forceinline__ void epilogue_tile_act(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
                                                   int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
-                                                  int block_step, bool skip_store) {
+                                                  int block_step) {
   // gelu_fused and silu get their own inlined loops; everything else shares the out-of-line switch
   if (ep.act == LEANFFN_ACT_GELU_TANH)
     epilogue_tile_t<BLOCK_N, KIND, LEANFFN_ACT_GELU_TANH>(ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane,
-                                                          block_begin, block_step, skip_store);
+                                                          block_begin, block_step);
   else if (ep.act == LEANFFN_ACT_SILU)
     epilogue_tile_t<BLOCK_N, KIND, LEANFFN_ACT_SILU>(ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane,
-                                                     block_begin, block_step, skip_store);
+                                                     block_begin, block_step);
   else
     epilogue_tile_t<BLOCK_N, KIND, -1>(ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, block_begin,
-                                       block_step, skip_store);
+                                       block_step);
 }
 
 template <int BLOCK_N>
 __device__ __forceinline__ void epilogue_tile(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
                                               int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
-                                              int block_step, bool skip_store = false) {
-#define LEANFFN_EPI_ARGS ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, block_begin, block_step, skip_store
+                                              int block_step) {
+#define LEANFFN_EPI_ARGS ep, glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, block_begin, block_step
   switch (ep.kind) {
     case LEANFFN_EPI_STORE: epilogue_tile_t<BLOCK_N, LEANFFN_EPI_STORE, -1>(LEANFFN_EPI_ARGS); break;
     case LEANFFN_EPI_DROPOUT_RESIDUAL: epilogue_tile_t<BLOCK_N, LEANFFN_EPI_DROPOUT_RESIDUAL, -1>(LEANFFN_EPI_ARGS); break;
