@@ -377,12 +377,6 @@ def _out_features(weight, forward_indices, matmul_op):
     return weight.shape[0]
 
 
-def _dropout_residual(out, p, seed, offset, residual):
-    """out = dropout(out) + residual as one elementwise kernel, for the configurations where the output GEMM
-    cannot fuse it (block-sparse output projection)."""
-    return ops.dropout(out, p, seed, offset, residual=residual)
-
-
 # ---- stages of the plain-autograd twin ---------------------------------------------------------------
 class _LayerNormFunction(torch.autograd.Function):
     @staticmethod
