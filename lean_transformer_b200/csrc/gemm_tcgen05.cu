@@ -310,6 +310,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
+#pragma unroll 1
+      for (int t = 0; t < MT; ++t)
+        epilogue_prefetch_aux<BLOCK_N>(ep, static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32, n_blk, lane,
+                                       (warp - 2) >> 2, 2);
       if (*abort_ptr != 0 || !mbar_wait_bounded(tfull_bar(acc_stage), acc_phase)) {
         report(p.status, LEANFFN_DEV_TIMEOUT_EPILOGUE);
         *abort_ptr = 1;

@@ -400,6 +400,33 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
   }
 }
 
+// Ask L2 for the residual / pre-activation rows that epilogue_tile will read for the same arguments.  Called while
+// the warp would otherwise sit waiting for the accumulator, so the epilogue's own loads find their data on chip.
+// One lane per 64-byte row segment issues the request.
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_prefetch_aux(const EpiParams& ep, int64_t row0, int n_blk, int lane,
+                                                      int block_begin, int block_step) {
+  const bool has_aux = ep.kind == LEANFFN_EPI_DROPOUT_RESIDUAL || ep.kind == LEANFFN_EPI_GLU_BWD ||
+                       ep.kind == LEANFFN_EPI_ACT_BWD;
+  if (!has_aux || ep.aux == nullptr || (lane & 3) != 0) return;
+  const int esize = ep.aux_dtype == LEANFFN_BF16 ? 2 : 4;
+  const char* aux = static_cast<const char*>(ep.aux);
+#pragma unroll 1
+  for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
+    const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
+    if (col >= ep.N) break;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t row = row0 + 8 * i + (lane >> 2);
+      if (row >= ep.M) continue;
+      const char* p = aux + (row * ep.ldaux + col) * esize;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+      if (esize == 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + 64));
+      if (ep.kind == LEANFFN_EPI_GLU_BWD) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + ep.N * esize));
+    }
+  }
+}
+
 template <int BLOCK_N, int KIND>
 __device__ __forceinline__ void epilogue_tile_act(const EpiParams& ep, int glu_split, uint32_t t_acc, int64_t row0,
                                                   int n_blk, bool acc_valid, float* patch, int lane, int block_begin,
