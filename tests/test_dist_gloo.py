@@ -82,6 +82,44 @@ def test_shard_tokens_covers_everything():
         ldist.shard_tokens(8, 2, 2)
 
 
+def _owner_worker(rank, world, port, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=20))
+    try:
+        from lean_transformer_b200 import dist as ldist
+        weight = torch.nn.Parameter(torch.zeros(6, 4))
+        bias = torch.nn.Parameter(torch.zeros(6, dtype=torch.float64))  # gradient arrives in another dtype
+        stranger = torch.zeros(3, 4)                                    # not among the registered parameters
+        sync = ldist.GradSync(params=[weight, bias], wire_dtype=torch.float32)
+        g_w = torch.full((6, 4), float(rank + 1))
+        g_b = torch.full((6,), float(10 * (rank + 1)))
+        g_s = torch.ones(3, 4)
+        # the calling convention of the backward: (name, gradient, parameter) -> taken?
+        assert sync.reduce("i2h_weight", g_w, weight.detach()) is True     # found by storage, not by object
+        assert sync.reduce("i2h_bias", g_b, bias) is True
+        assert sync.reduce("i2h_lowrank_first", g_s, stranger) is False   # left to autograd, unreduced
+        assert weight.grad is None and bias.grad is None                  # nothing is delivered before finish()
+        assert sync.finish() == 2 and sync.unclaimed == ["i2h_lowrank_first"]
+        total = sum(range(1, world + 1))
+        assert torch.equal(weight.grad, torch.full((6, 4), float(total)))
+        assert bias.grad.dtype == torch.float64 and torch.equal(bias.grad, torch.full((6,), 10.0 * total, dtype=torch.float64))
+        assert torch.equal(g_s, torch.ones(3, 4))
+        # a second backward before the optimizer step accumulates
+        assert sync.reduce("i2h_weight", torch.ones(6, 4), weight) is True
+        sync.finish()
+        assert torch.equal(weight.grad, torch.full((6, 4), float(total + world)))
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_grad_sync_takes_ownership_of_hooked_gradients(tmp_path):
+    """GradSync as the gradient-ready callback: it keeps the gradient, reduces it and delivers ``param.grad`` in
+    ``finish()`` (autograd never touches a tensor that a collective is still writing)."""
+    mp.spawn(_owner_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
 def test_failed_rank_surfaces_as_error_not_hang(tmp_path):
     """A rank that dies before the collective: the job ends with an exception within the group timeout."""
     with pytest.raises(Exception):
