@@ -1,0 +1,45 @@
+"""The C ABI from a host that is not Python: the header must be valid C and C++, and a plain-C program linked against
+libleanffn_b200.so and the CUDA runtime must get correct results from the kernels."""
+import os
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "leanffn_b200.h"
+CUDA = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+
+
+@pytest.mark.parametrize("compiler,flags", [("gcc", ["-x", "c", "-std=c99"]), ("g++", ["-x", "c++", "-std=c++11"])])
+def test_header_is_valid_c_and_cxx(compiler, flags):
+    if shutil.which(compiler) is None:
+        pytest.skip(f"{compiler} not installed")
+    res = subprocess.run([compiler, "-fsyntax-only", "-Wall", "-Werror", *flags, str(HEADER)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+
+
+def _build_c_host(out_dir: Path) -> Path:
+    from lean_transformer_b200 import build
+    lib = build.build()
+    exe = out_dir / "leanffn_c_host"
+    cmd = ["gcc", "-std=c99", "-O1", "-Wall", "-I", str(ROOT / "include"), "-I", str(CUDA / "include"),
+           str(ROOT / "tests" / "c_host" / "leanffn_c_host.c"), "-o", str(exe), str(lib),
+           "-L", str(CUDA / "lib64"), "-lcudart", "-lm", f"-Wl,-rpath,{lib.parent}", f"-Wl,-rpath,{CUDA / 'lib64'}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    return exe
+
+
+def test_c_host_compiles_and_links(tmp_path):
+    if shutil.which("gcc") is None or not (CUDA / "include" / "cuda_runtime_api.h").exists():
+        pytest.skip("gcc or the CUDA toolkit headers are not installed")
+    assert _build_c_host(tmp_path).exists()
+
+
+@pytest.mark.gpu
+def test_c_host_runs_the_kernels(tmp_path):
+    exe = _build_c_host(tmp_path)
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "C HOST OK" in res.stdout, res.stdout + res.stderr
