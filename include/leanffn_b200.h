@@ -29,6 +29,7 @@ extern "C" {
 /* element types */
 #define LEANFFN_F32 0
 #define LEANFFN_BF16 1
+#define LEANFFN_TF32 2 /* leanffn_gemm in_dtype only: fp32 storage, TF32 multiplication on the tensor cores */
 
 /* activations: lean_transformer/utils.py:24-38 (gelu_fused) and the transformers ACT2FN names
  * the reference re-exports at lean_transformer/utils.py:80 */
@@ -199,7 +200,8 @@ int32_t leanffn_transpose(const void* x, int32_t dtype, int64_t ldx, void* y, in
  */
 typedef struct leanffn_gemm_desc {
   int32_t M, N, K;
-  int32_t in_dtype;      /* LEANFFN_BF16: tcgen05 tensor-core path; LEANFFN_F32: SIMT fp32 path */
+  int32_t in_dtype;      /* LEANFFN_BF16: tcgen05 tensor-core path; LEANFFN_F32: SIMT fp32 path;
+                            LEANFFN_TF32: fp32 operands on the tensor cores, see leanffn_split_tf32 */
   const void* A;
   int64_t lda;
   int32_t a_mn_major;
@@ -256,6 +258,21 @@ typedef struct leanffn_gemm_desc {
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
+
+/* fp32 accuracy from TF32 tensor-core multiplications ("3xTF32").  A TF32 multiplication reads only the 10 leading
+ * mantissa bits of each fp32 operand.  Write x = hi + lo with hi = x truncated to those bits and lo = x - hi; then
+ * a.b = a_hi.b_hi + a_hi.b_lo + a_lo.b_hi up to a relative 2^-21, and the three products are ONE product over a
+ * reduction axis of three times the length.  This call writes, for x [rows, cols] (leading dimension ldx),
+ *   role 0 (the A operand):  out [rows, 3*cols] = ( hi | hi | lo )
+ *   role 1 (the B operand):  out [rows, 3*cols] = ( hi | lo | hi )
+ * and leanffn_gemm with in_dtype LEANFFN_TF32, K = 3*cols on the two outputs gives the fp32-accurate product
+ * (K-major operands, dense, LEANFFN_EPI_STORE with optional bias, fp32 result, M, N >= 64, N a multiple of 8,
+ * cols a multiple of 4).  With in_dtype LEANFFN_TF32, `aux` (fp32 [M, N], may be D itself) is added to the
+ * result: tensor-core accumulators truncate, so the error grows with the length of the reduction axis, and a long
+ * axis is covered by several calls over slices of it that keep a running sum.
+ * Stands in for the fp32 cuBLAS products of the reference's fp32 (non-autocast) mode. */
+int32_t leanffn_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int32_t role,
+                           void* stream);
 
 /* Strided device-to-device copy of `height` pieces of `width_bytes` (cudaMemcpy2DAsync; between two GPUs with peer
  * access it runs on a copy engine and occupies no SM).  Used to hand the reduced row blocks of a scattered weight

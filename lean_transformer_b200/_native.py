@@ -12,7 +12,7 @@ LIB_NAME = "libleanffn_b200.so"
 LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
 
 # element types / activations / epilogues: keep in sync with include/leanffn_b200.h
-F32, BF16 = 0, 1
+F32, BF16, TF32 = 0, 1, 2
 ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_TANH, ACT_SIGMOID, ACT_IDENTITY = range(7)
 EPI_STORE, EPI_GLU_FWD, EPI_ACT_FWD, EPI_DROPOUT_RESIDUAL, EPI_GLU_BWD, EPI_ACT_BWD = range(6)
 DEV_STATUS_NAMES = {0: "ok", 1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out"}
@@ -63,6 +63,7 @@ _SIGNATURES = {
     "leanffn_cast": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_void_p]),
     "leanffn_transpose": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "leanffn_copy_2d": (c_int32, [c_void_p, c_uint64, c_void_p, c_uint64, c_uint64, c_uint64, c_void_p]),
+    "leanffn_split_tf32": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
 }
 

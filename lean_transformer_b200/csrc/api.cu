@@ -42,7 +42,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   if (d == nullptr) return LEANFFN_ERR_NULL;
   if (d->M < 0 || d->N <= 0 || d->K <= 0 || d->K2 < 0) return LEANFFN_ERR_SHAPE;
   if (d->M > 0 && (d->A == nullptr || d->B == nullptr || d->D == nullptr)) return LEANFFN_ERR_NULL;
-  if (d->in_dtype != LEANFFN_F32 && d->in_dtype != LEANFFN_BF16) return LEANFFN_ERR_DTYPE;
+  if (d->in_dtype != LEANFFN_F32 && d->in_dtype != LEANFFN_BF16 && d->in_dtype != LEANFFN_TF32) return LEANFFN_ERR_DTYPE;
   if (d->d_dtype != LEANFFN_F32 && d->d_dtype != LEANFFN_BF16) return LEANFFN_ERR_DTYPE;
   if (d->epilogue < LEANFFN_EPI_STORE || d->epilogue > LEANFFN_EPI_ACT_BWD) return LEANFFN_ERR_UNSUPPORTED;
   if (d->act < 0 || d->act >= LEANFFN_ACT_COUNT) return LEANFFN_ERR_UNSUPPORTED;
@@ -107,6 +107,32 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   ep.scatter_world = d->scatter_world;
   ep.scatter_shift = d->scatter_block_shift;
   for (int k = 0; k < 8; ++k) ep.scatter_D[k] = k < d->scatter_world ? d->scatter_D[k] : nullptr;
+
+  // ---- fp32 operands on the tensor cores (TF32 multiplication) ---------------------------------------
+  if (d->in_dtype == LEANFFN_TF32) {
+    if (d->a_mn_major || d->b_mn_major || d->bs_mode != 0 || d->K2 != 0 || epi != LEANFFN_EPI_STORE ||
+        d->d_dtype != LEANFFN_F32 || d->scatter_world != 0 || d->M < 64 || d->N < 64 || d->K < 32 || d->N % 8 != 0)
+      return LEANFFN_ERR_UNSUPPORTED;
+    if (!aligned16(d->A) || !aligned16(d->B) || !aligned16(d->D) || !pitch16(d->lda, LEANFFN_F32) ||
+        !pitch16(d->ldb, LEANFFN_F32) || !pitch16(d->ldd, LEANFFN_F32) || (d->bias != nullptr && !aligned16(d->bias)))
+      return LEANFFN_ERR_ALIGN;
+    if (d->aux != nullptr && (d->aux_dtype != LEANFFN_F32 || !aligned16(d->aux) || !pitch16(d->ldaux, LEANFFN_F32)))
+      return LEANFFN_ERR_ALIGN;
+    TcParams p{};
+    p.ep = ep;
+    p.status = d->status_word;
+    p.max_ctas = d->max_ctas;
+    p.m_subtiles = 1;
+    const int block_n = d->N <= 128 ? 128 : 256;
+    p.num_m_blocks = static_cast<int32_t>((d->M + 127) / 128);
+    p.num_n_blocks = static_cast<int32_t>((d->N + block_n - 1) / block_n);
+    p.num_k_blocks = static_cast<int32_t>((d->K + 31) / 32);
+    TcOperand A{}, B{};
+    A.ptr = d->A, A.ld = d->lda, A.rows = d->M, A.cols = d->K;
+    B.ptr = d->B, B.ld = d->ldb, B.rows = d->N, B.cols = d->K;
+    cudaError_t ce;
+    return gemm_tcgen05(false, false, A, B, nullptr, nullptr, p, block_n, st, &ce, true);
+  }
 
   // Reduction length seen by the kernels.
   int64_t k_eff = d->K;
@@ -304,5 +330,14 @@ extern "C" int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const vo
   if (dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes) return LEANFFN_ERR_SHAPE;
   const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch_bytes, src, src_pitch_bytes, width_bytes, height,
                                           cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+}
+
+extern "C" int32_t leanffn_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int32_t role,
+                                      void* stream) {
+  if (rows < 0 || cols <= 0 || (role != 0 && role != 1)) return LEANFFN_ERR_SHAPE;
+  if (rows == 0) return LEANFFN_OK;
+  if (x == nullptr || out == nullptr) return LEANFFN_ERR_NULL;
+  const cudaError_t e = launch_split_tf32(x, ldx, out, rows, cols, role, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }

@@ -58,7 +58,9 @@ __device__ __forceinline__ void report(int32_t* status, int32_t code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
-template <bool A_MN, bool B_MN, int BLOCK_N, int MT>
+// TF32: the operands are fp32 (32 elements = 128 bytes per k-block row, K-major only) multiplied as TF32; the byte
+// geometry of stages, boxes and descriptors is the same as for bf16.
+template <bool A_MN, bool B_MN, int BLOCK_N, int MT, bool TF32 = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
@@ -67,6 +69,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int STAGES = Cfg::STAGES;
   constexpr int ACC_STAGES = Cfg::ACC_STAGES;
   constexpr int TILE_M = BLOCK_M * MT;
+  constexpr int KE = TF32 ? BLOCK_K / 2 : BLOCK_K;  // elements per k-block along the reduction axis
+  static_assert(!TF32 || (!A_MN && !B_MN), "TF32 operands are K-major");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * Cfg::STAGE_BYTES;
@@ -161,12 +165,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int a_k, a_r, b_k, b_r, b_r2 = 0, a_r1 = -1;
         if (second) {
           const int k2 = kb - kb_main;
-          a_k = b_k = k2 * BLOCK_K;
+          a_k = b_k = k2 * KE;
           a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
           if (p.glu_split > 0) b_r = n_blk * 128, b_r2 = p.glu_split + n_blk * 128;
         } else if (p.bs_mode == 0) {
-          a_k = b_k = kb * BLOCK_K;
+          a_k = b_k = kb * KE;
           a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
           if (p.glu_split > 0) b_r = n_blk * 128, b_r2 = p.glu_split + n_blk * 128;
@@ -245,7 +249,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------- MMA issuer ----------------------------------------------
-    constexpr uint32_t idesc = make_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
+    constexpr uint32_t idesc = TF32 ? make_idesc_tf32(BLOCK_M, BLOCK_N) : make_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
     constexpr uint64_t a_hi = A_MN ? make_smem_desc_hi(CHUNK_BYTES, 1024) : make_smem_desc_hi(16, 1024);
     constexpr uint64_t b_hi = B_MN ? make_smem_desc_hi(CHUNK_BYTES, 1024) : make_smem_desc_hi(16, 1024);
     constexpr uint32_t a_kstep = A_MN ? 2048u : 32u;  // bytes per UMMA_K step inside a stage
@@ -282,7 +286,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int t = 0; t < MT; ++t) {  // the sub-tiles read the same B stage
             const uint64_t da = make_smem_desc(sa + t * A_STAGE_BYTES + k * a_kstep, a_hi);
-            umma_bf16(d_tmem + t * BLOCK_N, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (TF32)
+              umma_tf32(d_tmem + t * BLOCK_N, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_bf16(d_tmem + t * BLOCK_N, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
         }
         umma_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
@@ -374,23 +381,24 @@ static EncodeTiledFn get_encode_fn() {
 // 2D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension ld (elements);
 // box = box_cols (inner, 64 elements = 128 bytes) x box_rows, 128-byte swizzle, zero fill out of bounds.
 bool make_tmap_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_cols,
-                    uint32_t box_rows) {
+                    uint32_t box_rows, bool fp32 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * (fp32 ? 4 : 2)};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  return fn(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+            dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool A_MN, bool B_MN, int BLOCK_N, int MT>
+template <bool A_MN, bool B_MN, int BLOCK_N, int MT, bool TF32 = false>
 static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2,
                                const CUtensorMap& b2, const TcParams& p, cudaStream_t st) {
   using Cfg = TcConfig<BLOCK_N, MT>;
-  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, BLOCK_N, MT>;
+  auto kern = gemm_tcgen05_kernel<A_MN, B_MN, BLOCK_N, MT, TF32>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -409,11 +417,12 @@ static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const
 // Returns LEANFFN_OK, or a negative code when the problem does not fit the tensor-core kernel's
 // constraints (the caller then uses the SIMT kernel).
 int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
-                     const TcOperand* B2, TcParams p, int block_n, cudaStream_t st, cudaError_t* cuda_err) {
+                     const TcOperand* B2, TcParams p, int block_n, cudaStream_t st, cudaError_t* cuda_err, bool tf32) {
   *cuda_err = cudaSuccess;
   CUtensorMap ta, tb, ta2, tb2;
   auto encode = [&](CUtensorMap* m, const TcOperand& o, bool mn) {
-    return make_tmap_bf16(m, o.ptr, o.rows, o.cols, o.ld, 64, mn ? 64 : 128);
+    if (tf32) return make_tmap_bf16(m, o.ptr, o.rows, o.cols, o.ld, 32, 128, true);
+    return make_tmap_bf16(m, o.ptr, o.rows, o.cols, o.ld, 64, mn ? 64 : 128, false);
   };
   if (!encode(&ta, A, a_mn) || !encode(&tb, B, b_mn)) return LEANFFN_ERR_DRIVER;
   if (A2 != nullptr && B2 != nullptr) {
@@ -424,7 +433,11 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
   }
   cudaError_t e;
 #define TC_GO(AM, BM, BN) e = tc_launch_t<AM, BM, BN, 1>(ta, tb, ta2, tb2, p, st)
-  if (block_n == 128 && p.m_subtiles == 2) {
+  if (tf32) {
+    if (a_mn || b_mn || p.m_subtiles != 1) return LEANFFN_ERR_UNSUPPORTED;
+    if (block_n == 256) e = tc_launch_t<false, false, 256, 1, true>(ta, tb, ta2, tb2, p, st);
+    else e = tc_launch_t<false, false, 128, 1, true>(ta, tb, ta2, tb2, p, st);
+  } else if (block_n == 128 && p.m_subtiles == 2) {
     if (!a_mn && !b_mn) e = tc_launch_t<false, false, 128, 2>(ta, tb, ta2, tb2, p, st);
     else if (!a_mn && b_mn) e = tc_launch_t<false, true, 128, 2>(ta, tb, ta2, tb2, p, st);
     else if (a_mn && b_mn) e = tc_launch_t<true, true, 128, 2>(ta, tb, ta2, tb2, p, st);

@@ -262,7 +262,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
 // ---- host side -------------------------------------------------------------------------------------
 bool make_tmap_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, uint32_t box_cols,
-                    uint32_t box_rows);
+                    uint32_t box_rows, bool fp32 = false);
 
 template <bool A_MN, bool B_MN>
 static cudaError_t pair_launch_t(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2,

@@ -106,6 +106,18 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with fp32 operands in shared memory read as TF32 (the low 13 mantissa bits are ignored).
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // mbarrier arrives once all previously issued UMMAs of this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -206,6 +218,14 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
          | (1u << 10)                                // B format: bf16
          | ((a_mn_major ? 1u : 0u) << 15)            // A major
          | ((b_mn_major ? 1u : 0u) << 16)            // B major
+         | (static_cast<uint32_t>(N >> 3) << 17)     // N / 8
+         | (static_cast<uint32_t>(M >> 4) << 24);    // M / 16
+}
+// Instruction descriptor for kind::tf32 (fp32 storage, TF32 multiplication), fp32 accumulation, K-major operands.
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N) {
+  return (1u << 4)                                   // D format: f32
+         | (2u << 7)                                 // A format: tf32
+         | (2u << 10)                                // B format: tf32
          | (static_cast<uint32_t>(N >> 3) << 17)     // N / 8
          | (static_cast<uint32_t>(M >> 4) << 24);    // M / 16
 }

@@ -254,6 +254,13 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           if (row >= ep.M) continue;
 #pragma unroll
           for (int q = 0; q < 8; ++q) v[i][q] += b[q];
+          if (ep.aux != nullptr && ep.aux_dtype == LEANFFN_F32) {
+            // running sum over calls that each cover a slice of a long reduction axis (aux may be D itself)
+            float prev[8];
+            load8(ep.aux, LEANFFN_F32, row * ep.ldaux + col, prev);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[i][q] += prev[q];
+          }
           if (ep.scatter_world > 0)
             red_add_f32x8(scatter_target(ep, row), row * ep.ldd + col, v[i]);
           else

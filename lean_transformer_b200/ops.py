@@ -144,26 +144,30 @@ def layer_norm_backward(dy: torch.Tensor, x: torch.Tensor, gamma: Optional[torch
     return dx, dgamma, dbeta
 
 
-def activation_forward(pre: torch.Tensor, gated: bool, act: int) -> torch.Tensor:
-    _require_cuda(pre)
+def activation_forward(pre: torch.Tensor, gated: bool, act: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(pre, out)
     assert pre.dim() == 2 and pre.is_contiguous()
     rows = pre.shape[0]
     inter = pre.shape[1] // 2 if gated else pre.shape[1]
-    hid = torch.empty((rows, inter), dtype=pre.dtype, device=pre.device)
+    hid = out if out is not None else torch.empty((rows, inter), dtype=pre.dtype, device=pre.device)
+    assert hid.shape == (rows, inter) and hid.dtype == pre.dtype and hid.is_contiguous()
     N.check(N.lib.leanffn_activation_forward(_ptr(pre), _ptr(hid), _dt(pre), rows, inter, int(gated), act,
                                              _stream(pre)), "leanffn_activation_forward")
     _count()
     return hid
 
 
-def activation_backward(dhid: torch.Tensor, pre: torch.Tensor, gated: bool, act: int, want_hid: bool = False):
-    _require_cuda(dhid, pre)
+def activation_backward(dhid: torch.Tensor, pre: torch.Tensor, gated: bool, act: int, want_hid: bool = False,
+                        out: Optional[torch.Tensor] = None, hid_out: Optional[torch.Tensor] = None):
+    _require_cuda(dhid, pre, out, hid_out)
     assert pre.dim() == 2 and pre.is_contiguous() and dhid.is_contiguous() and dhid.dtype == pre.dtype
     rows = pre.shape[0]
     inter = pre.shape[1] // 2 if gated else pre.shape[1]
     assert dhid.shape == (rows, inter)
-    dpre = torch.empty_like(pre)
-    hid = torch.empty_like(dhid) if want_hid else None
+    dpre = out if out is not None else torch.empty_like(pre)
+    assert dpre.shape == pre.shape and dpre.dtype == pre.dtype and dpre.is_contiguous()
+    hid = hid_out if hid_out is not None else (torch.empty_like(dhid) if want_hid else None)
+    assert hid is None or (hid.shape == dhid.shape and hid.dtype == dhid.dtype and hid.is_contiguous())
     N.check(N.lib.leanffn_activation_backward(_ptr(dhid), _ptr(pre), _ptr(dpre), _ptr(hid), _dt(pre), rows, inter,
                                               int(gated), act, _stream(pre)), "leanffn_activation_backward")
     _count()
@@ -227,6 +231,95 @@ def transpose(x: torch.Tensor) -> torch.Tensor:
     return y
 
 
+# ---- fp32 products on the tensor cores ---------------------------------------------------------------
+# fp32 mode multiplies on the tensor cores as three TF32 products folded into one reduction axis (see
+# leanffn_split_tf32 in the header); shapes the kernel does not take (tiny, odd or strided ones) use the SIMT kernel.
+_fp32_tensor_cores = True
+_TF32_SLICE = 1024  # reduction-axis elements per launch: keeps the accumulators' truncation drift near 1e-5 relative
+
+
+def set_fp32_tensor_cores(enabled: bool) -> bool:
+    """Switch fp32 products between the TF32x3 tensor-core path (default) and the fp32 SIMT kernel."""
+    global _fp32_tensor_cores
+    previous, _fp32_tensor_cores = _fp32_tensor_cores, bool(enabled)
+    return previous
+
+
+def _split_tf32(x: torch.Tensor, role: int) -> torch.Tensor:
+    rows, cols = x.shape
+    out = torch.empty((rows, 3 * cols), dtype=torch.float32, device=x.device)
+    N.check(N.lib.leanffn_split_tf32(_ptr(x), x.stride(0), _ptr(out), rows, cols, role, _stream(x)), "leanffn_split_tf32")
+    _count()
+    return out
+
+
+def _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilogue, act, out2, aux, dropout_p, seed,
+                      elem_offset):
+    """fp32 product on the tensor cores with the fused-epilogue semantics of ``gemm``; NotImplemented if the shape
+    or the arguments do not fit (the caller then takes the SIMT kernel)."""
+    m, k = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
+    n = b.shape[1] if b_mn_major else b.shape[0]
+    wide = 2 * n if epilogue == N.EPI_GLU_BWD else n
+    if m < 64 or n < 64 or k < 32 or k % 4 or n % 8 or (out_dtype not in (None, torch.float32)):
+        return NotImplemented
+    if out is not None and (out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (m, wide)):
+        return NotImplemented
+    if bias is not None and bias.dtype != torch.float32:
+        return NotImplemented
+    if aux is not None and (aux.dtype != torch.float32 or not aux.is_contiguous()):
+        return NotImplemented
+    backward_kind = epilogue in (N.EPI_GLU_BWD, N.EPI_ACT_BWD)
+    a_k = transpose(a) if a_mn_major else a
+    b_k = transpose(b) if b_mn_major else b
+    plain = out if (out is not None and not backward_kind) else torch.empty((m, n), dtype=torch.float32, device=a.device)
+    # the accumulators truncate: keep every call's reduction axis short and carry a running sum between calls
+    flops_timer = _gemm_timer
+    for first in range(0, k, _TF32_SLICE):
+        width = min(_TF32_SLICE, k - first)
+        if width < 32:  # a tail too short for a launch of its own: fold it into the previous slice's range
+            break
+        if k - (first + width) < 32:
+            width = k - first
+        a3 = _split_tf32(a_k[:, first:first + width], 0)
+        b3 = _split_tf32(b_k[:, first:first + width], 1)
+        d = N.GemmDesc()
+        d.M, d.N, d.K = int(m), int(n), int(3 * width)
+        d.in_dtype = N.TF32
+        d.A, d.lda, d.B, d.ldb = _ptr(a3), 3 * width, _ptr(b3), 3 * width
+        d.epilogue = N.EPI_STORE
+        d.D, d.ldd, d.d_dtype = _ptr(plain), n, N.F32
+        if first == 0:
+            if bias is not None and not backward_kind:
+                d.bias, d.bias_dtype = _ptr(bias), N.F32
+        else:
+            d.aux, d.ldaux, d.aux_dtype = _ptr(plain), n, N.F32
+        d.status_word = _ptr(status_word(a.device))
+        d.max_ctas = _max_ctas
+        _count()
+        if flops_timer is not None:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
+            end.record()
+            flops_timer.records.append((start, end, 2.0 * m * n * width))
+        else:
+            N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
+        if width == k - first:
+            break
+    if epilogue == N.EPI_STORE:
+        return plain
+    if epilogue == N.EPI_DROPOUT_RESIDUAL:
+        if dropout_p == 0.0 and aux is None:
+            return plain
+        return dropout(plain, dropout_p, seed, elem_offset, residual=aux)
+    gated = epilogue in (N.EPI_GLU_FWD, N.EPI_GLU_BWD)
+    if not backward_kind:
+        activation_forward(plain, gated, act, out=out2)
+        return plain
+    dpre, _ = activation_backward(plain, aux, gated, act, want_hid=out2 is not None, out=out, hid_out=out2)
+    return dpre
+
+
 # ---- GEMM -----------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          M: Optional[int] = None, N_: Optional[int] = None, K: Optional[int] = None,
@@ -248,6 +341,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     """
     _require_cuda(a, b, out, bias, out2, aux, a2, b2, bs_index, bs_count)
     assert a.dim() == 2 and a.stride(1) == 1 and a.dtype == b.dtype
+    if (a.dtype == torch.float32 and _fp32_tensor_cores and not force_simt and bs_mode == 0 and a2 is None
+            and scatter is None and b.dim() == 2 and b.stride(1) == 1):
+        result = _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilogue, act, out2, aux,
+                                   dropout_p, seed, elem_offset)
+        if result is not NotImplemented:
+            return result
     d = N.GemmDesc()
     if bs_mode == 0:
         assert b.dim() == 2 and b.stride(1) == 1

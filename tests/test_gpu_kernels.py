@@ -156,8 +156,28 @@ def test_gemm_fp32_simt(ops, cuda_device, a_mn, b_mn, M, N, K):
     torch.manual_seed(M + N + K)
     A, B, As, Bs = _gemm_inputs(M, N, K, a_mn, b_mn, torch.float32, cuda_device)
     bias = torch.randn(N)
-    D = ops.gemm(As, Bs, a_mn_major=a_mn, b_mn_major=b_mn, bias=bias.to(cuda_device))
+    D = ops.gemm(As, Bs, a_mn_major=a_mn, b_mn_major=b_mn, bias=bias.to(cuda_device), force_simt=True)
     assert_close(D, _cpu64(A) @ _cpu64(B).t() + bias.double(), FP32_RTOL, FP32_ATOL, "fp32 gemm", scale_atol=True)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(64, 64, 32), (200, 136, 100), (1000, 776, 520), (300, 264, 4100), (256, 512, 16384)])
+def test_gemm_fp32_on_tensor_cores(ops, cuda_device, a_mn, b_mn, M, N, K):
+    """fp32 products as three TF32 products over one reduction axis, sliced so that the accumulators' truncation
+    stays below the fp32-mode tolerance whatever the length of the axis."""
+    from lean_transformer_b200 import ops as raw_ops
+    torch.manual_seed(M + N + K)
+    A, B, As, Bs = _gemm_inputs(M, N, K, a_mn, b_mn, torch.float32, cuda_device)
+    bias = torch.randn(N)
+    before = raw_ops.launch_count
+    D = ops.gemm(As, Bs, a_mn_major=a_mn, b_mn_major=b_mn, bias=bias.to(cuda_device))
+    slices = max(1, -(-K // 1024) - (1 if K % 1024 and K % 1024 < 32 and K > 1024 else 0))
+    assert raw_ops.launch_count - before >= 3 * slices  # two splits + one product per slice: the tensor-core path ran
+    ref = _cpu64(A) @ _cpu64(B).t() + bias.double()
+    assert_close(D, ref, FP32_RTOL, FP32_ATOL, "fp32 gemm on tensor cores", scale_atol=True)
+    # and with a tighter, K-independent bound: 3e-5 of the largest entry
+    assert (D.double().cpu() - ref).abs().max() <= 3e-5 * ref.abs().max()
+    ops.check_device_status(cuda_device)
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
