@@ -10,6 +10,10 @@ One JSON line is printed by rank 0.  Workloads (synthetic data, random-init weig
                      configuration the 1/2/4/8-GPU metric is quoted on and it fits one GPU)
   mixed_bf16_h1024   hidden 1024, intermediate 4096, GeGLU, 16 x 1024 tokens per rank, fp32 parameters and
                      residual stream with bf16 compute, dropout 0.1
+  pixelfly_bf16_h4096  hidden 4096, intermediate 16384, both projections pixelfly block-sparse (128-blocks) plus a
+                     rank-128 low-rank term, bf16, 65536 tokens per rank
+  dense_fp32_h768    hidden 768, intermediate 3072, 8 x 512 tokens, fp32 end to end (the reference's CPU-runnable
+                     case): products run as three TF32 tensor-core products with fp32 accuracy
 """
 import argparse
 import json
@@ -28,6 +32,8 @@ sys.path.insert(0, str(ROOT))
 WORKLOADS = {
     "dense_bf16_h8192": dict(hidden=8192, inter=32768, total_tokens=65536, scaling="strong", dropout=0.0, mixed=False),
     "mixed_bf16_h1024": dict(hidden=1024, inter=4096, tokens_per_rank=16384, scaling="weak", dropout=0.1, mixed=True),
+    "dense_fp32_h768": dict(hidden=768, inter=3072, tokens_per_rank=4096, scaling="weak", dropout=0.0, mixed=False,
+                            fp32=True),
     "pixelfly_bf16_h4096": dict(hidden=4096, inter=16384, tokens_per_rank=65536, scaling="weak", dropout=0.0, mixed=False,
                                 layout="pixelfly(block_size=128)", lowrank=128),
 }
@@ -190,7 +196,7 @@ def build_module(wl, device):
             if wl.get("layout"):
                 proj.matrix.lowrank_first.normal_(0.0, 0.02, generator=gen)
                 proj.matrix.lowrank_second.normal_(0.0, 0.02, generator=gen)
-    if not wl["mixed"]:
+    if not wl["mixed"] and not wl.get("fp32"):
         ffn = ffn.bfloat16()
     return ffn.train()
 
@@ -220,12 +226,12 @@ def run_ours(args, wl, name):
     else:
         tokens = wl["tokens_per_rank"]
         total_tokens = tokens * world
-    in_dtype = torch.float32 if wl["mixed"] else torch.bfloat16
+    in_dtype = torch.float32 if (wl["mixed"] or wl.get("fp32")) else torch.bfloat16
     ffn = build_module(wl, device)
     params = [p for p in ffn.parameters()]
     gen = torch.Generator(device=device).manual_seed(1000 + rank)
     x_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(in_dtype)
-    g_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(torch.bfloat16)
+    g_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(torch.float32 if wl.get("fp32") else torch.bfloat16)
     sync = (ldist.GradSync(wire_dtype=torch.bfloat16, comm_sms=args.comm_sms if args.grad_exchange == "nccl" else None,
                            measure_tail=True, params=params) if world > 1 else None)
     reducer = None
@@ -385,10 +391,11 @@ def run_ours(args, wl, name):
     line = dict(
         metric="LeanFFN fwd+bwd tokens/sec", value=tokens_per_s, unit="tokens/s", n_gpus=world, steps=args.steps,
         warmup=args.warmup, ms_per_step=seconds / args.steps * 1e3, higher_is_better=True, scaling=wl["scaling"],
-        vs_baseline=None, dtype="bf16", data="synthetic",
+        vs_baseline=None, dtype="f32" if wl.get("fp32") else "bf16", data="synthetic",
         config=dict(workload=name, hidden=hidden, intermediate=inter, gated=True, activation="gelu_fused",
                     dropout=wl["dropout"], total_tokens=total_tokens, tokens_per_gpu=tokens,
-                    parameters="fp32 masters + bf16 compute (autocast)" if wl["mixed"] else "bf16",
+                    parameters=("fp32 masters + bf16 compute (autocast)" if wl["mixed"] else
+                                "fp32, products as three TF32 tensor-core products" if wl.get("fp32") else "bf16"),
                     parallelism=f"dp{world} token partition" + (
                         "" if world == 1 else ", weight gradients reduce-scattered inside their GEMMs (NVLink peer atomics) "
                         "+ copy-engine all-gather, NCCL for the small tensors" if reducer is not None
@@ -427,8 +434,8 @@ def quick_measure(wl, device, args):
 
     ffn = build_module(wl, device)
     tokens, hidden = wl.get("tokens_per_rank") or wl["total_tokens"], wl["hidden"]
-    x = torch.randn(tokens, hidden, device=device).to(torch.float32 if wl["mixed"] else torch.bfloat16)
-    g = torch.randn(tokens, hidden, device=device).to(torch.bfloat16)
+    x = torch.randn(tokens, hidden, device=device).to(torch.float32 if (wl["mixed"] or wl.get("fp32")) else torch.bfloat16)
+    g = torch.randn(tokens, hidden, device=device).to(torch.float32 if wl.get("fp32") else torch.bfloat16)
     params = list(ffn.parameters())
 
     from lean_transformer_b200.blocksparse.linear import clear_cast_cache
@@ -456,7 +463,8 @@ def quick_measure(wl, device, args):
     s = a.elapsed_time(b) * 1e-3 / n
     return dict(tokens_per_s=tokens / s, ms_per_step=s * 1e3, tflops=tokens / s * flops_per_token(hidden, wl["inter"], wl) / 1e12,
                 config=dict(hidden=hidden, intermediate=wl["inter"], tokens=tokens, dropout=wl["dropout"],
-                            parameters="fp32 masters + bf16 compute" if wl["mixed"] else "bf16"))
+                            parameters=("fp32 masters + bf16 compute" if wl["mixed"] else
+                                        "fp32 (TF32x3 tensor cores)" if wl.get("fp32") else "bf16")))
 
 
 def main():
