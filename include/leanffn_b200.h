@@ -262,17 +262,19 @@ int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
 /* fp32 accuracy from TF32 tensor-core multiplications ("3xTF32").  A TF32 multiplication reads only the 10 leading
  * mantissa bits of each fp32 operand.  Write x = hi + lo with hi = x truncated to those bits and lo = x - hi; then
  * a.b = a_hi.b_hi + a_hi.b_lo + a_lo.b_hi up to a relative 2^-21, and the three products are ONE product over a
- * reduction axis of three times the length.  This call writes, for x [rows, cols] (leading dimension ldx),
- *   role 0 (the A operand):  out [rows, 3*cols] = ( hi | hi | lo )
- *   role 1 (the B operand):  out [rows, 3*cols] = ( hi | lo | hi )
- * and leanffn_gemm with in_dtype LEANFFN_TF32, K = 3*cols on the two outputs gives the fp32-accurate product
- * (K-major operands, dense, LEANFFN_EPI_STORE with optional bias, fp32 result, M, N >= 64, N a multiple of 8,
- * cols a multiple of 4).  With in_dtype LEANFFN_TF32, `aux` (fp32 [M, N], may be D itself) is added to the
- * result: tensor-core accumulators truncate, so the error grows with the length of the reduction axis, and a long
- * axis is covered by several calls over slices of it that keep a running sum.
+ * reduction axis of three times the length.  Tensor-core accumulators truncate, so the error of such a product grows
+ * with the length of its reduction axis; a long axis is therefore cut into slices that are multiplied by separate
+ * calls keeping a running sum.  This call prepares all slices at once.  For x [rows, cols] (leading dimension ldx)
+ * and a slice width s, the columns are cut into max(1, cols / s) slices (the last one takes the remainder), and
+ * slice j, covering columns [f, f + w), lands in out [rows, 3*cols] at columns [3f, 3f + 3w) as
+ *   role 0 (the A operand):  ( hi | hi | lo )        role 1 (the B operand):  ( hi | lo | hi ),   each part w wide.
+ * leanffn_gemm with in_dtype LEANFFN_TF32, A = outA + 3f, B = outB + 3f, lda = ldb = 3*cols and K = 3w then
+ * gives the fp32-accurate product over that slice (K-major operands, dense, LEANFFN_EPI_STORE with optional bias,
+ * fp32 result, M, N >= 64, N a multiple of 8, f and w multiples of 4).  With in_dtype LEANFFN_TF32, `aux`
+ * (fp32 [M, N], may be D itself) is added to the result: that is the running sum over slices.
  * Stands in for the fp32 cuBLAS products of the reference's fp32 (non-autocast) mode. */
 int32_t leanffn_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int32_t role,
-                           void* stream);
+                           int64_t slice, void* stream);
 
 /* Strided device-to-device copy of `height` pieces of `width_bytes` (cudaMemcpy2DAsync; between two GPUs with peer
  * access it runs on a copy engine and occupies no SM).  Used to hand the reduced row blocks of a scattered weight

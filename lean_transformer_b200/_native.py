@@ -63,7 +63,7 @@ _SIGNATURES = {
     "leanffn_cast": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_void_p]),
     "leanffn_transpose": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "leanffn_copy_2d": (c_int32, [c_void_p, c_uint64, c_void_p, c_uint64, c_uint64, c_uint64, c_void_p]),
-    "leanffn_split_tf32": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_void_p]),
+    "leanffn_split_tf32": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
 }
 

@@ -334,10 +334,10 @@ extern "C" int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const vo
 }
 
 extern "C" int32_t leanffn_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int32_t role,
-                                      void* stream) {
-  if (rows < 0 || cols <= 0 || (role != 0 && role != 1)) return LEANFFN_ERR_SHAPE;
+                                      int64_t slice, void* stream) {
+  if (rows < 0 || cols <= 0 || (role != 0 && role != 1) || slice <= 0) return LEANFFN_ERR_SHAPE;
   if (rows == 0) return LEANFFN_OK;
   if (x == nullptr || out == nullptr) return LEANFFN_ERR_NULL;
-  const cudaError_t e = launch_split_tf32(x, ldx, out, rows, cols, role, static_cast<cudaStream_t>(stream));
+  const cudaError_t e = launch_split_tf32(x, ldx, out, rows, cols, role, slice, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }

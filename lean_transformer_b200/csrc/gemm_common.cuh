@@ -98,8 +98,10 @@ int sm_count();
 cudaError_t gemm_simt(const SimtOperands& o, const EpiParams& ep, int32_t in_dtype, cudaStream_t st);
 int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
                      const TcOperand* B2, TcParams p, int block_n, cudaStream_t st, cudaError_t* cuda_err, bool tf32 = false);
-// x [rows, cols] -> out [rows, 3*cols] = (hi | hi | lo) for role 0, (hi | lo | hi) for role 1 (see the header).
-cudaError_t launch_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int role, cudaStream_t st);
+// x [rows, cols] -> out [rows, 3*cols]: per slice of the columns (hi | hi | lo) for role 0, (hi | lo | hi) for role 1
+// (see the header).
+cudaError_t launch_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int role, int64_t slice,
+                              cudaStream_t st);
 // CTA-pair (cta_group::2) kernel for dense products; tile counts in p are in 256 x 256 tiles.
 int32_t gemm_tcgen05_pair(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
                           const TcOperand* B2, TcParams p, cudaStream_t st);

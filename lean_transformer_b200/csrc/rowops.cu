@@ -711,27 +711,33 @@ static int32_t ln_bwd_dispatch(const void* dy, const void* x, const void* gamma,
 // ---- split of fp32 values into two TF32-exact parts -------------------------------------------------
 // hi = x with the 13 low mantissa bits cleared (what a TF32 multiplication reads), lo = x - hi (exact in fp32).
 __global__ void split_tf32_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ out, int64_t rows,
-                                  int64_t cols, int role) {
+                                  int64_t cols, int role, int64_t slice) {
   const int64_t total = rows * cols;
+  const int64_t slices = cols / slice > 0 ? cols / slice : 1;  // the last slice takes the remainder
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t r = i / cols, c = i - r * cols;
+    int64_t s = c / slice;
+    if (s >= slices) s = slices - 1;
+    const int64_t first = s * slice;
+    const int64_t width = s == slices - 1 ? cols - first : slice;
     const float v = x[r * ldx + c];
     const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
     const float lo = v - hi;
-    float* o = out + r * 3 * cols + c;
+    float* o = out + r * 3 * cols + 3 * first + (c - first);
     o[0] = hi;
-    o[cols] = role == 0 ? hi : lo;
-    o[2 * cols] = role == 0 ? lo : hi;
+    o[width] = role == 0 ? hi : lo;
+    o[2 * width] = role == 0 ? lo : hi;
   }
 }
 
 cudaError_t launch_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int role,
-                              cudaStream_t st) {
+                              int64_t slice, cudaStream_t st) {
   const int64_t total = rows * cols;
   const int64_t want = (total + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
-  split_tf32_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(x, ldx, out, rows, cols, role);
+  split_tf32_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(x, ldx, out, rows, cols, role,
+                                                                                slice);
   return cudaGetLastError();
 }
 

@@ -245,10 +245,11 @@ def set_fp32_tensor_cores(enabled: bool) -> bool:
     return previous
 
 
-def _split_tf32(x: torch.Tensor, role: int) -> torch.Tensor:
+def _split_tf32(x: torch.Tensor, role: int, slice_width: int) -> torch.Tensor:
     rows, cols = x.shape
     out = torch.empty((rows, 3 * cols), dtype=torch.float32, device=x.device)
-    N.check(N.lib.leanffn_split_tf32(_ptr(x), x.stride(0), _ptr(out), rows, cols, role, _stream(x)), "leanffn_split_tf32")
+    N.check(N.lib.leanffn_split_tf32(_ptr(x), x.stride(0), _ptr(out), rows, cols, role, slice_width, _stream(x)),
+            "leanffn_split_tf32")
     _count()
     return out
 
@@ -274,21 +275,20 @@ def _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilog
     plain = out if (out is not None and not backward_kind) else torch.empty((m, n), dtype=torch.float32, device=a.device)
     # the accumulators truncate: keep every call's reduction axis short and carry a running sum between calls
     flops_timer = _gemm_timer
-    for first in range(0, k, _TF32_SLICE):
-        width = min(_TF32_SLICE, k - first)
-        if width < 32:  # a tail too short for a launch of its own: fold it into the previous slice's range
-            break
-        if k - (first + width) < 32:
-            width = k - first
-        a3 = _split_tf32(a_k[:, first:first + width], 0)
-        b3 = _split_tf32(b_k[:, first:first + width], 1)
+    a3 = _split_tf32(a_k, 0, _TF32_SLICE)
+    b3 = _split_tf32(b_k, 1, _TF32_SLICE)
+    slices = max(1, k // _TF32_SLICE)  # the last slice takes the remainder (same rule as the split kernel)
+    for index in range(slices):
+        first = index * _TF32_SLICE
+        width = k - first if index == slices - 1 else _TF32_SLICE
         d = N.GemmDesc()
         d.M, d.N, d.K = int(m), int(n), int(3 * width)
         d.in_dtype = N.TF32
-        d.A, d.lda, d.B, d.ldb = _ptr(a3), 3 * width, _ptr(b3), 3 * width
+        d.A, d.lda = a3.data_ptr() + 12 * first, 3 * k
+        d.B, d.ldb = b3.data_ptr() + 12 * first, 3 * k
         d.epilogue = N.EPI_STORE
         d.D, d.ldd, d.d_dtype = _ptr(plain), n, N.F32
-        if first == 0:
+        if index == 0:
             if bias is not None and not backward_kind:
                 d.bias, d.bias_dtype = _ptr(bias), N.F32
         else:
@@ -304,8 +304,6 @@ def _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilog
             flops_timer.records.append((start, end, 2.0 * m * n * width))
         else:
             N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
-        if width == k - first:
-            break
     if epilogue == N.EPI_STORE:
         return plain
     if epilogue == N.EPI_DROPOUT_RESIDUAL:
