@@ -37,6 +37,10 @@ class GradSync:
     concatenation of a shared low-rank factor and an adapter) are left to autograd, unreduced, and their names are
     collected in ``unclaimed``; reduce those after the backward (``all_reduce_module_gradients``).
 
+    ``bucket_elems``: taken gradients with at most this many elements (biases, LayerNorm parameters) are not reduced
+    one by one: ``finish()`` sums them all in ONE fp32 all-reduce of their concatenation, which costs one collective
+    latency instead of one per tensor.
+
     ``comm_sms``: the tensor-core GEMMs are persistent kernels holding one CTA on every SM until they end, so a
     collective started meanwhile would find no SM to run on.  With ``comm_sms`` set, the GEMM grid is capped at
     ``SMs - comm_sms`` CTAs from the first started reduction until ``finish()``; GEMMs that run while nothing is in
@@ -47,7 +51,8 @@ class GradSync:
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, wire_dtype: Optional[torch.dtype] = None,
-                 average: bool = False, comm_sms: Optional[int] = None, measure_tail: bool = False, params=None):
+                 average: bool = False, comm_sms: Optional[int] = None, measure_tail: bool = False, params=None,
+                 bucket_elems: int = 1 << 18):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.group = group
@@ -57,6 +62,8 @@ class GradSync:
         self.comm_sms = comm_sms
         self.measure_tail = measure_tail
         self._owners = {p.data_ptr(): p for p in params} if params is not None else {}
+        self.bucket_elems = int(bucket_elems)
+        self._small: List[tuple] = []
         self.unclaimed: List[str] = []
         self._tail_events: List[tuple] = []
         self._pending: List[tuple] = []
@@ -82,6 +89,9 @@ class GradSync:
         if self.world_size == 1:
             self.reduced_names.append(name)
             return False
+        if owner is not None and grad.numel() <= self.bucket_elems:
+            self._small.append((name, grad, owner))
+            return True
         wire = grad
         if self.wire_dtype is not None and grad.dtype != self.wire_dtype:
             wire = grad.to(self.wire_dtype)
@@ -97,7 +107,11 @@ class GradSync:
 
     def finish(self) -> int:
         done = 0
-        timed = self.measure_tail and self._pending and self._pending[0][1].is_cuda
+        if self._small:
+            flat = torch.cat([g.reshape(-1).to(torch.float32) for _, g, _ in self._small])
+            small_work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        timed = bool(self.measure_tail and ((self._pending and self._pending[0][1].is_cuda) or
+                                            (self._small and self._small[0][1].is_cuda)))
         if timed:
             before, after = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             before.record()
@@ -118,6 +132,22 @@ class GradSync:
                     owner.grad.add_(result)
             self.reduced_names.append(name)
             done += 1
+        if self._small:
+            small_work.wait()
+            if self.average:
+                flat.div_(self.world_size)
+            offset = 0
+            for name, grad, owner in self._small:
+                piece = flat[offset:offset + grad.numel()].view(grad.shape)
+                piece = piece.clone() if owner.dtype == torch.float32 else piece.to(owner.dtype)  # own storage
+                offset += grad.numel()
+                if owner.grad is None:
+                    owner.grad = piece
+                else:
+                    owner.grad.add_(piece)
+                self.reduced_names.append(name)
+                done += 1
+            self._small.clear()
         if timed:
             after.record()
             self._tail_events.append((before, after))

@@ -82,7 +82,7 @@ def test_shard_tokens_covers_everything():
         ldist.shard_tokens(8, 2, 2)
 
 
-def _owner_worker(rank, world, port, result_dir):
+def _owner_worker(rank, world, port, result_dir, bucket_elems):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=__import__("datetime").timedelta(seconds=20))
     try:
@@ -90,7 +90,7 @@ def _owner_worker(rank, world, port, result_dir):
         weight = torch.nn.Parameter(torch.zeros(6, 4))
         bias = torch.nn.Parameter(torch.zeros(6, dtype=torch.float64))  # gradient arrives in another dtype
         stranger = torch.zeros(3, 4)                                    # not among the registered parameters
-        sync = ldist.GradSync(params=[weight, bias], wire_dtype=torch.float32)
+        sync = ldist.GradSync(params=[weight, bias], wire_dtype=torch.float32, bucket_elems=bucket_elems)
         g_w = torch.full((6, 4), float(rank + 1))
         g_b = torch.full((6,), float(10 * (rank + 1)))
         g_s = torch.ones(3, 4)
@@ -113,10 +113,11 @@ def _owner_worker(rank, world, port, result_dir):
         dist.destroy_process_group()
 
 
-def test_grad_sync_takes_ownership_of_hooked_gradients(tmp_path):
+@pytest.mark.parametrize("bucket_elems", [0, 1 << 18])  # one all-reduce per tensor / one for all small tensors
+def test_grad_sync_takes_ownership_of_hooked_gradients(tmp_path, bucket_elems):
     """GradSync as the gradient-ready callback: it keeps the gradient, reduces it and delivers ``param.grad`` in
     ``finish()`` (autograd never touches a tensor that a collective is still writing)."""
-    mp.spawn(_owner_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_owner_worker, args=(2, _free_port(), str(tmp_path), bucket_elems), nprocs=2, join=True)
     assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
 
 
