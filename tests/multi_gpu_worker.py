@@ -16,16 +16,23 @@ from lean_transformer_b200 import LeanFFN, dist as ldist, ffn as lffn, ops  # no
 from lean_transformer_b200.blocksparse.linear import set_weight_grad_reducer  # noqa: E402
 
 
-def main():
-    rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=device)
+def scenario(device, rank, world, mixed):
+    """``mixed``: fp32 parameters and residual stream with bf16 compute (fp32 gradients, fp32 atomics in the fused
+    exchange); otherwise bf16 everywhere."""
     hidden, inter, tokens = 512, 1024, 1024 * world
     torch.manual_seed(0)
-    ffn = LeanFFN(hidden, inter, gated=True).to(device).to(torch.bfloat16)  # same seed: same weights on every rank
+    ffn = LeanFFN(hidden, inter, gated=True).to(device)  # same seed: same weights on every rank
+    if not mixed:
+        ffn = ffn.to(torch.bfloat16)
+    _forward = ffn.forward
+
+    def forward(x):
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=mixed):
+            return _forward(x)
+
+    in_dtype = torch.float32 if mixed else torch.bfloat16
     gen = torch.Generator(device=device).manual_seed(1)
-    x_all = torch.randn(tokens, hidden, device=device, generator=gen).bfloat16()
+    x_all = torch.randn(tokens, hidden, device=device, generator=gen).to(in_dtype)
     g_all = torch.randn(tokens, hidden, device=device, generator=gen).bfloat16()
     start, count = ldist.shard_tokens(tokens, world, rank)
     x, g = x_all[start:start + count], g_all[start:start + count]
@@ -41,14 +48,14 @@ def main():
 
     # whole batch on this GPU
     clear()
-    ffn(x_all.clone().requires_grad_(True)).backward(g_all)
+    forward(x_all.clone().requires_grad_(True)).backward(g_all)
     full = grads()
 
     # NCCL exchange
     clear()
     sync = ldist.GradSync(params=list(ffn.parameters()))
     lffn.set_grad_ready_hook(sync.reduce)
-    ffn(x.clone().requires_grad_(True)).backward(g)
+    forward(x.clone().requires_grad_(True)).backward(g)
     sync.finish()
     nccl = grads()
     lffn.set_grad_ready_hook(None)
@@ -62,7 +69,7 @@ def main():
     for _ in range(2):
         clear()
         reducer.begin_step()
-        ffn(x.clone().requires_grad_(True)).backward(g)
+        forward(x.clone().requires_grad_(True)).backward(g)
         sync.finish()
         assert reducer.finish() == 2
         fused = grads()
@@ -82,6 +89,18 @@ def main():
                          nccl_vs_full=(nccl[k] - full[k]).abs().max().item() / scale,
                          fused_vs_full=(fused[k] - full[k]).abs().max().item() / scale,
                          fused_vs_nccl=(fused[k] - nccl[k]).abs().max().item() / scale)
+    return report
+
+
+def main():
+    rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    report = {}
+    for mixed in (False, True):
+        for key, value in scenario(device, rank, world, mixed).items():
+            report[("mixed." if mixed else "bf16.") + key] = value
     gathered = [None] * world
     dist.all_gather_object(gathered, report)
     if rank == 0:
