@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     obj_dir = CSRC / "build"
     obj_dir.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
-    extra += os.environ.get("LEANFFN_NVCC_EXTRA", "").split()  # e.g. probe builds
+    extra += os.environ.get("LEANFFN_NVCC_EXTRA", "").split()  # extra compiler flags, e.g. -DNDEBUG or -Xptxas -v
 
     def compile_one(src: str) -> Path:
         obj = obj_dir / (src[:-3] + ".o")
