@@ -52,9 +52,9 @@ def flops_per_token(hidden, inter, wl=None):
 
 
 # DRAM bytes (read + written) per GEMM launch and per token of the GPU's shard, from one `ncu --set full` capture of the
-# six GEMMs of a step at 8192 tokens (profiles/gemm_tcgen05_dense_bf16_h8192_tokens8192.md): 38.83 GB over 6 launches.
+# six GEMMs of a step at 8192 tokens (profiles/gemm_tcgen05_dense_bf16_h8192_tokens8192.md): 42.07 GB over 6 launches.
 # Operand re-reads and activation traffic both grow with the token count, so the figure is scaled by tokens.
-GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH = {"dense_bf16_h8192": 38.83e9 / 6 / 8192}
+GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH = {"dense_bf16_h8192": 42.07e9 / 6 / 8192}
 
 
 def load_peaks():
