@@ -42,3 +42,33 @@ def test_mismatched_layout_is_rejected():
     other[o, i] = True
     with pytest.raises(ValueError):
         C.native_to_triton_permutation(bwd, other)
+
+
+def test_round_trips_on_random_balanced_layouts():
+    """Circulant layouts with a random set of offsets are balanced (same number of blocks per row and per column), the
+    case the native order supports; the converters must round-trip on all of them."""
+    from hypothesis import given, settings, strategies as st
+
+    from lean_transformer_b200.blocksparse import convert as C, layout as LY
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.integers(2, 12), st.integers(1, 3), st.sets(st.integers(0, 11), min_size=1, max_size=5), st.integers(0, 2**31))
+    def check(n, reps, offsets, seed):
+        offsets = sorted({o % n for o in offsets})
+        base = torch.zeros(n, n, dtype=torch.bool)
+        rows = torch.arange(n)
+        for o in offsets:
+            base[rows, (rows + o) % n] = True
+        layout = base.repeat(reps, 1)  # [reps*n out blocks, n in blocks]: still balanced
+        fwd, bwd = LY.get_indices_from_layout(layout)
+        bs = 4
+        gen = torch.Generator().manual_seed(seed)
+        native = torch.randn(n * bs, bwd.shape[1], bs, generator=gen, dtype=torch.float64)
+        dense = C.native_weight_to_dense(native, bwd, layout.shape[0] * bs)
+        triton = C.native_to_triton_weight(native, bwd, layout)
+        assert torch.equal(C.triton_weight_to_dense(triton, layout), dense)
+        assert torch.equal(C.triton_to_native_weight(triton, bwd, layout), native)
+        x = torch.randn(3, n * bs, generator=gen, dtype=torch.float64)
+        assert torch.allclose(O.blocksparse_matmul(x, native, fwd), x @ dense.t(), rtol=1e-12, atol=1e-12)
+
+    check()
