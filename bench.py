@@ -420,7 +420,7 @@ def run_ours(args, wl, name):
         gpu_launches=launches, clocks=clocks)
     if world > 1:
         line["comm"] = dict(exposed_allreduce_ms_per_step=exposed_ms,
-                            sms_left_free_during_exchange=4 if reducer is not None else args.comm_sms,
+                            sms_left_free_during_exchange=2 if reducer is not None else args.comm_sms,
                             grad_exchange=exchange_note,
                             note="time the compute stream of rank 0 waited for gradient all-reduces after its last kernel")
     if extra:

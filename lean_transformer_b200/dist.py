@@ -205,7 +205,7 @@ class ScatteredGradReducer:
     BLOCK_SHIFT = 8  # 256 rows: the tile height of the weight-gradient GEMM
 
     def __init__(self, weights: Dict[str, torch.Tensor], group: Optional[dist.ProcessGroup] = None,
-                 spare_sms: int = 4):
+                 spare_sms: int = 2):
         import torch.distributed._symmetric_memory as symm
 
         if not dist.is_initialized():
