@@ -1,8 +1,10 @@
-// bf16 GEMM on the Blackwell tensor cores: TMA tiled loads (each CTA fetches its own tiles) stage 128-byte
-// swizzled operand tiles in shared memory, one elected thread issues tcgen05.mma with the fp32
-// accumulator in tensor memory (TMEM), and four epilogue warps read the accumulator back with
-// tcgen05.ld and apply the fused epilogue (bias / gated activation forward and backward / dropout /
-// residual) while the next tile's MMAs already run into the other TMEM accumulator stage.
+// GEMM on the Blackwell tensor cores (bf16 operands; fp32 operands multiplied as TF32): TMA tiled loads (each CTA
+// fetches its own tiles) stage 128-byte swizzled operand tiles in shared memory, one elected thread issues
+// tcgen05.mma with the fp32 accumulator in tensor memory (TMEM), and eight epilogue warps read the accumulator
+// back with tcgen05.ld and apply the fused epilogue (bias / gated activation forward and backward / dropout /
+// residual / reduce-scatter into peer replicas).  With 128-row tiles the next tile's MMAs already run into the
+// other TMEM accumulator stage meanwhile; 256 x 256 tiles fill the whole TMEM and expose the epilogue, but move a
+// third less operand data per flop.
 //
 // One persistent CTA per SM walks a static, M-grouped tile order.  Warp roles:
 //   warp 0       TMA producer (one elected lane)

@@ -17,8 +17,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include <cstdio>
-
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 #include "tc_epilogue.cuh"
