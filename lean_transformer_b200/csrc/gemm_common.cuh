@@ -82,7 +82,7 @@ struct TcParams {
   int32_t glu_split;  // > 0: B rows [n, n+128) and [glu_split + n, ...) form one 256-wide tile
   int32_t max_ctas;   // > 0: cap on the persistent grid
   int32_t group_m;    // M-tiles that share one sweep over N in the tile order (0 = kernel default)
-  int32_t m_subtiles; // one-CTA kernel: 1 = 128-row tiles (two accumulator stages), 2 = 256 x 256 tiles
+  int32_t m_subtiles; // one-CTA kernel: 128-row sub-tiles per CTA tile (1: 128 x N tiles; 2: 256 x 256 or 256 x 128)
   int32_t* status;
   EpiParams ep;
 };
