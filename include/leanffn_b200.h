@@ -76,7 +76,8 @@ const char* leanffn_status_string(int32_t status);
  * y = dropout(y) (Philox mask, see leanffn_dropout) and y += residual.
  * Replaces F.layer_norm at lean_transformer/ffn.py:184, :200 and :283, torch.dropout_ at :204
  * and torch.add at :207 (post-LN configuration). x, residual: x_dtype; gamma, beta: param_dtype
- * (may be NULL = ones / zeros); y: y_dtype. */
+ * (may be NULL = ones / zeros); y: y_dtype.  Pointers that are not 16-byte aligned (or cols % 4 != 0) take a
+ * slower scalar kernel. */
 int32_t leanffn_layer_norm_forward(const void* x, int32_t x_dtype, const void* gamma, const void* beta,
                                    int32_t param_dtype, void* y, int32_t y_dtype, int64_t rows, int64_t cols,
                                    float eps, float dropout_p, uint64_t seed, uint64_t elem_offset,
@@ -90,7 +91,8 @@ size_t leanffn_layer_norm_backward_scratch_bytes(int64_t rows, int64_t cols);
  *   dgamma = sum_rows(dy * xn), dbeta = sum_rows(dy).
  * Replaces torch.autograd.grad over the rematerialised F.layer_norm at
  * lean_transformer/ffn.py:247-259 and :280-293, and the residual add at :297-300.
- * dgamma/dbeta are fp32 [cols] (may be NULL together); dx may be NULL. */
+ * dgamma/dbeta are fp32 [cols] (may be NULL together); dx may be NULL.  With cols % 4 == 0 and cols <= 16384 every
+ * pointer must be 16-byte aligned (LEANFFN_ERR_ALIGN otherwise). */
 int32_t leanffn_layer_norm_backward(const void* dy, int32_t dy_dtype, const void* x, int32_t x_dtype,
                                     const void* gamma, int32_t param_dtype, const void* dresidual,
                                     int32_t dresidual_dtype, void* dx, int32_t dx_dtype, float* dgamma,
@@ -99,7 +101,8 @@ int32_t leanffn_layer_norm_backward(const void* dy, int32_t dy_dtype, const void
 
 /* hid = act(pre) (gated == 0, pre [rows, inter]) or act(pre[:, :inter]) * pre[:, inter:]
  * (gated != 0, pre [rows, 2*inter]).  Replaces _LeanFFN._apply_activation,
- * lean_transformer/ffn.py:138-144 (the first half of the last dim is the gate). */
+ * lean_transformer/ffn.py:138-144 (the first half of the last dim is the gate).  inter % 4 == 0 and 16-byte
+ * aligned pointers are required (LEANFFN_ERR_SHAPE / LEANFFN_ERR_ALIGN); the same holds for the backward. */
 int32_t leanffn_activation_forward(const void* pre, void* hid, int32_t dtype, int64_t rows, int64_t inter,
                                    int32_t gated, int32_t act, void* stream);
 
@@ -127,7 +130,8 @@ int32_t leanffn_dropout_mask(uint8_t* mask, int64_t n, float p, uint64_t seed, u
                              void* stream);
 
 size_t leanffn_column_sum_scratch_bytes(int64_t rows, int64_t cols);
-/* out[c] = sum_r x[r, c] in fp32, deterministic two-stage reduction.
+/* out[c] = sum_r x[r, c] in fp32, deterministic two-stage reduction.  x may be any view with ld >= cols; rows
+ * are read with 4-element vector loads when the base address and ld allow it, element by element otherwise.
  * Replaces grad_output_flat.sum(dim=0) at lean_transformer/blocksparse/linear.py:293-294. */
 int32_t leanffn_column_sum(const void* x, int32_t x_dtype, int64_t ld, float* out, void* scratch,
                            int64_t rows, int64_t cols, void* stream);
@@ -182,6 +186,8 @@ int32_t leanffn_transpose(const void* x, int32_t dtype, int64_t ldx, void* y, in
  * Triton tensor [1, nnz, block, block] (f = rank of the block in layout.nonzero()).  Which blocks meet
  * is given by bs_index, a table of int32 PAIRS with bs_nnz pairs per row, and bs_count (int32 per
  * table row: how many leading pairs are valid; NULL = bs_nnz everywhere):
+ * Table entries are TRUSTED: the kernels use them as block addresses without range checks, so the caller
+ * validates tables that come from outside (lean_transformer_b200 does so when it first builds them).
  *   bs_mode 0: dense.
  *   bs_mode 1: forward.  A = x [M, K=in_features], N = out_features.  Table row = output block,
  *              pair = (weight block f, input block j):  D[:, i] = sum_t x[:, j_t] . W_f_t^T.
@@ -255,9 +261,19 @@ typedef struct leanffn_gemm_desc {
    * (equal second entries of their table rows; bs_num_blocks even), as in the reference's native order with an
    * even number of blocks per input block.  One CTA then computes both blocks from one tile of x. */
   int32_t bs_wgrad_pairs;
+  /* SM clocks a warp role of the tensor-core kernel waits on a stalled peer role before it gives up and records a
+   * LEANFFN_DEV_TIMEOUT_* code in status_word (0 = the default, about 2e9 clocks = one second). */
+  int64_t wait_limit_cycles;
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
+
+/* Self-test of the bounded device-side wait: launches one warp whose thread 0 waits, for at most limit_cycles SM
+ * clocks (clamped to [1000, 10000000]), on an mbarrier that nothing ever arrives at.  The wait gives up, the kernel
+ * records LEANFFN_DEV_TIMEOUT_EPILOGUE in *status_word with the same code path the GEMM roles use, and returns;
+ * nothing hangs or traps and the context stays usable.  Lets a host-side test exercise "a wait ran out -> status
+ * word -> error on the host" without stalling a real kernel.  No counterpart in the reference. */
+int32_t leanffn_selftest_wait_timeout(int32_t* status_word, int64_t limit_cycles, void* stream);
 
 /* fp32 accuracy from TF32 tensor-core multiplications ("3xTF32").  A TF32 multiplication reads only the 10 leading
  * mantissa bits of each fp32 operand.  Write x = hi + lo with hi = x truncated to those bits and lo = x - hi; then

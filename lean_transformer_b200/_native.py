@@ -36,7 +36,7 @@ class GemmDesc(ctypes.Structure):
         ("dropout_p", c_float), ("seed", c_uint64), ("elem_offset", c_uint64),
         ("status_word", c_void_p), ("force_simt", c_int32), ("max_ctas", c_int32),
         ("scatter_world", c_int32), ("scatter_block_shift", c_int32), ("scatter_D", c_void_p * 8),
-        ("bs_wgrad_pairs", c_int32),
+        ("bs_wgrad_pairs", c_int32), ("wait_limit_cycles", c_int64),
     ]
 
 
@@ -65,6 +65,7 @@ _SIGNATURES = {
     "leanffn_copy_2d": (c_int32, [c_void_p, c_uint64, c_void_p, c_uint64, c_uint64, c_uint64, c_void_p]),
     "leanffn_split_tf32": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
+    "leanffn_selftest_wait_timeout": (c_int32, [c_void_p, c_int64, c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
@@ -91,7 +92,7 @@ def _load():
             raise NativeLibraryError(f"{LIB_PATH} does not export {name}") from e
         fn.restype = restype
         fn.argtypes = argtypes
-    if lib.leanffn_abi_version() != 1:
+    if lib.leanffn_abi_version() != 2:
         raise NativeLibraryError("libleanffn_b200.so has an unexpected ABI version; rebuild it")
     return lib
 

@@ -133,7 +133,9 @@ def set_weight_grad_reducer(reducer):
 def dense_weight_grad(dy2d, x2d, weight):
     """dW = dyT . x for a dense weight (linear.py:304-305 of the reference), through the installed reducer if any."""
     reducer = _weight_grad_reducer
-    target = reducer.target(weight) if reducer is not None else None
+    # the scattering epilogue exists in the bf16 tensor-core kernel only: fp32 products keep the plain gradient,
+    # which the caller's gradient hook (dist.GradSync) then reduces like any other
+    target = reducer.target(weight) if (reducer is not None and dy2d.dtype == torch.bfloat16) else None
     if target is None:
         return ops.gemm(dy2d, x2d, a_mn_major=True, b_mn_major=True, out_dtype=weight.dtype)
     out, scatter = target

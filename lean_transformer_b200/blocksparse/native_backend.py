@@ -28,6 +28,40 @@ def backward_indices_from_forward(forward_indices: torch.Tensor, blocks_per_inpu
     return backward.view(-1, blocks_per_input)
 
 
+def _validate_indices(forward_indices: Optional[torch.Tensor], backward_indices: Optional[torch.Tensor],
+                      blocks_per_input: int):
+    """Index buffers come from a state dict or straight from the caller, and the kernels use their entries as
+    addresses without looking at them again: check them once, on the host, when their tables are first built."""
+    if forward_indices is not None:
+        if forward_indices.dim() != 2 or forward_indices.numel() == 0 or forward_indices.numel() % blocks_per_input:
+            raise ValueError(f"forward_indices of shape {tuple(forward_indices.shape)} do not describe weight blocks "
+                             f"with {blocks_per_input} blocks per input block")
+        flat = forward_indices.to(torch.int64).flatten()
+        if not bool(torch.equal(torch.sort(flat).values, torch.arange(flat.numel(), device=flat.device))):
+            raise ValueError("forward_indices must list every weight block id 0 .. in_blocks * blocks_per_input - 1 "
+                             "exactly once")
+    if backward_indices is not None:
+        if backward_indices.dim() != 2 or backward_indices.shape[1] != blocks_per_input:
+            raise ValueError(f"backward_indices of shape {tuple(backward_indices.shape)} do not match a weight with "
+                             f"{blocks_per_input} blocks per input block")
+        low, high = int(backward_indices.min().item()), int(backward_indices.max().item())
+        out_blocks = forward_indices.shape[0] if forward_indices is not None else high + 1
+        if low < 0 or high >= out_blocks:
+            raise ValueError(f"backward_indices entries must lie in [0, {out_blocks}); found [{low}, {high}]")
+        if forward_indices is None:
+            counts = torch.bincount(backward_indices.flatten().to(torch.int64), minlength=out_blocks)
+            if not bool((counts == counts[0]).all()):
+                raise ValueError("backward_indices describe an unbalanced layout (output blocks with different numbers "
+                                 "of weight blocks); the native order needs a balanced one")
+        elif forward_indices.shape[0] * forward_indices.shape[1] != backward_indices.numel():
+            raise ValueError("forward_indices and backward_indices describe different numbers of weight blocks")
+        else:
+            owner = backward_indices.to(torch.int64).flatten()[forward_indices.to(torch.int64).flatten()]
+            expect = torch.arange(forward_indices.shape[0], device=owner.device).repeat_interleave(forward_indices.shape[1])
+            if not bool(torch.equal(owner, expect)):
+                raise ValueError("forward_indices and backward_indices contradict each other")
+
+
 def native_tables(forward_indices: Optional[torch.Tensor], backward_indices: Optional[torch.Tensor],
                   blocks_per_input: int):
     """(forward, dgrad, wgrad) pair tables on the indices' device.  Cached per index-tensor OBJECT (module
@@ -41,6 +75,7 @@ def native_tables(forward_indices: Optional[torch.Tensor], backward_indices: Opt
     hit = _TABLE_CACHE.get(key)
     if hit is not None and hit[0]() is anchor and (other is None or hit[1]() is other) and hit[2] == stamp:
         return hit[3]
+    _validate_indices(forward_indices, backward_indices, blocks_per_input)
     if backward_indices is None:
         backward_indices = backward_indices_from_forward(forward_indices, blocks_per_input)
     if forward_indices is None:

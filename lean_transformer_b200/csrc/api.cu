@@ -20,7 +20,7 @@ static inline bool pitch16(int64_t ld, int32_t dtype) { return (ld * static_cast
 
 using namespace leanffn;
 
-extern "C" int32_t leanffn_abi_version(void) { return 1; }
+extern "C" int32_t leanffn_abi_version(void) { return 2; }
 
 extern "C" const char* leanffn_status_string(int32_t s) {
   switch (s) {
@@ -48,6 +48,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   if (d->act < 0 || d->act >= LEANFFN_ACT_COUNT) return LEANFFN_ERR_UNSUPPORTED;
   if (d->bs_mode < 0 || d->bs_mode > 3) return LEANFFN_ERR_UNSUPPORTED;
   if (!(d->dropout_p >= 0.f && d->dropout_p < 1.f)) return LEANFFN_ERR_UNSUPPORTED;
+  if (d->wait_limit_cycles < 0) return LEANFFN_ERR_UNSUPPORTED;
   if (d->K2 > 0 && (d->A2 == nullptr || d->B2 == nullptr)) return LEANFFN_ERR_NULL;
   const int epi = d->epilogue;
   const bool needs_d2 = epi == LEANFFN_EPI_GLU_FWD || epi == LEANFFN_EPI_ACT_FWD;
@@ -121,6 +122,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     TcParams p{};
     p.ep = ep;
     p.status = d->status_word;
+    p.wait_limit = d->wait_limit_cycles;
     p.max_ctas = d->max_ctas;
     p.m_subtiles = 1;
     const int block_n = d->N <= 128 ? 128 : 256;
@@ -160,6 +162,7 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     TcParams p{};
     p.ep = ep;
     p.status = d->status_word;
+    p.wait_limit = d->wait_limit_cycles;
     p.bs_mode = d->bs_mode;
     p.bs_block = d->bs_mode ? d->bs_block : 0;
     p.bs_nnz = d->bs_nnz;
@@ -321,6 +324,13 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
     return launch_act_bwd(plain.D, ldpre, d->aux, d->D, d->D2, d->d_dtype, d->M, inter, gated ? 1 : 0, d->act, st);
   }
+}
+
+extern "C" int32_t leanffn_selftest_wait_timeout(int32_t* status_word, int64_t limit_cycles, void* stream) {
+  if (status_word == nullptr) return LEANFFN_ERR_NULL;
+  long long limit = limit_cycles < 1000 ? 1000 : (limit_cycles > 10000000 ? 10000000 : limit_cycles);
+  const cudaError_t e = launch_wait_timeout_probe(status_word, limit, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }
 
 extern "C" int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const void* src, uint64_t src_pitch_bytes,

@@ -84,6 +84,7 @@ struct TcParams {
   int32_t group_m;    // M-tiles that share one sweep over N in the tile order (0 = kernel default)
   int32_t m_subtiles; // one-CTA kernel: 128-row sub-tiles per CTA tile (1: 128 x N tiles; 2: 256 x 256 or 256 x 128)
   int32_t* status;
+  long long wait_limit;  // SM clocks a role waits on an mbarrier before it gives up (0 = the default, about a second)
   EpiParams ep;
 };
 
@@ -102,6 +103,7 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
 // (see the header).
 cudaError_t launch_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int role, int64_t slice,
                               cudaStream_t st);
+cudaError_t launch_wait_timeout_probe(int32_t* status, long long limit, cudaStream_t st);
 // CTA-pair (cta_group::2) kernel for dense products; tile counts in p are in 256 x 256 tiles.
 int32_t gemm_tcgen05_pair(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,
                           const TcOperand* B2, TcParams p, cudaStream_t st);

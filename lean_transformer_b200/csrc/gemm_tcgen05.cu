@@ -118,6 +118,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  const long long wait_limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   const int kpb = p.bs_block > 0 ? p.bs_block / BLOCK_K : 1;  // k-blocks per sparse block
   const int sub = p.bs_block >= BLOCK_N ? p.bs_block / BLOCK_N : 1;  // tiles per sparse block along N (and M for wgrad)
@@ -149,7 +150,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int kb_main = main_k_blocks(n_blk);
       const int kb_total = kb_main + p.num_k2_blocks;
       for (int kb = 0; kb < kb_total; ++kb) {
-        if (*abort_ptr != 0 || !mbar_wait_bounded(empty_bar(stage), phase ^ 1u)) {
+        if (*abort_ptr != 0 || !mbar_wait_bounded(empty_bar(stage), phase ^ 1u, wait_limit)) {
           report(p.status, LEANFFN_DEV_TIMEOUT_PRODUCER);
           *abort_ptr = 1;
           ok = false;
@@ -262,7 +263,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      if (*abort_ptr != 0 || !mbar_wait_bounded(tempty_bar(acc_stage), acc_phase ^ 1u)) {
+      if (*abort_ptr != 0 || !mbar_wait_bounded(tempty_bar(acc_stage), acc_phase ^ 1u, wait_limit)) {
         report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
         *abort_ptr = 1;
         break;
@@ -273,7 +274,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tile_coords(tile, m_blk, n_blk);
       const int kb_total = main_k_blocks(n_blk) + p.num_k2_blocks;
       for (int kb = 0; kb < kb_total; ++kb) {
-        if (*abort_ptr != 0 || !mbar_wait_bounded(full_bar(stage), phase)) {
+        if (*abort_ptr != 0 || !mbar_wait_bounded(full_bar(stage), phase, wait_limit)) {
           report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
           *abort_ptr = 1;
           ok = false;
@@ -323,7 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int t = 0; t < MT; ++t)
         epilogue_prefetch_aux<BLOCK_N>(ep, static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32, n_blk, lane,
                                        (warp - 2) >> 2, 2);
-      if (*abort_ptr != 0 || !mbar_wait_bounded(tfull_bar(acc_stage), acc_phase)) {
+      if (*abort_ptr != 0 || !mbar_wait_bounded(tfull_bar(acc_stage), acc_phase, wait_limit)) {
         report(p.status, LEANFFN_DEV_TIMEOUT_EPILOGUE);
         *abort_ptr = 1;
         break;
@@ -359,6 +360,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// One thread waits, with the given limit, on an mbarrier that nobody ever arrives at: the wait must give up, record
+// its code in the status word and return, exactly as the roles of the GEMM kernel do when a peer role stalls.
+__global__ void wait_timeout_probe_kernel(int32_t* status, long long limit) {
+  __shared__ alignas(8) uint64_t bar;
+  const uint32_t addr = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(addr, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait_bounded(addr, 0u, limit)) report(status, LEANFFN_DEV_TIMEOUT_EPILOGUE);
+}
+
+cudaError_t launch_wait_timeout_probe(int32_t* status, long long limit, cudaStream_t st) {
+  wait_timeout_probe_kernel<<<1, 32, 0, st>>>(status, limit);
+  return cudaGetLastError();
 }
 
 // ---- host side -----------------------------------------------------------------------------------

@@ -53,13 +53,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: gives up after ~WAIT_LIMIT_CYCLES SM clocks (about a second) and returns false.
+// Bounded wait: gives up after `limit` SM clocks (default ~WAIT_LIMIT_CYCLES, about a second) and returns false.
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }

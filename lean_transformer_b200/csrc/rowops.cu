@@ -385,18 +385,19 @@ ln_bwd_generic_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const
 
 // ---- column sums ------------------------------------------------------------------------------
 // Block = 32 column lanes (4 columns each) x 8 row lanes; grid = (ceil(cols/128), chunks).
-// out[chunk * out_stride + c] = sum over the chunk's rows.
+// out[chunk * out_stride + c] = sum over the chunk's rows.  vec_ok (decided on the host from the base address
+// and the leading dimension) allows 4-element vector loads; otherwise every element is loaded on its own.
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_kernel(const T* __restrict__ x, int64_t ld, float* __restrict__ out, int64_t out_stride, int64_t rows,
-              int64_t cols, int64_t rows_per_chunk) {
+              int64_t cols, int64_t rows_per_chunk, int vec_ok) {
   __shared__ float sm[8][132];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int64_t c = (static_cast<int64_t>(blockIdx.x) * 32 + cx) * 4;
   const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_chunk;
   const int64_t r1 = min(rows, r0 + rows_per_chunk);
   float a[4] = {0.f, 0.f, 0.f, 0.f};
-  if (c + 3 < cols && (ld & 3) == 0) {
+  if (c + 3 < cols && vec_ok) {
     for (int64_t r = r0 + ry; r < r1; r += 8) {
       Vec4<T> q;
       float f[4];
@@ -437,14 +438,17 @@ static int32_t colsum_launch(const T* x, int64_t ld, float* out, float* scratch,
                              cudaStream_t st) {
   const int64_t chunks = colsum_chunks(rows, cols);
   const dim3 grid1(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>(chunks));
+  // a row of 4 elements is loaded as one vector only if every such vector is naturally aligned
+  const int vec1 = (ld % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T)) == 0);
   if (chunks == 1) {
-    colsum_kernel<T><<<grid1, 256, 0, st>>>(x, ld, out, cols, rows, cols, rows);
+    colsum_kernel<T><<<grid1, 256, 0, st>>>(x, ld, out, cols, rows, cols, rows, vec1);
     return launch_status();
   }
   const int64_t rpc = (rows + chunks - 1) / chunks;
-  colsum_kernel<T><<<grid1, 256, 0, st>>>(x, ld, scratch, cols, rows, cols, rpc);
+  colsum_kernel<T><<<grid1, 256, 0, st>>>(x, ld, scratch, cols, rows, cols, rpc, vec1);
   const dim3 grid2(static_cast<unsigned>((cols + 127) / 128), 1);
-  colsum_kernel<float><<<grid2, 256, 0, st>>>(scratch, cols, out, cols, chunks, cols, chunks);
+  const int vec2 = (cols % 4 == 0) && (reinterpret_cast<uintptr_t>(scratch) % 16 == 0);
+  colsum_kernel<float><<<grid2, 256, 0, st>>>(scratch, cols, out, cols, chunks, cols, chunks, vec2);
   return launch_status();
 }
 
@@ -608,7 +612,10 @@ static int32_t ln_fwd_dispatch(const void* x, const void* gamma, const void* bet
   const TR* rp = static_cast<const TR*>(residual);
   const int c = static_cast<int>(cols);
   const int sms = sm_count();
-  const bool vec = (cols % 4 == 0) && (thr == 0u || off % 4 == 0);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  // the register path moves 4-element vectors: every pointer 16-byte aligned, else the scalar kernel below
+  const bool vec = (cols % 4 == 0) && (thr == 0u || off % 4 == 0) && al16(x) && al16(y) && al16(gamma) && al16(beta) &&
+                   al16(residual);
 #define LN_FWD_CASE(VPT, WPR)                                                                                       \
   {                                                                                                                 \
     constexpr int RPB = (LN_THREADS / 32) / WPR;                                                                    \
@@ -806,6 +813,11 @@ extern "C" int32_t leanffn_layer_norm_backward(const void* dy, int32_t dy_dtype,
     }
     return LEANFFN_OK;
   }
+  if (cols % 4 == 0 && cols <= 16384) {
+    // the register path moves 4-element vectors
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!al16(dy) || !al16(x) || !al16(gamma) || !al16(dresidual) || !al16(dx) || !al16(scratch)) return LEANFFN_ERR_ALIGN;
+  }
   if (dresidual == nullptr) dresidual_dtype = dy_dtype;
 #define LN_BWD_GO(TD, TX, TP, TR, TO)                                                                             \
   return ln_bwd_dispatch<TD, TX, TP, TR, TO>(dy, x, gamma, dresidual, dx, dgamma, dbeta, scratch, rows, cols, eps, \
@@ -858,6 +870,7 @@ extern "C" int32_t leanffn_activation_forward(const void* pre, void* hid, int32_
   if (rows < 0 || inter <= 0 || inter % 4 != 0) return LEANFFN_ERR_SHAPE;
   if (!dtype_ok(dtype)) return LEANFFN_ERR_DTYPE;
   if (act < 0 || act >= LEANFFN_ACT_COUNT) return LEANFFN_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(pre) | reinterpret_cast<uintptr_t>(hid)) & 15u) return LEANFFN_ERR_ALIGN;
   if (rows == 0) return LEANFFN_OK;
   return launch_act_fwd(pre, hid, dtype, rows, inter, gated, act, static_cast<cudaStream_t>(stream));
 }
@@ -869,6 +882,9 @@ extern "C" int32_t leanffn_activation_backward(const void* dhid, const void* pre
   if (rows < 0 || inter <= 0 || inter % 4 != 0) return LEANFFN_ERR_SHAPE;
   if (!dtype_ok(dtype)) return LEANFFN_ERR_DTYPE;
   if (act < 0 || act >= LEANFFN_ACT_COUNT) return LEANFFN_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(dhid) | reinterpret_cast<uintptr_t>(pre) | reinterpret_cast<uintptr_t>(dpre) |
+       reinterpret_cast<uintptr_t>(hid_out)) & 15u)
+    return LEANFFN_ERR_ALIGN;
   if (rows == 0) return LEANFFN_OK;
   return launch_act_bwd(dhid, inter, pre, dpre, hid_out, dtype, rows, inter, gated, act,
                         static_cast<cudaStream_t>(stream));
@@ -972,7 +988,8 @@ extern "C" int32_t leanffn_column_sum_static(const void* x, int32_t x_dtype, int
     // first call on this device (it is the current device): resolve the symbol's device address
     float* ptr = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_colsum_static_scratch);
-    if (e != cudaSuccess || ptr == nullptr) return 1000 + static_cast<int32_t>(e);
+    if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+    if (ptr == nullptr) return LEANFFN_ERR_DRIVER;
     g_colsum_static_ptr[dev] = ptr;
   }
   float* scratch = g_colsum_static_ptr[dev];

@@ -200,6 +200,13 @@ class ScatteredGradReducer:
     Summation order across ranks is not fixed, so results are not bit-reproducible (bf16 gradients are also
     accumulated in bf16 at the owner).  Micro-batch accumulation: call ``begin_step`` once, run several
     backwards, then ``finish`` — every backward adds into the same blocks.
+
+    ``finish`` makes ``param.grad`` a VIEW of the exchange buffer: the next ``begin_step`` zeroes part of that
+    storage, so consume the gradient (optimizer step, or a copy) before it.  A gradient that some other path left
+    in ``param.grad`` since ``begin_step`` (a shared matrix also used outside LeanFFN, whose contribution came
+    through autograd) is added into the view on every rank's own replica only, i.e. it is NOT summed over ranks;
+    reduce such contributions separately.  Registered weights must be bf16 or fp32 weights of bf16 products: the
+    scattering epilogue exists in the tensor-core kernel only, so a model computing in fp32 keeps ``GradSync``.
     """
 
     BLOCK_SHIFT = 8  # 256 rows: the tile height of the weight-gradient GEMM
@@ -225,6 +232,8 @@ class ScatteredGradReducer:
                 raise ValueError(f"{name}: dense, contiguous 2-D CUDA weights only")
             if w.shape[0] % block_rows != 0:
                 raise ValueError(f"{name}: {w.shape[0]} rows are not a multiple of {block_rows}")
+            if w.dtype not in (torch.bfloat16, torch.float32):
+                raise ValueError(f"{name}: {w.dtype} weights are not supported (bf16, or fp32 masters of bf16 products)")
             device = w.device
             nbytes = w.numel() * w.element_size()
             self._slices[name] = (offset, tuple(w.shape), w.dtype)
@@ -311,7 +320,11 @@ class ScatteredGradReducer:
             self._capped = False
         for name, w in self._params.items():
             if isinstance(w, torch.nn.Parameter) or w.requires_grad:
-                w.grad = self._views[name]
+                view = self._views[name]
+                stray = w.grad
+                if stray is not None and stray.data_ptr() != view.data_ptr():
+                    view.add_(stray.to(view.dtype))  # delivered by another path since begin_step: keep it
+                w.grad = view
         return count
 
 

@@ -5,19 +5,43 @@
 this package's drop-ins.  Parameters and buffers are re-used (the very same ``nn.Parameter`` objects), so optimizer
 state, weight sharing between layers (``share_large_matrices``) and checkpoints keep working.  Classes are recognised
 by name, so the reference does not have to be importable here.
+
+Every drop-in is an instance of a class derived from BOTH this package's class and the class it replaces (this
+package's first in the method resolution order, so all behaviour is this package's).  The model's own code keeps
+recognising its modules that way: ``LeanTransformer.set_optimizations`` finds its FFNs with ``isinstance(module,
+LeanFFN)`` (lean_transformer/transformer.py:139-147, which otherwise asserts on any other module that has an
+``ffn_custom_grad`` attribute) and re-generates block-sparse operators with ``isinstance(module, GeneralizedMatrix)``
+(:149-152).
 """
-from typing import Dict
+from typing import Dict, Tuple
 
 import torch.nn as nn
 
 from .blocksparse.linear import GeneralizedLinear, GeneralizedMatrix
 from .ffn import LeanFFN
 
+_DROPIN_CLASSES: Dict[Tuple[type, type], type] = {}
+
+
+def _dropin_class(ours: type, theirs: type) -> type:
+    """``ours`` if ``theirs`` already derives from it, else a class derived from (ours, theirs)."""
+    if issubclass(theirs, ours):
+        return theirs
+    key = (ours, theirs)
+    cls = _DROPIN_CLASSES.get(key)
+    if cls is None:
+        cls = type(ours.__name__, (ours, theirs), {"__module__": ours.__module__, "__doc__": ours.__doc__})
+        _DROPIN_CLASSES[key] = cls
+    return cls
+
 
 def _convert_matrix(ref, memo: Dict[int, nn.Module]) -> GeneralizedMatrix:
+    if isinstance(ref, GeneralizedMatrix):
+        return ref
     if id(ref) in memo:
         return memo[id(ref)]
-    new = GeneralizedMatrix.__new__(GeneralizedMatrix)
+    cls = _dropin_class(GeneralizedMatrix, type(ref))
+    new = cls.__new__(cls)
     nn.Module.__init__(new)
     new.out_features, new.in_features = ref.out_features, ref.in_features
     new.blocksparse_backend = getattr(ref, "blocksparse_backend", "native")
@@ -39,7 +63,8 @@ def _convert_linear(ref, memo: Dict[int, nn.Module]) -> nn.Module:
         return ref
     if id(ref) in memo:
         return memo[id(ref)]
-    new = GeneralizedLinear.__new__(GeneralizedLinear)
+    cls = _dropin_class(GeneralizedLinear, type(ref))
+    new = cls.__new__(cls)
     nn.Module.__init__(new)
     new.matrix = _convert_matrix(ref.matrix, memo)
     new.out_features, new.in_features = ref.out_features, ref.in_features
@@ -50,7 +75,10 @@ def _convert_linear(ref, memo: Dict[int, nn.Module]) -> nn.Module:
 
 
 def _convert_ffn(ref, memo: Dict[int, nn.Module]) -> LeanFFN:
-    new = LeanFFN.__new__(LeanFFN)
+    if id(ref) in memo:
+        return memo[id(ref)]
+    cls = _dropin_class(LeanFFN, type(ref))
+    new = cls.__new__(cls)
     nn.Module.__init__(new)
     new.i2h_proj = _convert_linear(ref.i2h_proj, memo)
     new.h2o_proj = _convert_linear(ref.h2o_proj, memo)
@@ -60,23 +88,41 @@ def _convert_ffn(ref, memo: Dict[int, nn.Module]) -> LeanFFN:
     new.gated, new.dropout, new.residual = ref.gated, ref.dropout, ref.residual
     new.ffn_custom_grad = ref.ffn_custom_grad
     new.train(ref.training)
+    memo[id(ref)] = new
     return new
+
+
+def _is_reference(module: nn.Module, name: str, ours: type) -> bool:
+    return type(module).__name__ == name and not isinstance(module, ours)
 
 
 def convert_model(model: nn.Module, convert_linears: bool = True) -> nn.Module:
     """Replace every reference ``LeanFFN`` (and, optionally, stand-alone ``GeneralizedLinear``) inside ``model``
-    by the CUDA drop-in.  Returns ``model``."""
+    by the CUDA drop-in.  Returns the converted model: ``model`` itself, modified in place, unless ``model`` IS a
+    reference ``LeanFFN`` / ``GeneralizedLinear``, in which case its drop-in is returned."""
     memo: Dict[int, nn.Module] = {}
+    if _is_reference(model, "LeanFFN", LeanFFN):
+        return _convert_ffn(model, memo)
+    if convert_linears and _is_reference(model, "GeneralizedLinear", GeneralizedLinear):
+        return _convert_linear(model, memo)
 
     def visit(parent: nn.Module):
         for name, child in list(parent.named_children()):
-            kind = type(child).__name__
-            if kind == "LeanFFN" and not isinstance(child, LeanFFN):
+            if _is_reference(child, "LeanFFN", LeanFFN):
                 setattr(parent, name, _convert_ffn(child, memo))
-            elif convert_linears and kind == "GeneralizedLinear" and not isinstance(child, GeneralizedLinear):
+            elif convert_linears and _is_reference(child, "GeneralizedLinear", GeneralizedLinear):
                 setattr(parent, name, _convert_linear(child, memo))
             else:
                 visit(child)
 
     visit(model)
+    # LeanTransformer keeps the layer sequence it runs in a plain tuple outside its module tree
+    # (lean_transformer/transformer.py:33-45); its wrappers still hold the replaced modules.  The memo maps each old
+    # module to the drop-in it already got, and the sequence keeps its checkpointing settings.
+    for module in list(model.modules()):
+        cached = getattr(module, "_sequential", None)
+        if isinstance(cached, tuple):
+            for sequence in cached:
+                if isinstance(sequence, nn.Module):
+                    visit(sequence)
     return model

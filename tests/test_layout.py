@@ -86,3 +86,29 @@ def test_pair_tables_cover_every_block_once():
         for t in range(int(c2[o])):
             f, j = fwd2[o, t].tolist()
             assert nz[f] == [o, j]
+
+
+def test_native_index_buffers_are_validated_before_any_kernel_uses_them():
+    """Entries of the index buffers become addresses inside the kernels: corrupt buffers must raise on the host."""
+    import pytest
+    from lean_transformer_b200.blocksparse.native_backend import _validate_indices
+    layout = L.get_blocksparse_layout(512, 256, "pixelfly(block_size=32)")
+    fwd, bwd = L.get_indices_from_layout(layout)
+    per_input = bwd.shape[1]
+    _validate_indices(fwd, bwd, per_input)
+    _validate_indices(fwd, None, per_input)
+    _validate_indices(None, bwd, per_input)
+    bad = fwd.clone(); bad[0, 0] = fwd.numel() + 3  # out of range
+    with pytest.raises(ValueError):
+        _validate_indices(bad, None, per_input)
+    bad = fwd.clone(); bad[0, 0] = bad[0, 1]  # not a permutation
+    with pytest.raises(ValueError):
+        _validate_indices(bad, bwd, per_input)
+    bad = bwd.clone(); bad[0, 0] = -1
+    with pytest.raises(ValueError):
+        _validate_indices(fwd, bad, per_input)
+    bad = bwd.clone(); bad[0, 0] = (int(bad[0, 0]) + 1) % fwd.shape[0]  # disagrees with forward_indices
+    with pytest.raises(ValueError):
+        _validate_indices(fwd, bad, per_input)
+    with pytest.raises(ValueError):
+        _validate_indices(fwd, bwd, per_input + 1)
