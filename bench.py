@@ -51,10 +51,21 @@ def flops_per_token(hidden, inter, wl=None):
     return 18.0 * hidden * inter  # gated FFN: forward 6*H*I, backward 12*H*I
 
 
-# DRAM bytes (read + written) per GEMM launch and per token of the GPU's shard, from one `ncu --set full` capture of the
-# six GEMMs of a step at 8192 tokens (profiles/gemm_tcgen05_dense_bf16_h8192_tokens8192.md): 42.07 GB over 6 launches.
-# Operand re-reads and activation traffic both grow with the token count, so the figure is scaled by tokens.
-GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH = {"dense_bf16_h8192": 42.07e9 / 6 / 8192}
+def captured_traffic(name, tokens):
+    """DRAM bytes (read + written) per GEMM launch for `tokens` tokens on this GPU, from the ncu counter captures
+    recorded per workload in profiles/dram_traffic.json (captured at a smaller token count under the capture-size
+    rule and scaled by tokens: operand re-reads and activation traffic both grow with the token count).  None for a
+    workload without a capture."""
+    path = ROOT / "profiles" / "dram_traffic.json"
+    if not path.exists():
+        return None, None
+    entry = json.loads(path.read_text()).get(name)
+    if not entry:
+        return None, None
+    per_launch = entry["dram_bytes_total"] / entry["gemm_launches"] * tokens / entry["tokens_captured"]
+    note = (f"ncu dram__bytes_read.sum + dram__bytes_write.sum over {entry['gemm_launches']} GEMM launches at "
+            f"{entry['tokens_captured']} tokens ({entry['source']}), scaled by tokens to {tokens}; bytes per launch")
+    return per_launch, note
 
 
 def load_peaks():
@@ -113,6 +124,53 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------------
 # CPU baseline / reference arm: the oracle (a CPU restatement of the reference's algorithm) on host cores
 # ------------------------------------------------------------------------------------------------------
+def reference_step_time(hidden, inter, sample_tokens, steps, warmup, threads, wl=None):
+    """Median fwd+bwd seconds of the REFERENCE's own LeanFFN (lean_transformer/ffn.py, ffn_custom_grad=True, fp32) on
+    the host cores, or None where its mirror (oracle/_ref, made by oracle/build_ref.py) is absent."""
+    from oracle import ref_harness
+
+    ref = ref_harness.import_reference()
+    if ref is None:
+        return None
+    torch.set_num_threads(threads)
+    torch.manual_seed(0)
+    i2h = h2o = None
+    if wl is not None and wl.get("layout"):
+        GM, GL = ref.linear.GeneralizedMatrix, ref.linear.GeneralizedLinear
+        i2h = GL(GM(hidden, 2 * inter, wl["layout"], wl["lowrank"]))
+        h2o = GL(GM(inter, hidden, wl["layout"], wl["lowrank"]))
+    ffn = ref.ffn.LeanFFN(hidden, inter, gated=True, dropout=0.0, i2h_proj=i2h, h2o_proj=h2o, ffn_custom_grad=True)
+    with torch.no_grad():
+        for proj in (ffn.i2h_proj, ffn.h2o_proj):
+            proj.weight.normal_(0.0, 0.02)
+            proj.bias.zero_()
+    x = torch.randn(1, sample_tokens, hidden)
+    g = torch.randn(1, sample_tokens, hidden)
+    times = []
+    for i in range(warmup + steps):
+        for p in ffn.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        t0 = time.perf_counter()
+        ffn(xi).backward(g)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def cpu_baseline_time(hidden, inter, sample_tokens, steps, warmup, threads, wl=None):
+    """(seconds per step, kind): the reference's own LeanFFN where it can be imported, else the CPU port."""
+    try:
+        t = reference_step_time(hidden, inter, sample_tokens, steps, warmup, threads, wl)
+    except Exception as e:  # an import or API problem of the mirrored package must not take the bench down
+        print(f"reference LeanFFN unavailable ({type(e).__name__}: {e}); timing the CPU port", file=sys.stderr)
+        t = None
+    if t is not None:
+        return t, "reference"
+    return cpu_step_time(hidden, inter, sample_tokens, steps, warmup, threads, wl), "port"
+
+
 def cpu_step_time(hidden, inter, sample_tokens, steps, warmup, threads, wl=None):
     from oracle import leanffn_oracle as O
 
@@ -157,16 +215,18 @@ def run_reference_arm(args, wl, name):
     hidden, inter = wl["hidden"], wl["inter"]
     threads = host_threads()
     sample = 512 if hidden >= 4096 else 4096
-    step_s = cpu_step_time(hidden, inter, sample, args.steps, args.warmup, threads, wl)
+    step_s, kind = cpu_baseline_time(hidden, inter, sample, args.steps, args.warmup, threads, wl)
     value = sample / step_s
+    what = ("the reference's own LeanFFN (lean_transformer/ffn.py, ffn_custom_grad=True)" if kind == "reference"
+            else "CPU restatement of the reference's LeanFFN")
     sample_desc = (f"{sample} tokens of the {name} workload per step (fp32, GeGLU, hidden {hidden}, intermediate {inter}), "
-                   f"median of {args.steps} steps after {args.warmup} warm-up")
+                   f"{what}, median of {args.steps} steps after {args.warmup} warm-up")
     line = dict(impl="reference", metric="LeanFFN fwd+bwd tokens/sec", value=value, unit="tokens/s", n_gpus=args.gpus,
                 steps=args.steps, warmup=args.warmup, ms_per_step=step_s * 1e3, higher_is_better=True,
                 scaling=wl["scaling"], vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(workload=name, hidden=hidden, intermediate=inter, gated=True, sample_tokens=sample,
                             parallelism="host cores only"),
-                cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=sample_desc),
+                cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind=kind, sample=sample_desc),
                 e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 gflops=value * flops_per_token(hidden, inter, wl) / 1e9)
     print(json.dumps(line), flush=True)
@@ -220,6 +280,7 @@ def run_ours(args, wl, name):
         dist.init_process_group("nccl", device_id=device)
 
     hidden, inter = wl["hidden"], wl["inter"]
+    start = 0
     if wl["scaling"] == "strong":
         start, tokens = ldist.shard_tokens(wl["total_tokens"], world, rank)
         total_tokens = wl["total_tokens"]
@@ -229,9 +290,21 @@ def run_ours(args, wl, name):
     in_dtype = torch.float32 if (wl["mixed"] or wl.get("fp32")) else torch.bfloat16
     ffn = build_module(wl, device)
     params = [p for p in ffn.parameters()]
-    gen = torch.Generator(device=device).manual_seed(1000 + rank)
-    x_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(in_dtype)
-    g_dev = torch.randn(tokens, hidden, device=device, generator=gen).to(torch.float32 if wl.get("fp32") else torch.bfloat16)
+    # Inputs are a function of the GLOBAL token index: chunk c of the batch (1/8 of the strong-scaling batch, one
+    # rank's shard otherwise) is drawn from a generator seeded with 1000 + c, and every rank draws the chunks of its
+    # own shard.  The strong-scaling batch is therefore the same tensor at every N, and so are its gradients.
+    first_token = start if wl["scaling"] == "strong" else rank * tokens
+    chunk = max(1, wl["total_tokens"] // 8) if wl["scaling"] == "strong" else tokens
+    if first_token % chunk or tokens % chunk:
+        chunk = tokens  # shards that do not line up with the chunks (odd --tokens overrides): one chunk per rank
+    g_dtype = torch.float32 if wl.get("fp32") else torch.bfloat16
+    x_parts, g_parts = [], []
+    for c in range(first_token // chunk, (first_token + tokens) // chunk):
+        gen = torch.Generator(device=device).manual_seed(1000 + c)
+        x_parts.append(torch.randn(chunk, hidden, device=device, generator=gen).to(in_dtype))
+        g_parts.append(torch.randn(chunk, hidden, device=device, generator=gen).to(g_dtype))
+    x_dev, g_dev = torch.cat(x_parts), torch.cat(g_parts)
+    del x_parts, g_parts
     sync = (ldist.GradSync(wire_dtype=torch.bfloat16, comm_sms=args.comm_sms if args.grad_exchange == "nccl" else None,
                            measure_tail=True, params=params) if world > 1 else None)
     reducer = None
@@ -268,7 +341,7 @@ def run_ours(args, wl, name):
             sync.finish()
         if reducer is not None:
             reducer.finish()
-        return out
+        return out, x.grad
 
     def barrier():
         if world > 1:
@@ -318,12 +391,32 @@ def run_ours(args, wl, name):
         return
 
     # ---- end-to-end through the module API with host buffers (e2e) --------------------------------------
+    # ---- N-invariant checksums of one more (untimed) step on the resident inputs --------------------------------
+    out, dx = step(x_dev.detach(), g_dev)
+    sums = torch.stack([(out.double().reshape(-1) * g_dev.double().reshape(-1)).sum(), dx.double().abs().sum()])
+    if world > 1:
+        dist.all_reduce(sums)  # partial sums over this rank's tokens -> whole batch
+    checksum = dict(sum_out_dot_g=float(sums[0]), sum_abs_grad_input=float(sums[1]),
+                    sum_abs_grad_i2h_weight=float(ffn.i2h_proj.weight.grad.double().abs().sum()),
+                    sum_abs_grad_h2o_weight=float(ffn.h2o_proj.weight.grad.double().abs().sum()),
+                    sum_abs_grad_i2h_bias=float(ffn.i2h_proj.bias.grad.double().abs().sum()),
+                    note=("computed on rank 0 after the gradient exchange; inputs are a function of the global token "
+                          "index, so with strong scaling every value is the same at every N up to bf16 summation "
+                          "order"))
+    out_dtype, dx_dtype, out_shape = out.dtype, dx.dtype, tuple(out.shape)
+    del out, dx, sums
+
     x_host = x_dev.detach().cpu().pin_memory()
     g_host = g_dev.cpu().pin_memory()
     copy_stream = torch.cuda.Stream(device)
     bufs = [(torch.empty_like(x_dev), torch.empty_like(g_dev)) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
+    # the step's results (output and input gradient) return to pinned host buffers, double-buffered like the uploads
+    out_host = [torch.empty(out_shape, dtype=out_dtype).pin_memory() for _ in range(2)]
+    dx_host = [torch.empty(out_shape, dtype=dx_dtype).pin_memory() for _ in range(2)]
+    produced = [torch.cuda.Event() for _ in range(2)]
+    drained = [torch.cuda.Event() for _ in range(2)]
 
     def upload(i):
         slot = i % 2
@@ -338,6 +431,7 @@ def run_ours(args, wl, name):
         main = torch.cuda.current_stream(device)
         for slot in range(2):
             consumed[slot].record(main)
+            drained[slot].record(copy_stream)
         upload(0)
         for i in range(n):
             slot = i % 2
@@ -345,10 +439,20 @@ def run_ours(args, wl, name):
                 upload(i + 1)  # the next step's inputs cross PCIe while this step computes
             main.wait_event(ready[slot])
             xb, gb = bufs[slot]
-            out = step(xb.detach(), gb)
-            loss = torch.dot(out.detach().reshape(-1), gb.reshape(-1))  # loss = sum(out * g)
+            out, dx = step(xb.detach(), gb)
+            loss = torch.dot(out.detach().reshape(-1).float(), gb.reshape(-1).float())  # loss = sum(out * g)
             consumed[slot].record(main)
-            losses.append(float(loss.item()))  # device -> host read of the step's result
+            produced[slot].record(main)
+            with torch.cuda.stream(copy_stream):  # results cross PCIe underneath the next step
+                copy_stream.wait_event(produced[slot])
+                out_host[slot].copy_(out.detach(), non_blocking=True)
+                dx_host[slot].copy_(dx, non_blocking=True)
+                drained[slot].record(copy_stream)
+            out.record_stream(copy_stream)
+            dx.record_stream(copy_stream)
+            losses.append(float(loss.item()))  # device -> host read of the step's loss
+        for slot in range(2):
+            main.wait_event(drained[slot])  # the timed region ends when the last results are on the host
         return losses
 
     e2e_loop(min(2, args.warmup))
@@ -364,9 +468,17 @@ def run_ours(args, wl, name):
     e_seconds = float(e_elapsed.item())
     L.check_device_status(device)
 
+    out_host_bytes = sum(t.numel() * t.element_size() for t in (out_host[0], dx_host[0]))
     extra = {}
-    if rank == 0 and world == 1 and args.extra_workload and args.extra_workload != name:
-        extra[args.extra_workload] = quick_measure(WORKLOADS[args.extra_workload], device, args)
+    if rank == 0 and world == 1 and args.extra_workload:
+        del bufs, out_host, dx_host
+        x_dev = g_dev = None
+        ffn = None
+        params = []
+        torch.cuda.empty_cache()
+        for other in [w.strip() for w in args.extra_workload.split(",") if w.strip()]:
+            if other != name and other in WORKLOADS:
+                extra[other] = quick_measure(WORKLOADS[other], device, args, other)
 
     if world > 1:
         lffn.set_grad_ready_hook(None)
@@ -380,14 +492,17 @@ def run_ours(args, wl, name):
     tokens_per_s = total_tokens * args.steps / seconds
     tflops = tokens_per_s * flops_per_token(hidden, inter, wl) / 1e12
     achieved = gemm_flops / gemm_seconds / 1e12 if gemm_seconds > 0 else None
+    traffic, traffic_note = captured_traffic(name, tokens)
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = host_threads()
         sample = 512 if hidden >= 4096 else 4096
-        cpu_s = cpu_step_time(hidden, inter, sample, 3, 1, threads, wl)
-        cpu = dict(value=sample / cpu_s, unit="tokens/s", cores=threads, kind="port",
-                   sample=f"{sample} tokens of the {name} workload per step in fp32 on the host cores "
-                          f"(CPU restatement of the reference's LeanFFN), median of 3 steps after 1 warm-up")
+        cpu_s, kind = cpu_baseline_time(hidden, inter, sample, 3, 1, threads, wl)
+        cpu = dict(value=sample / cpu_s, unit="tokens/s", cores=threads, kind=kind,
+                   sample=f"{sample} tokens of the {name} workload per step in fp32 on the host cores ("
+                          + ("the reference's own LeanFFN, lean_transformer/ffn.py, ffn_custom_grad=True"
+                             if kind == "reference" else "CPU restatement of the reference's LeanFFN")
+                          + "), median of 3 steps after 1 warm-up")
     line = dict(
         metric="LeanFFN fwd+bwd tokens/sec", value=tokens_per_s, unit="tokens/s", n_gpus=world, steps=args.steps,
         warmup=args.warmup, ms_per_step=seconds / args.steps * 1e3, higher_is_better=True, scaling=wl["scaling"],
@@ -406,18 +521,18 @@ def run_ours(args, wl, name):
         pct_of_bf16_peak_datasheet=100.0 * tflops / world / 2250.0,
         roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
                       frac=(achieved / peaks["bf16_sustained"]) if achieved else None,
-                      traffic=(GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH[name] * tokens
-                               if name in GEMM_DRAM_BYTES_PER_TOKEN_AND_LAUNCH else None),
-                      traffic_unit="bytes per launch (ncu dram read + write of a smaller capture, scaled by tokens)",
+                      traffic=traffic, traffic_note=traffic_note,
                       kernel="gemm_tcgen05_kernel (all GEMM launches of the timed region)", launches=gemm_launches,
                       peak_source=f"bf16_tflops_sustained of {peaks['source']} peaks (kernel timed inside a long step)"),
         cpu_baseline=cpu,
         e2e=dict(value=total_tokens * args.steps / e_seconds, unit="tokens/s",
                  h2d_bytes_per_step=(x_host.numel() * x_host.element_size() + g_host.numel() * g_host.element_size()) * world,
-                 d2h_bytes_per_step=2 * world, ms_per_step=e_seconds / args.steps * 1e3,
-                 api="LeanFFN.forward / Tensor.backward with pinned host inputs, double-buffered uploads",
+                 d2h_bytes_per_step=(out_host_bytes + 4) * world, ms_per_step=e_seconds / args.steps * 1e3,
+                 api="LeanFFN.forward / Tensor.backward with pinned host inputs (double-buffered uploads); the output, "
+                     "the input gradient and the loss return to pinned host memory every step",
                  last_loss=losses[-1] if losses else None),
-        gpu_launches=launches, clocks=clocks)
+        gpu_launches=launches, clocks=clocks, checksum=checksum,
+        tokens_per_s_per_sm_mhz=(tokens_per_s / clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None)
     if world > 1:
         line["comm"] = dict(exposed_allreduce_ms_per_step=exposed_ms,
                             sms_left_free_during_exchange=2 if reducer is not None else args.comm_sms,
@@ -428,9 +543,10 @@ def run_ours(args, wl, name):
     print(json.dumps(line), flush=True)
 
 
-def quick_measure(wl, device, args):
+def quick_measure(wl, device, args, name=""):
     """Device-resident fwd+bwd rate of a second workload on one GPU (reported next to the headline)."""
     import lean_transformer_b200 as L
+    from lean_transformer_b200 import ops
 
     ffn = build_module(wl, device)
     tokens, hidden = wl.get("tokens_per_rank") or wl["total_tokens"], wl["hidden"]
@@ -452,16 +568,27 @@ def quick_measure(wl, device, args):
     for _ in range(5):
         step()
     torch.cuda.synchronize()
-    n = 50
+    n = 20 if tokens * hidden >= (1 << 27) else 50
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(n):
-        step()
-    b.record()
-    torch.cuda.synchronize()
+    launches0 = ops.launch_count
+    with ops.GemmTimer() as timer:
+        a.record()
+        for _ in range(n):
+            step()
+        b.record()
+        torch.cuda.synchronize()
     L.check_device_status(device)
     s = a.elapsed_time(b) * 1e-3 / n
+    gemm_flops, gemm_seconds, gemm_launches = timer.summary()
+    peaks = load_peaks()
+    achieved = gemm_flops / gemm_seconds / 1e12 if gemm_seconds > 0 else None
+    traffic, traffic_note = captured_traffic(name, tokens)
     return dict(tokens_per_s=tokens / s, ms_per_step=s * 1e3, tflops=tokens / s * flops_per_token(hidden, wl["inter"], wl) / 1e12,
+                steps=n, warmup=5, gpu_launches_per_step=(ops.launch_count - launches0) / n,
+                roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
+                              frac=(achieved / peaks["bf16_sustained"]) if achieved else None, traffic=traffic,
+                              traffic_note=traffic_note, launches=gemm_launches,
+                              kernel="all GEMM launches of the timed region (CUDA events around each launch)"),
                 config=dict(hidden=hidden, intermediate=wl["inter"], tokens=tokens, dropout=wl["dropout"],
                             parameters=("fp32 masters + bf16 compute" if wl["mixed"] else
                                         "fp32 (TF32x3 tensor cores)" if wl.get("fp32") else "bf16")))
@@ -474,7 +601,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="dense_bf16_h8192")
-    ap.add_argument("--extra-workload", default="mixed_bf16_h1024")
+    ap.add_argument("--extra-workload", default="mixed_bf16_h1024,dense_fp32_h768,pixelfly_bf16_h4096",
+                    help="comma-separated workloads measured device-resident on one GPU after the headline one and "
+                         "reported under other_workloads ('' = none)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to NCCL while GEMMs run (N > 1)")
     ap.add_argument("--grad-exchange", choices=("nccl", "fused"), default="fused",
                     help="N > 1: all-reduce every gradient with NCCL, or reduce-scatter the dense weight gradients inside "

@@ -90,3 +90,55 @@ def random_params(hidden: int, inter: int, gated: bool, *, seed: int = 0, std: f
     if post_ln:
         p.update(post_ln_weight=1 + 0.1 * rn(hidden), post_ln_bias=0.1 * rn(hidden))
     return p
+
+
+# ---- noise-floor twin: the same step with stock PyTorch operators ---------------------------------------------------
+def torch_twin_step(params: Dict[str, torch.Tensor], x: torch.Tensor, g: torch.Tensor, *, gated: bool,
+                    residual: bool = True, dropout_p: float = 0.0, keep_mask: Optional[torch.Tensor] = None,
+                    autocast: bool = True, eps: float = 1e-12, device="cuda"):
+    """out, grads (oracle names) of loss = sum(out * g) computed by stock torch operators and autograd on the GPU,
+    under ``torch.autocast(bfloat16)`` when ``autocast``: the arithmetic the reference's own mixed-precision run
+    performs (cuBLAS bf16 products with fp32 accumulation, fp32 LayerNorm, every elementwise result rounded to bf16).
+    TEST-ONLY code: its distance from the fp32 oracle is the noise floor of bf16 arithmetic for these shapes, which
+    is what the kernels' distance is compared with.  Block-sparse weights are expanded to dense masked matrices."""
+    import torch.nn.functional as F
+
+    from lean_transformer_b200.blocksparse.convert import native_weight_to_dense
+
+    leaves = {k: v.to(device).clone().requires_grad_(True) for k, v in params.items() if v.is_floating_point()}
+    x = x.to(device).clone().requires_grad_(True)
+    g = g.to(device)
+    hidden = x.shape[-1]
+
+    def project(prefix, inp, out_features):
+        weight = leaves[f"{prefix}_weight"]
+        if weight.ndim == 3:
+            weight = native_weight_to_dense(weight, params[f"{prefix}_backward_indices"].to(device), out_features)
+        out = F.linear(inp, weight, leaves.get(f"{prefix}_bias"))
+        if f"{prefix}_lowrank_first" in leaves:
+            out = out + F.linear(F.linear(inp, leaves[f"{prefix}_lowrank_first"]), leaves[f"{prefix}_lowrank_second"])
+        return out
+
+    def gelu_tanh(t):  # lean_transformer/utils.py:30, one rounding per elementwise operator under autocast
+        return t * 0.5 * (1.0 + torch.tanh(0.79788456 * t * (1 + 0.044715 * t * t)))
+
+    inter = leaves["h2o_weight"].shape[1] if leaves["h2o_weight"].ndim == 2 else leaves["h2o_weight"].shape[0]
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+        ln = F.layer_norm(x, (hidden,), leaves["ln_weight"], leaves["ln_bias"], eps)
+        pre = project("i2h", ln, 2 * inter if gated else inter)
+        if gated:
+            gate, lin = pre.split(inter, dim=-1)
+            hid = gelu_tanh(gate) * lin
+        else:
+            hid = gelu_tanh(pre)
+        out = project("h2o", hid, hidden)
+        if "post_ln_weight" in leaves:
+            out = F.layer_norm(out, (hidden,), leaves["post_ln_weight"], leaves["post_ln_bias"], eps)
+        if dropout_p:
+            out = out * (keep_mask.to(device).to(out.dtype) / (1.0 - dropout_p))
+        if residual:
+            out = out + x
+    (out.float() * g.float()).sum().backward()
+    grads = {k: v.grad for k, v in leaves.items()}  # block-sparse weights: gradient in the leaf's own block format
+    grads["input"] = x.grad
+    return out.detach(), grads

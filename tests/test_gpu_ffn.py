@@ -9,29 +9,39 @@ also for the elements that cancel to ~0 (or cancel against the residual), so tho
 import pytest
 import torch
 
-from conftest import (BF16_ATOL, BF16_RTOL, FP32_ATOL, FP32_RTOL, assert_close, golden_ffn_case, load_golden)
-from helpers import make_ffn, random_params, run_step
+from conftest import (BF16_ATOL, BF16_RTOL, FP32_ATOL, FP32_RTOL, assert_close, golden_ffn_case, load_golden,
+                      record_closeness)
+from helpers import make_ffn, random_params, run_step, torch_twin_step
 from oracle import leanffn_oracle as O
 
 pytestmark = pytest.mark.gpu
 
 
-def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None, residual=None):
-    """``residual`` = (x, g) when the block adds its input: out = x + branch and grad_input = g + branch'."""
+def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None, residual=None, twin=None, label=""):
+    """``residual`` = (x, g) when the block adds its input: out = x + branch and grad_input = g + branch'.
+    ``twin`` = (out, grads) of the same step computed by stock PyTorch operators (helpers.torch_twin_step): its
+    distance from the oracle is recorded next to the kernels' (rows "twin:..." of the parity report), not asserted."""
     out_branch = dx_branch = None
     if residual is not None:
         x, g = (t.detach().double().cpu().reshape(ref_out.shape) for t in residual)
         out_branch, dx_branch = ref_out.double() - x, ref_grads["input"].double().reshape(ref_out.shape) - g
     budget = 1e-3 if rtol >= 1e-2 else 0.0  # bf16 runs: random rounding noise has tails
-    assert_close(out, ref_out, rtol, atol, "out", branch=out_branch, scale_atol=True, outlier_frac=budget)
-    assert_close(grads["input"], ref_grads["input"], rtol, atol, "grad_input", branch=dx_branch, scale_atol=True,
-                 outlier_frac=budget)
+    tag = f"{label}:" if label else ""
+    assert_close(out, ref_out, rtol, atol, f"{tag}out", branch=out_branch, scale_atol=True, outlier_frac=budget)
+    assert_close(grads["input"], ref_grads["input"].reshape(grads["input"].shape), rtol, atol, f"{tag}grad_input",
+                 branch=dx_branch, scale_atol=True, outlier_frac=budget)
+    if twin is not None:
+        record_closeness(twin[0].reshape(ref_out.shape), ref_out, rtol, atol, f"twin:{tag}out", branch=out_branch)
+        record_closeness(twin[1]["input"].reshape(ref_out.shape), ref_grads["input"].reshape(ref_out.shape), rtol, atol,
+                         f"twin:{tag}grad_input", branch=dx_branch)
     n = 0
     for key, ref in ref_grads.items():
         if key == "input" or ref is None:
             continue
         assert grads.get(key) is not None, f"no gradient for {key}"
-        assert_close(grads[key], ref, param_rtol or rtol, atol, f"grad_{key}", scale_atol=True, outlier_frac=budget)
+        assert_close(grads[key], ref, param_rtol or rtol, atol, f"{tag}grad_{key}", scale_atol=True, outlier_frac=budget)
+        if twin is not None and twin[1].get(key) is not None:
+            record_closeness(twin[1][key], ref, param_rtol or rtol, atol, f"twin:{tag}grad_{key}")
         n += 1
     return n
 
@@ -77,8 +87,12 @@ def test_fp32_mode_vs_oracle(cuda_device, hidden, inter, gated, post_ln, residua
     ref_out, ref_grads = O.leanffn_step(x.double(), g.double(), p64, **kw)
     ffn = make_ffn(params, gated=gated, residual=residual, activation=act)
     out, grads = run_step(ffn, x.view(1, tokens, hidden).to(cuda_device), g.view(1, tokens, hidden).to(cuda_device))
+    twin = None
+    if hidden == 768:  # config 1: stock fp32 PyTorch (cuBLAS fp32 products) on the same inputs, for the record
+        twin = torch_twin_step(params, x, g, gated=gated, residual=residual, autocast=False, device=cuda_device)
     _check(out.view(tokens, hidden), {k: (v.view(tokens, hidden) if k == "input" else v) for k, v in grads.items()},
-           ref_out, ref_grads, FP32_RTOL, FP32_ATOL, residual=(x, g) if residual else None)
+           ref_out, ref_grads, FP32_RTOL, FP32_ATOL, residual=(x, g) if residual else None, twin=twin,
+           label="config1" if hidden == 768 else "")
 
 
 @pytest.mark.parametrize("tokens,hidden,inter,p", [(16384, 1024, 4096, 0.1), (1000, 512, 1024, 0.0), (2048, 768, 3072, 0.0)])
@@ -98,7 +112,11 @@ def test_bf16_autocast_vs_oracle(cuda_device, tokens, hidden, inter, p):
     out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device), autocast=True)
     assert out.dtype == torch.bfloat16 and grads["input"].dtype == torch.float32
     assert grads["i2h_weight"].dtype == torch.float32
-    _check(out, grads, ref_out, ref_grads, BF16_RTOL, BF16_ATOL, residual=(x, g))
+    twin = None
+    if tokens == 16384:  # config 2: the same step by stock PyTorch under autocast(bf16), same injected mask
+        twin = torch_twin_step(params, x, g, gated=True, dropout_p=p, keep_mask=keep, device=cuda_device)
+    _check(out, grads, ref_out, ref_grads, BF16_RTOL, BF16_ATOL, residual=(x, g), twin=twin,
+           label="config2" if tokens == 16384 else "")
 
 
 def test_pure_bf16_model_vs_oracle(cuda_device):
@@ -134,6 +152,63 @@ def test_pixelfly_lowrank_ffn_vs_oracle(cuda_device, dtype):
     out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device), autocast=dtype == "autocast")
     rtol, atol = (BF16_RTOL, BF16_ATOL) if dtype == "autocast" else (FP32_RTOL, FP32_ATOL)
     assert _check(out, grads, ref_out, ref_grads, rtol, atol, residual=(x, g)) >= 10
+
+
+def _pixelfly_params(hidden, inter, block, rank, seed=0):
+    from lean_transformer_b200.blocksparse import layout as LY
+    gen = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=gen)  # noqa: E731
+    params = dict(ln_weight=1 + 0.1 * rn(hidden), ln_bias=0.1 * rn(hidden))
+    for prefix, fin, fout in (("i2h", hidden, 2 * inter), ("h2o", inter, hidden)):
+        fwd, bwd = LY.get_indices_from_layout(LY.get_blocksparse_layout(fout, fin, f"pixelfly(block_size={block})"))
+        params.update({f"{prefix}_weight": 0.02 * rn(fin, bwd.shape[1], block), f"{prefix}_bias": 0.02 * rn(fout),
+                       f"{prefix}_lowrank_first": 0.02 * rn(rank, fin), f"{prefix}_lowrank_second": 0.02 * rn(fout, rank),
+                       f"{prefix}_forward_indices": fwd, f"{prefix}_backward_indices": bwd})
+    return params, rn
+
+
+@pytest.mark.parametrize("tokens", [512, 300])
+def test_config3_real_widths_vs_oracle(cuda_device, tokens):
+    """Config 3 at its real widths: hidden 4096, intermediate 16384, both projections pixelfly block-sparse with
+    128-blocks (256 x 32 and 32 x 128 block layouts, 6 and 24 blocks per row) plus a rank-128 low-rank term, GeGLU,
+    pure bf16 module; forward and every gradient against the fp32 oracle.  512 tokens run the 256-row tiles (two
+    token sub-tiles per weight block), 300 tokens the ragged 128-row ones.  The token count is what keeps the CPU
+    oracle in seconds; widths, block tables and tile paths are those of the full configuration."""
+    hidden, inter = 4096, 16384
+    params, rn = _pixelfly_params(hidden, inter, 128, 128)
+    assert params["i2h_weight"].shape == (4096, 48, 128) and params["h2o_weight"].shape == (16384, 6, 128)
+    p_b = {k: (v.bfloat16() if v.is_floating_point() else v) for k, v in params.items()}
+    p_f = {k: (v.float() if v.is_floating_point() else v) for k, v in p_b.items()}
+    x, g = rn(tokens, hidden).bfloat16(), rn(tokens, hidden).bfloat16()
+    ref_out, ref_grads = O.leanffn_step(x.float(), g.float(), p_f, gated=True)
+    ffn = make_ffn(p_b, gated=True, dtype=torch.bfloat16)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device))
+    twin = torch_twin_step(p_f, x.float(), g.float(), gated=True, device=cuda_device) if tokens == 512 else None
+    assert _check(out, grads, ref_out, ref_grads, BF16_RTOL, BF16_ATOL, residual=(x, g), twin=twin,
+                  label=f"config3@{tokens}") >= 10
+
+
+@pytest.mark.parametrize("tokens", [512, 333])
+def test_config5_widths_vs_oracle(cuda_device, tokens):
+    """Config 5 widths (hidden 8192, intermediate 32768, GeGLU, dense, pure bf16 module): forward AND every gradient
+    against the fp32 oracle, at 512 tokens (256 x 256 tiles) and at a token count that is no multiple of any tile
+    height.  The 65 536 tokens of the full configuration only add more rows of the same computation (tokens are
+    independent, parameter gradients are sums over tokens: see the additivity test below)."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2**30:
+        pytest.skip("needs ~40 GB of free device memory")
+    hidden, inter = 8192, 32768
+    params = random_params(hidden, inter, True, seed=0)
+    p_b = {k: v.bfloat16() for k, v in params.items()}
+    p_f = {k: v.float() for k, v in p_b.items()}
+    torch.manual_seed(1)
+    x, g = torch.randn(tokens, hidden).bfloat16(), torch.randn(tokens, hidden).bfloat16()
+    ref_out, ref_grads = O.leanffn_step(x.float(), g.float(), p_f, gated=True)
+    ffn = make_ffn(p_b, gated=True, dtype=torch.bfloat16)
+    out, grads = run_step(ffn, x.to(cuda_device), g.to(cuda_device))
+    twin = torch_twin_step(p_f, x.float(), g.float(), gated=True, device=cuda_device) if tokens == 512 else None
+    assert _check(out, grads, ref_out, ref_grads, BF16_RTOL, BF16_ATOL, residual=(x, g), twin=twin,
+                  label=f"config5@{tokens}") >= 6
 
 
 # ---- behaviours the reference's own tests pin --------------------------------------------------------

@@ -425,3 +425,59 @@ def test_row_major_block_order_operator(cuda_device, bs, dtype):
     assert_close(wd.grad, ref_dw, rtol, atol, "dw", scale_atol=True)
     with pytest.raises(ValueError):
         op.forward_functional(x.detach(), torch.zeros(nnz, bs, bs, device=cuda_device, dtype=dtype))
+
+
+# ---- argument alignment and the bounded device wait ---------------------------------------------------------
+def test_views_offset_by_one_element_take_the_scalar_paths(ops, cuda_device):
+    """A C-ABI host may pass any view: a base address that is not a multiple of the vector width must give the
+    same numbers through element-wise loads (column sum, LayerNorm forward) or a clean error code, never a
+    misaligned-address fault."""
+    from lean_transformer_b200 import _native as N
+    torch.manual_seed(3)
+    for dtype in (torch.float32, torch.bfloat16):
+        flat = torch.randn(300 * 64 + 8, device=cuda_device).to(dtype)
+        aligned = flat[:300 * 64].view(300, 64)
+        shifted = flat[1:1 + 300 * 64].view(300, 64)  # ld % 4 == 0, base off by one element
+        assert shifted.data_ptr() % 8 != 0
+        expect = _cpu64(shifted).sum(0)
+        assert_close(ops.column_sum(shifted), expect, 1e-5, 1e-4, f"column sum of a shifted view ({dtype})")
+        assert_close(ops.column_sum(aligned), _cpu64(aligned).sum(0), 1e-5, 1e-4, "aligned view")
+        sub = aligned[:, 1:61]  # odd first column, ld 64
+        assert_close(ops.column_sum(sub), _cpu64(sub).sum(0), 1e-5, 1e-4, "column window")
+    # LayerNorm forward: a shifted (contiguous) matrix goes through the scalar kernel
+    flat = torch.randn(40 * 128 + 4, device=cuda_device)
+    x = flat[1:1 + 40 * 128].view(40, 128)
+    gamma, beta = torch.randn(128, device=cuda_device), torch.randn(128, device=cuda_device)
+    ref = O.layer_norm_forward(_cpu64(x), _cpu64(gamma), _cpu64(beta), 1e-12)
+    assert_close(ops.layer_norm_forward(x, gamma, beta, 1e-12, torch.float32), ref, FP32_RTOL, FP32_ATOL, "shifted LN")
+    # LayerNorm backward and the activations reject such pointers before launching anything
+    y = torch.empty(40, 128, device=cuda_device)
+    code = N.lib.leanffn_layer_norm_backward(x.data_ptr(), N.F32, x.data_ptr(), N.F32, None, N.F32, None, 0, y.data_ptr(),
+                                             N.F32, None, None, None, 40, 128, 1e-5, None)
+    assert code == -3 and "align" in N.status_string(code)
+    code = N.lib.leanffn_activation_forward(x.data_ptr(), y.data_ptr(), N.F32, 40, 64, 1, 0, None)
+    assert code == -3
+    torch.cuda.synchronize()
+
+
+def test_bounded_wait_runs_out_and_reports(ops, cuda_device):
+    """A device-side wait that nothing satisfies must return with a status code the host can read; the context
+    stays usable.  The probe waits ~1e5 SM clocks on an mbarrier without arrivals, through the same bounded-wait
+    and status-word code the GEMM roles use."""
+    from lean_transformer_b200 import _native as N
+    word = ops.status_word(cuda_device)
+    ops.check_device_status(cuda_device)  # clean before
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    N.check(N.lib.leanffn_selftest_wait_timeout(word.data_ptr(), 100000, stream), "selftest")
+    torch.cuda.synchronize()
+    assert int(word.item()) == 3  # LEANFFN_DEV_TIMEOUT_EPILOGUE
+    with pytest.raises(RuntimeError, match="timed out"):
+        ops.check_device_status(cuda_device)
+    ops.check_device_status(cuda_device)  # the check cleared the word
+    # a real product with a short (but sufficient) wait limit still completes, and ordinary calls work afterwards
+    a = torch.randn(512, 256, device=cuda_device).bfloat16()
+    b = torch.randn(384, 256, device=cuda_device).bfloat16()
+    out = ops.gemm(a, b)
+    ops.check_device_status(cuda_device)
+    assert_close(out, _cpu64(a) @ _cpu64(b).T, BF16_RTOL, BF16_ATOL, "gemm after the probe", scale_atol=True)
+    assert N.lib.leanffn_selftest_wait_timeout(None, 1000, stream) == -1

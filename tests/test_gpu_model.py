@@ -1,0 +1,111 @@
+"""The reference's own LeanGPT model with this package's kernels swapped in (needs a B200 and the reference mirror
+that ``oracle/build_ref.py`` makes; skipped where the mirror is absent).
+
+Pattern of the reference's tests/test_modifications.py:10-78 and tests/test_triton.py:62-97: one model, one batch,
+one seed; run it with the reference's implementation, swap, run again with every memory-saving option toggled, and
+compare logits, loss and every parameter gradient.  The model exercises the features the conversion has to keep:
+matrices shared between layer groups with per-layer adapters, rotary attention, GeGLU, gradient checkpointing, the
+``ffn_custom_grad`` switch, tied embeddings.
+"""
+import pytest
+import torch
+
+from conftest import BF16_ATOL, BF16_RTOL, FP32_ATOL, FP32_RTOL, assert_close, record_closeness
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference():
+    from oracle import ref_harness
+    ref = ref_harness.import_reference()
+    if ref is None:
+        pytest.skip("oracle/_ref has not been built (python oracle/build_ref.py on a machine with the reference)")
+    return ref
+
+
+def _tiny_gpt(ref, **overrides):
+    kw = dict(vocab_size=200, hidden_size=128, embedding_size=128, num_hidden_layers=4, num_hidden_groups=2,
+              num_attention_heads=4, intermediate_size=256, position_embedding_type="rotary", hidden_act_gated=True,
+              tie_word_embeddings=True, share_large_matrices=True, adapter_dim=8, hidden_dropout_prob=0.0)
+    kw.update(overrides)
+    return ref.gpt.LeanGPTModel(ref.gpt.LeanGPTConfig(**kw))
+
+
+def _run(model, ids, autocast=False, seed=1337):
+    model.zero_grad(set_to_none=True)
+    torch.manual_seed(seed)
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+        out = model(input_ids=ids, labels=ids)
+    out.loss.backward()
+    grads = {n: p.grad.detach().clone() for n, p in model.named_parameters() if p.grad is not None}
+    return out.logits.detach().float().clone(), float(out.loss.detach()), grads
+
+
+def _compare(got, want, rtol, atol, label, outlier_frac=0.0):
+    assert_close(got[0], want[0], rtol, atol, f"{label}:logits", scale_atol=True, outlier_frac=outlier_frac)
+    assert abs(got[1] - want[1]) <= atol + rtol * abs(want[1]), f"{label}: loss {got[1]} vs {want[1]}"
+    assert set(got[2]) == set(want[2]), f"{label}: parameters with gradients differ"
+    for name, ref_grad in want[2].items():
+        assert_close(got[2][name], ref_grad, rtol, atol, f"{label}:grad {name}", scale_atol=True,
+                     outlier_frac=outlier_frac)
+
+
+def test_tiny_gpt_swapped_ffn_matches_reference_fp32(cuda_device):
+    import lean_transformer_b200 as L
+    from lean_transformer_b200.integration import convert_model
+
+    ref = _reference()
+    torch.manual_seed(0)
+    model = _tiny_gpt(ref).to(cuda_device).train()
+    ids = torch.randint(0, 200, (3, 48), generator=torch.Generator().manual_seed(5)).to(cuda_device)
+    model.set_optimizations(ffn_custom_grad=True)
+    want = _run(model, ids)  # the reference's own kernels (stock PyTorch CUDA operators), fp32
+    convert_model(model)
+    assert sum(isinstance(m, L.LeanFFN) for m in model.modules()) == 2
+    launches = L.ops.launch_count
+    for checkpoints, custom in ((False, True), (False, False), (True, True), (2, True)):
+        model.set_optimizations(gradient_checkpointing=checkpoints, ffn_custom_grad=custom)
+        got = _run(model, ids)
+        _compare(got, want, FP32_RTOL, FP32_ATOL, f"gpt fp32 ckpt={checkpoints} custom={custom}")
+    assert L.ops.launch_count > launches, "the converted model did not launch this package's kernels"
+    L.check_device_status(cuda_device)
+
+
+def test_tiny_gpt_swapped_ffn_matches_reference_bf16(cuda_device):
+    """Same under autocast(bf16): the swapped model against the reference's fp32 run, with the reference's own
+    autocast run recorded beside it as the noise floor."""
+    from lean_transformer_b200.integration import convert_model
+
+    ref = _reference()
+    torch.manual_seed(0)
+    model = _tiny_gpt(ref).to(cuda_device).train()
+    ids = torch.randint(0, 200, (4, 64), generator=torch.Generator().manual_seed(6)).to(cuda_device)
+    want = _run(model, ids)
+    floor = _run(model, ids, autocast=True)
+    convert_model(model)
+    got = _run(model, ids, autocast=True)
+    record_closeness(floor[0], want[0], BF16_RTOL, BF16_ATOL, "twin:gpt bf16:logits")
+    for name, ref_grad in want[2].items():
+        record_closeness(floor[2][name], ref_grad, BF16_RTOL, BF16_ATOL, f"twin:gpt bf16:grad {name}")
+    _compare(got, want, BF16_RTOL, BF16_ATOL, "gpt bf16", outlier_frac=1e-3)
+
+
+def test_dropout_runs_are_consistent_across_optimizations(cuda_device):
+    """tests/test_modifications.py: with dropout 0.1 and one seed, checkpointing and the custom-gradient switch must
+    not change logits or gradients (the dropout masks are regenerated, not re-drawn)."""
+    from lean_transformer_b200.integration import convert_model
+
+    ref = _reference()
+    torch.manual_seed(0)
+    model = convert_model(_tiny_gpt(ref, hidden_dropout_prob=0.1).to(cuda_device).train())
+    ids = torch.randint(0, 200, (2, 32), generator=torch.Generator().manual_seed(7)).to(cuda_device)
+    model.set_optimizations(gradient_checkpointing=False, checkpoint_last=False, checkpoint_attention_core=False,
+                            ffn_custom_grad=False)
+    want = _run(model, ids)
+    for checkpoints, last, attn, custom in ((False, False, True, True), (True, True, False, True), (3, False, True, True)):
+        model.set_optimizations(gradient_checkpointing=checkpoints, checkpoint_last=last,
+                                checkpoint_attention_core=attn, ffn_custom_grad=custom)
+        got = _run(model, ids)
+        _compare(got, want, FP32_RTOL, FP32_ATOL, f"dropout ckpt={checkpoints} custom={custom}")
+    other = _run(model, ids, seed=4242)
+    assert not torch.allclose(other[0], want[0], rtol=1e-3, atol=1e-5), "dropout ignored the seed"
