@@ -66,6 +66,8 @@ extern "C" {
 #define LEANFFN_DEV_TIMEOUT_MMA 2
 #define LEANFFN_DEV_TIMEOUT_EPILOGUE 3
 
+/* Version of this header; leanffn_abi_version() returns the one the library was built from. */
+#define LEANFFN_ABI_VERSION 2
 int32_t leanffn_abi_version(void);
 const char* leanffn_status_string(int32_t status);
 
@@ -123,6 +125,17 @@ int32_t leanffn_activation_backward(const void* dhid, const void* pre, void* dpr
 int32_t leanffn_dropout(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t n, float p,
                         uint64_t seed, uint64_t elem_offset, const void* residual, int32_t residual_dtype,
                         void* stream);
+
+/* y = dropout(x) cast to y_dtype over a [rows, cols] matrix (contiguous), and colsum[c] = sum_r y[r, c] of the rounded
+ * values, in one pass over x: the first step of the backward, where the incoming gradient is masked with the
+ * forward's mask, cast to the compute type and summed into the output projection's bias gradient.
+ * Replaces torch.dropout at lean_transformer/ffn.py:245 followed by grad_output.sum(0) at
+ * lean_transformer/blocksparse/linear.py:293-294.  p == 0 makes it a cast + column sum.  scratch: at least
+ * leanffn_dropout_colsum_scratch_bytes(rows, cols) bytes, 16-byte aligned. */
+size_t leanffn_dropout_colsum_scratch_bytes(int64_t rows, int64_t cols);
+int32_t leanffn_dropout_colsum(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t rows, int64_t cols,
+                               float p, uint64_t seed, uint64_t elem_offset, float* colsum, void* scratch,
+                               void* stream);
 
 /* mask[i] = keep(seed, elem_offset + i) as uint8; lets a checker inject the very same mask into
  * another implementation. */
@@ -264,6 +277,13 @@ typedef struct leanffn_gemm_desc {
   /* SM clocks a warp role of the tensor-core kernel waits on a stalled peer role before it gives up and records a
    * LEANFFN_DEV_TIMEOUT_* code in status_word (0 = the default, about 2e9 clocks = one second). */
   int64_t wait_limit_cycles;
+  /* LEANFFN_EPI_GLU_BWD / LEANFFN_EPI_ACT_BWD only (may be NULL): the bias gradient of the layer in front of the
+   * activation, db = D.sum(rows) (lean_transformer/blocksparse/linear.py:293-294), rides in this epilogue.  The
+   * kernel writes fp32 partial sums, one row per 32 rows of D: colsum_partial[(r / 32) * ld_colsum + c] = sum of the
+   * stored (rounded) D[r', c] over the rows r' of that group; ceil(M / 32) rows of as many columns as D has.
+   * leanffn_column_sum over those partial rows finishes the reduction (deterministic). */
+  float* colsum_partial;
+  int64_t ld_colsum;
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);

@@ -37,6 +37,7 @@ class GemmDesc(ctypes.Structure):
         ("status_word", c_void_p), ("force_simt", c_int32), ("max_ctas", c_int32),
         ("scatter_world", c_int32), ("scatter_block_shift", c_int32), ("scatter_D", c_void_p * 8),
         ("bs_wgrad_pairs", c_int32), ("wait_limit_cycles", c_int64),
+        ("colsum_partial", c_void_p), ("ld_colsum", c_int64),
     ]
 
 
@@ -55,6 +56,9 @@ _SIGNATURES = {
                                               c_int32, c_int32, c_void_p]),
     "leanffn_dropout": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_float, c_uint64, c_uint64, c_void_p,
                                   c_int32, c_void_p]),
+    "leanffn_dropout_colsum_scratch_bytes": (c_size_t, [c_int64, c_int64]),
+    "leanffn_dropout_colsum": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_int64, c_int64, c_float, c_uint64,
+                                         c_uint64, c_void_p, c_void_p, c_void_p]),
     "leanffn_dropout_mask": (c_int32, [c_void_p, c_int64, c_float, c_uint64, c_uint64, c_void_p]),
     "leanffn_column_sum_scratch_bytes": (c_size_t, [c_int64, c_int64]),
     "leanffn_column_sum": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

@@ -169,17 +169,19 @@ def input_grad(kind, dy2d, weight, forward_indices, backward_indices, matmul_op,
 
 def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_second, forward_indices,
                          backward_indices, matmul_op, needs_input_grad, cdt, *, dgrad_epilogue=N.EPI_STORE, act=0,
-                         dgrad_aux=None, dgrad_out=None, dgrad_out2=None, bias_dtype=None, on_param_grads=None):
+                         dgrad_aux=None, dgrad_out=None, dgrad_out2=None, bias_dtype=None, on_param_grads=None,
+                         grad_bias=None):
     """Gradients of linear_forward_core in the reference's order
     (input, weight, bias, lowrank_first, lowrank_second); ``x2d`` / ``dy2d`` are in the compute dtype.
     Weight-like gradients come back in their parameter's dtype.  The input gradient may carry a fused
     activation-backward epilogue.  ``on_param_grads(weight, bias, lowrank_first, lowrank_second)``
     is called once the parameter gradients are launched and before the input gradient is, so a data-parallel
     caller can start their reduction underneath the input-gradient product; it returns the four values to hand
-    back (None for a gradient it has taken over)."""
+    back (None for a gradient it has taken over).  ``grad_bias``: the bias gradient if the caller already has it
+    (the kernel that produced ``dy2d`` can emit its column sums)."""
     kind = _kind(weight, forward_indices, backward_indices, matmul_op)
     need_x, need_w, need_b, need_l1, need_l2 = (list(needs_input_grad) + [False] * 5)[:5]
-    grad_input = grad_weight = grad_bias = grad_l1 = grad_l2 = None
+    grad_input = grad_weight = grad_l1 = grad_l2 = None
     has_lowrank = lowrank_first is not None and lowrank_second is not None
     l1 = cast_cached(lowrank_first, cdt) if has_lowrank else None
     l2 = cast_cached(lowrank_second, cdt) if has_lowrank else None
@@ -190,8 +192,11 @@ def linear_backward_core(dy2d, x2d, lowrank_hid, weight, lowrank_first, lowrank_
         grad_l2 = ops.gemm(dy2d, lowrank_hid, a_mn_major=True, b_mn_major=True, out_dtype=lowrank_second.dtype)
     if has_lowrank and need_l1:
         grad_l1 = ops.gemm(grad_lowrank_hid, x2d, a_mn_major=True, b_mn_major=True, out_dtype=lowrank_first.dtype)
-    if need_b:
+    if not need_b:
+        grad_bias = None
+    elif grad_bias is None:
         grad_bias = ops.column_sum(dy2d)
+    if need_b:
         if bias_dtype is not None and bias_dtype != torch.float32:
             grad_bias = ops.cast(grad_bias, bias_dtype)
     if need_w:

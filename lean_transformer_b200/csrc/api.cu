@@ -20,7 +20,7 @@ static inline bool pitch16(int64_t ld, int32_t dtype) { return (ld * static_cast
 
 using namespace leanffn;
 
-extern "C" int32_t leanffn_abi_version(void) { return 2; }
+extern "C" int32_t leanffn_abi_version(void) { return LEANFFN_ABI_VERSION; }
 
 extern "C" const char* leanffn_status_string(int32_t s) {
   switch (s) {
@@ -83,6 +83,12 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
       if (!aligned16(d->scatter_D[k])) return LEANFFN_ERR_ALIGN;
     }
   }
+  if (d->colsum_partial != nullptr) {
+    if (!needs_aux) return LEANFFN_ERR_UNSUPPORTED;  // activation-backward epilogues only
+    const int64_t width = epi == LEANFFN_EPI_GLU_BWD ? 2 * static_cast<int64_t>(d->N) : d->N;
+    if (d->ld_colsum < width || d->ld_colsum % 2 != 0) return LEANFFN_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(d->colsum_partial) % 8 != 0) return LEANFFN_ERR_ALIGN;
+  }
   if (d->M == 0) return LEANFFN_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -108,6 +114,8 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
   ep.scatter_world = d->scatter_world;
   ep.scatter_shift = d->scatter_block_shift;
   for (int k = 0; k < 8; ++k) ep.scatter_D[k] = k < d->scatter_world ? d->scatter_D[k] : nullptr;
+  ep.colsum = d->colsum_partial;
+  ep.ldcolsum = d->ld_colsum;
 
   // ---- fp32 operands on the tensor cores (TF32 multiplication) ---------------------------------------
   if (d->in_dtype == LEANFFN_TF32) {
@@ -322,7 +330,10 @@ extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
     plain.bias = nullptr;
     e = gemm_simt(o, plain, d->in_dtype, st);
     if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
-    return launch_act_bwd(plain.D, ldpre, d->aux, d->D, d->D2, d->d_dtype, d->M, inter, gated ? 1 : 0, d->act, st);
+    const int32_t s = launch_act_bwd(plain.D, ldpre, d->aux, d->D, d->D2, d->d_dtype, d->M, inter, gated ? 1 : 0, d->act, st);
+    if (s != LEANFFN_OK || d->colsum_partial == nullptr) return s;
+    // same contract as the tensor-core epilogue: the partial rows sum to the column sums of D (row 0 carries them all)
+    return launch_colsum_into_partials(d->D, d->d_dtype, ldpre, d->colsum_partial, d->ld_colsum, d->M, ldpre, st);
   }
 }
 

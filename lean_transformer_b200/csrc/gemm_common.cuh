@@ -28,6 +28,9 @@ struct EpiParams {
   int32_t scatter_world;
   int32_t scatter_shift;
   void* scatter_D[8];
+  // activation-backward kinds: per-32-row partial column sums of D (the bias gradient), fp32 [ceil(M/32), ldcolsum]
+  float* colsum;
+  int64_t ldcolsum;
 };
 
 __device__ __forceinline__ float load_any(const void* p, int32_t dtype, int64_t i) {
@@ -103,6 +106,9 @@ int32_t gemm_tcgen05(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& 
 // (see the header).
 cudaError_t launch_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int role, int64_t slice,
                               cudaStream_t st);
+// partial[0, :] = column sums of x [rows, cols]; partial rows 1 .. ceil(rows/32)-1 are zeroed.
+int32_t launch_colsum_into_partials(const void* x, int32_t dtype, int64_t ld, float* partial, int64_t ld_partial,
+                                    int64_t rows, int64_t cols, cudaStream_t st);
 cudaError_t launch_wait_timeout_probe(int32_t* status, long long limit, cudaStream_t st);
 // CTA-pair (cta_group::2) kernel for dense products; tile counts in p are in 256 x 256 tiles.
 int32_t gemm_tcgen05_pair(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,

@@ -17,6 +17,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "gemm_common.cuh"
 #include "ptx.cuh"
 #include "tc_epilogue.cuh"
@@ -275,12 +278,7 @@ static cudaError_t pair_launch_t(const CUtensorMap& a, const CUtensorMap& b, con
     configured[dev] = true;
   }
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  int pairs = sm_count() / 2;
-  if (p.max_ctas > 0 && pairs > p.max_ctas / 2) pairs = p.max_ctas / 2;
-  if (pairs > tiles) pairs = tiles;
-  if (pairs < 1) pairs = 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
   cfg.blockDim = dim3(pair::THREADS, 1, 1);
   cfg.dynamicSmemBytes = pair::SMEM_BYTES;
   cfg.stream = st;
@@ -291,6 +289,22 @@ static cudaError_t pair_launch_t(const CUtensorMap& a, const CUtensorMap& b, con
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // A persistent grid must be co-resident.  Clusters of two need both SMs in one GPC, so fewer pairs than
+  // SMs / 2 may fit at a time (GPCs with an odd number of usable SMs): ask the runtime once per device.
+  static int max_pairs[64] = {0};
+  if (dev >= 0 && dev < 64 && max_pairs[dev] == 0) {
+    int n = 0;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * (sm_count() / 2)), 1, 1);
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = sm_count() / 2;
+    max_pairs[dev] = n;
+    if (getenv("LEANFFN_DEBUG") != nullptr) fprintf(stderr, "leanffn: %d CTA pairs fit on device %d (%d SMs)\n", n, dev, sm_count());
+  }
+  int pairs = (dev >= 0 && dev < 64) ? max_pairs[dev] : sm_count() / 2;
+  if (pairs > sm_count() / 2) pairs = sm_count() / 2;
+  if (p.max_ctas > 0 && pairs > p.max_ctas / 2) pairs = p.max_ctas / 2;
+  if (pairs > tiles) pairs = tiles;
+  if (pairs < 1) pairs = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
   return cudaLaunchKernelEx(&cfg, kern, a, b, a2, b2, p);
 }
 

@@ -452,6 +452,25 @@ static int32_t colsum_launch(const T* x, int64_t ld, float* out, float* scratch,
   return launch_status();
 }
 
+int32_t launch_colsum_into_partials(const void* x, int32_t dtype, int64_t ld, float* partial, int64_t ld_partial,
+                                    int64_t rows, int64_t cols, cudaStream_t st) {
+  const int64_t groups = (rows + 31) / 32;
+  if (groups > 1) {
+    const cudaError_t e = cudaMemset2DAsync(partial + ld_partial, sizeof(float) * ld_partial, 0, sizeof(float) * cols,
+                                            static_cast<size_t>(groups - 1), st);
+    if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+  }
+  const dim3 grid(static_cast<unsigned>((cols + 127) / 128), 1);
+  if (dtype == LEANFFN_BF16) {
+    const int vec = (ld % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 8 == 0);
+    colsum_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ld, partial, ld_partial, rows, cols, rows, vec);
+  } else {
+    const int vec = (ld % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+    colsum_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ld, partial, ld_partial, rows, cols, rows, vec);
+  }
+  return launch_status();
+}
+
 // ---- activation forward / backward -------------------------------------------------------------
 template <typename T, bool FAST>
 __global__ void __launch_bounds__(256)
@@ -567,6 +586,76 @@ dropout_kernel(const TX* __restrict__ x, TY* __restrict__ y, const TR* __restric
     if (residual != nullptr) f += to_f32(residual[i]);
     y[i] = from_f32<TY>(f);
   }
+}
+
+// y = dropout(x) cast to TY, and partial[chunk, c] = sum over the chunk's rows of the ROUNDED y[r, c]: the incoming
+// gradient of the block is masked, cast and column-summed (bias gradient of the output projection) in one pass.
+// Block = 8 warps; a lane owns 8 consecutive columns (16-byte accesses for bf16), the warps stride over the rows of
+// the chunk; grid = (cols / 256 rounded up, chunks).  Needs cols % 8 == 0, 16-byte aligned x / y, elem_offset % 4 == 0.
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256)
+dropout_colsum_kernel(const TX* __restrict__ x, TY* __restrict__ y, float* __restrict__ partial, int64_t rows,
+                      int64_t cols, int64_t rows_per_chunk, uint32_t threshold, float keep_scale, uint64_t seed,
+                      uint64_t elem_offset) {
+  __shared__ float sm[8][264];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * 8;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_chunk;
+  const int64_t r1 = min(rows, r0 + rows_per_chunk);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c < cols) {
+    for (int64_t r = r0 + warp; r < r1; r += 8) {
+      float f[8];
+      Vec4<TX> q0, q1;
+      q0.load(x + r * cols + c);
+      q1.load(x + r * cols + c + 4);
+      float a[4], b[4];
+      q0.get(a);
+      q1.get(b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) f[j] = a[j], f[4 + j] = b[j];
+      if (threshold != 0u) {
+        const uint64_t e0 = elem_offset + static_cast<uint64_t>(r) * cols + c;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          bool keep[4];
+          dropout_keep4((e0 >> 2) + h, seed, threshold, keep);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) f[4 * h + j] = keep[j] ? f[4 * h + j] * keep_scale : 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f[j] = to_f32(from_f32<TY>(f[j]));
+        acc[j] += f[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[j] = f[j], b[j] = f[4 + j];
+      Vec4<TY> o0, o1;
+      o0.set(a);
+      o1.set(b);
+      o0.store(y + r * cols + c);
+      o1.store(y + r * cols + c + 4);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+    const int64_t cc = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (cc < cols) partial[static_cast<int64_t>(blockIdx.y) * cols + cc] = t;
+  }
+}
+
+static int64_t dropout_colsum_chunks(int64_t rows, int64_t cols) {
+  const int64_t col_blocks = (cols + 255) / 256;
+  int64_t chunks = (static_cast<int64_t>(sm_count()) * 4 + col_blocks - 1) / col_blocks;
+  const int64_t max_chunks = (rows + 15) / 16;
+  if (chunks > max_chunks) chunks = max_chunks;
+  return chunks < 1 ? 1 : chunks;
 }
 
 __global__ void __launch_bounds__(256)
@@ -954,6 +1043,56 @@ extern "C" int32_t leanffn_column_sum(const void* x, int32_t x_dtype, int64_t ld
   if (x_dtype == LEANFFN_BF16)
     return colsum_launch<bf16>(static_cast<const bf16*>(x), ld, out, static_cast<float*>(scratch), rows, cols, st);
   return colsum_launch<float>(static_cast<const float*>(x), ld, out, static_cast<float*>(scratch), rows, cols, st);
+}
+
+extern "C" size_t leanffn_dropout_colsum_scratch_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int64_t fused = dropout_colsum_chunks(rows, cols);
+  // fused path: [chunks, cols] partials + the second stage's own scratch; unfused path: the plain column sum's scratch
+  const int64_t a = fused * cols + colsum_chunks(fused, cols) * cols;
+  const int64_t b = colsum_chunks(rows, cols) * cols;
+  return sizeof(float) * static_cast<size_t>(a > b ? a : b);
+}
+
+extern "C" int32_t leanffn_dropout_colsum(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, int64_t rows,
+                                          int64_t cols, float p, uint64_t seed, uint64_t elem_offset, float* colsum,
+                                          void* scratch, void* stream) {
+  if (x == nullptr || y == nullptr || colsum == nullptr) return LEANFFN_ERR_NULL;
+  if (rows < 0 || cols <= 0) return LEANFFN_ERR_SHAPE;
+  if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return LEANFFN_ERR_DTYPE;
+  if (!(p >= 0.f && p < 1.f)) return LEANFFN_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    cudaMemsetAsync(colsum, 0, sizeof(float) * cols, st);
+    return launch_status();
+  }
+  if (scratch == nullptr) return LEANFFN_ERR_NULL;
+  const bool fused = cols % 8 == 0 && elem_offset % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(scratch) % 16 == 0;
+  if (!fused) {
+    const int32_t s = leanffn_dropout(x, x_dtype, y, y_dtype, rows * cols, p, seed, elem_offset, nullptr, 0, stream);
+    if (s != LEANFFN_OK) return s;
+    return leanffn_column_sum(y, y_dtype, cols, colsum, scratch, rows, cols, stream);
+  }
+  const uint32_t thr = p > 0.f ? dropout_threshold(p) : 0u;
+  const float ks = 1.0f / (1.0f - p);
+  const int64_t chunks = dropout_colsum_chunks(rows, cols);
+  const int64_t rpc = (rows + chunks - 1) / chunks;
+  float* partial = static_cast<float*>(scratch);
+  const dim3 grid(static_cast<unsigned>((cols + 255) / 256), static_cast<unsigned>(chunks));
+#define DC_GO(TX, TY)                                                                                              \
+  dropout_colsum_kernel<TX, TY><<<grid, 256, 0, st>>>(static_cast<const TX*>(x), static_cast<TY*>(y), partial, rows, \
+                                                      cols, rpc, thr, ks, seed, elem_offset)
+  switch (x_dtype * 2 + y_dtype) {
+    case 0: DC_GO(float, float); break;
+    case 1: DC_GO(float, bf16); break;
+    case 2: DC_GO(bf16, float); break;
+    default: DC_GO(bf16, bf16); break;
+  }
+#undef DC_GO
+  const int32_t s = launch_status();
+  if (s != LEANFFN_OK) return s;
+  return colsum_launch<float>(partial, cols, colsum, partial + chunks * cols, chunks, cols, st);
 }
 
 // ---- column sum without any allocation --------------------------------------------------------------------

@@ -153,6 +153,43 @@ __device__ __forceinline__ void load_block_transposed(uint32_t taddr, float* pat
   __syncwarp();
 }
 
+// Column sums over the 32 rows of a block.  Each lane holds, for its 8 columns ((lane % 4) * 8 .. + 7), the sum over its
+// own 4 rows of NV / 8 tensors (NV = 8 or 16 values).  The 8 lanes that share a column group differ in lane bits 2-4;
+// recursive halving over those bits (xor 16, 8, 4) leaves every lane with NV / 8 finished sums: value index
+// ((lane >> 4) & 1) * NV/2 + ((lane >> 3) & 1) * NV/4 + ((lane >> 2) & 1) * NV/8 + j.  NV - NV/8 shuffles in total.
+template <int NV>
+__device__ __forceinline__ void halve_columns(float (&v)[NV], int lane, float (&out)[NV / 8]) {
+  float a[NV / 2];
+  {
+    const bool hi = (lane & 16) != 0;
+#pragma unroll
+    for (int j = 0; j < NV / 2; ++j) {
+      const float send = hi ? v[j] : v[j + NV / 2];
+      const float keep = hi ? v[j + NV / 2] : v[j];
+      a[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+  }
+  float b[NV / 4];
+  {
+    const bool hi = (lane & 8) != 0;
+#pragma unroll
+    for (int j = 0; j < NV / 4; ++j) {
+      const float send = hi ? a[j] : a[j + NV / 4];
+      const float keep = hi ? a[j + NV / 4] : a[j];
+      b[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+  }
+  {
+    const bool hi = (lane & 4) != 0;
+#pragma unroll
+    for (int j = 0; j < NV / 8; ++j) {
+      const float send = hi ? b[j] : b[j + NV / 8];
+      const float keep = hi ? b[j + NV / 8] : b[j];
+      out[j] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+  }
+}
+
 // Activation on 8 values.  ACT >= 0: one inlined activation.  ACT < 0: the run-time switch lives in ONE
 // out-of-line copy, so rarely used activations do not bloat (and evict) the hot epilogue code.
 static __device__ __noinline__ void act_fwd8_generic(int act, float* x) {
@@ -342,11 +379,17 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
         load_bias32(ep.bias, ep.bias_dtype, col0, ep.N, bias);
         load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w);
       }
-      if (!live) continue;
+      constexpr bool IS_BWD = KIND == LEANFFN_EPI_GLU_BWD || KIND == LEANFFN_EPI_ACT_BWD;
+      constexpr int NCS = KIND == LEANFFN_EPI_GLU_BWD ? 16 : 8;
+      float cs[NCS];  // backward kinds: this lane's column sums of the ROUNDED values it stores (bias gradient)
+#pragma unroll
+      for (int q = 0; q < NCS; ++q) cs[q] = 0.f;
+      const bool want_cs = IS_BWD && ep.colsum != nullptr;  // warp-uniform
+      if (!live && !want_cs) continue;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int64_t row = row0 + 8 * i + sub_row;
-        if (row >= ep.M) continue;
+        if (row >= ep.M || !live) continue;
         float x[8];
         unpack8(w[i], x);
         if constexpr (KIND == LEANFFN_EPI_ACT_FWD) {
@@ -393,6 +436,14 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           store8(ep.D, ep.d_dtype, row * ep.ldd + col, d);
           store8(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl);
           if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, y);
+          if (want_cs) {
+            const bool rounds = ep.d_dtype == LEANFFN_BF16;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              cs[q] += rounds ? bf16_round(d[q]) : d[q];
+              cs[8 + q] += rounds ? bf16_round(dl[q]) : dl[q];
+            }
+          }
         } else if constexpr (KIND == LEANFFN_EPI_ACT_BWD) {
           float pre[8], y[8], d[8];
           unpack8(c0[i], pre);
@@ -401,6 +452,30 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           for (int q = 0; q < 8; ++q) x[q] *= d[q];
           store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
           if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, y);
+          if (want_cs) {
+            const bool rounds = ep.d_dtype == LEANFFN_BF16;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) cs[q] += rounds ? bf16_round(x[q]) : x[q];
+          }
+        }
+      }
+      if constexpr (IS_BWD) {
+        if (want_cs) {
+          // every lane takes part in the exchange (dead lanes contribute zeros); row0 is a multiple of 32
+          float fin[NCS / 8];
+          halve_columns<NCS>(cs, lane, fin);
+          if (row0 < ep.M) {
+            float* prow = ep.colsum + (row0 >> 5) * ep.ldcolsum;
+            if constexpr (KIND == LEANFFN_EPI_GLU_BWD) {
+              // value index = half * 8 + column offset: half 0 = gate columns, half 1 = linear columns
+              const int off = ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2;
+              const int64_t c = ((lane & 16) ? ep.N : 0) + col + off;
+              if (col + off < ep.N) *reinterpret_cast<float2*>(prow + c) = make_float2(fin[0], fin[1]);
+            } else {
+              const int off = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+              if (col + off < ep.N) prow[col + off] = fin[0];
+            }
+          }
         }
       }
     }

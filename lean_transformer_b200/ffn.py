@@ -283,9 +283,14 @@ class _LeanFFN(torch.autograd.Function):
 
         # backward(... -> post_norm -> dropout -> residual)
         grad_residual_2d = ops.cast(grad_output_2d, cdt) if ctx._residual else None
-        if ctx._dropout_stream is not None:
-            seed, offset = ctx._dropout_stream
-            grad_h2o_out = ops.dropout(grad_output_2d, ctx._dropout, seed, offset, out_dtype=cdt)
+        grad_h2o_bias = None
+        seed, offset = ctx._dropout_stream if ctx._dropout_stream is not None else (0, 0)
+        p_drop = ctx._dropout if ctx._dropout_stream is not None else 0.0
+        if needs[11] and not ctx._use_post_ln and (p_drop or grad_output_2d.dtype != cdt):
+            # mask + cast + column sums (the output projection's bias gradient) in one pass over the incoming gradient
+            grad_h2o_out, grad_h2o_bias = ops.dropout_colsum(grad_output_2d, p_drop, seed, offset, out_dtype=cdt)
+        elif p_drop:
+            grad_h2o_out = ops.dropout(grad_output_2d, p_drop, seed, offset, out_dtype=cdt)
         else:
             grad_h2o_out = ops.cast(grad_output_2d, cdt)
         if ctx._use_post_ln:
@@ -300,7 +305,13 @@ class _LeanFFN(torch.autograd.Function):
         need_hid = bool(needs[10] or needs[12])  # hid_act feeds the weight and first-low-rank gradients
         grad_pre = torch.empty_like(pre_activation)
         hid_act = torch.empty((tokens, inter), dtype=cdt, device=input.device) if need_hid else None
-        grad_h2o_bias = ops.column_sum(grad_h2o_out) if needs[11] else None
+        if needs[11] and grad_h2o_bias is None:
+            grad_h2o_bias = ops.column_sum(grad_h2o_out)
+        # the input projection's bias gradient (column sums of grad_pre) rides in the epilogue that produces grad_pre
+        bias1_partial = None
+        if needs[4] and cdt == torch.bfloat16 and tokens > 0:
+            bias1_partial = torch.empty(((tokens + 31) // 32, pre_activation.shape[1]), dtype=torch.float32,
+                                        device=input.device)
         grad_lowrank_hid = a2 = b2 = None
         if h2o_lowrank_first is not None:
             grad_lowrank_hid = ops.gemm(grad_h2o_out, cast_cached(h2o_lowrank_second, cdt), b_mn_major=True)
@@ -309,7 +320,9 @@ class _LeanFFN(torch.autograd.Function):
         # rematerialises hid_act, which the weight gradients below then consume
         input_grad(h2o_kind, grad_h2o_out, h2o_weight, h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op,
                    cdt, a2=a2, b2=b2, epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=act,
-                   aux=pre_activation, out=grad_pre, out2=hid_act)
+                   aux=pre_activation, out=grad_pre, out2=hid_act, colsum=bias1_partial)
+        grad_i2h_bias_ready = ops.column_sum(bias1_partial) if bias1_partial is not None else None
+        del bias1_partial
         grad_h2o_weight = grad_h2o_lowrank_first = grad_h2o_lowrank_second = None
         if needs[10]:
             grad_h2o_weight = weight_grad(h2o_kind, grad_h2o_out, hid_act, h2o_weight, h2o_forward_indices,
@@ -340,7 +353,7 @@ class _LeanFFN(torch.autograd.Function):
          grad_i2h_lowrank_second) = linear_backward_core(
             grad_pre, input_ln, i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second,
             i2h_forward_indices, i2h_backward_indices, ctx._i2h_matmul_op, i2h_needs, cdt,
-            on_param_grads=lambda w, b, l1, l2: (_offer("i2h_weight", w, i2h_weight), _offer("i2h_bias", b, i2h_bias),
+            grad_bias=grad_i2h_bias_ready, on_param_grads=lambda w, b, l1, l2: (_offer("i2h_weight", w, i2h_weight), _offer("i2h_bias", b, i2h_bias),
                                                  _offer("i2h_lowrank_first", l1, i2h_lowrank_first),
                                                  _offer("i2h_lowrank_second", l2, i2h_lowrank_second)))
         del grad_pre, input_ln

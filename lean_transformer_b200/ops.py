@@ -189,6 +189,21 @@ def dropout(x: torch.Tensor, p: float, seed: int, elem_offset: int, out_dtype: O
     return y
 
 
+def dropout_colsum(x: torch.Tensor, p: float, seed: int, elem_offset: int, out_dtype: Optional[torch.dtype] = None):
+    """(y, colsum): y = dropout(x) cast to ``out_dtype`` and the fp32 column sums of y, one pass over x."""
+    _require_cuda(x)
+    assert x.dim() == 2 and x.is_contiguous()
+    rows, cols = x.shape
+    y = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    nbytes = N.lib.leanffn_dropout_colsum_scratch_bytes(rows, cols)
+    scratch = torch.empty(max(nbytes, 4) // 4, dtype=torch.float32, device=x.device)
+    N.check(N.lib.leanffn_dropout_colsum(_ptr(x), _dt(x), _ptr(y), _dt(y), rows, cols, float(p), int(seed),
+                                         int(elem_offset), _ptr(out), _ptr(scratch), _stream(x)), "leanffn_dropout_colsum")
+    _count(3)
+    return y, out
+
+
 def dropout_mask(numel: int, p: float, seed: int, elem_offset: int, device) -> torch.Tensor:
     mask = torch.empty(numel, dtype=torch.uint8, device=device)
     _require_cuda(mask)
@@ -328,7 +343,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0,
          bs_mode: int = 0, bs_block: int = 0, bs_nnz: int = 0, bs_num_blocks: int = 0,
          bs_index: Optional[torch.Tensor] = None, bs_count: Optional[torch.Tensor] = None,
-         force_simt: bool = False, scatter=None, bs_wgrad_pairs: bool = False) -> torch.Tensor:
+         force_simt: bool = False, scatter=None, bs_wgrad_pairs: bool = False,
+         colsum: Optional[torch.Tensor] = None) -> torch.Tensor:
     """D = A(m,k) . B(n,k) with the fused epilogues of ``leanffn_gemm`` (see include/leanffn_b200.h).
 
     Dense operands are 2-D with unit inner stride: a K-major A is [M, K], an MN-major A is [K, M];
@@ -336,11 +352,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
 
     ``scatter = (replica_addresses, block_shift)``: instead of being stored, the result is added into the replica
     of ``out`` that owns each row block (``out`` is this rank's replica; see ``scatter_world`` in the header).
+
+    ``colsum`` (activation-backward epilogues, bf16): fp32 ``[ceil(M / 32), columns of out]`` buffer that receives
+    per-32-row partial column sums of the result; ``column_sum(colsum)`` is then the bias gradient.
     """
     _require_cuda(a, b, out, bias, out2, aux, a2, b2, bs_index, bs_count)
     assert a.dim() == 2 and a.stride(1) == 1 and a.dtype == b.dtype
     if (a.dtype == torch.float32 and _fp32_tensor_cores and not force_simt and bs_mode == 0 and a2 is None
-            and scatter is None and b.dim() == 2 and b.stride(1) == 1):
+            and scatter is None and colsum is None and b.dim() == 2 and b.stride(1) == 1):
         result = _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilogue, act, out2, aux,
                                    dropout_p, seed, elem_offset)
         if result is not NotImplemented:
@@ -391,6 +410,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     d.force_simt = int(force_simt)
     d.max_ctas = _max_ctas
     d.bs_wgrad_pairs = int(bs_wgrad_pairs)
+    if colsum is not None:
+        assert colsum.dtype == torch.float32 and colsum.dim() == 2 and colsum.stride(1) == 1
+        assert colsum.shape[0] == (m + 31) // 32 and colsum.shape[1] == out.shape[-1]
+        d.colsum_partial, d.ld_colsum = _ptr(colsum), colsum.stride(0)
     if scatter is not None:
         addresses, shift = scatter
         assert 1 <= len(addresses) <= 8 and epilogue == N.EPI_STORE and bias is None and out.dim() == 2

@@ -47,7 +47,7 @@ static int close_enough(const float* got, const double* want, size_t n, double t
 int main(void) {
   enum { ROWS = 96, COLS = 200, OUT = 72 };
   uint32_t rng = 12345u;
-  if (leanffn_abi_version() != 1) return 1;
+  if (leanffn_abi_version() != LEANFFN_ABI_VERSION) return 1;
 
   float *x = malloc(sizeof(float) * ROWS * COLS), *w = malloc(sizeof(float) * OUT * COLS);
   float *gamma = malloc(sizeof(float) * COLS), *beta = malloc(sizeof(float) * COLS), *bias = malloc(sizeof(float) * OUT);

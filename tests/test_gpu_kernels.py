@@ -113,6 +113,25 @@ def test_dropout_mask_is_the_oracle_philox_mask(ops, cuda_device, p, seed, offse
                                  torch.zeros_like(x)) + res, 1e-6, 1e-6, "dropout + residual")
 
 
+@pytest.mark.parametrize("rows,cols,p,in_dtype,out_dtype", [
+    (16384, 1024, 0.1, torch.bfloat16, torch.bfloat16), (1000, 512, 0.3, torch.float32, torch.bfloat16),
+    (37, 8192, 0.0, torch.float32, torch.bfloat16), (515, 100, 0.2, torch.float32, torch.float32),
+    (64, 256, 0.5, torch.bfloat16, torch.float32), (1, 8, 0.1, torch.float32, torch.float32)])
+def test_dropout_with_column_sums(ops, cuda_device, rows, cols, p, in_dtype, out_dtype):
+    """Mask + cast + column sums in one pass equals the two separate kernels bit for bit (y) and the oracle."""
+    torch.manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device=cuda_device).to(in_dtype)
+    seed, offset = 11, 4 * 123
+    y, sums = ops.dropout_colsum(x, p, seed, offset, out_dtype=out_dtype)
+    assert torch.equal(y, ops.dropout(x, p, seed, offset, out_dtype=out_dtype))
+    keep = torch.from_numpy(O.dropout_keep_mask(rows * cols, p, seed, offset)).view(rows, cols).double()
+    ref = _cpu64(x) * keep / (1 - p)
+    assert_close(y, ref, 1e-2 if out_dtype == torch.bfloat16 else 1e-6, 1e-6, "masked values")
+    assert_close(sums, _cpu64(y).sum(0), 1e-5, 1e-3, "column sums of the rounded output")
+    y2, sums2 = ops.dropout_colsum(x, p, seed, offset + 1, out_dtype=out_dtype)  # unaligned stream offset: two kernels
+    assert_close(sums2, _cpu64(y2).sum(0), 1e-5, 1e-3, "fallback path")
+
+
 def test_dropout_rate_and_identity(ops, cuda_device):
     x = torch.ones(1 << 22, device=cuda_device)
     for p in (0.1, 0.5):
@@ -247,6 +266,21 @@ def test_gemm_fused_epilogues_bf16(ops, cuda_device, gated):
     dhid = _cpu64(dy) @ _cpu64(W2)
     assert_close(dpre, O.apply_activation_backward(dhid, _cpu64(pre), "gelu_tanh", gated), BF16_RTOL, BF16_ATOL, "dpre")
     assert torch.equal(hid2, hid)
+    # the same product also emits per-32-row partial column sums of dPre (the input projection's bias gradient):
+    # nothing else changes, and the partials add up to the column sums of the stored (rounded) result
+    dpre2, hid3 = torch.empty_like(pre), torch.empty_like(hid)
+    partial = torch.full(((T + 31) // 32, width), float("nan"), device=cuda_device)
+    ops.gemm(dy.to(cuda_device), W2.to(cuda_device), b_mn_major=True,
+             epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=0, aux=pre, out=dpre2, out2=hid3, colsum=partial)
+    assert torch.equal(dpre2, dpre) and torch.equal(hid3, hid)
+    assert not torch.isnan(partial).any()
+    assert_close(partial[3], _cpu64(dpre[96:128]).sum(0), 1e-5, 1e-4, "one group of 32 rows")
+    assert_close(ops.column_sum(partial), _cpu64(dpre).sum(0), 1e-5, 1e-3, "bias gradient from the epilogue")
+    # the SIMT path keeps the contract (all sums in the first partial row)
+    partial.fill_(float("nan"))
+    ops.gemm(dy.to(cuda_device), W2.to(cuda_device), b_mn_major=True, force_simt=True,
+             epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=0, aux=pre, out=dpre2, out2=hid3, colsum=partial)
+    assert_close(ops.column_sum(partial), _cpu64(dpre2).sum(0), 1e-5, 1e-3, "bias gradient, SIMT path")
     ops.check_device_status(cuda_device)
 
 

@@ -84,10 +84,20 @@ def test_tiny_gpt_swapped_ffn_matches_reference_bf16(cuda_device):
     floor = _run(model, ids, autocast=True)
     convert_model(model)
     got = _run(model, ids, autocast=True)
-    record_closeness(floor[0], want[0], BF16_RTOL, BF16_ATOL, "twin:gpt bf16:logits")
-    for name, ref_grad in want[2].items():
-        record_closeness(floor[2][name], ref_grad, BF16_RTOL, BF16_ATOL, f"twin:gpt bf16:grad {name}")
-    _compare(got, want, BF16_RTOL, BF16_ATOL, "gpt bf16", outlier_frac=1e-3)
+    # Through four layers the rounding noise of bf16 arithmetic compounds (the reference's own autocast run misses the
+    # single-layer bound on some tensors by 1.7x), so each tensor is judged against that run: the swapped model's
+    # rms distance from the fp32 run may be at most twice the reference-autocast run's, and no element may lie
+    # beyond 3x the single-layer bound.
+    assert abs(got[1] - want[1]) <= BF16_ATOL + BF16_RTOL * abs(want[1])
+    pairs = [("logits", got[0], floor[0], want[0])] + [(f"grad {n}", got[2][n], floor[2][n], r) for n, r in want[2].items()]
+    for name, ours, theirs, ref in pairs:
+        mine = record_closeness(ours, ref, BF16_RTOL, BF16_ATOL, f"gpt bf16:{name}")
+        record_closeness(theirs, ref, BF16_RTOL, BF16_ATOL, f"twin:gpt bf16:{name}")
+        rms = lambda t: float((t.double().cpu() - ref.double().cpu()).pow(2).mean().sqrt())  # noqa: E731
+        floor_rms = rms(theirs)
+        assert rms(ours) <= 2.0 * floor_rms + 1e-3 * max(mine["rms_ref"], 1e-6), \
+            f"{name}: rms error {rms(ours):.4g} vs {floor_rms:.4g} for the reference's own autocast run"
+        assert mine["scaled_worst"] <= 3.0, f"{name}: an element lies {mine['scaled_worst']:.2f}x beyond the bound"
 
 
 def test_dropout_runs_are_consistent_across_optimizations(cuda_device):
