@@ -67,7 +67,7 @@ extern "C" {
 #define LEANFFN_DEV_TIMEOUT_EPILOGUE 3
 
 /* Version of this header; leanffn_abi_version() returns the one the library was built from. */
-#define LEANFFN_ABI_VERSION 2
+#define LEANFFN_ABI_VERSION 3
 int32_t leanffn_abi_version(void);
 const char* leanffn_status_string(int32_t status);
 
@@ -284,9 +284,110 @@ typedef struct leanffn_gemm_desc {
    * leanffn_column_sum over those partial rows finishes the reduction (deterministic). */
   float* colsum_partial;
   int64_t ld_colsum;
+  /* Optional (NULL = off): a timer made by leanffn_timer_create.  The call then records a CUDA event pair around its
+   * kernel on `stream` and books the launch's algorithmic FLOPs (2 * M * N * (K_effective + K2)) with it. */
+  void* timer;
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
+
+/* ---- timing of GEMM launches ---------------------------------------------------------------------- */
+
+/* A timer owns `capacity` CUDA event pairs (created here, once: nothing is allocated while it is in use).  Every
+ * leanffn_gemm call whose descriptor names the timer (directly, or through leanffn_ffn_desc.timer) records one pair
+ * around its kernel on the launching stream and notes the launch's algorithmic FLOPs; launches beyond the capacity
+ * are counted but not timed.  leanffn_timer_summary synchronises on the recorded events and returns the sums over the
+ * timed launches; leanffn_timer_reset forgets them.  One timer serves one device and one host thread at a time.
+ * No counterpart in the reference (it times with torch.profiler from outside). */
+int32_t leanffn_timer_create(int32_t capacity, void** timer);
+int32_t leanffn_timer_reset(void* timer);
+int32_t leanffn_timer_summary(void* timer, double* flops, double* seconds, int32_t* timed_launches,
+                              int32_t* dropped_launches);
+int32_t leanffn_timer_destroy(void* timer);
+
+/* ---- the whole block in one call ---------------------------------------------------------------------- */
+
+/* One projection of the block (lean_transformer/blocksparse/linear.py:19-149): a dense [out, in] weight, or an
+ * array of bs_block x bs_block weight blocks with the three pair tables of leanffn_gemm (forward / dgrad / wgrad;
+ * see bs_mode above), plus an optional low-rank pair and bias.  Weights and low-rank factors are given in the
+ * compute type (bf16); masters kept in fp32 are converted by the caller. */
+typedef struct leanffn_linear_desc {
+  const void* weight;
+  const void* bias; /* [out] or NULL */
+  int32_t bias_dtype;
+  int32_t rank;               /* 0: no low-rank term; else a multiple of 8 */
+  const void* lowrank_first;  /* [rank, in]  */
+  const void* lowrank_second; /* [out, rank] */
+  int32_t bs_block;           /* 0: dense */
+  int32_t bs_num_blocks;
+  const int32_t* fwd_index;
+  const int32_t* fwd_count; /* may be NULL */
+  int32_t fwd_nnz;
+  int32_t dgrad_nnz;
+  const int32_t* dgrad_index;
+  const int32_t* dgrad_count; /* may be NULL */
+  const int32_t* wgrad_index;
+  int32_t wgrad_pairs;        /* see leanffn_gemm_desc.bs_wgrad_pairs */
+  int32_t fuse_gated_forward; /* block-sparse input projection of a gated block: the caller guarantees what
+                                 LEANFFN_EPI_GLU_FWD asks of the forward table (gate / linear rows pair up) */
+} leanffn_linear_desc;
+
+/* The block: lean_transformer/ffn.py:35-64 (module) and :148-175 (the autograd function's arguments).
+ * Compute type bf16 (fp32 accumulation); the residual stream x / grad_input is io_dtype (fp32 or bf16); LayerNorm
+ * parameters and all parameter gradients are param_dtype (fp32 masters under autocast, or bf16), bias gradients and
+ * LayerNorm gradients always fp32.  Without the post-LayerNorm option (post_layer_norm=True is driven piecewise). */
+typedef struct leanffn_ffn_desc {
+  int64_t tokens;
+  int32_t hidden, intermediate;
+  int32_t gated, act, residual;
+  int32_t compute_dtype;  /* LEANFFN_BF16 */
+  int32_t io_dtype;       /* x, grad_input */
+  int32_t grad_out_dtype; /* the gradient arriving at the block's output */
+  int32_t param_dtype;    /* ln_weight / ln_bias, weight-like gradients */
+  float eps;
+  float dropout_p;        /* 0: no dropout (evaluation, or p = 0) */
+  uint64_t seed, elem_offset;
+  const void* ln_weight; /* may be NULL (ones) */
+  const void* ln_bias;   /* may be NULL (zeros) */
+  leanffn_linear_desc i2h, h2o;
+  int32_t* status_word; /* see leanffn_gemm_desc */
+  int32_t max_ctas;
+  void* timer;          /* see leanffn_gemm_desc */
+} leanffn_ffn_desc;
+
+/* Where the backward puts each gradient; NULL = not needed (the work is skipped where that is possible).
+ * Weight-like gradients have the weight's own shape and storage order in param_dtype; bias and LayerNorm
+ * gradients are fp32 vectors (grad_ln_weight and grad_ln_bias come together or not at all). */
+typedef struct leanffn_ffn_grads {
+  void* grad_input;
+  float* grad_ln_weight;
+  float* grad_ln_bias;
+  void* grad_i2h_weight;
+  float* grad_i2h_bias;
+  void* grad_i2h_lowrank_first;
+  void* grad_i2h_lowrank_second;
+  void* grad_h2o_weight;
+  float* grad_h2o_bias;
+  void* grad_h2o_lowrank_first;
+  void* grad_h2o_lowrank_second;
+} leanffn_ffn_grads;
+
+/* Bytes of workspace leanffn_ffn_forward (backward == 0) or leanffn_ffn_backward (backward != 0) needs for this
+ * descriptor; 0 for a descriptor the calls would reject.  The workspace must be 256-byte aligned. */
+size_t leanffn_ffn_workspace_bytes(const leanffn_ffn_desc* desc, int32_t backward);
+
+/* out = [x +] dropout(act(LN(x) . W1^T + b1) . W2^T + b2), the forward of lean_transformer/ffn.py:146-217.
+ * x [tokens, hidden] io_dtype; out [tokens, hidden] bf16; pre_activation [tokens, intermediate * (1 + gated)] bf16 is
+ * written for the backward (with x it is all the backward needs: ffn.py:209-216), as are the low-rank hidden states
+ * [tokens, rank] bf16 of projections that have a low-rank term (NULL otherwise). */
+int32_t leanffn_ffn_forward(const leanffn_ffn_desc* desc, const void* x, void* out, void* pre_activation,
+                            void* i2h_lowrank_hid, void* h2o_lowrank_hid, void* workspace, void* stream);
+
+/* The memory-lean backward of lean_transformer/ffn.py:220-306: the dropout mask is regenerated from (seed,
+ * elem_offset), the activation and the LayerNorm output are rematerialised from pre_activation and x. */
+int32_t leanffn_ffn_backward(const leanffn_ffn_desc* desc, const void* grad_out, const void* x,
+                             const void* pre_activation, const void* i2h_lowrank_hid, const void* h2o_lowrank_hid,
+                             const leanffn_ffn_grads* grads, void* workspace, void* stream);
 
 /* Self-test of the bounded device-side wait: launches one warp whose thread 0 waits, for at most limit_cycles SM
  * clocks (clamped to [1000, 10000000]), on an mbarrier that nothing ever arrives at.  The wait gives up, the kernel

@@ -13,6 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
 
 # element types / activations / epilogues: keep in sync with include/leanffn_b200.h
 F32, BF16, TF32 = 0, 1, 2
+ABI_VERSION = 3
 ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_TANH, ACT_SIGMOID, ACT_IDENTITY = range(7)
 EPI_STORE, EPI_GLU_FWD, EPI_ACT_FWD, EPI_DROPOUT_RESIDUAL, EPI_GLU_BWD, EPI_ACT_BWD = range(6)
 DEV_STATUS_NAMES = {0: "ok", 1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out"}
@@ -37,8 +38,44 @@ class GemmDesc(ctypes.Structure):
         ("status_word", c_void_p), ("force_simt", c_int32), ("max_ctas", c_int32),
         ("scatter_world", c_int32), ("scatter_block_shift", c_int32), ("scatter_D", c_void_p * 8),
         ("bs_wgrad_pairs", c_int32), ("wait_limit_cycles", c_int64),
-        ("colsum_partial", c_void_p), ("ld_colsum", c_int64),
+        ("colsum_partial", c_void_p), ("ld_colsum", c_int64), ("timer", c_void_p),
     ]
+
+
+class LinearDesc(ctypes.Structure):
+    """Mirror of ``leanffn_linear_desc``."""
+
+    _fields_ = [
+        ("weight", c_void_p), ("bias", c_void_p), ("bias_dtype", c_int32), ("rank", c_int32),
+        ("lowrank_first", c_void_p), ("lowrank_second", c_void_p),
+        ("bs_block", c_int32), ("bs_num_blocks", c_int32),
+        ("fwd_index", c_void_p), ("fwd_count", c_void_p), ("fwd_nnz", c_int32), ("dgrad_nnz", c_int32),
+        ("dgrad_index", c_void_p), ("dgrad_count", c_void_p), ("wgrad_index", c_void_p),
+        ("wgrad_pairs", c_int32), ("fuse_gated_forward", c_int32),
+    ]
+
+
+class FfnDesc(ctypes.Structure):
+    """Mirror of ``leanffn_ffn_desc``."""
+
+    _fields_ = [
+        ("tokens", c_int64), ("hidden", c_int32), ("intermediate", c_int32),
+        ("gated", c_int32), ("act", c_int32), ("residual", c_int32),
+        ("compute_dtype", c_int32), ("io_dtype", c_int32), ("grad_out_dtype", c_int32), ("param_dtype", c_int32),
+        ("eps", c_float), ("dropout_p", c_float), ("seed", c_uint64), ("elem_offset", c_uint64),
+        ("ln_weight", c_void_p), ("ln_bias", c_void_p),
+        ("i2h", LinearDesc), ("h2o", LinearDesc),
+        ("status_word", c_void_p), ("max_ctas", c_int32), ("timer", c_void_p),
+    ]
+
+
+class FfnGrads(ctypes.Structure):
+    """Mirror of ``leanffn_ffn_grads``."""
+
+    _fields_ = [(name, c_void_p) for name in (
+        "grad_input", "grad_ln_weight", "grad_ln_bias", "grad_i2h_weight", "grad_i2h_bias", "grad_i2h_lowrank_first",
+        "grad_i2h_lowrank_second", "grad_h2o_weight", "grad_h2o_bias", "grad_h2o_lowrank_first",
+        "grad_h2o_lowrank_second")]
 
 
 _SIGNATURES = {
@@ -70,6 +107,16 @@ _SIGNATURES = {
     "leanffn_split_tf32": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
     "leanffn_selftest_wait_timeout": (c_int32, [c_void_p, c_int64, c_void_p]),
+    "leanffn_timer_create": (c_int32, [c_int32, POINTER(c_void_p)]),
+    "leanffn_timer_reset": (c_int32, [c_void_p]),
+    "leanffn_timer_summary": (c_int32, [c_void_p, POINTER(ctypes.c_double), POINTER(ctypes.c_double), POINTER(c_int32),
+                                        POINTER(c_int32)]),
+    "leanffn_timer_destroy": (c_int32, [c_void_p]),
+    "leanffn_ffn_workspace_bytes": (c_size_t, [POINTER(FfnDesc), c_int32]),
+    "leanffn_ffn_forward": (c_int32, [POINTER(FfnDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p]),
+    "leanffn_ffn_backward": (c_int32, [POINTER(FfnDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       POINTER(FfnGrads), c_void_p, c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
@@ -96,7 +143,7 @@ def _load():
             raise NativeLibraryError(f"{LIB_PATH} does not export {name}") from e
         fn.restype = restype
         fn.argtypes = argtypes
-    if lib.leanffn_abi_version() != 2:
+    if lib.leanffn_abi_version() != ABI_VERSION:
         raise NativeLibraryError("libleanffn_b200.so has an unexpected ABI version; rebuild it")
     return lib
 

@@ -9,6 +9,7 @@
 #include <cstring>
 
 #include "gemm_common.cuh"
+#include "nvtx_range.cuh"
 
 namespace leanffn {
 
@@ -38,7 +39,104 @@ extern "C" const char* leanffn_status_string(int32_t s) {
   return "unknown status";
 }
 
+// ---- timing of GEMM launches ------------------------------------------------------------------------------
+namespace {
+struct GemmTimer {
+  int32_t capacity;
+  int32_t timed;
+  int32_t dropped;
+  cudaEvent_t* events;  // 2 per slot
+  double* flops;
+};
+}  // namespace
+
+extern "C" int32_t leanffn_timer_create(int32_t capacity, void** timer) {
+  if (timer == nullptr) return LEANFFN_ERR_NULL;
+  if (capacity <= 0 || capacity > (1 << 20)) return LEANFFN_ERR_SHAPE;
+  GemmTimer* t = new GemmTimer{capacity, 0, 0, new cudaEvent_t[2 * static_cast<size_t>(capacity)], new double[capacity]};
+  for (int32_t i = 0; i < 2 * capacity; ++i) {
+    const cudaError_t e = cudaEventCreate(&t->events[i]);
+    if (e != cudaSuccess) {
+      for (int32_t j = 0; j < i; ++j) cudaEventDestroy(t->events[j]);
+      delete[] t->events;
+      delete[] t->flops;
+      delete t;
+      return 1000 + static_cast<int32_t>(e);
+    }
+  }
+  *timer = t;
+  return LEANFFN_OK;
+}
+
+extern "C" int32_t leanffn_timer_reset(void* timer) {
+  if (timer == nullptr) return LEANFFN_ERR_NULL;
+  GemmTimer* t = static_cast<GemmTimer*>(timer);
+  t->timed = t->dropped = 0;
+  return LEANFFN_OK;
+}
+
+extern "C" int32_t leanffn_timer_summary(void* timer, double* flops, double* seconds, int32_t* timed_launches,
+                                         int32_t* dropped_launches) {
+  if (timer == nullptr) return LEANFFN_ERR_NULL;
+  GemmTimer* t = static_cast<GemmTimer*>(timer);
+  double f = 0.0, s = 0.0;
+  for (int32_t i = 0; i < t->timed; ++i) {
+    cudaError_t e = cudaEventSynchronize(t->events[2 * i + 1]);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, t->events[2 * i], t->events[2 * i + 1]);
+    if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+    f += t->flops[i];
+    s += 1e-3 * static_cast<double>(ms);
+  }
+  if (flops != nullptr) *flops = f;
+  if (seconds != nullptr) *seconds = s;
+  if (timed_launches != nullptr) *timed_launches = t->timed;
+  if (dropped_launches != nullptr) *dropped_launches = t->dropped;
+  return LEANFFN_OK;
+}
+
+extern "C" int32_t leanffn_timer_destroy(void* timer) {
+  if (timer == nullptr) return LEANFFN_OK;
+  GemmTimer* t = static_cast<GemmTimer*>(timer);
+  for (int32_t i = 0; i < 2 * t->capacity; ++i) cudaEventDestroy(t->events[i]);
+  delete[] t->events;
+  delete[] t->flops;
+  delete t;
+  return LEANFFN_OK;
+}
+
+static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream);
+
 extern "C" int32_t leanffn_gemm(const leanffn_gemm_desc* d, void* stream) {
+  if (d == nullptr) return LEANFFN_ERR_NULL;
+  static const char* const kNames[6] = {"leanffn_gemm store", "leanffn_gemm glu_fwd", "leanffn_gemm act_fwd",
+                                        "leanffn_gemm dropout_residual", "leanffn_gemm glu_bwd", "leanffn_gemm act_bwd"};
+  NvtxRange range(d->epilogue >= 0 && d->epilogue < 6 ? kNames[d->epilogue] : "leanffn_gemm");
+  GemmTimer* t = static_cast<GemmTimer*>(d->timer);
+  int32_t slot = -1;
+  if (t != nullptr && d->M > 0) {
+    if (t->timed < t->capacity) {
+      slot = t->timed;
+      cudaEventRecord(t->events[2 * slot], static_cast<cudaStream_t>(stream));
+    } else {
+      ++t->dropped;
+    }
+  }
+  const int32_t status = gemm_impl(d, stream);
+  if (slot >= 0) {
+    cudaEventRecord(t->events[2 * slot + 1], static_cast<cudaStream_t>(stream));
+    if (status == LEANFFN_OK) {
+      double k = d->K;
+      if (d->bs_mode == 1 || d->bs_mode == 2) k = static_cast<double>(d->bs_nnz) * d->bs_block;
+      if (d->in_dtype == LEANFFN_TF32) k /= 3.0;  // three TF32 products stand for one fp32 product
+      t->flops[slot] = 2.0 * d->M * static_cast<double>(d->N) * (k + d->K2);
+      ++t->timed;
+    }
+  }
+  return status;
+}
+
+static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
   if (d == nullptr) return LEANFFN_ERR_NULL;
   if (d->M < 0 || d->N <= 0 || d->K <= 0 || d->K2 < 0) return LEANFFN_ERR_SHAPE;
   if (d->M > 0 && (d->A == nullptr || d->B == nullptr || d->D == nullptr)) return LEANFFN_ERR_NULL;

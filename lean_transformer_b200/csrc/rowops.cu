@@ -221,46 +221,56 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc_g[i][j] = acc_b[i][j] = 0.f;
 
-  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_BLOCK; row0 < rows;
-       row0 += static_cast<int64_t>(gridDim.x) * ROWS_PER_BLOCK) {
-    const int64_t row = row0 + row_in_block;
-    const bool row_ok = row < rows;
+  // One row's operands in registers.  Variants with few values per thread keep TWO rows: the loads of the next row are issued
+  // before the reductions of the current one, which doubles the bytes each thread has in flight (the kernel is a
+  // chain of dependent block reductions per row, so nothing else hides the memory latency).
+  struct RowData {
     float v[VPT][4], d[VPT][4];
     Vec4<TR> res[VPT];  // residual gradient, requested together with x and dy (one memory round trip per row)
-    float s = 0.f;
-    {
-      // the row this thread visits next goes to L2 now: a block works on one row at a time, so nothing else
-      // hides the DRAM latency of its loads
-      const int64_t next = row + static_cast<int64_t>(gridDim.x) * ROWS_PER_BLOCK;
-      if (next < rows) {
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-          const int c = (t_in_row + i * 32 * WPR) * 4;
-          if (c < cols) {
-            prefetch_l2(x + next * cols + c);
-            prefetch_l2(dy + next * cols + c);
-            if (dres != nullptr && dx != nullptr) prefetch_l2(dres + next * cols + c);
-          }
-        }
-      }
-    }
+  };
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * ROWS_PER_BLOCK;
+  const bool use_res = dres != nullptr && dx != nullptr;
+  auto load_row = [&](RowData& r, int64_t row0) {
+    const int64_t row = row0 + row_in_block;
+    const bool row_ok = row < rows;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = (t_in_row + i * 32 * WPR) * 4;
       if (row_ok && c < cols) {
         Vec4<TX> q;
         q.load(x + row * cols + c);
-        q.get(v[i]);
+        q.get(r.v[i]);
         Vec4<TD> qd;
         qd.load(dy + row * cols + c);
-        qd.get(d[i]);
-        if (dres != nullptr && dx != nullptr) res[i].load(dres + row * cols + c);
+        qd.get(r.d[i]);
+        if (use_res) r.res[i].load(dres + row * cols + c);
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[i][j] = d[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) r.v[i][j] = r.d[i][j] = 0.f;
       }
-      s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
     }
+  };
+  auto prefetch_row = [&](int64_t row0) {
+    // the row this thread visits after the ones held in registers goes to L2 now
+    const int64_t next = row0 + row_in_block;
+    if (next < rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = (t_in_row + i * 32 * WPR) * 4;
+        if (c < cols) {
+          prefetch_l2(x + next * cols + c);
+          prefetch_l2(dy + next * cols + c);
+          if (use_res) prefetch_l2(dres + next * cols + c);
+        }
+      }
+    }
+  };
+  auto process_row = [&](RowData& r, int64_t row0) {
+    const int64_t row = row0 + row_in_block;
+    const bool row_ok = row < rows;
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) s += (r.v[i][0] + r.v[i][1]) + (r.v[i][2] + r.v[i][3]);
     const float mean = row_sum_pair<WPR>(s, 0.f, red, THREADS / 32, parity, row_in_block, warp_in_row, lane).x * inv_cols;
     float s2 = 0.f;
 #pragma unroll
@@ -269,7 +279,7 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
       if (c < cols) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float t = v[i][j] - mean;
+          const float t = r.v[i][j] - mean;
           s2 += t * t;
         }
       }
@@ -289,13 +299,13 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float xn = (c < cols && row_ok) ? (v[i][j] - mean) * rstd : 0.f;
-        v[i][j] = xn;
-        acc_g[i][j] += d[i][j] * xn;
-        acc_b[i][j] += d[i][j];
-        d[i][j] *= g[j];
-        sg += d[i][j];
-        sgx += d[i][j] * xn;
+        const float xn = (c < cols && row_ok) ? (r.v[i][j] - mean) * rstd : 0.f;
+        r.v[i][j] = xn;
+        acc_g[i][j] += r.d[i][j] * xn;
+        acc_b[i][j] += r.d[i][j];
+        r.d[i][j] *= g[j];
+        sg += r.d[i][j];
+        sgx += r.d[i][j] * xn;
       }
     }
     const float2 sums = row_sum_pair<WPR>(sg, sgx, red, THREADS / 32, parity, row_in_block, warp_in_row, lane);
@@ -307,18 +317,42 @@ ln_bwd_kernel(const TD* __restrict__ dy, const TX* __restrict__ x, const TP* __r
         if (row_ok && c < cols) {
           float o[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) o[j] = rstd * (d[i][j] - mg - v[i][j] * mgx);
+          for (int j = 0; j < 4; ++j) o[j] = rstd * (r.d[i][j] - mg - r.v[i][j] * mgx);
           if (dres != nullptr) {
-            float r[4];
-            res[i].get(r);
+            float rr[4];
+            r.res[i].get(rr);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] += r[j];
+            for (int j = 0; j < 4; ++j) o[j] += rr[j];
           }
           Vec4<TO> out;
           out.set(o);
           out.store(dx + row * cols + c);
         }
       }
+    }
+  };
+
+  int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_BLOCK;
+  if constexpr (VPT <= 2 && WPR <= 16) {  // 1024-thread blocks have 64 registers per thread: no room for two rows
+    RowData a, b;
+    if (row0 < rows) load_row(a, row0);
+    while (row0 < rows) {
+      if (row0 + stride < rows) load_row(b, row0 + stride);
+      prefetch_row(row0 + 2 * stride);
+      process_row(a, row0);
+      row0 += stride;
+      if (row0 >= rows) break;
+      if (row0 + stride < rows) load_row(a, row0 + stride);
+      prefetch_row(row0 + 2 * stride);
+      process_row(b, row0);
+      row0 += stride;
+    }
+  } else {
+    RowData a;
+    for (; row0 < rows; row0 += stride) {
+      prefetch_row(row0 + stride);
+      load_row(a, row0);
+      process_row(a, row0);
     }
   }
   if (part != nullptr) {

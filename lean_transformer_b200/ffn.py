@@ -14,6 +14,7 @@ are rematerialised there.  The kernel schedule in bf16 is
 Dropout masks are a pure function of (seed, offset, element index), so backward regenerates the forward's
 mask from two integers instead of restoring RNG state (reference: ffn.py:243-245, :308-321).
 """
+import os
 from typing import Optional
 
 import torch
@@ -175,6 +176,90 @@ def _projection_args(proj):
     return None, None, None, None, None
 
 
+# ---- the whole block through one C call ------------------------------------------------------------------------------
+# ``leanffn_ffn_forward`` / ``leanffn_ffn_backward`` run the schedule below inside the library (one ctypes call per
+# direction instead of one per kernel).  They cover the bf16 compute path without post-LayerNorm; everything else, and
+# any step that must interleave Python between the kernels (gradient-ready callbacks, scattered gradient exchange),
+# takes the piecewise schedule, which launches the same kernels.
+_BLOCK_CALLS = os.environ.get("LEANFFN_BLOCK_CALLS", "1") != "0"
+
+
+def set_block_calls(enabled: bool) -> bool:
+    """Switch between the one-call-per-direction schedule (default) and the piecewise one; returns the previous value."""
+    global _BLOCK_CALLS
+    previous, _BLOCK_CALLS = _BLOCK_CALLS, bool(enabled)
+    return previous
+
+
+def _fill_linear(field, weight, bias, first, second, forward_indices, backward_indices, matmul_op, cdt, gated_input,
+                 keep):
+    """Describe one projection for the C call; returns False if it cannot be described."""
+    from .blocksparse.native_backend import native_tables, weight_blocks_pair_up
+    kind = _kind(weight, forward_indices, backward_indices, matmul_op)
+    w = cast_cached(weight, cdt)
+    keep.append(w)
+    field.weight = w.data_ptr()
+    if bias is not None:
+        if bias.dtype not in (torch.float32, torch.bfloat16) or not bias.is_contiguous():
+            return False
+        field.bias, field.bias_dtype = bias.data_ptr(), ops._dt(bias)
+    if first is not None and second is not None:
+        if first.shape[0] % 8 != 0:
+            return False
+        l1, l2 = cast_cached(first, cdt), cast_cached(second, cdt)
+        keep.extend((l1, l2))
+        field.rank, field.lowrank_first, field.lowrank_second = first.shape[0], l1.data_ptr(), l2.data_ptr()
+    if kind == "dense":
+        return weight.dim() == 2
+    block = weight.shape[-1]
+    if kind == "native":
+        fwd, dgrad, wgrad = native_tables(forward_indices, backward_indices, weight.shape[1])
+        fwd_count = dgrad_count = None
+    else:
+        fwd, fwd_count, dgrad, dgrad_count, wgrad = matmul_op._tables(weight.device)
+    keep.extend((fwd, dgrad, wgrad, fwd_count, dgrad_count))
+    field.bs_block, field.bs_num_blocks = block, weight.numel() // (block * block)
+    field.fwd_index, field.fwd_nnz = fwd.data_ptr(), fwd.shape[1]
+    field.dgrad_index, field.dgrad_nnz = dgrad.data_ptr(), dgrad.shape[1]
+    field.wgrad_index = wgrad.data_ptr()
+    if fwd_count is not None:
+        field.fwd_count, field.dgrad_count = fwd_count.data_ptr(), dgrad_count.data_ptr()
+    field.wgrad_pairs = int(block == 128 and weight_blocks_pair_up(wgrad))
+    field.fuse_gated_forward = int(gated_input and can_fuse_gated_forward(weight, forward_indices, backward_indices,
+                                                                         matmul_op, cdt))
+    return True
+
+
+def _block_descriptor(input_2d, grad_dtype, ln_weight, ln_bias, i2h, h2o, act, gated, residual, ln_eps, cdt, inter):
+    """(FfnDesc, keep-alive list) for the C call, or None when the configuration needs the piecewise schedule.
+    ``i2h`` / ``h2o`` = (weight, bias, lowrank_first, lowrank_second, forward_indices, backward_indices, matmul_op)."""
+    from .blocksparse import linear as _linear
+    if not _BLOCK_CALLS or cdt != torch.bfloat16 or _grad_ready_hook is not None or _linear._weight_grad_reducer is not None:
+        return None
+    hidden = input_2d.shape[1]
+    if hidden % 8 or inter % 8 or input_2d.dtype not in (torch.float32, torch.bfloat16):
+        return None
+    params = [t for t in (ln_weight, ln_bias, i2h[0], i2h[2], i2h[3], h2o[0], h2o[2], h2o[3]) if t is not None]
+    param_dtype = i2h[0].dtype
+    if param_dtype not in (torch.float32, torch.bfloat16) or any(t.dtype != param_dtype for t in params):
+        return None
+    if input_2d.dtype == torch.float32 and param_dtype == torch.bfloat16:
+        return None
+    if ln_weight is None or ln_bias is None or not ln_weight.is_contiguous() or not ln_bias.is_contiguous():
+        return None
+    d = N.FfnDesc()
+    d.tokens, d.hidden, d.intermediate = input_2d.shape[0], hidden, inter
+    d.gated, d.act, d.residual = int(gated), act, int(residual)
+    d.compute_dtype, d.io_dtype, d.param_dtype = N.BF16, ops._dt(input_2d), N.BF16 if param_dtype == torch.bfloat16 else N.F32
+    d.grad_out_dtype = N.BF16 if grad_dtype == torch.bfloat16 else N.F32
+    d.eps = float(ln_eps)  # dropout_p / seed / elem_offset: set by the caller once it has drawn the stream position
+    d.ln_weight, d.ln_bias = ln_weight.data_ptr(), ln_bias.data_ptr()
+    keep = [ln_weight, ln_bias]
+    if not _fill_linear(d.i2h, *i2h, cdt, gated, keep) or not _fill_linear(d.h2o, *h2o, cdt, False, keep):
+        return None
+    return d, keep
+
+
 class _LeanFFN(torch.autograd.Function):
     """Autograd function for the transformer FFN with the reference's 25-argument signature."""
 
@@ -214,6 +299,38 @@ class _LeanFFN(torch.autograd.Function):
             i2h_weight, i2h_forward_indices, i2h_matmul_op)
         inter = out_features1 // 2 if gated else out_features1
 
+        use_dropout = bool(training and dropout)
+        ctx._block = None
+        if not ctx._use_post_ln and tokens > 0:
+            block = _block_descriptor(
+                input_2d, cdt, ln_weight, ln_bias,
+                (i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices, i2h_backward_indices,
+                 i2h_matmul_op),
+                (h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices, h2o_backward_indices,
+                 h2o_matmul_op), act, gated, residual, ln_eps, cdt, inter)
+            if block is not None:
+                desc, keep = block
+                seed = offset = 0
+                if use_dropout:
+                    seed, offset = next_dropout_stream(input.device, tokens * hidden, hidden)
+                    desc.dropout_p, desc.seed, desc.elem_offset = float(dropout), seed, offset
+                new = lambda *shape: torch.empty(shape, dtype=cdt, device=input.device)  # noqa: E731
+                out, pre_activation = new(tokens, hidden), new(tokens, out_features1)
+                i2h_lowrank_hid = new(tokens, desc.i2h.rank) if desc.i2h.rank else None
+                h2o_lowrank_hid = new(tokens, desc.h2o.rank) if desc.h2o.rank else None
+                fused = desc.i2h.bs_block == 0 or desc.i2h.fuse_gated_forward
+                ops.ffn_forward(desc, input_2d, out, pre_activation, i2h_lowrank_hid, h2o_lowrank_hid,
+                                launches=3 + (not fused) + bool(desc.i2h.rank) + bool(desc.h2o.rank))
+                ctx._block = True
+                ctx._dropout_stream = (seed, offset) if use_dropout else None
+                ctx.save_for_backward(
+                    input, pre_activation, ln_weight, ln_bias, None, post_ln_weight, post_ln_bias,
+                    i2h_lowrank_hid, i2h_weight, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices,
+                    i2h_backward_indices,
+                    h2o_lowrank_hid, h2o_weight, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices,
+                    h2o_backward_indices, i2h_bias, h2o_bias)
+                return out.view(*input.shape)
+
         input_ln = ops.layer_norm_forward(input_2d, ln_weight, ln_bias, ln_eps, cdt)
 
         pre_activation = torch.empty((tokens, out_features1), dtype=cdt, device=input.device)
@@ -232,7 +349,6 @@ class _LeanFFN(torch.autograd.Function):
             hid_act = ops.activation_forward(pre_activation, gated, act)
         del input_ln
 
-        use_dropout = bool(training and dropout)
         seed = offset = 0
         if use_dropout:
             seed, offset = next_dropout_stream(input.device, tokens * hidden, hidden)
@@ -280,6 +396,20 @@ class _LeanFFN(torch.autograd.Function):
         if not grad_output_2d.is_contiguous():
             grad_output_2d = grad_output_2d.contiguous()
         grad_post_ln_weight = grad_post_ln_bias = None
+
+        if getattr(ctx, "_block", None) and grad_output_2d.dtype in (torch.float32, torch.bfloat16):
+            block = _block_descriptor(
+                input_2d, grad_output_2d.dtype, ln_weight, ln_bias,
+                (i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, i2h_forward_indices, i2h_backward_indices,
+                 ctx._i2h_matmul_op),
+                (h2o_weight, h2o_bias, h2o_lowrank_first, h2o_lowrank_second, h2o_forward_indices, h2o_backward_indices,
+                 ctx._h2o_matmul_op), act, gated, ctx._residual, ctx._ln_eps, cdt,
+                pre_activation.shape[1] // 2 if gated else pre_activation.shape[1])
+            if block is not None:
+                return _LeanFFN._backward_block(ctx, block, needs, input, input_2d, grad_output_2d, pre_activation,
+                                                i2h_lowrank_hid, h2o_lowrank_hid, ln_weight, i2h_weight, i2h_bias,
+                                                i2h_lowrank_first, i2h_lowrank_second, h2o_weight, h2o_bias,
+                                                h2o_lowrank_first, h2o_lowrank_second)
 
         # backward(... -> post_norm -> dropout -> residual)
         grad_residual_2d = ops.cast(grad_output_2d, cdt) if ctx._residual else None
@@ -380,6 +510,52 @@ class _LeanFFN(torch.autograd.Function):
 
 def only_if(flag, value):
     return value if flag else None
+
+
+def _backward_block(ctx, block, needs, input, input_2d, grad_output_2d, pre_activation, i2h_lowrank_hid, h2o_lowrank_hid,
+                    ln_weight, i2h_weight, i2h_bias, i2h_lowrank_first, i2h_lowrank_second, h2o_weight, h2o_bias,
+                    h2o_lowrank_first, h2o_lowrank_second):
+    """The backward through ``leanffn_ffn_backward``: allocate the gradients autograd asked for, one C call."""
+    desc, keep = block
+    if ctx._dropout_stream is not None:
+        desc.dropout_p = float(ctx._dropout)
+        desc.seed, desc.elem_offset = ctx._dropout_stream
+    device = input.device
+    grads = N.FfnGrads()
+    out = {}
+
+    def want(flag, name, like=None, shape=None, dtype=None):
+        if not flag:
+            return None
+        t = torch.empty_like(like) if like is not None else torch.empty(shape, dtype=dtype, device=device)
+        setattr(grads, name, t.data_ptr())
+        out[name] = t
+        return t
+
+    grad_input = want(needs[0], "grad_input", shape=input_2d.shape, dtype=input.dtype)
+    grad_ln = None
+    if needs[1] or needs[2]:
+        grad_ln = torch.empty((2, input_2d.shape[1]), dtype=torch.float32, device=device)
+        grads.grad_ln_weight, grads.grad_ln_bias = grad_ln[0].data_ptr(), grad_ln[1].data_ptr()
+    g_w1 = want(needs[3], "grad_i2h_weight", like=i2h_weight)
+    g_b1 = want(needs[4] and i2h_bias is not None, "grad_i2h_bias", shape=(pre_activation.shape[1],), dtype=torch.float32)
+    g_l11 = want(needs[5] and i2h_lowrank_first is not None, "grad_i2h_lowrank_first", like=i2h_lowrank_first)
+    g_l12 = want(needs[6] and i2h_lowrank_second is not None, "grad_i2h_lowrank_second", like=i2h_lowrank_second)
+    g_w2 = want(needs[10], "grad_h2o_weight", like=h2o_weight)
+    g_b2 = want(needs[11] and h2o_bias is not None, "grad_h2o_bias", shape=(input_2d.shape[1],), dtype=torch.float32)
+    g_l21 = want(needs[12] and h2o_lowrank_first is not None, "grad_h2o_lowrank_first", like=h2o_lowrank_first)
+    g_l22 = want(needs[13] and h2o_lowrank_second is not None, "grad_h2o_lowrank_second", like=h2o_lowrank_second)
+    launches = 6 + 3 * bool(desc.i2h.rank) + 3 * bool(desc.h2o.rank) + 3 * (grad_ln is not None) + 4
+    ops.ffn_backward(desc, grad_output_2d, input_2d, pre_activation, i2h_lowrank_hid, h2o_lowrank_hid, grads, launches)
+    del keep
+    return (grad_input.view(*input.shape) if grad_input is not None else None,
+            grad_ln[0] if (grad_ln is not None and needs[1]) else None,
+            grad_ln[1] if (grad_ln is not None and needs[2]) else None,
+            g_w1, g_b1, g_l11, g_l12, None, None, None, g_w2, g_b2, g_l21, g_l22, None, None, None,
+            None, None, None, None, None, None, None, None)
+
+
+_LeanFFN._backward_block = staticmethod(_backward_block)
 
 
 def _out_features(weight, forward_indices, matmul_op):

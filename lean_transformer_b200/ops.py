@@ -25,14 +25,20 @@ def set_max_ctas(n: int):
 
 
 class GemmTimer:
-    """Records a CUDA-event pair around every GEMM launch on the launching stream, with the launch's
-    algorithmic FLOPs (2 * M * N * K_effective), so a benchmark can report the kernel's achieved rate."""
+    """Times every GEMM launch of the library while it is active (``with GemmTimer() as t: ...``): the C ABI records
+    a CUDA-event pair around each ``leanffn_gemm`` kernel on the launching stream, also for the launches made inside
+    the whole-block calls, together with the launch's algorithmic FLOPs (2 * M * N * K_effective), so a benchmark
+    can report the kernel's achieved rate.  Launches beyond ``capacity`` are counted, not timed."""
 
-    def __init__(self):
-        self.records = []
+    def __init__(self, capacity: int = 8192):
+        import ctypes
+        handle = ctypes.c_void_p()
+        N.check(N.lib.leanffn_timer_create(int(capacity), ctypes.byref(handle)), "leanffn_timer_create")
+        self.handle = handle
 
     def __enter__(self):
         global _gemm_timer
+        N.check(N.lib.leanffn_timer_reset(self.handle), "leanffn_timer_reset")
         _gemm_timer = self
         return self
 
@@ -41,10 +47,24 @@ class GemmTimer:
         _gemm_timer = None
 
     def summary(self):
-        """(total_flops, total_seconds, launches) after a device synchronisation."""
-        flops = sum(r[2] for r in self.records)
-        seconds = sum(r[0].elapsed_time(r[1]) for r in self.records) * 1e-3
-        return flops, seconds, len(self.records)
+        """(total_flops, total_seconds, launches) of the timed launches; waits for their events."""
+        import ctypes
+        flops, seconds = ctypes.c_double(), ctypes.c_double()
+        timed, dropped = ctypes.c_int32(), ctypes.c_int32()
+        N.check(N.lib.leanffn_timer_summary(self.handle, ctypes.byref(flops), ctypes.byref(seconds), ctypes.byref(timed),
+                                            ctypes.byref(dropped)), "leanffn_timer_summary")
+        self.dropped = dropped.value
+        return flops.value, seconds.value, timed.value
+
+    def __del__(self):
+        try:
+            N.lib.leanffn_timer_destroy(self.handle)
+        except Exception:
+            pass
+
+
+def _timer_handle():
+    return _gemm_timer.handle if _gemm_timer is not None else None
 
 
 
@@ -250,7 +270,11 @@ def transpose(x: torch.Tensor) -> torch.Tensor:
 # fp32 mode multiplies on the tensor cores as three TF32 products folded into one reduction axis (see
 # leanffn_split_tf32 in the header); shapes the kernel does not take (tiny, odd or strided ones) use the SIMT kernel.
 _fp32_tensor_cores = True
-_TF32_SLICE = 1024  # reduction-axis elements per launch: keeps the accumulators' truncation drift near 1e-5 relative
+# Reduction-axis elements per launch.  The tensor cores truncate their fp32 accumulator after every instruction, a bias
+# that grows with the length of the axis: 1024-element slices leave ~1e-5 of the largest entry (6x the literal
+# rtol = atol = 1e-4 bound on a few weight-gradient elements of the 4096-token fp32 configuration), 128-element
+# slices are as close to an fp64 result as exact fp32 FMA arithmetic is (measured; ~1.7x the launches' time).
+_TF32_SLICE = 128
 
 
 def set_fp32_tensor_cores(enabled: bool) -> bool:
@@ -289,7 +313,6 @@ def _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilog
     b_k = transpose(b) if b_mn_major else b
     plain = out if (out is not None and not backward_kind) else torch.empty((m, n), dtype=torch.float32, device=a.device)
     # the accumulators truncate: keep every call's reduction axis short and carry a running sum between calls
-    flops_timer = _gemm_timer
     a3 = _split_tf32(a_k, 0, _TF32_SLICE)
     b3 = _split_tf32(b_k, 1, _TF32_SLICE)
     slices = max(1, k // _TF32_SLICE)  # the last slice takes the remainder (same rule as the split kernel)
@@ -310,15 +333,9 @@ def _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilog
             d.aux, d.ldaux, d.aux_dtype = _ptr(plain), n, N.F32
         d.status_word = _ptr(status_word(a.device))
         d.max_ctas = _max_ctas
+        d.timer = _timer_handle()
         _count()
-        if flops_timer is not None:
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
-            end.record()
-            flops_timer.records.append((start, end, 2.0 * m * n * width))
-        else:
-            N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
+        N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
     if epilogue == N.EPI_STORE:
         return plain
     if epilogue == N.EPI_DROPOUT_RESIDUAL:
@@ -422,15 +439,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
             d.scatter_D[i] = int(address)
     global launch_count
     launch_count += 1
-    if _gemm_timer is not None:
-        k_eff = bs_nnz * bs_block if bs_mode in (1, 2) else k
-        flops = 2.0 * m * n * (k_eff + (d.K2 or 0))
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
-        end.record()
-        _gemm_timer.records.append((start, end, flops))
-        return out
+    d.timer = _timer_handle()
     N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
     return out
 
@@ -441,3 +450,32 @@ def copy_2d(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width_by
     handle = (stream or torch.cuda.current_stream()).cuda_stream
     N.check(N.lib.leanffn_copy_2d(int(dst_ptr), int(dst_pitch), int(src_ptr), int(src_pitch), int(width_bytes),
                                   int(height), handle), "leanffn_copy_2d")
+
+
+# ---- the whole block in one call ------------------------------------------------------------------------------------
+def ffn_workspace(desc, backward: bool, device) -> torch.Tensor:
+    nbytes = N.lib.leanffn_ffn_workspace_bytes(desc, int(backward))
+    if nbytes == 0:
+        raise RuntimeError("leanffn_ffn_workspace_bytes rejected the block descriptor")
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+
+def ffn_forward(desc, x, out, pre_activation, i2h_lowrank_hid, h2o_lowrank_hid, launches: int):
+    """``leanffn_ffn_forward`` on torch tensors; ``launches`` = kernels the call enqueues (bookkeeping only)."""
+    workspace = ffn_workspace(desc, False, x.device)
+    desc.status_word = _ptr(status_word(x.device))
+    desc.max_ctas = _max_ctas
+    desc.timer = _timer_handle()
+    N.check(N.lib.leanffn_ffn_forward(desc, _ptr(x), _ptr(out), _ptr(pre_activation), _ptr(i2h_lowrank_hid),
+                                      _ptr(h2o_lowrank_hid), _ptr(workspace), _stream(x)), "leanffn_ffn_forward")
+    _count(launches)
+
+
+def ffn_backward(desc, grad_out, x, pre_activation, i2h_lowrank_hid, h2o_lowrank_hid, grads, launches: int):
+    workspace = ffn_workspace(desc, True, x.device)
+    desc.status_word = _ptr(status_word(x.device))
+    desc.max_ctas = _max_ctas
+    desc.timer = _timer_handle()
+    N.check(N.lib.leanffn_ffn_backward(desc, _ptr(grad_out), _ptr(x), _ptr(pre_activation), _ptr(i2h_lowrank_hid),
+                                       _ptr(h2o_lowrank_hid), grads, _ptr(workspace), _stream(x)), "leanffn_ffn_backward")
+    _count(launches)

@@ -1,6 +1,9 @@
 /* A host written in plain C that drives the kernels through the C ABI alone (no Python, no torch): LayerNorm forward,
  * a GEMM with bias, the column sum with library-resident scratch, and a dropout mask, each checked against loops on
- * the host.  Built and run by tests/test_c_host.py; prints "C HOST OK" and exits 0 on success. */
+ * the host.  With a file name as its argument it also runs one whole LeanFFN step (leanffn_ffn_forward +
+ * leanffn_ffn_backward) on the case stored in that file and compares the output and every gradient with the values
+ * stored beside the inputs (tests/test_c_host.py writes the file from a golden vector the reference produced).
+ * Built and run by tests/test_c_host.py; prints "C HOST OK" and exits 0 on success. */
 #include <cuda_runtime_api.h>
 #include <math.h>
 #include <stdint.h>
@@ -44,7 +47,121 @@ static int close_enough(const float* got, const double* want, size_t n, double t
   return worst <= tol;
 }
 
-int main(void) {
+/* ---- one LeanFFN step from a flat file ----------------------------------------------------------------------------
+ * File: 10 int64 (magic 0x4C45414E, tokens, hidden, intermediate, gated, residual, seed, elem_offset, dropout in ppm,
+ * 0), then float32 arrays: x, g [T*H]; ln_w, ln_b [H]; W1 [N1*H], b1 [N1]; W2 [H*I], b2 [H]; then the expected
+ * out, grad_input [T*H]; grad ln_w, ln_b [H]; grad W1, b1, W2, b2. */
+static float* read_floats(FILE* f, size_t n) {
+  float* p = malloc(sizeof(float) * (n ? n : 1));
+  if (p != NULL && fread(p, sizeof(float), n, f) != n) {
+    free(p);
+    return NULL;
+  }
+  return p;
+}
+
+static int matches(const float* got, const float* want, size_t n, const char* what) {
+  /* The rule of the Python parity tests for bf16 products against an fp64 run: |got - want| <= 1e-2 * max(1, S) +
+   * 2e-2 * max(|want|, S) with S = rms(want); rounding noise has tails, so up to 0.1 % of the elements (at least one)
+   * may lie beyond the bound, none beyond 4 times the bound. */
+  double ss = 0.0, worst = 0.0;
+  size_t beyond = 0;
+  for (size_t i = 0; i < n; ++i) ss += (double)want[i] * want[i];
+  const double S = sqrt(ss / (n ? n : 1));
+  for (size_t i = 0; i < n; ++i) {
+    const double mag = fabs(want[i]) > S ? fabs(want[i]) : S;
+    const double ratio = fabs((double)got[i] - want[i]) / (1e-2 * (S > 1.0 ? S : 1.0) + 2e-2 * mag);
+    if (!(ratio <= worst)) worst = ratio;
+    if (!(ratio <= 1.0)) ++beyond;
+  }
+  printf("%-28s worst error / bound %.3f, %zu of %zu beyond the bound\n", what, worst, beyond, n);
+  return worst <= 4.0 && beyond <= 1 + n / 1000;
+}
+
+static int upload(void** dst, const float* src, size_t n) {
+  if (cudaMalloc(dst, sizeof(float) * (n ? n : 1)) != cudaSuccess) return 0;
+  return cudaMemcpy(*dst, src, sizeof(float) * n, cudaMemcpyHostToDevice) == cudaSuccess;
+}
+
+static int run_block_case(const char* path) {
+  FILE* f = fopen(path, "rb");
+  if (f == NULL) return 20;
+  int64_t head[10];
+  if (fread(head, sizeof(int64_t), 10, f) != 10 || head[0] != 0x4C45414E) return 21;
+  const int64_t T = head[1], H = head[2], I = head[3], gated = head[4], residual = head[5];
+  const int64_t N1 = gated ? 2 * I : I;
+  const float p_drop = (float)head[8] * 1e-6f;
+  const size_t sizes[16] = {T * H, T * H, H, H, N1 * H, N1, H * I, H, T * H, T * H, H, H, N1 * H, N1, H * I, H};
+  float* h[16];
+  for (int i = 0; i < 16; ++i)
+    if ((h[i] = read_floats(f, sizes[i])) == NULL) return 22;
+  fclose(f);
+
+  void* dev[8]; /* x, g, ln_w, ln_b, W1 (fp32), b1, W2 (fp32), b2 */
+  for (int i = 0; i < 8; ++i)
+    if (!upload(&dev[i], h[i], sizes[i])) return 23;
+  cudaStream_t stream;
+  CHECK_CUDA(cudaStreamCreate(&stream));
+  /* weights enter the block in the compute type: bf16 copies made on the device */
+  void *w1_bf16, *w2_bf16;
+  CHECK_CUDA(cudaMalloc(&w1_bf16, 2 * sizes[4]));
+  CHECK_CUDA(cudaMalloc(&w2_bf16, 2 * sizes[6]));
+  CHECK_LEAN(leanffn_cast(dev[4], LEANFFN_F32, w1_bf16, LEANFFN_BF16, (int64_t)sizes[4], stream));
+  CHECK_LEAN(leanffn_cast(dev[6], LEANFFN_F32, w2_bf16, LEANFFN_BF16, (int64_t)sizes[6], stream));
+  int32_t* status;
+  CHECK_CUDA(cudaMalloc((void**)&status, sizeof(int32_t)));
+  CHECK_CUDA(cudaMemset(status, 0, sizeof(int32_t)));
+
+  leanffn_ffn_desc d;
+  memset(&d, 0, sizeof(d));
+  d.tokens = T, d.hidden = (int32_t)H, d.intermediate = (int32_t)I;
+  d.gated = (int32_t)gated, d.act = LEANFFN_ACT_GELU_TANH, d.residual = (int32_t)residual;
+  d.compute_dtype = LEANFFN_BF16, d.io_dtype = LEANFFN_F32, d.grad_out_dtype = LEANFFN_F32, d.param_dtype = LEANFFN_F32;
+  d.eps = 1e-12f, d.dropout_p = p_drop, d.seed = (uint64_t)head[6], d.elem_offset = (uint64_t)head[7];
+  d.ln_weight = dev[2], d.ln_bias = dev[3];
+  d.i2h.weight = w1_bf16, d.i2h.bias = dev[5], d.i2h.bias_dtype = LEANFFN_F32;
+  d.h2o.weight = w2_bf16, d.h2o.bias = dev[7], d.h2o.bias_dtype = LEANFFN_F32;
+  d.status_word = status;
+
+  const size_t ws_f = leanffn_ffn_workspace_bytes(&d, 0), ws_b = leanffn_ffn_workspace_bytes(&d, 1);
+  if (ws_f == 0 || ws_b == 0) return 24;
+  void *workspace, *out_bf16, *pre;
+  CHECK_CUDA(cudaMalloc(&workspace, ws_f > ws_b ? ws_f : ws_b));
+  CHECK_CUDA(cudaMalloc(&out_bf16, 2 * sizes[0]));
+  CHECK_CUDA(cudaMalloc(&pre, 2 * (size_t)(T * N1)));
+  CHECK_LEAN(leanffn_ffn_forward(&d, dev[0], out_bf16, pre, NULL, NULL, workspace, stream));
+
+  leanffn_ffn_grads grads;
+  memset(&grads, 0, sizeof(grads));
+  void* gdev[8]; /* out (fp32 copy), grad_input, ln_w, ln_b, W1, b1, W2, b2 */
+  for (int i = 0; i < 8; ++i) CHECK_CUDA(cudaMalloc(&gdev[i], sizeof(float) * (sizes[8 + i] ? sizes[8 + i] : 1)));
+  grads.grad_input = gdev[1], grads.grad_ln_weight = gdev[2], grads.grad_ln_bias = gdev[3];
+  grads.grad_i2h_weight = gdev[4], grads.grad_i2h_bias = gdev[5];
+  grads.grad_h2o_weight = gdev[6], grads.grad_h2o_bias = gdev[7];
+  CHECK_LEAN(leanffn_ffn_backward(&d, dev[1], dev[0], pre, NULL, NULL, &grads, workspace, stream));
+  CHECK_LEAN(leanffn_cast(out_bf16, LEANFFN_BF16, gdev[0], LEANFFN_F32, (int64_t)sizes[0], stream));
+  CHECK_CUDA(cudaStreamSynchronize(stream));
+  int32_t code = -1;
+  CHECK_CUDA(cudaMemcpy(&code, status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  if (code != LEANFFN_DEV_OK) return 25;
+
+  static const char* names[8] = {"block: out", "block: grad_input", "block: grad ln weight", "block: grad ln bias",
+                                 "block: grad W1", "block: grad b1", "block: grad W2", "block: grad b2"};
+  int ok = 1;
+  for (int i = 0; i < 8; ++i) {
+    float* got = malloc(sizeof(float) * (sizes[8 + i] ? sizes[8 + i] : 1));
+    CHECK_CUDA(cudaMemcpy(got, gdev[i], sizeof(float) * sizes[8 + i], cudaMemcpyDeviceToHost));
+    ok &= matches(got, h[8 + i], sizes[8 + i], names[i]);
+    free(got);
+  }
+  /* a rejected descriptor costs nothing: no workspace, a negative code */
+  d.hidden = 31;
+  ok &= leanffn_ffn_workspace_bytes(&d, 0) == 0;
+  ok &= leanffn_ffn_forward(&d, dev[0], out_bf16, pre, NULL, NULL, workspace, stream) == LEANFFN_ERR_SHAPE;
+  return ok ? 0 : 26;
+}
+
+int main(int argc, char** argv) {
   enum { ROWS = 96, COLS = 200, OUT = 72 };
   uint32_t rng = 12345u;
   if (leanffn_abi_version() != LEANFFN_ABI_VERSION) return 1;
@@ -139,6 +256,13 @@ int main(void) {
   d.K = 0;
   ok &= leanffn_gemm(&d, stream) == LEANFFN_ERR_SHAPE;
   if (!ok) return 6;
+  if (argc > 1) {
+    const int code = run_block_case(argv[1]);
+    if (code != 0) {
+      fprintf(stderr, "whole-block step failed with code %d\n", code);
+      return code;
+    }
+  }
   printf("C HOST OK\n");
   return 0;
 }

@@ -24,17 +24,14 @@ def test_header_symbols_are_exported_and_bound():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(_native.EXPORTED_SYMBOLS) == names, "ctypes bindings and header disagree"
-    assert _native.lib.leanffn_abi_version() == 2
+    assert _native.lib.leanffn_abi_version() == _native.ABI_VERSION == 3
     assert _native.status_string(0) == "ok"
     assert "shape" in _native.status_string(-2)
 
 
-def test_descriptor_layout_matches_header():
-    """Field order of the ctypes mirror equals the field order of the C struct."""
-    from lean_transformer_b200 import _native
-
+def _struct_fields(name: str):
     text = (ROOT / "include" / "leanffn_b200.h").read_text()
-    body = text[text.index("typedef struct leanffn_gemm_desc {"):text.index("} leanffn_gemm_desc;")]
+    body = text[text.index(f"typedef struct {name} {{"):text.index(f"}} {name};")]
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
     fields = []
     for decl in body.split("{", 1)[1].split(";"):
@@ -45,8 +42,16 @@ def test_descriptor_layout_matches_header():
         first = names[0].split()[-1].lstrip("*")
         fields.append(first)
         fields.extend(n.strip().lstrip("*") for n in names[1:])
-    fields = [re.sub(r"\[\d+\]$", "", f) for f in fields]  # array members: name[8] -> name
-    assert fields == [f[0] for f in _native.GemmDesc._fields_]
+    return [re.sub(r"\[\d+\]$", "", f) for f in fields]  # array members: name[8] -> name
+
+
+def test_descriptor_layout_matches_header():
+    """Field order of every ctypes mirror equals the field order of its C struct."""
+    from lean_transformer_b200 import _native
+
+    for c_name, mirror in (("leanffn_gemm_desc", _native.GemmDesc), ("leanffn_linear_desc", _native.LinearDesc),
+                           ("leanffn_ffn_desc", _native.FfnDesc), ("leanffn_ffn_grads", _native.FfnGrads)):
+        assert _struct_fields(c_name) == [f[0] for f in mirror._fields_], c_name
 
 
 def test_argument_validation_without_gpu():
@@ -73,3 +78,31 @@ def test_cpu_tensors_are_rejected_loudly():
         ffn(torch.randn(2, 3, 32))
     with pytest.raises(RuntimeError, match="CUDA"):
         L.blocksparse.linear.GeneralizedLinear(L.GeneralizedMatrix(32, 32))(torch.randn(2, 32))
+
+
+def test_struct_sizes_and_offsets_match_a_c_compiler(tmp_path):
+    """The ctypes mirrors have the size and the member offsets a C compiler gives the header's structs."""
+    import shutil
+    import subprocess
+    from lean_transformer_b200 import _native
+
+    gcc = shutil.which("gcc") or shutil.which("cc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    structs = {"leanffn_gemm_desc": _native.GemmDesc, "leanffn_linear_desc": _native.LinearDesc,
+               "leanffn_ffn_desc": _native.FfnDesc, "leanffn_ffn_grads": _native.FfnGrads}
+    lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "leanffn_b200.h"', 'int main(void) {']
+    for c_name, mirror in structs.items():
+        lines.append(f'  printf("{c_name} %zu\\n", sizeof({c_name}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{c_name}.{field} %zu\\n", offsetof({c_name}, {field}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    got = dict(line.split() for line in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.splitlines())
+    for c_name, mirror in structs.items():
+        assert int(got[c_name]) == ctypes.sizeof(mirror), c_name
+        for field, _ in mirror._fields_:
+            assert int(got[f"{c_name}.{field}"]) == getattr(mirror, field).offset, f"{c_name}.{field}"

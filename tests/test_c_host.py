@@ -38,8 +38,30 @@ def test_c_host_compiles_and_links(tmp_path):
     assert _build_c_host(tmp_path).exists()
 
 
+def _write_block_case(path: Path, name: str = "ffn_dropout_mask"):
+    """A golden vector of the reference (gated, residual, dropout with the Philox mask) as the flat file the C host
+    reads: int64 header, then float32 inputs, parameters and expected results."""
+    import numpy as np
+    blob = np.load(ROOT / "tests" / "golden" / f"{name}.npz")
+    x = blob["x"].reshape(-1, blob["x"].shape[-1])
+    tokens, hidden = x.shape
+    inter = blob["param_h2o_weight"].shape[1]
+    head = np.array([0x4C45414E, tokens, hidden, inter, int(blob["meta_gated"]), int(blob["meta_residual"]),
+                     int(blob["meta_seed"]), int(blob["meta_offset"]), round(float(blob["meta_dropout"]) * 1e6), 0],
+                    dtype=np.int64)
+    order = ["x", "g", "param_ln_weight", "param_ln_bias", "param_i2h_weight", "param_i2h_bias", "param_h2o_weight",
+             "param_h2o_bias", "out", "grad_input", "grad_ln_weight", "grad_ln_bias", "grad_i2h_weight", "grad_i2h_bias",
+             "grad_h2o_weight", "grad_h2o_bias"]
+    with open(path, "wb") as f:
+        f.write(head.tobytes())
+        for key in order:
+            f.write(np.ascontiguousarray(blob[key], dtype=np.float32).tobytes())
+
+
 @pytest.mark.gpu
 def test_c_host_runs_the_kernels(tmp_path):
     exe = _build_c_host(tmp_path)
-    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
-    assert res.returncode == 0 and "C HOST OK" in res.stdout, res.stdout + res.stderr
+    case = tmp_path / "block_case.bin"
+    _write_block_case(case)
+    res = subprocess.run([str(exe), str(case)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "C HOST OK" in res.stdout and "block: grad W2" in res.stdout, res.stdout + res.stderr

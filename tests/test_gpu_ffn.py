@@ -25,11 +25,19 @@ def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None, residual
     if residual is not None:
         x, g = (t.detach().double().cpu().reshape(ref_out.shape) for t in residual)
         out_branch, dx_branch = ref_out.double() - x, ref_grads["input"].double().reshape(ref_out.shape) - g
-    budget = 1e-3 if rtol >= 1e-2 else 0.0  # bf16 runs: random rounding noise has tails
+    if rtol >= 1e-2:
+        # bf16: elements are judged at the scale of the sums that produced them.  Stock PyTorch bf16 arithmetic leaves
+        # up to 1e-5 of the elements beyond that bound (worst 1.6x), the kernels fewer: budget 1e-4, none beyond 2x.
+        rule = dict(scale_atol=True, outlier_frac=1e-4, outlier_cap=2.0)
+    else:
+        # fp32 mode: the literal rule |got - ref| <= 1e-4 + 1e-4 |ref|.  Exact fp32 arithmetic (this library's FMA
+        # kernel, cuBLAS fp32) still leaves about one element per million up to 1.1x beyond it against an fp64 run.
+        rule = dict(scale_atol=False, outlier_frac=1e-5, outlier_cap=1.5)
+        out_branch = dx_branch = None
     tag = f"{label}:" if label else ""
-    assert_close(out, ref_out, rtol, atol, f"{tag}out", branch=out_branch, scale_atol=True, outlier_frac=budget)
+    assert_close(out, ref_out, rtol, atol, f"{tag}out", branch=out_branch, **rule)
     assert_close(grads["input"], ref_grads["input"].reshape(grads["input"].shape), rtol, atol, f"{tag}grad_input",
-                 branch=dx_branch, scale_atol=True, outlier_frac=budget)
+                 branch=dx_branch, **rule)
     if twin is not None:
         record_closeness(twin[0].reshape(ref_out.shape), ref_out, rtol, atol, f"twin:{tag}out", branch=out_branch)
         record_closeness(twin[1]["input"].reshape(ref_out.shape), ref_grads["input"].reshape(ref_out.shape), rtol, atol,
@@ -39,7 +47,7 @@ def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None, residual
         if key == "input" or ref is None:
             continue
         assert grads.get(key) is not None, f"no gradient for {key}"
-        assert_close(grads[key], ref, param_rtol or rtol, atol, f"{tag}grad_{key}", scale_atol=True, outlier_frac=budget)
+        assert_close(grads[key], ref, param_rtol or rtol, atol, f"{tag}grad_{key}", **rule)
         if twin is not None and twin[1].get(key) is not None:
             record_closeness(twin[1][key], ref, param_rtol or rtol, atol, f"twin:{tag}grad_{key}")
         n += 1
@@ -327,6 +335,56 @@ def test_run_to_run_determinism_and_needs_input_grad(cuda_device):
     assert ffn.i2h_proj.weight.grad is None and ffn.h2o_proj.weight.grad is not None
 
 
+@pytest.mark.parametrize("case", ["dense_autocast_dropout", "dense_bf16_ungated", "pixelfly_lowrank", "rowmajor_order",
+                                  "frozen_input_projection"])
+def test_block_call_equals_piecewise_schedule(cuda_device, case):
+    """The one-call-per-direction schedule (leanffn_ffn_forward / leanffn_ffn_backward) launches the same kernels in
+    the same order as the piecewise schedule driven from Python: outputs and gradients agree bit for bit."""
+    import lean_transformer_b200 as L
+    from lean_transformer_b200 import ffn as lffn
+    from lean_transformer_b200.blocksparse.linear import GeneralizedLinear, GeneralizedMatrix
+    torch.manual_seed(11)
+    autocast, p = False, 0.0
+    if case in ("dense_autocast_dropout", "frozen_input_projection"):
+        ffn, tokens, hidden, autocast, p = make_ffn(random_params(256, 512, True, seed=1, bias_std=0.1), gated=True,
+                                                    dropout=0.2).train(), 700, 256, True, 0.2
+    elif case == "dense_bf16_ungated":
+        ffn, tokens, hidden = make_ffn({k: v.bfloat16() for k, v in random_params(128, 384, False, seed=2).items()},
+                                       gated=False, dtype=torch.bfloat16), 300, 128
+    else:
+        backend = "triton" if case == "rowmajor_order" else "native"
+        hidden, inter, tokens = 256, 512, 520
+        i2h = GeneralizedLinear(GeneralizedMatrix(hidden, 2 * inter, "pixelfly(block_size=128)", 16, backend), adapter_dim=8)
+        h2o = GeneralizedLinear(GeneralizedMatrix(inter, hidden, "pixelfly(block_size=128)", 16, backend))
+        with torch.no_grad():
+            i2h.adapter_second.normal_(0, 0.02)
+        ffn = L.LeanFFN(hidden, inter, gated=True, i2h_proj=i2h, h2o_proj=h2o).to(cuda_device).bfloat16()
+    if case == "frozen_input_projection":
+        for param in ffn.i2h_proj.parameters():
+            param.requires_grad_(False)
+    dtype = torch.bfloat16 if next(ffn.parameters()).dtype == torch.bfloat16 else torch.float32
+    x = torch.randn(tokens, hidden, device=cuda_device).to(dtype)
+    g = torch.randn(tokens, hidden, device=cuda_device).to(dtype)
+    runs = []
+    for block_calls in (True, False):
+        previous = lffn.set_block_calls(block_calls)
+        try:
+            torch.manual_seed(99)
+            launches = L.ops.launch_count
+            out, grads = run_step(ffn, x, g, autocast=autocast)
+            runs.append((out, {k: (None if v is None else v.clone()) for k, v in grads.items()}, L.ops.launch_count - launches))
+        finally:
+            lffn.set_block_calls(previous)
+    (out_a, grads_a, n_a), (out_b, grads_b, n_b) = runs
+    assert torch.equal(out_a, out_b)
+    assert set(grads_a) == set(grads_b)
+    for key in grads_a:
+        assert (grads_a[key] is None) == (grads_b[key] is None), key
+        if grads_a[key] is not None:
+            assert grads_a[key].dtype == grads_b[key].dtype and torch.equal(grads_a[key], grads_b[key]), key
+    assert n_a > 0 and n_b > 0
+
+
 def test_generalized_linear_golden_and_variants(cuda_device):
     """tests/test_linear.py: reference outputs for pixelfly(8) + shared low rank + adapter, fp32 mode."""
     from lean_transformer_b200.blocksparse.linear import GeneralizedLinear, GeneralizedMatrix, _GeneralizedLinear
@@ -381,7 +439,7 @@ def test_full_size_config5_properties(cuda_device):
     rows = torch.randperm(tokens, generator=torch.Generator().manual_seed(1))[:48]
     ref_rows, _ = O.leanffn_forward(x[rows], params, gated=True)
     assert_close(out[rows.to(cuda_device)], ref_rows, BF16_RTOL, BF16_ATOL, "sampled rows of the forward",
-                 branch=ref_rows - x[rows], scale_atol=True, outlier_frac=1e-3)
+                 branch=ref_rows - x[rows], scale_atol=True, outlier_frac=1e-4, outlier_cap=2.0)
     full = {k: v.clone() for k, v in grads.items() if k != "input"}
     halves = []
     for sl in (slice(0, tokens // 2), slice(tokens // 2, tokens)):
