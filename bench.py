@@ -14,6 +14,8 @@ One JSON line is printed by rank 0.  Workloads (synthetic data, random-init weig
                      rank-128 low-rank term, bf16, 65536 tokens per rank
   dense_fp32_h768    hidden 768, intermediate 3072, 8 x 512 tokens, fp32 end to end (the reference's CPU-runnable
                      case): products run as three TF32 tensor-core products with fp32 accuracy
+  leangpt_bf16_h768  (other_workloads only) the reference's 12-layer LeanGPT, 32 x 2048 tokens, autocast bf16, with the
+                     reference's modules and with its FFN / linear modules swapped for this package's
 """
 import argparse
 import json
@@ -396,6 +398,7 @@ def run_ours(args, wl, name):
     sums = torch.stack([(out.double().reshape(-1) * g_dev.double().reshape(-1)).sum(), dx.double().abs().sum()])
     if world > 1:
         dist.all_reduce(sums)  # partial sums over this rank's tokens -> whole batch
+    sums = sums.detach()
     checksum = dict(sum_out_dot_g=float(sums[0]), sum_abs_grad_input=float(sums[1]),
                     sum_abs_grad_i2h_weight=float(ffn.i2h_proj.weight.grad.double().abs().sum()),
                     sum_abs_grad_h2o_weight=float(ffn.h2o_proj.weight.grad.double().abs().sum()),
@@ -479,6 +482,12 @@ def run_ours(args, wl, name):
         for other in [w.strip() for w in args.extra_workload.split(",") if w.strip()]:
             if other != name and other in WORKLOADS:
                 extra[other] = quick_measure(WORKLOADS[other], device, args, other)
+            elif other == "leangpt_bf16_h768":
+                try:
+                    extra[other] = leangpt_measure(device)
+                except Exception as e:  # the mirrored reference model must not take the headline number down
+                    extra[other] = dict(unavailable=f"{type(e).__name__}: {e}")
+                torch.cuda.empty_cache()
 
     if world > 1:
         lffn.set_grad_ready_hook(None)
@@ -594,6 +603,89 @@ def quick_measure(wl, device, args, name=""):
                                         "fp32 (TF32x3 tensor cores)" if wl.get("fp32") else "bf16")))
 
 
+def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
+    """BASELINE config 4: the REFERENCE's own 12-layer LeanGPT (hidden 768, 16 heads, rotary, GeGLU, tied embeddings,
+    vocab 10 000; imported from the mirror oracle/_ref) on the GPU under autocast(bf16), forward + backward on 32 x 2048
+    random token ids with labels = ids, timed twice on the same weights: with the reference's own modules (stock
+    PyTorch CUDA operators), then with its LeanFFN / GeneralizedLinear modules swapped for this package's
+    (integration.convert_model).  Embeddings, attention core, LM head and loss stay the reference's code in both runs.
+    Also reports the time spent inside the FFN modules (CUDA events around their forward and backward)."""
+    from oracle import ref_harness
+
+    ref = ref_harness.import_reference()
+    if ref is None:
+        return dict(unavailable="the reference mirror oracle/_ref is absent (python oracle/build_ref.py builds it "
+                                "where the reference checkout exists)")
+    import lean_transformer_b200 as L
+    from lean_transformer_b200.integration import convert_model
+
+    torch.manual_seed(0)
+    config = ref.gpt.LeanGPTConfig(vocab_size=10000, hidden_size=768, num_hidden_layers=12, num_attention_heads=16,
+                                   position_embedding_type="rotary", hidden_act_gated=True, tie_word_embeddings=True)
+    model = ref.gpt.LeanGPTModel(config).to(device).train()
+    ids = torch.randint(0, 10000, (batch, seq), device=device, generator=torch.Generator(device=device).manual_seed(0))
+    params = list(model.parameters())
+    tokens = batch * seq
+
+    def ffn_modules():
+        return [m for m in model.modules() if type(m).__name__ == "LeanFFN"]
+
+    def timed(n_steps):
+        events = []
+
+        def pre(_m, *_a):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            events.append([e, None])
+
+        def post(_m, *_a):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            events[-1][1] = e
+
+        handles = []
+        for m in ffn_modules():
+            handles += [m.register_forward_pre_hook(pre), m.register_forward_hook(post),
+                        m.register_full_backward_pre_hook(pre), m.register_full_backward_hook(post)]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        losses = []
+        a.record()
+        for _ in range(n_steps):
+            for p in params:
+                p.grad = None
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = model(input_ids=ids, labels=ids).loss
+            loss.backward()
+            losses.append(loss.detach())
+        b.record()
+        torch.cuda.synchronize()
+        for h in handles:
+            h.remove()
+        ffn_ms = sum(s.elapsed_time(e) for s, e in events if e is not None) / n_steps
+        return a.elapsed_time(b) / n_steps, ffn_ms, float(losses[-1])
+
+    out = dict(config=dict(model="LeanGPT (reference lean_transformer/models/gpt.py)", layers=12, hidden=768, heads=16,
+                           intermediate=3072, gated=True, vocab=10000, batch=batch, seq_len=seq, tokens=tokens,
+                           dtype="autocast bf16, fp32 parameters", steps=steps, warmup=warmup))
+    for label in ("reference_modules", "swapped_ffn_and_linears"):
+        if label != "reference_modules":
+            convert_model(model)
+        timed(warmup)
+        launches = L.ops.launch_count
+        ms, ffn_ms, loss = timed(steps)
+        out[label] = dict(ms_per_step=ms, tokens_per_s=tokens / ms * 1e3, ffn_ms_per_step=ffn_ms,
+                          ffn_share=ffn_ms / ms, loss=loss,
+                          leanffn_b200_launches_per_step=(L.ops.launch_count - launches) / steps)
+    L.check_device_status(device)
+    ffn_flops = 12 * tokens * flops_per_token(768, 3072)
+    out["swapped_ffn_and_linears"]["ffn_tflops"] = ffn_flops / out["swapped_ffn_and_linears"]["ffn_ms_per_step"] / 1e9
+    out["reference_modules"]["ffn_tflops"] = ffn_flops / out["reference_modules"]["ffn_ms_per_step"] / 1e9
+    out["speedup_whole_step"] = out["reference_modules"]["ms_per_step"] / out["swapped_ffn_and_linears"]["ms_per_step"]
+    out["speedup_ffn_modules"] = (out["reference_modules"]["ffn_ms_per_step"]
+                                  / out["swapped_ffn_and_linears"]["ffn_ms_per_step"])
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -601,7 +693,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="dense_bf16_h8192")
-    ap.add_argument("--extra-workload", default="mixed_bf16_h1024,dense_fp32_h768,pixelfly_bf16_h4096",
+    ap.add_argument("--extra-workload", default="mixed_bf16_h1024,dense_fp32_h768,pixelfly_bf16_h4096,leangpt_bf16_h768",
                     help="comma-separated workloads measured device-resident on one GPU after the headline one and "
                          "reported under other_workloads ('' = none)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to NCCL while GEMMs run (N > 1)")

@@ -6,6 +6,9 @@ this package's drop-ins.  Parameters and buffers are re-used (the very same ``nn
 state, weight sharing between layers (``share_large_matrices``) and checkpoints keep working.  Classes are recognised
 by name, so the reference does not have to be importable here.
 
+``LeanSelfAttention`` blocks keep their own attention core module (rotary, Q.K^T, softmax, P.V are not kernels of this
+package); their LayerNorm, qkv projection and output projection + dropout + residual run on this package's kernels.
+
 Every drop-in is an instance of a class derived from BOTH this package's class and the class it replaces (this
 package's first in the method resolution order, so all behaviour is this package's).  The model's own code keeps
 recognising its modules that way: ``LeanTransformer.set_optimizations`` finds its FFNs with ``isinstance(module,
@@ -17,6 +20,7 @@ from typing import Dict, Tuple
 
 import torch.nn as nn
 
+from .attn import LeanSelfAttention
 from .blocksparse.linear import GeneralizedLinear, GeneralizedMatrix
 from .ffn import LeanFFN
 
@@ -92,17 +96,39 @@ def _convert_ffn(ref, memo: Dict[int, nn.Module]) -> LeanFFN:
     return new
 
 
+def _convert_attention(ref, memo: Dict[int, nn.Module]) -> LeanSelfAttention:
+    """The attention block shell (lean_transformer/attn.py:11-82): LayerNorm and both projections move to this
+    package's kernels, the attention core module is the model's own and is passed through untouched."""
+    if id(ref) in memo:
+        return memo[id(ref)]
+    cls = _dropin_class(LeanSelfAttention, type(ref))
+    new = cls.__new__(cls)
+    nn.Module.__init__(new)
+    new.hidden_size = ref.hidden_size
+    new.attention_core = ref.attention_core
+    new.qkv_proj = _convert_linear(ref.qkv_proj, memo)
+    new.out_proj = _convert_linear(ref.out_proj, memo)
+    new.pre_layer_norm, new.post_layer_norm = ref.pre_layer_norm, ref.post_layer_norm
+    new.output_dropout = ref.output_dropout
+    new.residual, new.checkpoint_attention_core = ref.residual, ref.checkpoint_attention_core
+    new.train(ref.training)
+    memo[id(ref)] = new
+    return new
+
+
 def _is_reference(module: nn.Module, name: str, ours: type) -> bool:
     return type(module).__name__ == name and not isinstance(module, ours)
 
 
-def convert_model(model: nn.Module, convert_linears: bool = True) -> nn.Module:
-    """Replace every reference ``LeanFFN`` (and, optionally, stand-alone ``GeneralizedLinear``) inside ``model``
-    by the CUDA drop-in.  Returns the converted model: ``model`` itself, modified in place, unless ``model`` IS a
-    reference ``LeanFFN`` / ``GeneralizedLinear``, in which case its drop-in is returned."""
+def convert_model(model: nn.Module, convert_linears: bool = True, convert_attention: bool = True) -> nn.Module:
+    """Replace every reference ``LeanFFN`` (and, optionally, ``LeanSelfAttention`` shell and stand-alone
+    ``GeneralizedLinear``) inside ``model`` by the CUDA drop-in.  Returns the converted model: ``model`` itself,
+    modified in place, unless ``model`` IS one of those modules, in which case its drop-in is returned."""
     memo: Dict[int, nn.Module] = {}
     if _is_reference(model, "LeanFFN", LeanFFN):
         return _convert_ffn(model, memo)
+    if convert_attention and _is_reference(model, "LeanSelfAttention", LeanSelfAttention):
+        return _convert_attention(model, memo)
     if convert_linears and _is_reference(model, "GeneralizedLinear", GeneralizedLinear):
         return _convert_linear(model, memo)
 
@@ -110,6 +136,8 @@ def convert_model(model: nn.Module, convert_linears: bool = True) -> nn.Module:
         for name, child in list(parent.named_children()):
             if _is_reference(child, "LeanFFN", LeanFFN):
                 setattr(parent, name, _convert_ffn(child, memo))
+            elif convert_attention and _is_reference(child, "LeanSelfAttention", LeanSelfAttention):
+                setattr(parent, name, _convert_attention(child, memo))
             elif convert_linears and _is_reference(child, "GeneralizedLinear", GeneralizedLinear):
                 setattr(parent, name, _convert_linear(child, memo))
             else:

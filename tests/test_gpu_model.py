@@ -119,3 +119,53 @@ def test_dropout_runs_are_consistent_across_optimizations(cuda_device):
         _compare(got, want, FP32_RTOL, FP32_ATOL, f"dropout ckpt={checkpoints} custom={custom}")
     other = _run(model, ids, seed=4242)
     assert not torch.allclose(other[0], want[0], rtol=1e-3, atol=1e-5), "dropout ignored the seed"
+
+
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_attention_shell_matches_reference_block(cuda_device, mode):
+    """lean_transformer/attn.py:11-82 with a rotary core, shared block-sparse-free GeneralizedLinear projections and an
+    fp32 residual stream: the reference block on stock operators against the same block after convert_model (its
+    LayerNorm, qkv projection and out projection + dropout + residual on this package's kernels, its own core)."""
+    import lean_transformer_b200 as L
+    from lean_transformer_b200.integration import convert_model
+
+    ref = _reference()
+    torch.manual_seed(3)
+    hidden, heads = 256, 8
+    GM, GL = ref.linear.GeneralizedMatrix, ref.linear.GeneralizedLinear
+    block = ref.attn.LeanSelfAttention(hidden, heads, dropout=0.0, attention_core=ref.attn.RotaryAttentionCore(hidden, heads),
+                                       qkv_proj=GL(GM(hidden, 3 * hidden, None, 16), adapter_dim=8),
+                                       out_proj=GL(GM(hidden, hidden, None, 0))).to(cuda_device).train()
+    with torch.no_grad():
+        block.qkv_proj.adapter_second.normal_(0, 0.02)
+    x = torch.randn(3, 96, hidden, device=cuda_device)
+    g = torch.randn(3, 96, hidden, device=cuda_device)
+    mask = torch.zeros(3, 1, 96, 96, device=cuda_device)
+    mask[1, :, :, 80:] = -10000.0
+    def run(module, autocast):
+        module.zero_grad(set_to_none=True)
+        inp = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+            (out,) = module(inp, mask)
+        (out.float() * g).sum().backward()
+        return out.detach(), inp.grad, {n: p.grad.clone() for n, p in module.named_parameters() if p.grad is not None}
+
+    want = run(block, False)  # the reference's own fp32 run is the yardstick
+    floor = run(block, True) if mode == "bf16" else None
+    new = convert_model(block)
+    assert isinstance(new, L.LeanSelfAttention) and isinstance(new, ref.attn.LeanSelfAttention)
+    assert new.attention_core is block.attention_core and isinstance(new.qkv_proj, L.GeneralizedLinear)
+    launches = L.ops.launch_count
+    got = run(new, mode == "bf16")
+    assert L.ops.launch_count - launches >= 8
+    assert got[0].dtype == torch.float32  # fp32 residual stream: attn.py:77
+    rtol, atol = (BF16_RTOL, BF16_ATOL) if mode == "bf16" else (FP32_RTOL, FP32_ATOL)
+    budget = dict(outlier_frac=1e-4, outlier_cap=2.0) if mode == "bf16" else {}
+    assert_close(got[0], want[0], rtol, atol, f"attention {mode}:out", branch=want[0] - x, scale_atol=True, **budget)
+    assert_close(got[1], want[1], rtol, atol, f"attention {mode}:grad_input", scale_atol=True, **budget)
+    assert set(got[2]) == set(want[2])
+    for name in want[2]:
+        assert_close(got[2][name], want[2][name], rtol, atol, f"attention {mode}:grad {name}", scale_atol=True, **budget)
+        if mode == "bf16":
+            record_closeness(floor[2][name], want[2][name], rtol, atol, f"twin:attention bf16:grad {name}")
+    L.check_device_status(cuda_device)
