@@ -65,6 +65,7 @@ extern "C" {
 #define LEANFFN_DEV_TIMEOUT_PRODUCER 1
 #define LEANFFN_DEV_TIMEOUT_MMA 2
 #define LEANFFN_DEV_TIMEOUT_EPILOGUE 3
+#define LEANFFN_DEV_TIMEOUT_PEER 4 /* leanffn_peer_barrier: a rank did not arrive within the limit */
 
 /* Version of this header; leanffn_abi_version() returns the one the library was built from. */
 #define LEANFFN_ABI_VERSION 3
@@ -412,6 +413,19 @@ int32_t leanffn_selftest_wait_timeout(int32_t* status_word, int64_t limit_cycles
  * Stands in for the fp32 cuBLAS products of the reference's fp32 (non-autocast) mode. */
 int32_t leanffn_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int32_t role,
                            int64_t slice, void* stream);
+
+/* Barrier between the ranks of one NVLink domain (at most 8 GPUs, one process per GPU) with a BOUNDED wait and no
+ * trap: rank r stores `epoch` into slot [channel][r] of every peer's flag array (release, system scope) and waits
+ * until every slot [channel][t] of its own array holds a value >= epoch (acquire loads).  flags[t] is the address,
+ * valid on this GPU, of rank t's flag array: 4 channels x 8 uint32, zero-initialised once, peer-mapped (for example
+ * a region of a symmetric-memory buffer).  Every rank calls with the same (channel, epoch); epochs of a channel
+ * increase by one per barrier (wrap-around safe).  A rank that waits longer than limit_cycles SM clocks (0 = about
+ * 20 s) records LEANFFN_DEV_TIMEOUT_PEER in *status_word and returns: nothing hangs, the host reads the word and
+ * decides.  Writes made by earlier kernels of this stream are visible to the peers' kernels that follow their
+ * barrier.  One warp, no shared memory: it fits beside a persistent GEMM that leaves one SM free.
+ * No counterpart in the reference (it has no distributed code). */
+int32_t leanffn_peer_barrier(void* const* flags, int32_t rank, int32_t world, int32_t channel, uint32_t epoch,
+                             int64_t limit_cycles, int32_t* status_word, void* stream);
 
 /* Strided device-to-device copy of `height` pieces of `width_bytes` (cudaMemcpy2DAsync; between two GPUs with peer
  * access it runs on a copy engine and occupies no SM).  Used to hand the reduced row blocks of a scattered weight

@@ -16,7 +16,8 @@ F32, BF16, TF32 = 0, 1, 2
 ABI_VERSION = 3
 ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_TANH, ACT_SIGMOID, ACT_IDENTITY = range(7)
 EPI_STORE, EPI_GLU_FWD, EPI_ACT_FWD, EPI_DROPOUT_RESIDUAL, EPI_GLU_BWD, EPI_ACT_BWD = range(6)
-DEV_STATUS_NAMES = {0: "ok", 1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out"}
+DEV_STATUS_NAMES = {0: "ok", 1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out",
+                    4: "wait for a peer rank timed out"}
 
 
 class GemmDesc(ctypes.Structure):
@@ -107,6 +108,8 @@ _SIGNATURES = {
     "leanffn_split_tf32": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32, c_int64, c_void_p]),
     "leanffn_gemm": (c_int32, [POINTER(GemmDesc), c_void_p]),
     "leanffn_selftest_wait_timeout": (c_int32, [c_void_p, c_int64, c_void_p]),
+    "leanffn_peer_barrier": (c_int32, [POINTER(c_void_p), c_int32, c_int32, c_int32, ctypes.c_uint32, c_int64, c_void_p,
+                                       c_void_p]),
     "leanffn_timer_create": (c_int32, [c_int32, POINTER(c_void_p)]),
     "leanffn_timer_reset": (c_int32, [c_void_p]),
     "leanffn_timer_summary": (c_int32, [c_void_p, POINTER(ctypes.c_double), POINTER(ctypes.c_double), POINTER(c_int32),

@@ -442,6 +442,20 @@ extern "C" int32_t leanffn_selftest_wait_timeout(int32_t* status_word, int64_t l
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }
 
+extern "C" int32_t leanffn_peer_barrier(void* const* flags, int32_t rank, int32_t world, int32_t channel, uint32_t epoch,
+                                        int64_t limit_cycles, int32_t* status_word, void* stream) {
+  if (flags == nullptr) return LEANFFN_ERR_NULL;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || channel < 0 || channel >= 4) return LEANFFN_ERR_SHAPE;
+  if (limit_cycles < 0) return LEANFFN_ERR_UNSUPPORTED;
+  for (int i = 0; i < world; ++i) {
+    if (flags[i] == nullptr) return LEANFFN_ERR_NULL;
+    if (reinterpret_cast<uintptr_t>(flags[i]) % 4 != 0) return LEANFFN_ERR_ALIGN;
+  }
+  if (world == 1) return LEANFFN_OK;
+  const long long limit = limit_cycles == 0 ? 40000000000LL : limit_cycles;  // ~20 s of SM clocks by default
+  return launch_peer_barrier(flags, rank, world, channel, epoch, limit, status_word, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const void* src, uint64_t src_pitch_bytes,
                                    uint64_t width_bytes, uint64_t height, void* stream) {
   if (width_bytes == 0 || height == 0) return LEANFFN_OK;

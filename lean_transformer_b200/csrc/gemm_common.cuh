@@ -109,6 +109,8 @@ cudaError_t launch_split_tf32(const float* x, int64_t ldx, float* out, int64_t r
 // partial[0, :] = column sums of x [rows, cols]; partial rows 1 .. ceil(rows/32)-1 are zeroed.
 int32_t launch_colsum_into_partials(const void* x, int32_t dtype, int64_t ld, float* partial, int64_t ld_partial,
                                     int64_t rows, int64_t cols, cudaStream_t st);
+int32_t launch_peer_barrier(void* const* flags, int32_t rank, int32_t world, int32_t channel, uint32_t epoch,
+                            long long limit, int32_t* status, cudaStream_t st);
 cudaError_t launch_wait_timeout_probe(int32_t* status, long long limit, cudaStream_t st);
 // CTA-pair (cta_group::2) kernel for dense products; tile counts in p are in 256 x 256 tiles.
 int32_t gemm_tcgen05_pair(bool a_mn, bool b_mn, const TcOperand& A, const TcOperand& B, const TcOperand* A2,

@@ -558,9 +558,11 @@ act_bwd_kernel(const T* dhid, int64_t ld_dhid, const T* __restrict__ pre, T* dpr
       for (int j = 0; j < 4; ++j) {
         float y, d;
         act_fwd_bwd<FAST>(act, g[j], y, d);
+        // every product of two stored tensors is rounded to the tensors' type (bf16: as the GEMM epilogue's packed
+        // products do), so the fused and the stand-alone formulations agree bit for bit
         y = to_f32(from_f32<T>(y));
         dl[j] = dh[j] * y;
-        dg[j] = dh[j] * l[j] * d;
+        dg[j] = to_f32(from_f32<T>(dh[j] * l[j])) * to_f32(from_f32<T>(d));
         h[j] = y * l[j];
       }
       q.set(dl);
@@ -570,7 +572,7 @@ act_bwd_kernel(const T* dhid, int64_t ld_dhid, const T* __restrict__ pre, T* dpr
       for (int j = 0; j < 4; ++j) {
         float y, d;
         act_fwd_bwd<FAST>(act, g[j], y, d);
-        dg[j] = dh[j] * d;
+        dg[j] = dh[j] * to_f32(from_f32<T>(d));
         h[j] = y;
       }
     }
@@ -835,6 +837,46 @@ static int32_t ln_bwd_dispatch(const void* dy, const void* x, const void* gamma,
   if (s != LEANFFN_OK) return s;
   cudaMemcpyAsync(dgamma, tail, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st);
   cudaMemcpyAsync(dbeta, tail + cols, sizeof(float) * cols, cudaMemcpyDeviceToDevice, st);
+  return launch_status();
+}
+
+// ---- barrier between ranks over peer-mapped flag words ---------------------------------------------------------
+struct PeerBarrierArgs {
+  uint32_t* flags[8];
+  int32_t rank, world, channel;
+  uint32_t epoch;
+  long long limit;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(32)
+peer_barrier_kernel(const PeerBarrierArgs a) {
+  const int t = threadIdx.x;
+  if (t < a.world && t != a.rank) {
+    __threadfence_system();  // earlier writes of this GPU (previous kernels of the stream) precede the signal
+    uint32_t* remote = a.flags[t] + a.channel * 8 + a.rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(a.epoch) : "memory");
+    const uint32_t* mine = a.flags[a.rank] + a.channel * 8 + t;
+    const long long t0 = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(v - a.epoch) >= 0) break;
+      if (clock64() - t0 > a.limit) {  // bounded: record which wait gave up and return
+        if (a.status != nullptr) atomicCAS(a.status, 0, LEANFFN_DEV_TIMEOUT_PEER);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+int32_t launch_peer_barrier(void* const* flags, int32_t rank, int32_t world, int32_t channel, uint32_t epoch,
+                            long long limit, int32_t* status, cudaStream_t st) {
+  PeerBarrierArgs a{};
+  for (int i = 0; i < world; ++i) a.flags[i] = static_cast<uint32_t*>(flags[i]);
+  a.rank = rank, a.world = world, a.channel = channel, a.epoch = epoch, a.limit = limit, a.status = status;
+  peer_barrier_kernel<<<1, 32, 0, st>>>(a);
   return launch_status();
 }
 

@@ -57,6 +57,34 @@ __device__ __forceinline__ void unpack8(const uint4& w, float (&v)[8]) {
     v[2 * h + 1] = __high2float(b);
   }
 }
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 w;
+  w.x = pack_bf16x2(v[0], v[1]);
+  w.y = pack_bf16x2(v[2], v[3]);
+  w.z = pack_bf16x2(v[4], v[5]);
+  w.w = pack_bf16x2(v[6], v[7]);
+  return w;
+}
+// Product of two packed bf16 pairs, rounded to nearest even.  The exact product of two bf16 values fits an fp32
+// mantissa, so this equals "multiply in fp32, round to bf16" bit for bit: one instruction for two elements and no
+// unpacking, which matters because the fused epilogues are bound by instruction issue, not by memory.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint4 mul8(const uint4& a, const uint4& b) {
+  return make_uint4(mul_bf16x2(a.x, b.x), mul_bf16x2(a.y, b.y), mul_bf16x2(a.z, b.z), mul_bf16x2(a.w, b.w));
+}
+// acc[0..7] += the 8 bf16 values packed in w
+__device__ __forceinline__ void add_packed8(float* acc, const uint4& w) {
+  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    acc[2 * h] += __uint_as_float(u[h] << 16);
+    acc[2 * h + 1] += __uint_as_float(u[h] & 0xFFFF0000u);
+  }
+}
 __device__ __forceinline__ void store_packed8(void* base, int32_t dtype, int64_t elem, const uint4& w) {
   if (dtype == LEANFFN_BF16) {
     *reinterpret_cast<uint4*>(static_cast<bf16*>(base) + elem) = w;
@@ -111,17 +139,25 @@ __device__ __forceinline__ uint32_t patch_offset(int row, int chunk) {
 // TMEM block (lane = row) + bias, rounded to bf16 ->  w[i] = 8 packed values of (row 8*i + lane/4,
 // columns (lane%4)*8 .. +7) of the block.
 __device__ __forceinline__ void load_block_bf16(uint32_t taddr, float* patch, int lane, bool valid,
-                                                const float (&bias)[32], uint4 (&w)[4]) {
+                                                const float (&bias)[32], uint4 (&w)[4], bool has_bias = true) {
   uint32_t r[32];
   __syncwarp();
   tmem_ld_32x32(taddr, r);
   tmem_ld_wait();
   char* base = reinterpret_cast<char*>(patch);
+  if (!valid) {  // empty reduction (warp-uniform): the accumulator was never written
+#pragma unroll
+    for (int q = 0; q < 32; ++q) r[q] = 0u;
+  }
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     float f[8];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) f[q] = (valid ? __uint_as_float(r[8 * c + q]) : 0.f) + bias[8 * c + q];
+    for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[8 * c + q]);
+    if (has_bias) {  // warp-uniform
+#pragma unroll
+      for (int q = 0; q < 8; ++q) f[q] += bias[8 * c + q];
+    }
     uint4 p;
     p.x = pack_bf16x2(f[0], f[1]);
     p.y = pack_bf16x2(f[2], f[3]);
@@ -248,12 +284,12 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
         {
           float bias[32];
           load_bias32(ep.bias, ep.bias_dtype, j0, inter, bias);
-          load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, g);
+          load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, g, ep.bias != nullptr);
         }
         {
           float bias[32];
           load_bias32(ep.bias, ep.bias_dtype, inter + j0, 2 * static_cast<int64_t>(inter), bias);
-          load_block_bf16(t_acc + 128 + blk * 32, patch, lane, acc_valid, bias, l);
+          load_block_bf16(t_acc + 128 + blk * 32, patch, lane, acc_valid, bias, l, ep.bias != nullptr);
         }
         if (!live) continue;
 #pragma unroll
@@ -262,13 +298,11 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           if (row >= ep.M) continue;
           store_packed8(ep.D, ep.d_dtype, row * ep.ldd + j, g[i]);
           store_packed8(ep.D, ep.d_dtype, row * ep.ldd + inter + j, l[i]);
-          float gf[8], lf[8], h[8];
+          float gf[8], h[8];
           unpack8(g[i], gf);
-          unpack8(l[i], lf);
           act_fwd8<ACT>(ep.act, gf, h);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) h[q] = bf16_round(h[q]) * lf[q];
-          store8(ep.D2, ep.d_dtype, row * ep.ldd2 + j, h);
+          // hid = bf16(act(gate)) * lin, as packed bf16 products
+          store_packed8(ep.D2, ep.d_dtype, row * ep.ldd2 + j, mul8(pack8(h), l[i]));
         }
       }
     }
@@ -315,7 +349,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       {
         float bias[32];
         load_bias32(ep.bias, ep.bias_dtype, col0, ep.N, bias);
-        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w);
+        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w, ep.bias != nullptr);
       }
       if (!live) continue;
 #pragma unroll
@@ -377,7 +411,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       {
         float bias[32];
         load_bias32(ep.bias, ep.bias_dtype, col0, ep.N, bias);
-        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w);
+        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w, ep.bias != nullptr);
       }
       constexpr bool IS_BWD = KIND == LEANFFN_EPI_GLU_BWD || KIND == LEANFFN_EPI_ACT_BWD;
       constexpr int NCS = KIND == LEANFFN_EPI_GLU_BWD ? 16 : 8;
@@ -421,42 +455,30 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           for (int q = 0; q < 8; ++q) x[q] += res[q];
           store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
         } else if constexpr (KIND == LEANFFN_EPI_GLU_BWD) {
-          // x = dHid[row, col..]; aux = pre [M, 2N] (a0 gate, a1 linear); D = dPre [M, 2N]; D2 = hid [M, N] (optional)
-          float gate[8], lin[8], y[8], d[8], dl[8];
+          // w = dHid[row, col..] (packed); aux = pre [M, 2N] (c0 gate, c1 linear); D = dPre [M, 2N]; D2 = hid (optional).
+          // The activation and its derivative are computed in fp32 from the gate, rounded once, and every product of
+          // two bf16 tensors (as in the unfused formulation, where each is a bf16 tensor) is a packed bf16 product.
+          float gate[8], y[8], d[8];
           unpack8(c0[i], gate);
-          unpack8(c1[i], lin);
           act_fwd_bwd8<ACT>(ep.act, gate, y, d);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            y[q] = bf16_round(y[q]);
-            dl[q] = x[q] * y[q];          // d/d(linear half)
-            d[q] = x[q] * lin[q] * d[q];  // d/d(gate)
-            y[q] = y[q] * lin[q];         // rematerialised hid
-          }
-          store8(ep.D, ep.d_dtype, row * ep.ldd + col, d);
-          store8(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl);
-          if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, y);
+          const uint4 y2 = pack8(y), d2 = pack8(d);
+          const uint4 dl = mul8(w[i], y2);                 // d/d(linear half) = dHid * act(gate)
+          const uint4 dg = mul8(mul8(w[i], c1[i]), d2);    // d/d(gate) = dHid * lin * act'(gate)
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, dg);
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl);
+          if (ep.D2 != nullptr) store_packed8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, mul8(y2, c1[i]));  // remat hid
           if (want_cs) {
-            const bool rounds = ep.d_dtype == LEANFFN_BF16;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              cs[q] += rounds ? bf16_round(d[q]) : d[q];
-              cs[8 + q] += rounds ? bf16_round(dl[q]) : dl[q];
-            }
+            add_packed8(cs, dg);
+            add_packed8(cs + 8, dl);
           }
         } else if constexpr (KIND == LEANFFN_EPI_ACT_BWD) {
           float pre[8], y[8], d[8];
           unpack8(c0[i], pre);
           act_fwd_bwd8<ACT>(ep.act, pre, y, d);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) x[q] *= d[q];
-          store8(ep.D, ep.d_dtype, row * ep.ldd + col, x);
+          const uint4 dx = mul8(w[i], pack8(d));
+          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, dx);
           if (ep.D2 != nullptr) store8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, y);
-          if (want_cs) {
-            const bool rounds = ep.d_dtype == LEANFFN_BF16;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) cs[q] += rounds ? bf16_round(x[q]) : x[q];
-          }
+          if (want_cs) add_packed8(cs, dx);
         }
       }
       if constexpr (IS_BWD) {

@@ -212,7 +212,7 @@ class ScatteredGradReducer:
     BLOCK_SHIFT = 8  # 256 rows: the tile height of the weight-gradient GEMM
 
     def __init__(self, weights: Dict[str, torch.Tensor], group: Optional[dist.ProcessGroup] = None,
-                 spare_sms: int = 2):
+                 spare_sms: int = 2, barrier_limit_cycles: int = 0):
         import torch.distributed._symmetric_memory as symm
 
         if not dist.is_initialized():
@@ -240,6 +240,9 @@ class ScatteredGradReducer:
             self._by_storage[w.data_ptr()] = name
             self._params[name] = w
             offset += (nbytes + 255) // 256 * 256
+        # flag words of the rank barrier (4 channels x 8 ranks x uint32) live behind the gradients in the same buffer
+        self._flag_offset = offset
+        offset += 256
         self._buffer = symm.empty(offset, dtype=torch.uint8, device=device)
         self._handle = symm.rendezvous(self._buffer, self.group.group_name)
         self._peer_bases = [int(p) for p in self._handle.buffer_ptrs]
@@ -251,7 +254,28 @@ class ScatteredGradReducer:
         self._sms = torch.cuda.get_device_properties(device).multi_processor_count
         self._spare_sms = max(1, int(spare_sms))
         self._buffer.zero_()
-        self._handle.barrier(channel=0)
+        import ctypes
+        self._flags = (ctypes.c_void_p * 8)(*[base + self._flag_offset for base in self._peer_bases])
+        self._epochs = [0, 0, 0, 0]
+        self._barrier_limit = int(barrier_limit_cycles)
+        # every rank's flags (and gradients) are zero before any rank can signal: host-level rendezvous, once
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)
+
+    def _barrier(self, channel: int, stream: Optional[torch.cuda.Stream] = None):
+        """Rank barrier on ``stream`` through ``leanffn_peer_barrier``: the wait is bounded (``barrier_limit_cycles`` SM
+        clocks, 0 = about 20 s) and a rank that never arrives makes the kernel record a status code and return; it
+        neither hangs nor traps.  ``ops.check_device_status`` raises on that code at the caller's next check.
+        (torch's own symmetric-memory ``barrier`` spins without limit when called with ``timeout_ms=0`` and traps the
+        context when a non-zero timeout expires; neither is wanted underneath a training step.)"""
+        from . import _native as N
+        from . import ops
+        self._epochs[channel] += 1
+        stream = stream if stream is not None else torch.cuda.current_stream()
+        N.check(N.lib.leanffn_peer_barrier(self._flags, self.rank, self.world_size, channel,
+                                           self._epochs[channel] & 0xFFFFFFFF, self._barrier_limit,
+                                           ops.status_word(self._buffer.device).data_ptr(), stream.cuda_stream),
+                "leanffn_peer_barrier")
 
     def gradient(self, name: str) -> torch.Tensor:
         """This rank's replica of the summed gradient (valid after ``finish``)."""
@@ -266,7 +290,7 @@ class ScatteredGradReducer:
                 view.view(rows // (block_rows * self.world_size), self.world_size, block_rows * cols)[:, self.rank].zero_()
             else:
                 view.zero_()
-        self._handle.barrier(channel=0)
+        self._barrier(0)
 
     def target(self, weight: torch.Tensor):
         """``(out, scatter)`` arguments of ``ops.gemm`` for the gradient of ``weight``, or None if not registered."""
@@ -293,14 +317,14 @@ class ScatteredGradReducer:
         self._side.wait_event(ready)
         first, pitch, width, height = handout_plan(rows, cols, dtype.itemsize, self.world_size, self.rank, self.BLOCK_SHIFT)
         with torch.cuda.stream(self._side):
-            self._handle.barrier(channel=1)  # every rank's contributions have landed
+            self._barrier(1, self._side)  # every rank's contributions have landed
             if height > 0:
                 start = offset + first
                 for shift in range(1, self.world_size):
                     peer = (self.rank + shift) % self.world_size
                     ops.copy_2d(self._peer_bases[peer] + start, pitch, self._peer_bases[self.rank] + start, pitch,
                                 width, height, self._side)
-            self._handle.barrier(channel=1)  # every rank's blocks have arrived here
+            self._barrier(1, self._side)  # every rank's blocks have arrived here
             done = torch.cuda.Event()
             done.record()
         self._done.append(done)

@@ -182,6 +182,7 @@ def _projection_args(proj):
 # any step that must interleave Python between the kernels (gradient-ready callbacks, scattered gradient exchange),
 # takes the piecewise schedule, which launches the same kernels.
 _BLOCK_CALLS = os.environ.get("LEANFFN_BLOCK_CALLS", "1") != "0"
+_EXPERIMENT_UNFUSED_ACT_BWD = os.environ.get("LEANFFN_UNFUSED_ACT_BWD", "0") == "1"  # piecewise schedule only
 
 
 def set_block_calls(enabled: bool) -> bool:
@@ -448,9 +449,17 @@ class _LeanFFN(torch.autograd.Function):
             a2, b2 = grad_lowrank_hid, cast_cached(h2o_lowrank_first, cdt)
         # the input-gradient epilogue (dense or block-sparse weight alike) applies the activation backward and
         # rematerialises hid_act, which the weight gradients below then consume
-        input_grad(h2o_kind, grad_h2o_out, h2o_weight, h2o_forward_indices, h2o_backward_indices, ctx._h2o_matmul_op,
-                   cdt, a2=a2, b2=b2, epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD, act=act,
-                   aux=pre_activation, out=grad_pre, out2=hid_act, colsum=bias1_partial)
+        if _EXPERIMENT_UNFUSED_ACT_BWD and h2o_kind != "dense":
+            # measurement switch: plain input-gradient product, then the activation backward as its own pass
+            grad_hid = input_grad(h2o_kind, grad_h2o_out, h2o_weight, h2o_forward_indices, h2o_backward_indices,
+                                  ctx._h2o_matmul_op, cdt, a2=a2, b2=b2)
+            ops.activation_backward(grad_hid, pre_activation, gated, act, out=grad_pre, hid_out=hid_act)
+            del grad_hid
+            bias1_partial = None
+        else:
+            input_grad(h2o_kind, grad_h2o_out, h2o_weight, h2o_forward_indices, h2o_backward_indices,
+                       ctx._h2o_matmul_op, cdt, a2=a2, b2=b2, epilogue=N.EPI_GLU_BWD if gated else N.EPI_ACT_BWD,
+                       act=act, aux=pre_activation, out=grad_pre, out2=hid_act, colsum=bias1_partial)
         grad_i2h_bias_ready = ops.column_sum(bias1_partial) if bias1_partial is not None else None
         del bias1_partial
         grad_h2o_weight = grad_h2o_lowrank_first = grad_h2o_lowrank_second = None

@@ -515,3 +515,33 @@ def test_bounded_wait_runs_out_and_reports(ops, cuda_device):
     ops.check_device_status(cuda_device)
     assert_close(out, _cpu64(a) @ _cpu64(b).T, BF16_RTOL, BF16_ATOL, "gemm after the probe", scale_atol=True)
     assert N.lib.leanffn_selftest_wait_timeout(None, 1000, stream) == -1
+
+
+def test_peer_barrier_signals_and_gives_up_within_its_limit(ops, cuda_device):
+    """leanffn_peer_barrier with the flag arrays of two "ranks" placed on this one GPU and the peer's arrival written
+    by the host: the kernel signals the peer, sees the arrival and returns; without the arrival it gives up after the
+    limit, records LEANFFN_DEV_TIMEOUT_PEER and returns (no hang, no trap), and the context stays usable."""
+    import ctypes
+    from lean_transformer_b200 import _native as N
+    flags = torch.zeros(2, 4, 8, dtype=torch.int32, device=cuda_device)  # [rank][channel][source rank]
+    table = (ctypes.c_void_p * 8)(flags[0].data_ptr(), flags[1].data_ptr())
+    word = ops.status_word(cuda_device)
+    ops.check_device_status(cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    flags[0, 1, 1] = 7  # rank 1 has arrived at epoch 7 of channel 1
+    N.check(N.lib.leanffn_peer_barrier(table, 0, 2, 1, 7, 100000, word.data_ptr(), stream), "peer barrier")
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0 and int(flags[1, 1, 0]) == 7  # our signal reached the peer's array
+    # a later epoch that the peer never reaches: bounded wait
+    N.check(N.lib.leanffn_peer_barrier(table, 0, 2, 1, 8, 100000, word.data_ptr(), stream), "peer barrier")
+    torch.cuda.synchronize()
+    assert int(word.item()) == 4 and int(flags[1, 1, 0]) == 8
+    with pytest.raises(RuntimeError, match="peer rank"):
+        ops.check_device_status(cuda_device)
+    # epochs compare modulo 2^32: arrival at epoch 1 after the counter wrapped satisfies a wait for epoch 0
+    flags[0, 2, 1] = 1
+    N.check(N.lib.leanffn_peer_barrier(table, 0, 2, 2, 0, 100000, word.data_ptr(), stream), "peer barrier")
+    torch.cuda.synchronize()
+    ops.check_device_status(cuda_device)
+    assert N.lib.leanffn_peer_barrier(table, 2, 2, 0, 1, 0, None, stream) == -2   # rank outside the world
+    assert N.lib.leanffn_peer_barrier(table, 0, 1, 0, 1, 0, None, stream) == 0    # a world of one: nothing to do
