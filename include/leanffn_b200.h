@@ -288,6 +288,11 @@ typedef struct leanffn_gemm_desc {
   /* Optional (NULL = off): a timer made by leanffn_timer_create.  The call then records a CUDA event pair around its
    * kernel on `stream` and books the launch's algorithmic FLOPs (2 * M * N * (K_effective + K2)) with it. */
   void* timer;
+  /* in_dtype LEANFFN_TF32 only: > 0 cuts the reduction axis into slices of this many elements (a multiple of 96: three
+   * parts of a multiple of 32), the last slice taking the remainder, i.e. the slices leanffn_split_tf32 lays out for
+   * slice width tf32_k_slice / 3.  The kernel accumulates every slice in tensor memory on its own and keeps the
+   * running fp32 sum in D, so one launch gives what one launch per slice (with aux = D) would. */
+  int32_t tf32_k_slice;
 } leanffn_gemm_desc;
 
 int32_t leanffn_gemm(const leanffn_gemm_desc* desc, void* stream);
@@ -409,7 +414,8 @@ int32_t leanffn_selftest_wait_timeout(int32_t* status_word, int64_t limit_cycles
  * leanffn_gemm with in_dtype LEANFFN_TF32, A = outA + 3f, B = outB + 3f, lda = ldb = 3*cols and K = 3w then
  * gives the fp32-accurate product over that slice (K-major operands, dense, LEANFFN_EPI_STORE with optional bias,
  * fp32 result, M, N >= 64, N a multiple of 8, f and w multiples of 4).  With in_dtype LEANFFN_TF32, `aux`
- * (fp32 [M, N], may be D itself) is added to the result: that is the running sum over slices.
+ * (fp32 [M, N], may be D itself) is added to the result: that is the running sum over slices.  ONE call covers all
+ * slices when the descriptor's tf32_k_slice = 3w is set (A = outA, B = outB, K = 3*cols; w a multiple of 32).
  * Stands in for the fp32 cuBLAS products of the reference's fp32 (non-autocast) mode. */
 int32_t leanffn_split_tf32(const float* x, int64_t ldx, float* out, int64_t rows, int64_t cols, int32_t role,
                            int64_t slice, void* stream);

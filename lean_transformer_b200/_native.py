@@ -40,6 +40,7 @@ class GemmDesc(ctypes.Structure):
         ("scatter_world", c_int32), ("scatter_block_shift", c_int32), ("scatter_D", c_void_p * 8),
         ("bs_wgrad_pairs", c_int32), ("wait_limit_cycles", c_int64),
         ("colsum_partial", c_void_p), ("ld_colsum", c_int64), ("timer", c_void_p),
+        ("tf32_k_slice", c_int32),
     ]
 
 

@@ -146,7 +146,7 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
   if (d->act < 0 || d->act >= LEANFFN_ACT_COUNT) return LEANFFN_ERR_UNSUPPORTED;
   if (d->bs_mode < 0 || d->bs_mode > 3) return LEANFFN_ERR_UNSUPPORTED;
   if (!(d->dropout_p >= 0.f && d->dropout_p < 1.f)) return LEANFFN_ERR_UNSUPPORTED;
-  if (d->wait_limit_cycles < 0) return LEANFFN_ERR_UNSUPPORTED;
+  if (d->wait_limit_cycles < 0 || d->tf32_k_slice < 0) return LEANFFN_ERR_UNSUPPORTED;
   if (d->K2 > 0 && (d->A2 == nullptr || d->B2 == nullptr)) return LEANFFN_ERR_NULL;
   const int epi = d->epilogue;
   const bool needs_d2 = epi == LEANFFN_EPI_GLU_FWD || epi == LEANFFN_EPI_ACT_FWD;
@@ -235,6 +235,18 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
     p.num_m_blocks = static_cast<int32_t>((d->M + 127) / 128);
     p.num_n_blocks = static_cast<int32_t>((d->N + block_n - 1) / block_n);
     p.num_k_blocks = static_cast<int32_t>((d->K + 31) / 32);
+    p.k_slices = 1;
+    p.k_blocks_last = p.num_k_blocks;
+    if (d->tf32_k_slice > 0) {
+      // slices of tf32_k_slice elements of the (tripled) reduction axis, the last one takes the remainder: the rule
+      // leanffn_split_tf32 lays the slices out by
+      if (d->tf32_k_slice % 96 != 0) return LEANFFN_ERR_SHAPE;  // 3 parts of a multiple of 32 elements (one k-block)
+      const int32_t slices = d->K / d->tf32_k_slice > 0 ? d->K / d->tf32_k_slice : 1;
+      p.k_slices = slices;
+      p.num_k_blocks = d->tf32_k_slice / 32;
+      p.k_blocks_last = static_cast<int32_t>((d->K - static_cast<int64_t>(slices - 1) * d->tf32_k_slice + 31) / 32);
+      if (slices > 1 && d->aux != nullptr) return LEANFFN_ERR_UNSUPPORTED;  // the running sum lives in D itself
+    }
     TcOperand A{}, B{};
     A.ptr = d->A, A.ld = d->lda, A.rows = d->M, A.cols = d->K;
     B.ptr = d->B, B.ld = d->ldb, B.rows = d->N, B.cols = d->K;
@@ -289,6 +301,8 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
     p.num_n_blocks = static_cast<int32_t>(n_tiles_n);
     p.num_k_blocks = static_cast<int32_t>((k_eff + 63) / 64);
     p.num_k2_blocks = static_cast<int32_t>((d->K2 + 63) / 64);
+    p.k_slices = 1;
+    p.k_blocks_last = p.num_k_blocks;
     TcOperand A{}, B{}, A2{}, B2{};
     A.ptr = d->A;
     A.ld = d->lda;

@@ -79,6 +79,9 @@ struct TcParams {
   int32_t num_m_blocks, num_n_blocks;
   int32_t num_k_blocks;   // main reduction, in 64-element units (dense: ceil(K/64); sparse: nnz * block/64)
   int32_t num_k2_blocks;  // low-rank continuation
+  // TF32 mode: the reduction axis is cut into k_slices slices of num_k_blocks k-blocks (the last one k_blocks_last);
+  // every slice is accumulated in tensor memory on its own and added to D by the epilogue (running fp32 sum)
+  int32_t k_slices, k_blocks_last;
   int32_t bs_mode, bs_block, bs_nnz;
   const int32_t* bs_index;  // int32 pairs, see include/leanffn_b200.h
   const int32_t* bs_count;  // entries per table row, or nullptr

@@ -147,7 +147,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
-      const int kb_main = main_k_blocks(n_blk);
+      const int slices = TF32 ? p.k_slices : 1;
+      for (int sl = 0; sl < slices && ok; ++sl) {
+      const int kb_main = (TF32 && sl == slices - 1) ? p.k_blocks_last : main_k_blocks(n_blk);
+      const int kb_base = TF32 ? sl * p.num_k_blocks : 0;  // first k-block of this slice
       const int kb_total = kb_main + p.num_k2_blocks;
       for (int kb = 0; kb < kb_total; ++kb) {
         if (*abort_ptr != 0 || !mbar_wait_bounded(empty_bar(stage), phase ^ 1u, wait_limit)) {
@@ -173,7 +176,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           b_r = n_blk * BLOCK_N;
           if (p.glu_split > 0) b_r = n_blk * 128, b_r2 = p.glu_split + n_blk * 128;
         } else if (p.bs_mode == 0) {
-          a_k = b_k = kb * KE;
+          a_k = b_k = (kb_base + kb) * KE;
           a_r = m_blk * TILE_M;
           b_r = n_blk * BLOCK_N;
           if (p.glu_split > 0) b_r = n_blk * 128, b_r2 = p.glu_split + n_blk * 128;
@@ -249,6 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           phase ^= 1u;
         }
       }
+      }
     }
   } else if (warp == 1 && lane == 0) {
     // ------------------------------- MMA issuer ----------------------------------------------
@@ -262,7 +266,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc_stage = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    const int mma_slices = TF32 ? p.k_slices : 1;
+    for (int vt = 0; ok; ++vt) {  // virtual tiles: (tile, slice) pairs of this CTA, in order
+      const int tile = blockIdx.x + (vt / mma_slices) * gridDim.x, sl = vt % mma_slices;
+      if (tile >= num_tiles) break;
       if (*abort_ptr != 0 || !mbar_wait_bounded(tempty_bar(acc_stage), acc_phase ^ 1u, wait_limit)) {
         report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
         *abort_ptr = 1;
@@ -272,7 +279,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t d_tmem = tmem_base + acc_stage * (MT * BLOCK_N);
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
-      const int kb_total = main_k_blocks(n_blk) + p.num_k2_blocks;
+      const int kb_total = ((TF32 && sl == mma_slices - 1) ? p.k_blocks_last : main_k_blocks(n_blk)) + p.num_k2_blocks;
       for (int kb = 0; kb < kb_total; ++kb) {
         if (*abort_ptr != 0 || !mbar_wait_bounded(full_bar(stage), phase, wait_limit)) {
           report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
@@ -317,16 +324,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                    (warp - 2) * EPI_PATCH_FLOATS;
     int acc_stage = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    // TF32 mode, slices after the first: no bias, and the running sum already in D is added (every element of D is
+    // written and read back by the same thread, so program order makes the earlier store visible)
+    EpiParams ep_sum = ep;
+    if constexpr (TF32) {
+      ep_sum.bias = nullptr;
+      ep_sum.aux = ep.D, ep_sum.ldaux = ep.ldd, ep_sum.aux_dtype = LEANFFN_F32;
+    }
+    const int epi_slices = TF32 ? p.k_slices : 1;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
 #pragma unroll 1
       for (int t = 0; t < MT; ++t)
         epilogue_prefetch_aux<BLOCK_N>(ep, static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32, n_blk, lane,
                                        (warp - 2) >> 2, 2);
+      for (int sl = 0; sl < epi_slices; ++sl) {
       if (*abort_ptr != 0 || !mbar_wait_bounded(tfull_bar(acc_stage), acc_phase, wait_limit)) {
         report(p.status, LEANFFN_DEV_TIMEOUT_EPILOGUE);
         *abort_ptr = 1;
+        alive = false;
         break;
       }
       tc_fence_after();
@@ -335,7 +353,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int t = 0; t < MT; ++t) {
         const int64_t row0 = static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32;
         const uint32_t t_acc = tmem_base + lane_addr + (acc_stage * MT + t) * BLOCK_N;
-        epilogue_tile<BLOCK_N>(ep, p.glu_split, t_acc, row0, n_blk, acc_valid, patch, lane, (warp - 2) >> 2, 2);
+        epilogue_tile<BLOCK_N>((TF32 && sl > 0) ? ep_sum : ep, p.glu_split, t_acc, row0, n_blk, acc_valid, patch, lane,
+                               (warp - 2) >> 2, 2);
       }
       tc_fence_before();
       __syncwarp();
@@ -343,6 +362,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (++acc_stage == ACC_STAGES) {
         acc_stage = 0;
         acc_phase ^= 1u;
+      }
       }
     }
     if (ep.scatter_world > 0) __threadfence_system();  // contributions to peer replicas are out before the kernel ends

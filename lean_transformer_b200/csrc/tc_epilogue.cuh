@@ -14,6 +14,10 @@
 
 namespace leanffn {
 
+#ifndef LEANFFN_EPI_LOOKAHEAD
+#define LEANFFN_EPI_LOOKAHEAD 0
+#endif
+
 constexpr int EPI_PATCH_FLOATS = 32 * 33;  // per-warp patch: fp32 exchange uses row pitch 33 (conflict-free);
                                            // the bf16 exchange uses its first 2 KiB
 
@@ -326,9 +330,15 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
 #pragma unroll
           for (int q = 0; q < 8; ++q) v[i][q] += b[q];
           if (ep.aux != nullptr && ep.aux_dtype == LEANFFN_F32) {
-            // running sum over calls that each cover a slice of a long reduction axis (aux may be D itself)
+            // running sum over slices of a long reduction axis.  aux may be D itself, written earlier in THIS launch by
+            // this very thread: read it through L2 (a non-coherent read-only load could return the stale value)
             float prev[8];
-            load8(ep.aux, LEANFFN_F32, row * ep.ldaux + col, prev);
+            {
+              const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(ep.aux) + row * ep.ldaux + col);
+              const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+              prev[0] = lo.x, prev[1] = lo.y, prev[2] = lo.z, prev[3] = lo.w;
+              prev[4] = hi.x, prev[5] = hi.y, prev[6] = hi.z, prev[7] = hi.w;
+            }
 #pragma unroll
             for (int q = 0; q < 8; ++q) v[i][q] += prev[q];
           }
@@ -363,9 +373,11 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       }
     }
   } else {
-    // The residual / pre-activation rows (bf16) of a block are requested one block ahead and stay packed in
-    // registers until used: the loads of block b+1 are in flight while block b is read from tensor memory,
-    // computed and stored, which doubles the bytes in flight per warp.
+    // The residual / pre-activation rows (bf16) of a block are requested before the block is read from tensor memory
+    // and transposed, and stay packed in registers until used; the tile's rows were asked into L2 while the warp
+    // waited for the accumulator (epilogue_prefetch_aux), so the request is an L2 hit that the transposition hides.
+    // (Requesting one block further ahead costs 32 more registers per thread, which spilled in the hot loop.)
+    constexpr bool LOOKAHEAD = LEANFFN_EPI_LOOKAHEAD != 0;
     constexpr bool HAS_AUX =
         KIND == LEANFFN_EPI_DROPOUT_RESIDUAL || KIND == LEANFFN_EPI_GLU_BWD || KIND == LEANFFN_EPI_ACT_BWD;
     constexpr int NUM_BLOCKS = BLOCK_N / 32;
@@ -393,7 +405,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
         }
       }
     };
-    if constexpr (HAS_AUX) {
+    if constexpr (HAS_AUX && LOOKAHEAD) {
       if (block_begin < NUM_BLOCKS) request_aux(block_begin);
     }
 #pragma unroll 1
@@ -403,9 +415,12 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       const bool live = col < ep.N;
       uint4 c0[4], c1[4];
       if constexpr (HAS_AUX) {
+        if constexpr (!LOOKAHEAD) request_aux(blk);
 #pragma unroll
         for (int i = 0; i < 4; ++i) c0[i] = n0[i], c1[i] = n1[i];
-        if (blk + block_step < NUM_BLOCKS) request_aux(blk + block_step);
+        if constexpr (LOOKAHEAD) {
+          if (blk + block_step < NUM_BLOCKS) request_aux(blk + block_step);
+        }
       }
       uint4 w[4];
       {

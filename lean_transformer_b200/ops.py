@@ -312,30 +312,26 @@ def _gemm_fp32_tensor(a, b, a_mn_major, b_mn_major, out, out_dtype, bias, epilog
     a_k = transpose(a) if a_mn_major else a
     b_k = transpose(b) if b_mn_major else b
     plain = out if (out is not None and not backward_kind) else torch.empty((m, n), dtype=torch.float32, device=a.device)
-    # the accumulators truncate: keep every call's reduction axis short and carry a running sum between calls
-    a3 = _split_tf32(a_k, 0, _TF32_SLICE)
-    b3 = _split_tf32(b_k, 1, _TF32_SLICE)
-    slices = max(1, k // _TF32_SLICE)  # the last slice takes the remainder (same rule as the split kernel)
-    for index in range(slices):
-        first = index * _TF32_SLICE
-        width = k - first if index == slices - 1 else _TF32_SLICE
-        d = N.GemmDesc()
-        d.M, d.N, d.K = int(m), int(n), int(3 * width)
-        d.in_dtype = N.TF32
-        d.A, d.lda = a3.data_ptr() + 12 * first, 3 * k
-        d.B, d.ldb = b3.data_ptr() + 12 * first, 3 * k
-        d.epilogue = N.EPI_STORE
-        d.D, d.ldd, d.d_dtype = _ptr(plain), n, N.F32
-        if index == 0:
-            if bias is not None and not backward_kind:
-                d.bias, d.bias_dtype = _ptr(bias), N.F32
-        else:
-            d.aux, d.ldaux, d.aux_dtype = _ptr(plain), n, N.F32
-        d.status_word = _ptr(status_word(a.device))
-        d.max_ctas = _max_ctas
-        d.timer = _timer_handle()
-        _count()
-        N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
+    # the accumulators truncate: the reduction axis is cut into short slices that the kernel accumulates one by one,
+    # keeping the running fp32 sum in the result (one launch; the split kernels lay the slices out)
+    slice_width = _TF32_SLICE if _TF32_SLICE % 32 == 0 else 0
+    a3 = _split_tf32(a_k, 0, slice_width or k)
+    b3 = _split_tf32(b_k, 1, slice_width or k)
+    d = N.GemmDesc()
+    d.M, d.N, d.K = int(m), int(n), int(3 * k)
+    d.in_dtype = N.TF32
+    d.A, d.lda = a3.data_ptr(), 3 * k
+    d.B, d.ldb = b3.data_ptr(), 3 * k
+    d.epilogue = N.EPI_STORE
+    d.D, d.ldd, d.d_dtype = _ptr(plain), n, N.F32
+    if bias is not None and not backward_kind:
+        d.bias, d.bias_dtype = _ptr(bias), N.F32
+    d.tf32_k_slice = 3 * slice_width
+    d.status_word = _ptr(status_word(a.device))
+    d.max_ctas = _max_ctas
+    d.timer = _timer_handle()
+    _count()
+    N.check(N.lib.leanffn_gemm(d, _stream(a)), "leanffn_gemm")
     if epilogue == N.EPI_STORE:
         return plain
     if epilogue == N.EPI_DROPOUT_RESIDUAL:
