@@ -410,7 +410,9 @@ int32_t leanffn_selftest_wait_timeout(int32_t* status_word, int64_t limit_cycles
  * calls keeping a running sum.  This call prepares all slices at once.  For x [rows, cols] (leading dimension ldx)
  * and a slice width s, the columns are cut into max(1, cols / s) slices (the last one takes the remainder), and
  * slice j, covering columns [f, f + w), lands in out [rows, 3*cols] at columns [3f, 3f + 3w) as
- *   role 0 (the A operand):  ( hi | hi | lo )        role 1 (the B operand):  ( hi | lo | hi ),   each part w wide.
+ *   role 0 (the A operand):  ( hi | lo | hi )        role 1 (the B operand):  ( lo | hi | hi ),   each part w wide
+ * (the two small cross products come first, so that they add up before the accumulator has grown and only the
+ * last third of the slice truncates an accumulator of full size).
  * leanffn_gemm with in_dtype LEANFFN_TF32, A = outA + 3f, B = outB + 3f, lda = ldb = 3*cols and K = 3w then
  * gives the fp32-accurate product over that slice (K-major operands, dense, LEANFFN_EPI_STORE with optional bias,
  * fp32 result, M, N >= 64, N a multiple of 8, f and w multiples of 4).  With in_dtype LEANFFN_TF32, `aux`

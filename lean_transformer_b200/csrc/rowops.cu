@@ -882,6 +882,7 @@ int32_t launch_peer_barrier(void* const* flags, int32_t rank, int32_t world, int
 
 // ---- split of fp32 values into two TF32-exact parts -------------------------------------------------
 // hi = x with the 13 low mantissa bits cleared (what a TF32 multiplication reads), lo = x - hi (exact in fp32).
+// Per slice the A operand is laid out as (hi | lo | hi) and the B operand as (lo | hi | hi).
 __global__ void split_tf32_kernel(const float* __restrict__ x, int64_t ldx, float* __restrict__ out, int64_t rows,
                                   int64_t cols, int role, int64_t slice) {
   const int64_t total = rows * cols;
@@ -896,10 +897,13 @@ __global__ void split_tf32_kernel(const float* __restrict__ x, int64_t ldx, floa
     const float v = x[r * ldx + c];
     const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
     const float lo = v - hi;
+    // parts of a slice: (a_hi b_lo) and (a_lo b_hi) come first, (a_hi b_hi) last.  The small cross terms then add up
+    // while the accumulator is still tiny (its truncation steps are 2^-11 of the result's), and only the last third
+    // of the slice's instructions truncate an accumulator of full size.
     float* o = out + r * 3 * cols + 3 * first + (c - first);
-    o[0] = hi;
-    o[width] = role == 0 ? hi : lo;
-    o[2 * width] = role == 0 ? lo : hi;
+    o[0] = role == 0 ? hi : lo;
+    o[width] = role == 0 ? lo : hi;
+    o[2 * width] = hi;
   }
 }
 
