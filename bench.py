@@ -443,7 +443,7 @@ def run_ours(args, wl, name):
             main.wait_event(ready[slot])
             xb, gb = bufs[slot]
             out, dx = step(xb.detach(), gb)
-            loss = torch.dot(out.detach().reshape(-1).float(), gb.reshape(-1).float())  # loss = sum(out * g)
+            loss = torch.dot(out.detach().reshape(-1), gb.reshape(-1).to(out.dtype))  # loss = sum(out * g)
             consumed[slot].record(main)
             produced[slot].record(main)
             with torch.cuda.stream(copy_stream):  # results cross PCIe underneath the next step

@@ -9,7 +9,9 @@ from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_size_t, c_uin
 from pathlib import Path
 
 LIB_NAME = "libleanffn_b200.so"
-LIB_PATH = Path(__file__).resolve().parent / LIB_NAME
+# LEANFFN_LIBRARY names another build of the same library (for example a measurement build); default: next to this file
+LIB_PATH = Path(os.environ["LEANFFN_LIBRARY"]).resolve() if os.environ.get("LEANFFN_LIBRARY") else \
+    Path(__file__).resolve().parent / LIB_NAME
 
 # element types / activations / epilogues: keep in sync with include/leanffn_b200.h
 F32, BF16, TF32 = 0, 1, 2

@@ -214,6 +214,12 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
   for (int k = 0; k < 8; ++k) ep.scatter_D[k] = k < d->scatter_world ? d->scatter_D[k] : nullptr;
   ep.colsum = d->colsum_partial;
   ep.ldcolsum = d->ld_colsum;
+#ifdef LEANFFN_ABLATE_RUNTIME
+  {
+    const char* v = getenv("LEANFFN_ABLATE");  // read on every call: the measurement script changes it between runs
+    ep.ablate = v != nullptr ? atoi(v) : 0;
+  }
+#endif
 
   // ---- fp32 operands on the tensor cores (TF32 multiplication) ---------------------------------------
   if (d->in_dtype == LEANFFN_TF32) {

@@ -31,6 +31,7 @@ struct EpiParams {
   // activation-backward kinds: per-32-row partial column sums of D (the bias gradient), fp32 [ceil(M/32), ldcolsum]
   float* colsum;
   int64_t ldcolsum;
+  int32_t ablate;  // measurement builds only (LEANFFN_ABLATE_RUNTIME): bit mask of epilogue phases to leave out
 };
 
 __device__ __forceinline__ float load_any(const void* p, int32_t dtype, int64_t i) {

@@ -39,8 +39,25 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One try: the hardware may park the thread until the phase completes or `LEANFFN_WAIT_HINT_NS` nanoseconds have
+// passed, whichever comes first (it wakes on completion, so the hint adds no latency; it only makes a waiting role
+// issue fewer polling instructions, which matters on a power-capped part).  0 = the hardware's default limit.
+#ifndef LEANFFN_WAIT_HINT_NS
+#define LEANFFN_WAIT_HINT_NS 0
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if LEANFFN_WAIT_HINT_NS > 0
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(LEANFFN_WAIT_HINT_NS))
+      : "memory");
+#else
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
@@ -50,6 +67,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 

@@ -18,6 +18,16 @@ namespace leanffn {
 #define LEANFFN_EPI_LOOKAHEAD 0
 #endif
 
+// Measurement builds (-DLEANFFN_ABLATE_RUNTIME) can leave out phases of the fused epilogues at run time to see what
+// each costs (results are then wrong on purpose); in product builds the mask is the constant 0 and folds away.
+//   1: no residual / pre-activation loads   2: no global stores   4: no activation arithmetic   8: no column sums
+//   16: no shared-memory transposition      32: no tensor-memory read
+#ifdef LEANFFN_ABLATE_RUNTIME
+#define LEANFFN_ABLATE_MASK(ep) ((ep).ablate)
+#else
+#define LEANFFN_ABLATE_MASK(ep) 0
+#endif
+
 constexpr int EPI_PATCH_FLOATS = 32 * 33;  // per-warp patch: fp32 exchange uses row pitch 33 (conflict-free);
                                            // the bf16 exchange uses its first 2 KiB
 
@@ -143,12 +153,28 @@ __device__ __forceinline__ uint32_t patch_offset(int row, int chunk) {
 // TMEM block (lane = row) + bias, rounded to bf16 ->  w[i] = 8 packed values of (row 8*i + lane/4,
 // columns (lane%4)*8 .. +7) of the block.
 __device__ __forceinline__ void load_block_bf16(uint32_t taddr, float* patch, int lane, bool valid,
-                                                const float (&bias)[32], uint4 (&w)[4], bool has_bias = true) {
+                                                const float (&bias)[32], uint4 (&w)[4], bool has_bias = true,
+                                                int ablate = 0) {
   uint32_t r[32];
   __syncwarp();
-  tmem_ld_32x32(taddr, r);
-  tmem_ld_wait();
+  if (ablate & 32) {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) r[q] = 0x3f000000u + lane + q;
+  } else {
+    tmem_ld_32x32(taddr, r);
+    tmem_ld_wait();
+  }
   char* base = reinterpret_cast<char*>(patch);
+  if (ablate & 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[8 * i + q]);
+      w[i] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    }
+    return;
+  }
   if (!valid) {  // empty reduction (warp-uniform): the accumulator was never written
 #pragma unroll
     for (int q = 0; q < 32; ++q) r[q] = 0u;
@@ -230,6 +256,14 @@ __device__ __forceinline__ void halve_columns(float (&v)[NV], int lane, float (&
   }
 }
 
+// Which 32-column blocks of a tile a warp takes: the warps that share a lane quarter walk the blocks round-robin
+// (share, share + shares, ...).  Giving each warp pairs of neighbouring blocks, so that both 64-byte halves of every
+// 128-byte line are touched by one warp back to back, was measured and changes nothing.
+__device__ __forceinline__ int epi_block(int j, int share, int shares) { return share + j * shares; }
+__device__ __forceinline__ int epi_block_count(int num_blocks, int share, int shares) {
+  return (num_blocks - share + shares - 1) / shares;
+}
+
 // Activation on 8 values.  ACT >= 0: one inlined activation.  ACT < 0: the run-time switch lives in ONE
 // out-of-line copy, so rarely used activations do not bloat (and evict) the hot epilogue code.
 static __device__ __noinline__ void act_fwd8_generic(int act, float* x) {
@@ -280,7 +314,8 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       // tile columns [0,128): gate, [128,256): linear half; output feature j = n_blk*128 + column
       const int inter = glu_split;
 #pragma unroll 1
-      for (int blk = block_begin; blk < 4; blk += block_step) {
+      for (int jb = 0; jb < epi_block_count(4, block_begin, block_step); ++jb) {
+        const int blk = epi_block(jb, block_begin, block_step);
         const int64_t j0 = static_cast<int64_t>(n_blk) * 128 + blk * 32;
         const int64_t j = j0 + sub_col;
         const bool live = j < inter;
@@ -315,7 +350,8 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
     if (ep.d_dtype != LEANFFN_BF16) {
       // full-precision output: fp32 exchange
 #pragma unroll 1
-      for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
+      for (int jb = 0; jb < epi_block_count(BLOCK_N / 32, block_begin, block_step); ++jb) {
+        const int blk = epi_block(jb, block_begin, block_step);
         const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32 + sub_col;
         const bool live = col < ep.N;
         float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -351,7 +387,8 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
       return;
     }
 #pragma unroll 1
-    for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
+    for (int jb = 0; jb < epi_block_count(BLOCK_N / 32, block_begin, block_step); ++jb) {
+      const int blk = epi_block(jb, block_begin, block_step);
       const int64_t col0 = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
       const int64_t col = col0 + sub_col;
       const bool live = col < ep.N;
@@ -378,6 +415,8 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
     // waited for the accumulator (epilogue_prefetch_aux), so the request is an L2 hit that the transposition hides.
     // (Requesting one block further ahead costs 32 more registers per thread, which spilled in the hot loop.)
     constexpr bool LOOKAHEAD = LEANFFN_EPI_LOOKAHEAD != 0;
+    const int ab = LEANFFN_ABLATE_MASK(ep);
+    uint32_t sink = 0;  // measurement builds: keeps arithmetic alive when the stores are left out
     constexpr bool HAS_AUX =
         KIND == LEANFFN_EPI_DROPOUT_RESIDUAL || KIND == LEANFFN_EPI_GLU_BWD || KIND == LEANFFN_EPI_ACT_BWD;
     constexpr int NUM_BLOCKS = BLOCK_N / 32;
@@ -391,7 +430,9 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
         const int64_t row = row0 + 8 * i + sub_row;
         const bool ok = live && row < ep.M;
         n0[i] = n1[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (ok) {
+        if (ab & 1) {
+          n0[i] = n1[i] = make_uint4(0x3f003e80u, 0x3e003d80u, 0x3f003e80u, 0x3e003d80u);
+        } else if (ok) {
           if (KIND == LEANFFN_EPI_DROPOUT_RESIDUAL && ep.aux_dtype == LEANFFN_F32) {
             // fp32 residual: the 8 columns fill both register sets (n0: columns 0-3, n1: columns 4-7)
             const uint4* src = reinterpret_cast<const uint4*>(static_cast<const float*>(ep.aux) + row * ep.ldaux + col);
@@ -405,11 +446,13 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
         }
       }
     };
+    const int my_blocks = epi_block_count(NUM_BLOCKS, block_begin, block_step);
     if constexpr (HAS_AUX && LOOKAHEAD) {
-      if (block_begin < NUM_BLOCKS) request_aux(block_begin);
+      if (my_blocks > 0) request_aux(epi_block(0, block_begin, block_step));
     }
 #pragma unroll 1
-    for (int blk = block_begin; blk < NUM_BLOCKS; blk += block_step) {
+    for (int jb = 0; jb < my_blocks; ++jb) {
+      const int blk = epi_block(jb, block_begin, block_step);
       const int64_t col0 = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
       const int64_t col = col0 + sub_col;
       const bool live = col < ep.N;
@@ -419,21 +462,21 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
 #pragma unroll
         for (int i = 0; i < 4; ++i) c0[i] = n0[i], c1[i] = n1[i];
         if constexpr (LOOKAHEAD) {
-          if (blk + block_step < NUM_BLOCKS) request_aux(blk + block_step);
+          if (jb + 1 < my_blocks) request_aux(epi_block(jb + 1, block_begin, block_step));
         }
       }
       uint4 w[4];
       {
         float bias[32];
         load_bias32(ep.bias, ep.bias_dtype, col0, ep.N, bias);
-        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w, ep.bias != nullptr);
+        load_block_bf16(t_acc + blk * 32, patch, lane, acc_valid, bias, w, ep.bias != nullptr, ab);
       }
       constexpr bool IS_BWD = KIND == LEANFFN_EPI_GLU_BWD || KIND == LEANFFN_EPI_ACT_BWD;
       constexpr int NCS = KIND == LEANFFN_EPI_GLU_BWD ? 16 : 8;
       float cs[NCS];  // backward kinds: this lane's column sums of the ROUNDED values it stores (bias gradient)
 #pragma unroll
       for (int q = 0; q < NCS; ++q) cs[q] = 0.f;
-      const bool want_cs = IS_BWD && ep.colsum != nullptr;  // warp-uniform
+      const bool want_cs = IS_BWD && ep.colsum != nullptr && !(ab & 8);  // warp-uniform
       if (!live && !want_cs) continue;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -475,13 +518,23 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
           // two bf16 tensors (as in the unfused formulation, where each is a bf16 tensor) is a packed bf16 product.
           float gate[8], y[8], d[8];
           unpack8(c0[i], gate);
-          act_fwd_bwd8<ACT>(ep.act, gate, y, d);
+          if (ab & 4) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) y[q] = gate[q], d[q] = 1.0f;
+          } else {
+            act_fwd_bwd8<ACT>(ep.act, gate, y, d);
+          }
           const uint4 y2 = pack8(y), d2 = pack8(d);
           const uint4 dl = mul8(w[i], y2);                 // d/d(linear half) = dHid * act(gate)
           const uint4 dg = mul8(mul8(w[i], c1[i]), d2);    // d/d(gate) = dHid * lin * act'(gate)
-          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, dg);
-          store_packed8(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl);
-          if (ep.D2 != nullptr) store_packed8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, mul8(y2, c1[i]));  // remat hid
+          if (ab & 2) {
+            const uint4 hv = mul8(y2, c1[i]);
+            sink ^= dg.x ^ dg.y ^ dg.z ^ dg.w ^ dl.x ^ dl.y ^ dl.z ^ dl.w ^ hv.x ^ hv.y ^ hv.z ^ hv.w;
+          } else {
+            store_packed8(ep.D, ep.d_dtype, row * ep.ldd + col, dg);
+            store_packed8(ep.D, ep.d_dtype, row * ep.ldd + ep.N + col, dl);
+            if (ep.D2 != nullptr) store_packed8(ep.D2, ep.d_dtype, row * ep.ldd2 + col, mul8(y2, c1[i]));  // remat hid
+          }
           if (want_cs) {
             add_packed8(cs, dg);
             add_packed8(cs + 8, dl);
@@ -516,6 +569,7 @@ __device__ __forceinline__ void epilogue_tile_t(const EpiParams& ep, int glu_spl
         }
       }
     }
+    if (sink == 0x9E3779B9u && ep.D != nullptr) *static_cast<uint32_t*>(ep.D) = sink;  // never true in practice
   }
 }
 
@@ -531,9 +585,10 @@ __device__ __forceinline__ void epilogue_prefetch_aux(const EpiParams& ep, int64
   const int esize = ep.aux_dtype == LEANFFN_BF16 ? 2 : 4;
   const char* aux = static_cast<const char*>(ep.aux);
 #pragma unroll 1
-  for (int blk = block_begin; blk < BLOCK_N / 32; blk += block_step) {
+  for (int jb = 0; jb < epi_block_count(BLOCK_N / 32, block_begin, block_step); ++jb) {
+    const int blk = epi_block(jb, block_begin, block_step);
     const int64_t col = static_cast<int64_t>(n_blk) * BLOCK_N + blk * 32;
-    if (col >= ep.N) break;
+    if (col >= ep.N) continue;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int64_t row = row0 + 8 * i + (lane >> 2);
