@@ -19,7 +19,6 @@ namespace {
 
 constexpr size_t ALIGN = 256;
 inline size_t up(size_t n) { return (n + ALIGN - 1) / ALIGN * ALIGN; }
-inline size_t esz(int32_t dtype) { return dtype == LEANFFN_BF16 ? 2 : 4; }
 
 struct Carver {
   char* base;
@@ -36,7 +35,7 @@ struct FwdPlan {
   size_t bytes;
 };
 struct BwdPlan {
-  void *dyp, *dres, *dpre, *hid, *xhat, *dxhat, *glr1, *glr2, *dhid_plain;
+  void *dyp, *dres, *dpre, *hid, *xhat, *dxhat, *glr1, *glr2;
   float* partial;
   void* scratch;
   size_t bytes;

@@ -99,9 +99,16 @@ __device__ __forceinline__ void add_packed8(float* acc, const uint4& w) {
     acc[2 * h + 1] += __uint_as_float(u[h] & 0xFFFF0000u);
   }
 }
+#ifndef LEANFFN_EPI_STREAMING_STORES
+#define LEANFFN_EPI_STREAMING_STORES 0
+#endif
 __device__ __forceinline__ void store_packed8(void* base, int32_t dtype, int64_t elem, const uint4& w) {
   if (dtype == LEANFFN_BF16) {
+#if LEANFFN_EPI_STREAMING_STORES
+    __stcs(reinterpret_cast<uint4*>(static_cast<bf16*>(base) + elem), w);  // written once, read by a later kernel
+#else
     *reinterpret_cast<uint4*>(static_cast<bf16*>(base) + elem) = w;
+#endif
   } else {
     float v[8];
     unpack8(w, v);
