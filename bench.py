@@ -686,6 +686,52 @@ def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
     return out
 
 
+def epilogue_ablation(device):
+    """What each phase of the fused GeGLU-backward epilogue costs: times the input-gradient product of config 2
+    (16 384 x 1024 . 1024 x 4096) and of config 5 at 8192 tokens with phases of its epilogue left out.  Needs a
+    MEASUREMENT build of the library, which reads the mask from LEANFFN_ABLATE on every call (results are wrong on
+    purpose, nothing here is a bench number):
+
+        LEANFFN_NVCC_EXTRA=-DLEANFFN_ABLATE_RUNTIME=1 python lean_transformer_b200/build.py --force
+        python bench.py --epilogue-ablation
+
+    Mask bits: 1 no residual / pre-activation loads, 2 no global stores, 4 no activation arithmetic, 8 no column
+    sums, 16 no shared-memory transposition, 32 no tensor-memory read."""
+    from lean_transformer_b200 import _native as N
+    from lean_transformer_b200 import ops
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e3
+
+    report = {}
+    for tokens, hidden, inter, tag in ((16384, 1024, 4096, "config2"), (8192, 8192, 32768, "config5_8192_tokens")):
+        torch.manual_seed(0)
+        dy = torch.randn(tokens, hidden, device=device).bfloat16()
+        w2 = (torch.randn(hidden, inter, device=device) * 0.02).bfloat16()
+        pre = torch.randn(tokens, 2 * inter, device=device).bfloat16()
+        dpre, hid = torch.empty_like(pre), torch.empty(tokens, inter, device=device, dtype=torch.bfloat16)
+        partial = torch.empty((tokens + 31) // 32, 2 * inter, device=device)
+        plain = torch.empty(tokens, inter, device=device, dtype=torch.bfloat16)
+        entry = {}
+        for mask in (0, 1, 2, 4, 8, 16, 32, 3, 7, 63):
+            os.environ["LEANFFN_ABLATE"] = str(mask)
+            entry[f"mask_{mask}_us"] = timed(lambda: ops.gemm(dy, w2, b_mn_major=True, epilogue=N.EPI_GLU_BWD, act=0, aux=pre,
+                                                              out=dpre, out2=hid, colsum=partial))
+        os.environ["LEANFFN_ABLATE"] = "0"
+        entry["plain_store_us"] = timed(lambda: ops.gemm(dy, w2, b_mn_major=True, out=plain))
+        report[tag] = entry
+    print(json.dumps(dict(epilogue_ablation=report, note="measurement build only; mask 0 = the complete epilogue")), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -704,8 +750,15 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the workload's token count (smaller cases for ncu captures; not a bench number)")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling runs)")
+    ap.add_argument("--epilogue-ablation", action="store_true",
+                    help="time the GeGLU-backward product with phases of its epilogue left out (measurement build of "
+                         "the library only; see epilogue_ablation)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    if args.epilogue_ablation:
+        torch.cuda.set_device(0)
+        epilogue_ablation(torch.device("cuda", 0))
+        return
     wl = dict(WORKLOADS[args.workload])
     if args.tokens:
         wl["total_tokens" if "total_tokens" in wl else "tokens_per_rank"] = args.tokens
