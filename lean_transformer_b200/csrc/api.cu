@@ -333,6 +333,15 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
       if (d->a_mn_major) A2.rows = d->K2, A2.cols = d->M; else A2.rows = d->M, A2.cols = d->K2;
       if (d->b_mn_major) B2.rows = d->K2, B2.cols = d->N; else B2.rows = d->N, B2.cols = d->K2;
     }
+    static const int tile_override = []() {
+      const char* v = getenv("LEANFFN_GEMM_TILE");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    static const int group_override = []() {
+      const char* v = getenv("LEANFFN_GROUP_M");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    p.group_m = group_override;
     // Dense products with at least one full 256 x 256 tile can run on CTA pairs (cta_group::2).  Under the
     // 1 kW power cap of long runs the one-CTA kernel sustains the higher rate, so it is the default;
     // LEANFFN_GEMM_KERNEL=pair selects the CTA-pair kernel (it wins on short, cool bursts).
@@ -348,15 +357,6 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
     // Long reductions run 256 x 256 tiles per CTA (two accumulator sub-tiles sharing each B stage): a third less
     // operand traffic per flop; the exposed epilogue is a few percent of such a tile.  LEANFFN_GEMM_TILE=128 / 256
     // forces one or the other.
-    static const int tile_override = []() {
-      const char* v = getenv("LEANFFN_GEMM_TILE");
-      return v != nullptr ? atoi(v) : 0;
-    }();
-    static const int group_override = []() {
-      const char* v = getenv("LEANFFN_GROUP_M");
-      return v != nullptr ? atoi(v) : 0;
-    }();
-    p.group_m = group_override;
     p.m_subtiles = 1;
     if (d->bs_mode == 0 && block_n == 256 && d->M >= 256) {
       const int64_t k_total = k_eff + d->K2;

@@ -115,11 +115,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int pair_id = blockIdx.x >> 1;
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;  // in 256 x 256 tiles
   const int kb_total = p.num_k_blocks + p.num_k2_blocks;
-  const int group_size = GROUP_M * p.num_n_blocks;
+  const int group_m = p.group_m > 0 ? p.group_m : GROUP_M;
+  const int group_size = group_m * p.num_n_blocks;
   auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
     const int group = tile / group_size;
-    const int first_m = group * GROUP_M;
-    const int gm = min(p.num_m_blocks - first_m, GROUP_M);
+    const int first_m = group * group_m;
+    const int gm = min(p.num_m_blocks - first_m, group_m);
     const int in_group = tile - group * group_size;
     m_blk = first_m + in_group % gm;
     n_blk = in_group / gm;
