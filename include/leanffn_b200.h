@@ -68,7 +68,7 @@ extern "C" {
 #define LEANFFN_DEV_TIMEOUT_PEER 4 /* leanffn_peer_barrier: a rank did not arrive within the limit */
 
 /* Version of this header; leanffn_abi_version() returns the one the library was built from. */
-#define LEANFFN_ABI_VERSION 3
+#define LEANFFN_ABI_VERSION 4
 int32_t leanffn_abi_version(void);
 const char* leanffn_status_string(int32_t status);
 
@@ -440,6 +440,67 @@ int32_t leanffn_peer_barrier(void* const* flags, int32_t rank, int32_t world, in
  * gradient to the other ranks.  No counterpart in the reference. */
 int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const void* src, uint64_t src_pitch_bytes,
                         uint64_t width_bytes, uint64_t height, void* stream);
+
+/* ---- attention core -------------------------------------------------------------------------- */
+
+/* Scaled dot-product attention over heads without materialising the [q_len, kv_len] matrices:
+ *   out[b, q, h, :] = softmax_k(scale * <Q[b, q, h, :], K[b, k, h, :]> + mask[b, h, q, k]) . V[b, k, h, :]
+ * Replaces SimpleAttentionCore._attention_core_forward (lean_transformer/attn.py:111-149: the key scaling at :125-126,
+ * both torch.matmul calls at :132 and :146, the mask addition at :135, torch.softmax at :138, the head transposes at
+ * :117-129 and :147) and what autograd derives from it in the backward pass.
+ *
+ * q, k, v, out, d_out, dk, dv are bf16 [batch, len, heads * head_dim] with a row pitch ld_* (elements), so the three
+ * slices of one fused qkv projection output can be passed in place (attn.py:56-57).  head_dim is a multiple of 16,
+ * at most 128; pointers 16-byte aligned, pitches multiples of 8.
+ * mask: optional fp32 additive mask addressed as mask[b * mask_stride_b + h * mask_stride_h + q * mask_stride_q + k]
+ * (stride 0 broadcasts; 0 where attention is allowed, a large negative number where it is not, attn.py:99).
+ * causal != 0 additionally forbids k > q + (kv_len - q_len) and skips the tiles that rule empties.
+ * lse: fp32 [batch, heads, q_len], log2 of the softmax denominator with the row maximum folded in, written by the
+ * forward call and read by the backward call.
+ * Attention-probability dropout (attn.py:141-144) is not implemented: the host rejects p > 0.
+ *
+ * Backward needs, besides the forward's q, k, v, out and lse: delta (fp32 [batch, heads, q_len], scratch),
+ * dq_accum (fp32 [batch, q_len, heads * head_dim] contiguous, zeroed by the call, receives dQ; convert / un-rotate it
+ * with leanffn_rotary), dk and dv (bf16).  Device waits are bounded (status_word, wait_limit_cycles as in
+ * leanffn_gemm_desc). */
+typedef struct leanffn_attention_desc {
+  int32_t batch, heads, q_len, kv_len, head_dim;
+  int32_t causal;
+  float scale;
+  int32_t reserved0;
+  const void* q;
+  const void* k;
+  const void* v;
+  int64_t ld_q, ld_k, ld_v;
+  const float* mask;
+  int64_t mask_stride_b, mask_stride_h, mask_stride_q;
+  void* out;
+  int64_t ld_out;
+  float* lse;
+  /* backward only */
+  const void* d_out;
+  int64_t ld_dout;
+  float* delta;
+  float* dq_accum;
+  void* dk;
+  void* dv;
+  int64_t ld_dk, ld_dv;
+  int32_t* status_word;
+  int64_t wait_limit_cycles;
+} leanffn_attention_desc;
+
+int32_t leanffn_attention_forward(const leanffn_attention_desc* desc, void* stream);
+int32_t leanffn_attention_backward(const leanffn_attention_desc* desc, void* stream);
+
+/* Rotary position embedding over [batch, len, heads, head_dim] (lean_transformer/rotary.py:63-68, applied to queries
+ * and keys at attn.py:163-171):  y = x * cos + rotate_half(x) * sin with rotate_half(x) = (-x_right, x_left) and
+ * cos / sin fp32 tables [>= len, head_dim] (row pitch ld_table) as rotary.py:48-60 builds them; arithmetic in fp32,
+ * one rounding to y_dtype.  inverse != 0 applies the transposed rotation (the backward pass: y = x * cos -
+ * rotate_half(x * sin)).  cos == NULL copies / converts without rotating.  x: row pitch ld_x, y: row pitch ld_y
+ * (elements); head_dim even. */
+int32_t leanffn_rotary(const void* x, int32_t x_dtype, int64_t ld_x, const float* cos_table, const float* sin_table,
+                       int64_t ld_table, void* y, int32_t y_dtype, int64_t ld_y, int32_t batch, int32_t len,
+                       int32_t heads, int32_t head_dim, int32_t inverse, void* stream);
 
 #ifdef __cplusplus
 }

@@ -15,7 +15,7 @@ LIB_PATH = Path(os.environ["LEANFFN_LIBRARY"]).resolve() if os.environ.get("LEAN
 
 # element types / activations / epilogues: keep in sync with include/leanffn_b200.h
 F32, BF16, TF32 = 0, 1, 2
-ABI_VERSION = 3
+ABI_VERSION = 4
 ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_TANH, ACT_SIGMOID, ACT_IDENTITY = range(7)
 EPI_STORE, EPI_GLU_FWD, EPI_ACT_FWD, EPI_DROPOUT_RESIDUAL, EPI_GLU_BWD, EPI_ACT_BWD = range(6)
 DEV_STATUS_NAMES = {0: "ok", 1: "TMA producer wait timed out", 2: "MMA wait timed out", 3: "epilogue wait timed out",
@@ -82,7 +82,26 @@ class FfnGrads(ctypes.Structure):
         "grad_h2o_lowrank_second")]
 
 
+class AttentionDesc(ctypes.Structure):
+    """Mirror of ``leanffn_attention_desc``."""
+
+    _fields_ = [
+        ("batch", c_int32), ("heads", c_int32), ("q_len", c_int32), ("kv_len", c_int32), ("head_dim", c_int32),
+        ("causal", c_int32), ("scale", c_float), ("reserved0", c_int32),
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("ld_q", c_int64), ("ld_k", c_int64), ("ld_v", c_int64),
+        ("mask", c_void_p), ("mask_stride_b", c_int64), ("mask_stride_h", c_int64), ("mask_stride_q", c_int64),
+        ("out", c_void_p), ("ld_out", c_int64), ("lse", c_void_p),
+        ("d_out", c_void_p), ("ld_dout", c_int64), ("delta", c_void_p), ("dq_accum", c_void_p),
+        ("dk", c_void_p), ("dv", c_void_p), ("ld_dk", c_int64), ("ld_dv", c_int64),
+        ("status_word", c_void_p), ("wait_limit_cycles", c_int64),
+    ]
+
+
 _SIGNATURES = {
+    "leanffn_attention_forward": (c_int32, [POINTER(AttentionDesc), c_void_p]),
+    "leanffn_attention_backward": (c_int32, [POINTER(AttentionDesc), c_void_p]),
+    "leanffn_rotary": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_int64,
+                                 c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "leanffn_abi_version": (c_int32, []),
     "leanffn_status_string": (c_char_p, [c_int32]),
     "leanffn_layer_norm_forward": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int64,

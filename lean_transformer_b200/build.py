@@ -15,7 +15,8 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 INCLUDE = PACKAGE_DIR.parent / "include"
 LIB_PATH = PACKAGE_DIR / "libleanffn_b200.so"
-SOURCES = ["api.cu", "ffn_block.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_simt.cu", "rowops.cu"]
+SOURCES = ["api.cu", "ffn_block.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_simt.cu", "rowops.cu",
+           "attn_tcgen05.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

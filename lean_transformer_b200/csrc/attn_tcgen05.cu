@@ -1,0 +1,785 @@
+// Attention core on tcgen05: softmax(scale * Q.K^T + mask) . V per (batch, head) without the [q_len, kv_len]
+// matrices ever reaching global memory, forward and backward.
+//
+// One CTA of 128 threads owns a 128-row tile: thread t owns row t (TMEM lane t) of every accumulator.  Thread 0
+// also issues the TMA loads and the MMAs.  All tiles are [128 rows x 64 columns] bf16 boxes (16 KiB, 128-byte
+// swizzle) fetched through a 4D tensor map over the [batch, len, heads, head_dim] view, so the head split and
+// transposes of the reference are address arithmetic; head_dim > 64 takes two boxes.  The same bytes serve as the
+// K-major operand of one product and the MN-major operand of another (a [128 x 64] box is 128 rows of 128 bytes
+// either way), so every tile is fetched once:
+//   forward, per key tile j:   S = Q_i . K_j^T -> softmax rows online -> P (bf16, written by the threads in the
+//                              swizzled K-major layout) -> O_j = P . V_j, accumulated in registers with the
+//                              running-maximum correction;
+//   backward, per query tile i (one CTA per key tile j):
+//                              S = Q_i . K_j^T, dP = dO_i . V_j^T -> P = exp2(S - lse), dS = P * (dP - delta) * scale
+//                              -> dV += P^T . dO_i, dK += dS^T . Q_i (TMEM, whole loop), dQ_i = dS . K_j (added
+//                              to an fp32 buffer with vector reductions).
+// The two phases of an iteration are serial inside a CTA; several CTAs per SM (forward, head_dim <= 64) overlap
+// them.  Every mbarrier wait is bounded and followed by a block-wide vote, so either all threads continue or all
+// leave (status word set, TMEM freed).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+
+#include "../../include/leanffn_b200.h"
+#include "gemm_common.cuh"
+#include "ptx.cuh"
+
+namespace leanffn {
+
+bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int64_t len, int64_t heads,
+                          int64_t head_dim, int64_t ld);
+
+namespace attn {
+
+constexpr int TILE = 128;               // query rows / keys per tile
+constexpr int THREADS = 128;
+constexpr uint32_t BOX_BYTES = 128 * 64 * 2;   // one [128 x 64] bf16 box
+constexpr uint32_t PS_BYTES = 2 * BOX_BYTES;   // a [128 x 128] bf16 matrix written by the threads
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Params {
+  int32_t B, H, Sq, Skv, d;
+  int32_t causal;
+  float scale;
+  const float* mask;
+  int64_t mask_sb, mask_sh, mask_sq;
+  bf16* out;
+  int64_t ld_out;
+  float* lse;
+  const float* delta;
+  float* dq_acc;
+  bf16* dk;
+  bf16* dv;
+  int64_t ld_dk, ld_dv;
+  int32_t* status;
+  long long wait_limit;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap* tmap, uint32_t bar, int32_t x,
+                                            int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of the 16-byte piece `piece` (0..15: 8 keys each) of row `row` inside a thread-written [128 x 128]
+// bf16 matrix laid out as two [128 x 64] K-major boxes with the 128-byte swizzle the tensor cores expect.
+__device__ __forceinline__ uint32_t ps_offset(int row, int piece) {
+  const int box = piece >> 3, j = piece & 7;
+  return static_cast<uint32_t>(box) * BOX_BYTES + static_cast<uint32_t>(row >> 3) * 1024u +
+         static_cast<uint32_t>(row & 7) * 128u + static_cast<uint32_t>((j ^ (row & 7)) << 4);
+}
+
+// The values of one 32-key chunk of a score row in log2 units: acc * scale_log2 + mask * log2(e), -inf where the
+// key does not exist or the causal rule forbids it.
+__device__ __forceinline__ void score_chunk(const uint32_t (&acc)[32], float (&v)[32], float scale_log2,
+                                            const float* mask_row, int k0, int kv_len, int k_limit) {
+#pragma unroll
+  for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(acc[c]) * scale_log2;
+  if (mask_row != nullptr) {
+    if (k0 + 32 <= kv_len && (reinterpret_cast<uintptr_t>(mask_row + k0) & 15u) == 0) {
+      const float4* m4 = reinterpret_cast<const float4*>(mask_row + k0);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 m = __ldg(m4 + c);
+        v[4 * c + 0] = fmaf(m.x, LOG2E, v[4 * c + 0]);
+        v[4 * c + 1] = fmaf(m.y, LOG2E, v[4 * c + 1]);
+        v[4 * c + 2] = fmaf(m.z, LOG2E, v[4 * c + 2]);
+        v[4 * c + 3] = fmaf(m.w, LOG2E, v[4 * c + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (k0 + c < kv_len) v[c] = fmaf(__ldg(mask_row + k0 + c), LOG2E, v[c]);
+    }
+  }
+  if (k0 + 32 > k_limit) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c)
+      if (k0 + c >= k_limit) v[c] = -INFINITY;
+  }
+}
+
+struct Smem {
+  uint32_t base;     // 1024-aligned shared address of the tile area
+  uint8_t* gen;      // the same address as a generic pointer
+};
+
+__device__ __forceinline__ Smem align_smem(uint8_t* raw) {
+  Smem s;
+  const uint32_t a = smem_u32(raw);
+  s.base = (a + 1023u) & ~1023u;
+  s.gen = raw + (s.base - a);
+  return s;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Forward.  grid = (query tiles, heads, batch).  DPAD = head_dim rounded up to 32 (registers of the output row).
+// Shared memory: Q, K, V (DC boxes each, DC = ceil(head_dim / 64)), P (2 boxes), barriers.
+// TMEM: columns [0, 128) S, [128, 128 + head_dim) the product P . V_j.
+template <int DPAD>
+__global__ void __launch_bounds__(THREADS)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const Smem sm = align_smem(smem_raw);
+  const int DC = (p.d + 63) >> 6;
+  const uint32_t tile_bytes = DC * BOX_BYTES;
+  const uint32_t sQ = sm.base, sK = sQ + tile_bytes, sV = sK + tile_bytes, sP = sV + tile_bytes;
+  const uint32_t bar0 = sP + PS_BYTES;
+  const uint32_t bar_q = bar0, bar_k = bar0 + 8, bar_v = bar0 + 16, bar_mma = bar0 + 24, tmem_slot = bar0 + 32;
+  uint8_t* gP = sm.gen + 3 * tile_bytes;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 3 * tile_bytes + PS_BYTES + 32);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + TILE - 1) / TILE;
+  const int qt = nq - 1 - static_cast<int>(blockIdx.x);  // long (late) rows first under the causal rule
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int off = p.Skv - p.Sq;
+  int nkv = nkv_all;
+  if (p.causal) {
+    const int last_q = min(qt * TILE + TILE - 1, p.Sq - 1);
+    const int last_k = last_q + off;  // largest key any row of the tile may see
+    nkv = last_k < 0 ? 0 : min(nkv_all, last_k / TILE + 1);
+  }
+  const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);  // this warp's 32 lanes
+
+  auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
+    mbar_arrive_expect_tx(bar, tile_bytes);
+    for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+  };
+  bool ok = true;
+  auto wait_all = [&](uint32_t bar, uint32_t parity) {
+    const bool mine = mbar_wait_bounded(bar, parity, limit);
+    return __syncthreads_and(mine) != 0;
+  };
+
+  if (tid == 0 && nkv > 0) {
+    load_tile(&tmQ, sQ, bar_q, qt * TILE);
+    load_tile(&tmK, sK, bar_k, 0);
+    load_tile(&tmV, sV, bar_v, 0);
+  }
+
+  const int q_row = qt * TILE + tid;
+  const int q_clamped = min(q_row, p.Sq - 1);
+  const float* mask_row = p.mask == nullptr ? nullptr
+                                            : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
+  const float scale_log2 = p.scale * LOG2E;
+  const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
+
+  float o_acc[DPAD];
+#pragma unroll
+  for (int x = 0; x < DPAD; ++x) o_acc[x] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  uint32_t mma_phase = 0;
+
+  const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+  const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
+  constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
+  constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
+
+  if (nkv > 0) ok = wait_all(bar_q, 0);
+  for (int j = 0; j < nkv && ok; ++j) {
+    ok = wait_all(bar_k, j & 1);
+    if (!ok) break;
+    if (tid == 0) {
+      tc_fence_after();
+      const int ksteps = p.d >> 4;
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+        umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_mma);
+    }
+    ok = wait_all(bar_mma, mma_phase);
+    mma_phase ^= 1u;
+    if (!ok) break;
+    if (tid == 0 && j + 1 < nkv) load_tile(&tmK, sK, bar_k, (j + 1) * TILE);  // K_j has been consumed
+    tc_fence_after();
+
+    // ---- softmax of this row over the tile: maximum first, then the probabilities ----
+    const int k0 = j * TILE;
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t acc[32];
+      float v[32];
+      tmem_ld_32x32(t_row + c * 32, acc);
+      tmem_ld_wait();
+      score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+      for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = exp2f(m_run - m_use);
+    float row_sum = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t acc[32];
+      float v[32];
+      tmem_ld_32x32(t_row + c * 32, acc);
+      tmem_ld_wait();
+      score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        v[x] = exp2f(v[x] - m_use);
+        row_sum += v[x];
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 w;
+        w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+        w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+        w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+        w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+        *reinterpret_cast<uint4*>(gP + ps_offset(tid, c * 4 + q4)) = w;
+      }
+    }
+    l_run = l_run * alpha + row_sum;
+    m_run = m_new;
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    ok = wait_all(bar_v, j & 1);
+    if (!ok) break;
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+        umma_bf16(tmem + 128, make_smem_desc(sP + oa, k_major_hi), make_smem_desc(sV + ks * 2048u, mn_major_hi), idesc_o,
+                  ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_mma);
+    }
+    ok = wait_all(bar_mma, mma_phase);
+    mma_phase ^= 1u;
+    if (!ok) break;
+    if (tid == 0 && j + 1 < nkv) load_tile(&tmV, sV, bar_v, (j + 1) * TILE);
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < DPAD / 32; ++c) {
+      uint32_t acc[32];
+      tmem_ld_32x32(t_row + 128 + c * 32, acc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 32; ++x) o_acc[c * 32 + x] = fmaf(o_acc[c * 32 + x], alpha, __uint_as_float(acc[x]));
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  if (ok) {
+    if (q_row < p.Sq) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* dst = p.out + (static_cast<int64_t>(b) * p.Sq + q_row) * p.ld_out + static_cast<int64_t>(h) * p.d;
+#pragma unroll
+      for (int x = 0; x < DPAD; x += 8) {
+        if (x < p.d) {
+          uint4 w;
+          w.x = pack_bf16x2(o_acc[x + 0] * inv, o_acc[x + 1] * inv);
+          w.y = pack_bf16x2(o_acc[x + 2] * inv, o_acc[x + 3] * inv);
+          w.z = pack_bf16x2(o_acc[x + 4] * inv, o_acc[x + 5] * inv);
+          w.w = pack_bf16x2(o_acc[x + 6] * inv, o_acc[x + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + x) = w;
+        }
+      }
+      // rows that saw no key at all get +inf so that the backward pass turns their probabilities into zeros
+      p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_run > 0.f ? m_run + log2f(l_run) : INFINITY;
+    }
+  } else {
+    if (tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// delta[b, h, q] = sum_x dO[b, q, h, x] * O[b, q, h, x]
+__global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t ld_dout, const bf16* __restrict__ out,
+                                       int64_t ld_out, float* __restrict__ delta, int B, int H, int Sq, int d) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(B) * Sq * H;
+  if (idx >= total) return;
+  const int h = static_cast<int>(idx % H);
+  const int64_t bq = idx / H;  // b * Sq + q
+  const uint4* a = reinterpret_cast<const uint4*>(d_out + bq * ld_dout + static_cast<int64_t>(h) * d);
+  const uint4* o = reinterpret_cast<const uint4*>(out + bq * ld_out + static_cast<int64_t>(h) * d);
+  float s = 0.f;
+  for (int x = 0; x < d / 8; ++x) {
+    const uint4 av = __ldg(a + x), ov = __ldg(o + x);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 af = __bfloat1622float2(a2[i]), of = __bfloat1622float2(o2[i]);
+      s = fmaf(af.x, of.x, s);
+      s = fmaf(af.y, of.y, s);
+    }
+  }
+  const int64_t b = bq / Sq, q = bq - b * Sq;
+  delta[(b * H + h) * Sq + q] = s;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Backward.  grid = (key tiles, heads, batch).  Shared memory: K, V, Q, dO (DC boxes each), P, dS (2 boxes each).
+// TMEM (512 columns): [0, 128) S, then dQ_i; [128, 256) dP; [256, 256 + d) dV; [384, 384 + d) dK.
+template <int DPAD>
+__global__ void __launch_bounds__(THREADS, 1)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const Smem sm = align_smem(smem_raw);
+  const int DC = (p.d + 63) >> 6;
+  const uint32_t tile_bytes = DC * BOX_BYTES;
+  const uint32_t sK = sm.base, sV = sK + tile_bytes, sQ = sV + tile_bytes, sdO = sQ + tile_bytes;
+  const uint32_t sP = sdO + tile_bytes, sdS = sP + PS_BYTES;
+  const uint32_t bar0 = sdS + PS_BYTES;
+  const uint32_t bar_kv = bar0, bar_q = bar0 + 8, bar_mma = bar0 + 16, tmem_slot = bar0 + 32;
+  uint8_t* gP = sm.gen + 4 * tile_bytes;
+  uint8_t* gdS = gP + PS_BYTES;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 32);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int nq = (p.Sq + TILE - 1) / TILE;
+  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int off = p.Skv - p.Sq;
+  int i_start = 0;
+  if (p.causal) {
+    const int first_q = kt * TILE - off;  // smallest query row that may see the first key of this tile
+    i_start = first_q <= 0 ? 0 : first_q / TILE;
+  }
+  const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
+
+  if (tid == 0) {
+    mbar_init(bar_kv, 1);
+    mbar_init(bar_q, 1);
+    mbar_init(bar_mma, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmdO);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  auto load_boxes = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
+    for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+  };
+  bool ok = true;
+  auto wait_all = [&](uint32_t bar, uint32_t parity) {
+    const bool mine = mbar_wait_bounded(bar, parity, limit);
+    return __syncthreads_and(mine) != 0;
+  };
+
+  const bool any = i_start < nq;
+  if (tid == 0 && any) {
+    mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
+    load_boxes(&tmK, sK, bar_kv, kt * TILE);
+    load_boxes(&tmV, sV, bar_kv, kt * TILE);
+    mbar_arrive_expect_tx(bar_q, 2 * tile_bytes);
+    load_boxes(&tmQ, sQ, bar_q, i_start * TILE);
+    load_boxes(&tmdO, sdO, bar_q, i_start * TILE);
+  }
+
+  const float scale_log2 = p.scale * LOG2E;
+  const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S and dP: both operands K-major
+  const uint32_t idesc_t = make_idesc_bf16(128, p.d, true, true);     // dV, dK: P^T / dS^T (MN-major A), MN-major B
+  const uint32_t idesc_q = make_idesc_bf16(128, p.d, false, true);    // dQ: dS K-major, K_j MN-major
+  constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
+  constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
+  uint32_t mma_phase = 0;
+
+  if (any) ok = wait_all(bar_kv, 0);
+  for (int i = i_start; i < nq && ok; ++i) {
+    ok = wait_all(bar_q, (i - i_start) & 1);
+    if (!ok) break;
+    if (tid == 0) {
+      tc_fence_after();
+      const int ksteps = p.d >> 4;
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+        umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
+      }
+      for (int ks = 0; ks < ksteps; ++ks) {
+        const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+        umma_bf16(tmem + 128, make_smem_desc(sdO + o, k_major_hi), make_smem_desc(sV + o, k_major_hi), idesc_s,
+                  ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_mma);
+    }
+    ok = wait_all(bar_mma, mma_phase);
+    mma_phase ^= 1u;
+    if (!ok) break;
+    tc_fence_after();
+
+    const int q_row = i * TILE + tid;
+    const bool q_valid = q_row < p.Sq;
+    const int q_clamped = min(q_row, p.Sq - 1);
+    const int64_t stat = (static_cast<int64_t>(b) * p.H + h) * p.Sq + q_clamped;
+    const float lse = q_valid ? __ldg(p.lse + stat) : INFINITY;  // +inf: the row's probabilities become zero
+    const float dlt = q_valid ? __ldg(p.delta + stat) : 0.f;
+    const float* mask_row = p.mask == nullptr ? nullptr
+                                              : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
+    const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
+    const int k0 = kt * TILE;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t acc[32], dp[32];
+      float v[32];
+      tmem_ld_32x32(t_row + c * 32, acc);
+      tmem_ld_32x32(t_row + 128 + c * 32, dp);
+      tmem_ld_wait();
+      score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+      float ds[32];
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        v[x] = exp2f(v[x] - lse);
+        ds[x] = v[x] * (__uint_as_float(dp[x]) - dlt) * p.scale;
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 w;
+        w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+        w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+        w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+        w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+        const uint32_t o = ps_offset(tid, c * 4 + q4);
+        *reinterpret_cast<uint4*>(gP + o) = w;
+        w.x = pack_bf16x2(ds[8 * q4 + 0], ds[8 * q4 + 1]);
+        w.y = pack_bf16x2(ds[8 * q4 + 2], ds[8 * q4 + 3]);
+        w.z = pack_bf16x2(ds[8 * q4 + 4], ds[8 * q4 + 5]);
+        w.w = pack_bf16x2(ds[8 * q4 + 6], ds[8 * q4 + 7]);
+        *reinterpret_cast<uint4*>(gdS + o) = w;
+      }
+    }
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t first = i == i_start ? 0u : 1u;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)  // dV[key, x] += sum_q P[q, key] * dO[q, x]
+        umma_bf16(tmem + 256, make_smem_desc(sP + ks * 2048u, mn_major_hi), make_smem_desc(sdO + ks * 2048u, mn_major_hi),
+                  idesc_t, ks > 0 ? 1u : first);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)  // dK[key, x] += sum_q dS[q, key] * Q[q, x]
+        umma_bf16(tmem + 384, make_smem_desc(sdS + ks * 2048u, mn_major_hi), make_smem_desc(sQ + ks * 2048u, mn_major_hi),
+                  idesc_t, ks > 0 ? 1u : first);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {  // dQ[q, x] = sum_key dS[q, key] * K[key, x]
+        const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+        umma_bf16(tmem, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi), idesc_q,
+                  ks > 0 ? 1u : 0u);
+      }
+      umma_commit(bar_mma);
+    }
+    ok = wait_all(bar_mma, mma_phase);
+    mma_phase ^= 1u;
+    if (!ok) break;
+    if (tid == 0 && i + 1 < nq) {  // Q_i and dO_i have been consumed
+      mbar_arrive_expect_tx(bar_q, 2 * tile_bytes);
+      load_boxes(&tmQ, sQ, bar_q, (i + 1) * TILE);
+      load_boxes(&tmdO, sdO, bar_q, (i + 1) * TILE);
+    }
+    tc_fence_after();
+    {
+      float* dst = p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q_clamped) * (static_cast<int64_t>(p.H) * p.d) +
+                   static_cast<int64_t>(h) * p.d;
+#pragma unroll
+      for (int c = 0; c < DPAD / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_32x32(t_row + c * 32, acc);
+        tmem_ld_wait();
+        if (q_valid) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 4)
+            if (c * 32 + x < p.d)
+              red_add_v4(dst + c * 32 + x, __uint_as_float(acc[x]), __uint_as_float(acc[x + 1]),
+                         __uint_as_float(acc[x + 2]), __uint_as_float(acc[x + 3]));
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  if (ok) {
+    // tcgen05.ld is warp-collective: every thread reads its lane, only the rows that exist are stored
+    const int key = kt * TILE + tid;
+    const bool key_valid = key < p.Skv;
+    const int64_t key_row = static_cast<int64_t>(b) * p.Skv + min(key, p.Skv - 1);
+    bf16* dv = p.dv + key_row * p.ld_dv + static_cast<int64_t>(h) * p.d;
+    bf16* dk = p.dk + key_row * p.ld_dk + static_cast<int64_t>(h) * p.d;
+#pragma unroll
+    for (int c = 0; c < DPAD / 32; ++c) {
+      uint32_t av[32], ak[32];
+      if (any) {
+        tmem_ld_32x32(t_row + 256 + c * 32, av);
+        tmem_ld_32x32(t_row + 384 + c * 32, ak);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) av[x] = 0u, ak[x] = 0u;
+      }
+      if (key_valid) {
+#pragma unroll
+        for (int x = 0; x < 32; x += 8) {
+          if (c * 32 + x < p.d) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(av[x + 0]), __uint_as_float(av[x + 1]));
+            w.y = pack_bf16x2(__uint_as_float(av[x + 2]), __uint_as_float(av[x + 3]));
+            w.z = pack_bf16x2(__uint_as_float(av[x + 4]), __uint_as_float(av[x + 5]));
+            w.w = pack_bf16x2(__uint_as_float(av[x + 6]), __uint_as_float(av[x + 7]));
+            *reinterpret_cast<uint4*>(dv + c * 32 + x) = w;
+            w.x = pack_bf16x2(__uint_as_float(ak[x + 0]), __uint_as_float(ak[x + 1]));
+            w.y = pack_bf16x2(__uint_as_float(ak[x + 2]), __uint_as_float(ak[x + 3]));
+            w.z = pack_bf16x2(__uint_as_float(ak[x + 4]), __uint_as_float(ak[x + 5]));
+            w.w = pack_bf16x2(__uint_as_float(ak[x + 6]), __uint_as_float(ak[x + 7]));
+            *reinterpret_cast<uint4*>(dk + c * 32 + x) = w;
+          }
+        }
+      }
+    }
+  } else {
+    if (tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Rotary embedding (and plain conversion) over [batch * len, heads, head_dim]; one thread per pair (x_left, x_right).
+template <typename TI, typename TO>
+__global__ void rotary_kernel(const TI* __restrict__ x, int64_t ld_x, const float* __restrict__ cos_t,
+                              const float* __restrict__ sin_t, int64_t ld_t, TO* __restrict__ y, int64_t ld_y,
+                              int64_t rows, int len, int heads, int d, int inverse) {
+  const int half = d >> 1;
+  const int64_t per_row = static_cast<int64_t>(heads) * half;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const int64_t row = idx / per_row;
+  const int rem = static_cast<int>(idx - row * per_row);
+  const int hh = rem / half, i = rem - hh * half;
+  const int pos = static_cast<int>(row % len);
+  const int64_t xo = row * ld_x + static_cast<int64_t>(hh) * d, yo = row * ld_y + static_cast<int64_t>(hh) * d;
+  const float xl = static_cast<float>(x[xo + i]), xr = static_cast<float>(x[xo + half + i]);
+  float yl = xl, yr = xr;
+  if (cos_t != nullptr) {
+    const float cl = cos_t[pos * ld_t + i], cr = cos_t[pos * ld_t + half + i];
+    const float sl = sin_t[pos * ld_t + i], sr = sin_t[pos * ld_t + half + i];
+    if (!inverse) {
+      yl = xl * cl - xr * sl;   // x * cos + (-x_right) * sin
+      yr = xr * cr + xl * sr;   // x * cos + x_left * sin
+    } else {
+      yl = xl * cl + xr * sr;
+      yr = xr * cr - xl * sl;
+    }
+  }
+  y[yo + i] = static_cast<TO>(yl);
+  y[yo + half + i] = static_cast<TO>(yr);
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int32_t validate(const leanffn_attention_desc* d, bool backward) {
+  if (d == nullptr || d->q == nullptr || d->k == nullptr || d->v == nullptr || d->out == nullptr || d->lse == nullptr)
+    return LEANFFN_ERR_NULL;
+  if (d->batch <= 0 || d->heads <= 0 || d->q_len <= 0 || d->kv_len <= 0) return LEANFFN_ERR_SHAPE;
+  if (d->head_dim < 16 || d->head_dim > 128 || d->head_dim % 16 != 0) return LEANFFN_ERR_UNSUPPORTED;
+  const int64_t width = static_cast<int64_t>(d->heads) * d->head_dim;
+  if (d->ld_q < width || d->ld_k < width || d->ld_v < width || d->ld_out < width) return LEANFFN_ERR_SHAPE;
+  if (d->ld_q % 8 || d->ld_k % 8 || d->ld_v % 8 || d->ld_out % 8) return LEANFFN_ERR_ALIGN;
+  if (!aligned16(d->q) || !aligned16(d->k) || !aligned16(d->v) || !aligned16(d->out)) return LEANFFN_ERR_ALIGN;
+  if (d->batch > 65535 || d->heads > 65535) return LEANFFN_ERR_TOO_LARGE;
+  if (backward) {
+    if (d->d_out == nullptr || d->delta == nullptr || d->dq_accum == nullptr || d->dk == nullptr || d->dv == nullptr)
+      return LEANFFN_ERR_NULL;
+    if (d->ld_dout < width || d->ld_dk < width || d->ld_dv < width) return LEANFFN_ERR_SHAPE;
+    if (d->ld_dout % 8 || d->ld_dk % 8 || d->ld_dv % 8) return LEANFFN_ERR_ALIGN;
+    if (!aligned16(d->d_out) || !aligned16(d->dk) || !aligned16(d->dv) || !aligned16(d->dq_accum)) return LEANFFN_ERR_ALIGN;
+  }
+  return LEANFFN_OK;
+}
+
+static Params make_params(const leanffn_attention_desc* d) {
+  Params p{};
+  p.B = d->batch, p.H = d->heads, p.Sq = d->q_len, p.Skv = d->kv_len, p.d = d->head_dim;
+  p.causal = d->causal;
+  p.scale = d->scale;
+  p.mask = d->mask;
+  p.mask_sb = d->mask_stride_b, p.mask_sh = d->mask_stride_h, p.mask_sq = d->mask_stride_q;
+  p.out = static_cast<bf16*>(d->out);
+  p.ld_out = d->ld_out;
+  p.lse = d->lse;
+  p.delta = d->delta;
+  p.dq_acc = d->dq_accum;
+  p.dk = static_cast<bf16*>(d->dk);
+  p.dv = static_cast<bf16*>(d->dv);
+  p.ld_dk = d->ld_dk, p.ld_dv = d->ld_dv;
+  p.status = d->status_word;
+  p.wait_limit = d->wait_limit_cycles;
+  return p;
+}
+
+template <typename K>
+static cudaError_t set_smem(K kern, size_t bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+}
+
+}  // namespace attn
+}  // namespace leanffn
+
+using namespace leanffn;
+
+extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, void* stream) {
+  const int32_t v = attn::validate(d, false);
+  if (v != LEANFFN_OK) return v;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tk, tv;
+  if (!make_tmap_bf16_heads(&tq, d->q, d->batch, d->q_len, d->heads, d->head_dim, d->ld_q) ||
+      !make_tmap_bf16_heads(&tk, d->k, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_k) ||
+      !make_tmap_bf16_heads(&tv, d->v, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_v))
+    return LEANFFN_ERR_DRIVER;
+  const attn::Params p = attn::make_params(d);
+  const int dc = (d->head_dim + 63) / 64;
+  const size_t smem = 3 * dc * attn::BOX_BYTES + attn::PS_BYTES + 64 + 1024;
+  const dim3 grid((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
+  cudaError_t e;
+#define ATTN_FWD(DPAD)                                                             \
+  {                                                                                \
+    auto kern = attn::attention_fwd_kernel<DPAD>;                                  \
+    e = attn::set_smem(kern, smem);                                                \
+    if (e == cudaSuccess) {                                                        \
+      kern<<<grid, attn::THREADS, smem, st>>>(tq, tk, tv, p);                      \
+      e = cudaGetLastError();                                                      \
+    }                                                                              \
+  }
+  if (d->head_dim <= 32) ATTN_FWD(32)
+  else if (d->head_dim <= 64) ATTN_FWD(64)
+  else if (d->head_dim <= 96) ATTN_FWD(96)
+  else ATTN_FWD(128)
+#undef ATTN_FWD
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+}
+
+extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, void* stream) {
+  const int32_t v = attn::validate(d, true);
+  if (v != LEANFFN_OK) return v;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_tmap_bf16_heads(&tq, d->q, d->batch, d->q_len, d->heads, d->head_dim, d->ld_q) ||
+      !make_tmap_bf16_heads(&tk, d->k, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_k) ||
+      !make_tmap_bf16_heads(&tv, d->v, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_v) ||
+      !make_tmap_bf16_heads(&tdo, d->d_out, d->batch, d->q_len, d->heads, d->head_dim, d->ld_dout))
+    return LEANFFN_ERR_DRIVER;
+  const attn::Params p = attn::make_params(d);
+  const int64_t rows = static_cast<int64_t>(d->batch) * d->q_len * d->heads;
+  cudaError_t e = cudaMemsetAsync(d->dq_accum, 0, static_cast<size_t>(rows) * d->head_dim * sizeof(float), st);
+  if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+  attn::attention_delta_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, st>>>(
+      static_cast<const bf16*>(d->d_out), d->ld_dout, static_cast<const bf16*>(d->out), d->ld_out, d->delta, d->batch,
+      d->heads, d->q_len, d->head_dim);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
+  const int dc = (d->head_dim + 63) / 64;
+  const size_t smem = 4 * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 64 + 1024;
+  const dim3 grid((d->kv_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
+#define ATTN_BWD(DPAD)                                                             \
+  {                                                                                \
+    auto kern = attn::attention_bwd_kernel<DPAD>;                                  \
+    e = attn::set_smem(kern, smem);                                                \
+    if (e == cudaSuccess) {                                                        \
+      kern<<<grid, attn::THREADS, smem, st>>>(tq, tk, tv, tdo, p);                 \
+      e = cudaGetLastError();                                                      \
+    }                                                                              \
+  }
+  if (d->head_dim <= 32) ATTN_BWD(32)
+  else if (d->head_dim <= 64) ATTN_BWD(64)
+  else if (d->head_dim <= 96) ATTN_BWD(96)
+  else ATTN_BWD(128)
+#undef ATTN_BWD
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+}
+
+extern "C" int32_t leanffn_rotary(const void* x, int32_t x_dtype, int64_t ld_x, const float* cos_table,
+                                  const float* sin_table, int64_t ld_table, void* y, int32_t y_dtype, int64_t ld_y,
+                                  int32_t batch, int32_t len, int32_t heads, int32_t head_dim, int32_t inverse,
+                                  void* stream) {
+  if (x == nullptr || y == nullptr) return LEANFFN_ERR_NULL;
+  if ((cos_table == nullptr) != (sin_table == nullptr)) return LEANFFN_ERR_NULL;
+  if (batch <= 0 || len <= 0 || heads <= 0 || head_dim <= 0 || head_dim % 2 != 0) return LEANFFN_ERR_SHAPE;
+  const int64_t width = static_cast<int64_t>(heads) * head_dim;
+  if (ld_x < width || ld_y < width || (cos_table != nullptr && ld_table < head_dim)) return LEANFFN_ERR_SHAPE;
+  if ((x_dtype != LEANFFN_F32 && x_dtype != LEANFFN_BF16) || (y_dtype != LEANFFN_F32 && y_dtype != LEANFFN_BF16))
+    return LEANFFN_ERR_DTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rows = static_cast<int64_t>(batch) * len;
+  const int64_t total = rows * heads * (head_dim / 2);
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+#define ROTARY(TI, TO)                                                                                         \
+  attn::rotary_kernel<TI, TO><<<blocks, 256, 0, st>>>(static_cast<const TI*>(x), ld_x, cos_table, sin_table,   \
+                                                      ld_table, static_cast<TO*>(y), ld_y, rows, len, heads,   \
+                                                      head_dim, inverse)
+  if (x_dtype == LEANFFN_BF16 && y_dtype == LEANFFN_BF16) ROTARY(bf16, bf16);
+  else if (x_dtype == LEANFFN_BF16) ROTARY(bf16, float);
+  else if (y_dtype == LEANFFN_BF16) ROTARY(float, bf16);
+  else ROTARY(float, float);
+#undef ROTARY
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+}

@@ -477,3 +477,116 @@ def ffn_backward(desc, grad_out, x, pre_activation, i2h_lowrank_hid, h2o_lowrank
     N.check(N.lib.leanffn_ffn_backward(desc, _ptr(grad_out), _ptr(x), _ptr(pre_activation), _ptr(i2h_lowrank_hid),
                                        _ptr(h2o_lowrank_hid), grads, _ptr(workspace), _stream(x)), "leanffn_ffn_backward")
     _count(launches)
+
+
+# ---- attention core ---------------------------------------------------------------------------------------------------
+def _rows_view(t: torch.Tensor) -> torch.Tensor:
+    """[batch, len, width] tensor whose (batch, len) rows lie at one pitch (e.g. a slice of a fused qkv output); anything
+    else is made contiguous."""
+    if t.dim() != 3:
+        raise ValueError(f"expected [batch, len, hidden], got {tuple(t.shape)}")
+    if t.stride(2) == 1 and t.stride(0) == t.shape[1] * t.stride(1) and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
+def rotary(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], heads: int, *, inverse: bool = False,
+           out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Rotary embedding of x [batch, len, heads * head_dim] with fp32 tables [>= len, head_dim] (``leanffn_rotary``);
+    ``inverse`` applies the transposed rotation (gradients).  Without tables: a dtype conversion into a contiguous
+    tensor."""
+    _require_cuda(x)
+    x = _rows_view(x)
+    batch, length, width = x.shape
+    head_dim = width // heads
+    if cos is not None:
+        if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.stride(-1) != 1 or sin.stride() != cos.stride():
+            raise ValueError("rotary tables must be float32 with unit inner stride and equal pitches")
+        if cos.shape[0] < length or cos.shape[-1] != head_dim:
+            raise ValueError(f"rotary tables {tuple(cos.shape)} do not cover length {length} x head_dim {head_dim}")
+    y = torch.empty(batch, length, width, dtype=out_dtype, device=x.device)
+    N.check(N.lib.leanffn_rotary(_ptr(x), _dt(x), x.stride(1), _ptr(cos), _ptr(sin), 0 if cos is None else cos.stride(0),
+                                 _ptr(y), _dt(y), width, batch, length, heads, head_dim, int(inverse), _stream(x)),
+            "leanffn_rotary")
+    _count()
+    return y
+
+
+def _mask_strides(mask: Optional[torch.Tensor], batch: int, heads: int, q_len: int, kv_len: int):
+    """(tensor kept alive, strides over batch / head / query) of an additive mask broadcastable to
+    [batch, heads, q_len, kv_len]."""
+    if mask is None:
+        return None, (0, 0, 0)
+    if not torch.is_floating_point(mask):
+        raise TypeError("expected float mask with negative values for masked items")
+    if mask.dim() == 3:
+        mask = mask.unsqueeze(1)
+    if mask.dim() != 4:
+        raise ValueError(f"attention mask must be [batch, (heads), q_len, kv_len], got {tuple(mask.shape)}")
+    if mask.dtype != torch.float32 or mask.shape[-1] != kv_len or mask.stride(-1) != 1:
+        mask = mask.to(torch.float32).expand(*mask.shape[:-1], kv_len).contiguous()
+    for size, full in zip(mask.shape[:3], (batch, heads, q_len)):
+        if size not in (1, full):
+            raise ValueError(f"attention mask {tuple(mask.shape)} does not broadcast to "
+                             f"[{batch}, {heads}, {q_len}, {kv_len}]")
+    strides = tuple(0 if mask.shape[i] == 1 else mask.stride(i) for i in range(3))
+    return mask, strides
+
+
+def _attention_desc(q, k, v, heads, scale, mask, causal):
+    batch, q_len, width = q.shape
+    kv_len = k.shape[1]
+    if width % heads != 0:
+        raise ValueError(f"hidden size {width} is not a multiple of {heads} heads")
+    head_dim = width // heads
+    if head_dim % 16 != 0 or head_dim > 128:
+        raise NotImplementedError(f"attention kernels take head sizes that are multiples of 16 up to 128, got {head_dim}")
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16:
+            raise TypeError("attention kernels compute in bfloat16 (run under autocast or pass bfloat16 tensors)")
+    if k.shape != v.shape or k.shape[0] != batch or k.shape[2] != width:
+        raise ValueError(f"query {tuple(q.shape)}, key {tuple(k.shape)}, value {tuple(v.shape)} do not match")
+    mask, (sb, sh, sq) = _mask_strides(mask, batch, heads, q_len, kv_len)
+    d = N.AttentionDesc()
+    d.batch, d.heads, d.q_len, d.kv_len, d.head_dim = batch, heads, q_len, kv_len, head_dim
+    d.causal, d.scale = int(causal), float(scale)
+    d.q, d.k, d.v = _ptr(q), _ptr(k), _ptr(v)
+    d.ld_q, d.ld_k, d.ld_v = q.stride(1), k.stride(1), v.stride(1)
+    d.mask, d.mask_stride_b, d.mask_stride_h, d.mask_stride_q = _ptr(mask), sb, sh, sq
+    d.status_word = _ptr(status_word(q.device))
+    return d, mask
+
+
+def attention_forward(q, k, v, heads: int, scale: float, mask=None, causal: bool = False):
+    """softmax(scale * q.k^T + mask).v per head (``leanffn_attention_forward``).  q [batch, q_len, hidden], k / v
+    [batch, kv_len, hidden] bfloat16 (slices of one qkv tensor are taken in place).  Returns (out bfloat16
+    [batch, q_len, hidden], lse float32 [batch, heads, q_len] for the backward pass)."""
+    _require_cuda(q, k, v, mask)
+    q, k, v = _rows_view(q), _rows_view(k), _rows_view(v)
+    d, mask = _attention_desc(q, k, v, heads, scale, mask, causal)
+    out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(q.shape[0], heads, q.shape[1], dtype=torch.float32, device=q.device)
+    d.out, d.ld_out, d.lse = _ptr(out), out.stride(1), _ptr(lse)
+    N.check(N.lib.leanffn_attention_forward(d, _stream(q)), "leanffn_attention_forward")
+    _count()
+    return out, lse
+
+
+def attention_backward(d_out, q, k, v, out, lse, heads: int, scale: float, mask=None, causal: bool = False):
+    """Gradients of ``attention_forward`` (``leanffn_attention_backward``): (dq float32 [batch, q_len, hidden], dk, dv
+    bfloat16 [batch, kv_len, hidden])."""
+    _require_cuda(d_out, q, k, v, out, lse, mask)
+    q, k, v, d_out = _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(d_out)
+    if d_out.dtype != torch.bfloat16:
+        d_out = d_out.to(torch.bfloat16)
+    d, mask = _attention_desc(q, k, v, heads, scale, mask, causal)
+    dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    dk = torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
+    delta = torch.empty_like(lse)
+    d.out, d.ld_out, d.lse = _ptr(out), out.stride(1), _ptr(lse)
+    d.d_out, d.ld_dout, d.delta, d.dq_accum = _ptr(d_out), d_out.stride(1), _ptr(delta), _ptr(dq)
+    d.dk, d.dv, d.ld_dk, d.ld_dv = _ptr(dk), _ptr(dv), dk.stride(1), dv.stride(1)
+    N.check(N.lib.leanffn_attention_backward(d, _stream(q)), "leanffn_attention_backward")
+    _count(3)
+    return dq, dk, dv

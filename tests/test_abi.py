@@ -24,7 +24,7 @@ def test_header_symbols_are_exported_and_bound():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(_native.EXPORTED_SYMBOLS) == names, "ctypes bindings and header disagree"
-    assert _native.lib.leanffn_abi_version() == _native.ABI_VERSION == 3
+    assert _native.lib.leanffn_abi_version() == _native.ABI_VERSION == 4
     assert _native.status_string(0) == "ok"
     assert "shape" in _native.status_string(-2)
 
