@@ -627,26 +627,30 @@ def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
     params = list(model.parameters())
     tokens = batch * seq
 
-    def ffn_modules():
-        return [m for m in model.modules() if type(m).__name__ == "LeanFFN"]
+    def modules_named(name):
+        return [m for m in model.modules() if type(m).__name__ == name]
 
     def timed(n_steps):
-        events = []
+        events, core_events = [], []
 
-        def pre(_m, *_a):
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            events.append([e, None])
+        def hooks(store):
+            def pre(_m, *_a):
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                store.append([e, None])
 
-        def post(_m, *_a):
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            events[-1][1] = e
+            def post(_m, *_a):
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                store[-1][1] = e
+            return pre, post
 
         handles = []
-        for m in ffn_modules():
-            handles += [m.register_forward_pre_hook(pre), m.register_forward_hook(post),
-                        m.register_full_backward_pre_hook(pre), m.register_full_backward_hook(post)]
+        for store, mods in ((events, modules_named("LeanFFN")), (core_events, modules_named("RotaryAttentionCore"))):
+            pre, post = hooks(store)
+            for m in mods:
+                handles += [m.register_forward_pre_hook(pre), m.register_forward_hook(post),
+                            m.register_full_backward_pre_hook(pre), m.register_full_backward_hook(post)]
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         losses = []
         a.record()
@@ -662,21 +666,35 @@ def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
         for h in handles:
             h.remove()
         ffn_ms = sum(s.elapsed_time(e) for s, e in events if e is not None) / n_steps
-        return a.elapsed_time(b) / n_steps, ffn_ms, float(losses[-1])
+        core_ms = sum(s.elapsed_time(e) for s, e in core_events if e is not None) / n_steps
+        return a.elapsed_time(b) / n_steps, ffn_ms, core_ms, float(losses[-1])
 
     out = dict(config=dict(model="LeanGPT (reference lean_transformer/models/gpt.py)", layers=12, hidden=768, heads=16,
                            intermediate=3072, gated=True, vocab=10000, batch=batch, seq_len=seq, tokens=tokens,
                            dtype="autocast bf16, fp32 parameters", steps=steps, warmup=warmup))
-    for label in ("reference_modules", "swapped_ffn_and_linears"):
-        if label != "reference_modules":
+    # three runs of the same model object: the reference's modules; FFN blocks, linear layers and the attention
+    # blocks' LayerNorm / projections swapped (attention core still the reference's stock operators); everything swapped
+    for label in ("reference_modules", "swapped_ffn_and_linears", "swapped_with_attention_core"):
+        if label == "swapped_ffn_and_linears":
+            convert_model(model, convert_attention_core=False)
+        elif label == "swapped_with_attention_core":
             convert_model(model)
         timed(warmup)
         launches = L.ops.launch_count
-        ms, ffn_ms, loss = timed(steps)
+        ms, ffn_ms, core_ms, loss = timed(steps)
         out[label] = dict(ms_per_step=ms, tokens_per_s=tokens / ms * 1e3, ffn_ms_per_step=ffn_ms,
-                          ffn_share=ffn_ms / ms, loss=loss,
+                          ffn_share=ffn_ms / ms, attention_core_ms_per_step=core_ms, loss=loss,
                           leanffn_b200_launches_per_step=(L.ops.launch_count - launches) / steps)
     L.check_device_status(device)
+    # attention core: 4 * len * len * head_dim FLOPs per head and batch row forward, 2.5 x that backward, halved by
+    # the causal rule
+    core_flops = 12 * batch * 16 * 3.5 * 4 * seq * seq * 48 / 2
+    out["swapped_with_attention_core"]["attention_core_tflops"] = (
+        core_flops / max(out["swapped_with_attention_core"]["attention_core_ms_per_step"], 1e-9) / 1e9)
+    out["speedup_attention_core"] = (out["swapped_ffn_and_linears"]["attention_core_ms_per_step"]
+                                     / max(out["swapped_with_attention_core"]["attention_core_ms_per_step"], 1e-9))
+    out["speedup_whole_step_with_attention_core"] = (out["reference_modules"]["ms_per_step"]
+                                                     / out["swapped_with_attention_core"]["ms_per_step"])
     ffn_flops = 12 * tokens * flops_per_token(768, 3072)
     out["swapped_ffn_and_linears"]["ffn_tflops"] = ffn_flops / out["swapped_ffn_and_linears"]["ffn_ms_per_step"] / 1e9
     out["reference_modules"]["ffn_tflops"] = ffn_flops / out["reference_modules"]["ffn_ms_per_step"] / 1e9

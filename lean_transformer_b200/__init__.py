@@ -6,7 +6,7 @@ Everything that computes lives in ``libleanffn_b200.so`` (hand-written CUDA, C A
 from . import _native  # noqa: F401  (loads the shared library; raises if it is absent)
 from .blocksparse import *  # noqa: F401,F403
 from .ffn import LeanFFN, _LeanFFN  # noqa: F401
-from .attn import LeanSelfAttention  # noqa: F401
+from .attn import LeanSelfAttention, RotaryAttentionCore, RotaryEmbeddings, SimpleAttentionCore  # noqa: F401
 from .fused_linear import linear_dropout_residual  # noqa: F401
 from .ops import check_device_status  # noqa: F401
 from .utils import ACT2FN, pad_to_multiple, resolve_activation  # noqa: F401

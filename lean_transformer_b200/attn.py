@@ -1,4 +1,4 @@
-"""Attention block shell with its projections on the sm_100a kernels (lean_transformer/attn.py:11-82).
+"""Attention block on the sm_100a kernels (lean_transformer/attn.py).
 
 ``LeanSelfAttention`` keeps the reference's constructor, attributes (``qkv_proj``, ``out_proj``, ``pre_layer_norm``,
 ``post_layer_norm``, ``output_dropout``, ``attention_core``, ``residual``, ``checkpoint_attention_core``) and
@@ -6,29 +6,100 @@
 
   pre-LayerNorm                       ``leanffn_layer_norm_forward / backward``  (attn.py:67)
   qkv projection                      one GEMM (+ bias, low rank, block sparsity)  (attn.py:68)
+  attention core                      ``leanffn_rotary`` + ``leanffn_attention_forward / backward``  (attn.py:85-171)
   output projection -> dropout -> + residual.to(float32)
                                       ONE GEMM with the fused epilogue  (attn.py:73-78)
 
-The attention core itself (attn.py:85-149: rotary, Q.K^T, softmax, P.V) is NOT a kernel of this library: the block
-calls whatever ``attention_core`` module it is given, which for converted models is the model's own core.  The
-default core below restates the reference's simple core with stock tensor operators so that the block is usable on
-its own; it is a convenience, not part of the accelerated path.
+``SimpleAttentionCore`` and ``RotaryAttentionCore`` mirror the reference's cores (same constructors, same
+``forward(query, key, value, attention_mask) -> (outputs, probs)``).  They never build the [query_len, kv_len]
+matrices, so ``probs`` is ``None`` and asking the block for ``output_attentions=True`` raises.  The three slices of
+the fused qkv output are read in place.  Any other ``attention_core`` module given to the block is called as is.
 """
 import math
-from typing import Optional
+import weakref
+from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
+from . import ops
 from .blocksparse.linear import GeneralizedLinear, _GeneralizedLinear
 from .ffn import _LayerNormFunction
 from .fused_linear import linear_dropout_residual
 
+_CAUSAL_CACHE = {}  # id(mask) -> (weak reference to the mask, its version counter, answer)
+
+
+def mask_is_causal(mask: Optional[torch.Tensor], q_len: int, kv_len: int) -> bool:
+    """True when the additive mask is exactly the causal pattern for every batch row and head: 0 where
+    key <= query + (kv_len - q_len), at most -1e4 elsewhere (what models/gpt.py:274-285 builds when nothing is padded).
+    The kernels then apply the rule themselves, skip the empty tiles and never read the mask.  The answer is cached
+    per mask tensor OBJECT (and its version counter), so the layers of a model that all receive the same tensor pay
+    for one reduction and one host read per forward pass."""
+    if mask is None or mask.dim() < 2 or mask.shape[-2] != q_len or mask.shape[-1] != kv_len:
+        return False
+    entry = _CAUSAL_CACHE.get(id(mask))
+    if entry is not None and entry[0]() is mask and entry[1] == mask._version:
+        return entry[2]
+    allowed = torch.ones(q_len, kv_len, dtype=torch.bool, device=mask.device).tril_(kv_len - q_len)
+    answer = bool(torch.where(allowed, mask == 0, mask <= -1e4).all().item())
+    if len(_CAUSAL_CACHE) > 64:
+        for key in [k for k, e in _CAUSAL_CACHE.items() if e[0]() is None]:
+            del _CAUSAL_CACHE[key]
+        if len(_CAUSAL_CACHE) > 64:
+            _CAUSAL_CACHE.clear()
+    _CAUSAL_CACHE[id(mask)] = (weakref.ref(mask), mask._version, answer)
+    return answer
+
+
+class _AttentionCoreFunction(torch.autograd.Function):
+    """(query, key, value) [batch, len, hidden] -> attention output [batch, query_len, hidden], bfloat16.
+    Saves the (rotated) queries and keys, the values, the output and one float per row and head; the backward
+    pass recomputes the probabilities tile by tile."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, attention_mask, heads: int, cos, sin, scale: float):
+        for t in (query, key, value):
+            if t.dtype != torch.bfloat16 and not torch.is_autocast_enabled():
+                raise NotImplementedError(
+                    "the attention kernels compute in bfloat16: run the block under torch.autocast(bfloat16) or pass "
+                    f"bfloat16 tensors (got {t.dtype})")
+        q_len, kv_len = query.shape[1], key.shape[1]
+        causal = mask_is_causal(attention_mask, q_len, kv_len)
+        mask = None if causal else attention_mask
+        if cos is not None:
+            q = ops.rotary(query, cos, sin, heads)
+            k = ops.rotary(key, cos, sin, heads)
+        else:
+            q = query if query.dtype == torch.bfloat16 else ops.rotary(query, None, None, heads)
+            k = key if key.dtype == torch.bfloat16 else ops.rotary(key, None, None, heads)
+        v = value if value.dtype == torch.bfloat16 else ops.rotary(value, None, None, heads)
+        out, lse = ops.attention_forward(q, k, v, heads, scale, mask, causal)
+        ctx.save_for_backward(q, k, v, out, lse, mask, cos, sin)
+        ctx.heads, ctx.scale, ctx.causal = heads, scale, causal
+        ctx.in_dtypes = (query.dtype, key.dtype, value.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, lse, mask, cos, sin = ctx.saved_tensors
+        heads = ctx.heads
+        dq, dk, dv = ops.attention_backward(grad_out, q, k, v, out, lse, heads, ctx.scale, mask, ctx.causal)
+        q_dtype, k_dtype, v_dtype = ctx.in_dtypes
+        grad_q = ops.rotary(dq, cos, sin, heads, inverse=True, out_dtype=q_dtype)  # fp32 accumulator -> input dtype
+        if cos is not None or k_dtype != torch.bfloat16:
+            dk = ops.rotary(dk, cos, sin, heads, inverse=True, out_dtype=k_dtype)
+        if v_dtype != torch.bfloat16:
+            dv = dv.to(v_dtype)
+        return grad_q, dk, dv, None, None, None, None, None
+
 
 class SimpleAttentionCore(nn.Module):
-    """softmax(Q K^T / sqrt(d) + mask) V with stock tensor operators (lean_transformer/attn.py:85-149).
-    Returns (outputs [batch, query_len, hidden], probs [batch, heads, query_len, kv_len])."""
+    """softmax(Q K^T / sqrt(head_size) + mask) V on the attention kernels (lean_transformer/attn.py:85-149).
+    ``forward`` returns (outputs [batch, query_len, hidden_size], None): the probabilities are never materialised."""
+
+    memory_lean = True  # keeps O(length) state for the backward pass: wrapping it in a checkpoint buys nothing
 
     def __init__(self, hidden_size: int, num_attention_heads: int, attention_probs_dropout: float = 0.0):
         super().__init__()
@@ -37,18 +108,91 @@ class SimpleAttentionCore(nn.Module):
         self.hidden_size, self.num_attention_heads = hidden_size, num_attention_heads
         self.attention_head_size = hidden_size // num_attention_heads
 
+    def _tables(self, length: int, device) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        return None, None
+
     def forward(self, query, key, value, attention_mask):
+        """
+        :param query: [batch_size, query_seq_len, hidden_size]
+        :param key: [batch_size, kv_seq_len, hidden_size]
+        :param value: [batch_size, kv_seq_len, hidden_size]
+        :param attention_mask: float [batch, (optional heads), query_seq_len, kv_seq_length], zero for non-masked
+          tokens and a large negative value for masked ones
+        :return: (outputs [batch_size, query_seq_len, hidden_size], None)
+        """
         if attention_mask is not None:
             assert torch.is_floating_point(attention_mask), "expected float mask with negative values for masked items"
-        heads = self.num_attention_heads
-        split = lambda t: t.view(*t.shape[:-1], heads, -1).permute(0, 2, 1, 3)  # noqa: E731
-        q, k, v = split(query), split(key), split(value)
-        scores = torch.matmul(q, k.transpose(-1, -2) / math.sqrt(q.shape[-1]))
-        if attention_mask is not None:
-            scores = scores + attention_mask
-        probs = self.attention_dropout(torch.softmax(scores, dim=-1))
-        out = torch.matmul(probs, v).transpose(2, 1).flatten(2)
-        return out, probs
+        if not query.is_cuda:
+            raise RuntimeError("the attention core (lean_transformer_b200) needs CUDA tensors: it exists only as "
+                               "sm_100a kernels")
+        if self.training and self.attention_dropout.p != 0:
+            raise NotImplementedError("dropout on the attention probabilities is not implemented in the attention "
+                                      "kernels (attention_probs_dropout must be 0)")
+        cos, sin = self._tables(max(query.shape[1], key.shape[1]), query.device)
+        scale = 1.0 / math.sqrt(self.attention_head_size)
+        out = _AttentionCoreFunction.apply(query, key, value, attention_mask, self.num_attention_heads, cos, sin, scale)
+        return out, None
+
+
+class RotaryEmbeddings(nn.Module):
+    """Cosine / sine tables of the rotary position embedding and their application (lean_transformer/rotary.py:15-68);
+    the tables are non-persistent buffers that grow on demand, as in the reference."""
+
+    def __init__(self, dim: int, base: int = 10_000):
+        super().__init__()
+        self.dim, self.base = dim, base
+        self.register_buffer("cos", torch.empty(1, dim), persistent=False)
+        self.register_buffer("sin", torch.empty(1, dim), persistent=False)
+
+    def _set_auxiliary_buffers(self, max_len: int, device: torch.device):
+        # rotary.py:48-60: inverse frequencies base ** linspace(0, -1 + 2 / dim, dim / 2), repeated for both halves
+        exponents = torch.linspace(0, -1 + 2 / self.dim, self.dim // 2, dtype=torch.float32, device=device)
+        inv_freq = torch.pow(self.base, exponents).repeat(2)
+        positions = torch.arange(max_len, dtype=torch.float32, device=device)
+        freqs = positions[:, None] * inv_freq[None, :]
+        self.register_buffer("cos", torch.cos(freqs), persistent=False)
+        self.register_buffer("sin", torch.sin(freqs), persistent=False)
+
+    def tables(self, length: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        if length > self.cos.shape[0] or self.cos.device != device:
+            self._set_auxiliary_buffers(max_len=length, device=device)
+        return self.cos, self.sin
+
+    def forward(self, x: torch.Tensor, offset: int = 0):
+        """:param x: [batch_size, seq_len, nhead, hid_size]; :param offset: added to all position indices"""
+        batch, length, heads, dim = x.shape
+        cos, sin = self.tables(length + offset, x.device)
+        flat = x.reshape(batch, length, heads * dim)
+        return ops.rotary(flat, cos[offset:], sin[offset:], heads, out_dtype=x.dtype).view(batch, length, heads, dim)
+
+
+def _rotary_tables(rotary_emb: nn.Module, length: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Tables of this package's or of the reference's ``RotaryEmbeddings`` module (same buffers, same builder)."""
+    if rotary_emb.cos.shape[0] < length or rotary_emb.cos.device != device:
+        rotary_emb._set_auxiliary_buffers(max_len=length, device=device)
+    cos, sin = rotary_emb.cos, rotary_emb.sin
+    if cos.dtype != torch.float32:
+        cos, sin = cos.float(), sin.float()
+    return cos, sin
+
+
+class RotaryAttentionCore(SimpleAttentionCore):
+    """Attention core that applies rotary embeddings to queries and keys before the dot products
+    (lean_transformer/attn.py:152-171)."""
+
+    def __init__(self, hidden_size: int, num_attention_heads: int, rotary_emb: Optional[nn.Module] = None, **kwargs):
+        super().__init__(hidden_size, num_attention_heads, **kwargs)
+        if rotary_emb is None:
+            rotary_emb = RotaryEmbeddings(self.attention_head_size)
+        self.rotary_emb = rotary_emb
+
+    def _tables(self, length: int, device):
+        return _rotary_tables(self.rotary_emb, length, device)
+
+    def rotate(self, tensor: torch.Tensor):
+        """:param tensor: query or key, shape: [batch_size, query_seq_len, hidden_size]"""
+        cos, sin = self._tables(tensor.shape[1], tensor.device)
+        return ops.rotary(tensor, cos, sin, self.num_attention_heads, out_dtype=tensor.dtype)
 
 
 class LeanSelfAttention(nn.Module):
@@ -61,7 +205,8 @@ class LeanSelfAttention(nn.Module):
     :param layer_norm_eps: see torch.nn.functional.layer_norm
     :param post_layer_norm: additional layer norm on the projected attention outputs before the residual
     :param residual: if True, adds the original layer input to the final layer output
-    :param attention_core: module ``(query, key, value, attention_mask) -> (outputs, probs)``
+    :param attention_core: module ``(query, key, value, attention_mask) -> (outputs, probs)``; default: this
+        package's ``SimpleAttentionCore``
     :param checkpoint_attention_core: re-compute attention weights during backward instead of storing them
     :param qkv_proj: custom QKV projection layer (hidden_size -> 3 * hidden_size)
     :param out_proj: custom output projection layer (hidden_size -> hidden_size)
@@ -118,9 +263,14 @@ class LeanSelfAttention(nn.Module):
             outputs = self.output_dropout(outputs)
             if residual is not None:
                 outputs = outputs + residual
+        if output_attentions and attention_probs is None:
+            raise NotImplementedError("output_attentions=True: the attention kernels never materialise the "
+                                      "[query_len, kv_len] probabilities")
         return (outputs, attention_probs) if output_attentions else (outputs,)
 
     def _maybe_checkpoint(self, func, *args):
+        if getattr(func, "memory_lean", False):
+            return func(*args)
         if torch.is_grad_enabled() and self.checkpoint_attention_core:
             return checkpoint(func, *args, use_reentrant=True)
         return func(*args)

@@ -21,6 +21,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "gemm_common.cuh"
 #include "ptx.cuh"
@@ -406,6 +408,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode_fn() {
+  // cuTensorMapEncodeTiled is a driver call and needs a current context on the calling thread.  A thread that has
+  // made no context-binding runtime call yet (an autograd worker whose first operation is this one) has none and the
+  // encoder answers CUDA_ERROR_INVALID_CONTEXT: bind the device's primary context once per thread.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   static bool tried = false;
   if (!tried) {
@@ -448,9 +458,15 @@ bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int
                                  static_cast<cuuint64_t>(len) * static_cast<cuuint64_t>(ld) * 2};
   const cuuint32_t box[4] = {64, 1, 128, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("LEANFFN_DEBUG") != nullptr)
+    fprintf(stderr, "leanffn: cuTensorMapEncodeTiled failed (%d): base %p dims %llu %llu %llu %llu strides %llu %llu %llu\n",
+            static_cast<int>(r), base, (unsigned long long)dims[0], (unsigned long long)dims[1],
+            (unsigned long long)dims[2], (unsigned long long)dims[3], (unsigned long long)strides[0],
+            (unsigned long long)strides[1], (unsigned long long)strides[2]);
+  return r == CUDA_SUCCESS;
 }
 
 template <bool A_MN, bool B_MN, int BLOCK_N, int MT, bool TF32 = false>

@@ -6,8 +6,9 @@ this package's drop-ins.  Parameters and buffers are re-used (the very same ``nn
 state, weight sharing between layers (``share_large_matrices``) and checkpoints keep working.  Classes are recognised
 by name, so the reference does not have to be importable here.
 
-``LeanSelfAttention`` blocks keep their own attention core module (rotary, Q.K^T, softmax, P.V are not kernels of this
-package); their LayerNorm, qkv projection and output projection + dropout + residual run on this package's kernels.
+``LeanSelfAttention`` blocks are converted too: LayerNorm, qkv projection, the attention core (the reference's
+``SimpleAttentionCore`` / ``RotaryAttentionCore``; any other core module is kept and called as is) and output
+projection + dropout + residual run on this package's kernels.
 
 Every drop-in is an instance of a class derived from BOTH this package's class and the class it replaces (this
 package's first in the method resolution order, so all behaviour is this package's).  The model's own code keeps
@@ -20,7 +21,7 @@ from typing import Dict, Tuple
 
 import torch.nn as nn
 
-from .attn import LeanSelfAttention
+from .attn import LeanSelfAttention, RotaryAttentionCore, SimpleAttentionCore
 from .blocksparse.linear import GeneralizedLinear, GeneralizedMatrix
 from .ffn import LeanFFN
 
@@ -96,16 +97,38 @@ def _convert_ffn(ref, memo: Dict[int, nn.Module]) -> LeanFFN:
     return new
 
 
-def _convert_attention(ref, memo: Dict[int, nn.Module]) -> LeanSelfAttention:
-    """The attention block shell (lean_transformer/attn.py:11-82): LayerNorm and both projections move to this
-    package's kernels, the attention core module is the model's own and is passed through untouched."""
+def _convert_core(ref, memo: Dict[int, nn.Module]) -> nn.Module:
+    """The reference's SimpleAttentionCore / RotaryAttentionCore (lean_transformer/attn.py:85-171) become this
+    package's kernel-backed cores; the rotary table module is kept (same buffers).  Any other core is passed through."""
+    name = type(ref).__name__
+    if name not in ("SimpleAttentionCore", "RotaryAttentionCore") or isinstance(ref, SimpleAttentionCore):
+        return ref
+    if id(ref) in memo:
+        return memo[id(ref)]
+    ours = RotaryAttentionCore if name == "RotaryAttentionCore" else SimpleAttentionCore
+    cls = _dropin_class(ours, type(ref))
+    new = cls.__new__(cls)
+    nn.Module.__init__(new)
+    new.attention_dropout = ref.attention_dropout
+    new.hidden_size, new.num_attention_heads = ref.hidden_size, ref.num_attention_heads
+    new.attention_head_size = ref.attention_head_size
+    if name == "RotaryAttentionCore":
+        new.rotary_emb = ref.rotary_emb
+    new.train(ref.training)
+    memo[id(ref)] = new
+    return new
+
+
+def _convert_attention(ref, memo: Dict[int, nn.Module], convert_core: bool = True) -> LeanSelfAttention:
+    """The attention block (lean_transformer/attn.py:11-82): LayerNorm, both projections and the reference's own
+    attention cores move to this package's kernels; a custom core module is passed through untouched."""
     if id(ref) in memo:
         return memo[id(ref)]
     cls = _dropin_class(LeanSelfAttention, type(ref))
     new = cls.__new__(cls)
     nn.Module.__init__(new)
     new.hidden_size = ref.hidden_size
-    new.attention_core = ref.attention_core
+    new.attention_core = _convert_core(ref.attention_core, memo) if convert_core else ref.attention_core
     new.qkv_proj = _convert_linear(ref.qkv_proj, memo)
     new.out_proj = _convert_linear(ref.out_proj, memo)
     new.pre_layer_norm, new.post_layer_norm = ref.pre_layer_norm, ref.post_layer_norm
@@ -120,15 +143,20 @@ def _is_reference(module: nn.Module, name: str, ours: type) -> bool:
     return type(module).__name__ == name and not isinstance(module, ours)
 
 
-def convert_model(model: nn.Module, convert_linears: bool = True, convert_attention: bool = True) -> nn.Module:
-    """Replace every reference ``LeanFFN`` (and, optionally, ``LeanSelfAttention`` shell and stand-alone
+def convert_model(model: nn.Module, convert_linears: bool = True, convert_attention: bool = True,
+                  convert_attention_core: bool = True) -> nn.Module:
+    """Replace every reference ``LeanFFN`` (and, optionally, ``LeanSelfAttention`` block and stand-alone
     ``GeneralizedLinear``) inside ``model`` by the CUDA drop-in.  Returns the converted model: ``model`` itself,
-    modified in place, unless ``model`` IS one of those modules, in which case its drop-in is returned."""
+    modified in place, unless ``model`` IS one of those modules, in which case its drop-in is returned.
+
+    ``convert_attention_core=False`` keeps the attention blocks' own core modules.  The kernel-backed cores compute in
+    bfloat16 (under ``torch.autocast`` or on bfloat16 tensors) and raise on float32 tensors outside autocast, so a
+    model that is to run in plain float32 keeps its cores."""
     memo: Dict[int, nn.Module] = {}
     if _is_reference(model, "LeanFFN", LeanFFN):
         return _convert_ffn(model, memo)
     if convert_attention and _is_reference(model, "LeanSelfAttention", LeanSelfAttention):
-        return _convert_attention(model, memo)
+        return _convert_attention(model, memo, convert_attention_core)
     if convert_linears and _is_reference(model, "GeneralizedLinear", GeneralizedLinear):
         return _convert_linear(model, memo)
 
@@ -137,10 +165,12 @@ def convert_model(model: nn.Module, convert_linears: bool = True, convert_attent
             if _is_reference(child, "LeanFFN", LeanFFN):
                 setattr(parent, name, _convert_ffn(child, memo))
             elif convert_attention and _is_reference(child, "LeanSelfAttention", LeanSelfAttention):
-                setattr(parent, name, _convert_attention(child, memo))
+                setattr(parent, name, _convert_attention(child, memo, convert_attention_core))
             elif convert_linears and _is_reference(child, "GeneralizedLinear", GeneralizedLinear):
                 setattr(parent, name, _convert_linear(child, memo))
             else:
+                if convert_attention_core and isinstance(child, LeanSelfAttention):
+                    child.attention_core = _convert_core(child.attention_core, memo)  # block converted earlier
                 visit(child)
 
     visit(model)

@@ -308,3 +308,63 @@ def leanffn_step(x, g, params, **kw):
     """One forward + backward with loss sum(out * g): returns (out, grads)."""
     out, saved = leanffn_forward(x, params, **kw)
     return out, leanffn_backward(g, x, params, saved, **kw)
+
+
+# ---------------------------------------------------------------------------------------------------
+# attention core: lean_transformer/attn.py:85-171, rotary tables and rotation: lean_transformer/rotary.py:43-68
+# ---------------------------------------------------------------------------------------------------
+def rotary_tables(length: int, dim: int, base: int = 10_000, dtype=torch.float64) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin [length, dim] (rotary.py:48-60: the exponents and the position products are computed in float32)."""
+    buf = torch.linspace(0, -1 + 2 / dim, dim // 2, dtype=torch.float32)
+    inv_freq = torch.pow(base, buf).repeat(2)
+    freqs = torch.arange(length, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    return torch.cos(freqs).to(dtype), torch.sin(freqs).to(dtype)
+
+
+def rotary_apply(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [batch, len, heads, dim] -> x * cos + cat(-x_right, x_left) * sin (rotary.py:63-68)."""
+    half = x.shape[-1] // 2
+    rotated = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
+    return x * cos[None, : x.shape[1], None, :] + rotated * sin[None, : x.shape[1], None, :]
+
+
+def rotary_apply_transposed(g: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Gradient of rotary_apply with respect to x for an incoming gradient g."""
+    half = g.shape[-1] // 2
+    gs = g * sin[None, : g.shape[1], None, :]
+    return g * cos[None, : g.shape[1], None, :] + torch.cat([gs[..., half:], -gs[..., :half]], dim=-1)
+
+
+def attention_core_step(query, key, value, mask, heads: int, grad_out=None, rotary: bool = False, base: int = 10_000):
+    """Forward of the attention core and, given grad_out, the gradients for query / key / value, without autograd.
+    query [batch, q_len, hidden], key / value [batch, kv_len, hidden], mask additive, broadcastable to
+    [batch, heads, q_len, kv_len].  Follows attn.py:117-147: head split, keys divided by sqrt(head size), scores + mask,
+    softmax over keys, probabilities times values, heads merged; with rotary=True queries and keys are rotated first
+    (attn.py:163-171).  Returns (out, dict(query=, key=, value=) or None)."""
+    batch, q_len, hidden = query.shape
+    kv_len, d = key.shape[1], hidden // heads
+    q4, k4, v4 = (t.reshape(batch, -1, heads, d) for t in (query, key, value))
+    if rotary:
+        cos, sin = rotary_tables(max(q_len, kv_len), d, base, query.dtype)
+        q4, k4 = rotary_apply(q4, cos, sin), rotary_apply(k4, cos, sin)
+    qh, kh, vh = (t.permute(0, 2, 1, 3) for t in (q4, k4, v4))  # [batch, heads, len, d]
+    inv = 1.0 / math.sqrt(d)
+    scores = qh @ (kh * inv).transpose(-1, -2)
+    if mask is not None:
+        scores = scores + mask
+    probs = torch.softmax(scores, dim=-1)
+    out = (probs @ vh).transpose(1, 2).reshape(batch, q_len, hidden)
+    if grad_out is None:
+        return out, None
+    go = grad_out.reshape(batch, q_len, heads, d).permute(0, 2, 1, 3)
+    d_v = probs.transpose(-1, -2) @ go
+    d_probs = go @ vh.transpose(-1, -2)
+    d_scores = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))
+    d_q = (d_scores @ kh) * inv
+    d_k = (d_scores.transpose(-1, -2) @ qh) * inv
+    d_q4, d_k4, d_v4 = (t.permute(0, 2, 1, 3) for t in (d_q, d_k, d_v))
+    if rotary:
+        d_q4, d_k4 = rotary_apply_transposed(d_q4, cos, sin), rotary_apply_transposed(d_k4, cos, sin)
+    grads = dict(query=d_q4.reshape(batch, q_len, hidden), key=d_k4.reshape(batch, kv_len, hidden),
+                 value=d_v4.reshape(batch, kv_len, hidden))
+    return out, grads

@@ -212,6 +212,26 @@ def main(ref_root: str):
                         dy=to_np(ref_utils.gelu_fused_grad(torch.ones_like(xs), xs)))
     print("wrote gelu_fused.npz")
 
+    # attention cores (lean_transformer/attn.py:85-171): outputs and input gradients in float64
+    from lean_transformer import attn as ref_attn
+    torch.manual_seed(11)
+    B, S, HID, HEADS = 2, 40, 96, 3
+    for kind, cls in (("simple", ref_attn.SimpleAttentionCore), ("rotary", ref_attn.RotaryAttentionCore)):
+        core = cls(HID, HEADS).double()
+        q, k, v = (torch.randn(B, S, HID, dtype=torch.float64, requires_grad=True) for _ in range(3))
+        g = torch.randn(B, S, HID, dtype=torch.float64)
+        causal = (1.0 - torch.ones(S, S, dtype=torch.float64).tril()).view(1, 1, S, S) * -10000.0
+        padding = torch.zeros(B, 1, 1, S, dtype=torch.float64)
+        padding[1, :, :, S - 7:] = -10000.0
+        mask = causal + padding
+        out, probs = core(q, k, v, mask)
+        out.backward(g)
+        np.savez_compressed(HERE / f"attention_core_{kind}.npz", query=to_np(q), key=to_np(k), value=to_np(v),
+                            mask=to_np(mask), grad_out=to_np(g), out=to_np(out), probs=to_np(probs),
+                            grad_query=to_np(q.grad), grad_key=to_np(k.grad), grad_value=to_np(v.grad),
+                            heads=np.array(HEADS))
+        print(f"wrote attention_core_{kind}.npz")
+
     # state-dict key names the drop-in modules must reproduce
     ffn = LeanFFN(H, I, gated=True, post_layer_norm=True,
                   i2h_proj=GL(GM(H, 2 * I, layout, 6), 2), h2o_proj=GL(GM(I, H, layout, 0, ), 0))

@@ -90,7 +90,8 @@ def test_struct_sizes_and_offsets_match_a_c_compiler(tmp_path):
     if gcc is None:
         pytest.skip("no C compiler")
     structs = {"leanffn_gemm_desc": _native.GemmDesc, "leanffn_linear_desc": _native.LinearDesc,
-               "leanffn_ffn_desc": _native.FfnDesc, "leanffn_ffn_grads": _native.FfnGrads}
+               "leanffn_ffn_desc": _native.FfnDesc, "leanffn_ffn_grads": _native.FfnGrads,
+               "leanffn_attention_desc": _native.AttentionDesc}
     lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "leanffn_b200.h"', 'int main(void) {']
     for c_name, mirror in structs.items():
         lines.append(f'  printf("{c_name} %zu\\n", sizeof({c_name}));')

@@ -1,0 +1,185 @@
+"""Attention-core kernels (leanffn_attention_forward / backward, leanffn_rotary) against the CPU oracle and the
+golden vectors the reference produced (needs a B200).
+
+Inputs are rounded to bfloat16 first and the oracle runs in float64 on exactly those values, so what is measured is
+the kernels' own arithmetic: bf16 tensor-core products with fp32 accumulation, fp32 softmax, probabilities and score
+gradients rounded to bf16 before the second products.  Tolerance: rtol 2e-2, atol 1e-2 (the bf16 bar)."""
+import math
+
+import pytest
+import torch
+
+from conftest import BF16_ATOL, BF16_RTOL, assert_close, load_golden
+from oracle import leanffn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(t):
+    return t.to(torch.bfloat16)
+
+
+def _check(got, want, what):
+    # an attention output is a convex combination of values, its gradients sums over a row of keys or queries:
+    # judged at the size of the tensor (scale_atol), like every other accumulated product in this suite
+    assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=True)
+
+
+def _run_case(device, batch, heads, q_len, kv_len, head_dim, mask_kind, rotary, seed=0):
+    import lean_transformer_b200 as L
+
+    torch.manual_seed(seed)
+    hidden = heads * head_dim
+    if q_len == kv_len:  # the three slices of one fused projection output, read in place
+        qkv = _bf16(torch.randn(batch, q_len, 3 * hidden)).to(device).requires_grad_(True)
+        q, k, v = qkv.split(hidden, dim=-1)
+    else:
+        q = _bf16(torch.randn(batch, q_len, hidden)).to(device).requires_grad_(True)
+        k = _bf16(torch.randn(batch, kv_len, hidden)).to(device).requires_grad_(True)
+        v = _bf16(torch.randn(batch, kv_len, hidden)).to(device).requires_grad_(True)
+    g = _bf16(torch.randn(batch, q_len, hidden)).to(device)
+    mask = None
+    if mask_kind == "causal":
+        mask = (1.0 - torch.ones(q_len, kv_len).tril(kv_len - q_len)).view(1, 1, q_len, kv_len) * -10000.0
+    elif mask_kind == "causal+padding":
+        mask = (1.0 - torch.ones(q_len, kv_len).tril(kv_len - q_len)).view(1, 1, q_len, kv_len) * -10000.0
+        pad = torch.zeros(batch, 1, 1, kv_len)
+        pad[-1, :, :, kv_len - kv_len // 5:] = -10000.0
+        mask = mask + pad
+    elif mask_kind == "keys":
+        mask = (torch.rand(batch, 1, 1, kv_len) < 0.3).float() * -10000.0
+        mask[..., 0] = 0.0
+    elif mask_kind == "per_head":
+        mask = torch.randn(batch, heads, q_len, kv_len)
+    core = (L.RotaryAttentionCore if rotary else L.SimpleAttentionCore)(hidden, heads).to(device).train()
+    dmask = None if mask is None else mask.to(device)
+    out, probs = core(q, k, v, dmask)
+    assert probs is None and out.dtype == torch.bfloat16 and out.shape == (batch, q_len, hidden)
+    out.backward(g)
+    leaves = (qkv,) if q_len == kv_len else (q, k, v)
+    got_grads = torch.cat([t.grad for t in leaves], dim=-1) if q_len == kv_len else None
+    want, grads = O.attention_core_step(q.detach().double().cpu(), k.detach().double().cpu(), v.detach().double().cpu(),
+                                        None if mask is None else mask.double(), heads, grad_out=g.double().cpu(),
+                                        rotary=rotary)
+    tag = f"attention b{batch} h{heads} q{q_len} kv{kv_len} d{head_dim} {mask_kind} rotary={rotary}"
+    _check(out, want, f"{tag}:out")
+    if q_len == kv_len:
+        gq, gk, gv = got_grads.split(hidden, dim=-1)
+    else:
+        gq, gk, gv = q.grad, k.grad, v.grad
+    _check(gq, grads["query"], f"{tag}:grad_query")
+    _check(gk, grads["key"], f"{tag}:grad_key")
+    _check(gv, grads["value"], f"{tag}:grad_value")
+    L.check_device_status(device)
+    return core
+
+
+@pytest.mark.parametrize("kind", ["simple", "rotary"])
+def test_attention_core_golden(cuda_device, kind):
+    """The reference's own cores (float64 run, tests/golden/make_golden.py): causal + padding mask, 3 heads of 32."""
+    import lean_transformer_b200 as L
+
+    blob = {k: torch.from_numpy(v) for k, v in load_golden(f"attention_core_{kind}").items()}
+    heads = int(blob["heads"])
+    hidden = blob["query"].shape[-1]
+    core = (L.RotaryAttentionCore if kind == "rotary" else L.SimpleAttentionCore)(hidden, heads).to(cuda_device)
+    q, k, v = (_bf16(blob[n]).to(cuda_device).requires_grad_(True) for n in ("query", "key", "value"))
+    out, _ = core(q, k, v, blob["mask"].float().to(cuda_device))
+    out.backward(_bf16(blob["grad_out"]).to(cuda_device))
+    # the golden run used the unrounded inputs: the input rounding (2^-9 relative per element) is part of the distance
+    _check(out, blob["out"], f"attention golden {kind}:out")
+    for n, t in (("query", q), ("key", k), ("value", v)):
+        _check(t.grad, blob[f"grad_{n}"], f"attention golden {kind}:grad_{n}")
+
+
+@pytest.mark.parametrize("batch,heads,q_len,kv_len,head_dim,mask_kind,rotary", [
+    (1, 1, 128, 128, 64, None, False),
+    (2, 3, 256, 256, 64, "causal", False),          # detected: mask never read, empty tiles skipped
+    (2, 3, 256, 256, 48, "causal+padding", True),   # config 4's head size, general mask path
+    (2, 2, 200, 200, 64, "per_head", False),        # ragged tiles, one mask per head
+    (1, 2, 384, 384, 128, "keys", True),            # two 64-wide boxes per tile
+    (1, 2, 100, 333, 32, "causal", False),          # cross lengths, offset causal rule
+    (1, 2, 300, 300, 96, "causal", True),
+    (2, 4, 77, 77, 16, None, True),                 # smallest head size, less than one tile
+    (1, 1, 513, 513, 80, "causal+padding", False),
+])
+def test_attention_core_vs_oracle(cuda_device, batch, heads, q_len, kv_len, head_dim, mask_kind, rotary):
+    _run_case(cuda_device, batch, heads, q_len, kv_len, head_dim, mask_kind, rotary)
+
+
+def test_attention_core_config4_shape(cuda_device):
+    """One batch row of config 4: 2048 tokens, 16 heads of 48, rotary, the causal mask the GPT model builds."""
+    _run_case(cuda_device, 1, 16, 2048, 2048, 48, "causal", True, seed=4)
+
+
+def test_causal_mask_is_detected_and_equivalent(cuda_device):
+    """The causal fast path (rule applied in the kernel, tiles skipped) and the general path (mask read) agree, and
+    the detection keys on the tensor object, not on its address."""
+    import lean_transformer_b200 as L
+    from lean_transformer_b200.attn import mask_is_causal
+
+    torch.manual_seed(2)
+    S, heads, d = 320, 2, 64
+    q, k, v = (_bf16(torch.randn(2, S, heads * d)).to(cuda_device) for _ in range(3))
+    causal = ((1.0 - torch.ones(S, S).tril()).view(1, 1, S, S) * -10000.0).to(cuda_device)
+    assert mask_is_causal(causal, S, S) and mask_is_causal(causal.expand(2, 1, S, S).contiguous(), S, S)
+    padded = causal.expand(2, 1, S, S).clone()
+    padded[1, :, :, 300:] = -10000.0
+    assert not mask_is_causal(padded, S, S)
+    causal[0, 0, 5, 3] = -10000.0  # in-place edit of a tensor already seen: the version counter invalidates the cache
+    assert not mask_is_causal(causal, S, S)
+    causal[0, 0, 5, 3] = 0.0
+    scale = 1.0 / math.sqrt(d)
+    fast, lse_fast = L.ops.attention_forward(q, k, v, heads, scale, None, True)
+    slow, lse_slow = L.ops.attention_forward(q, k, v, heads, scale, causal, False)
+    torch.testing.assert_close(fast.float(), slow.float(), rtol=0, atol=1e-2)
+    torch.testing.assert_close(lse_fast, lse_slow, rtol=1e-5, atol=1e-5)
+
+
+def test_rotary_kernel_matches_oracle(cuda_device):
+    import lean_transformer_b200 as L
+
+    torch.manual_seed(1)
+    batch, length, heads, d = 2, 70, 3, 48
+    x = torch.randn(batch, length, heads * d)
+    emb = L.RotaryEmbeddings(d).to(cuda_device)
+    cos, sin = emb.tables(length, cuda_device)
+    ocos, osin = O.rotary_tables(length, d, dtype=torch.float32)
+    torch.testing.assert_close(cos.cpu(), ocos, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(sin.cpu(), osin, rtol=1e-6, atol=1e-6)
+    want = O.rotary_apply(x.view(batch, length, heads, d).double(), ocos.double(), osin.double())
+    got = L.ops.rotary(x.to(cuda_device), cos, sin, heads, out_dtype=torch.float32)
+    torch.testing.assert_close(got.cpu().view_as(want).double(), want, rtol=1e-5, atol=1e-5)
+    back = L.ops.rotary(x.to(cuda_device), cos, sin, heads, inverse=True, out_dtype=torch.float32)
+    want_back = O.rotary_apply_transposed(x.view(batch, length, heads, d).double(), ocos.double(), osin.double())
+    torch.testing.assert_close(back.cpu().view_as(want_back).double(), want_back, rtol=1e-5, atol=1e-5)
+    via_module = emb(x.to(cuda_device).view(batch, length, heads, d))
+    torch.testing.assert_close(via_module.cpu().double(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_attention_rejections(cuda_device):
+    """What the kernels do not cover fails loudly instead of running something else."""
+    import lean_transformer_b200 as L
+
+    x = torch.randn(1, 64, 128, device=cuda_device)
+    core = L.SimpleAttentionCore(128, 2).to(cuda_device)
+    with pytest.raises(NotImplementedError, match="bfloat16"):
+        core(x, x, x, None)  # float32 outside autocast
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out, _ = core(x, x, x, None)  # same tensors under autocast: computed in bf16
+    assert out.dtype == torch.bfloat16
+    xb = x.bfloat16()
+    with pytest.raises(NotImplementedError, match="head sizes"):
+        L.SimpleAttentionCore(120, 5).to(cuda_device)(xb[..., :120], xb[..., :120], xb[..., :120], None)  # head size 24
+    dropping = L.SimpleAttentionCore(128, 2, attention_probs_dropout=0.1).to(cuda_device).train()
+    with pytest.raises(NotImplementedError, match="dropout"):
+        dropping(xb, xb, xb, None)
+    dropping.eval()
+    dropping(xb, xb, xb, None)  # no dropout in evaluation mode
+    with pytest.raises(AssertionError, match="float mask"):
+        core(xb, xb, xb, torch.ones(1, 1, 64, 64, dtype=torch.bool, device=cuda_device))
+    block = L.LeanSelfAttention(128, 2).to(cuda_device)
+    with torch.autocast("cuda", dtype=torch.bfloat16), pytest.raises(NotImplementedError, match="output_attentions"):
+        block(x, None, output_attentions=True)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        core(xb.cpu(), xb.cpu(), xb.cpu(), None)

@@ -60,7 +60,7 @@ def test_tiny_gpt_swapped_ffn_matches_reference_fp32(cuda_device):
     ids = torch.randint(0, 200, (3, 48), generator=torch.Generator().manual_seed(5)).to(cuda_device)
     model.set_optimizations(ffn_custom_grad=True)
     want = _run(model, ids)  # the reference's own kernels (stock PyTorch CUDA operators), fp32
-    convert_model(model)
+    convert_model(model, convert_attention_core=False)  # plain fp32: the attention kernels are bf16-only
     assert sum(isinstance(m, L.LeanFFN) for m in model.modules()) == 2
     launches = L.ops.launch_count
     for checkpoints, custom in ((False, True), (False, False), (True, True), (2, True)):
@@ -83,6 +83,8 @@ def test_tiny_gpt_swapped_ffn_matches_reference_bf16(cuda_device):
     want = _run(model, ids)
     floor = _run(model, ids, autocast=True)
     convert_model(model)
+    import lean_transformer_b200 as L
+    assert sum(isinstance(m, L.RotaryAttentionCore) for m in model.modules()) >= 1
     got = _run(model, ids, autocast=True)
     # Through four layers the rounding noise of bf16 arithmetic compounds (the reference's own autocast run misses the
     # single-layer bound on some tensors by 1.7x), so each tensor is judged against that run: the swapped model's
@@ -107,7 +109,8 @@ def test_dropout_runs_are_consistent_across_optimizations(cuda_device):
 
     ref = _reference()
     torch.manual_seed(0)
-    model = convert_model(_tiny_gpt(ref, hidden_dropout_prob=0.1).to(cuda_device).train())
+    model = convert_model(_tiny_gpt(ref, hidden_dropout_prob=0.1).to(cuda_device).train(),
+                          convert_attention_core=False)
     ids = torch.randint(0, 200, (2, 32), generator=torch.Generator().manual_seed(7)).to(cuda_device)
     model.set_optimizations(gradient_checkpointing=False, checkpoint_last=False, checkpoint_attention_core=False,
                             ffn_custom_grad=False)
@@ -125,7 +128,8 @@ def test_dropout_runs_are_consistent_across_optimizations(cuda_device):
 def test_attention_shell_matches_reference_block(cuda_device, mode):
     """lean_transformer/attn.py:11-82 with a rotary core, shared block-sparse-free GeneralizedLinear projections and an
     fp32 residual stream: the reference block on stock operators against the same block after convert_model (its
-    LayerNorm, qkv projection and out projection + dropout + residual on this package's kernels, its own core)."""
+    LayerNorm, qkv projection and out projection + dropout + residual on this package's kernels; in bf16 mode the rotary
+    attention core too, in plain fp32 its own core)."""
     import lean_transformer_b200 as L
     from lean_transformer_b200.integration import convert_model
 
@@ -152,9 +156,15 @@ def test_attention_shell_matches_reference_block(cuda_device, mode):
 
     want = run(block, False)  # the reference's own fp32 run is the yardstick
     floor = run(block, True) if mode == "bf16" else None
-    new = convert_model(block)
+    new = convert_model(block, convert_attention_core=mode == "bf16")
     assert isinstance(new, L.LeanSelfAttention) and isinstance(new, ref.attn.LeanSelfAttention)
-    assert new.attention_core is block.attention_core and isinstance(new.qkv_proj, L.GeneralizedLinear)
+    assert isinstance(new.qkv_proj, L.GeneralizedLinear)
+    if mode == "bf16":
+        assert isinstance(new.attention_core, L.RotaryAttentionCore)
+        assert isinstance(new.attention_core, ref.attn.RotaryAttentionCore)
+        assert new.attention_core.rotary_emb is block.attention_core.rotary_emb
+    else:
+        assert new.attention_core is block.attention_core
     launches = L.ops.launch_count
     got = run(new, mode == "bf16")
     assert L.ops.launch_count - launches >= 8

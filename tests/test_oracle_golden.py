@@ -105,3 +105,24 @@ def test_layer_norm_edge_cases():
     assert_close(dx, x.grad, what="dx", **TIGHT)
     assert_close(dg, gam.grad, what="dgamma", **TIGHT)
     assert_close(db, bet.grad, what="dbeta", **TIGHT)
+
+
+@pytest.mark.parametrize("kind", ["simple", "rotary"])
+def test_attention_core_matches_reference(kind):
+    """The attention-core restatement (forward and hand-derived backward) against the reference's
+    SimpleAttentionCore / RotaryAttentionCore run in float64 (tests/golden/make_golden.py)."""
+    blob = {k: torch.from_numpy(v) for k, v in load_golden(f"attention_core_{kind}").items()}
+    out, grads = O.attention_core_step(blob["query"], blob["key"], blob["value"], blob["mask"], int(blob["heads"]),
+                                       grad_out=blob["grad_out"], rotary=kind == "rotary")
+    torch.testing.assert_close(out, blob["out"], rtol=1e-9, atol=1e-11)
+    for name in ("query", "key", "value"):
+        torch.testing.assert_close(grads[name], blob[f"grad_{name}"], rtol=1e-9, atol=1e-11)
+
+
+def test_rotary_transposed_is_the_gradient():
+    torch.manual_seed(0)
+    x = torch.randn(2, 9, 3, 8, dtype=torch.float64, requires_grad=True)
+    g = torch.randn_like(x)
+    cos, sin = O.rotary_tables(9, 8)
+    O.rotary_apply(x, cos, sin).backward(g)
+    torch.testing.assert_close(O.rotary_apply_transposed(g, cos, sin), x.grad, rtol=1e-12, atol=1e-12)
