@@ -11,7 +11,7 @@
 //                              swizzled K-major layout) -> O_j = P . V_j, accumulated in registers with the
 //                              running-maximum correction;
 //   backward, per query tile i (one CTA per key tile j):
-//                              S = Q_i . K_j^T, dP = dO_i . V_j^T -> P = exp2(S - lse), dS = P * (dP - delta) * scale
+//                              S = Q_i . K_j^T, dP = dO_i . V_j^T -> P = exp2(S - lse), dS = P * (dP - delta)
 //                              -> dV += P^T . dO_i, dK += dS^T . Q_i (TMEM, whole loop), dQ_i = dS . K_j (added
 //                              to an fp32 buffer with vector reductions).
 // The two phases of an iteration are serial inside a CTA; several CTAs per SM (forward, head_dim <= 64) overlap
@@ -34,7 +34,6 @@ bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int
 namespace attn {
 
 constexpr int TILE = 128;               // query rows / keys per tile
-constexpr int THREADS = 128;
 constexpr uint32_t BOX_BYTES = 128 * 64 * 2;   // one [128 x 64] bf16 box
 constexpr uint32_t PS_BYTES = 2 * BOX_BYTES;   // a [128 x 128] bf16 matrix written by the threads
 constexpr float LOG2E = 1.4426950408889634f;
@@ -42,6 +41,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 struct Params {
   int32_t B, H, Sq, Skv, d;
   int32_t causal;
+  int32_t experiment;
   float scale;
   const float* mask;
   int64_t mask_sb, mask_sh, mask_sq;
@@ -67,6 +67,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// 2^x on the special-function unit (one instruction; results below 2^-126 flush to zero, which is what a
+// probability that small rounds to in bf16 anyway)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -112,6 +120,22 @@ __device__ __forceinline__ void score_chunk(const uint32_t (&acc)[32], float (&v
   }
 }
 
+// Measurement builds (-DLEANFFN_ATTN_PROFILE): thread 0 of block (0, 0, 0) adds the SM clocks each phase of its loop
+// took to g_attn_prof[slot]; leanffn_attention_profile copies the counters out and clears them.
+#ifdef LEANFFN_ATTN_PROFILE
+__device__ long long g_attn_prof[16];
+#define ATTN_PROF_DECL long long prof_t = clock64(); const bool prof_on = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0
+#define ATTN_PROF(slot)                                  \
+  if (prof_on) {                                         \
+    const long long now = clock64();                     \
+    g_attn_prof[slot] += now - prof_t;                   \
+    prof_t = now;                                        \
+  }
+#else
+#define ATTN_PROF_DECL
+#define ATTN_PROF(slot)
+#endif
+
 struct Smem {
   uint32_t base;     // 1024-aligned shared address of the tile area
   uint8_t* gen;      // the same address as a generic pointer
@@ -126,24 +150,34 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Forward.  grid = (query tiles, heads, batch).  DPAD = head_dim rounded up to 32 (registers of the output row).
-// Shared memory: Q, K, V (DC boxes each, DC = ceil(head_dim / 64)), P (2 boxes), barriers.
-// TMEM: columns [0, 128) S, [128, 128 + head_dim) the product P . V_j.
+// Forward.  grid = (query tiles, heads, batch), 256 threads.  DPAD = head_dim rounded up to 32.
+// Two thread groups of 128 (warps 0-3, warps 4-7) split the keys of every tile: group g owns keys [64g, 64g + 64)
+// of the tile for row tid % 128 -- its own running maximum, denominator and output row, its own half of P and its
+// own product O_g = P_g . V_g in tensor memory.  The groups never exchange anything inside the loop; their two
+// partial softmax states are merged once at the end.
+// Shared memory: Q, K, V (DC boxes each, DC = ceil(head_dim / 64)), P (2 boxes: one per group), barriers.
+// TMEM: columns [0, 128) S; then one block of OCOLS columns per group for O_g.
+constexpr int FWD_THREADS = 256;
+
 template <int DPAD>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(FWD_THREADS)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const Params p) {
+  constexpr int OCOLS = DPAD <= 64 ? 64 : 128;
+  constexpr uint32_t TMEM_COLS = DPAD <= 64 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
   const uint32_t tile_bytes = DC * BOX_BYTES;
   const uint32_t sQ = sm.base, sK = sQ + tile_bytes, sV = sK + tile_bytes, sP = sV + tile_bytes;
   const uint32_t bar0 = sP + PS_BYTES;
-  const uint32_t bar_q = bar0, bar_k = bar0 + 8, bar_v = bar0 + 16, bar_mma = bar0 + 24, tmem_slot = bar0 + 32;
+  const uint32_t bar_q = bar0, bar_k = bar0 + 8, bar_v = bar0 + 16, bar_mma = bar0 + 24, bar_s = bar0 + 32;
+  const uint32_t tmem_slot = bar0 + 48;
   uint8_t* gP = sm.gen + 3 * tile_bytes;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 3 * tile_bytes + PS_BYTES + 32);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 3 * tile_bytes + PS_BYTES + 48);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int grp = warp >> 2, row = tid & 127;
   const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + TILE - 1) / TILE;
   const int qt = nq - 1 - static_cast<int>(blockIdx.x);  // long (late) rows first under the causal rule
   const int h = blockIdx.y, b = blockIdx.z;
@@ -161,20 +195,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_k, 1);
     mbar_init(bar_v, 1);
     mbar_init(bar_mma, 1);
+    mbar_init(bar_s, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
   }
   if (warp == 0) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);  // this warp's 32 lanes
+  const uint32_t t_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
+  const uint32_t t_out = t_row + 128 + grp * OCOLS;
 
   auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
     mbar_arrive_expect_tx(bar, tile_bytes);
@@ -191,8 +227,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     load_tile(&tmK, sK, bar_k, 0);
     load_tile(&tmV, sV, bar_v, 0);
   }
+  if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
 
-  const int q_row = qt * TILE + tid;
+  const int q_row = qt * TILE + row;
   const int q_clamped = min(q_row, p.Sq - 1);
   const float* mask_row = p.mask == nullptr ? nullptr
                                             : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
@@ -205,59 +242,86 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float m_run = -INFINITY, l_run = 0.f;
   uint32_t mma_phase = 0;
 
-  const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+  const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
   const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
   constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
   constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
 
-  if (nkv > 0) ok = wait_all(bar_q, 0);
-  for (int j = 0; j < nkv && ok; ++j) {
-    ok = wait_all(bar_k, j & 1);
-    if (!ok) break;
-    if (tid == 0) {
-      tc_fence_after();
-      const int ksteps = p.d >> 4;
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-        umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_mma);
+  // thread 0: S = Q . K^T as two independent accumulation chains (keys 0-63 and 64-127 of the tile), interleaved so
+  // that consecutive instructions do not wait for one another's accumulator
+  auto issue_s = [&]() {
+    const int ksteps = p.d >> 4;
+    for (int ks = 0; ks < ksteps; ++ks) {
+      const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+        umma_bf16(tmem + g * 64, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o + g * 8192u, k_major_hi),
+                  idesc_s, ks > 0 ? 1u : 0u);
     }
-    ok = wait_all(bar_mma, mma_phase);
-    mma_phase ^= 1u;
+    umma_commit(bar_s);
+  };
+  if (nkv > 0) {
+    ok = wait_all(bar_q, 0);
+    if (ok) ok = wait_all(bar_k, 0);
+    if (ok && tid == 0) {
+      tc_fence_after();
+      issue_s();
+    }
+    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
+  }
+  ATTN_PROF_DECL;
+  for (int j = 0; j < nkv && ok; ++j) {
+    ATTN_PROF(0);
+    ATTN_PROF(1);
+    ok = wait_all(bar_s, j & 1);
     if (!ok) break;
     if (tid == 0 && j + 1 < nkv) load_tile(&tmK, sK, bar_k, (j + 1) * TILE);  // K_j has been consumed
+    if (warp == 0) __syncwarp();
     tc_fence_after();
+    ATTN_PROF(2);
 
-    // ---- softmax of this row over the tile: maximum first, then the probabilities ----
-    const int k0 = j * TILE;
+    // ---- softmax of this group's 64 keys of the row: maximum first, then the probabilities ----
+    const int k0 = j * TILE + grp * 64;
+    // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
+    const bool plain = p.mask == nullptr && j * TILE + TILE <= p.Skv &&
+                       (!p.causal || j * TILE + TILE - 1 <= qt * TILE + off);
     float mx = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t acc[32];
-      float v[32];
-      tmem_ld_32x32(t_row + c * 32, acc);
-      tmem_ld_wait();
-      score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
 #pragma unroll
-      for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+    for (int c = 0; c < 2; ++c) {
+      uint32_t acc[32];
+      tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
+      tmem_ld_wait();
+      if (plain) {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
+      } else {
+        float v[32];
+        score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+      }
     }
+    if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
     const float m_new = fmaxf(m_run, mx);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
     const float alpha = exp2f(m_run - m_use);
     float row_sum = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
       uint32_t acc[32];
       float v[32];
-      tmem_ld_32x32(t_row + c * 32, acc);
+      tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
       tmem_ld_wait();
-      score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+      if (plain) {
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        v[x] = exp2f(v[x] - m_use);
-        row_sum += v[x];
+        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
+      } else {
+        score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
       }
+#pragma unroll
+      for (int x = 0; x < 32; ++x) row_sum += v[x];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         uint4 w;
@@ -265,61 +329,89 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
         w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
         w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-        *reinterpret_cast<uint4*>(gP + ps_offset(tid, c * 4 + q4)) = w;
+        *reinterpret_cast<uint4*>(gP + ps_offset(row, grp * 8 + c * 4 + q4)) = w;
       }
     }
     l_run = l_run * alpha + row_sum;
     m_run = m_new;
+    ATTN_PROF(3);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
+    ATTN_PROF(4);
 
     ok = wait_all(bar_v, j & 1);
     if (!ok) break;
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-        umma_bf16(tmem + 128, make_smem_desc(sP + oa, k_major_hi), make_smem_desc(sV + ks * 2048u, mn_major_hi), idesc_o,
-                  ks > 0 ? 1u : 0u);
+      for (int ks = 0; ks < 4; ++ks) {  // O_g = P_g . V_g over the group's 64 keys, the two chains interleaved
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+          umma_bf16(tmem + 128 + g * OCOLS, make_smem_desc(sP + g * BOX_BYTES + ks * 32u, k_major_hi),
+                    make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, ks > 0 ? 1u : 0u);
       }
       umma_commit(bar_mma);
+      // the next tile's scores right behind: S_j has been consumed, K_{j+1} was requested a softmax ago (if it
+      // never arrives the scores are not issued and every thread's wait for them runs out)
+      if (j + 1 < nkv && mbar_wait_bounded(bar_k, (j + 1) & 1, limit)) issue_s();
     }
+    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
     ok = wait_all(bar_mma, mma_phase);
     mma_phase ^= 1u;
     if (!ok) break;
     if (tid == 0 && j + 1 < nkv) load_tile(&tmV, sV, bar_v, (j + 1) * TILE);
+    if (warp == 0) __syncwarp();
     tc_fence_after();
+    ATTN_PROF(5);
 #pragma unroll
     for (int c = 0; c < DPAD / 32; ++c) {
       uint32_t acc[32];
-      tmem_ld_32x32(t_row + 128 + c * 32, acc);
+      tmem_ld_32x32(t_out + c * 32, acc);
       tmem_ld_wait();
 #pragma unroll
       for (int x = 0; x < 32; ++x) o_acc[c * 32 + x] = fmaf(o_acc[c * 32 + x], alpha, __uint_as_float(acc[x]));
     }
+    ATTN_PROF(6);
     tc_fence_before();
     __syncthreads();
   }
 
   if (ok) {
-    if (q_row < p.Sq) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    // merge the two groups' partial states through shared memory (every product has completed: K, V and P are free)
+    float* xch = reinterpret_cast<float*>(sm.gen + tile_bytes) + row * (DPAD + 2);
+    if (grp == 1) {
+#pragma unroll
+      for (int x = 0; x < DPAD; ++x) xch[x] = o_acc[x];
+      xch[DPAD] = m_run;
+      xch[DPAD + 1] = l_run;
+    }
+    __syncthreads();
+    if (grp == 0 && q_row < p.Sq) {
+      const float m_b = xch[DPAD], l_b = xch[DPAD + 1];
+      const float m_all = fmaxf(m_run, m_b);
+      const float m_use = m_all == -INFINITY ? 0.f : m_all;
+      const float wa = exp2f(m_run - m_use), wb = exp2f(m_b - m_use);
+      const float l_all = l_run * wa + l_b * wb;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      const float fa = wa * inv, fb = wb * inv;
       bf16* dst = p.out + (static_cast<int64_t>(b) * p.Sq + q_row) * p.ld_out + static_cast<int64_t>(h) * p.d;
 #pragma unroll
       for (int x = 0; x < DPAD; x += 8) {
         if (x < p.d) {
+          float r[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) r[i] = o_acc[x + i] * fa + xch[x + i] * fb;
           uint4 w;
-          w.x = pack_bf16x2(o_acc[x + 0] * inv, o_acc[x + 1] * inv);
-          w.y = pack_bf16x2(o_acc[x + 2] * inv, o_acc[x + 3] * inv);
-          w.z = pack_bf16x2(o_acc[x + 4] * inv, o_acc[x + 5] * inv);
-          w.w = pack_bf16x2(o_acc[x + 6] * inv, o_acc[x + 7] * inv);
+          w.x = pack_bf16x2(r[0], r[1]);
+          w.y = pack_bf16x2(r[2], r[3]);
+          w.z = pack_bf16x2(r[4], r[5]);
+          w.w = pack_bf16x2(r[6], r[7]);
           *reinterpret_cast<uint4*>(dst + x) = w;
         }
       }
       // rows that saw no key at all get +inf so that the backward pass turns their probabilities into zeros
-      p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_run > 0.f ? m_run + log2f(l_run) : INFINITY;
+      p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_all > 0.f ? m_all + log2f(l_all) : INFINITY;
     }
   } else {
     if (tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
@@ -330,7 +422,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -361,25 +453,43 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Backward.  grid = (key tiles, heads, batch).  Shared memory: K, V, Q, dO (DC boxes each), P, dS (2 boxes each).
-// TMEM (512 columns): [0, 128) S, then dQ_i; [128, 256) dP; [256, 256 + d) dV; [384, 384 + d) dK.
+// Backward.  grid = (key tiles, heads, batch), 512 threads: four threads per row, thread group c = warp / 4 owns the
+// 32 columns [32c, 32c + 32) of every 128-column accumulator row (no reduction across the threads of a row is
+// needed: the row statistics lse and delta are inputs).
+//
+// Per query tile i:  group A(i) = {S = Q_i . K^T, dP = dO_i . V^T},  elementwise(i) = {P, dS -> shared memory},
+//                    group B(i) = {dV += P^T . dO_i, dK += dS^T . Q_i, dQ_i = dS . K},  read-out(i) = dQ_i -> global.
+// head_dim <= 64 (PIPE): Q / dO are double-buffered and fetched two tiles ahead, dQ has its own TMEM columns, and
+// thread 0 issues A(i + 1) right behind B(i), so the tensor cores compute the next scores while the threads drain
+// dQ_i; only elementwise(i) -> B(i) stays serial.  head_dim > 64: one Q / dO buffer, dQ_i reuses the S columns, the
+// four steps run one after the other.
+// Shared memory: K, V, NBUF x (Q, dO) (DC boxes each), P, dS (2 boxes each).
+// TMEM (512 columns): [0, 128) S; [128, 256) dP; PIPE: [256, 320) dV, [320, 384) dK, [384, 448) dQ;
+//                     otherwise [256, 384) dV, [384, 512) dK, dQ in [0, 128).
+constexpr int BWD_THREADS = 512;
+
 template <int DPAD>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const Params p) {
+  constexpr bool PIPE = DPAD <= 64;
+  constexpr int NBUF = PIPE ? 2 : 1;
+  constexpr uint32_t COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
   const uint32_t tile_bytes = DC * BOX_BYTES;
-  const uint32_t sK = sm.base, sV = sK + tile_bytes, sQ = sV + tile_bytes, sdO = sQ + tile_bytes;
-  const uint32_t sP = sdO + tile_bytes, sdS = sP + PS_BYTES;
+  const uint32_t sK = sm.base, sV = sK + tile_bytes, sQ0 = sV + tile_bytes;  // then per buffer: Q, dO
+  const uint32_t sP = sQ0 + 2 * NBUF * tile_bytes, sdS = sP + PS_BYTES;
   const uint32_t bar0 = sdS + PS_BYTES;
-  const uint32_t bar_kv = bar0, bar_q = bar0 + 8, bar_mma = bar0 + 16, tmem_slot = bar0 + 32;
-  uint8_t* gP = sm.gen + 4 * tile_bytes;
+  const uint32_t bar_kv = bar0, bar_a = bar0 + 8, bar_b = bar0 + 16, bar_q0 = bar0 + 24 /* NBUF barriers */;
+  const uint32_t tmem_slot = bar0 + 48;
+  uint8_t* gP = sm.gen + (2 + 2 * NBUF) * tile_bytes;
   uint8_t* gdS = gP + PS_BYTES;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 32);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 48);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int chunk = warp >> 2, row = tid & 127;
   const int nq = (p.Sq + TILE - 1) / TILE;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int off = p.Skv - p.Sq;
@@ -392,8 +502,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
-    mbar_init(bar_q, 1);
-    mbar_init(bar_mma, 1);
+    mbar_init(bar_a, 1);
+    mbar_init(bar_b, 1);
+    for (int n = 0; n < NBUF; ++n) mbar_init(bar_q0 + 8 * n, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -408,10 +519,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t t_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
   auto load_boxes = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
     for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+  };
+  auto load_q_do = [&](int i, int buf) {  // thread 0
+    const uint32_t bar = bar_q0 + 8 * buf, dst = sQ0 + 2 * buf * tile_bytes;
+    mbar_arrive_expect_tx(bar, 2 * tile_bytes);
+    load_boxes(&tmQ, dst, bar, i * TILE);
+    load_boxes(&tmdO, dst + tile_bytes, bar, i * TILE);
   };
   bool ok = true;
   auto wait_all = [&](uint32_t bar, uint32_t parity) {
@@ -419,48 +536,71 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     return __syncthreads_and(mine) != 0;
   };
 
-  const bool any = i_start < nq;
-  if (tid == 0 && any) {
-    mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
-    load_boxes(&tmK, sK, bar_kv, kt * TILE);
-    load_boxes(&tmV, sV, bar_kv, kt * TILE);
-    mbar_arrive_expect_tx(bar_q, 2 * tile_bytes);
-    load_boxes(&tmQ, sQ, bar_q, i_start * TILE);
-    load_boxes(&tmdO, sdO, bar_q, i_start * TILE);
-  }
-
   const float scale_log2 = p.scale * LOG2E;
   const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S and dP: both operands K-major
   const uint32_t idesc_t = make_idesc_bf16(128, p.d, true, true);     // dV, dK: P^T / dS^T (MN-major A), MN-major B
   const uint32_t idesc_q = make_idesc_bf16(128, p.d, false, true);    // dQ: dS K-major, K_j MN-major
   constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
   constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
-  uint32_t mma_phase = 0;
 
-  if (any) ok = wait_all(bar_kv, 0);
-  for (int i = i_start; i < nq && ok; ++i) {
-    ok = wait_all(bar_q, (i - i_start) & 1);
-    if (!ok) break;
-    if (tid == 0) {
-      tc_fence_after();
-      const int ksteps = p.d >> 4;
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-        umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
-      }
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-        umma_bf16(tmem + 128, make_smem_desc(sdO + o, k_major_hi), make_smem_desc(sV + o, k_major_hi), idesc_s,
-                  ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_mma);
+  // thread 0: the two products of group A for query tile i (its Q / dO are in buffer buf)
+  // Consecutive instructions on one accumulator wait for one another; the independent accumulation chains of a group
+  // are therefore issued interleaved (S with dP; dV with dK with dQ).
+  auto issue_a = [&](int buf) {
+    const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
+    const int ksteps = p.d >> 4;
+    for (int ks = 0; ks < ksteps; ++ks) {
+      const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+      umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
+      umma_bf16(tmem + 128, make_smem_desc(sdO + o, k_major_hi), make_smem_desc(sV + o, k_major_hi), idesc_s,
+                ks > 0 ? 1u : 0u);
     }
-    ok = wait_all(bar_mma, mma_phase);
-    mma_phase ^= 1u;
-    if (!ok) break;
-    tc_fence_after();
+    umma_commit(bar_a);
+  };
+  auto issue_b = [&](int buf, uint32_t accumulate) {
+    const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      // dV[key, x] += sum_q P[q, key] * dO[q, x]
+      umma_bf16(tmem + COL_DV, make_smem_desc(sP + ks * 2048u, mn_major_hi), make_smem_desc(sdO + ks * 2048u, mn_major_hi),
+                idesc_t, ks > 0 ? 1u : accumulate);
+      // dK[key, x] += sum_q dS[q, key] * Q[q, x]
+      umma_bf16(tmem + COL_DK, make_smem_desc(sdS + ks * 2048u, mn_major_hi), make_smem_desc(sQ + ks * 2048u, mn_major_hi),
+                idesc_t, ks > 0 ? 1u : accumulate);
+      // dQ[q, x] = sum_key dS[q, key] * K[key, x]
+      const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+      umma_bf16(tmem + COL_DQ, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi), idesc_q,
+                ks > 0 ? 1u : 0u);
+    }
+    umma_commit(bar_b);
+  };
 
-    const int q_row = i * TILE + tid;
+  const bool any = i_start < nq;
+  if (tid == 0 && any) {
+    mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
+    load_boxes(&tmK, sK, bar_kv, kt * TILE);
+    load_boxes(&tmV, sV, bar_kv, kt * TILE);
+    load_q_do(i_start, 0);
+    if (PIPE && i_start + 1 < nq) load_q_do(i_start + 1, 1);
+  }
+  if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
+  uint32_t phase_a = 0, phase_b = 0;
+  if (any) {
+    ok = wait_all(bar_kv, 0);
+    if (ok) ok = wait_all(bar_q0, 0);
+    if (ok && tid == 0) {
+      tc_fence_after();
+      issue_a(0);
+    }
+    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
+  }
+  ATTN_PROF_DECL;
+  for (int i = i_start; i < nq && ok; ++i) {
+    const int n = i - i_start;
+    const int buf = PIPE ? (n & 1) : 0;
+    ATTN_PROF(0);
+    // row statistics of this tile: requested before the wait for the scores
+    const int q_row = i * TILE + row;
     const bool q_valid = q_row < p.Sq;
     const int q_clamped = min(q_row, p.Sq - 1);
     const int64_t stat = (static_cast<int64_t>(b) * p.H + h) * p.Sq + q_clamped;
@@ -470,20 +610,32 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                                               : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
     const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
     const int k0 = kt * TILE;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+
+    ok = wait_all(bar_a, phase_a);
+    phase_a ^= 1u;
+    if (!ok) break;
+    tc_fence_after();
+    ATTN_PROF(1);
+    {
+      const int c = chunk;
       uint32_t acc[32], dp[32];
       float v[32];
       tmem_ld_32x32(t_row + c * 32, acc);
       tmem_ld_32x32(t_row + 128 + c * 32, dp);
       tmem_ld_wait();
-      score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+      // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
+      const bool plain = p.mask == nullptr && k0 + TILE <= p.Skv && (!p.causal || k0 + TILE - 1 <= i * TILE + off);
+      if (plain) {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -lse));
+      } else {
+        score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - lse);
+      }
       float ds[32];
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        v[x] = exp2f(v[x] - lse);
-        ds[x] = v[x] * (__uint_as_float(dp[x]) - dlt) * p.scale;
-      }
+      for (int x = 0; x < 32; ++x) ds[x] = v[x] * (__uint_as_float(dp[x]) - dlt);  // the score scale is applied to dQ / dK
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         uint4 w;
@@ -491,7 +643,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
         w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
         w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-        const uint32_t o = ps_offset(tid, c * 4 + q4);
+        const uint32_t o = ps_offset(row, c * 4 + q4);
         *reinterpret_cast<uint4*>(gP + o) = w;
         w.x = pack_bf16x2(ds[8 * q4 + 0], ds[8 * q4 + 1]);
         w.y = pack_bf16x2(ds[8 * q4 + 2], ds[8 * q4 + 3]);
@@ -500,72 +652,86 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         *reinterpret_cast<uint4*>(gdS + o) = w;
       }
     }
+    ATTN_PROF(2);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
+    ATTN_PROF(3);
 
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t first = i == i_start ? 0u : 1u;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)  // dV[key, x] += sum_q P[q, key] * dO[q, x]
-        umma_bf16(tmem + 256, make_smem_desc(sP + ks * 2048u, mn_major_hi), make_smem_desc(sdO + ks * 2048u, mn_major_hi),
-                  idesc_t, ks > 0 ? 1u : first);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks)  // dK[key, x] += sum_q dS[q, key] * Q[q, x]
-        umma_bf16(tmem + 384, make_smem_desc(sdS + ks * 2048u, mn_major_hi), make_smem_desc(sQ + ks * 2048u, mn_major_hi),
-                  idesc_t, ks > 0 ? 1u : first);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {  // dQ[q, x] = sum_key dS[q, key] * K[key, x]
-        const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-        umma_bf16(tmem, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi), idesc_q,
-                  ks > 0 ? 1u : 0u);
+      issue_b(buf, n == 0 ? 0u : 1u);
+      ATTN_PROF(8);
+      if (PIPE && i + 1 < nq) {
+        // the next tile's Q / dO were requested two tiles ago; if they never arrive, A(i + 1) is not issued and
+        // every thread's wait for it runs out
+        const bool landed = mbar_wait_bounded(bar_q0 + 8 * (buf ^ 1), ((n + 1) >> 1) & 1, limit);
+        ATTN_PROF(9);
+        if (landed) issue_a(buf ^ 1);
+        ATTN_PROF(10);
       }
-      umma_commit(bar_mma);
     }
-    ok = wait_all(bar_mma, mma_phase);
-    mma_phase ^= 1u;
+    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
+    ATTN_PROF(4);
+    ok = wait_all(bar_b, phase_b);
+    phase_b ^= 1u;
     if (!ok) break;
-    if (tid == 0 && i + 1 < nq) {  // Q_i and dO_i have been consumed
-      mbar_arrive_expect_tx(bar_q, 2 * tile_bytes);
-      load_boxes(&tmQ, sQ, bar_q, (i + 1) * TILE);
-      load_boxes(&tmdO, sdO, bar_q, (i + 1) * TILE);
+    ATTN_PROF(5);
+    if (tid == 0) {  // Q_i and dO_i have been consumed
+      if (PIPE) {
+        if (i + 2 < nq) load_q_do(i + 2, buf);
+      } else if (i + 1 < nq) {
+        load_q_do(i + 1, 0);
+      }
     }
+    if (warp == 0) __syncwarp();
     tc_fence_after();
     {
       float* dst = p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q_clamped) * (static_cast<int64_t>(p.H) * p.d) +
                    static_cast<int64_t>(h) * p.d;
-#pragma unroll
-      for (int c = 0; c < DPAD / 32; ++c) {
+      if (chunk < DPAD / 32) {  // uniform per warp
+        const int c = chunk;
         uint32_t acc[32];
-        tmem_ld_32x32(t_row + c * 32, acc);
+        tmem_ld_32x32(t_row + COL_DQ + c * 32, acc);
         tmem_ld_wait();
-        if (q_valid) {
+        if (q_valid && !(p.experiment & 1)) {
 #pragma unroll
           for (int x = 0; x < 32; x += 4)
             if (c * 32 + x < p.d)
-              red_add_v4(dst + c * 32 + x, __uint_as_float(acc[x]), __uint_as_float(acc[x + 1]),
-                         __uint_as_float(acc[x + 2]), __uint_as_float(acc[x + 3]));
+              red_add_v4(dst + c * 32 + x, __uint_as_float(acc[x]) * p.scale, __uint_as_float(acc[x + 1]) * p.scale,
+                         __uint_as_float(acc[x + 2]) * p.scale, __uint_as_float(acc[x + 3]) * p.scale);
         }
       }
     }
     tc_fence_before();
-    __syncthreads();
+    ATTN_PROF(6);
+    if (!PIPE) {
+      __syncthreads();  // dQ_i lives in the S columns: it must be drained before A(i + 1) overwrites them
+      if (i + 1 < nq) {
+        ok = wait_all(bar_q0, (n + 1) & 1);
+        if (!ok) break;
+        if (tid == 0) {
+          tc_fence_after();
+          issue_a(0);
+        }
+        if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
+      }
+    }
   }
 
   if (ok) {
     // tcgen05.ld is warp-collective: every thread reads its lane, only the rows that exist are stored
-    const int key = kt * TILE + tid;
+    const int key = kt * TILE + row;
     const bool key_valid = key < p.Skv;
     const int64_t key_row = static_cast<int64_t>(b) * p.Skv + min(key, p.Skv - 1);
     bf16* dv = p.dv + key_row * p.ld_dv + static_cast<int64_t>(h) * p.d;
     bf16* dk = p.dk + key_row * p.ld_dk + static_cast<int64_t>(h) * p.d;
-#pragma unroll
-    for (int c = 0; c < DPAD / 32; ++c) {
+    if (chunk < DPAD / 32) {  // uniform per warp
+      const int c = chunk;
       uint32_t av[32], ak[32];
       if (any) {
-        tmem_ld_32x32(t_row + 256 + c * 32, av);
-        tmem_ld_32x32(t_row + 384 + c * 32, ak);
+        tmem_ld_32x32(t_row + COL_DV + c * 32, av);
+        tmem_ld_32x32(t_row + COL_DK + c * 32, ak);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -581,10 +747,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             w.z = pack_bf16x2(__uint_as_float(av[x + 4]), __uint_as_float(av[x + 5]));
             w.w = pack_bf16x2(__uint_as_float(av[x + 6]), __uint_as_float(av[x + 7]));
             *reinterpret_cast<uint4*>(dv + c * 32 + x) = w;
-            w.x = pack_bf16x2(__uint_as_float(ak[x + 0]), __uint_as_float(ak[x + 1]));
-            w.y = pack_bf16x2(__uint_as_float(ak[x + 2]), __uint_as_float(ak[x + 3]));
-            w.z = pack_bf16x2(__uint_as_float(ak[x + 4]), __uint_as_float(ak[x + 5]));
-            w.w = pack_bf16x2(__uint_as_float(ak[x + 6]), __uint_as_float(ak[x + 7]));
+            w.x = pack_bf16x2(__uint_as_float(ak[x + 0]) * p.scale, __uint_as_float(ak[x + 1]) * p.scale);
+            w.y = pack_bf16x2(__uint_as_float(ak[x + 2]) * p.scale, __uint_as_float(ak[x + 3]) * p.scale);
+            w.z = pack_bf16x2(__uint_as_float(ak[x + 4]) * p.scale, __uint_as_float(ak[x + 5]) * p.scale);
+            w.w = pack_bf16x2(__uint_as_float(ak[x + 6]) * p.scale, __uint_as_float(ak[x + 7]) * p.scale);
             *reinterpret_cast<uint4*>(dk + c * 32 + x) = w;
           }
         }
@@ -660,6 +826,7 @@ static Params make_params(const leanffn_attention_desc* d) {
   Params p{};
   p.B = d->batch, p.H = d->heads, p.Sq = d->q_len, p.Skv = d->kv_len, p.d = d->head_dim;
   p.causal = d->causal;
+  p.experiment = d->reserved0;
   p.scale = d->scale;
   p.mask = d->mask;
   p.mask_sb = d->mask_stride_b, p.mask_sh = d->mask_stride_h, p.mask_sq = d->mask_stride_q;
@@ -705,7 +872,7 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
     auto kern = attn::attention_fwd_kernel<DPAD>;                                  \
     e = attn::set_smem(kern, smem);                                                \
     if (e == cudaSuccess) {                                                        \
-      kern<<<grid, attn::THREADS, smem, st>>>(tq, tk, tv, p);                      \
+      kern<<<grid, attn::FWD_THREADS, smem, st>>>(tq, tk, tv, p);                      \
       e = cudaGetLastError();                                                      \
     }                                                                              \
   }
@@ -737,14 +904,14 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
   e = cudaGetLastError();
   if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
   const int dc = (d->head_dim + 63) / 64;
-  const size_t smem = 4 * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 64 + 1024;
+  const size_t smem = (dc == 1 ? 6 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 64 + 1024;
   const dim3 grid((d->kv_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
 #define ATTN_BWD(DPAD)                                                             \
   {                                                                                \
     auto kern = attn::attention_bwd_kernel<DPAD>;                                  \
     e = attn::set_smem(kern, smem);                                                \
     if (e == cudaSuccess) {                                                        \
-      kern<<<grid, attn::THREADS, smem, st>>>(tq, tk, tv, tdo, p);                 \
+      kern<<<grid, attn::BWD_THREADS, smem, st>>>(tq, tk, tv, tdo, p);                 \
       e = cudaGetLastError();                                                      \
     }                                                                              \
   }
@@ -755,6 +922,16 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
 #undef ATTN_BWD
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }
+
+#ifdef LEANFFN_ATTN_PROFILE
+extern "C" int32_t leanffn_attention_profile(long long* out16) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, attn::g_attn_prof, sizeof(long long) * 16);
+  long long zero[16] = {0};
+  cudaMemcpyToSymbol(attn::g_attn_prof, zero, sizeof(zero));
+  return 0;
+}
+#endif
 
 extern "C" int32_t leanffn_rotary(const void* x, int32_t x_dtype, int64_t ld_x, const float* cos_table,
                                   const float* sin_table, int64_t ld_table, void* y, int32_t y_dtype, int64_t ld_y,
