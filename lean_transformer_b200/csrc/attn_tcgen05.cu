@@ -453,20 +453,27 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Backward.  grid = (key tiles, heads, batch), 512 threads: four threads per row, thread group c = warp / 4 owns the
-// 32 columns [32c, 32c + 32) of every 128-column accumulator row (no reduction across the threads of a row is
-// needed: the row statistics lse and delta are inputs).
+// Backward.  grid = (key tiles, heads, batch).  16 compute warps + 1 issuing warp.
 //
-// Per query tile i:  group A(i) = {S = Q_i . K^T, dP = dO_i . V^T},  elementwise(i) = {P, dS -> shared memory},
-//                    group B(i) = {dV += P^T . dO_i, dK += dS^T . Q_i, dQ_i = dS . K},  read-out(i) = dQ_i -> global.
-// head_dim <= 64 (PIPE): Q / dO are double-buffered and fetched two tiles ahead, dQ has its own TMEM columns, and
-// thread 0 issues A(i + 1) right behind B(i), so the tensor cores compute the next scores while the threads drain
-// dQ_i; only elementwise(i) -> B(i) stays serial.  head_dim > 64: one Q / dO buffer, dQ_i reuses the S columns, the
-// four steps run one after the other.
-// Shared memory: K, V, NBUF x (Q, dO) (DC boxes each), P, dS (2 boxes each).
+// Compute warps: four threads per row, thread group c = warp / 4 owns the 32 columns [32c, 32c + 32) of every
+// 128-column accumulator row (no reduction across the threads of a row is needed: the row statistics lse and delta are
+// inputs).  Lane 0 of the issuing warp requests every tile (TMA) and issues every product; issuing blocks while the
+// tensor cores' queue is full, so this thread does nothing else and the compute warps never wait for it to come back.
+//
+// Per query tile i:  group A(i) = {S = Q_i . K^T, dP = dO_i . V^T}          -> bar_a
+//                    elementwise(i): P = exp2(S - lse), dS = P * (dP - delta) -> shared memory, 16 arrivals on bar_pds
+//                    group B(i) = {dQ_i = dS . K -> bar_dq;  dV += P^T . dO_i, dK += dS^T . Q_i -> bar_b}
+//                    read-out(i): dQ_i * scale added to the fp32 gradient in global memory -> 16 arrivals on bar_drain
+// The only hand-overs are mbarriers with bounded waits: no block-wide barrier inside the loop.  Order on the tensor cores:
+// A(i), dQ(i), dV/dK(i), A(i + 1), ...: the compute warps drain dQ_i while dV/dK(i) and A(i + 1) run.
+// head_dim <= 64 (PIPE): Q / dO double-buffered and fetched two tiles ahead, dQ has its own TMEM columns and is
+// transposed through shared memory so that a warp's vector reductions cover whole rows (full 32-byte sectors).
+// head_dim > 64: one Q / dO buffer; dQ_i reuses the S columns, so A(i + 1) waits for the read-out (bar_drain).
+// Shared memory: K, V, NBUF x (Q, dO) (DC boxes each), P, dS (2 boxes each), PIPE: dQ staging [128][DPAD + 4] fp32.
 // TMEM (512 columns): [0, 128) S; [128, 256) dP; PIPE: [256, 320) dV, [320, 384) dK, [384, 448) dQ;
 //                     otherwise [256, 384) dV, [384, 512) dK, dQ in [0, 128).
-constexpr int BWD_THREADS = 512;
+constexpr int BWD_COMPUTE_WARPS = 16;
+constexpr int BWD_THREADS = 32 * (BWD_COMPUTE_WARPS + 1);
 
 template <int DPAD>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -475,6 +482,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr bool PIPE = DPAD <= 64;
   constexpr int NBUF = PIPE ? 2 : 1;
   constexpr uint32_t COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
+  constexpr int STAGE_PITCH = DPAD + 4;  // floats per staged dQ row
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
@@ -482,14 +490,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t sK = sm.base, sV = sK + tile_bytes, sQ0 = sV + tile_bytes;  // then per buffer: Q, dO
   const uint32_t sP = sQ0 + 2 * NBUF * tile_bytes, sdS = sP + PS_BYTES;
   const uint32_t bar0 = sdS + PS_BYTES;
-  const uint32_t bar_kv = bar0, bar_a = bar0 + 8, bar_b = bar0 + 16, bar_q0 = bar0 + 24 /* NBUF barriers */;
-  const uint32_t tmem_slot = bar0 + 48;
+  const uint32_t bar_kv = bar0, bar_a = bar0 + 8, bar_b = bar0 + 16, bar_dq = bar0 + 24, bar_pds = bar0 + 32;
+  const uint32_t bar_drain = bar0 + 40, bar_q0 = bar0 + 48 /* NBUF barriers */, bar_stage = bar0 + 64, tmem_slot = bar0 + 72;
   uint8_t* gP = sm.gen + (2 + 2 * NBUF) * tile_bytes;
   uint8_t* gdS = gP + PS_BYTES;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 48);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 72);
+  float* stage = reinterpret_cast<float*>(gdS + PS_BYTES + 128);  // PIPE only
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk = warp >> 2, row = tid & 127;
+  const bool issuer = warp == BWD_COMPUTE_WARPS;
   const int nq = (p.Sq + TILE - 1) / TILE;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int off = p.Skv - p.Sq;
@@ -498,12 +508,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int first_q = kt * TILE - off;  // smallest query row that may see the first key of this tile
     i_start = first_q <= 0 ? 0 : first_q / TILE;
   }
+  const int n_iter = max(nq - i_start, 0);
   const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
     mbar_init(bar_a, 1);
     mbar_init(bar_b, 1);
+    mbar_init(bar_dq, 1);
+    mbar_init(bar_pds, BWD_COMPUTE_WARPS);
+    mbar_init(bar_drain, BWD_COMPUTE_WARPS);
+    mbar_init(bar_stage, BWD_COMPUTE_WARPS);
     for (int n = 0; n < NBUF; ++n) mbar_init(bar_q0 + 8 * n, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -520,244 +535,260 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t t_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-
-  auto load_boxes = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
-    for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
-  };
-  auto load_q_do = [&](int i, int buf) {  // thread 0
-    const uint32_t bar = bar_q0 + 8 * buf, dst = sQ0 + 2 * buf * tile_bytes;
-    mbar_arrive_expect_tx(bar, 2 * tile_bytes);
-    load_boxes(&tmQ, dst, bar, i * TILE);
-    load_boxes(&tmdO, dst + tile_bytes, bar, i * TILE);
-  };
   bool ok = true;
-  auto wait_all = [&](uint32_t bar, uint32_t parity) {
-    const bool mine = mbar_wait_bounded(bar, parity, limit);
-    return __syncthreads_and(mine) != 0;
-  };
 
-  const float scale_log2 = p.scale * LOG2E;
-  const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S and dP: both operands K-major
-  const uint32_t idesc_t = make_idesc_bf16(128, p.d, true, true);     // dV, dK: P^T / dS^T (MN-major A), MN-major B
-  const uint32_t idesc_q = make_idesc_bf16(128, p.d, false, true);    // dQ: dS K-major, K_j MN-major
-  constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
-  constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
-
-  // thread 0: the two products of group A for query tile i (its Q / dO are in buffer buf)
-  // Consecutive instructions on one accumulator wait for one another; the independent accumulation chains of a group
-  // are therefore issued interleaved (S with dP; dV with dK with dQ).
-  auto issue_a = [&](int buf) {
-    const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
-    const int ksteps = p.d >> 4;
-    for (int ks = 0; ks < ksteps; ++ks) {
-      const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-      umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
-      umma_bf16(tmem + 128, make_smem_desc(sdO + o, k_major_hi), make_smem_desc(sV + o, k_major_hi), idesc_s,
-                ks > 0 ? 1u : 0u);
-    }
-    umma_commit(bar_a);
-  };
-  auto issue_b = [&](int buf, uint32_t accumulate) {
-    const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      // dV[key, x] += sum_q P[q, key] * dO[q, x]
-      umma_bf16(tmem + COL_DV, make_smem_desc(sP + ks * 2048u, mn_major_hi), make_smem_desc(sdO + ks * 2048u, mn_major_hi),
-                idesc_t, ks > 0 ? 1u : accumulate);
-      // dK[key, x] += sum_q dS[q, key] * Q[q, x]
-      umma_bf16(tmem + COL_DK, make_smem_desc(sdS + ks * 2048u, mn_major_hi), make_smem_desc(sQ + ks * 2048u, mn_major_hi),
-                idesc_t, ks > 0 ? 1u : accumulate);
-      // dQ[q, x] = sum_key dS[q, key] * K[key, x]
-      const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-      umma_bf16(tmem + COL_DQ, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi), idesc_q,
-                ks > 0 ? 1u : 0u);
-    }
-    umma_commit(bar_b);
-  };
-
-  const bool any = i_start < nq;
-  if (tid == 0 && any) {
-    mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
-    load_boxes(&tmK, sK, bar_kv, kt * TILE);
-    load_boxes(&tmV, sV, bar_kv, kt * TILE);
-    load_q_do(i_start, 0);
-    if (PIPE && i_start + 1 < nq) load_q_do(i_start + 1, 1);
-  }
-  if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
-  uint32_t phase_a = 0, phase_b = 0;
-  if (any) {
-    ok = wait_all(bar_kv, 0);
-    if (ok) ok = wait_all(bar_q0, 0);
-    if (ok && tid == 0) {
-      tc_fence_after();
-      issue_a(0);
-    }
-    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
-  }
-  ATTN_PROF_DECL;
-  for (int i = i_start; i < nq && ok; ++i) {
-    const int n = i - i_start;
-    const int buf = PIPE ? (n & 1) : 0;
-    ATTN_PROF(0);
-    // row statistics of this tile: requested before the wait for the scores
-    const int q_row = i * TILE + row;
-    const bool q_valid = q_row < p.Sq;
-    const int q_clamped = min(q_row, p.Sq - 1);
-    const int64_t stat = (static_cast<int64_t>(b) * p.H + h) * p.Sq + q_clamped;
-    const float lse = q_valid ? __ldg(p.lse + stat) : INFINITY;  // +inf: the row's probabilities become zero
-    const float dlt = q_valid ? __ldg(p.delta + stat) : 0.f;
-    const float* mask_row = p.mask == nullptr ? nullptr
-                                              : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
-    const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
-    const int k0 = kt * TILE;
-
-    ok = wait_all(bar_a, phase_a);
-    phase_a ^= 1u;
-    if (!ok) break;
-    tc_fence_after();
-    ATTN_PROF(1);
-    {
-      const int c = chunk;
-      uint32_t acc[32], dp[32];
-      float v[32];
-      tmem_ld_32x32(t_row + c * 32, acc);
-      tmem_ld_32x32(t_row + 128 + c * 32, dp);
-      tmem_ld_wait();
-      // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
-      const bool plain = p.mask == nullptr && k0 + TILE <= p.Skv && (!p.causal || k0 + TILE - 1 <= i * TILE + off);
-      if (plain) {
-#pragma unroll
-        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -lse));
-      } else {
-        score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
-#pragma unroll
-        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - lse);
-      }
-      float ds[32];
-#pragma unroll
-      for (int x = 0; x < 32; ++x) ds[x] = v[x] * (__uint_as_float(dp[x]) - dlt);  // the score scale is applied to dQ / dK
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint4 w;
-        w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-        w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-        w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-        w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-        const uint32_t o = ps_offset(row, c * 4 + q4);
-        *reinterpret_cast<uint4*>(gP + o) = w;
-        w.x = pack_bf16x2(ds[8 * q4 + 0], ds[8 * q4 + 1]);
-        w.y = pack_bf16x2(ds[8 * q4 + 2], ds[8 * q4 + 3]);
-        w.z = pack_bf16x2(ds[8 * q4 + 4], ds[8 * q4 + 5]);
-        w.w = pack_bf16x2(ds[8 * q4 + 6], ds[8 * q4 + 7]);
-        *reinterpret_cast<uint4*>(gdS + o) = w;
-      }
-    }
-    ATTN_PROF(2);
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    ATTN_PROF(3);
-
-    if (tid == 0) {
-      tc_fence_after();
-      issue_b(buf, n == 0 ? 0u : 1u);
-      ATTN_PROF(8);
-      if (PIPE && i + 1 < nq) {
-        // the next tile's Q / dO were requested two tiles ago; if they never arrive, A(i + 1) is not issued and
-        // every thread's wait for it runs out
-        const bool landed = mbar_wait_bounded(bar_q0 + 8 * (buf ^ 1), ((n + 1) >> 1) & 1, limit);
-        ATTN_PROF(9);
-        if (landed) issue_a(buf ^ 1);
-        ATTN_PROF(10);
-      }
-    }
-    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
-    ATTN_PROF(4);
-    ok = wait_all(bar_b, phase_b);
-    phase_b ^= 1u;
-    if (!ok) break;
-    ATTN_PROF(5);
-    if (tid == 0) {  // Q_i and dO_i have been consumed
-      if (PIPE) {
-        if (i + 2 < nq) load_q_do(i + 2, buf);
-      } else if (i + 1 < nq) {
-        load_q_do(i + 1, 0);
-      }
-    }
-    if (warp == 0) __syncwarp();
-    tc_fence_after();
-    {
-      float* dst = p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q_clamped) * (static_cast<int64_t>(p.H) * p.d) +
-                   static_cast<int64_t>(h) * p.d;
-      if (chunk < DPAD / 32) {  // uniform per warp
-        const int c = chunk;
-        uint32_t acc[32];
-        tmem_ld_32x32(t_row + COL_DQ + c * 32, acc);
-        tmem_ld_wait();
-        if (q_valid && !(p.experiment & 1)) {
-#pragma unroll
-          for (int x = 0; x < 32; x += 4)
-            if (c * 32 + x < p.d)
-              red_add_v4(dst + c * 32 + x, __uint_as_float(acc[x]) * p.scale, __uint_as_float(acc[x + 1]) * p.scale,
-                         __uint_as_float(acc[x + 2]) * p.scale, __uint_as_float(acc[x + 3]) * p.scale);
+  if (issuer) {
+    if (lane == 0 && n_iter > 0) {
+      auto load_boxes = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
+        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+      };
+      auto load_q_do = [&](int i, int buf) {
+        const uint32_t bar = bar_q0 + 8 * buf, dst = sQ0 + 2 * buf * tile_bytes;
+        mbar_arrive_expect_tx(bar, 2 * tile_bytes);
+        load_boxes(&tmQ, dst, bar, i * TILE);
+        load_boxes(&tmdO, dst + tile_bytes, bar, i * TILE);
+      };
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S and dP: both operands K-major
+      const uint32_t idesc_t = make_idesc_bf16(128, p.d, true, true);     // dV, dK: P^T / dS^T (MN-major A), MN-major B
+      const uint32_t idesc_q = make_idesc_bf16(128, p.d, false, true);    // dQ: dS K-major, K_j MN-major
+      constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
+      constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
+      auto issue_a = [&](int buf) {
+        const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
+        const int ksteps = p.d >> 4;
+        for (int ks = 0; ks < ksteps; ++ks) {
+          const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+          umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
+          umma_bf16(tmem + 128, make_smem_desc(sdO + o, k_major_hi), make_smem_desc(sV + o, k_major_hi), idesc_s,
+                    ks > 0 ? 1u : 0u);
         }
+        umma_commit(bar_a);
+      };
+      auto issue_b = [&](int buf, uint32_t accumulate) {
+        const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // dQ[q, x] = sum_key dS[q, key] * K[key, x]: first, the compute warps wait for it
+          const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+          umma_bf16(tmem + COL_DQ, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi),
+                    idesc_q, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_dq);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // dV[key, x] += sum_q P[q, key] * dO[q, x]
+          umma_bf16(tmem + COL_DV, make_smem_desc(sP + ks * 2048u, mn_major_hi),
+                    make_smem_desc(sdO + ks * 2048u, mn_major_hi), idesc_t, ks > 0 ? 1u : accumulate);
+          // dK[key, x] += sum_q dS[q, key] * Q[q, x]
+          umma_bf16(tmem + COL_DK, make_smem_desc(sdS + ks * 2048u, mn_major_hi),
+                    make_smem_desc(sQ + ks * 2048u, mn_major_hi), idesc_t, ks > 0 ? 1u : accumulate);
+        }
+        umma_commit(bar_b);
+      };
+
+      mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
+      load_boxes(&tmK, sK, bar_kv, kt * TILE);
+      load_boxes(&tmV, sV, bar_kv, kt * TILE);
+      load_q_do(i_start, 0);
+      if (PIPE && n_iter > 1) load_q_do(i_start + 1, 1);
+      bool go = mbar_wait_bounded(bar_kv, 0, limit) && mbar_wait_bounded(bar_q0, 0, limit);
+      if (go) {
+        tc_fence_after();
+        issue_a(0);
       }
-    }
-    tc_fence_before();
-    ATTN_PROF(6);
-    if (!PIPE) {
-      __syncthreads();  // dQ_i lives in the S columns: it must be drained before A(i + 1) overwrites them
-      if (i + 1 < nq) {
-        ok = wait_all(bar_q0, (n + 1) & 1);
-        if (!ok) break;
-        if (tid == 0) {
+      for (int n = 0; n < n_iter && go; ++n) {
+        const int i = i_start + n;
+        const int buf = PIPE ? (n & 1) : 0;
+        go = mbar_wait_bounded(bar_pds, n & 1, limit);  // P, dS written; S, dP read; dQ of the tile before drained
+        if (!go) break;
+        tc_fence_after();
+        issue_b(buf, n == 0 ? 0u : 1u);
+        if (PIPE) {
+          if (n + 1 < n_iter) {
+            go = mbar_wait_bounded(bar_q0 + 8 * (buf ^ 1), ((n + 1) >> 1) & 1, limit);
+            if (!go) break;
+            issue_a(buf ^ 1);
+          }
+          go = mbar_wait_bounded(bar_b, n & 1, limit);  // Q_i, dO_i consumed: their buffer takes tile i + 2
+          if (!go) break;
+          if (n + 2 < n_iter) load_q_do(i + 2, buf);
+        } else if (n + 1 < n_iter) {
+          go = mbar_wait_bounded(bar_b, n & 1, limit);
+          if (!go) break;
+          load_q_do(i + 1, 0);
+          // dQ_i lives in the S columns: the next scores wait until the compute warps have drained it
+          go = mbar_wait_bounded(bar_drain, n & 1, limit) && mbar_wait_bounded(bar_q0, (n + 1) & 1, limit);
+          if (!go) break;
           tc_fence_after();
           issue_a(0);
         }
-        if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
       }
+      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
     }
-  }
+    __syncwarp();
+  } else {
+    const float scale_log2 = p.scale * LOG2E;
+    const int k0 = kt * TILE;
+    auto wait_warp = [&](uint32_t bar, uint32_t parity) {  // the whole warp continues or the whole warp leaves
+      return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, limit)) != 0;
+    };
+    for (int n = 0; n < n_iter; ++n) {
+      const int i = i_start + n;
+      // row statistics of this tile: requested before the wait for the scores
+      const int q_row = i * TILE + row;
+      const bool q_valid = q_row < p.Sq;
+      const int q_clamped = min(q_row, p.Sq - 1);
+      const int64_t stat = (static_cast<int64_t>(b) * p.H + h) * p.Sq + q_clamped;
+      const float lse = q_valid ? __ldg(p.lse + stat) : INFINITY;  // +inf: the row's probabilities become zero
+      const float dlt = q_valid ? __ldg(p.delta + stat) : 0.f;
+      const float* mask_row = p.mask == nullptr ? nullptr
+                                                : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
+      const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
 
-  if (ok) {
-    // tcgen05.ld is warp-collective: every thread reads its lane, only the rows that exist are stored
-    const int key = kt * TILE + row;
-    const bool key_valid = key < p.Skv;
-    const int64_t key_row = static_cast<int64_t>(b) * p.Skv + min(key, p.Skv - 1);
-    bf16* dv = p.dv + key_row * p.ld_dv + static_cast<int64_t>(h) * p.d;
-    bf16* dk = p.dk + key_row * p.ld_dk + static_cast<int64_t>(h) * p.d;
-    if (chunk < DPAD / 32) {  // uniform per warp
-      const int c = chunk;
-      uint32_t av[32], ak[32];
-      if (any) {
-        tmem_ld_32x32(t_row + COL_DV + c * 32, av);
-        tmem_ld_32x32(t_row + COL_DK + c * 32, ak);
+      ok = wait_warp(bar_a, n & 1);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        const int c = chunk;
+        uint32_t acc[32], dp[32];
+        float v[32];
+        tmem_ld_32x32(t_row + c * 32, acc);
+        tmem_ld_32x32(t_row + 128 + c * 32, dp);
         tmem_ld_wait();
-      } else {
+        // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
+        const bool plain = p.mask == nullptr && k0 + TILE <= p.Skv && (!p.causal || k0 + TILE - 1 <= i * TILE + off);
+        if (plain) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) av[x] = 0u, ak[x] = 0u;
+          for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -lse));
+        } else {
+          score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+          for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - lse);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+          w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+          w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+          w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+          *reinterpret_cast<uint4*>(gP + ps_offset(row, c * 4 + q4)) = w;
+        }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) v[x] *= __uint_as_float(dp[x]) - dlt;  // dS; the score scale is applied to dQ / dK
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+          w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+          w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+          w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+          *reinterpret_cast<uint4*>(gdS + ps_offset(row, c * 4 + q4)) = w;
+        }
       }
-      if (key_valid) {
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pds);
+
+      ok = wait_warp(bar_dq, n & 1);
+      if (!ok) break;
+      tc_fence_after();
+      if (PIPE) {
+        // transpose dQ_i through shared memory: lane = row on the way in, consecutive lanes = consecutive 16-byte
+        // pieces of a row on the way out
+        if (chunk < DPAD / 32) {  // uniform per warp
+          uint32_t acc[32];
+          tmem_ld_32x32(t_row + COL_DQ + chunk * 32, acc);
+          tmem_ld_wait();
+          float4* dst4 = reinterpret_cast<float4*>(stage + row * STAGE_PITCH + chunk * 32);
 #pragma unroll
-        for (int x = 0; x < 32; x += 8) {
-          if (c * 32 + x < p.d) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(av[x + 0]), __uint_as_float(av[x + 1]));
-            w.y = pack_bf16x2(__uint_as_float(av[x + 2]), __uint_as_float(av[x + 3]));
-            w.z = pack_bf16x2(__uint_as_float(av[x + 4]), __uint_as_float(av[x + 5]));
-            w.w = pack_bf16x2(__uint_as_float(av[x + 6]), __uint_as_float(av[x + 7]));
-            *reinterpret_cast<uint4*>(dv + c * 32 + x) = w;
-            w.x = pack_bf16x2(__uint_as_float(ak[x + 0]) * p.scale, __uint_as_float(ak[x + 1]) * p.scale);
-            w.y = pack_bf16x2(__uint_as_float(ak[x + 2]) * p.scale, __uint_as_float(ak[x + 3]) * p.scale);
-            w.z = pack_bf16x2(__uint_as_float(ak[x + 4]) * p.scale, __uint_as_float(ak[x + 5]) * p.scale);
-            w.w = pack_bf16x2(__uint_as_float(ak[x + 6]) * p.scale, __uint_as_float(ak[x + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(dk + c * 32 + x) = w;
+          for (int x = 0; x < 8; ++x)
+            dst4[x] = make_float4(__uint_as_float(acc[4 * x]) * p.scale, __uint_as_float(acc[4 * x + 1]) * p.scale,
+                                  __uint_as_float(acc[4 * x + 2]) * p.scale, __uint_as_float(acc[4 * x + 3]) * p.scale);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_stage);  // staged rows of all 16 warps: a bounded wait, like every other hand-over
+        ok = wait_warp(bar_stage, n & 1);
+        if (!ok) break;
+        const int pieces = p.d >> 2;                    // 16-byte pieces per row
+        const int total = 8 * pieces;                   // this warp's 8 rows
+        const int64_t width = static_cast<int64_t>(p.H) * p.d;
+        for (int idx = lane; idx < total; idx += 32) {
+          const int r = warp * 8 + idx / pieces, c4 = idx % pieces;
+          const int q = i * TILE + r;
+          if (q < p.Sq && !(p.experiment & 1)) {
+            const float4 val = *reinterpret_cast<const float4*>(stage + r * STAGE_PITCH + c4 * 4);
+            red_add_v4(p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q) * width + static_cast<int64_t>(h) * p.d + c4 * 4,
+                       val.x, val.y, val.z, val.w);
+          }
+        }
+      } else {
+        float* dst = p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q_clamped) * (static_cast<int64_t>(p.H) * p.d) +
+                     static_cast<int64_t>(h) * p.d;
+        if (chunk < DPAD / 32) {  // uniform per warp
+          const int c = chunk;
+          uint32_t acc[32];
+          tmem_ld_32x32(t_row + COL_DQ + c * 32, acc);
+          tmem_ld_wait();
+          if (q_valid && !(p.experiment & 1)) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 4)
+              if (c * 32 + x < p.d)
+                red_add_v4(dst + c * 32 + x, __uint_as_float(acc[x]) * p.scale, __uint_as_float(acc[x + 1]) * p.scale,
+                           __uint_as_float(acc[x + 2]) * p.scale, __uint_as_float(acc[x + 3]) * p.scale);
+          }
+        }
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_drain);
+    }
+    if (ok && n_iter > 0) ok = wait_warp(bar_b, (n_iter - 1) & 1);  // the last dV / dK products
+    if (ok) {
+      tc_fence_after();
+      // tcgen05.ld is warp-collective: every thread reads its lane, only the rows that exist are stored
+      const int key = kt * TILE + row;
+      const bool key_valid = key < p.Skv;
+      const int64_t key_row = static_cast<int64_t>(b) * p.Skv + min(key, p.Skv - 1);
+      bf16* dv = p.dv + key_row * p.ld_dv + static_cast<int64_t>(h) * p.d;
+      bf16* dk = p.dk + key_row * p.ld_dk + static_cast<int64_t>(h) * p.d;
+      if (chunk < DPAD / 32) {  // uniform per warp
+        const int c = chunk;
+        uint32_t av[32], ak[32];
+        if (n_iter > 0) {
+          tmem_ld_32x32(t_row + COL_DV + c * 32, av);
+          tmem_ld_32x32(t_row + COL_DK + c * 32, ak);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) av[x] = 0u, ak[x] = 0u;
+        }
+        if (key_valid) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            if (c * 32 + x < p.d) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(av[x + 0]), __uint_as_float(av[x + 1]));
+              w.y = pack_bf16x2(__uint_as_float(av[x + 2]), __uint_as_float(av[x + 3]));
+              w.z = pack_bf16x2(__uint_as_float(av[x + 4]), __uint_as_float(av[x + 5]));
+              w.w = pack_bf16x2(__uint_as_float(av[x + 6]), __uint_as_float(av[x + 7]));
+              *reinterpret_cast<uint4*>(dv + c * 32 + x) = w;
+              w.x = pack_bf16x2(__uint_as_float(ak[x + 0]) * p.scale, __uint_as_float(ak[x + 1]) * p.scale);
+              w.y = pack_bf16x2(__uint_as_float(ak[x + 2]) * p.scale, __uint_as_float(ak[x + 3]) * p.scale);
+              w.z = pack_bf16x2(__uint_as_float(ak[x + 4]) * p.scale, __uint_as_float(ak[x + 5]) * p.scale);
+              w.w = pack_bf16x2(__uint_as_float(ak[x + 6]) * p.scale, __uint_as_float(ak[x + 7]) * p.scale);
+              *reinterpret_cast<uint4*>(dk + c * 32 + x) = w;
+            }
           }
         }
       }
+    } else if (lane == 0 && p.status != nullptr) {
+      atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
     }
-  } else {
-    if (tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
+  }
+  // teardown: after a timeout give copies and products still in flight time to land before the memory is released
+  if (!__syncthreads_and(ok)) {
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) {
     }
@@ -904,7 +935,10 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
   e = cudaGetLastError();
   if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
   const int dc = (d->head_dim + 63) / 64;
-  const size_t smem = (dc == 1 ? 6 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 64 + 1024;
+  // head_dim <= 64: double-buffered Q / dO and the dQ staging rows [128][round32(head_dim) + 4] fp32
+  const int dpad = (d->head_dim + 31) / 32 * 32;
+  const size_t smem = (dc == 1 ? 6 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 128 + 1024 +
+                      (dc == 1 ? 128 * (dpad + 4) * sizeof(float) : 0);
   const dim3 grid((d->kv_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
 #define ATTN_BWD(DPAD)                                                             \
   {                                                                                \
