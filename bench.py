@@ -14,8 +14,11 @@ One JSON line is printed by rank 0.  Workloads (synthetic data, random-init weig
                      rank-128 low-rank term, bf16, 65536 tokens per rank
   dense_fp32_h768    hidden 768, intermediate 3072, 8 x 512 tokens, fp32 end to end (the reference's CPU-runnable
                      case): products run as three TF32 tensor-core products with fp32 accuracy
+  attention_bf16_h768  (other_workloads only, or --attention-only) the attention core of that model alone: rotary +
+                     causal attention, 32 x 2048 tokens, 16 heads of 48, forward + backward
   leangpt_bf16_h768  (other_workloads only) the reference's 12-layer LeanGPT, 32 x 2048 tokens, autocast bf16, with the
-                     reference's modules and with its FFN / linear modules swapped for this package's
+                     reference's modules, with its FFN / linear modules swapped for this package's, and with its
+                     attention cores swapped too
 """
 import argparse
 import json
@@ -482,6 +485,9 @@ def run_ours(args, wl, name):
         for other in [w.strip() for w in args.extra_workload.split(",") if w.strip()]:
             if other != name and other in WORKLOADS:
                 extra[other] = quick_measure(WORKLOADS[other], device, args, other)
+            elif other == "attention_bf16_h768":
+                extra[other] = attention_measure(device)
+                torch.cuda.empty_cache()
             elif other == "leangpt_bf16_h768":
                 try:
                     extra[other] = leangpt_measure(device)
@@ -603,13 +609,61 @@ def quick_measure(wl, device, args, name=""):
                                         "fp32 (TF32x3 tensor cores)" if wl.get("fp32") else "bf16")))
 
 
+def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=20, warmup=3):
+    """The attention core of BASELINE config 4 on its own: rotary + causal attention over batch x seq tokens, heads x
+    head_dim (this package's RotaryAttentionCore: leanffn_rotary + leanffn_attention_forward / backward), forward +
+    backward, device-resident.  FLOPs: 4 * seq^2 * head_dim per head and batch row forward, 2.5 x that backward, halved
+    by the causal rule.  The kernels are bound by the tensor cores' operand feed and the exponentials, so the fraction
+    of the dense-GEMM peak reported here is low by construction; DESIGN.md gives the per-tile budget."""
+    import lean_transformer_b200 as L
+    from lean_transformer_b200 import ops
+
+    hidden = heads * head_dim
+    torch.manual_seed(0)
+    core = L.RotaryAttentionCore(hidden, heads).to(device).train()
+    qkv = torch.randn(batch, seq, 3 * hidden, device=device).to(torch.bfloat16)
+    g = torch.randn(batch, seq, hidden, device=device).to(torch.bfloat16)
+    mask = ((1.0 - torch.ones(seq, seq, device=device).tril()) * -10000.0).view(1, 1, seq, seq)
+
+    def step():
+        leaf = qkv.detach().requires_grad_(True)
+        q, k, v = leaf.split(hidden, dim=-1)
+        out, _ = core(q, k, v, mask)
+        out.backward(g)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    L.check_device_status(device)
+    s = a.elapsed_time(b) * 1e-3 / steps
+    flops = 3.5 * 4.0 * seq * seq * head_dim * heads * batch / 2
+    peaks = load_peaks()
+    achieved = flops / s / 1e12
+    return dict(tokens_per_s=batch * seq / s, ms_per_step=s * 1e3, tflops=achieved, steps=steps, warmup=warmup,
+                gpu_launches_per_step=(ops.launch_count - launches0) / steps,
+                roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
+                              frac=achieved / peaks["bf16_sustained"], traffic=None,
+                              kernel="rotary + attention forward + backward (CUDA events around the whole step)"),
+                config=dict(batch=batch, seq_len=seq, heads=heads, head_dim=head_dim, mask="causal (detected)",
+                            dtype="bf16"))
+
+
 def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
     """BASELINE config 4: the REFERENCE's own 12-layer LeanGPT (hidden 768, 16 heads, rotary, GeGLU, tied embeddings,
     vocab 10 000; imported from the mirror oracle/_ref) on the GPU under autocast(bf16), forward + backward on 32 x 2048
-    random token ids with labels = ids, timed twice on the same weights: with the reference's own modules (stock
-    PyTorch CUDA operators), then with its LeanFFN / GeneralizedLinear modules swapped for this package's
-    (integration.convert_model).  Embeddings, attention core, LM head and loss stay the reference's code in both runs.
-    Also reports the time spent inside the FFN modules (CUDA events around their forward and backward)."""
+    random token ids with labels = ids, timed three times on the same weights: with the reference's own modules (stock
+    PyTorch CUDA operators); with its LeanFFN / GeneralizedLinear modules and the attention blocks' LayerNorm and
+    projections swapped for this package's (integration.convert_model, attention core still the reference's); and with
+    the attention cores swapped too.  Embeddings, LM head and loss stay the reference's code in all runs.
+    Also reports the time spent inside the FFN modules and inside the attention cores (CUDA events around their forward
+    and backward)."""
     from oracle import ref_harness
 
     ref = ref_harness.import_reference()
@@ -757,7 +811,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="dense_bf16_h8192")
-    ap.add_argument("--extra-workload", default="mixed_bf16_h1024,dense_fp32_h768,pixelfly_bf16_h4096,leangpt_bf16_h768",
+    ap.add_argument("--extra-workload", default="mixed_bf16_h1024,dense_fp32_h768,pixelfly_bf16_h4096,attention_bf16_h768,leangpt_bf16_h768",
                     help="comma-separated workloads measured device-resident on one GPU after the headline one and "
                          "reported under other_workloads ('' = none)")
     ap.add_argument("--comm-sms", type=int, default=20, help="SMs left to NCCL while GEMMs run (N > 1)")
@@ -768,11 +822,20 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the workload's token count (smaller cases for ncu captures; not a bench number)")
     ap.add_argument("--skip-e2e", action="store_true", help="device-resident timing only (profiling runs)")
+    ap.add_argument("--attention-only", action="store_true",
+                    help="measure the attention-core workload alone (attention_bf16_h768) and print its line "
+                         "(profiling runs)")
     ap.add_argument("--epilogue-ablation", action="store_true",
                     help="time the GeGLU-backward product with phases of its epilogue left out (measurement build of "
                          "the library only; see epilogue_ablation)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    if args.attention_only:
+        torch.cuda.set_device(0)
+        print(json.dumps(dict(workload="attention_bf16_h768",
+                              **attention_measure(torch.device("cuda", 0), steps=args.steps, warmup=args.warmup))),
+              flush=True)
+        return
     if args.epilogue_ablation:
         torch.cuda.set_device(0)
         epilogue_ablation(torch.device("cuda", 0))

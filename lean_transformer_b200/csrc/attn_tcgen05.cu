@@ -41,7 +41,6 @@ constexpr float LOG2E = 1.4426950408889634f;
 struct Params {
   int32_t B, H, Sq, Skv, d;
   int32_t causal;
-  int32_t experiment;
   float scale;
   const float* mask;
   int64_t mask_sb, mask_sh, mask_sq;
@@ -717,7 +716,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         for (int idx = lane; idx < total; idx += 32) {
           const int r = warp * 8 + idx / pieces, c4 = idx % pieces;
           const int q = i * TILE + r;
-          if (q < p.Sq && !(p.experiment & 1)) {
+          if (q < p.Sq) {
             const float4 val = *reinterpret_cast<const float4*>(stage + r * STAGE_PITCH + c4 * 4);
             red_add_v4(p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q) * width + static_cast<int64_t>(h) * p.d + c4 * 4,
                        val.x, val.y, val.z, val.w);
@@ -731,7 +730,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           uint32_t acc[32];
           tmem_ld_32x32(t_row + COL_DQ + c * 32, acc);
           tmem_ld_wait();
-          if (q_valid && !(p.experiment & 1)) {
+          if (q_valid) {
 #pragma unroll
             for (int x = 0; x < 32; x += 4)
               if (c * 32 + x < p.d)
@@ -857,7 +856,6 @@ static Params make_params(const leanffn_attention_desc* d) {
   Params p{};
   p.B = d->batch, p.H = d->heads, p.Sq = d->q_len, p.Skv = d->kv_len, p.d = d->head_dim;
   p.causal = d->causal;
-  p.experiment = d->reserved0;
   p.scale = d->scale;
   p.mask = d->mask;
   p.mask_sb = d->mask_stride_b, p.mask_sh = d->mask_stride_h, p.mask_sq = d->mask_stride_q;

@@ -4,8 +4,6 @@ device memory and streams only; every computation is a kernel of ``libleanffn_b2
 """
 from typing import Optional, Tuple
 
-import os
-
 import torch
 
 from . import _native as N
@@ -552,7 +550,6 @@ def _attention_desc(q, k, v, heads, scale, mask, causal):
     d = N.AttentionDesc()
     d.batch, d.heads, d.q_len, d.kv_len, d.head_dim = batch, heads, q_len, kv_len, head_dim
     d.causal, d.scale = int(causal), float(scale)
-    d.reserved0 = int(os.environ.get('LEANFFN_ATTN_EXPERIMENT', '0'))
     d.q, d.k, d.v = _ptr(q), _ptr(k), _ptr(v)
     d.ld_q, d.ld_k, d.ld_v = q.stride(1), k.stride(1), v.stride(1)
     d.mask, d.mask_stride_b, d.mask_stride_h, d.mask_stride_q = _ptr(mask), sb, sh, sq
