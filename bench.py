@@ -609,6 +609,11 @@ def quick_measure(wl, device, args, name=""):
                                         "fp32 (TF32x3 tensor cores)" if wl.get("fp32") else "bf16")))
 
 
+def N_lib():
+    from lean_transformer_b200 import _native
+    return _native.lib
+
+
 def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=20, warmup=3):
     """The attention core of BASELINE config 4 on its own: rotary + causal attention over batch x seq tokens, heads x
     head_dim (this package's RotaryAttentionCore: leanffn_rotary + leanffn_attention_forward / backward), forward +
@@ -646,7 +651,49 @@ def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=2
     flops = 3.5 * 4.0 * seq * seq * head_dim * heads * batch / 2
     peaks = load_peaks()
     achieved = flops / s / 1e12
+
+    def timed(fn, n=10):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / n
+
+    # the kernels alone (no rotary, no autograd bookkeeping), and the library's fused attention on the same shape for
+    # context (torch.nn.functional.scaled_dot_product_attention: whichever flash / cuDNN kernel torch picks)
+    scale = head_dim ** -0.5
+    q, k, v = qkv.split(hidden, dim=-1)
+    out, lse = ops.attention_forward(q, k, v, heads, scale, None, True)
+    fwd_ms = timed(lambda: ops.attention_forward(q, k, v, heads, scale, None, True))
+    bwd_ms = timed(lambda: ops.attention_backward(g, q, k, v, out, lse, heads, scale, None, True))
+    library = None
+    try:
+        import torch.nn.functional as F
+        q4, k4, v4 = (t.reshape(batch, seq, heads, head_dim).transpose(1, 2).contiguous().requires_grad_() for t in (q, k, v))
+        g4 = g.reshape(batch, seq, heads, head_dim).transpose(1, 2).contiguous()
+        lib_fwd = timed(lambda: F.scaled_dot_product_attention(q4, k4, v4, is_causal=True))
+        lib_both = timed(lambda: torch.autograd.grad(F.scaled_dot_product_attention(q4, k4, v4, is_causal=True),
+                                                     (q4, k4, v4), g4))
+        library = dict(forward_ms=lib_fwd, forward_backward_ms=lib_both)
+    except Exception as e:  # context only
+        library = dict(unavailable=f"{type(e).__name__}: {e}")
+    phase_clocks = None
+    if hasattr(N_lib(), "leanffn_attention_profile"):  # measurement builds (-DLEANFFN_ATTN_PROFILE) only
+        import ctypes
+        buf = (ctypes.c_longlong * 16)()
+        N_lib().leanffn_attention_profile(buf)
+        ops.attention_forward(q, k, v, heads, scale, None, True)
+        N_lib().leanffn_attention_profile(buf)
+        tiles = (seq + 127) // 128
+        phase_clocks = dict(kernel="attention_fwd_kernel, block (0, 0, 0): SM clocks per key tile",
+                            slots=[int(x) // tiles for x in buf[:8]])
     return dict(tokens_per_s=batch * seq / s, ms_per_step=s * 1e3, tflops=achieved, steps=steps, warmup=warmup,
+                forward_kernel_ms=fwd_ms, backward_kernels_ms=bwd_ms, library_sdpa=library, phase_clocks=phase_clocks,
                 gpu_launches_per_step=(ops.launch_count - launches0) / steps,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
                               frac=achieved / peaks["bf16_sustained"], traffic=None,
