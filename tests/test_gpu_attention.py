@@ -3,7 +3,8 @@ golden vectors the reference produced (needs a B200).
 
 Inputs are rounded to bfloat16 first and the oracle runs in float64 on exactly those values, so what is measured is
 the kernels' own arithmetic: bf16 tensor-core products with fp32 accumulation, fp32 softmax, probabilities and score
-gradients rounded to bf16 before the second products.  Tolerance: rtol 2e-2, atol 1e-2 (the bf16 bar)."""
+gradients rounded to bf16 before the second products.  Tolerance: rtol 2e-2, atol 1e-2 (the bf16 bar), applied
+literally to every element (torch.allclose's rule)."""
 import math
 
 import pytest
@@ -20,9 +21,8 @@ def _bf16(t):
 
 
 def _check(got, want, what):
-    # an attention output is a convex combination of values, its gradients sums over a row of keys or queries:
-    # judged at the size of the tensor (scale_atol), like every other accumulated product in this suite
-    assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=True)
+    # the literal rule |got - ref| <= atol + rtol * |ref| for every element, no outlier budget
+    assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=False)
 
 
 def _run_case(device, batch, heads, q_len, kv_len, head_dim, mask_kind, rotary, seed=0):
