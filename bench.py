@@ -648,6 +648,7 @@ def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=2
     torch.cuda.synchronize()
     L.check_device_status(device)
     s = a.elapsed_time(b) * 1e-3 / steps
+    launches_per_step = (ops.launch_count - launches0) / steps
     flops = 3.5 * 4.0 * seq * seq * head_dim * heads * batch / 2
     peaks = load_peaks()
     achieved = flops / s / 1e12
@@ -694,7 +695,7 @@ def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=2
                             slots=[int(x) // tiles for x in buf[:8]])
     return dict(tokens_per_s=batch * seq / s, ms_per_step=s * 1e3, tflops=achieved, steps=steps, warmup=warmup,
                 forward_kernel_ms=fwd_ms, backward_kernels_ms=bwd_ms, library_sdpa=library, phase_clocks=phase_clocks,
-                gpu_launches_per_step=(ops.launch_count - launches0) / steps,
+                gpu_launches_per_step=launches_per_step,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
                               frac=achieved / peaks["bf16_sustained"], traffic=None,
                               kernel="rotary + attention forward + backward (CUDA events around the whole step)"),

@@ -830,6 +830,77 @@ __global__ void rotary_kernel(const TI* __restrict__ x, int64_t ld_x, const floa
   y[yo + half + i] = static_cast<TO>(yr);
 }
 
+// Same, eight pairs per thread with 16-byte (bf16) / 32-byte (fp32) accesses: half = head_dim / 2 a multiple of 8.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h2[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+  uint4 w;
+  w.x = pack_bf16x2(v[0], v[1]);
+  w.y = pack_bf16x2(v[2], v[3]);
+  w.z = pack_bf16x2(v[4], v[5]);
+  w.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = w;
+}
+
+template <typename TI, typename TO>
+__global__ void rotary_vec_kernel(const TI* __restrict__ x, int64_t ld_x, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, int64_t ld_t, TO* __restrict__ y, int64_t ld_y,
+                                  int64_t rows, int len, int heads, int d, int inverse) {
+  const int half = d >> 1, vecs = half >> 3;
+  const int64_t per_row = static_cast<int64_t>(heads) * vecs;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const int64_t row = idx / per_row;
+  const int rem = static_cast<int>(idx - row * per_row);
+  const int hh = rem / vecs, i = (rem - hh * vecs) * 8;
+  const int pos = static_cast<int>(row % len);
+  const int64_t xo = row * ld_x + static_cast<int64_t>(hh) * d + i, yo = row * ld_y + static_cast<int64_t>(hh) * d + i;
+  float xl[8], xr[8], yl[8], yr[8];
+  load8(x + xo, xl);
+  load8(x + xo + half, xr);
+  if (cos_t != nullptr) {
+    float cl[8], cr[8], sl[8], sr[8];
+    load8(cos_t + pos * ld_t + i, cl);
+    load8(cos_t + pos * ld_t + half + i, cr);
+    load8(sin_t + pos * ld_t + i, sl);
+    load8(sin_t + pos * ld_t + half + i, sr);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (!inverse) {
+        yl[k] = xl[k] * cl[k] - xr[k] * sl[k];
+        yr[k] = xr[k] * cr[k] + xl[k] * sr[k];
+      } else {
+        yl[k] = xl[k] * cl[k] + xr[k] * sr[k];
+        yr[k] = xr[k] * cr[k] - xl[k] * sl[k];
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) yl[k] = xl[k], yr[k] = xr[k];
+  }
+  store8(y + yo, yl);
+  store8(y + yo + half, yr);
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int32_t validate(const leanffn_attention_desc* d, bool backward) {
@@ -978,16 +1049,29 @@ extern "C" int32_t leanffn_rotary(const void* x, int32_t x_dtype, int64_t ld_x, 
     return LEANFFN_ERR_DTYPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t rows = static_cast<int64_t>(batch) * len;
-  const int64_t total = rows * heads * (head_dim / 2);
+  const int half = head_dim / 2;
+  // eight pairs per thread where every access is a whole aligned vector; one pair per thread otherwise
+  const auto vec_ok = [](const void* p, int64_t ld, int32_t dtype) {
+    const int64_t bytes = dtype == LEANFFN_BF16 ? 2 : 4;
+    return (reinterpret_cast<uintptr_t>(p) % 16 == 0) && (ld * bytes) % 16 == 0;
+  };
+  const bool vec = half % 8 == 0 && vec_ok(x, ld_x, x_dtype) && vec_ok(y, ld_y, y_dtype) &&
+                   (cos_table == nullptr || (vec_ok(cos_table, ld_table, LEANFFN_F32) && vec_ok(sin_table, ld_table, LEANFFN_F32)));
+  const int64_t total = rows * heads * (vec ? half / 8 : half);
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-#define ROTARY(TI, TO)                                                                                         \
-  attn::rotary_kernel<TI, TO><<<blocks, 256, 0, st>>>(static_cast<const TI*>(x), ld_x, cos_table, sin_table,   \
-                                                      ld_table, static_cast<TO*>(y), ld_y, rows, len, heads,   \
-                                                      head_dim, inverse)
-  if (x_dtype == LEANFFN_BF16 && y_dtype == LEANFFN_BF16) ROTARY(bf16, bf16);
-  else if (x_dtype == LEANFFN_BF16) ROTARY(bf16, float);
-  else if (y_dtype == LEANFFN_BF16) ROTARY(float, bf16);
-  else ROTARY(float, float);
+#define ROTARY(TI, TO)                                                                                              \
+  if (vec)                                                                                                          \
+    attn::rotary_vec_kernel<TI, TO><<<blocks, 256, 0, st>>>(static_cast<const TI*>(x), ld_x, cos_table, sin_table,  \
+                                                            ld_table, static_cast<TO*>(y), ld_y, rows, len, heads,  \
+                                                            head_dim, inverse);                                     \
+  else                                                                                                              \
+    attn::rotary_kernel<TI, TO><<<blocks, 256, 0, st>>>(static_cast<const TI*>(x), ld_x, cos_table, sin_table,      \
+                                                        ld_table, static_cast<TO*>(y), ld_y, rows, len, heads,      \
+                                                        head_dim, inverse)
+  if (x_dtype == LEANFFN_BF16 && y_dtype == LEANFFN_BF16) { ROTARY(bf16, bf16); }
+  else if (x_dtype == LEANFFN_BF16) { ROTARY(bf16, float); }
+  else if (y_dtype == LEANFFN_BF16) { ROTARY(float, bf16); }
+  else { ROTARY(float, float); }
 #undef ROTARY
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);

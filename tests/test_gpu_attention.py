@@ -155,6 +155,17 @@ def test_rotary_kernel_matches_oracle(cuda_device):
     torch.testing.assert_close(back.cpu().view_as(want_back).double(), want_back, rtol=1e-5, atol=1e-5)
     via_module = emb(x.to(cuda_device).view(batch, length, heads, d))
     torch.testing.assert_close(via_module.cpu().double(), want, rtol=1e-5, atol=1e-5)
+    # a head size whose halves are not a multiple of eight takes the one-pair-per-thread kernel
+    d2 = 20
+    x2 = torch.randn(batch, length, heads * d2)
+    cos2, sin2 = O.rotary_tables(length, d2, dtype=torch.float32)
+    want2 = O.rotary_apply(x2.view(batch, length, heads, d2).double(), cos2.double(), sin2.double())
+    got2 = L.ops.rotary(x2.to(cuda_device), cos2.to(cuda_device), sin2.to(cuda_device), heads, out_dtype=torch.float32)
+    torch.testing.assert_close(got2.cpu().view_as(want2).double(), want2, rtol=1e-5, atol=1e-5)
+    # bf16 in and out: one rounding of the fp32 result
+    got_bf16 = L.ops.rotary(x.to(cuda_device).bfloat16(), cos, sin, heads)
+    want_bf16 = O.rotary_apply(x.bfloat16().view(batch, length, heads, d).double(), ocos.double(), osin.double())
+    torch.testing.assert_close(got_bf16.cpu().view_as(want_bf16).double(), want_bf16, rtol=2 ** -8, atol=1e-3)
 
 
 def test_attention_rejections(cuda_device):
