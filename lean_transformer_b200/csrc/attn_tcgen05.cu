@@ -30,6 +30,7 @@ namespace leanffn {
 
 bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int64_t len, int64_t heads,
                           int64_t head_dim, int64_t ld);
+bool make_tmap_f32_heads(CUtensorMap* out, void* base, int64_t batch, int64_t len, int64_t heads, int64_t head_dim);
 
 namespace attn {
 
@@ -63,6 +64,19 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const CUtensorMap
       ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+
+// Adds a [128 x 32] fp32 box in shared memory (128-byte swizzle) to global memory through the TMA unit: one
+// instruction instead of a thousand vector reductions from the SM; the adds themselves happen in L2.
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tmap, uint32_t smem_src, int32_t x, int32_t y,
+                                                  int32_t z, int32_t w) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -466,9 +480,9 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 // The only hand-overs are mbarriers with bounded waits: no block-wide barrier inside the loop.  Order on the tensor cores:
 // A(i), dQ(i), dV/dK(i), A(i + 1), ...: the compute warps drain dQ_i while dV/dK(i) and A(i + 1) run.
 // head_dim <= 64 (PIPE): Q / dO double-buffered and fetched two tiles ahead, dQ has its own TMEM columns and is
-// transposed through shared memory so that a warp's vector reductions cover whole rows (full 32-byte sectors).
+// handed to the TMA unit through shared memory ([128 x 32] fp32 boxes, cp.reduce.async.bulk.tensor .add).
 // head_dim > 64: one Q / dO buffer; dQ_i reuses the S columns, so A(i + 1) waits for the read-out (bar_drain).
-// Shared memory: K, V, NBUF x (Q, dO) (DC boxes each), P, dS (2 boxes each), PIPE: dQ staging [128][DPAD + 4] fp32.
+// Shared memory: K, V, NBUF x (Q, dO) (DC boxes each), P, dS (2 boxes each), PIPE: dQ staging (DPAD / 32 boxes).
 // TMEM (512 columns): [0, 128) S; [128, 256) dP; PIPE: [256, 320) dV, [320, 384) dK, [384, 448) dQ;
 //                     otherwise [256, 384) dV, [384, 512) dK, dQ in [0, 128).
 constexpr int BWD_COMPUTE_WARPS = 16;
@@ -477,11 +491,11 @@ constexpr int BWD_THREADS = 32 * (BWD_COMPUTE_WARPS + 1);
 template <int DPAD>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const Params p) {
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                     const __grid_constant__ CUtensorMap tmdQ, const Params p) {
   constexpr bool PIPE = DPAD <= 64;
   constexpr int NBUF = PIPE ? 2 : 1;
   constexpr uint32_t COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
-  constexpr int STAGE_PITCH = DPAD + 4;  // floats per staged dQ row
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
@@ -494,7 +508,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* gP = sm.gen + (2 + 2 * NBUF) * tile_bytes;
   uint8_t* gdS = gP + PS_BYTES;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 72);
-  float* stage = reinterpret_cast<float*>(gdS + PS_BYTES + 128);  // PIPE only
+  uint8_t* g_stage = gdS + PS_BYTES + 1024;  // PIPE only: DPAD / 32 boxes [128 x 32] fp32, 1024-byte aligned
+  const uint32_t s_stage = sdS + PS_BYTES + 1024;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk = warp >> 2, row = tid & 127;
@@ -524,6 +539,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmdO);
+    if (PIPE) prefetch_tmap(&tmdQ);
   }
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
@@ -686,6 +702,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       fence_proxy_async_smem();
       tc_fence_before();
+      // the staging area of the tile before must have been read by the TMA unit before this arrival lets the next dQ
+      // products (and with them the next staging writes) start
+      if (PIPE && tid == 0) bulk_wait_group_read0();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pds);
 
@@ -693,34 +712,31 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (!ok) break;
       tc_fence_after();
       if (PIPE) {
-        // transpose dQ_i through shared memory: lane = row on the way in, consecutive lanes = consecutive 16-byte
-        // pieces of a row on the way out
+        // dQ_i * scale goes to shared memory as [128 x 32] fp32 boxes (swizzled like every other tile) and from there
+        // to the fp32 gradient in global memory by TMA reductions: rows beyond q_len and columns beyond head_dim are
+        // clipped by the tensor map
         if (chunk < DPAD / 32) {  // uniform per warp
           uint32_t acc[32];
           tmem_ld_32x32(t_row + COL_DQ + chunk * 32, acc);
           tmem_ld_wait();
-          float4* dst4 = reinterpret_cast<float4*>(stage + row * STAGE_PITCH + chunk * 32);
 #pragma unroll
           for (int x = 0; x < 8; ++x)
-            dst4[x] = make_float4(__uint_as_float(acc[4 * x]) * p.scale, __uint_as_float(acc[4 * x + 1]) * p.scale,
-                                  __uint_as_float(acc[4 * x + 2]) * p.scale, __uint_as_float(acc[4 * x + 3]) * p.scale);
+            *reinterpret_cast<float4*>(g_stage + ps_offset(row, chunk * 8 + x)) =
+                make_float4(__uint_as_float(acc[4 * x]) * p.scale, __uint_as_float(acc[4 * x + 1]) * p.scale,
+                            __uint_as_float(acc[4 * x + 2]) * p.scale, __uint_as_float(acc[4 * x + 3]) * p.scale);
+          fence_proxy_async_smem();
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_stage);  // staged rows of all 16 warps: a bounded wait, like every other hand-over
-        ok = wait_warp(bar_stage, n & 1);
-        if (!ok) break;
-        const int pieces = p.d >> 2;                    // 16-byte pieces per row
-        const int total = 8 * pieces;                   // this warp's 8 rows
-        const int64_t width = static_cast<int64_t>(p.H) * p.d;
-        for (int idx = lane; idx < total; idx += 32) {
-          const int r = warp * 8 + idx / pieces, c4 = idx % pieces;
-          const int q = i * TILE + r;
-          if (q < p.Sq) {
-            const float4 val = *reinterpret_cast<const float4*>(stage + r * STAGE_PITCH + c4 * 4);
-            red_add_v4(p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q) * width + static_cast<int64_t>(h) * p.d + c4 * 4,
-                       val.x, val.y, val.z, val.w);
+        if (lane == 0) mbar_arrive(bar_stage);
+        if (warp == 0) {  // one thread hands the staged tile to the TMA unit once all 16 warps have written their rows
+          ok = wait_warp(bar_stage, n & 1);
+          if (!ok) break;
+          if (lane == 0) {
+            for (int c = 0; c * 32 < p.d; ++c) tma_reduce_add_4d(&tmdQ, s_stage + c * BOX_BYTES, c * 32, h, i * TILE, b);
+            bulk_commit_group();
           }
+          __syncwarp();
         }
       } else {
         float* dst = p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q_clamped) * (static_cast<int64_t>(p.H) * p.d) +
@@ -786,6 +802,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
     }
   }
+  if (PIPE && tid == 0) bulk_wait_group0();  // the reductions of this block have been performed
   // teardown: after a timeout give copies and products still in flight time to land before the memory is released
   if (!__syncthreads_and(ok)) {
     const long long t0 = clock64();
@@ -1004,17 +1021,19 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
   e = cudaGetLastError();
   if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
   const int dc = (d->head_dim + 63) / 64;
-  // head_dim <= 64: double-buffered Q / dO and the dQ staging rows [128][round32(head_dim) + 4] fp32
+  // head_dim <= 64: double-buffered Q / dO and the dQ staging boxes ([128 x 32] fp32 each)
   const int dpad = (d->head_dim + 31) / 32 * 32;
-  const size_t smem = (dc == 1 ? 6 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 128 + 1024 +
-                      (dc == 1 ? 128 * (dpad + 4) * sizeof(float) : 0);
+  const size_t smem = (dc == 1 ? 6 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 1024 + 1024 +
+                      (dc == 1 ? (dpad / 32) * attn::BOX_BYTES : 0);
+  CUtensorMap tdq;
+  if (!make_tmap_f32_heads(&tdq, d->dq_accum, d->batch, d->q_len, d->heads, d->head_dim)) return LEANFFN_ERR_DRIVER;
   const dim3 grid((d->kv_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
 #define ATTN_BWD(DPAD)                                                             \
   {                                                                                \
     auto kern = attn::attention_bwd_kernel<DPAD>;                                  \
     e = attn::set_smem(kern, smem);                                                \
     if (e == cudaSuccess) {                                                        \
-      kern<<<grid, attn::BWD_THREADS, smem, st>>>(tq, tk, tv, tdo, p);                 \
+      kern<<<grid, attn::BWD_THREADS, smem, st>>>(tq, tk, tv, tdo, tdq, p);                 \
       e = cudaGetLastError();                                                      \
     }                                                                              \
   }

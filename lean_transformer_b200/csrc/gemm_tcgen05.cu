@@ -469,6 +469,23 @@ bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int
   return r == CUDA_SUCCESS;
 }
 
+// 4D fp32 tensor map over a contiguous [batch, len, heads, head_dim] tensor for TMA reductions of [128 rows x 32
+// columns] boxes (128 bytes per row, 128-byte swizzle in shared memory); rows beyond len and columns beyond head_dim
+// are clipped.
+bool make_tmap_f32_heads(CUtensorMap* out, void* base, int64_t batch, int64_t len, int64_t heads, int64_t head_dim) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(heads),
+                              static_cast<cuuint64_t>(len), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_dim) * 4, static_cast<cuuint64_t>(heads * head_dim) * 4,
+                                 static_cast<cuuint64_t>(len) * static_cast<cuuint64_t>(heads * head_dim) * 4};
+  const cuuint32_t box[4] = {32, 1, 128, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <bool A_MN, bool B_MN, int BLOCK_N, int MT, bool TF32 = false>
 static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2,
                                const CUtensorMap& b2, const TcParams& p, cudaStream_t st) {
