@@ -477,8 +477,10 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 //                    elementwise(i): P = exp2(S - lse), dS = P * (dP - delta) -> shared memory, 16 arrivals on bar_pds
 //                    group B(i) = {dQ_i = dS . K -> bar_dq;  dV += P^T . dO_i, dK += dS^T . Q_i -> bar_b}
 //                    read-out(i): dQ_i * scale added to the fp32 gradient in global memory -> 16 arrivals on bar_drain
-// The only hand-overs are mbarriers with bounded waits: no block-wide barrier inside the loop.  Order on the tensor cores:
-// A(i), dQ(i), dV/dK(i), A(i + 1), ...: the compute warps drain dQ_i while dV/dK(i) and A(i + 1) run.
+// The only hand-overs are mbarriers with bounded waits: no block-wide barrier inside the loop.  Order on the tensor cores
+// for head_dim <= 64: A(i), dQ(i), A(i + 1), dV/dK(i), dQ(i + 1), ...: while dV/dK(i) run, the compute warps hand dQ_i
+// to the TMA unit and take the exponentials of tile i + 1; they hold the new P / dS in registers until bar_b says the
+// old ones are no longer operands.
 // head_dim <= 64 (PIPE): Q / dO double-buffered and fetched two tiles ahead, dQ has its own TMEM columns and is
 // handed to the TMA unit through shared memory ([128 x 32] fp32 boxes, cp.reduce.async.bulk.tensor .add).
 // head_dim > 64: one Q / dO buffer; dQ_i reuses the S columns, so A(i + 1) waits for the read-out (bar_drain).
@@ -579,15 +581,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(bar_a);
       };
-      auto issue_b = [&](int buf, uint32_t accumulate) {
-        const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
+      auto issue_dq = [&]() {  // dQ[q, x] = sum_key dS[q, key] * K[key, x]: first, the compute warps wait for it
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // dQ[q, x] = sum_key dS[q, key] * K[key, x]: first, the compute warps wait for it
+        for (int ks = 0; ks < 8; ++ks) {
           const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
           umma_bf16(tmem + COL_DQ, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi),
                     idesc_q, ks > 0 ? 1u : 0u);
         }
         umma_commit(bar_dq);
+      };
+      auto issue_dv_dk = [&](int buf, uint32_t accumulate) {
+        const uint32_t sQ = sQ0 + 2 * buf * tile_bytes, sdO = sQ + tile_bytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           // dV[key, x] += sum_q P[q, key] * dO[q, x]
@@ -616,17 +620,24 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         go = mbar_wait_bounded(bar_pds, n & 1, limit);  // P, dS written; S, dP read; dQ of the tile before drained
         if (!go) break;
         tc_fence_after();
-        issue_b(buf, n == 0 ? 0u : 1u);
+        issue_dq();
         if (PIPE) {
+          // the next tile's scores go in front of this tile's dV / dK products: S and dP have been read, and the
+          // compute warps can take the exponentials of tile i + 1 while dV / dK of tile i run (they keep the new P
+          // and dS in registers until bar_b says the old ones are no longer operands)
           if (n + 1 < n_iter) {
             go = mbar_wait_bounded(bar_q0 + 8 * (buf ^ 1), ((n + 1) >> 1) & 1, limit);
             if (!go) break;
             issue_a(buf ^ 1);
           }
+          issue_dv_dk(buf, n == 0 ? 0u : 1u);
           go = mbar_wait_bounded(bar_b, n & 1, limit);  // Q_i, dO_i consumed: their buffer takes tile i + 2
           if (!go) break;
           if (n + 2 < n_iter) load_q_do(i + 2, buf);
-        } else if (n + 1 < n_iter) {
+        } else {
+          issue_dv_dk(buf, n == 0 ? 0u : 1u);
+        }
+        if (!PIPE && n + 1 < n_iter) {
           go = mbar_wait_bounded(bar_b, n & 1, limit);
           if (!go) break;
           load_q_do(i + 1, 0);
@@ -679,27 +690,35 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - lse);
         }
+        uint4 wp[4], wd[4];  // this thread's 32 probabilities and 32 score gradients, packed bf16
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-          w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-          w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-          w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-          *reinterpret_cast<uint4*>(gP + ps_offset(row, c * 4 + q4)) = w;
+          wp[q4].x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+          wp[q4].y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+          wp[q4].z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+          wp[q4].w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
         }
 #pragma unroll
         for (int x = 0; x < 32; ++x) v[x] *= __uint_as_float(dp[x]) - dlt;  // dS; the score scale is applied to dQ / dK
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-          w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-          w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-          w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-          *reinterpret_cast<uint4*>(gdS + ps_offset(row, c * 4 + q4)) = w;
+          wd[q4].x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+          wd[q4].y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+          wd[q4].z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+          wd[q4].w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+        }
+        // P and dS of the tile before are operands of its dV / dK products until bar_b completes
+        if (n > 0) ok = wait_warp(bar_b, (n - 1) & 1);
+        if (ok) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t o = ps_offset(row, c * 4 + q4);
+            *reinterpret_cast<uint4*>(gP + o) = wp[q4];
+            *reinterpret_cast<uint4*>(gdS + o) = wd[q4];
+          }
         }
       }
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before();
       // the staging area of the tile before must have been read by the TMA unit before this arrival lets the next dQ
