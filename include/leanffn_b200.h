@@ -457,7 +457,10 @@ int32_t leanffn_copy_2d(void* dst, uint64_t dst_pitch_bytes, const void* src, ui
  * causal != 0 additionally forbids k > q + (kv_len - q_len) and skips the tiles that rule empties.
  * lse: fp32 [batch, heads, q_len], log2 of the softmax denominator with the row maximum folded in, written by the
  * forward call and read by the backward call.
- * Attention-probability dropout (attn.py:141-144) is not implemented: the host rejects p > 0.
+ * dropout_p > 0: dropout on the attention probabilities (attn.py:141-144): probability (b, h, q, k) is kept iff the
+ * Philox word of element index elem_offset + ((b * heads + h) * q_len + q) * kv_len + k passes the threshold (the
+ * mask function of leanffn_dropout), kept ones are scaled by 1 / (1 - p); forward and backward must be given the same
+ * (dropout_p, seed, elem_offset).
  *
  * Backward needs, besides the forward's q, k, v, out and lse: delta (fp32 [batch, heads, q_len], scratch),
  * dq_accum (fp32 [batch, q_len, heads * head_dim] contiguous, zeroed by the call, receives dQ; convert / un-rotate it
@@ -467,7 +470,7 @@ typedef struct leanffn_attention_desc {
   int32_t batch, heads, q_len, kv_len, head_dim;
   int32_t causal;
   float scale;
-  int32_t reserved0;
+  float dropout_p;
   const void* q;
   const void* k;
   const void* v;
@@ -487,6 +490,8 @@ typedef struct leanffn_attention_desc {
   int64_t ld_dk, ld_dv;
   int32_t* status_word;
   int64_t wait_limit_cycles;
+  uint64_t seed;
+  uint64_t elem_offset;
 } leanffn_attention_desc;
 
 int32_t leanffn_attention_forward(const leanffn_attention_desc* desc, void* stream);

@@ -87,13 +87,13 @@ class AttentionDesc(ctypes.Structure):
 
     _fields_ = [
         ("batch", c_int32), ("heads", c_int32), ("q_len", c_int32), ("kv_len", c_int32), ("head_dim", c_int32),
-        ("causal", c_int32), ("scale", c_float), ("reserved0", c_int32),
+        ("causal", c_int32), ("scale", c_float), ("dropout_p", c_float),
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("ld_q", c_int64), ("ld_k", c_int64), ("ld_v", c_int64),
         ("mask", c_void_p), ("mask_stride_b", c_int64), ("mask_stride_h", c_int64), ("mask_stride_q", c_int64),
         ("out", c_void_p), ("ld_out", c_int64), ("lse", c_void_p),
         ("d_out", c_void_p), ("ld_dout", c_int64), ("delta", c_void_p), ("dq_accum", c_void_p),
         ("dk", c_void_p), ("dv", c_void_p), ("ld_dk", c_int64), ("ld_dv", c_int64),
-        ("status_word", c_void_p), ("wait_limit_cycles", c_int64),
+        ("status_word", c_void_p), ("wait_limit_cycles", c_int64), ("seed", c_uint64), ("elem_offset", c_uint64),
     ]
 
 

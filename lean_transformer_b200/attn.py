@@ -12,7 +12,9 @@
 
 ``SimpleAttentionCore`` and ``RotaryAttentionCore`` mirror the reference's cores (same constructors, same
 ``forward(query, key, value, attention_mask) -> (outputs, probs)``).  They never build the [query_len, kv_len]
-matrices, so ``probs`` is ``None`` and asking the block for ``output_attentions=True`` raises.  The three slices of
+matrices, so ``probs`` is ``None`` and asking the block for ``output_attentions=True`` raises; dropout on the
+probabilities (``attention_probs_dropout``) is a Philox mask over the [batch, heads, query_len, kv_len] index space,
+regenerated in the backward pass.  The three slices of
 the fused qkv output are read in place.  Any other ``attention_core`` module given to the block is called as is.
 """
 import math
@@ -25,7 +27,7 @@ from torch.utils.checkpoint import checkpoint
 
 from . import ops
 from .blocksparse.linear import GeneralizedLinear, _GeneralizedLinear
-from .ffn import _LayerNormFunction
+from .ffn import _LayerNormFunction, next_dropout_stream
 from .fused_linear import linear_dropout_residual
 
 _CAUSAL_CACHE = {}  # id(mask) -> (weak reference to the mask, its version counter, answer)
@@ -59,7 +61,7 @@ class _AttentionCoreFunction(torch.autograd.Function):
     pass recomputes the probabilities tile by tile."""
 
     @staticmethod
-    def forward(ctx, query, key, value, attention_mask, heads: int, cos, sin, scale: float):
+    def forward(ctx, query, key, value, attention_mask, heads: int, cos, sin, scale: float, dropout_p: float = 0.0):
         for t in (query, key, value):
             if t.dtype != torch.bfloat16 and not torch.is_autocast_enabled():
                 raise NotImplementedError(
@@ -75,9 +77,12 @@ class _AttentionCoreFunction(torch.autograd.Function):
             q = query if query.dtype == torch.bfloat16 else ops.rotary(query, None, None, heads)
             k = key if key.dtype == torch.bfloat16 else ops.rotary(key, None, None, heads)
         v = value if value.dtype == torch.bfloat16 else ops.rotary(value, None, None, heads)
-        out, lse = ops.attention_forward(q, k, v, heads, scale, mask, causal)
+        seed = offset = 0
+        if dropout_p > 0:  # position in the device's Philox stream: the backward pass regenerates the same mask
+            seed, offset = next_dropout_stream(query.device, query.shape[0] * heads * q_len * kv_len)
+        out, lse = ops.attention_forward(q, k, v, heads, scale, mask, causal, dropout_p, seed, offset)
         ctx.save_for_backward(q, k, v, out, lse, mask, cos, sin)
-        ctx.heads, ctx.scale, ctx.causal = heads, scale, causal
+        ctx.heads, ctx.scale, ctx.causal, ctx.dropout = heads, scale, causal, (dropout_p, seed, offset)
         ctx.in_dtypes = (query.dtype, key.dtype, value.dtype)
         return out
 
@@ -85,14 +90,14 @@ class _AttentionCoreFunction(torch.autograd.Function):
     def backward(ctx, grad_out):
         q, k, v, out, lse, mask, cos, sin = ctx.saved_tensors
         heads = ctx.heads
-        dq, dk, dv = ops.attention_backward(grad_out, q, k, v, out, lse, heads, ctx.scale, mask, ctx.causal)
+        dq, dk, dv = ops.attention_backward(grad_out, q, k, v, out, lse, heads, ctx.scale, mask, ctx.causal, *ctx.dropout)
         q_dtype, k_dtype, v_dtype = ctx.in_dtypes
         grad_q = ops.rotary(dq, cos, sin, heads, inverse=True, out_dtype=q_dtype)  # fp32 accumulator -> input dtype
         if cos is not None or k_dtype != torch.bfloat16:
             dk = ops.rotary(dk, cos, sin, heads, inverse=True, out_dtype=k_dtype)
         if v_dtype != torch.bfloat16:
             dv = dv.to(v_dtype)
-        return grad_q, dk, dv, None, None, None, None, None
+        return grad_q, dk, dv, None, None, None, None, None, None
 
 
 class SimpleAttentionCore(nn.Module):
@@ -125,12 +130,11 @@ class SimpleAttentionCore(nn.Module):
         if not query.is_cuda:
             raise RuntimeError("the attention core (lean_transformer_b200) needs CUDA tensors: it exists only as "
                                "sm_100a kernels")
-        if self.training and self.attention_dropout.p != 0:
-            raise NotImplementedError("dropout on the attention probabilities is not implemented in the attention "
-                                      "kernels (attention_probs_dropout must be 0)")
+        dropout_p = float(self.attention_dropout.p) if self.training else 0.0
         cos, sin = self._tables(max(query.shape[1], key.shape[1]), query.device)
         scale = 1.0 / math.sqrt(self.attention_head_size)
-        out = _AttentionCoreFunction.apply(query, key, value, attention_mask, self.num_attention_heads, cos, sin, scale)
+        out = _AttentionCoreFunction.apply(query, key, value, attention_mask, self.num_attention_heads, cos, sin, scale,
+                                           dropout_p)
         return out, None
 
 

@@ -43,6 +43,9 @@ struct Params {
   int32_t B, H, Sq, Skv, d;
   int32_t causal;
   float scale;
+  uint32_t drop_threshold;  // 0: no dropout on the probabilities
+  float inv_keep;           // 1 / (1 - p)
+  uint64_t seed, elem_offset;
   const float* mask;
   int64_t mask_sb, mask_sh, mask_sq;
   bf16* out;
@@ -149,6 +152,27 @@ __device__ long long g_attn_prof[16];
 #define ATTN_PROF(slot)
 #endif
 
+// Dropout factors of 32 consecutive probabilities starting at element index e0: f[x] = 1 / (1 - p) if kept, else 0.
+// Not inlined: the counter-based generator needs many registers; f lives in local memory.  `aligned` must be uniform
+// over the warp (it is a property of kv_len and the stream offset, not of the row): the callers execute warp-collective
+// tensor-memory loads right after, so no lane may take a different path here.
+__device__ __noinline__ void dropout_factors(float* f, uint64_t e0, bool aligned, uint64_t seed, uint32_t threshold,
+                                             float inv_keep) {
+  if (aligned) {  // e0 is a multiple of 4: eight whole Philox groups
+#pragma unroll 1
+    for (int g = 0; g < 8; ++g) {
+      bool keep[4];
+      dropout_keep4((e0 >> 2) + g, seed, threshold, keep);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) f[4 * g + i] = keep[i] ? inv_keep : 0.f;
+    }
+  } else {  // kv_len or the offset not a multiple of 4: the groups of four straddle the chunks
+#pragma unroll 1
+    for (int x = 0; x < 32; ++x) f[x] = dropout_keep1(e0 + x, seed, threshold) ? inv_keep : 0.f;
+  }
+  __syncwarp();
+}
+
 struct Smem {
   uint32_t base;     // 1024-aligned shared address of the tile area
   uint8_t* gen;      // the same address as a generic pointer
@@ -172,8 +196,8 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 // TMEM: columns [0, 128) S; then one block of OCOLS columns per group for O_g.
 constexpr int FWD_THREADS = 256;
 
-template <int DPAD>
-__global__ void __launch_bounds__(FWD_THREADS)
+template <int DPAD, bool DROP>
+__global__ void __launch_bounds__(FWD_THREADS, DPAD <= 64 ? 2 : 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const Params p) {
   constexpr int OCOLS = DPAD <= 64 ? 64 : 128;
@@ -248,6 +272,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                                             : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
   const float scale_log2 = p.scale * LOG2E;
   const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
+  const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
+  const bool drop_aligned = ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0;  // uniform: every chunk starts a Philox group
 
   float o_acc[DPAD];
 #pragma unroll
@@ -335,6 +361,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
 #pragma unroll
       for (int x = 0; x < 32; ++x) row_sum += v[x];
+      if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
+        float f[32];
+        dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) v[x] *= f[x];
+      }
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         uint4 w;
@@ -490,7 +522,7 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 constexpr int BWD_COMPUTE_WARPS = 16;
 constexpr int BWD_THREADS = 32 * (BWD_COMPUTE_WARPS + 1);
 
-template <int DPAD>
+template <int DPAD, bool DROP>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -691,12 +723,29 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - lse);
         }
         uint4 wp[4], wd[4];  // this thread's 32 probabilities and 32 score gradients, packed bf16
+        if constexpr (DROP) {
+          // dV takes the kept probabilities scaled by 1 / (1 - p); the gradient of a dropped probability is zero
+          float f[32];
+          const uint64_t e0 = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv +
+                              static_cast<uint64_t>(k0 + c * 32);
+          dropout_factors(f, e0, ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0, p.seed, p.drop_threshold, p.inv_keep);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          wp[q4].x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-          wp[q4].y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-          wp[q4].z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-          wp[q4].w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+          for (int q4 = 0; q4 < 4; ++q4) {
+            wp[q4].x = pack_bf16x2(v[8 * q4 + 0] * f[8 * q4 + 0], v[8 * q4 + 1] * f[8 * q4 + 1]);
+            wp[q4].y = pack_bf16x2(v[8 * q4 + 2] * f[8 * q4 + 2], v[8 * q4 + 3] * f[8 * q4 + 3]);
+            wp[q4].z = pack_bf16x2(v[8 * q4 + 4] * f[8 * q4 + 4], v[8 * q4 + 5] * f[8 * q4 + 5]);
+            wp[q4].w = pack_bf16x2(v[8 * q4 + 6] * f[8 * q4 + 6], v[8 * q4 + 7] * f[8 * q4 + 7]);
+          }
+#pragma unroll
+          for (int x = 0; x < 32; ++x) dp[x] = __float_as_uint(__uint_as_float(dp[x]) * f[x]);
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            wp[q4].x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+            wp[q4].y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+            wp[q4].z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+            wp[q4].w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+          }
         }
 #pragma unroll
         for (int x = 0; x < 32; ++x) v[x] *= __uint_as_float(dp[x]) - dlt;  // dS; the score scale is applied to dQ / dK
@@ -949,6 +998,7 @@ static int32_t validate(const leanffn_attention_desc* d, bool backward) {
   if (d->ld_q % 8 || d->ld_k % 8 || d->ld_v % 8 || d->ld_out % 8) return LEANFFN_ERR_ALIGN;
   if (!aligned16(d->q) || !aligned16(d->k) || !aligned16(d->v) || !aligned16(d->out)) return LEANFFN_ERR_ALIGN;
   if (d->batch > 65535 || d->heads > 65535) return LEANFFN_ERR_TOO_LARGE;
+  if (!(d->dropout_p >= 0.f) || d->dropout_p >= 1.f) return LEANFFN_ERR_SHAPE;
   if (backward) {
     if (d->d_out == nullptr || d->delta == nullptr || d->dq_accum == nullptr || d->dk == nullptr || d->dv == nullptr)
       return LEANFFN_ERR_NULL;
@@ -964,6 +1014,9 @@ static Params make_params(const leanffn_attention_desc* d) {
   p.B = d->batch, p.H = d->heads, p.Sq = d->q_len, p.Skv = d->kv_len, p.d = d->head_dim;
   p.causal = d->causal;
   p.scale = d->scale;
+  p.drop_threshold = d->dropout_p > 0.f ? dropout_threshold(d->dropout_p) : 0u;
+  p.inv_keep = d->dropout_p > 0.f ? 1.f / (1.f - d->dropout_p) : 1.f;
+  p.seed = d->seed, p.elem_offset = d->elem_offset;
   p.mask = d->mask;
   p.mask_sb = d->mask_stride_b, p.mask_sh = d->mask_stride_h, p.mask_sq = d->mask_stride_q;
   p.out = static_cast<bf16*>(d->out);
@@ -1005,7 +1058,8 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
   cudaError_t e;
 #define ATTN_FWD(DPAD)                                                             \
   {                                                                                \
-    auto kern = attn::attention_fwd_kernel<DPAD>;                                  \
+    auto kern = p.drop_threshold != 0u ? attn::attention_fwd_kernel<DPAD, true>    \
+                                       : attn::attention_fwd_kernel<DPAD, false>;  \
     e = attn::set_smem(kern, smem);                                                \
     if (e == cudaSuccess) {                                                        \
       kern<<<grid, attn::FWD_THREADS, smem, st>>>(tq, tk, tv, p);                      \
@@ -1049,7 +1103,8 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
   const dim3 grid((d->kv_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
 #define ATTN_BWD(DPAD)                                                             \
   {                                                                                \
-    auto kern = attn::attention_bwd_kernel<DPAD>;                                  \
+    auto kern = p.drop_threshold != 0u ? attn::attention_bwd_kernel<DPAD, true>    \
+                                       : attn::attention_bwd_kernel<DPAD, false>;  \
     e = attn::set_smem(kern, smem);                                                \
     if (e == cudaSuccess) {                                                        \
       kern<<<grid, attn::BWD_THREADS, smem, st>>>(tq, tk, tv, tdo, tdq, p);                 \

@@ -533,7 +533,7 @@ def _mask_strides(mask: Optional[torch.Tensor], batch: int, heads: int, q_len: i
     return mask, strides
 
 
-def _attention_desc(q, k, v, heads, scale, mask, causal):
+def _attention_desc(q, k, v, heads, scale, mask, causal, dropout_p=0.0, seed=0, elem_offset=0):
     batch, q_len, width = q.shape
     kv_len = k.shape[1]
     if width % heads != 0:
@@ -550,6 +550,7 @@ def _attention_desc(q, k, v, heads, scale, mask, causal):
     d = N.AttentionDesc()
     d.batch, d.heads, d.q_len, d.kv_len, d.head_dim = batch, heads, q_len, kv_len, head_dim
     d.causal, d.scale = int(causal), float(scale)
+    d.dropout_p, d.seed, d.elem_offset = float(dropout_p), int(seed), int(elem_offset)
     d.q, d.k, d.v = _ptr(q), _ptr(k), _ptr(v)
     d.ld_q, d.ld_k, d.ld_v = q.stride(1), k.stride(1), v.stride(1)
     d.mask, d.mask_stride_b, d.mask_stride_h, d.mask_stride_q = _ptr(mask), sb, sh, sq
@@ -557,13 +558,15 @@ def _attention_desc(q, k, v, heads, scale, mask, causal):
     return d, mask
 
 
-def attention_forward(q, k, v, heads: int, scale: float, mask=None, causal: bool = False):
+def attention_forward(q, k, v, heads: int, scale: float, mask=None, causal: bool = False, dropout_p: float = 0.0,
+                      seed: int = 0, elem_offset: int = 0):
     """softmax(scale * q.k^T + mask).v per head (``leanffn_attention_forward``).  q [batch, q_len, hidden], k / v
-    [batch, kv_len, hidden] bfloat16 (slices of one qkv tensor are taken in place).  Returns (out bfloat16
-    [batch, q_len, hidden], lse float32 [batch, heads, q_len] for the backward pass)."""
+    [batch, kv_len, hidden] bfloat16 (slices of one qkv tensor are taken in place).  ``dropout_p`` > 0 drops attention
+    probabilities with the Philox mask of (seed, elem_offset) over the [batch, heads, q_len, kv_len] index space.
+    Returns (out bfloat16 [batch, q_len, hidden], lse float32 [batch, heads, q_len] for the backward pass)."""
     _require_cuda(q, k, v, mask)
     q, k, v = _rows_view(q), _rows_view(k), _rows_view(v)
-    d, mask = _attention_desc(q, k, v, heads, scale, mask, causal)
+    d, mask = _attention_desc(q, k, v, heads, scale, mask, causal, dropout_p, seed, elem_offset)
     out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
     lse = torch.empty(q.shape[0], heads, q.shape[1], dtype=torch.float32, device=q.device)
     d.out, d.ld_out, d.lse = _ptr(out), out.stride(1), _ptr(lse)
@@ -572,14 +575,15 @@ def attention_forward(q, k, v, heads: int, scale: float, mask=None, causal: bool
     return out, lse
 
 
-def attention_backward(d_out, q, k, v, out, lse, heads: int, scale: float, mask=None, causal: bool = False):
-    """Gradients of ``attention_forward`` (``leanffn_attention_backward``): (dq float32 [batch, q_len, hidden], dk, dv
-    bfloat16 [batch, kv_len, hidden])."""
+def attention_backward(d_out, q, k, v, out, lse, heads: int, scale: float, mask=None, causal: bool = False,
+                       dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0):
+    """Gradients of ``attention_forward`` (``leanffn_attention_backward``) for the same (mask, causal, dropout_p, seed,
+    elem_offset): (dq float32 [batch, q_len, hidden], dk, dv bfloat16 [batch, kv_len, hidden])."""
     _require_cuda(d_out, q, k, v, out, lse, mask)
     q, k, v, d_out = _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(d_out)
     if d_out.dtype != torch.bfloat16:
         d_out = d_out.to(torch.bfloat16)
-    d, mask = _attention_desc(q, k, v, heads, scale, mask, causal)
+    d, mask = _attention_desc(q, k, v, heads, scale, mask, causal, dropout_p, seed, elem_offset)
     dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
     dk = torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
     dv = torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)

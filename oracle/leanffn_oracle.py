@@ -335,12 +335,14 @@ def rotary_apply_transposed(g: torch.Tensor, cos: torch.Tensor, sin: torch.Tenso
     return g * cos[None, : g.shape[1], None, :] + torch.cat([gs[..., half:], -gs[..., :half]], dim=-1)
 
 
-def attention_core_step(query, key, value, mask, heads: int, grad_out=None, rotary: bool = False, base: int = 10_000):
+def attention_core_step(query, key, value, mask, heads: int, grad_out=None, rotary: bool = False, base: int = 10_000,
+                        dropout_p: float = 0.0, keep_mask: Optional[torch.Tensor] = None):
     """Forward of the attention core and, given grad_out, the gradients for query / key / value, without autograd.
     query [batch, q_len, hidden], key / value [batch, kv_len, hidden], mask additive, broadcastable to
     [batch, heads, q_len, kv_len].  Follows attn.py:117-147: head split, keys divided by sqrt(head size), scores + mask,
     softmax over keys, probabilities times values, heads merged; with rotary=True queries and keys are rotated first
-    (attn.py:163-171).  Returns (out, dict(query=, key=, value=) or None)."""
+    (attn.py:163-171); with dropout_p > 0 the probabilities are multiplied by keep_mask / (1 - dropout_p) (attn.py:141-144,
+    keep_mask [batch, heads, q_len, kv_len]).  Returns (out, dict(query=, key=, value=) or None)."""
     batch, q_len, hidden = query.shape
     kv_len, d = key.shape[1], hidden // heads
     q4, k4, v4 = (t.reshape(batch, -1, heads, d) for t in (query, key, value))
@@ -353,12 +355,18 @@ def attention_core_step(query, key, value, mask, heads: int, grad_out=None, rota
     if mask is not None:
         scores = scores + mask
     probs = torch.softmax(scores, dim=-1)
-    out = (probs @ vh).transpose(1, 2).reshape(batch, q_len, hidden)
+    drop = None
+    if dropout_p and keep_mask is not None:
+        drop = keep_mask.reshape(probs.shape).to(probs.dtype) / (1.0 - dropout_p)
+    kept = probs if drop is None else probs * drop
+    out = (kept @ vh).transpose(1, 2).reshape(batch, q_len, hidden)
     if grad_out is None:
         return out, None
     go = grad_out.reshape(batch, q_len, heads, d).permute(0, 2, 1, 3)
-    d_v = probs.transpose(-1, -2) @ go
+    d_v = kept.transpose(-1, -2) @ go
     d_probs = go @ vh.transpose(-1, -2)
+    if drop is not None:
+        d_probs = d_probs * drop
     d_scores = probs * (d_probs - (d_probs * probs).sum(-1, keepdim=True))
     d_q = (d_scores @ kh) * inv
     d_k = (d_scores.transpose(-1, -2) @ qh) * inv

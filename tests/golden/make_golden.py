@@ -232,6 +232,27 @@ def main(ref_root: str):
                             heads=np.array(HEADS))
         print(f"wrote attention_core_{kind}.npz")
 
+    # attention core with dropout on the probabilities: the oracle's Philox mask injected into the reference
+    torch.manual_seed(12)
+    p_attn, seed_attn, offset_attn = 0.25, 77, 4096
+    keep_attn = torch.from_numpy(dropout_keep_mask(B * HEADS * S * S, p_attn, seed_attn, offset_attn)).view(B, HEADS, S, S)
+    core = ref_attn.SimpleAttentionCore(HID, HEADS, attention_probs_dropout=p_attn).double().train()
+    q, k, v = (torch.randn(B, S, HID, dtype=torch.float64, requires_grad=True) for _ in range(3))
+    g = torch.randn(B, S, HID, dtype=torch.float64)
+    orig_inplace = torch.dropout_
+    # out of place: softmax's backward needs its own output unchanged (same values and gradients as the in-place form)
+    torch.dropout_ = lambda t, prob, train: t * (keep_attn.to(t.dtype) / (1 - prob))
+    try:
+        out, probs = core(q, k, v, causal)
+        out.backward(g)
+    finally:
+        torch.dropout_ = orig_inplace
+    np.savez_compressed(HERE / "attention_core_dropout.npz", query=to_np(q), key=to_np(k), value=to_np(v),
+                        mask=to_np(causal), grad_out=to_np(g), out=to_np(out), grad_query=to_np(q.grad),
+                        grad_key=to_np(k.grad), grad_value=to_np(v.grad), heads=np.array(HEADS),
+                        dropout=np.array(p_attn), seed=np.array(seed_attn), offset=np.array(offset_attn))
+    print("wrote attention_core_dropout.npz")
+
     # state-dict key names the drop-in modules must reproduce
     ffn = LeanFFN(H, I, gated=True, post_layer_norm=True,
                   i2h_proj=GL(GM(H, 2 * I, layout, 6), 2), h2o_proj=GL(GM(I, H, layout, 0, ), 0))

@@ -20,9 +20,10 @@ def _bf16(t):
     return t.to(torch.bfloat16)
 
 
-def _check(got, want, what):
-    # the literal rule |got - ref| <= atol + rtol * |ref| for every element, no outlier budget
-    assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=False)
+def _check(got, want, what, scaled=False):
+    # the literal rule |got - ref| <= atol + rtol * |ref| for every element, no outlier budget; ``scaled`` (dropout
+    # cases only): errors are judged at the rms size of the tensor, see test_attention_dropout_golden_and_oracle
+    assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=scaled)
 
 
 def _run_case(device, batch, heads, q_len, kv_len, head_dim, mask_kind, rotary, seed=0):
@@ -136,6 +137,70 @@ def test_causal_mask_is_detected_and_equivalent(cuda_device):
     torch.testing.assert_close(lse_fast, lse_slow, rtol=1e-5, atol=1e-5)
 
 
+def test_attention_dropout_golden_and_oracle(cuda_device):
+    """Dropout on the probabilities: the kernels' mask is the Philox function of (seed, offset, element index over
+    [batch, heads, q_len, kv_len]); with that mask injected, the reference's core (golden vector) and the oracle agree
+    with the kernels, forward and backward."""
+    import lean_transformer_b200 as L
+
+    blob = load_golden("attention_core_dropout")
+    p, seed, offset, heads = float(blob["dropout"]), int(blob["seed"]), int(blob["offset"]), int(blob["heads"])
+    t = {k: torch.from_numpy(v) for k, v in blob.items() if v.ndim > 0}
+    q, k, v = (_bf16(t[n]).to(cuda_device) for n in ("query", "key", "value"))
+    g = _bf16(t["grad_out"]).to(cuda_device)
+    mask = t["mask"].float().to(cuda_device)
+    d = q.shape[-1] // heads
+    out, lse = L.ops.attention_forward(q, k, v, heads, d ** -0.5, mask, False, p, seed, offset)
+    dq, dk, dv = L.ops.attention_backward(g, q, k, v, out, lse, heads, d ** -0.5, mask, False, p, seed, offset)
+    _check(out, t["out"], "attention dropout golden:out")
+    for name, got in (("query", dq), ("key", dk), ("value", dv)):
+        _check(got, t[f"grad_{name}"], f"attention dropout golden:grad_{name}", scaled=True)
+    # a key length that is not a multiple of four (mask groups straddle the chunks), ragged tiles, 2 heads of 48
+    torch.manual_seed(9)
+    batch, heads, q_len, kv_len, d = 2, 2, 150, 203, 48
+    q = _bf16(torch.randn(batch, q_len, heads * d)).to(cuda_device)
+    k, v = (_bf16(torch.randn(batch, kv_len, heads * d)).to(cuda_device) for _ in range(2))
+    g = _bf16(torch.randn(batch, q_len, heads * d)).to(cuda_device)
+    p, seed, offset = 0.1, 1234567, 8
+    keep = torch.from_numpy(O.dropout_keep_mask(batch * heads * q_len * kv_len, p, seed, offset)).view(batch, heads, q_len, kv_len)
+    out, lse = L.ops.attention_forward(q, k, v, heads, d ** -0.5, None, True, p, seed, offset)
+    dq, dk, dv = L.ops.attention_backward(g, q, k, v, out, lse, heads, d ** -0.5, None, True, p, seed, offset)
+    causal = (1.0 - torch.ones(q_len, kv_len).tril(kv_len - q_len)).view(1, 1, q_len, kv_len).double() * -10000.0
+    want, grads = O.attention_core_step(q.double().cpu(), k.double().cpu(), v.double().cpu(), causal, heads,
+                                        grad_out=g.double().cpu(), dropout_p=p, keep_mask=keep)
+    _check(out, want, "attention dropout ragged:out")
+    for name, got in (("query", dq), ("key", dk), ("value", dv)):
+        _check(got, grads[name], f"attention dropout ragged:grad_{name}", scaled=True)
+    L.check_device_status(cuda_device)
+
+
+def test_attention_dropout_module_behaviour(cuda_device):
+    """Module level: the mask follows torch's CUDA generator (same seed, same result; another seed, another result),
+    forward and backward use the same mask (gradient check against a finite difference is not needed: the golden test
+    pins both), and evaluation mode drops nothing."""
+    import lean_transformer_b200 as L
+
+    core = L.SimpleAttentionCore(128, 2, attention_probs_dropout=0.3).to(cuda_device).train()
+    x = _bf16(torch.randn(2, 96, 128)).to(cuda_device)
+
+    def run(seed):
+        torch.manual_seed(seed)
+        leaf = x.clone().requires_grad_(True)
+        out, _ = core(leaf, leaf, leaf, None)
+        out.float().sum().backward()
+        return out.detach().clone(), leaf.grad.clone()
+
+    a, ga = run(1)
+    b, gb = run(1)
+    c, _ = run(2)
+    assert torch.equal(a, b) and torch.equal(ga, gb), "same generator state must give the same mask"
+    assert not torch.equal(a, c), "the mask ignored the generator"
+    core.eval()
+    e1, _ = core(x, x, x, None)
+    plain, _ = L.SimpleAttentionCore(128, 2).to(cuda_device)(x, x, x, None)
+    assert torch.equal(e1, plain), "dropout must be off in evaluation mode"
+
+
 def test_rotary_kernel_matches_oracle(cuda_device):
     import lean_transformer_b200 as L
 
@@ -182,11 +247,6 @@ def test_attention_rejections(cuda_device):
     xb = x.bfloat16()
     with pytest.raises(NotImplementedError, match="head sizes"):
         L.SimpleAttentionCore(120, 5).to(cuda_device)(xb[..., :120], xb[..., :120], xb[..., :120], None)  # head size 24
-    dropping = L.SimpleAttentionCore(128, 2, attention_probs_dropout=0.1).to(cuda_device).train()
-    with pytest.raises(NotImplementedError, match="dropout"):
-        dropping(xb, xb, xb, None)
-    dropping.eval()
-    dropping(xb, xb, xb, None)  # no dropout in evaluation mode
     with pytest.raises(AssertionError, match="float mask"):
         core(xb, xb, xb, torch.ones(1, 1, 64, 64, dtype=torch.bool, device=cuda_device))
     block = L.LeanSelfAttention(128, 2).to(cuda_device)

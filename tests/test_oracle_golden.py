@@ -126,3 +126,18 @@ def test_rotary_transposed_is_the_gradient():
     cos, sin = O.rotary_tables(9, 8)
     O.rotary_apply(x, cos, sin).backward(g)
     torch.testing.assert_close(O.rotary_apply_transposed(g, cos, sin), x.grad, rtol=1e-12, atol=1e-12)
+
+
+def test_attention_core_dropout_matches_reference():
+    """Dropout on the probabilities: the reference's SimpleAttentionCore with the oracle's Philox mask injected in
+    place of torch's (tests/golden/make_golden.py), against the restatement given the same mask."""
+    blob = load_golden("attention_core_dropout")
+    p, seed, offset, heads = float(blob["dropout"]), int(blob["seed"]), int(blob["offset"]), int(blob["heads"])
+    t = {k: torch.from_numpy(v) for k, v in blob.items() if v.ndim > 0}
+    batch, length = t["query"].shape[:2]
+    keep = torch.from_numpy(O.dropout_keep_mask(batch * heads * length * length, p, seed, offset)).view(batch, heads, length, length)
+    out, grads = O.attention_core_step(t["query"], t["key"], t["value"], t["mask"], heads, grad_out=t["grad_out"],
+                                       dropout_p=p, keep_mask=keep)
+    torch.testing.assert_close(out, t["out"], rtol=1e-9, atol=1e-11)
+    for name in ("query", "key", "value"):
+        torch.testing.assert_close(grads[name], t[f"grad_{name}"], rtol=1e-9, atol=1e-11)
