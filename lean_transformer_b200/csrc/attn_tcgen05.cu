@@ -281,21 +281,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   float m_run = -INFINITY, l_run = 0.f;
   uint32_t mma_phase = 0;
 
-  const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+  const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
   const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
   constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
   constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
 
-  // thread 0: S = Q . K^T as two independent accumulation chains (keys 0-63 and 64-127 of the tile), interleaved so
-  // that consecutive instructions do not wait for one another's accumulator
+  // thread 0: S = Q . K^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
+  // 128 x 16 block of Q once more per instruction, and the operand feed is what bounds these products)
   auto issue_s = [&]() {
     const int ksteps = p.d >> 4;
     for (int ks = 0; ks < ksteps; ++ks) {
       const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-#pragma unroll
-      for (int g = 0; g < 2; ++g)
-        umma_bf16(tmem + g * 64, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o + g * 8192u, k_major_hi),
-                  idesc_s, ks > 0 ? 1u : 0u);
+      umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
     }
     umma_commit(bar_s);
   };
