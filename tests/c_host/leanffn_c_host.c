@@ -161,6 +161,73 @@ static int run_block_case(const char* path) {
   return ok ? 0 : 26;
 }
 
+/* ---- one attention-core step from a flat file ----------------------------------------------------------------------
+ * File: 6 int64 (magic 0x4154544E, batch, len, heads, head_dim, 0), then float32 arrays: q, k, v, grad_out
+ * [batch * len * hidden]; mask [batch * len * len] (additive, shared by the heads); then the expected out, grad_q,
+ * grad_k, grad_v [batch * len * hidden] of the reference's SimpleAttentionCore. */
+static int run_attention_case(const char* path) {
+  FILE* f = fopen(path, "rb");
+  if (f == NULL) return 30;
+  int64_t head[6];
+  if (fread(head, sizeof(int64_t), 6, f) != 6 || head[0] != 0x4154544E) return 31;
+  const int64_t B = head[1], S = head[2], HEADS = head[3], D = head[4];
+  const size_t n = (size_t)(B * S * HEADS * D), nm = (size_t)(B * S * S);
+  const size_t sizes[9] = {n, n, n, n, nm, n, n, n, n};
+  float* h[9];
+  for (int i = 0; i < 9; ++i)
+    if ((h[i] = read_floats(f, sizes[i])) == NULL) return 32;
+  fclose(f);
+
+  cudaStream_t stream;
+  if (cudaStreamCreate(&stream) != cudaSuccess) return 33;
+  void *f32[4], *b16[4], *mask, *out, *dk, *dv, *lse, *delta, *dq, *back;
+  int32_t* status;
+  for (int i = 0; i < 4; ++i) { /* q, k, v, grad_out: upload as fp32, convert to bf16 on the device */
+    if (!upload(&f32[i], h[i], n) || cudaMalloc(&b16[i], 2 * n) != cudaSuccess) return 34;
+    if (leanffn_cast(f32[i], LEANFFN_F32, b16[i], LEANFFN_BF16, (int64_t)n, stream) != LEANFFN_OK) return 35;
+  }
+  if (!upload(&mask, h[4], nm)) return 34;
+  if (cudaMalloc(&out, 2 * n) != cudaSuccess || cudaMalloc(&dk, 2 * n) != cudaSuccess || cudaMalloc(&dv, 2 * n) != cudaSuccess ||
+      cudaMalloc(&dq, 4 * n) != cudaSuccess || cudaMalloc(&back, 4 * n) != cudaSuccess ||
+      cudaMalloc(&lse, 4 * (size_t)(B * HEADS * S)) != cudaSuccess || cudaMalloc(&delta, 4 * (size_t)(B * HEADS * S)) != cudaSuccess ||
+      cudaMalloc((void**)&status, sizeof(int32_t)) != cudaSuccess || cudaMemset(status, 0, sizeof(int32_t)) != cudaSuccess)
+    return 34;
+
+  leanffn_attention_desc d;
+  memset(&d, 0, sizeof(d));
+  d.batch = (int32_t)B, d.heads = (int32_t)HEADS, d.q_len = (int32_t)S, d.kv_len = (int32_t)S, d.head_dim = (int32_t)D;
+  d.scale = 1.0f / sqrtf((float)D);
+  d.q = b16[0], d.k = b16[1], d.v = b16[2];
+  d.ld_q = d.ld_k = d.ld_v = HEADS * D;
+  d.mask = (const float*)mask, d.mask_stride_b = S * S, d.mask_stride_h = 0, d.mask_stride_q = S;
+  d.out = out, d.ld_out = HEADS * D, d.lse = (float*)lse;
+  d.d_out = b16[3], d.ld_dout = HEADS * D, d.delta = (float*)delta, d.dq_accum = (float*)dq;
+  d.dk = dk, d.dv = dv, d.ld_dk = d.ld_dv = HEADS * D;
+  d.status_word = status;
+  if (leanffn_attention_forward(&d, stream) != LEANFFN_OK) return 36;
+  if (leanffn_attention_backward(&d, stream) != LEANFFN_OK) return 37;
+  float* got = malloc(sizeof(float) * n);
+  int32_t word = -1;
+  int ok = got != NULL;
+  void* results[3] = {out, dk, dv};
+  const int expected[3] = {5, 7, 8};
+  const char* names[3] = {"attention: out", "attention: grad k", "attention: grad v"};
+  for (int i = 0; ok && i < 3; ++i) { /* bf16 results come back through the cast kernel */
+    ok &= leanffn_cast(results[i], LEANFFN_BF16, back, LEANFFN_F32, (int64_t)n, stream) == LEANFFN_OK;
+    ok &= cudaMemcpyAsync(got, back, 4 * n, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    ok &= cudaStreamSynchronize(stream) == cudaSuccess;
+    ok &= matches(got, h[expected[i]], n, names[i]);
+  }
+  ok &= cudaMemcpy(got, dq, 4 * n, cudaMemcpyDeviceToHost) == cudaSuccess && matches(got, h[6], n, "attention: grad q");
+  ok &= cudaMemcpy(&word, status, sizeof(word), cudaMemcpyDeviceToHost) == cudaSuccess && word == 0;
+  /* rejected arguments: a head size the kernels do not take, a missing output */
+  d.head_dim = 24;
+  ok &= leanffn_attention_forward(&d, stream) == LEANFFN_ERR_UNSUPPORTED;
+  d.head_dim = (int32_t)D, d.out = NULL;
+  ok &= leanffn_attention_forward(&d, stream) == LEANFFN_ERR_NULL;
+  return ok ? 0 : 38;
+}
+
 int main(int argc, char** argv) {
   enum { ROWS = 96, COLS = 200, OUT = 72 };
   uint32_t rng = 12345u;
@@ -260,6 +327,13 @@ int main(int argc, char** argv) {
     const int code = run_block_case(argv[1]);
     if (code != 0) {
       fprintf(stderr, "whole-block step failed with code %d\n", code);
+      return code;
+    }
+  }
+  if (argc > 2) {
+    const int code = run_attention_case(argv[2]);
+    if (code != 0) {
+      fprintf(stderr, "attention step failed with code %d\n", code);
       return code;
     }
   }

@@ -58,10 +58,27 @@ def _write_block_case(path: Path, name: str = "ffn_dropout_mask"):
             f.write(np.ascontiguousarray(blob[key], dtype=np.float32).tobytes())
 
 
+def _write_attention_case(path: Path, name: str = "attention_core_simple"):
+    """A golden vector of the reference's SimpleAttentionCore (causal + padding mask) as the flat file the C host reads."""
+    import numpy as np
+    blob = np.load(ROOT / "tests" / "golden" / f"{name}.npz")
+    batch, length, hidden = blob["query"].shape
+    heads = int(blob["heads"])
+    head = np.array([0x4154544E, batch, length, heads, hidden // heads, 0], dtype=np.int64)
+    mask = np.broadcast_to(blob["mask"], (batch, 1, length, length)).reshape(batch, length, length)
+    with open(path, "wb") as f:
+        f.write(head.tobytes())
+        for arr in (blob["query"], blob["key"], blob["value"], blob["grad_out"], mask, blob["out"], blob["grad_query"],
+                    blob["grad_key"], blob["grad_value"]):
+            f.write(np.ascontiguousarray(arr, dtype=np.float32).tobytes())
+
+
 @pytest.mark.gpu
 def test_c_host_runs_the_kernels(tmp_path):
     exe = _build_c_host(tmp_path)
-    case = tmp_path / "block_case.bin"
+    case, attention = tmp_path / "block_case.bin", tmp_path / "attention_case.bin"
     _write_block_case(case)
-    res = subprocess.run([str(exe), str(case)], capture_output=True, text=True, timeout=120)
-    assert res.returncode == 0 and "C HOST OK" in res.stdout and "block: grad W2" in res.stdout, res.stdout + res.stderr
+    _write_attention_case(attention)
+    res = subprocess.run([str(exe), str(case), str(attention)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and "C HOST OK" in res.stdout and "block: grad W2" in res.stdout \
+        and "attention: grad q" in res.stdout, res.stdout + res.stderr
