@@ -615,11 +615,11 @@ def N_lib():
 
 
 def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=20, warmup=3):
-    """The attention core of BASELINE config 4 on its own: rotary + causal attention over batch x seq tokens, heads x
+    """The attention core of the 12-layer GPT configuration (hidden 768, 16 heads, 32 x 2048 tokens) on its own: rotary + causal attention over batch x seq tokens, heads x
     head_dim (this package's RotaryAttentionCore: leanffn_rotary + leanffn_attention_forward / backward), forward +
     backward, device-resident.  FLOPs: 4 * seq^2 * head_dim per head and batch row forward, 2.5 x that backward, halved
     by the causal rule.  The kernels are bound by the tensor cores' operand feed and the exponentials, so the fraction
-    of the dense-GEMM peak reported here is low by construction; DESIGN.md gives the per-tile budget."""
+    of the dense-GEMM peak reported here is low by construction."""
     import lean_transformer_b200 as L
     from lean_transformer_b200 import ops
 
@@ -704,7 +704,7 @@ def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=2
 
 
 def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
-    """BASELINE config 4: the REFERENCE's own 12-layer LeanGPT (hidden 768, 16 heads, rotary, GeGLU, tied embeddings,
+    """The full-model configuration: the REFERENCE's own 12-layer LeanGPT (hidden 768, 16 heads, rotary, GeGLU, tied embeddings,
     vocab 10 000; imported from the mirror oracle/_ref) on the GPU under autocast(bf16), forward + backward on 32 x 2048
     random token ids with labels = ids, timed three times on the same weights: with the reference's own modules (stock
     PyTorch CUDA operators); with its LeanFFN / GeneralizedLinear modules and the attention blocks' LayerNorm and

@@ -40,8 +40,8 @@ def golden_ffn_case(name: str, dtype=torch.float64):
 
 
 # Every comparison made through assert_close / record_closeness leaves a row here; a GPU session writes them to
-# gpurun_out/parity_report.json so the distance of each tensor from the LITERAL rule |got - ref| <= atol + rtol * |ref|
-# is on record next to the rule the tests enforce.
+# parity_report.json (in the folder GPU runs hand back) so the distance of each tensor from the LITERAL rule
+# |got - ref| <= atol + rtol * |ref| is on record next to the rule the tests enforce.
 PARITY_REPORT = []
 
 
