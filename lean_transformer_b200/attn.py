@@ -100,6 +100,54 @@ class _AttentionCoreFunction(torch.autograd.Function):
         return grad_q, dk, dv, None, None, None, None, None, None
 
 
+class _AttentionCoreQKVFunction(torch.autograd.Function):
+    """The same on the fused projection output qkv [batch, len, 3 * hidden] (queries | keys | values): the three slices
+    are read in place, queries and keys are rotated by one launch, and the backward pass writes the three gradients
+    straight into one [batch, len, 3 * hidden] tensor (no concatenation of split gradients)."""
+
+    @staticmethod
+    def forward(ctx, qkv, attention_mask, heads: int, cos, sin, scale: float, dropout_p: float = 0.0):
+        if qkv.dtype != torch.bfloat16 and not torch.is_autocast_enabled():
+            raise NotImplementedError(
+                "the attention kernels compute in bfloat16: run the block under torch.autocast(bfloat16) or pass "
+                f"bfloat16 tensors (got {qkv.dtype})")
+        batch, length, width3 = qkv.shape
+        hidden = width3 // 3
+        causal = mask_is_causal(attention_mask, length, length)
+        mask = None if causal else attention_mask
+        src = qkv if qkv.dtype == torch.bfloat16 else ops.rotary(qkv, None, None, 3 * heads)  # bf16 copy
+        if cos is not None:
+            qk = ops.rotary(src[..., :2 * hidden], cos, sin, 2 * heads)  # queries and keys: 2 * heads heads in a row
+            q, k = qk[..., :hidden], qk[..., hidden:]
+        else:
+            q, k = src[..., :hidden], src[..., hidden:2 * hidden]
+        v = src[..., 2 * hidden:]
+        seed = offset = 0
+        if dropout_p > 0:
+            seed, offset = next_dropout_stream(qkv.device, batch * heads * length * length)
+        out, lse = ops.attention_forward(q, k, v, heads, scale, mask, causal, dropout_p, seed, offset)
+        ctx.save_for_backward(q, k, v, out, lse, mask, cos, sin)
+        ctx.heads, ctx.scale, ctx.causal, ctx.dropout = heads, scale, causal, (dropout_p, seed, offset)
+        ctx.in_dtype = qkv.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, lse, mask, cos, sin = ctx.saved_tensors
+        heads, hidden = ctx.heads, q.shape[-1]
+        batch, length = q.shape[:2]
+        grad = torch.empty(batch, length, 3 * hidden, dtype=torch.bfloat16, device=q.device)
+        g_q, g_k, g_v = grad[..., :hidden], grad[..., hidden:2 * hidden], grad[..., 2 * hidden:]
+        dq, dk, _ = ops.attention_backward(grad_out, q, k, v, out, lse, heads, ctx.scale, mask, ctx.causal, *ctx.dropout,
+                                           out_dk=None if cos is not None else g_k, out_dv=g_v)
+        ops.rotary(dq, cos, sin, heads, inverse=True, out=g_q)  # fp32 accumulator -> bf16 slice
+        if cos is not None:
+            ops.rotary(dk, cos, sin, heads, inverse=True, out=g_k)
+        if ctx.in_dtype != torch.bfloat16:
+            grad = grad.to(ctx.in_dtype)
+        return grad, None, None, None, None, None, None
+
+
 class SimpleAttentionCore(nn.Module):
     """softmax(Q K^T / sqrt(head_size) + mask) V on the attention kernels (lean_transformer/attn.py:85-149).
     ``forward`` returns (outputs [batch, query_len, hidden_size], None): the probabilities are never materialised."""
@@ -135,6 +183,22 @@ class SimpleAttentionCore(nn.Module):
         scale = 1.0 / math.sqrt(self.attention_head_size)
         out = _AttentionCoreFunction.apply(query, key, value, attention_mask, self.num_attention_heads, cos, sin, scale,
                                            dropout_p)
+        return out, None
+
+    def forward_qkv(self, qkv, attention_mask):
+        """Self-attention on the fused projection output [batch, len, 3 * hidden_size] (queries | keys | values, the
+        layout ``LeanSelfAttention`` splits at lean_transformer/attn.py:69): same result as ``forward`` on the three
+        slices, without the copies that splitting and re-joining cost."""
+        if attention_mask is not None:
+            assert torch.is_floating_point(attention_mask), "expected float mask with negative values for masked items"
+        if not qkv.is_cuda:
+            raise RuntimeError("the attention core (lean_transformer_b200) needs CUDA tensors: it exists only as "
+                               "sm_100a kernels")
+        assert qkv.shape[-1] == 3 * self.hidden_size
+        dropout_p = float(self.attention_dropout.p) if self.training else 0.0
+        cos, sin = self._tables(qkv.shape[1], qkv.device)
+        scale = 1.0 / math.sqrt(self.attention_head_size)
+        out = _AttentionCoreQKVFunction.apply(qkv, attention_mask, self.num_attention_heads, cos, sin, scale, dropout_p)
         return out, None
 
 
@@ -251,9 +315,13 @@ class LeanSelfAttention(nn.Module):
         flat = hidden_states.reshape(-1, hidden_states.shape[-1])
         hidden_states_ln = _LayerNormFunction.apply(flat, ln.weight, ln.bias, ln.eps).view(*hidden_states.shape)
         qkv_output = self._project(self.qkv_proj, hidden_states_ln)
-        query, key, value = qkv_output.split(self.hidden_size, dim=qkv_output.ndim - 1)
-        attention_output, attention_probs = self._maybe_checkpoint(self.attention_core, query, key, value,
-                                                                   attention_mask)
+        if getattr(self.attention_core, "memory_lean", False) and qkv_output.dim() == 3:
+            # this package's cores take the fused projection output as it is
+            attention_output, attention_probs = self.attention_core.forward_qkv(qkv_output, attention_mask)
+        else:
+            query, key, value = qkv_output.split(self.hidden_size, dim=qkv_output.ndim - 1)
+            attention_output, attention_probs = self._maybe_checkpoint(self.attention_core, query, key, value,
+                                                                       attention_mask)
         p, training = self.output_dropout.p, self.training
         residual = hidden_states.to(torch.float32, copy=False) if self.residual else None
         if self.post_layer_norm is None:

@@ -491,10 +491,10 @@ def _rows_view(t: torch.Tensor) -> torch.Tensor:
 
 
 def rotary(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], heads: int, *, inverse: bool = False,
-           out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+           out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rotary embedding of x [batch, len, heads * head_dim] with fp32 tables [>= len, head_dim] (``leanffn_rotary``);
     ``inverse`` applies the transposed rotation (gradients).  Without tables: a dtype conversion into a contiguous
-    tensor."""
+    tensor.  ``out``: write into this tensor instead (same shape; a column slice of a wider tensor is fine)."""
     _require_cuda(x)
     x = _rows_view(x)
     batch, length, width = x.shape
@@ -504,9 +504,14 @@ def rotary(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Ten
             raise ValueError("rotary tables must be float32 with unit inner stride and equal pitches")
         if cos.shape[0] < length or cos.shape[-1] != head_dim:
             raise ValueError(f"rotary tables {tuple(cos.shape)} do not cover length {length} x head_dim {head_dim}")
-    y = torch.empty(batch, length, width, dtype=out_dtype, device=x.device)
+    if out is None:
+        y = torch.empty(batch, length, width, dtype=out_dtype, device=x.device)
+    else:
+        y = out
+        if y.shape != x.shape or y.stride(2) != 1 or y.stride(0) != length * y.stride(1):
+            raise ValueError(f"rotary output {tuple(y.shape)} / strides {y.stride()} does not match the input rows")
     N.check(N.lib.leanffn_rotary(_ptr(x), _dt(x), x.stride(1), _ptr(cos), _ptr(sin), 0 if cos is None else cos.stride(0),
-                                 _ptr(y), _dt(y), width, batch, length, heads, head_dim, int(inverse), _stream(x)),
+                                 _ptr(y), _dt(y), y.stride(1), batch, length, heads, head_dim, int(inverse), _stream(x)),
             "leanffn_rotary")
     _count()
     return y
@@ -576,17 +581,21 @@ def attention_forward(q, k, v, heads: int, scale: float, mask=None, causal: bool
 
 
 def attention_backward(d_out, q, k, v, out, lse, heads: int, scale: float, mask=None, causal: bool = False,
-                       dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0):
+                       dropout_p: float = 0.0, seed: int = 0, elem_offset: int = 0, out_dk=None, out_dv=None):
     """Gradients of ``attention_forward`` (``leanffn_attention_backward``) for the same (mask, causal, dropout_p, seed,
-    elem_offset): (dq float32 [batch, q_len, hidden], dk, dv bfloat16 [batch, kv_len, hidden])."""
+    elem_offset): (dq float32 [batch, q_len, hidden], dk, dv bfloat16 [batch, kv_len, hidden]).  ``out_dk`` / ``out_dv``:
+    bfloat16 tensors to write dk / dv into (row views of a wider tensor are fine)."""
     _require_cuda(d_out, q, k, v, out, lse, mask)
     q, k, v, d_out = _rows_view(q), _rows_view(k), _rows_view(v), _rows_view(d_out)
     if d_out.dtype != torch.bfloat16:
         d_out = d_out.to(torch.bfloat16)
     d, mask = _attention_desc(q, k, v, heads, scale, mask, causal, dropout_p, seed, elem_offset)
     dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
-    dk = torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
-    dv = torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
+    dk = out_dk if out_dk is not None else torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
+    dv = out_dv if out_dv is not None else torch.empty(k.shape, dtype=torch.bfloat16, device=q.device)
+    for t in (dk, dv):
+        if t.dtype != torch.bfloat16 or t.shape != k.shape or t.stride(2) != 1 or t.stride(0) != t.shape[1] * t.stride(1):
+            raise ValueError("dk / dv outputs must be bfloat16 row views of the key shape")
     delta = torch.empty_like(lse)
     d.out, d.ld_out, d.lse = _ptr(out), out.stride(1), _ptr(lse)
     d.d_out, d.ld_dout, d.delta, d.dq_accum = _ptr(d_out), d_out.stride(1), _ptr(delta), _ptr(dq)

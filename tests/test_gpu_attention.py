@@ -201,6 +201,31 @@ def test_attention_dropout_module_behaviour(cuda_device):
     assert torch.equal(e1, plain), "dropout must be off in evaluation mode"
 
 
+@pytest.mark.parametrize("rotary", [False, True])
+def test_fused_qkv_entry_equals_the_three_slice_call(cuda_device, rotary):
+    """forward_qkv (what this package's LeanSelfAttention calls) against forward on the three slices: same kernels,
+    same bits, and the gradient arrives as one [batch, len, 3 * hidden] tensor."""
+    import lean_transformer_b200 as L
+
+    torch.manual_seed(5)
+    heads, d, length = 4, 48, 200
+    hidden = heads * d
+    core = (L.RotaryAttentionCore if rotary else L.SimpleAttentionCore)(hidden, heads).to(cuda_device).train()
+    base = _bf16(torch.randn(2, length, 3 * hidden)).to(cuda_device)
+    g = _bf16(torch.randn(2, length, hidden)).to(cuda_device)
+    mask = ((1.0 - torch.ones(length, length).tril()).view(1, 1, length, length) * -10000.0).to(cuda_device)
+    mask = mask + torch.zeros(2, 1, 1, length, device=cuda_device)
+    mask[1, :, :, length - 20:] = -10000.0
+    a = base.clone().requires_grad_(True)
+    out_a, _ = core(*a.split(hidden, dim=-1), mask)
+    out_a.backward(g)
+    b = base.clone().requires_grad_(True)
+    out_b, probs = core.forward_qkv(b, mask)
+    out_b.backward(g)
+    assert probs is None and torch.equal(out_a, out_b)
+    assert b.grad.shape == base.shape and torch.equal(a.grad, b.grad)
+
+
 def test_rotary_kernel_matches_oracle(cuda_device):
     import lean_transformer_b200 as L
 
