@@ -166,6 +166,8 @@ class SimpleAttentionCore(nn.Module):
 
     def forward(self, query, key, value, attention_mask):
         """
+        (``key is None and value is None``: ``query`` is the fused projection output, see ``forward_qkv``.)
+
         :param query: [batch_size, query_seq_len, hidden_size]
         :param key: [batch_size, kv_seq_len, hidden_size]
         :param value: [batch_size, kv_seq_len, hidden_size]
@@ -173,6 +175,8 @@ class SimpleAttentionCore(nn.Module):
           tokens and a large negative value for masked ones
         :return: (outputs [batch_size, query_seq_len, hidden_size], None)
         """
+        if key is None and value is None:
+            return self.forward_qkv(query, attention_mask)
         if attention_mask is not None:
             assert torch.is_floating_point(attention_mask), "expected float mask with negative values for masked items"
         if not query.is_cuda:
@@ -316,8 +320,8 @@ class LeanSelfAttention(nn.Module):
         hidden_states_ln = _LayerNormFunction.apply(flat, ln.weight, ln.bias, ln.eps).view(*hidden_states.shape)
         qkv_output = self._project(self.qkv_proj, hidden_states_ln)
         if getattr(self.attention_core, "memory_lean", False) and qkv_output.dim() == 3:
-            # this package's cores take the fused projection output as it is
-            attention_output, attention_probs = self.attention_core.forward_qkv(qkv_output, attention_mask)
+            # this package's cores take the fused projection output as it is (a module call, so that hooks see it)
+            attention_output, attention_probs = self.attention_core(qkv_output, None, None, attention_mask)
         else:
             query, key, value = qkv_output.split(self.hidden_size, dim=qkv_output.ndim - 1)
             attention_output, attention_probs = self._maybe_checkpoint(self.attention_core, query, key, value,
