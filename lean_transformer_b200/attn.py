@@ -41,6 +41,10 @@ def mask_is_causal(mask: Optional[torch.Tensor], q_len: int, kv_len: int) -> boo
     for one reduction and one host read per forward pass."""
     if mask is None or mask.dim() < 2 or mask.shape[-2] != q_len or mask.shape[-1] != kv_len:
         return False
+    if kv_len < q_len:
+        # some rows would see no key at all: with a finite mask value the reference then attends uniformly-shifted raw
+        # scores, which the in-kernel rule (no key = zero output) does not reproduce; such masks are read as they are
+        return False
     entry = _CAUSAL_CACHE.get(id(mask))
     if entry is not None and entry[0]() is mask and entry[1] == mask._version:
         return entry[2]

@@ -113,6 +113,42 @@ def test_attention_core_config4_shape(cuda_device):
     _run_case(cuda_device, 1, 16, 2048, 2048, 48, "causal", True, seed=4)
 
 
+def test_attention_edge_shapes(cuda_device):
+    """One query against a long key sequence (a decoding step); more queries than keys under a finite causal mask
+    (rows that see no key attend the shifted raw scores, as in the reference: the mask is read, not replaced by the
+    in-kernel rule); a mask with -inf entries next to finite ones; a batch of three with one mask per batch row."""
+    import lean_transformer_b200 as L
+    from lean_transformer_b200.attn import mask_is_causal
+
+    def one(batch, heads, q_len, kv_len, d, mask, tag):
+        torch.manual_seed(13)
+        q = _bf16(torch.randn(batch, q_len, heads * d)).to(cuda_device).requires_grad_(True)
+        k = _bf16(torch.randn(batch, kv_len, heads * d)).to(cuda_device).requires_grad_(True)
+        v = _bf16(torch.randn(batch, kv_len, heads * d)).to(cuda_device).requires_grad_(True)
+        g = _bf16(torch.randn(batch, q_len, heads * d)).to(cuda_device)
+        core = L.SimpleAttentionCore(heads * d, heads).to(cuda_device)
+        out, _ = core(q, k, v, None if mask is None else mask.to(cuda_device))
+        out.backward(g)
+        want, grads = O.attention_core_step(q.detach().double().cpu(), k.detach().double().cpu(),
+                                            v.detach().double().cpu(), None if mask is None else mask.double(), heads,
+                                            grad_out=g.double().cpu())
+        _check(out, want, f"attention edge {tag}:out")
+        for name, t in (("query", q), ("key", k), ("value", v)):
+            _check(t.grad, grads[name], f"attention edge {tag}:grad_{name}")
+
+    one(2, 4, 1, 300, 64, None, "decode step")
+    more_q = (1.0 - torch.ones(300, 100).tril(100 - 300)).view(1, 1, 300, 100) * -10000.0
+    assert not mask_is_causal(more_q.to(cuda_device), 300, 100)
+    one(1, 2, 300, 100, 32, more_q, "more queries than keys")
+    partial = torch.zeros(2, 1, 130, 130)
+    partial[:, :, :, 100:] = float("-inf")
+    partial[1, :, :, :7] = -10000.0
+    one(2, 2, 130, 130, 48, partial, "-inf and finite mask values")
+    per_row = torch.randn(3, 1, 1, 257)
+    one(3, 2, 257, 257, 112, per_row, "batch of three, key mask, head size 112")
+    L.check_device_status(cuda_device)
+
+
 def test_causal_mask_is_detected_and_equivalent(cuda_device):
     """The causal fast path (rule applied in the kernel, tiles skipped) and the general path (mask read) agree, and
     the detection keys on the tensor object, not on its address."""
