@@ -806,6 +806,36 @@ def leangpt_measure(device, steps=3, warmup=1, batch=32, seq=2048):
     return out
 
 
+def leangpt_converted_steps(device, steps=2, batch=32, seq=2048):
+    """The converted 12-layer GPT alone (no reference runs): ``steps`` forward + backward passes, for launch lists."""
+    from oracle import ref_harness
+
+    ref = ref_harness.import_reference()
+    if ref is None:
+        raise RuntimeError("the mirrored reference package (oracle/_ref) is missing")
+    import lean_transformer_b200 as L
+    from lean_transformer_b200.integration import convert_model
+
+    torch.manual_seed(0)
+    config = ref.gpt.LeanGPTConfig(vocab_size=10000, hidden_size=768, num_hidden_layers=12, num_attention_heads=16,
+                                   position_embedding_type="rotary", hidden_act_gated=True, tie_word_embeddings=True)
+    model = convert_model(ref.gpt.LeanGPTModel(config).to(device).train())
+    ids = torch.randint(0, 10000, (batch, seq), device=device, generator=torch.Generator(device=device).manual_seed(0))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        for p in model.parameters():
+            p.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+    b.record()
+    torch.cuda.synchronize()
+    L.check_device_status(device)
+    return dict(workload="leangpt_bf16_h768 (converted model only)", steps=steps, ms_per_step_including_first=a.elapsed_time(b) / steps,
+                loss=float(loss.detach()))
+
+
 def epilogue_ablation(device):
     """What each phase of the fused GeGLU-backward epilogue costs: times the input-gradient product of config 2
     (16 384 x 1024 . 1024 x 4096) and of config 5 at 8192 tokens with phases of its epilogue left out.  Needs a
@@ -873,6 +903,9 @@ def main():
     ap.add_argument("--attention-only", action="store_true",
                     help="measure the attention-core workload alone (attention_bf16_h768) and print its line "
                          "(profiling runs)")
+    ap.add_argument("--leangpt-only", action="store_true",
+                    help="run --steps forward + backward passes of the converted 12-layer GPT and nothing else "
+                         "(profiling runs)")
     ap.add_argument("--epilogue-ablation", action="store_true",
                     help="time the GeGLU-backward product with phases of its epilogue left out (measurement build of "
                          "the library only; see epilogue_ablation)")
@@ -883,6 +916,10 @@ def main():
         print(json.dumps(dict(workload="attention_bf16_h768",
                               **attention_measure(torch.device("cuda", 0), steps=args.steps, warmup=args.warmup))),
               flush=True)
+        return
+    if args.leangpt_only:
+        torch.cuda.set_device(0)
+        print(json.dumps(leangpt_converted_steps(torch.device("cuda", 0), steps=max(args.steps, 1))), flush=True)
         return
     if args.epilogue_ablation:
         torch.cuda.set_device(0)
