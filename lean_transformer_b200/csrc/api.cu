@@ -394,6 +394,39 @@ static int32_t gemm_impl(const leanffn_gemm_desc* d, void* stream) {
       p.m_subtiles = 2;  // 256 x 128 tile = two weight blocks that share their x tile
       p.num_m_blocks = d->bs_num_blocks / 2;
     }
+    // Split-K: a dense product whose output has fewer 128-row tiles than the device has SMs and whose reduction is
+    // long (the weight gradients of narrow layers: [768, 768] from 65 536 tokens is 18 tiles) cuts the reduction into
+    // parts that run as tiles of their own and add into a zeroed fp32 result.  LEANFFN_SPLIT_K=1 turns it off.
+    p.split_k = 1;
+    static const int split_override = []() {
+      const char* v = getenv("LEANFFN_SPLIT_K");
+      return v != nullptr ? atoi(v) : 0;
+    }();
+    if (d->bs_mode == 0 && p.m_subtiles == 1 && epi == LEANFFN_EPI_STORE && d->bias == nullptr && d->K2 == 0 &&
+        d->scatter_world == 0 && d->d_dtype == LEANFFN_F32 && split_override != 1) {
+      const int sms = p.max_ctas > 0 && p.max_ctas < sm_count() ? p.max_ctas : sm_count();
+      const int64_t tiles = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
+      auto wave_eff = [sms](int64_t t) {
+        return static_cast<double>(t) / static_cast<double>(((t + sms - 1) / sms) * sms);
+      };
+      int best = 1;
+      double best_eff = wave_eff(tiles);
+      for (int s = 2; s <= 8; ++s) {
+        if (p.num_k_blocks / s < 16) break;  // at least 1024 elements of the reduction per part
+        const double e = wave_eff(tiles * s);
+        if (e > best_eff + 0.1) best = s, best_eff = e;
+      }
+      if (split_override > 1 && p.num_k_blocks / split_override >= 1) best = split_override;
+      if (best > 1) {
+        const cudaError_t me = cudaMemset2DAsync(d->D, static_cast<size_t>(d->ldd) * 4, 0, static_cast<size_t>(d->N) * 4,
+                                                 static_cast<size_t>(d->M), st);
+        if (me != cudaSuccess) return 1000 + static_cast<int32_t>(me);
+        p.split_k = best;
+        p.ep.scatter_world = 1;   // the epilogue adds (red.global.add.f32) instead of storing
+        p.ep.scatter_shift = 30;
+        p.ep.scatter_D[0] = d->D;
+      }
+    }
     cudaError_t ce;
     return gemm_tcgen05(d->a_mn_major != 0, d->b_mn_major != 0, A, B, d->K2 > 0 ? &A2 : nullptr,
                         d->K2 > 0 ? &B2 : nullptr, p, block_n, st, &ce);

@@ -83,6 +83,9 @@ struct TcParams {
   // TF32 mode: the reduction axis is cut into k_slices slices of num_k_blocks k-blocks (the last one k_blocks_last);
   // every slice is accumulated in tensor memory on its own and added to D by the epilogue (running fp32 sum)
   int32_t k_slices, k_blocks_last;
+  // dense bf16 products with few output tiles and a long reduction: the reduction axis is cut into split_k parts that
+  // run as separate tiles (on other SMs) and add their results into a zeroed D (ep.scatter_world = 1); 0 / 1 = off
+  int32_t split_k;
   int32_t bs_mode, bs_block, bs_nnz;
   const int32_t* bs_index;  // int32 pairs, see include/leanffn_b200.h
   const int32_t* bs_count;  // entries per table row, or nullptr

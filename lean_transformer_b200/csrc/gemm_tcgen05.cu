@@ -141,18 +141,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     n_blk = in_group / gm;
   };
 
+  // split-K (dense bf16 only): virtual tile v = part * num_tiles + tile; part s covers k-blocks [s * kps, (s + 1) * kps)
+  const int split = (!TF32 && p.split_k > 1) ? p.split_k : 1;
+  const int kps = (p.num_k_blocks + split - 1) / split;
+  const int num_vtiles = num_tiles * split;
+  auto part_k_blocks = [&](int part, int n_blk) {
+    return split > 1 ? max(0, min(kps, p.num_k_blocks - part * kps)) : main_k_blocks(n_blk);
+  };
+
   if (warp == 0 && lane == 0) {
     // ------------------------------- TMA producer --------------------------------------------
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int vtile = blockIdx.x; vtile < num_vtiles && ok; vtile += gridDim.x) {
+      const int tile = vtile % num_tiles, part = vtile / num_tiles;
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
       const int slices = TF32 ? p.k_slices : 1;
       for (int sl = 0; sl < slices && ok; ++sl) {
-      const int kb_main = (TF32 && sl == slices - 1) ? p.k_blocks_last : main_k_blocks(n_blk);
-      const int kb_base = TF32 ? sl * p.num_k_blocks : 0;  // first k-block of this slice
+      const int kb_main = (TF32 && sl == slices - 1) ? p.k_blocks_last : part_k_blocks(part, n_blk);
+      const int kb_base = TF32 ? sl * p.num_k_blocks : part * kps;  // first k-block of this slice / part
       const int kb_total = kb_main + p.num_k2_blocks;
       for (int kb = 0; kb < kb_total; ++kb) {
         if (*abort_ptr != 0 || !mbar_wait_bounded(empty_bar(stage), phase ^ 1u, wait_limit)) {
@@ -270,8 +279,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     const int mma_slices = TF32 ? p.k_slices : 1;
     for (int vt = 0; ok; ++vt) {  // virtual tiles: (tile, slice) pairs of this CTA, in order
-      const int tile = blockIdx.x + (vt / mma_slices) * gridDim.x, sl = vt % mma_slices;
-      if (tile >= num_tiles) break;
+      const int vtile = blockIdx.x + (vt / mma_slices) * gridDim.x, sl = vt % mma_slices;
+      if (vtile >= num_vtiles) break;
+      const int tile = vtile % num_tiles, part = vtile / num_tiles;
       if (*abort_ptr != 0 || !mbar_wait_bounded(tempty_bar(acc_stage), acc_phase ^ 1u, wait_limit)) {
         report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
         *abort_ptr = 1;
@@ -281,7 +291,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t d_tmem = tmem_base + acc_stage * (MT * BLOCK_N);
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
-      const int kb_total = ((TF32 && sl == mma_slices - 1) ? p.k_blocks_last : main_k_blocks(n_blk)) + p.num_k2_blocks;
+      const int kb_total = ((TF32 && sl == mma_slices - 1) ? p.k_blocks_last : part_k_blocks(part, n_blk)) + p.num_k2_blocks;
       for (int kb = 0; kb < kb_total; ++kb) {
         if (*abort_ptr != 0 || !mbar_wait_bounded(full_bar(stage), phase, wait_limit)) {
           report(p.status, LEANFFN_DEV_TIMEOUT_MMA);
@@ -335,7 +345,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     const int epi_slices = TF32 ? p.k_slices : 1;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+    for (int vtile = blockIdx.x; vtile < num_vtiles && alive; vtile += gridDim.x) {
+      const int tile = vtile % num_tiles, part = vtile / num_tiles;
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
 #pragma unroll 1
@@ -350,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         break;
       }
       tc_fence_after();
-      const bool acc_valid = main_k_blocks(n_blk) + p.num_k2_blocks > 0;  // empty reduction: acc is all zeros
+      const bool acc_valid = part_k_blocks(part, n_blk) + p.num_k2_blocks > 0;  // empty reduction: acc is all zeros
 #pragma unroll 1
       for (int t = 0; t < MT; ++t) {
         const int64_t row0 = static_cast<int64_t>(m_blk) * TILE_M + t * BLOCK_M + quarter * 32;
@@ -499,7 +510,7 @@ static cudaError_t tc_launch_t(const CUtensorMap& a, const CUtensorMap& b, const
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int tiles = p.num_m_blocks * p.num_n_blocks * (p.split_k > 1 ? p.split_k : 1);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   kern<<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(a, b, a2, b2, p);

@@ -217,6 +217,26 @@ def test_gemm_bf16_tensor_core(ops, cuda_device, a_mn, b_mn, M, N, K):
     ops.check_device_status(cuda_device)
 
 
+@pytest.mark.parametrize("a_mn,b_mn,M,N,K", [
+    (True, True, 768, 768, 65536),     # the output-projection weight gradient of the 12-layer GPT: 18 tiles, 8 parts
+    (True, True, 768, 3072, 16384),    # 72 tiles: 2 parts
+    (False, False, 200, 520, 32768),   # ragged tiles, K-major operands
+    (False, True, 256, 256, 20000),    # a reduction length that the parts do not divide evenly
+])
+def test_gemm_split_k_accumulates_in_fp32(ops, cuda_device, a_mn, b_mn, M, N, K):
+    """Dense bf16 products with an fp32 result, few output tiles and a long reduction run as split-K (the parts add
+    into a zeroed result): same values as the unsplit product up to fp32 summation order."""
+    torch.manual_seed(0)
+    a = (torch.randn((K, M) if a_mn else (M, K), device=cuda_device) * 0.1).to(torch.bfloat16)
+    b = (torch.randn((K, N) if b_mn else (N, K), device=cuda_device) * 0.1).to(torch.bfloat16)
+    out = torch.full((M, N), 7.0, device=cuda_device)  # the call must zero it itself
+    got = ops.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out, out_dtype=torch.float32)
+    A = (a.t() if a_mn else a).double().cpu()
+    B = (b.t() if b_mn else b).double().cpu()
+    ref = A @ B.t()
+    assert_close(got, ref, 1e-4, 1e-4, f"split-k gemm {M}x{N}x{K}", scale_atol=True)
+
+
 def test_gemm_rejects_bad_arguments(ops, cuda_device):
     a = torch.randn(8, 8, device=cuda_device)
     with pytest.raises(AssertionError):
