@@ -1,22 +1,23 @@
 // Attention core on tcgen05: softmax(scale * Q.K^T + mask) . V per (batch, head) without the [q_len, kv_len]
 // matrices ever reaching global memory, forward and backward.
 //
-// One CTA of 128 threads owns a 128-row tile: thread t owns row t (TMEM lane t) of every accumulator.  Thread 0
-// also issues the TMA loads and the MMAs.  All tiles are [128 rows x 64 columns] bf16 boxes (16 KiB, 128-byte
-// swizzle) fetched through a 4D tensor map over the [batch, len, heads, head_dim] view, so the head split and
-// transposes of the reference are address arithmetic; head_dim > 64 takes two boxes.  The same bytes serve as the
-// K-major operand of one product and the MN-major operand of another (a [128 x 64] box is 128 rows of 128 bytes
-// either way), so every tile is fetched once:
+// A CTA owns a 128-row tile; row r of every accumulator is TMEM lane r, and the threads that share a row split its
+// columns (two per row in the forward pass, four in the backward pass).  All tiles are [128 rows x 64 columns] bf16
+// boxes (16 KiB, 128-byte swizzle) fetched through a 4D tensor map over the [batch, len, heads, head_dim] view, so
+// the head split and transposes of the reference are address arithmetic; head_dim > 64 takes two boxes.  The same
+// bytes serve as the K-major operand of one product and the MN-major operand of another (a [128 x 64] box is 128 rows
+// of 128 bytes either way), so every tile is fetched once:
 //   forward, per key tile j:   S = Q_i . K_j^T -> softmax rows online -> P (bf16, written by the threads in the
 //                              swizzled K-major layout) -> O_j = P . V_j, accumulated in registers with the
-//                              running-maximum correction;
+//                              running-maximum correction; thread 0 issues the loads and products, two CTAs per SM
+//                              (head_dim <= 64) overlap one another's phases;
 //   backward, per query tile i (one CTA per key tile j):
 //                              S = Q_i . K_j^T, dP = dO_i . V_j^T -> P = exp2(S - lse), dS = P * (dP - delta)
 //                              -> dV += P^T . dO_i, dK += dS^T . Q_i (TMEM, whole loop), dQ_i = dS . K_j (added
-//                              to an fp32 buffer with vector reductions).
-// The two phases of an iteration are serial inside a CTA; several CTAs per SM (forward, head_dim <= 64) overlap
-// them.  Every mbarrier wait is bounded and followed by a block-wide vote, so either all threads continue or all
-// leave (status word set, TMEM freed).
+//                              to an fp32 buffer by TMA reductions); a dedicated warp issues the loads and
+//                              products, the hand-overs are mbarriers.
+// Every mbarrier wait is bounded; a wait that runs out sets the status word, every role leaves its loop and TMEM is
+// freed.  Warp-collective tensor-memory loads sit behind warp-uniform conditions only.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
