@@ -30,33 +30,62 @@ from .blocksparse.linear import GeneralizedLinear, _GeneralizedLinear
 from .ffn import _LayerNormFunction, next_dropout_stream
 from .fused_linear import linear_dropout_residual
 
-_CAUSAL_CACHE = {}  # id(mask) -> (weak reference to the mask, its version counter, answer)
+_MASK_CACHE = {}  # id(mask) -> (weak reference to the mask, its version counter, (causal, key mask or None))
 
 
-def mask_is_causal(mask: Optional[torch.Tensor], q_len: int, kv_len: int) -> bool:
-    """True when the additive mask is exactly the causal pattern for every batch row and head: 0 where
-    key <= query + (kv_len - q_len), at most -1e4 elsewhere (what models/gpt.py:274-285 builds when nothing is padded).
-    The kernels then apply the rule themselves, skip the empty tiles and never read the mask.  The answer is cached
-    per mask tensor OBJECT (and its version counter), so the layers of a model that all receive the same tensor pay
-    for one reduction and one host read per forward pass."""
-    if mask is None or mask.dim() < 2 or mask.shape[-2] != q_len or mask.shape[-1] != kv_len:
-        return False
-    if kv_len < q_len:
-        # some rows would see no key at all: with a finite mask value the reference then attends uniformly-shifted raw
-        # scores, which the in-kernel rule (no key = zero output) does not reproduce; such masks are read as they are
-        return False
-    entry = _CAUSAL_CACHE.get(id(mask))
+def analyze_mask(mask: Optional[torch.Tensor], q_len: int, kv_len: int):
+    """Split an additive attention mask into what the kernels can apply without reading [q_len, kv_len] values.
+
+    Returns ``(causal, mask_to_read)``:
+
+    * ``(True, None)``: the mask is exactly the causal pattern for every batch row and head (0 where
+      key <= query + (kv_len - q_len), at most -1e4 elsewhere: what models/gpt.py:274-285 builds when nothing is padded).
+      The kernels apply the rule themselves and skip the tiles it empties.
+    * ``(True, key_mask)`` with ``key_mask`` [batch, heads or 1, 1, kv_len]: the causal pattern plus a per-key term
+      (padding: gpt.py:274-276 + :278-285).  The rule is applied in the kernel, the per-key term is read (one row per
+      batch entry instead of q_len rows).  Only taken when every query row keeps at least one visible key whose per-key
+      term is 0, so that the entries the rule removes are exactly the ones whose probability underflows to 0.
+    * ``(False, mask)``: anything else is read as it is.
+
+    The answer is cached per mask tensor OBJECT (and its version counter), so the layers of a model that all receive the
+    same tensor pay for the analysis (a few elementwise passes and one host read) once per forward pass."""
+    if mask is None:
+        return False, None
+    if mask.dim() < 2 or mask.shape[-2] != q_len or mask.shape[-1] != kv_len or kv_len < q_len or mask.dim() > 4:
+        # kv_len < q_len: some rows would see no key at all; with a finite mask value the reference then attends the
+        # shifted raw scores, which the in-kernel rule (no key = zero output) does not reproduce
+        return False, mask
+    entry = _MASK_CACHE.get(id(mask))
     if entry is not None and entry[0]() is mask and entry[1] == mask._version:
         return entry[2]
     allowed = torch.ones(q_len, kv_len, dtype=torch.bool, device=mask.device).tril_(kv_len - q_len)
-    answer = bool(torch.where(allowed, mask == 0, mask <= -1e4).all().item())
-    if len(_CAUSAL_CACHE) > 64:
-        for key in [k for k, e in _CAUSAL_CACHE.items() if e[0]() is None]:
-            del _CAUSAL_CACHE[key]
-        if len(_CAUSAL_CACHE) > 64:
-            _CAUSAL_CACHE.clear()
-    _CAUSAL_CACHE[id(mask)] = (weakref.ref(mask), mask._version, answer)
+    per_key = mask[..., q_len - 1:q_len, :]  # the last query row sees every key: its entries are the per-key terms
+    structured = torch.where(allowed, mask == per_key, mask <= -1e4).all()
+    anchored = ((per_key == 0) & allowed).any(dim=-1).all()  # every row keeps a visible key with term 0
+    plain = (per_key == 0).all()
+    structured, anchored, plain = (bool(v) for v in torch.stack([structured, anchored, plain]).tolist())
+    if structured and plain:
+        answer = (True, None)
+    elif structured and anchored:
+        key_mask = per_key.to(torch.float32).contiguous()
+        while key_mask.dim() < 4:
+            key_mask = key_mask.unsqueeze(0)
+        answer = (True, key_mask)
+    else:
+        answer = (False, mask)
+    if len(_MASK_CACHE) > 64:
+        for key in [k for k, e in _MASK_CACHE.items() if e[0]() is None]:
+            del _MASK_CACHE[key]
+        if len(_MASK_CACHE) > 64:
+            _MASK_CACHE.clear()
+    _MASK_CACHE[id(mask)] = (weakref.ref(mask), mask._version, answer)
     return answer
+
+
+def mask_is_causal(mask: Optional[torch.Tensor], q_len: int, kv_len: int) -> bool:
+    """True when the additive mask is exactly the causal pattern (see ``analyze_mask``)."""
+    causal, to_read = analyze_mask(mask, q_len, kv_len)
+    return causal and to_read is None
 
 
 class _AttentionCoreFunction(torch.autograd.Function):
@@ -72,8 +101,7 @@ class _AttentionCoreFunction(torch.autograd.Function):
                     "the attention kernels compute in bfloat16: run the block under torch.autocast(bfloat16) or pass "
                     f"bfloat16 tensors (got {t.dtype})")
         q_len, kv_len = query.shape[1], key.shape[1]
-        causal = mask_is_causal(attention_mask, q_len, kv_len)
-        mask = None if causal else attention_mask
+        causal, mask = analyze_mask(attention_mask, q_len, kv_len)
         if cos is not None:
             q = ops.rotary(query, cos, sin, heads)
             k = ops.rotary(key, cos, sin, heads)
@@ -117,8 +145,7 @@ class _AttentionCoreQKVFunction(torch.autograd.Function):
                 f"bfloat16 tensors (got {qkv.dtype})")
         batch, length, width3 = qkv.shape
         hidden = width3 // 3
-        causal = mask_is_causal(attention_mask, length, length)
-        mask = None if causal else attention_mask
+        causal, mask = analyze_mask(attention_mask, length, length)
         src = qkv if qkv.dtype == torch.bfloat16 else ops.rotary(qkv, None, None, 3 * heads)  # bf16 copy
         if cos is not None:
             qk = ops.rotary(src[..., :2 * hidden], cos, sin, 2 * heads)  # queries and keys: 2 * heads heads in a row

@@ -171,6 +171,23 @@ def test_causal_mask_is_detected_and_equivalent(cuda_device):
     slow, lse_slow = L.ops.attention_forward(q, k, v, heads, scale, causal, False)
     torch.testing.assert_close(fast.float(), slow.float(), rtol=0, atol=1e-2)
     torch.testing.assert_close(lse_fast, lse_slow, rtol=1e-5, atol=1e-5)
+    # causal + padding at the end of a row: the rule in the kernel plus one mask row per batch entry
+    from lean_transformer_b200.attn import analyze_mask
+    is_causal, key_mask = analyze_mask(padded, S, S)
+    assert is_causal and key_mask is not None and key_mask.shape == (2, 1, 1, S)
+    split, lse_split = L.ops.attention_forward(q, k, v, heads, scale, key_mask, True)
+    whole, lse_whole = L.ops.attention_forward(q, k, v, heads, scale, padded, False)
+    torch.testing.assert_close(split.float(), whole.float(), rtol=0, atol=1e-2)
+    torch.testing.assert_close(lse_split, lse_whole, rtol=1e-5, atol=1e-5)
+    g = _bf16(torch.randn(2, S, heads * d)).to(cuda_device)
+    grads_split = L.ops.attention_backward(g, q, k, v, split, lse_split, heads, scale, key_mask, True)
+    grads_whole = L.ops.attention_backward(g, q, k, v, whole, lse_whole, heads, scale, padded, False)
+    for a, b in zip(grads_split, grads_whole):
+        torch.testing.assert_close(a.float(), b.float(), rtol=0, atol=2e-2)
+    # padding at the START of a row leaves early queries without an unpadded visible key: read as it is
+    left = causal.expand(2, 1, S, S).clone()
+    left[1, :, :, :9] += -10000.0
+    assert analyze_mask(left, S, S) == (False, left) or analyze_mask(left, S, S)[0] is False
 
 
 def test_attention_dropout_golden_and_oracle(cuda_device):
