@@ -78,3 +78,33 @@ def test_pad_to_multiple():
     assert torch.allclose(L.pad_to_multiple(x, multiple=4, dims=1).sum(), x.sum())
     assert L.pad_to_multiple(x, multiple=10, dims=0)[3:].norm() == 0
     assert torch.equal(L.pad_to_multiple(x, multiple=2, dims=-1)[:, :3], x)
+
+
+def test_attention_mask_analysis():
+    """Host-side recognition of the causal pattern and of causal + per-key padding (no device needed)."""
+    import torch
+    from lean_transformer_b200.attn import analyze_mask, mask_is_causal
+
+    S = 12
+    causal = (1.0 - torch.ones(S, S).tril()).view(1, 1, S, S) * -10000.0
+    assert analyze_mask(None, S, S) == (False, None)
+    assert analyze_mask(causal, S, S) == (True, None) and mask_is_causal(causal, S, S)
+    right = torch.zeros(3, 1, 1, S)
+    right[1, 0, 0, 8:] = -10000.0
+    is_causal, key_mask = analyze_mask(right + causal, S, S)
+    assert is_causal and key_mask.shape == (3, 1, 1, S) and torch.equal(key_mask, right)
+    assert not mask_is_causal(right + causal, S, S)
+    left = torch.zeros(3, 1, 1, S)
+    left[2, 0, 0, :4] = -10000.0  # the first query rows of that batch entry see padded keys only
+    is_causal, to_read = analyze_mask(left + causal, S, S)
+    assert not is_causal and to_read.shape == (3, 1, S, S)
+    assert analyze_mask(torch.randn(2, 1, S, S), S, S)[0] is False
+    assert analyze_mask(torch.zeros(1, 1, S, S), S, S)[0] is False  # no mask at all is not the causal pattern
+    wide = (1.0 - torch.ones(S, S + 5).tril(5)).view(1, 1, S, S + 5) * -10000.0  # keys of a cache before the queries
+    assert analyze_mask(wide, S, S + 5) == (True, None)
+    tall = (1.0 - torch.ones(S + 5, S).tril(-5)).view(1, 1, S + 5, S) * -10000.0  # more queries than keys: read as it is
+    assert analyze_mask(tall, S + 5, S)[0] is False
+    edited = causal.clone()
+    assert analyze_mask(edited, S, S) == (True, None)
+    edited[0, 0, 3, 1] = -5.0  # an in-place edit of a tensor already analysed: the version counter invalidates the answer
+    assert analyze_mask(edited, S, S)[0] is False
