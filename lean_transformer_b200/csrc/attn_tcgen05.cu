@@ -383,9 +383,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     __syncthreads();
     ATTN_PROF(4);
 
-    ok = wait_all(bar_v, j & 1);
-    if (!ok) break;
-    if (tid == 0) {
+    // only the issuing thread needs V_j; if it never arrives nothing is issued and every thread's wait below runs out
+    if (tid == 0 && mbar_wait_bounded(bar_v, j & 1, limit)) {
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {  // O_g = P_g . V_g over the group's 64 keys, the two chains interleaved
@@ -416,8 +415,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int x = 0; x < 32; ++x) o_acc[c * 32 + x] = fmaf(o_acc[c * 32 + x], alpha, __uint_as_float(acc[x]));
     }
     ATTN_PROF(6);
-    tc_fence_before();
-    __syncthreads();
+    tc_fence_before();  // the block barrier inside the next wait_all orders these reads before the next products
   }
 
   if (ok) {
