@@ -137,22 +137,6 @@ __device__ __forceinline__ void score_chunk(const uint32_t (&acc)[32], float (&v
   }
 }
 
-// Measurement builds (-DLEANFFN_ATTN_PROFILE): thread 0 of block (0, 0, 0) adds the SM clocks each phase of its loop
-// took to g_attn_prof[slot]; leanffn_attention_profile copies the counters out and clears them.
-#ifdef LEANFFN_ATTN_PROFILE
-__device__ long long g_attn_prof[16];
-#define ATTN_PROF_DECL long long prof_t = clock64(); const bool prof_on = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0
-#define ATTN_PROF(slot)                                  \
-  if (prof_on) {                                         \
-    const long long now = clock64();                     \
-    g_attn_prof[slot] += now - prof_t;                   \
-    prof_t = now;                                        \
-  }
-#else
-#define ATTN_PROF_DECL
-#define ATTN_PROF(slot)
-#endif
-
 // Dropout factors of 32 consecutive probabilities starting at element index e0: f[x] = 1 / (1 - p) if kept, else 0.
 // Not inlined: the counter-based generator needs many registers; f lives in local memory.  `aligned` must be uniform
 // over the warp (it is a property of kv_len and the stream offset, not of the row): the callers execute warp-collective
@@ -188,14 +172,30 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Forward.  grid = (query tiles, heads, batch), 256 threads.  DPAD = head_dim rounded up to 32.
-// Two thread groups of 128 (warps 0-3, warps 4-7) split the keys of every tile: group g owns keys [64g, 64g + 64)
-// of the tile for row tid % 128 -- its own running maximum, denominator and output row, its own half of P and its
-// own product O_g = P_g . V_g in tensor memory.  The groups never exchange anything inside the loop; their two
-// partial softmax states are merged once at the end.
-// Shared memory: Q, K, V (DC boxes each, DC = ceil(head_dim / 64)), P (2 boxes: one per group), barriers.
+// Forward.  grid = (query tiles, heads, batch).  8 compute warps + 1 issuing warp; two CTAs per SM for head_dim <= 64.
+// DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own instantiation, so that the
+// counter-based generator costs the plain kernels nothing).
+//
+// Compute warps: two thread groups of 128 (warps 0-3, warps 4-7) split the keys of every tile: group g owns keys
+// [64g, 64g + 64) of the tile for row tid % 128 -- its own reference maximum and denominator, its own half of P and
+// its own output row O_g, which stays in tensor memory for the whole loop: the products P_g . V_g accumulate there.
+// The reference maximum of a row only moves when a tile's maximum exceeds it by more than 2^8 (then the row of O_g
+// and the denominator are rescaled, a tensor-memory load / store); otherwise probabilities are taken against the old
+// reference and may reach 2^8, which bf16 and the fp32 sums hold without loss.  The two groups never exchange anything
+// inside the loop; their partial states are merged once at the end.  Lane 0 of the issuing warp requests every tile
+// (TMA) and issues every product: issuing blocks while the tensor cores' queue is full, so that thread does nothing
+// else, and products complete in issue order, so "S_{j+1} is complete" also tells the compute warps that P.V of tile j
+// is (P_j is free, O_g is up to date).
+//
+// Per key tile j:  compute: wait S_j -> maximum -> (rescale O_g) -> P = exp2(S - m) -> shared memory -> 8 arrivals on bar_p
+//                  issuer:  wait bar_p -> P.V of tile j into O_g -> S_{j+1} -> request K_{j+2}; once S_{j+1} is complete,
+//                           request V_{j+1}
+// Hand-overs are mbarriers with bounded waits only; the second CTA on the SM fills the gaps that remain.
+// Shared memory: Q, 2 x K, V (DC boxes each, DC = ceil(head_dim / 64)), P (2 boxes: one per group), barriers.
 // TMEM: columns [0, 128) S; then one block of OCOLS columns per group for O_g.
-constexpr int FWD_THREADS = 256;
+constexpr int FWD_COMPUTE_WARPS = 8;
+constexpr int FWD_THREADS = 32 * (FWD_COMPUTE_WARPS + 1);
+constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 template <int DPAD, bool DROP>
 __global__ void __launch_bounds__(FWD_THREADS, DPAD <= 64 ? 2 : 1)
@@ -207,15 +207,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
   const uint32_t tile_bytes = DC * BOX_BYTES;
-  const uint32_t sQ = sm.base, sK = sQ + tile_bytes, sV = sK + tile_bytes, sP = sV + tile_bytes;
+  const uint32_t sQ = sm.base, sK0 = sQ + tile_bytes, sV = sK0 + 2 * tile_bytes, sP = sV + tile_bytes;
   const uint32_t bar0 = sP + PS_BYTES;
-  const uint32_t bar_q = bar0, bar_k = bar0 + 8, bar_v = bar0 + 16, bar_mma = bar0 + 24, bar_s = bar0 + 32;
-  const uint32_t tmem_slot = bar0 + 48;
-  uint8_t* gP = sm.gen + 3 * tile_bytes;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 3 * tile_bytes + PS_BYTES + 48);
+  const uint32_t bar_q = bar0, bar_k0 = bar0 + 8 /* 2 */, bar_v = bar0 + 24, bar_s = bar0 + 32, bar_o = bar0 + 40;
+  const uint32_t bar_p = bar0 + 48, tmem_slot = bar0 + 56;
+  uint8_t* gP = sm.gen + 4 * tile_bytes;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gP + PS_BYTES + 56);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int grp = warp >> 2, row = tid & 127;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = (warp >> 2) & 1, row = tid & 127;
+  const bool issuer = warp == FWD_COMPUTE_WARPS;
   const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + TILE - 1) / TILE;
   const int qt = nq - 1 - static_cast<int>(blockIdx.x);  // long (late) rows first under the causal rule
   const int h = blockIdx.y, b = blockIdx.z;
@@ -230,10 +231,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_k, 1);
+    mbar_init(bar_k0, 1);
+    mbar_init(bar_k0 + 8, 1);
     mbar_init(bar_v, 1);
-    mbar_init(bar_mma, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    mbar_init(bar_p, FWD_COMPUTE_WARPS);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -249,186 +252,203 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem = *tmem_slot_ptr;
   const uint32_t t_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
   const uint32_t t_out = t_row + 128 + grp * OCOLS;
-
-  auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
-    mbar_arrive_expect_tx(bar, tile_bytes);
-    for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
-  };
   bool ok = true;
-  auto wait_all = [&](uint32_t bar, uint32_t parity) {
-    const bool mine = mbar_wait_bounded(bar, parity, limit);
-    return __syncthreads_and(mine) != 0;
-  };
-
-  if (tid == 0 && nkv > 0) {
-    load_tile(&tmQ, sQ, bar_q, qt * TILE);
-    load_tile(&tmK, sK, bar_k, 0);
-    load_tile(&tmV, sV, bar_v, 0);
-  }
-  if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
 
   const int q_row = qt * TILE + row;
-  const int q_clamped = min(q_row, p.Sq - 1);
-  const float* mask_row = p.mask == nullptr ? nullptr
-                                            : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
-  const float scale_log2 = p.scale * LOG2E;
-  const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
-  const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
-  const bool drop_aligned = ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0;  // uniform: every chunk starts a Philox group
-
-  float o_acc[DPAD];
-#pragma unroll
-  for (int x = 0; x < DPAD; ++x) o_acc[x] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
-  uint32_t mma_phase = 0;
 
-  const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-  const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
-  constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
-  constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
-
-  // thread 0: S = Q . K^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
-  // 128 x 16 block of Q once more per instruction, and the operand feed is what bounds these products)
-  auto issue_s = [&]() {
-    const int ksteps = p.d >> 4;
-    for (int ks = 0; ks < ksteps; ++ks) {
-      const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-      umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s, ks > 0 ? 1u : 0u);
+  if (issuer) {
+    if (lane == 0 && nkv > 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
+      constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
+      constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
+      auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
+        mbar_arrive_expect_tx(bar, tile_bytes);
+        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+      };
+      // S_j = Q . K_j^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
+      // 128 x 16 block of Q once more per instruction, and the operand feed is what bounds these products)
+      auto issue_s = [&](int j) {
+        const uint32_t sK = sK0 + (j & 1) * tile_bytes;
+        const int ksteps = p.d >> 4;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          if (ks < ksteps) {
+            const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+            umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s,
+                      ks > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(bar_s);
+      };
+      load_tile(&tmQ, sQ, bar_q, qt * TILE);
+      load_tile(&tmK, sK0, bar_k0, 0);
+      if (nkv > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, TILE);
+      load_tile(&tmV, sV, bar_v, 0);
+      bool go = mbar_wait_bounded(bar_q, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
+      if (go) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < nkv && go; ++j) {
+        go = mbar_wait_bounded(bar_p, j & 1, limit);  // P_j is in shared memory, S_j has been read, O_g rescaled
+        if (go) go = mbar_wait_bounded(bar_v, j & 1, limit);
+        if (!go) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {  // O_g += P_g . V_g over the group's 64 keys, the two chains interleaved
+#pragma unroll
+          for (int g = 0; g < 2; ++g)
+            umma_bf16(tmem + 128 + g * OCOLS, make_smem_desc(sP + g * BOX_BYTES + ks * 32u, k_major_hi),
+                      make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        if (j + 1 < nkv) {
+          go = mbar_wait_bounded(bar_k0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, limit);  // requested a tile ago
+          if (!go) break;
+          issue_s(j + 1);
+          if (j + 2 < nkv) load_tile(&tmK, sK0 + (j & 1) * tile_bytes, bar_k0 + 8 * (j & 1), (j + 2) * TILE);  // K_j is free
+          go = mbar_wait_bounded(bar_s, (j + 1) & 1, limit);  // S_{j+1} complete: so is P.V of tile j, V_j is free
+          if (!go) break;
+          load_tile(&tmV, sV, bar_v, (j + 1) * TILE);
+        } else {
+          umma_commit(bar_o);  // the last product: the output rows are complete
+        }
+      }
+      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
     }
-    umma_commit(bar_s);
-  };
-  if (nkv > 0) {
-    ok = wait_all(bar_q, 0);
-    if (ok) ok = wait_all(bar_k, 0);
-    if (ok && tid == 0) {
+    __syncwarp();
+  } else {
+    const int q_clamped = min(q_row, p.Sq - 1);
+    const float* mask_row = p.mask == nullptr ? nullptr
+                                              : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
+    const float scale_log2 = p.scale * LOG2E;
+    const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
+    const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
+    const bool drop_aligned = ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0;  // uniform: every chunk starts a Philox group
+    auto wait_warp = [&](uint32_t bar, uint32_t parity) {  // the whole warp continues or the whole warp leaves
+      return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, limit)) != 0;
+    };
+    for (int j = 0; j < nkv; ++j) {
+      // S_j complete; products complete in issue order, so P.V of tile j - 1 is complete too
+      ok = wait_warp(bar_s, j & 1);
+      if (!ok) break;
       tc_fence_after();
-      issue_s();
-    }
-    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
-  }
-  ATTN_PROF_DECL;
-  for (int j = 0; j < nkv && ok; ++j) {
-    ATTN_PROF(0);
-    ATTN_PROF(1);
-    ok = wait_all(bar_s, j & 1);
-    if (!ok) break;
-    if (tid == 0 && j + 1 < nkv) load_tile(&tmK, sK, bar_k, (j + 1) * TILE);  // K_j has been consumed
-    if (warp == 0) __syncwarp();
-    tc_fence_after();
-    ATTN_PROF(2);
-
-    // ---- softmax of this group's 64 keys of the row: maximum first, then the probabilities ----
-    const int k0 = j * TILE + grp * 64;
-    // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
-    const bool plain = p.mask == nullptr && j * TILE + TILE <= p.Skv &&
-                       (!p.causal || j * TILE + TILE - 1 <= qt * TILE + off);
-    float mx = -INFINITY;
+      const int k0 = j * TILE + grp * 64;
+      // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
+      const bool plain = p.mask == nullptr && j * TILE + TILE <= p.Skv && scale_log2 > 0.f &&
+                         (!p.causal || j * TILE + TILE - 1 <= qt * TILE + off);
+      float mx = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t acc[32];
-      tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-      tmem_ld_wait();
-      if (plain) {
+      for (int c = 0; c < 2; ++c) {
+        uint32_t acc[32];
+        tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
+        tmem_ld_wait();
+        if (plain) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
-      } else {
+          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
+        } else {
+          float v[32];
+          score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+        }
+      }
+      if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
+      // the reference maximum moves only when this tile exceeds it by more than the threshold (always on the first
+      // tile that has a finite score); the decision is taken per warp, the tensor-memory accesses are warp-collective
+      const bool move = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, move)) {
+        const float m_new = move ? mx : m_run;
+        const float alpha = (move && m_run > -INFINITY) ? fast_exp2(m_run - m_new) : 1.f;
+        if (j > 0) {  // rows of O_g that exist already (uniform)
+#pragma unroll
+          for (int c = 0; c < DPAD / 32; ++c) {
+            uint32_t acc[32];
+            tmem_ld_32x32(t_out + c * 32, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) acc[x] = __float_as_uint(__uint_as_float(acc[x]) * alpha);
+            tmem_st_32x32(t_out + c * 32, acc);
+          }
+          tmem_st_wait();
+        }
+        l_run *= alpha;
+        m_run = m_new;
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      float row_sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t acc[32];
         float v[32];
-        score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+        tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
+        tmem_ld_wait();
+        if (plain) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+          for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
+        } else {
+          score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+          for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
+        }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) row_sum += v[x];
+        if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
+          float f[32];
+          dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
+#pragma unroll
+          for (int x = 0; x < 32; ++x) v[x] *= f[x];
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 w;
+          w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
+          w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
+          w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
+          w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+          *reinterpret_cast<uint4*>(gP + ps_offset(row, grp * 8 + c * 4 + q4)) = w;
+        }
       }
+      l_run += row_sum;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
     }
-    if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
-    const float m_new = fmaxf(m_run, mx);
-    const float m_use = m_new == -INFINITY ? 0.f : m_new;
-    const float alpha = exp2f(m_run - m_use);
-    float row_sum = 0.f;
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t acc[32];
-      float v[32];
-      tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-      tmem_ld_wait();
-      if (plain) {
-#pragma unroll
-        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
-      } else {
-        score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
-#pragma unroll
-        for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
-      }
-#pragma unroll
-      for (int x = 0; x < 32; ++x) row_sum += v[x];
-      if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
-        float f[32];
-        dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
-#pragma unroll
-        for (int x = 0; x < 32; ++x) v[x] *= f[x];
-      }
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint4 w;
-        w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-        w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-        w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-        w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-        *reinterpret_cast<uint4*>(gP + ps_offset(row, grp * 8 + c * 4 + q4)) = w;
-      }
-    }
-    l_run = l_run * alpha + row_sum;
-    m_run = m_new;
-    ATTN_PROF(3);
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    ATTN_PROF(4);
-
-    // only the issuing thread needs V_j; if it never arrives nothing is issued and every thread's wait below runs out
-    if (tid == 0 && mbar_wait_bounded(bar_v, j & 1, limit)) {
-      tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {  // O_g = P_g . V_g over the group's 64 keys, the two chains interleaved
-#pragma unroll
-        for (int g = 0; g < 2; ++g)
-          umma_bf16(tmem + 128 + g * OCOLS, make_smem_desc(sP + g * BOX_BYTES + ks * 32u, k_major_hi),
-                    make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, ks > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_mma);
-      // the next tile's scores right behind: S_j has been consumed, K_{j+1} was requested a softmax ago (if it
-      // never arrives the scores are not issued and every thread's wait for them runs out)
-      if (j + 1 < nkv && mbar_wait_bounded(bar_k, (j + 1) & 1, limit)) issue_s();
-    }
-    if (warp == 0) __syncwarp();  // the other lanes of the issuing warp wait here instead of spinning beside it
-    ok = wait_all(bar_mma, mma_phase);
-    mma_phase ^= 1u;
-    if (!ok) break;
-    if (tid == 0 && j + 1 < nkv) load_tile(&tmV, sV, bar_v, (j + 1) * TILE);
-    if (warp == 0) __syncwarp();
-    tc_fence_after();
-    ATTN_PROF(5);
-#pragma unroll
-    for (int c = 0; c < DPAD / 32; ++c) {
-      uint32_t acc[32];
-      tmem_ld_32x32(t_out + c * 32, acc);
-      tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 32; ++x) o_acc[c * 32 + x] = fmaf(o_acc[c * 32 + x], alpha, __uint_as_float(acc[x]));
-    }
-    ATTN_PROF(6);
-    tc_fence_before();  // the block barrier inside the next wait_all orders these reads before the next products
+    if (ok && nkv > 0) ok = wait_warp(bar_o, 0);  // the last P.V
+    if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
   }
 
-  if (ok) {
-    // merge the two groups' partial states through shared memory (every product has completed: K, V and P are free)
+  // every product has completed (or a wait ran out): K, V and P are free for the merge of the two groups' states
+  const bool all_ok = __syncthreads_and(ok) != 0;
+  if (all_ok) {
+    tc_fence_after();
     float* xch = reinterpret_cast<float*>(sm.gen + tile_bytes) + row * (DPAD + 2);
-    if (grp == 1) {
+    float o_acc[DPAD];
+    if (!issuer) {  // uniform per warp: the output row of this thread's group
+#pragma unroll
+      for (int c = 0; c < DPAD / 32; ++c) {
+        uint32_t acc[32];
+        if (nkv > 0) {
+          tmem_ld_32x32(t_out + c * 32, acc);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) acc[x] = 0u;
+        }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) o_acc[c * 32 + x] = __uint_as_float(acc[x]);
+      }
+    }
+    if (!issuer && grp == 1) {
 #pragma unroll
       for (int x = 0; x < DPAD; ++x) xch[x] = o_acc[x];
       xch[DPAD] = m_run;
       xch[DPAD + 1] = l_run;
     }
     __syncthreads();
-    if (grp == 0 && q_row < p.Sq) {
+    if (!issuer && grp == 0 && q_row < p.Sq) {
       const float m_b = xch[DPAD], l_b = xch[DPAD + 1];
       const float m_all = fmaxf(m_run, m_b);
       const float m_use = m_all == -INFINITY ? 0.f : m_all;
@@ -455,7 +475,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_all > 0.f ? m_all + log2f(l_all) : INFINITY;
     }
   } else {
-    if (tid == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) {
     }
@@ -1049,7 +1068,7 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
     return LEANFFN_ERR_DRIVER;
   const attn::Params p = attn::make_params(d);
   const int dc = (d->head_dim + 63) / 64;
-  const size_t smem = 3 * dc * attn::BOX_BYTES + attn::PS_BYTES + 64 + 1024;
+  const size_t smem = 4 * dc * attn::BOX_BYTES + attn::PS_BYTES + 64 + 1024;
   const dim3 grid((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
   cudaError_t e;
 #define ATTN_FWD(DPAD)                                                             \
@@ -1114,16 +1133,6 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
 #undef ATTN_BWD
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
 }
-
-#ifdef LEANFFN_ATTN_PROFILE
-extern "C" int32_t leanffn_attention_profile(long long* out16) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, attn::g_attn_prof, sizeof(long long) * 16);
-  long long zero[16] = {0};
-  cudaMemcpyToSymbol(attn::g_attn_prof, zero, sizeof(zero));
-  return 0;
-}
-#endif
 
 extern "C" int32_t leanffn_rotary(const void* x, int32_t x_dtype, int64_t ld_x, const float* cos_table,
                                   const float* sin_table, int64_t ld_table, void* y, int32_t y_dtype, int64_t ld_y,
