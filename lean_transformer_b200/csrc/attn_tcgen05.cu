@@ -207,12 +207,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
   const uint32_t tile_bytes = DC * BOX_BYTES;
-  const uint32_t sQ = sm.base, sK0 = sQ + tile_bytes, sV = sK0 + 2 * tile_bytes, sP = sV + tile_bytes;
-  const uint32_t bar0 = sP + PS_BYTES;
-  const uint32_t bar_q = bar0, bar_k0 = bar0 + 8 /* 2 */, bar_v = bar0 + 24, bar_s = bar0 + 32, bar_o = bar0 + 40;
-  const uint32_t bar_p = bar0 + 48, tmem_slot = bar0 + 56;
-  uint8_t* gP = sm.gen + 4 * tile_bytes;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gP + PS_BYTES + 56);
+  const uint32_t sQ = sm.base, sK0 = sQ + tile_bytes, sV0 = sK0 + 2 * tile_bytes;
+  const uint32_t bar0 = sV0 + 2 * tile_bytes;
+  const uint32_t bar_q = bar0, bar_k0 = bar0 + 8 /* 2 */, bar_v0 = bar0 + 24 /* 2 */, bar_s = bar0 + 40, bar_o = bar0 + 48;
+  const uint32_t bar_p = bar0 + 56, tmem_slot = bar0 + 64;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 5 * tile_bytes + 64);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = (warp >> 2) & 1, row = tid & 127;
@@ -233,7 +232,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_q, 1);
     mbar_init(bar_k0, 1);
     mbar_init(bar_k0 + 8, 1);
-    mbar_init(bar_v, 1);
+    mbar_init(bar_v0, 1);
+    mbar_init(bar_v0 + 8, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     mbar_init(bar_p, FWD_COMPUTE_WARPS);
@@ -285,7 +285,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       load_tile(&tmQ, sQ, bar_q, qt * TILE);
       load_tile(&tmK, sK0, bar_k0, 0);
       if (nkv > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, TILE);
-      load_tile(&tmV, sV, bar_v, 0);
+      load_tile(&tmV, sV0, bar_v0, 0);
       bool go = mbar_wait_bounded(bar_q, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
       if (go) {
         tc_fence_after();
@@ -293,24 +293,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       for (int j = 0; j < nkv && go; ++j) {
         go = mbar_wait_bounded(bar_p, j & 1, limit);  // P_j is in shared memory, S_j has been read, O_g rescaled
-        if (go) go = mbar_wait_bounded(bar_v, j & 1, limit);
+        if (go) go = mbar_wait_bounded(bar_v0 + 8 * (j & 1), (j >> 1) & 1, limit);
         if (!go) break;
         tc_fence_after();
+        const uint32_t sV = sV0 + (j & 1) * tile_bytes;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {  // O_g += P_g . V_g over the group's 64 keys, the two chains interleaved
 #pragma unroll
           for (int g = 0; g < 2; ++g)
-            umma_bf16(tmem + 128 + g * OCOLS, make_smem_desc(sP + g * BOX_BYTES + ks * 32u, k_major_hi),
-                      make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+            umma_bf16_tmem_a(tmem + 128 + g * OCOLS, tmem + g * 64 + ks * 8,
+                             make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
         if (j + 1 < nkv) {
           go = mbar_wait_bounded(bar_k0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, limit);  // requested a tile ago
           if (!go) break;
-          issue_s(j + 1);
+          issue_s(j + 1);  // executes behind the products above, which read P_j from the columns it overwrites
           if (j + 2 < nkv) load_tile(&tmK, sK0 + (j & 1) * tile_bytes, bar_k0 + 8 * (j & 1), (j + 2) * TILE);  // K_j is free
-          go = mbar_wait_bounded(bar_s, (j + 1) & 1, limit);  // S_{j+1} complete: so is P.V of tile j, V_j is free
-          if (!go) break;
-          load_tile(&tmV, sV, bar_v, (j + 1) * TILE);
+          // the compute warps saw S_j complete before they arrived on bar_p: P.V of tile j - 1 is complete, its V free
+          load_tile(&tmV, sV0 + ((j + 1) & 1) * tile_bytes, bar_v0 + 8 * ((j + 1) & 1), (j + 1) * TILE);
         } else {
           umma_commit(bar_o);  // the last product: the output rows are complete
         }
@@ -400,18 +400,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int x = 0; x < 32; ++x) v[x] *= f[x];
         }
+        // P as the A operand in tensor memory: two bf16 per column, over the score columns this group has read already
+        uint32_t packed[16];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 w;
-          w.x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-          w.y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-          w.z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-          w.w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
-          *reinterpret_cast<uint4*>(gP + ps_offset(row, grp * 8 + c * 4 + q4)) = w;
-        }
+        for (int x = 0; x < 16; ++x) packed[x] = pack_bf16x2(v[2 * x], v[2 * x + 1]);
+        tmem_st_32x16(t_row + grp * 64 + c * 16, packed);
       }
       l_run += row_sum;
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
@@ -1068,7 +1064,7 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
     return LEANFFN_ERR_DRIVER;
   const attn::Params p = attn::make_params(d);
   const int dc = (d->head_dim + 63) / 64;
-  const size_t smem = 4 * dc * attn::BOX_BYTES + attn::PS_BYTES + 64 + 1024;
+  const size_t smem = 5 * dc * attn::BOX_BYTES + 128 + 1024;
   const dim3 grid((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
   cudaError_t e;
 #define ATTN_FWD(DPAD)                                                             \
