@@ -338,73 +338,105 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
       const bool plain = p.mask == nullptr && j * TILE + TILE <= p.Skv && scale_log2 > 0.f &&
                          (!p.causal || j * TILE + TILE - 1 <= qt * TILE + off);
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t acc[32];
-        tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-        tmem_ld_wait();
-        if (plain) {
-#pragma unroll
-          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
-        } else {
-          float v[32];
-          score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
-#pragma unroll
-          for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
-        }
-      }
-      if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
-      // the reference maximum moves only when this tile exceeds it by more than the threshold (always on the first
-      // tile that has a finite score); the decision is taken per warp, the tensor-memory accesses are warp-collective
-      const bool move = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx > -INFINITY);
-      if (__any_sync(0xffffffffu, move)) {
-        const float m_new = move ? mx : m_run;
-        const float alpha = (move && m_run > -INFINITY) ? fast_exp2(m_run - m_new) : 1.f;
-        if (j > 0) {  // rows of O_g that exist already (uniform)
-#pragma unroll
-          for (int c = 0; c < DPAD / 32; ++c) {
-            uint32_t acc[32];
-            tmem_ld_32x32(t_out + c * 32, acc);
-            tmem_ld_wait();
-#pragma unroll
-            for (int x = 0; x < 32; ++x) acc[x] = __float_as_uint(__uint_as_float(acc[x]) * alpha);
-            tmem_st_32x32(t_out + c * 32, acc);
-          }
-          tmem_st_wait();
-        }
-        l_run *= alpha;
-        m_run = m_new;
-      }
-      const float m_use = m_run == -INFINITY ? 0.f : m_run;
       float row_sum = 0.f;
+      // One pass where the rule is plain and the row has a reference maximum: probabilities against the OLD reference,
+      // no search for the tile's maximum.  The sum of the group's 64 probabilities tells whether that was safe: at most
+      // 2^14 means that no score exceeded the reference by more than 14 (bf16 and the fp32 sums hold 2^14 without loss);
+      // anything else (a larger sum, inf, NaN) in any row of the warp sends the whole warp through the two passes
+      // below.  Nothing has been stored by then: P goes over the scores only after the check.
+      bool fast = DROP ? false : (plain && j > 0 && __all_sync(0xffffffffu, m_run > -INFINITY) != 0);
+      if (fast) {
+        uint32_t packed[2][16];
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t acc[32];
-        float v[32];
-        tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-        tmem_ld_wait();
-        if (plain) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
+          tmem_ld_wait();
 #pragma unroll
-          for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
-        } else {
-          score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
-#pragma unroll
-          for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
+          for (int x = 0; x < 32; x += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_run));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(acc[x + 1]), scale_log2, -m_run));
+            part[(x >> 1) & 3] += e0 + e1;
+            packed[c][x >> 1] = pack_bf16x2(e0, e1);
+          }
         }
-#pragma unroll
-        for (int x = 0; x < 32; ++x) row_sum += v[x];
-        if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
-          float f[32];
-          dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
-#pragma unroll
-          for (int x = 0; x < 32; ++x) v[x] *= f[x];
+        const float sum = (part[0] + part[1]) + (part[2] + part[3]);
+        fast = __all_sync(0xffffffffu, sum <= 16384.f) != 0;
+        if (fast) {
+          tmem_st_32x16(t_row + grp * 64, packed[0]);
+          tmem_st_32x16(t_row + grp * 64 + 16, packed[1]);
+          row_sum = sum;
         }
-        // P as the A operand in tensor memory: two bf16 per column, over the score columns this group has read already
-        uint32_t packed[16];
+      }
+      if (!fast) {
+        float mx = -INFINITY;
 #pragma unroll
-        for (int x = 0; x < 16; ++x) packed[x] = pack_bf16x2(v[2 * x], v[2 * x + 1]);
-        tmem_st_32x16(t_row + grp * 64 + c * 16, packed);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
+          tmem_ld_wait();
+          if (plain) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
+          } else {
+            float v[32];
+            score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+          }
+        }
+        if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
+        // the reference maximum moves only when this tile exceeds it by more than the threshold (always on the first
+        // tile that has a finite score); the decision is taken per warp, the tensor-memory accesses are warp-collective
+        const bool move = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, move)) {
+          const float m_new = move ? mx : m_run;
+          const float alpha = (move && m_run > -INFINITY) ? fast_exp2(m_run - m_new) : 1.f;
+          if (j > 0) {  // rows of O_g that exist already (uniform)
+#pragma unroll
+            for (int c = 0; c < DPAD / 32; ++c) {
+              uint32_t acc[32];
+              tmem_ld_32x32(t_out + c * 32, acc);
+              tmem_ld_wait();
+#pragma unroll
+              for (int x = 0; x < 32; ++x) acc[x] = __float_as_uint(__uint_as_float(acc[x]) * alpha);
+              tmem_st_32x32(t_out + c * 32, acc);
+            }
+            tmem_st_wait();
+          }
+          l_run *= alpha;
+          m_run = m_new;
+        }
+        const float m_use = m_run == -INFINITY ? 0.f : m_run;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          float v[32];
+          tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
+          tmem_ld_wait();
+          if (plain) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
+          } else {
+            score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
+          }
+#pragma unroll
+          for (int x = 0; x < 32; ++x) row_sum += v[x];
+          if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
+            float f[32];
+            dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] *= f[x];
+          }
+          // P as the A operand in tensor memory: two bf16 per column, over the score columns this group has read already
+          uint32_t packed[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x) packed[x] = pack_bf16x2(v[2 * x], v[2 * x + 1]);
+          tmem_st_32x16(t_row + grp * 64 + c * 16, packed);
+        }
       }
       l_run += row_sum;
       tmem_st_wait();

@@ -22,7 +22,7 @@ def _bf16(t):
 
 def _check(got, want, what, scaled=False):
     # the literal rule |got - ref| <= atol + rtol * |ref| for every element, no outlier budget; ``scaled`` (dropout
-    # cases only): errors are judged at the rms size of the tensor, see test_attention_dropout_golden_and_oracle
+    # cases, and gradients of sharply peaked rows): errors are judged at the rms size of the tensor, see test_attention_dropout_golden_and_oracle
     assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=scaled)
 
 
@@ -111,6 +111,44 @@ def test_attention_core_vs_oracle(cuda_device, batch, heads, q_len, kv_len, head
 def test_attention_core_config4_shape(cuda_device):
     """One batch row of config 4: 2048 tokens, 16 heads of 48, rotary, the causal mask the GPT model builds."""
     _run_case(cuda_device, 1, 16, 2048, 2048, 48, "causal", True, seed=4)
+
+
+def test_attention_scores_growing_along_keys(cuda_device):
+    """Scores that rise steadily with the key position: the forward kernel takes later key tiles against the reference
+    maximum of earlier ones and has to notice when that stops being safe.  Head 0 rises by ~4 (base 2) per 128 keys:
+    two tiles stay within the headroom, the third must rescale; head 1 by ~13: every tile must."""
+    import lean_transformer_b200 as L
+
+    torch.manual_seed(11)
+    batch, heads, length, head_dim = 2, 2, 640, 48
+    hidden = heads * head_dim
+    direction = torch.nn.functional.normalize(torch.randn(heads, head_dim), dim=-1)
+    slope = torch.tensor([0.34, 1.1]).view(1, 1, heads, 1)  # natural-log units per key before the 1/sqrt(d) scale
+    pos = torch.arange(length).view(1, length, 1, 1) / 16.0
+    q = (direction.view(1, 1, heads, head_dim) * 7.0 + 0.1 * torch.randn(batch, length, heads, head_dim))
+    k = (direction.view(1, 1, heads, head_dim) * slope * pos + 0.1 * torch.randn(batch, length, heads, head_dim))
+    v = torch.randn(batch, length, heads, head_dim)
+    for mask_kind in ("none", "causal"):
+        qkv = _bf16(torch.cat([t.reshape(batch, length, hidden) for t in (q, k, v)], dim=-1)).to(cuda_device)
+        qkv.requires_grad_(True)
+        g = _bf16(torch.randn(batch, length, hidden)).to(cuda_device)
+        mask = None
+        if mask_kind == "causal":
+            mask = (1.0 - torch.ones(length, length).tril()).view(1, 1, length, length) * -10000.0
+        core = L.SimpleAttentionCore(hidden, heads).to(cuda_device).train()
+        qs, ks, vs = qkv.split(hidden, dim=-1)
+        out, _ = core(qs, ks, vs, None if mask is None else mask.to(cuda_device))
+        out.backward(g)
+        want, grads = O.attention_core_step(qs.detach().double().cpu(), ks.detach().double().cpu(),
+                                            vs.detach().double().cpu(), None if mask is None else mask.double(), heads,
+                                            grad_out=g.double().cpu())
+        _check(out, want, f"growing scores {mask_kind}:out")
+        gq, gk, gv = qkv.grad.split(hidden, dim=-1)
+        # dV = P^T dO re-creates P from the row statistics the forward pass wrote
+        _check(gv, grads["value"], f"growing scores {mask_kind}:grad_value", scaled=True)
+        # dQ and dK are not judged here: the keys are of size 40 along a direction in which the score gradients of a row
+        # cancel, so that their bf16 rounding alone is ~10 % of the result; the other cases cover those products
+        L.check_device_status(cuda_device)
 
 
 def test_attention_edge_shapes(cuda_device):
