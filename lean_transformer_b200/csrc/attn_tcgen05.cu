@@ -172,30 +172,54 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Forward.  grid = (query tiles, heads, batch).  8 compute warps + 1 issuing warp; two CTAs per SM for head_dim <= 64.
-// DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own instantiation, so that the
-// counter-based generator costs the plain kernels nothing).
+// Forward.  grid = (pairs of query tiles, heads, batch).  8 compute warps + 1 issuing warp; two CTAs per SM for
+// head_dim <= 64.  DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own instantiation, so
+// that the counter-based generator costs the plain kernels nothing).
+//
+// A CTA takes two query tiles one after the other: tile nq - 1 - x and tile x, a long and a short one under the causal
+// rule, so that every CTA has the same number of key tiles.  Its work is ONE flat sequence of steps
+// (segment, key tile): the loads and the products of the second segment follow those of the first without a drain.
 //
 // Compute warps: two thread groups of 128 (warps 0-3, warps 4-7) split the keys of every tile: group g owns keys
 // [64g, 64g + 64) of the tile for row tid % 128 -- its own reference maximum and denominator, its own half of P and
-// its own output row O_g, which stays in tensor memory for the whole loop: the products P_g . V_g accumulate there.
+// its own output row O_g, which stays in tensor memory for the whole segment: the products P_g . V_g accumulate there.
 // The reference maximum of a row only moves when a tile's maximum exceeds it by more than 2^8 (then the row of O_g
 // and the denominator are rescaled, a tensor-memory load / store); otherwise probabilities are taken against the old
-// reference and may reach 2^8, which bf16 and the fp32 sums hold without loss.  The two groups never exchange anything
-// inside the loop; their partial states are merged once at the end.  Lane 0 of the issuing warp requests every tile
-// (TMA) and issues every product: issuing blocks while the tensor cores' queue is full, so that thread does nothing
-// else, and products complete in issue order, so "S_{j+1} is complete" also tells the compute warps that P.V of tile j
-// is (P_j is free, O_g is up to date).
+// reference.  P replaces the scores in tensor memory (two bf16 per column) and is the A operand of P . V from there.
+// The two groups never exchange anything inside a segment; at its end they exchange their (maximum, denominator)
+// pairs through shared memory and each writes half of the columns of the merged output row, reading both O_g.
+// Lane 0 of the issuing warp requests every tile (TMA) and issues every product: issuing blocks while the tensor
+// cores' queue is full, so that thread does nothing else, and a commit covers everything issued before it, so
+// "S of step t + 1 is complete" also tells the compute warps that P.V of step t is (O_g is up to date).
 //
-// Per key tile j:  compute: wait S_j -> maximum -> (rescale O_g) -> P = exp2(S - m) -> shared memory -> 8 arrivals on bar_p
-//                  issuer:  wait bar_p -> P.V of tile j into O_g -> S_{j+1} -> request K_{j+2}; once S_{j+1} is complete,
-//                           request V_{j+1}
+// Per step t:  compute: wait S_t -> [first step of the second segment: write out the first] -> P = exp2(S - m) over S
+//                       -> 8 arrivals on bar_p
+//              issuer:  wait bar_p -> P.V of step t into O_g -> S_{t+1} -> request K_{t+2}, V_{t+1}
 // Hand-overs are mbarriers with bounded waits only; the second CTA on the SM fills the gaps that remain.
-// Shared memory: Q, 2 x K, V (DC boxes each, DC = ceil(head_dim / 64)), P (2 boxes: one per group), barriers.
-// TMEM: columns [0, 128) S; then one block of OCOLS columns per group for O_g.
+// Shared memory: 2 x Q, 2 x K, 2 x V (DC boxes each, DC = ceil(head_dim / 64)), barriers, (maximum, denominator) pairs.
+// TMEM: columns [0, 128) S / P; then one block of OCOLS columns per group for O_g.
 constexpr int FWD_COMPUTE_WARPS = 8;
 constexpr int FWD_THREADS = 32 * (FWD_COMPUTE_WARPS + 1);
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+constexpr uint32_t FWD_TAIL_BYTES = 128 + 4096;  // barriers and the TMEM slot; 2 segments x 2 groups x 128 x (m, l)
+
+__device__ __forceinline__ void compute_warps_sync() {  // the 256 compute threads, not the issuing warp
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+__device__ __forceinline__ bool compute_warps_all(bool pred) {  // same barrier, AND of the predicate
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 256, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
 
 template <int DPAD, bool DROP>
 __global__ void __launch_bounds__(FWD_THREADS, DPAD <= 64 ? 2 : 1)
@@ -207,36 +231,33 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
   const uint32_t tile_bytes = DC * BOX_BYTES;
-  const uint32_t sQ = sm.base, sK0 = sQ + tile_bytes, sV0 = sK0 + 2 * tile_bytes;
+  const uint32_t sQ0 = sm.base, sK0 = sQ0 + 2 * tile_bytes, sV0 = sK0 + 2 * tile_bytes;
   const uint32_t bar0 = sV0 + 2 * tile_bytes;
-  const uint32_t bar_q = bar0, bar_k0 = bar0 + 8 /* 2 */, bar_v0 = bar0 + 24 /* 2 */, bar_s = bar0 + 40, bar_o = bar0 + 48;
-  const uint32_t bar_p = bar0 + 56, tmem_slot = bar0 + 64;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 5 * tile_bytes + 64);
+  const uint32_t bar_q0 = bar0 /* 2 */, bar_k0 = bar0 + 16 /* 2 */, bar_v0 = bar0 + 32 /* 2 */, bar_s = bar0 + 48;
+  const uint32_t bar_o = bar0 + 56, bar_p = bar0 + 64, tmem_slot = bar0 + 72;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 6 * tile_bytes + 72);
+  float2* ml_all = reinterpret_cast<float2*>(sm.gen + 6 * tile_bytes + 128);  // [segment][group][row]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = (warp >> 2) & 1, row = tid & 127;
   const bool issuer = warp == FWD_COMPUTE_WARPS;
   const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + TILE - 1) / TILE;
-  const int qt = nq - 1 - static_cast<int>(blockIdx.x);  // long (late) rows first under the causal rule
   const int h = blockIdx.y, b = blockIdx.z;
   const int off = p.Skv - p.Sq;
-  int nkv = nkv_all;
-  if (p.causal) {
+  auto key_tiles = [&](int qt) {
+    if (!p.causal) return nkv_all;
     const int last_q = min(qt * TILE + TILE - 1, p.Sq - 1);
     const int last_k = last_q + off;  // largest key any row of the tile may see
-    nkv = last_k < 0 ? 0 : min(nkv_all, last_k / TILE + 1);
-  }
+    return last_k < 0 ? 0 : min(nkv_all, last_k / TILE + 1);
+  };
+  const int qt_first = nq - 1 - static_cast<int>(blockIdx.x), qt_second = static_cast<int>(blockIdx.x);
+  const int nseg = qt_second < qt_first ? 2 : 1;  // the middle tile of an odd count is alone
+  const int n0 = key_tiles(qt_first), n1 = nseg == 2 ? key_tiles(qt_second) : 0;
+  const int steps = n0 + n1;
   const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
 
   if (tid == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(bar_k0, 1);
-    mbar_init(bar_k0 + 8, 1);
-    mbar_init(bar_v0, 1);
-    mbar_init(bar_v0 + 8, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
-    mbar_init(bar_p, FWD_COMPUTE_WARPS);
+    for (int i = 0; i < 9; ++i) mbar_init(bar0 + 8 * i, i == 8 ? FWD_COMPUTE_WARPS : 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -254,11 +275,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t t_out = t_row + 128 + grp * OCOLS;
   bool ok = true;
 
-  const int q_row = qt * TILE + row;
-  float m_run = -INFINITY, l_run = 0.f;
-
   if (issuer) {
-    if (lane == 0 && nkv > 0) {
+    if (lane == 0 && steps > 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
       constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
@@ -267,10 +285,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mbar_arrive_expect_tx(bar, tile_bytes);
         for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
       };
-      // S_j = Q . K_j^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
+      auto key_row = [&](int t) { return (t < n0 ? t : t - n0) * TILE; };
+      // S_t = Q . K^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
       // 128 x 16 block of Q once more per instruction, and the operand feed is what bounds these products)
-      auto issue_s = [&](int j) {
-        const uint32_t sK = sK0 + (j & 1) * tile_bytes;
+      auto issue_s = [&](int t) {
+        const uint32_t sQ = sQ0 + (t < n0 ? 0u : tile_bytes);
+        const uint32_t sK = sK0 + (t & 1) * tile_bytes;
         const int ksteps = p.d >> 4;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -282,35 +302,38 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(bar_s);
       };
-      load_tile(&tmQ, sQ, bar_q, qt * TILE);
-      load_tile(&tmK, sK0, bar_k0, 0);
-      if (nkv > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, TILE);
-      load_tile(&tmV, sV0, bar_v0, 0);
-      bool go = mbar_wait_bounded(bar_q, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
+      if (n0 > 0) load_tile(&tmQ, sQ0, bar_q0, qt_first * TILE);
+      load_tile(&tmK, sK0, bar_k0, key_row(0));
+      load_tile(&tmV, sV0, bar_v0, key_row(0));
+      if (steps > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, key_row(1));
+      if (n1 > 0) load_tile(&tmQ, sQ0 + tile_bytes, bar_q0 + 8, qt_second * TILE);
+      bool go = mbar_wait_bounded(n0 > 0 ? bar_q0 : bar_q0 + 8, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
       if (go) {
         tc_fence_after();
         issue_s(0);
       }
-      for (int j = 0; j < nkv && go; ++j) {
-        go = mbar_wait_bounded(bar_p, j & 1, limit);  // P_j is in shared memory, S_j has been read, O_g rescaled
-        if (go) go = mbar_wait_bounded(bar_v0 + 8 * (j & 1), (j >> 1) & 1, limit);
+      for (int t = 0; t < steps && go; ++t) {
+        go = mbar_wait_bounded(bar_p, t & 1, limit);  // P_t is in tensor memory, S_t has been read, O_g rescaled
+        if (go) go = mbar_wait_bounded(bar_v0 + 8 * (t & 1), (t >> 1) & 1, limit);
         if (!go) break;
         tc_fence_after();
-        const uint32_t sV = sV0 + (j & 1) * tile_bytes;
+        const uint32_t sV = sV0 + (t & 1) * tile_bytes;
+        const bool first = t == 0 || t == n0;  // of its segment: O_g starts from zero
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {  // O_g += P_g . V_g over the group's 64 keys, the two chains interleaved
 #pragma unroll
           for (int g = 0; g < 2; ++g)
             umma_bf16_tmem_a(tmem + 128 + g * OCOLS, tmem + g * 64 + ks * 8,
-                             make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+                             make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, (!first || ks > 0) ? 1u : 0u);
         }
-        if (j + 1 < nkv) {
-          go = mbar_wait_bounded(bar_k0 + 8 * ((j + 1) & 1), ((j + 1) >> 1) & 1, limit);  // requested a tile ago
+        if (t + 1 < steps) {
+          go = mbar_wait_bounded(bar_k0 + 8 * ((t + 1) & 1), ((t + 1) >> 1) & 1, limit);  // requested a step ago
+          if (go && t + 1 == n0) go = mbar_wait_bounded(bar_q0 + 8, 0, limit);            // requested at the start
           if (!go) break;
-          issue_s(j + 1);  // executes behind the products above, which read P_j from the columns it overwrites
-          if (j + 2 < nkv) load_tile(&tmK, sK0 + (j & 1) * tile_bytes, bar_k0 + 8 * (j & 1), (j + 2) * TILE);  // K_j is free
-          // the compute warps saw S_j complete before they arrived on bar_p: P.V of tile j - 1 is complete, its V free
-          load_tile(&tmV, sV0 + ((j + 1) & 1) * tile_bytes, bar_v0 + 8 * ((j + 1) & 1), (j + 1) * TILE);
+          issue_s(t + 1);  // executes behind the products above, which read P_t from the columns it overwrites
+          if (t + 2 < steps) load_tile(&tmK, sK0 + (t & 1) * tile_bytes, bar_k0 + 8 * (t & 1), key_row(t + 2));  // K_t is free
+          // the compute warps saw S_t complete before they arrived on bar_p: P.V of step t - 1 is complete, its V free
+          load_tile(&tmV, sV0 + ((t + 1) & 1) * tile_bytes, bar_v0 + 8 * ((t + 1) & 1), key_row(t + 1));
         } else {
           umma_commit(bar_o);  // the last product: the output rows are complete
         }
@@ -319,21 +342,74 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     __syncwarp();
   } else {
-    const int q_clamped = min(q_row, p.Sq - 1);
-    const float* mask_row = p.mask == nullptr ? nullptr
-                                              : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
     const float scale_log2 = p.scale * LOG2E;
-    const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
-    const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
     const bool drop_aligned = ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0;  // uniform: every chunk starts a Philox group
     auto wait_warp = [&](uint32_t bar, uint32_t parity) {  // the whole warp continues or the whole warp leaves
       return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, limit)) != 0;
     };
-    for (int j = 0; j < nkv; ++j) {
-      // S_j complete; products complete in issue order, so P.V of tile j - 1 is complete too
-      ok = wait_warp(bar_s, j & 1);
+    float m_run = -INFINITY, l_run = 0.f;
+    // End of a segment: the two groups' partial states of a row are merged; group g writes columns
+    // [g DPAD / 2, (g + 1) DPAD / 2) of the output, reading both O_0 and O_1 (same lanes of tensor memory).
+    auto write_out = [&](int seg, bool have_rows) {
+      float2* ml = ml_all + seg * 256;
+      ml[grp * 128 + row] = make_float2(m_run, l_run);
+      compute_warps_sync();
+      const float2 other = ml[(grp ^ 1) * 128 + row];
+      const float m_all = fmaxf(m_run, other.x);
+      const float m_use = m_all == -INFINITY ? 0.f : m_all;
+      const float w_own = exp2f(m_run - m_use), w_other = exp2f(other.x - m_use);
+      const float l_all = l_run * w_own + other.y * w_other;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      const float f_own = w_own * inv, f_other = w_other * inv;
+      const int q_row = (seg == 0 ? qt_first : qt_second) * TILE + row;
+      bf16* dst = p.out + (static_cast<int64_t>(b) * p.Sq + q_row) * p.ld_out + static_cast<int64_t>(h) * p.d;
+#pragma unroll
+      for (int c = 0; c < DPAD / 32; ++c) {
+        const int col = grp * (DPAD / 2) + c * 16;
+        uint32_t own[16], oth[16];
+        if (have_rows) {  // uniform
+          tmem_ld_32x16(t_row + 128 + grp * OCOLS + col, own);
+          tmem_ld_32x16(t_row + 128 + (grp ^ 1) * OCOLS + col, oth);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) own[x] = oth[x] = 0u;
+        }
+        if (q_row < p.Sq && col < p.d) {
+          uint4 w[2];
+          uint32_t* wp = reinterpret_cast<uint32_t*>(w);
+#pragma unroll
+          for (int x = 0; x < 8; ++x)
+            wp[x] = pack_bf16x2(__uint_as_float(own[2 * x]) * f_own + __uint_as_float(oth[2 * x]) * f_other,
+                                __uint_as_float(own[2 * x + 1]) * f_own + __uint_as_float(oth[2 * x + 1]) * f_other);
+          *reinterpret_cast<uint4*>(dst + col) = w[0];
+          *reinterpret_cast<uint4*>(dst + col + 8) = w[1];
+        }
+      }
+      // rows that saw no key at all get +inf so that the backward pass turns their probabilities into zeros
+      if (grp == 0 && q_row < p.Sq)
+        p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_all > 0.f ? m_all + log2f(l_all) : INFINITY;
+      m_run = -INFINITY;
+      l_run = 0.f;
+    };
+    if (n0 == 0) write_out(0, false);  // a first segment whose rows see no key (more queries than keys, causal)
+    bool mid_done = !(n0 > 0 && n1 > 0);  // the first segment is written out from inside the loop
+    for (int t = 0; t < steps; ++t) {
+      // S_t complete; a commit covers everything issued before it, so P.V of step t - 1 is complete too
+      ok = wait_warp(bar_s, t & 1);
       if (!ok) break;
       tc_fence_after();
+      const int seg = t < n0 ? 0 : 1, j = t - seg * n0, qt = seg == 0 ? qt_first : qt_second;
+      if (seg == 1 && j == 0 && n0 > 0) {
+        write_out(0, true);
+        mid_done = true;
+      }
+      const int q_row = qt * TILE + row;
+      const int q_clamped = min(q_row, p.Sq - 1);
+      const float* mask_row = p.mask == nullptr ? nullptr
+                                                : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
+      const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
+      const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
       const int k0 = j * TILE + grp * 64;
       // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
       const bool plain = p.mask == nullptr && j * TILE + TILE <= p.Skv && scale_log2 > 0.f &&
@@ -444,65 +520,26 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p);
     }
-    if (ok && nkv > 0) ok = wait_warp(bar_o, 0);  // the last P.V
+    if (ok && steps > 0) ok = wait_warp(bar_o, 0);  // the last P.V
     if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
+    // the merge has a barrier among the compute warps: if a wait ran out in any of them, all skip it (a warp that
+    // left the loop before the barrier inside it makes up for that one first, so that the counts agree)
+    if (!mid_done) compute_warps_sync();
+    ok = compute_warps_all(ok);
+    if (ok) {
+      tc_fence_after();
+      if (nseg == 1) {
+        if (n0 > 0) write_out(0, true);
+      } else if (n1 > 0) {
+        write_out(1, true);
+      } else {
+        if (n0 > 0) write_out(0, true);
+        write_out(1, false);
+      }
+    }
   }
 
-  // every product has completed (or a wait ran out): K, V and P are free for the merge of the two groups' states
-  const bool all_ok = __syncthreads_and(ok) != 0;
-  if (all_ok) {
-    tc_fence_after();
-    float* xch = reinterpret_cast<float*>(sm.gen + tile_bytes) + row * (DPAD + 2);
-    float o_acc[DPAD];
-    if (!issuer) {  // uniform per warp: the output row of this thread's group
-#pragma unroll
-      for (int c = 0; c < DPAD / 32; ++c) {
-        uint32_t acc[32];
-        if (nkv > 0) {
-          tmem_ld_32x32(t_out + c * 32, acc);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int x = 0; x < 32; ++x) acc[x] = 0u;
-        }
-#pragma unroll
-        for (int x = 0; x < 32; ++x) o_acc[c * 32 + x] = __uint_as_float(acc[x]);
-      }
-    }
-    if (!issuer && grp == 1) {
-#pragma unroll
-      for (int x = 0; x < DPAD; ++x) xch[x] = o_acc[x];
-      xch[DPAD] = m_run;
-      xch[DPAD + 1] = l_run;
-    }
-    __syncthreads();
-    if (!issuer && grp == 0 && q_row < p.Sq) {
-      const float m_b = xch[DPAD], l_b = xch[DPAD + 1];
-      const float m_all = fmaxf(m_run, m_b);
-      const float m_use = m_all == -INFINITY ? 0.f : m_all;
-      const float wa = exp2f(m_run - m_use), wb = exp2f(m_b - m_use);
-      const float l_all = l_run * wa + l_b * wb;
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      const float fa = wa * inv, fb = wb * inv;
-      bf16* dst = p.out + (static_cast<int64_t>(b) * p.Sq + q_row) * p.ld_out + static_cast<int64_t>(h) * p.d;
-#pragma unroll
-      for (int x = 0; x < DPAD; x += 8) {
-        if (x < p.d) {
-          float r[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) r[i] = o_acc[x + i] * fa + xch[x + i] * fb;
-          uint4 w;
-          w.x = pack_bf16x2(r[0], r[1]);
-          w.y = pack_bf16x2(r[2], r[3]);
-          w.z = pack_bf16x2(r[4], r[5]);
-          w.w = pack_bf16x2(r[6], r[7]);
-          *reinterpret_cast<uint4*>(dst + x) = w;
-        }
-      }
-      // rows that saw no key at all get +inf so that the backward pass turns their probabilities into zeros
-      p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_all > 0.f ? m_all + log2f(l_all) : INFINITY;
-    }
-  } else {
+  if (__syncthreads_and(ok) == 0) {  // a wait ran out: leave time for what is in flight before tensor memory goes back
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) {
     }
@@ -1096,8 +1133,9 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
     return LEANFFN_ERR_DRIVER;
   const attn::Params p = attn::make_params(d);
   const int dc = (d->head_dim + 63) / 64;
-  const size_t smem = 5 * dc * attn::BOX_BYTES + 128 + 1024;
-  const dim3 grid((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
+  const size_t smem = 6 * dc * attn::BOX_BYTES + attn::FWD_TAIL_BYTES + 1024;
+  const int q_tiles = (d->q_len + attn::TILE - 1) / attn::TILE;
+  const dim3 grid((q_tiles + 1) / 2, d->heads, d->batch);  // a CTA takes query tiles x and q_tiles - 1 - x
   cudaError_t e;
 #define ATTN_FWD(DPAD)                                                             \
   {                                                                                \
