@@ -199,7 +199,7 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 // Shared memory: 2 x Q, 2 x K, 2 x V (DC boxes each, DC = ceil(head_dim / 64)), barriers, (maximum, denominator) pairs.
 // TMEM: columns [0, 128) S / P; then one block of OCOLS columns per group for O_g.
 constexpr int FWD_COMPUTE_WARPS = 8;
-constexpr int FWD_THREADS = 32 * (FWD_COMPUTE_WARPS + 1);
+constexpr int FWD_THREADS = 32 * (FWD_COMPUTE_WARPS + 2);  // + the issuing warp and the loading warp
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 constexpr uint32_t FWD_TAIL_BYTES = 128 + 4096;  // barriers and the TMEM slot; 2 segments x 2 groups x 128 x (m, l)
 
@@ -240,7 +240,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = (warp >> 2) & 1, row = tid & 127;
-  const bool issuer = warp == FWD_COMPUTE_WARPS;
+  const bool issuer = warp == FWD_COMPUTE_WARPS, loader = warp == FWD_COMPUTE_WARPS + 1;
   const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + TILE - 1) / TILE;
   const int h = blockIdx.y, b = blockIdx.z;
   const int off = p.Skv - p.Sq;
@@ -281,11 +281,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
       constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
       constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
-      auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
-        mbar_arrive_expect_tx(bar, tile_bytes);
-        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
-      };
-      auto key_row = [&](int t) { return (t < n0 ? t : t - n0) * TILE; };
       // S_t = Q . K^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
       // 128 x 16 block of Q once more per instruction, and the operand feed is what bounds these products)
       auto issue_s = [&](int t) {
@@ -302,11 +297,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(bar_s);
       };
-      if (n0 > 0) load_tile(&tmQ, sQ0, bar_q0, qt_first * TILE);
-      load_tile(&tmK, sK0, bar_k0, key_row(0));
-      load_tile(&tmV, sV0, bar_v0, key_row(0));
-      if (steps > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, key_row(1));
-      if (n1 > 0) load_tile(&tmQ, sQ0 + tile_bytes, bar_q0 + 8, qt_second * TILE);
       bool go = mbar_wait_bounded(n0 > 0 ? bar_q0 : bar_q0 + 8, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
       if (go) {
         tc_fence_after();
@@ -331,14 +321,38 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (go && t + 1 == n0) go = mbar_wait_bounded(bar_q0 + 8, 0, limit);            // requested at the start
           if (!go) break;
           issue_s(t + 1);  // executes behind the products above, which read P_t from the columns it overwrites
-          if (t + 2 < steps) load_tile(&tmK, sK0 + (t & 1) * tile_bytes, bar_k0 + 8 * (t & 1), key_row(t + 2));  // K_t is free
-          // the compute warps saw S_t complete before they arrived on bar_p: P.V of step t - 1 is complete, its V free
-          load_tile(&tmV, sV0 + ((t + 1) & 1) * tile_bytes, bar_v0 + 8 * ((t + 1) & 1), key_row(t + 1));
         } else {
           umma_commit(bar_o);  // the last product: the output rows are complete
         }
       }
       if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
+    }
+    __syncwarp();
+  } else if (loader) {
+    // Lane 0 requests every tile as soon as its buffer is free: a request costs the requesting thread a few hundred
+    // clocks and the tile takes a microsecond or two to arrive, so neither belongs on the issuing thread's path.
+    if (lane == 0 && steps > 0) {
+      auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
+        mbar_arrive_expect_tx(bar, tile_bytes);
+        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+      };
+      auto key_row = [&](int t) { return (t < n0 ? t : t - n0) * TILE; };
+      if (n0 > 0) load_tile(&tmQ, sQ0, bar_q0, qt_first * TILE);
+      load_tile(&tmK, sK0, bar_k0, key_row(0));
+      load_tile(&tmV, sV0, bar_v0, key_row(0));
+      if (steps > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, key_row(1));
+      if (n1 > 0) load_tile(&tmQ, sQ0 + tile_bytes, bar_q0 + 8, qt_second * TILE);
+      bool go = true;
+      for (int t = 0; t + 1 < steps && go; ++t) {
+        // S_t complete: K_t is free; a commit covers everything issued before it, so P.V of step t - 1 is complete
+        // too and the other V buffer is free.  (This thread cannot fall two steps behind: S_{t+2} needs the K
+        // requested here.)
+        go = mbar_wait_bounded(bar_s, t & 1, limit);
+        if (!go) break;
+        if (t + 2 < steps) load_tile(&tmK, sK0 + (t & 1) * tile_bytes, bar_k0 + 8 * (t & 1), key_row(t + 2));
+        load_tile(&tmV, sV0 + ((t + 1) & 1) * tile_bytes, bar_v0 + 8 * ((t + 1) & 1), key_row(t + 1));
+      }
+      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_PRODUCER);
     }
     __syncwarp();
   } else {
