@@ -609,11 +609,6 @@ def quick_measure(wl, device, args, name=""):
                                         "fp32 (TF32x3 tensor cores)" if wl.get("fp32") else "bf16")))
 
 
-def N_lib():
-    from lean_transformer_b200 import _native
-    return _native.lib
-
-
 def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=20, warmup=3):
     """The attention core of the 12-layer GPT configuration (hidden 768, 16 heads, 32 x 2048 tokens) on its own: rotary + causal attention over batch x seq tokens, heads x
     head_dim (this package's RotaryAttentionCore: leanffn_rotary + leanffn_attention_forward / backward), forward +
@@ -683,18 +678,8 @@ def attention_measure(device, batch=32, seq=2048, heads=16, head_dim=48, steps=2
         library = dict(forward_ms=lib_fwd, forward_backward_ms=lib_both)
     except Exception as e:  # context only
         library = dict(unavailable=f"{type(e).__name__}: {e}")
-    phase_clocks = None
-    if hasattr(N_lib(), "leanffn_attention_profile"):  # measurement builds (-DLEANFFN_ATTN_PROFILE) only
-        import ctypes
-        buf = (ctypes.c_longlong * 16)()
-        N_lib().leanffn_attention_profile(buf)
-        ops.attention_forward(q, k, v, heads, scale, None, True)
-        N_lib().leanffn_attention_profile(buf)
-        tiles = (seq + 127) // 128
-        phase_clocks = dict(kernel="attention_fwd_kernel, block (0, 0, 0): SM clocks per key tile",
-                            slots=[int(x) // tiles for x in buf[:8]])
     return dict(tokens_per_s=batch * seq / s, ms_per_step=s * 1e3, tflops=achieved, steps=steps, warmup=warmup,
-                forward_kernel_ms=fwd_ms, backward_kernels_ms=bwd_ms, library_sdpa=library, phase_clocks=phase_clocks,
+                forward_kernel_ms=fwd_ms, backward_kernels_ms=bwd_ms, library_sdpa=library,
                 gpu_launches_per_step=launches_per_step,
                 roofline=dict(bound="tensor", achieved=achieved, peak=peaks["bf16_sustained"], unit="TFLOP/s",
                               frac=achieved / peaks["bf16_sustained"], traffic=None,
