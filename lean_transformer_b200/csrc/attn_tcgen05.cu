@@ -624,6 +624,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   constexpr bool PIPE = DPAD <= 64;
   constexpr int NBUF = PIPE ? 2 : 1;
   constexpr uint32_t COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
+  constexpr uint32_t COL_DS = 448;  // PIPE only: dS as the tensor-memory A operand of dQ (two bf16 per column)
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = align_smem(smem_raw);
   const int DC = (p.d + 63) >> 6;
@@ -633,6 +634,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t bar0 = sdS + PS_BYTES;
   const uint32_t bar_kv = bar0, bar_a = bar0 + 8, bar_b = bar0 + 16, bar_dq = bar0 + 24, bar_pds = bar0 + 32;
   const uint32_t bar_drain = bar0 + 40, bar_q0 = bar0 + 48 /* NBUF barriers */, bar_stage = bar0 + 64, tmem_slot = bar0 + 72;
+  const uint32_t bar_dst = bar0 + 80;  // PIPE only: dS is in tensor memory
   uint8_t* gP = sm.gen + (2 + 2 * NBUF) * tile_bytes;
   uint8_t* gdS = gP + PS_BYTES;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 72);
@@ -661,6 +663,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_pds, BWD_COMPUTE_WARPS);
     mbar_init(bar_drain, BWD_COMPUTE_WARPS);
     mbar_init(bar_stage, BWD_COMPUTE_WARPS);
+    mbar_init(bar_dst, BWD_COMPUTE_WARPS);
     for (int n = 0; n < NBUF; ++n) mbar_init(bar_q0 + 8 * n, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -710,9 +713,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       auto issue_dq = [&]() {  // dQ[q, x] = sum_key dS[q, key] * K[key, x]: first, the compute warps wait for it
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-          umma_bf16(tmem + COL_DQ, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi),
-                    idesc_q, ks > 0 ? 1u : 0u);
+          if constexpr (PIPE) {  // dS from tensor memory: the product does not wait for the copy in shared memory
+            umma_bf16_tmem_a(tmem + COL_DQ, tmem + COL_DS + ks * 8, make_smem_desc(sK + ks * 2048u, mn_major_hi),
+                             idesc_q, ks > 0 ? 1u : 0u);
+          } else {
+            const uint32_t oa = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
+            umma_bf16(tmem + COL_DQ, make_smem_desc(sdS + oa, k_major_hi), make_smem_desc(sK + ks * 2048u, mn_major_hi),
+                      idesc_q, ks > 0 ? 1u : 0u);
+          }
         }
         umma_commit(bar_dq);
       };
@@ -743,7 +751,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int n = 0; n < n_iter && go; ++n) {
         const int i = i_start + n;
         const int buf = PIPE ? (n & 1) : 0;
-        go = mbar_wait_bounded(bar_pds, n & 1, limit);  // P, dS written; S, dP read; dQ of the tile before drained
+        // PIPE: dS is in tensor memory (S, dP read; dQ of the tile before drained; its staging boxes read);
+        // otherwise: P, dS written to shared memory
+        go = mbar_wait_bounded(PIPE ? bar_dst : bar_pds, n & 1, limit);
         if (!go) break;
         tc_fence_after();
         issue_dq();
@@ -756,6 +766,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (!go) break;
             issue_a(buf ^ 1);
           }
+          go = mbar_wait_bounded(bar_pds, n & 1, limit);  // P, dS are in shared memory too
+          if (!go) break;
+          tc_fence_after();
           issue_dv_dk(buf, n == 0 ? 0u : 1u);
           go = mbar_wait_bounded(bar_b, n & 1, limit);  // Q_i, dO_i consumed: their buffer takes tile i + 2
           if (!go) break;
@@ -816,7 +829,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - lse);
         }
-        uint4 wp[4], wd[4];  // this thread's 32 probabilities and 32 score gradients, packed bf16
+        uint4 wp[4];        // this thread's 32 probabilities, packed bf16
+        uint32_t wd[16];    // and its 32 score gradients
         if constexpr (DROP) {
           // dV takes the kept probabilities scaled by 1 / (1 - p); the gradient of a dropped probability is zero
           float f[32];
@@ -844,11 +858,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int x = 0; x < 32; ++x) v[x] *= __uint_as_float(dp[x]) - dlt;  // dS; the score scale is applied to dQ / dK
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          wd[q4].x = pack_bf16x2(v[8 * q4 + 0], v[8 * q4 + 1]);
-          wd[q4].y = pack_bf16x2(v[8 * q4 + 2], v[8 * q4 + 3]);
-          wd[q4].z = pack_bf16x2(v[8 * q4 + 4], v[8 * q4 + 5]);
-          wd[q4].w = pack_bf16x2(v[8 * q4 + 6], v[8 * q4 + 7]);
+        for (int x = 0; x < 16; ++x) wd[x] = pack_bf16x2(v[2 * x], v[2 * x + 1]);
+        if constexpr (PIPE) {
+          // dS into tensor memory as the A operand of dQ_i = dS . K: that product starts now, not after the copies below
+          tmem_st_32x16(t_row + COL_DS + c * 16, wd);
+          tmem_st_wait();
+          tc_fence_before();
+          // the staging boxes of the tile before must have been read by the TMA unit before this arrival lets dQ_i
+          // (and with it the next staging writes) start
+          if (tid == 0) bulk_wait_group_read0();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_dst);
         }
         // P and dS of the tile before are operands of its dV / dK products until bar_b completes
         if (n > 0) ok = wait_warp(bar_b, (n - 1) & 1);
@@ -857,16 +877,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int q4 = 0; q4 < 4; ++q4) {
             const uint32_t o = ps_offset(row, c * 4 + q4);
             *reinterpret_cast<uint4*>(gP + o) = wp[q4];
-            *reinterpret_cast<uint4*>(gdS + o) = wd[q4];
+            *reinterpret_cast<uint4*>(gdS + o) = make_uint4(wd[4 * q4], wd[4 * q4 + 1], wd[4 * q4 + 2], wd[4 * q4 + 3]);
           }
         }
       }
       if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before();
-      // the staging area of the tile before must have been read by the TMA unit before this arrival lets the next dQ
-      // products (and with them the next staging writes) start
-      if (PIPE && tid == 0) bulk_wait_group_read0();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pds);
 
