@@ -614,7 +614,7 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 // TMEM (512 columns): [0, 128) S; [128, 256) dP; PIPE: [256, 320) dV, [320, 384) dK, [384, 448) dQ;
 //                     otherwise [256, 384) dV, [384, 512) dK, dQ in [0, 128).
 constexpr int BWD_COMPUTE_WARPS = 16;
-constexpr int BWD_THREADS = 32 * (BWD_COMPUTE_WARPS + 1);
+constexpr int BWD_THREADS = 32 * (BWD_COMPUTE_WARPS + 2);  // + the issuing warp and the copy warp
 
 template <int DPAD, bool DROP>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -635,6 +635,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t bar_kv = bar0, bar_a = bar0 + 8, bar_b = bar0 + 16, bar_dq = bar0 + 24, bar_pds = bar0 + 32;
   const uint32_t bar_drain = bar0 + 40, bar_q0 = bar0 + 48 /* NBUF barriers */, bar_stage = bar0 + 64, tmem_slot = bar0 + 72;
   const uint32_t bar_dst = bar0 + 80;  // PIPE only: dS is in tensor memory
+  const uint32_t bar_sfree = bar0 + 88;  // PIPE only: the TMA unit has read the staging boxes
   uint8_t* gP = sm.gen + (2 + 2 * NBUF) * tile_bytes;
   uint8_t* gdS = gP + PS_BYTES;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 72);
@@ -643,7 +644,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int chunk = warp >> 2, row = tid & 127;
-  const bool issuer = warp == BWD_COMPUTE_WARPS;
+  const bool issuer = warp == BWD_COMPUTE_WARPS, copier = warp == BWD_COMPUTE_WARPS + 1;
   const int nq = (p.Sq + TILE - 1) / TILE;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int off = p.Skv - p.Sq;
@@ -664,6 +665,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_drain, BWD_COMPUTE_WARPS);
     mbar_init(bar_stage, BWD_COMPUTE_WARPS);
     mbar_init(bar_dst, BWD_COMPUTE_WARPS);
+    mbar_init(bar_sfree, 1);
     for (int n = 0; n < NBUF; ++n) mbar_init(bar_q0 + 8 * n, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -685,15 +687,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (issuer) {
     if (lane == 0 && n_iter > 0) {
-      auto load_boxes = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
-        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
-      };
-      auto load_q_do = [&](int i, int buf) {
-        const uint32_t bar = bar_q0 + 8 * buf, dst = sQ0 + 2 * buf * tile_bytes;
-        mbar_arrive_expect_tx(bar, 2 * tile_bytes);
-        load_boxes(&tmQ, dst, bar, i * TILE);
-        load_boxes(&tmdO, dst + tile_bytes, bar, i * TILE);
-      };
       const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S and dP: both operands K-major
       const uint32_t idesc_t = make_idesc_bf16(128, p.d, true, true);     // dV, dK: P^T / dS^T (MN-major A), MN-major B
       const uint32_t idesc_q = make_idesc_bf16(128, p.d, false, true);    // dQ: dS K-major, K_j MN-major
@@ -738,22 +731,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         umma_commit(bar_b);
       };
 
-      mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
-      load_boxes(&tmK, sK, bar_kv, kt * TILE);
-      load_boxes(&tmV, sV, bar_kv, kt * TILE);
-      load_q_do(i_start, 0);
-      if (PIPE && n_iter > 1) load_q_do(i_start + 1, 1);
       bool go = mbar_wait_bounded(bar_kv, 0, limit) && mbar_wait_bounded(bar_q0, 0, limit);
       if (go) {
         tc_fence_after();
         issue_a(0);
       }
       for (int n = 0; n < n_iter && go; ++n) {
-        const int i = i_start + n;
         const int buf = PIPE ? (n & 1) : 0;
         // PIPE: dS is in tensor memory (S, dP read; dQ of the tile before drained; its staging boxes read);
         // otherwise: P, dS written to shared memory
         go = mbar_wait_bounded(PIPE ? bar_dst : bar_pds, n & 1, limit);
+        // PIPE: the staging boxes of the tile before have been read (dQ_i will be written there)
+        if (PIPE && go && n > 0) go = mbar_wait_bounded(bar_sfree, (n - 1) & 1, limit);
         if (!go) break;
         tc_fence_after();
         issue_dq();
@@ -770,16 +759,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           if (!go) break;
           tc_fence_after();
           issue_dv_dk(buf, n == 0 ? 0u : 1u);
-          go = mbar_wait_bounded(bar_b, n & 1, limit);  // Q_i, dO_i consumed: their buffer takes tile i + 2
-          if (!go) break;
-          if (n + 2 < n_iter) load_q_do(i + 2, buf);
         } else {
           issue_dv_dk(buf, n == 0 ? 0u : 1u);
         }
         if (!PIPE && n + 1 < n_iter) {
-          go = mbar_wait_bounded(bar_b, n & 1, limit);
-          if (!go) break;
-          load_q_do(i + 1, 0);
           // dQ_i lives in the S columns: the next scores wait until the compute warps have drained it
           go = mbar_wait_bounded(bar_drain, n & 1, limit) && mbar_wait_bounded(bar_q0, (n + 1) & 1, limit);
           if (!go) break;
@@ -788,6 +771,49 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
       }
       if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
+    }
+    __syncwarp();
+  } else if (copier) {
+    // Lane 0 does every TMA request: the loads (K, V once; Q / dO per tile as soon as their buffer is free) and, PIPE,
+    // the reductions of the staged dQ tiles.  A request costs the requesting thread a few hundred clocks, which
+    // neither the issuing thread nor a compute warp has to spare.
+    if (lane == 0 && n_iter > 0) {
+      auto load_boxes = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
+        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
+      };
+      auto load_q_do = [&](int i, int buf) {
+        const uint32_t bar = bar_q0 + 8 * buf, dst = sQ0 + 2 * buf * tile_bytes;
+        mbar_arrive_expect_tx(bar, 2 * tile_bytes);
+        load_boxes(&tmQ, dst, bar, i * TILE);
+        load_boxes(&tmdO, dst + tile_bytes, bar, i * TILE);
+      };
+      mbar_arrive_expect_tx(bar_kv, 2 * tile_bytes);
+      load_boxes(&tmK, sK, bar_kv, kt * TILE);
+      load_boxes(&tmV, sV, bar_kv, kt * TILE);
+      load_q_do(i_start, 0);
+      if (PIPE && n_iter > 1) load_q_do(i_start + 1, 1);
+      bool go = true;
+      for (int n = 0; n < n_iter && go; ++n) {
+        const int i = i_start + n;
+        if (PIPE) {
+          go = mbar_wait_bounded(bar_stage, n & 1, limit);  // all 16 warps have written their rows of dQ_i
+          if (!go) break;
+          for (int c = 0; c * 32 < p.d; ++c) tma_reduce_add_4d(&tmdQ, s_stage + c * BOX_BYTES, c * 32, h, i * TILE, b);
+          bulk_commit_group();
+          bulk_wait_group_read0();
+          mbar_arrive(bar_sfree);  // dQ_{i+1} may be issued: its read-out writes the boxes again
+        }
+        // dV / dK of tile i complete (and with them everything issued before): Q_i, dO_i are free.  (This thread
+        // cannot fall two tiles behind: those products of a later tile need the Q / dO requested here.)
+        const int next = PIPE ? n + 2 : n + 1;
+        if (next < n_iter) {
+          go = mbar_wait_bounded(bar_b, n & 1, limit);
+          if (!go) break;
+          load_q_do(i_start + next, PIPE ? (n & 1) : 0);
+        }
+      }
+      if (PIPE) bulk_wait_group0();  // the reductions of this block have been performed
+      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_PRODUCER);
     }
     __syncwarp();
   } else {
@@ -864,9 +890,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tmem_st_32x16(t_row + COL_DS + c * 16, wd);
           tmem_st_wait();
           tc_fence_before();
-          // the staging boxes of the tile before must have been read by the TMA unit before this arrival lets dQ_i
-          // (and with it the next staging writes) start
-          if (tid == 0) bulk_wait_group_read0();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_dst);
         }
@@ -907,16 +930,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_stage);
-        if (warp == 0) {  // one thread hands the staged tile to the TMA unit once all 16 warps have written their rows
-          ok = wait_warp(bar_stage, n & 1);
-          if (!ok) break;
-          if (lane == 0) {
-            for (int c = 0; c * 32 < p.d; ++c) tma_reduce_add_4d(&tmdQ, s_stage + c * BOX_BYTES, c * 32, h, i * TILE, b);
-            bulk_commit_group();
-          }
-          __syncwarp();
-        }
+        if (lane == 0) mbar_arrive(bar_stage);  // the copy warp hands the staged tile to the TMA unit
       } else {
         float* dst = p.dq_acc + (static_cast<int64_t>(b) * p.Sq + q_clamped) * (static_cast<int64_t>(p.H) * p.d) +
                      static_cast<int64_t>(h) * p.d;
@@ -981,7 +995,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
     }
   }
-  if (PIPE && tid == 0) bulk_wait_group0();  // the reductions of this block have been performed
   // teardown: after a timeout give copies and products still in flight time to land before the memory is released
   if (!__syncthreads_and(ok)) {
     const long long t0 = clock64();
