@@ -622,7 +622,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                      const __grid_constant__ CUtensorMap tmdQ, const Params p) {
   constexpr bool PIPE = DPAD <= 64;
-  constexpr int NBUF = PIPE ? 2 : 1;
+  constexpr int NBUF = PIPE ? 3 : 1;
   constexpr uint32_t COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
   constexpr uint32_t COL_DS = 448;  // PIPE only: dS as the tensor-memory A operand of dQ (two bf16 per column)
   extern __shared__ uint8_t smem_raw[];
@@ -633,9 +633,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t sP = sQ0 + 2 * NBUF * tile_bytes, sdS = sP + PS_BYTES;
   const uint32_t bar0 = sdS + PS_BYTES;
   const uint32_t bar_kv = bar0, bar_a = bar0 + 8, bar_b = bar0 + 16, bar_dq = bar0 + 24, bar_pds = bar0 + 32;
-  const uint32_t bar_drain = bar0 + 40, bar_q0 = bar0 + 48 /* NBUF barriers */, bar_stage = bar0 + 64, tmem_slot = bar0 + 72;
+  const uint32_t bar_drain = bar0 + 40, bar_q0 = bar0 + 96 /* NBUF barriers */, bar_stage = bar0 + 64, tmem_slot = bar0 + 72;
   const uint32_t bar_dst = bar0 + 80;  // PIPE only: dS is in tensor memory
   const uint32_t bar_sfree = bar0 + 88;  // PIPE only: the TMA unit has read the staging boxes
+  const uint32_t bar_sread = bar0 + 48;  // PIPE only: S and dP of this tile are in registers
   uint8_t* gP = sm.gen + (2 + 2 * NBUF) * tile_bytes;
   uint8_t* gdS = gP + PS_BYTES;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gdS + PS_BYTES + 72);
@@ -666,6 +667,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar_stage, BWD_COMPUTE_WARPS);
     mbar_init(bar_dst, BWD_COMPUTE_WARPS);
     mbar_init(bar_sfree, 1);
+    mbar_init(bar_sread, BWD_COMPUTE_WARPS);
     for (int n = 0; n < NBUF; ++n) mbar_init(bar_q0 + 8 * n, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -737,9 +739,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         issue_a(0);
       }
       for (int n = 0; n < n_iter && go; ++n) {
-        const int buf = PIPE ? (n & 1) : 0;
-        // PIPE: dS is in tensor memory (S, dP read; dQ of the tile before drained; its staging boxes read);
-        // otherwise: P, dS written to shared memory
+        const int buf = PIPE ? n % NBUF : 0;
+        if (PIPE && n + 1 < n_iter) {
+          // the next tile's scores go first: as soon as the compute warps hold S_i and dP_i in registers the columns
+          // are free, and Q / dO of tile i + 1 were requested three tiles ago.  The compute warps then never wait
+          // for scores: S_{i+1}, dP_{i+1} complete while they work on tile i.
+          const int nb = (n + 1) % NBUF;
+          go = mbar_wait_bounded(bar_sread, n & 1, limit) &&
+               mbar_wait_bounded(bar_q0 + 8 * nb, ((n + 1) / NBUF) & 1, limit);
+          if (!go) break;
+          tc_fence_after();
+          issue_a(nb);
+        }
+        // PIPE: dS is in tensor memory (dQ of the tile before drained); otherwise: P, dS written to shared memory
         go = mbar_wait_bounded(PIPE ? bar_dst : bar_pds, n & 1, limit);
         // PIPE: the staging boxes of the tile before have been read (dQ_i will be written there)
         if (PIPE && go && n > 0) go = mbar_wait_bounded(bar_sfree, (n - 1) & 1, limit);
@@ -747,21 +759,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tc_fence_after();
         issue_dq();
         if (PIPE) {
-          // the next tile's scores go in front of this tile's dV / dK products: S and dP have been read, and the
-          // compute warps can take the exponentials of tile i + 1 while dV / dK of tile i run (they keep the new P
-          // and dS in registers until bar_b says the old ones are no longer operands)
-          if (n + 1 < n_iter) {
-            go = mbar_wait_bounded(bar_q0 + 8 * (buf ^ 1), ((n + 1) >> 1) & 1, limit);
-            if (!go) break;
-            issue_a(buf ^ 1);
-          }
+          // the compute warps keep the new P and dS in registers until bar_b says the old ones are no longer operands
           go = mbar_wait_bounded(bar_pds, n & 1, limit);  // P, dS are in shared memory too
           if (!go) break;
           tc_fence_after();
-          issue_dv_dk(buf, n == 0 ? 0u : 1u);
-        } else {
-          issue_dv_dk(buf, n == 0 ? 0u : 1u);
         }
+        issue_dv_dk(buf, n == 0 ? 0u : 1u);
         if (!PIPE && n + 1 < n_iter) {
           // dQ_i lives in the S columns: the next scores wait until the compute warps have drained it
           go = mbar_wait_bounded(bar_drain, n & 1, limit) && mbar_wait_bounded(bar_q0, (n + 1) & 1, limit);
@@ -792,6 +795,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       load_boxes(&tmV, sV, bar_kv, kt * TILE);
       load_q_do(i_start, 0);
       if (PIPE && n_iter > 1) load_q_do(i_start + 1, 1);
+      if (PIPE && n_iter > 2) load_q_do(i_start + 2, 2);
       bool go = true;
       for (int n = 0; n < n_iter && go; ++n) {
         const int i = i_start + n;
@@ -805,11 +809,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         // dV / dK of tile i complete (and with them everything issued before): Q_i, dO_i are free.  (This thread
         // cannot fall two tiles behind: those products of a later tile need the Q / dO requested here.)
-        const int next = PIPE ? n + 2 : n + 1;
+        const int next = PIPE ? n + NBUF : n + 1;
         if (next < n_iter) {
           go = mbar_wait_bounded(bar_b, n & 1, limit);
           if (!go) break;
-          load_q_do(i_start + next, PIPE ? (n & 1) : 0);
+          load_q_do(i_start + next, PIPE ? n % NBUF : 0);
         }
       }
       if (PIPE) bulk_wait_group0();  // the reductions of this block have been performed
@@ -845,6 +849,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld_32x32(t_row + c * 32, acc);
         tmem_ld_32x32(t_row + 128 + c * 32, dp);
         tmem_ld_wait();
+        if constexpr (PIPE) {  // the score columns are free for the next tile
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_sread);
+        }
         // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
         const bool plain = p.mask == nullptr && k0 + TILE <= p.Skv && (!p.causal || k0 + TILE - 1 <= i * TILE + off);
         if (plain) {
@@ -1221,7 +1230,7 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
   const int dc = (d->head_dim + 63) / 64;
   // head_dim <= 64: double-buffered Q / dO and the dQ staging boxes ([128 x 32] fp32 each)
   const int dpad = (d->head_dim + 31) / 32 * 32;
-  const size_t smem = (dc == 1 ? 6 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 1024 + 1024 +
+  const size_t smem = (dc == 1 ? 8 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 1024 + 1024 +
                       (dc == 1 ? (dpad / 32) * attn::BOX_BYTES : 0);
   CUtensorMap tdq;
   if (!make_tmap_f32_heads(&tdq, d->dq_accum, d->batch, d->q_len, d->heads, d->head_dim)) return LEANFFN_ERR_DRIVER;
