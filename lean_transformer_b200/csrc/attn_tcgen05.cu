@@ -592,26 +592,30 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, int64_t l
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Backward.  grid = (key tiles, heads, batch).  16 compute warps + 1 issuing warp.
+// Backward.  grid = (key tiles, heads, batch).  16 compute warps + an issuing warp + a copy warp.
 //
 // Compute warps: four threads per row, thread group c = warp / 4 owns the 32 columns [32c, 32c + 32) of every
 // 128-column accumulator row (no reduction across the threads of a row is needed: the row statistics lse and delta are
-// inputs).  Lane 0 of the issuing warp requests every tile (TMA) and issues every product; issuing blocks while the
-// tensor cores' queue is full, so this thread does nothing else and the compute warps never wait for it to come back.
+// inputs).  Lane 0 of the issuing warp issues every product; issuing blocks while the tensor cores' queue is full, so
+// this thread does nothing else.  Lane 0 of the copy warp makes every TMA request (K, V once; Q / dO per tile as soon
+// as a buffer is free; the reductions of the staged dQ tiles): a request costs its thread a few hundred clocks.
 //
 // Per query tile i:  group A(i) = {S = Q_i . K^T, dP = dO_i . V^T}          -> bar_a
 //                    elementwise(i): P = exp2(S - lse), dS = P * (dP - delta) -> shared memory, 16 arrivals on bar_pds
 //                    group B(i) = {dQ_i = dS . K -> bar_dq;  dV += P^T . dO_i, dK += dS^T . Q_i -> bar_b}
 //                    read-out(i): dQ_i * scale added to the fp32 gradient in global memory -> 16 arrivals on bar_drain
-// The only hand-overs are mbarriers with bounded waits: no block-wide barrier inside the loop.  Order on the tensor cores
-// for head_dim <= 64: A(i), dQ(i), A(i + 1), dV/dK(i), dQ(i + 1), ...: while dV/dK(i) run, the compute warps hand dQ_i
-// to the TMA unit and take the exponentials of tile i + 1; they hold the new P / dS in registers until bar_b says the
-// old ones are no longer operands.
-// head_dim <= 64 (PIPE): Q / dO double-buffered and fetched two tiles ahead, dQ has its own TMEM columns and is
-// handed to the TMA unit through shared memory ([128 x 32] fp32 boxes, cp.reduce.async.bulk.tensor .add).
-// head_dim > 64: one Q / dO buffer; dQ_i reuses the S columns, so A(i + 1) waits for the read-out (bar_drain).
+// The only hand-overs are mbarriers with bounded waits: no block-wide barrier inside the loop.
+// head_dim <= 64 (PIPE): three Q / dO buffers fetched three tiles ahead.  The compute warps say so (bar_sread) as soon
+// as S_i and dP_i are in their registers, and A(i + 1) is issued right then: they never wait for scores.  dS goes to
+// tensor memory first (two bf16 per column, bar_dst) and is the A operand of dQ_i from there, so that product runs
+// while P and dS are copied to shared memory for dV / dK (the copies wait for bar_b of the tile before: the old P / dS
+// are operands until then).  dQ has its own TMEM columns and is handed to the TMA unit through shared memory
+// ([128 x 32] fp32 boxes, cp.reduce.async.bulk.tensor .add; bar_stage: boxes written, bar_sfree: boxes read).
+// Order on the tensor cores: A(i + 1), dQ(i), dV/dK(i), A(i + 2), ...
+// head_dim > 64: one Q / dO buffer; dS from shared memory; dQ_i reuses the S columns, so A(i + 1) waits for the
+// read-out (bar_drain).
 // Shared memory: K, V, NBUF x (Q, dO) (DC boxes each), P, dS (2 boxes each), PIPE: dQ staging (DPAD / 32 boxes).
-// TMEM (512 columns): [0, 128) S; [128, 256) dP; PIPE: [256, 320) dV, [320, 384) dK, [384, 448) dQ;
+// TMEM (512 columns): [0, 128) S; [128, 256) dP; PIPE: [256, 320) dV, [320, 384) dK, [384, 448) dQ, [448, 512) dS;
 //                     otherwise [256, 384) dV, [384, 512) dK, dQ in [0, 128).
 constexpr int BWD_COMPUTE_WARPS = 16;
 constexpr int BWD_THREADS = 32 * (BWD_COMPUTE_WARPS + 2);  // + the issuing warp and the copy warp
@@ -1228,7 +1232,7 @@ extern "C" int32_t leanffn_attention_backward(const leanffn_attention_desc* d, v
   e = cudaGetLastError();
   if (e != cudaSuccess) return 1000 + static_cast<int32_t>(e);
   const int dc = (d->head_dim + 63) / 64;
-  // head_dim <= 64: double-buffered Q / dO and the dQ staging boxes ([128 x 32] fp32 each)
+  // head_dim <= 64: three Q / dO buffers and the dQ staging boxes ([128 x 32] fp32 each)
   const int dpad = (d->head_dim + 31) / 32 * 32;
   const size_t smem = (dc == 1 ? 8 : 4) * dc * attn::BOX_BYTES + 2 * attn::PS_BYTES + 1024 + 1024 +
                       (dc == 1 ? (dpad / 32) * attn::BOX_BYTES : 0);
