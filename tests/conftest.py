@@ -96,7 +96,7 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, rtol: float, atol: float,
                  branch: torch.Tensor = None, outlier_frac: float = 0.0, outlier_cap: float = 4.0):
     """|got - ref| <= atol * max(1, S) + rtol * max(|ref|, |branch|, S), elementwise.
 
-    With S = 0 and no branch this is torch.allclose's rule.  The two extensions judge an element at the scale
+    With S = 0 and no branch this is torch.allclose's rule.  The two extensions check an element at the scale
     of the computation that produced it rather than at the size it happens to end up with:
 
     ``scale_atol``: S = rms of the GEMM-produced tensor (``branch`` if given, else ``ref``).  A matrix product
@@ -104,7 +104,7 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, rtol: float, atol: float,
     the accumulated sums, also for the elements whose terms cancel to ~0.
 
     ``branch``: where a residual is added exactly (out = x + branch, dx = g + branch'), the reference value of
-    the computed branch; an output that cancels against the residual is judged at the branch's size.
+    the computed branch; an output that cancels against the residual is checked at the branch's size.
 
     ``outlier_frac``: up to this fraction of the elements may exceed the bound, none by more than ``outlier_cap``
     times.  Used only where the recorded noise floor of stock PyTorch arithmetic shows the same tails."""

@@ -22,7 +22,7 @@ def _bf16(t):
 
 def _check(got, want, what, scaled=False):
     # the literal rule |got - ref| <= atol + rtol * |ref| for every element, no outlier budget; ``scaled`` (dropout
-    # cases, and gradients of sharply peaked rows): errors are judged at the rms size of the tensor, see test_attention_dropout_golden_and_oracle
+    # cases, and gradients of sharply peaked rows): errors are checked at the rms size of the tensor, see test_attention_dropout_golden_and_oracle
     assert_close(got.float().cpu(), want.float(), BF16_RTOL, BF16_ATOL, what, scale_atol=scaled)
 
 
@@ -146,7 +146,7 @@ def test_attention_scores_growing_along_keys(cuda_device):
         gq, gk, gv = qkv.grad.split(hidden, dim=-1)
         # dV = P^T dO re-creates P from the row statistics the forward pass wrote
         _check(gv, grads["value"], f"growing scores {mask_kind}:grad_value", scaled=True)
-        # dQ and dK are not judged here: the keys are of size 40 along a direction in which the score gradients of a row
+        # dQ and dK are not checked here: the keys are of size 40 along a direction in which the score gradients of a row
         # cancel, so that their bf16 rounding alone is ~10 % of the result; the other cases cover those products
         L.check_device_status(cuda_device)
 

@@ -4,7 +4,7 @@ Tolerances: fp32 mode rtol = atol = 1e-4; bf16 mode rtol 2e-2 / atol 1e-2, appli
 conftest.assert_close: |got - ref| <= atol * max(1, S) + rtol * max(|ref|, |branch|, S), where S is the rms of
 the GEMM-produced tensor and ``branch`` the computed part of a residual sum.  Every checked quantity is the
 output of matrix products over 10^2..10^4 terms; the rounding noise of such a sum is set by the rms of the sums,
-also for the elements that cancel to ~0 (or cancel against the residual), so those are judged at that scale.
+also for the elements that cancel to ~0 (or cancel against the residual), so those are checked at that scale.
 """
 import pytest
 import torch
@@ -27,7 +27,7 @@ def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None, residual
         x, g = (t.detach().double().cpu().reshape(ref_out.shape) for t in residual)
         out_branch, dx_branch = ref_out.double() - x, ref_grads["input"].double().reshape(ref_out.shape) - g
     if rtol >= 1e-2:
-        # bf16: elements are judged at the scale of the sums that produced them.  Stock PyTorch bf16 arithmetic leaves
+        # bf16: elements are checked at the scale of the sums that produced them.  Stock PyTorch bf16 arithmetic leaves
         # up to 1e-5 of the elements beyond that bound (worst 1.6x), the kernels fewer: budget 1e-4, none beyond 2x.
         rule = dict(scale_atol=True, outlier_frac=1e-4, outlier_cap=2.0)
     elif literal:
@@ -39,7 +39,7 @@ def _check(out, grads, ref_out, ref_grads, rtol, atol, param_rtol=None, residual
     else:
         # fp32 mode in general: same rule as bf16 with rtol = atol = 1e-4 and no outliers.  Where sums of hundreds of
         # terms cancel to ~0 the literal rule is below the rounding noise of ANY fp32 summation (an exact-FMA fp32
-        # product misses it by 3x on a 515-term sum with entries up to 235), so elements are judged at the scale S.
+        # product misses it by 3x on a 515-term sum with entries up to 235), so elements are checked at the scale S.
         rule = dict(scale_atol=True)
     tag = f"{label}:" if label else ""
     assert_close(out, ref_out, rtol, atol, f"{tag}out", branch=out_branch, **rule)

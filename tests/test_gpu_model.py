@@ -87,7 +87,7 @@ def test_tiny_gpt_swapped_ffn_matches_reference_bf16(cuda_device):
     assert sum(isinstance(m, L.RotaryAttentionCore) for m in model.modules()) >= 1
     got = _run(model, ids, autocast=True)
     # Through four layers the rounding noise of bf16 arithmetic compounds (the reference's own autocast run misses the
-    # single-layer bound on some tensors by 1.7x), so each tensor is judged against that run: the swapped model's
+    # single-layer bound on some tensors by 1.7x), so each tensor is checked against that run: the swapped model's
     # rms distance from the fp32 run may be at most twice the reference-autocast run's, and no element may lie
     # beyond 3x the single-layer bound.
     assert abs(got[1] - want[1]) <= BF16_ATOL + BF16_RTOL * abs(want[1])
