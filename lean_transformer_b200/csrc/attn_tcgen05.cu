@@ -30,7 +30,7 @@
 namespace leanffn {
 
 bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int64_t len, int64_t heads,
-                          int64_t head_dim, int64_t ld);
+                          int64_t head_dim, int64_t ld, int box_rows = 128);
 bool make_tmap_f32_heads(CUtensorMap* out, void* base, int64_t batch, int64_t len, int64_t heads, int64_t head_dim);
 
 namespace attn {
@@ -550,6 +550,300 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (n0 > 0) write_out(0, true);
         write_out(1, false);
       }
+    }
+  }
+
+  if (__syncthreads_and(ok) == 0) {  // a wait ran out: leave time for what is in flight before tensor memory goes back
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Forward for head_dim <= 64, 64 keys per step: FOUR CTAs per SM.  grid = (query tiles, heads, batch), late (long)
+// query tiles first.  One step of a CTA is a chain of hand-overs (scores complete -> exponentials -> arrive -> issue ->
+// commit) whose latencies a CTA cannot hide from itself; what hides them is more CTAs per SM.  Half as many keys per
+// step halves everything a CTA holds: 128 TMEM columns (64 S / P, 64 O), 48 KB of shared memory (Q, 2 x K, 2 x V of
+// 64 rows), 4 compute warps (one thread per query row, all 64 keys of the step) + the issuing warp + the loading warp.
+// The rules are those of the kernel above: O stays in tensor memory and is rescaled only when the reference maximum
+// moves (by more than 2^8); P goes over the scores as the tensor-memory A operand of P . V; plain tiles take one pass
+// against the old reference, checked by the row sum; all hand-overs are mbarriers with bounded waits.
+constexpr int KSTEP = 64;
+constexpr int FWD64_COMPUTE_WARPS = 4;
+constexpr int FWD64_THREADS = 32 * (FWD64_COMPUTE_WARPS + 2);
+constexpr uint32_t KV_BOX_BYTES = KSTEP * 128;  // 64 rows of 128 bytes
+
+template <int DPAD, bool DROP>
+__global__ void __launch_bounds__(FWD64_THREADS, 4)
+attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const Params p) {
+  static_assert(DPAD <= 64, "one 64-column box per tile");
+  constexpr uint32_t TMEM_COLS = 128, COL_O = 64;
+  extern __shared__ uint8_t smem_raw[];
+  const Smem sm = align_smem(smem_raw);
+  const uint32_t sQ = sm.base, sK0 = sQ + BOX_BYTES, sV0 = sK0 + 2 * KV_BOX_BYTES;
+  const uint32_t bar0 = sV0 + 2 * KV_BOX_BYTES;
+  const uint32_t bar_q = bar0, bar_k0 = bar0 + 8 /* 2 */, bar_v0 = bar0 + 24 /* 2 */, bar_s = bar0 + 40;
+  const uint32_t bar_o = bar0 + 48, bar_p = bar0 + 56, tmem_slot = bar0 + 64;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(sm.gen + BOX_BYTES + 4 * KV_BOX_BYTES + 64);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = tid & 127;
+  const bool issuer = warp == FWD64_COMPUTE_WARPS, loader = warp == FWD64_COMPUTE_WARPS + 1;
+  const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + KSTEP - 1) / KSTEP;
+  const int qt = nq - 1 - static_cast<int>(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int off = p.Skv - p.Sq;
+  int steps = nkv_all;
+  if (p.causal) {
+    const int last_q = min(qt * TILE + TILE - 1, p.Sq - 1);
+    const int last_k = last_q + off;  // largest key any row of the tile may see
+    steps = last_k < 0 ? 0 : min(nkv_all, last_k / KSTEP + 1);
+  }
+  const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
+
+  if (tid == 0) {
+    for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8 * i, i == 7 ? FWD64_COMPUTE_WARPS : 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_ptr;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
+  const uint32_t t_out = t_row + COL_O;
+  bool ok = true;
+
+  if (issuer) {
+    if (lane == 0 && steps > 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, KSTEP, false, false);
+      const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
+      constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
+      constexpr uint64_t mn_major_hi = make_smem_desc_hi(KV_BOX_BYTES, 1024);
+      auto issue_s = [&](int t) {  // S_t = Q . K_t^T: 64 columns, one product per 16 columns of the head
+        const uint32_t sK = sK0 + (t & 1) * KV_BOX_BYTES;
+        const int ksteps = p.d >> 4;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          if (ks < ksteps)
+            umma_bf16(tmem, make_smem_desc(sQ + ks * 32u, k_major_hi), make_smem_desc(sK + ks * 32u, k_major_hi), idesc_s,
+                      ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s);
+      };
+      bool go = mbar_wait_bounded(bar_q, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
+      if (go) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int t = 0; t < steps && go; ++t) {
+        go = mbar_wait_bounded(bar_p, t & 1, limit);  // P_t is in tensor memory, S_t has been read, O rescaled
+        if (go) go = mbar_wait_bounded(bar_v0 + 8 * (t & 1), (t >> 1) & 1, limit);
+        if (!go) break;
+        tc_fence_after();
+        const uint32_t sV = sV0 + (t & 1) * KV_BOX_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)  // O += P . V_t over the 64 keys
+          umma_bf16_tmem_a(tmem + COL_O, tmem + ks * 8, make_smem_desc(sV + ks * 2048u, mn_major_hi), idesc_o,
+                           (t > 0 || ks > 0) ? 1u : 0u);
+        if (t + 1 < steps) {
+          go = mbar_wait_bounded(bar_k0 + 8 * ((t + 1) & 1), ((t + 1) >> 1) & 1, limit);  // requested a step ago
+          if (!go) break;
+          issue_s(t + 1);  // executes behind the products above, which read P_t from the columns it overwrites
+        } else {
+          umma_commit(bar_o);  // the last product: the output rows are complete
+        }
+      }
+      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
+    }
+    __syncwarp();
+  } else if (loader) {
+    if (lane == 0 && steps > 0) {
+      auto load_kv = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int t) {
+        mbar_arrive_expect_tx(bar, KV_BOX_BYTES);
+        tma_load_4d(dst, m, bar, 0, h, t * KSTEP, b);
+      };
+      mbar_arrive_expect_tx(bar_q, BOX_BYTES);
+      tma_load_4d(sQ, &tmQ, bar_q, 0, h, qt * TILE, b);
+      load_kv(&tmK, sK0, bar_k0, 0);
+      load_kv(&tmV, sV0, bar_v0, 0);
+      if (steps > 1) load_kv(&tmK, sK0 + KV_BOX_BYTES, bar_k0 + 8, 1);
+      bool go = true;
+      for (int t = 0; t + 1 < steps && go; ++t) {
+        // S_t complete: K_t is free; a commit covers everything issued before it, so P.V of step t - 1 is complete
+        // too and the other V buffer is free.  (This thread cannot fall two steps behind: S_{t+2} needs the K
+        // requested here.)
+        go = mbar_wait_bounded(bar_s, t & 1, limit);
+        if (!go) break;
+        if (t + 2 < steps) load_kv(&tmK, sK0 + (t & 1) * KV_BOX_BYTES, bar_k0 + 8 * (t & 1), t + 2);
+        load_kv(&tmV, sV0 + ((t + 1) & 1) * KV_BOX_BYTES, bar_v0 + 8 * ((t + 1) & 1), t + 1);
+      }
+      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_PRODUCER);
+    }
+    __syncwarp();
+  } else {
+    const float scale_log2 = p.scale * LOG2E;
+    const bool drop_aligned = ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0;  // uniform: every chunk starts a Philox group
+    auto wait_warp = [&](uint32_t bar, uint32_t parity) {  // the whole warp continues or the whole warp leaves
+      return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, limit)) != 0;
+    };
+    const int q_row = qt * TILE + row;
+    const int q_clamped = min(q_row, p.Sq - 1);
+    const float* mask_row = p.mask == nullptr ? nullptr
+                                              : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
+    const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
+    const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
+    float m_run = -INFINITY, l_run = 0.f;
+    for (int t = 0; t < steps; ++t) {
+      // S_t complete; a commit covers everything issued before it, so P.V of step t - 1 is complete too
+      ok = wait_warp(bar_s, t & 1);
+      if (!ok) break;
+      tc_fence_after();
+      const int k0 = t * KSTEP;
+      // whole step inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
+      const bool plain = p.mask == nullptr && k0 + KSTEP <= p.Skv && scale_log2 > 0.f &&
+                         (!p.causal || k0 + KSTEP - 1 <= qt * TILE + off);
+      float row_sum = 0.f;
+      // one pass against the OLD reference maximum where the rule is plain, checked by the row sum (see the kernel above)
+      bool fast = DROP ? false : (plain && t > 0 && __all_sync(0xffffffffu, m_run > -INFINITY) != 0);
+      if (fast) {
+        uint32_t packed[2][16];
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          tmem_ld_32x32(t_row + c * 32, acc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 32; x += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_run));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(acc[x + 1]), scale_log2, -m_run));
+            part[(x >> 1) & 3] += e0 + e1;
+            packed[c][x >> 1] = pack_bf16x2(e0, e1);
+          }
+        }
+        const float sum = (part[0] + part[1]) + (part[2] + part[3]);
+        fast = __all_sync(0xffffffffu, sum <= 16384.f) != 0;
+        if (fast) {
+          tmem_st_32x16(t_row, packed[0]);
+          tmem_st_32x16(t_row + 16, packed[1]);
+          row_sum = sum;
+        }
+      }
+      if (!fast) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          tmem_ld_32x32(t_row + c * 32, acc);
+          tmem_ld_wait();
+          if (plain) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
+          } else {
+            float v[32];
+            score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+          }
+        }
+        if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
+        const bool move = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx > -INFINITY);
+        if (__any_sync(0xffffffffu, move)) {
+          const float m_new = move ? mx : m_run;
+          const float alpha = (move && m_run > -INFINITY) ? fast_exp2(m_run - m_new) : 1.f;
+          if (t > 0) {  // rows of O that exist already (uniform)
+#pragma unroll
+            for (int c = 0; c < DPAD / 32; ++c) {
+              uint32_t acc[32];
+              tmem_ld_32x32(t_out + c * 32, acc);
+              tmem_ld_wait();
+#pragma unroll
+              for (int x = 0; x < 32; ++x) acc[x] = __float_as_uint(__uint_as_float(acc[x]) * alpha);
+              tmem_st_32x32(t_out + c * 32, acc);
+            }
+            tmem_st_wait();
+          }
+          l_run *= alpha;
+          m_run = m_new;
+        }
+        const float m_use = m_run == -INFINITY ? 0.f : m_run;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t acc[32];
+          float v[32];
+          tmem_ld_32x32(t_row + c * 32, acc);
+          tmem_ld_wait();
+          if (plain) {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
+          } else {
+            score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
+          }
+#pragma unroll
+          for (int x = 0; x < 32; ++x) row_sum += v[x];
+          if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
+            float f[32];
+            dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] *= f[x];
+          }
+          uint32_t packed[16];
+#pragma unroll
+          for (int x = 0; x < 16; ++x) packed[x] = pack_bf16x2(v[2 * x], v[2 * x + 1]);
+          tmem_st_32x16(t_row + c * 16, packed);
+        }
+      }
+      l_run += row_sum;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+    }
+    if (ok && steps > 0) ok = wait_warp(bar_o, 0);  // the last P.V
+    if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* dst = p.out + (static_cast<int64_t>(b) * p.Sq + q_row) * p.ld_out + static_cast<int64_t>(h) * p.d;
+#pragma unroll
+      for (int c = 0; c < DPAD / 16; ++c) {
+        uint32_t o[16];
+        if (steps > 0) {  // uniform
+          tmem_ld_32x16(t_out + c * 16, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) o[x] = 0u;
+        }
+        if (q_row < p.Sq && c * 16 < p.d) {
+          uint4 w[2];
+          uint32_t* wp = reinterpret_cast<uint32_t*>(w);
+#pragma unroll
+          for (int x = 0; x < 8; ++x)
+            wp[x] = pack_bf16x2(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
+          *reinterpret_cast<uint4*>(dst + c * 16) = w[0];
+          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = w[1];
+        }
+      }
+      // rows that saw no key at all get +inf so that the backward pass turns their probabilities into zeros
+      if (q_row < p.Sq)
+        p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_run > 0.f ? m_run + log2f(l_run) : INFINITY;
     }
   }
 
@@ -1183,17 +1477,36 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
   const int32_t v = attn::validate(d, false);
   if (v != LEANFFN_OK) return v;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool narrow = d->head_dim <= 64;  // 64 keys per step, four CTAs per SM
   CUtensorMap tq, tk, tv;
   if (!make_tmap_bf16_heads(&tq, d->q, d->batch, d->q_len, d->heads, d->head_dim, d->ld_q) ||
-      !make_tmap_bf16_heads(&tk, d->k, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_k) ||
-      !make_tmap_bf16_heads(&tv, d->v, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_v))
+      !make_tmap_bf16_heads(&tk, d->k, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_k, narrow ? attn::KSTEP : 128) ||
+      !make_tmap_bf16_heads(&tv, d->v, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_v, narrow ? attn::KSTEP : 128))
     return LEANFFN_ERR_DRIVER;
   const attn::Params p = attn::make_params(d);
+  cudaError_t e;
+  if (narrow) {
+    const size_t smem64 = attn::BOX_BYTES + 4 * attn::KV_BOX_BYTES + 128 + 1024;
+    const dim3 grid64((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
+#define ATTN_FWD64(DPAD)                                                             \
+  {                                                                                  \
+    auto kern = p.drop_threshold != 0u ? attn::attention_fwd64_kernel<DPAD, true>    \
+                                       : attn::attention_fwd64_kernel<DPAD, false>;  \
+    e = attn::set_smem(kern, smem64);                                                \
+    if (e == cudaSuccess) {                                                          \
+      kern<<<grid64, attn::FWD64_THREADS, smem64, st>>>(tq, tk, tv, p);              \
+      e = cudaGetLastError();                                                        \
+    }                                                                                \
+  }
+    if (d->head_dim <= 32) ATTN_FWD64(32)
+    else ATTN_FWD64(64)
+#undef ATTN_FWD64
+    return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
+  }
   const int dc = (d->head_dim + 63) / 64;
   const size_t smem = 6 * dc * attn::BOX_BYTES + attn::FWD_TAIL_BYTES + 1024;
   const int q_tiles = (d->q_len + attn::TILE - 1) / attn::TILE;
   const dim3 grid((q_tiles + 1) / 2, d->heads, d->batch);  // a CTA takes query tiles x and q_tiles - 1 - x
-  cudaError_t e;
 #define ATTN_FWD(DPAD)                                                             \
   {                                                                                \
     auto kern = p.drop_threshold != 0u ? attn::attention_fwd_kernel<DPAD, true>    \

@@ -457,17 +457,17 @@ bool make_tmap_bf16(CUtensorMap* out, const void* base, int64_t rows, int64_t co
 }
 
 // 4D bf16 tensor map over a [batch, len, heads, head_dim] view: element (b, s, h, x) lies at
-// base + ((b * len + s) * ld + h * head_dim + x) * 2 bytes.  Box = 64 x 1 x 128 x 1 (head_dim, head, rows, batch),
+// base + ((b * len + s) * ld + h * head_dim + x) * 2 bytes.  Box = 64 x 1 x box_rows x 1 (head_dim, head, rows, batch),
 // 128-byte swizzle; columns beyond head_dim and rows beyond len read as zero.
 bool make_tmap_bf16_heads(CUtensorMap* out, const void* base, int64_t batch, int64_t len, int64_t heads,
-                          int64_t head_dim, int64_t ld) {
+                          int64_t head_dim, int64_t ld, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(heads),
                               static_cast<cuuint64_t>(len), static_cast<cuuint64_t>(batch)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(ld) * 2,
                                  static_cast<cuuint64_t>(len) * static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
