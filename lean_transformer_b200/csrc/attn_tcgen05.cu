@@ -172,9 +172,10 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Forward.  grid = (pairs of query tiles, heads, batch).  8 compute warps + 1 issuing warp; two CTAs per SM for
-// head_dim <= 64.  DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own instantiation, so
-// that the counter-based generator costs the plain kernels nothing).
+// Forward, 128 keys per step (used for head_dim > 64, one CTA per SM; head sizes up to 64 take the 64-key kernel
+// further down, which runs four CTAs per SM).  grid = (pairs of query tiles, heads, batch).  8 compute warps + an
+// issuing warp + a loading warp.  DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own
+// instantiation, so that the counter-based generator costs the plain kernels nothing).
 //
 // A CTA takes two query tiles one after the other: tile nq - 1 - x and tile x, a long and a short one under the causal
 // rule, so that every CTA has the same number of key tiles.  Its work is ONE flat sequence of steps
@@ -1517,9 +1518,7 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
       e = cudaGetLastError();                                                      \
     }                                                                              \
   }
-  if (d->head_dim <= 32) ATTN_FWD(32)
-  else if (d->head_dim <= 64) ATTN_FWD(64)
-  else if (d->head_dim <= 96) ATTN_FWD(96)
+  if (d->head_dim <= 96) ATTN_FWD(96)  // head sizes up to 64 took the 64-key kernel above
   else ATTN_FWD(128)
 #undef ATTN_FWD
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
