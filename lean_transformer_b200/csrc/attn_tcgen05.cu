@@ -18,6 +18,7 @@
 //                              products, the hand-overs are mbarriers.
 // Every mbarrier wait is bounded; a wait that runs out sets the status word, every role leaves its loop and TMEM is
 // freed.  Warp-collective tensor-memory loads sit behind warp-uniform conditions only.
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -172,431 +173,58 @@ __device__ __forceinline__ Smem align_smem(uint8_t* raw) {
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// Forward, 128 keys per step (used for head_dim > 64, one CTA per SM; head sizes up to 64 take the 64-key kernel
-// further down, which runs four CTAs per SM).  grid = (pairs of query tiles, heads, batch).  8 compute warps + an
-// issuing warp + a loading warp.  DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own
+// Forward.  grid = (query tiles, heads, batch), late (long) query tiles first.  A CTA takes one tile of 128 query rows
+// and walks over the keys 64 at a time; 4 compute warps (one thread per query row, all 64 keys of the step) + an issuing
+// warp + a loading warp.  DPAD = head_dim rounded up to 32; DROP = dropout on the probabilities (its own
 // instantiation, so that the counter-based generator costs the plain kernels nothing).
 //
-// A CTA takes two query tiles one after the other: tile nq - 1 - x and tile x, a long and a short one under the causal
-// rule, so that every CTA has the same number of key tiles.  Its work is ONE flat sequence of steps
-// (segment, key tile): the loads and the products of the second segment follow those of the first without a drain.
+// Why 64 keys: one step of a CTA is a chain of hand-overs (scores complete -> exponentials -> arrive -> issue -> commit)
+// whose latencies a CTA cannot hide from itself; what hides them is more CTAs per SM, and a CTA of this shape holds
+// little: 128 TMEM columns (64 S / P, 64 O) and 48 KB of shared memory (Q, 2 x K, 2 x V of 64 rows) for head_dim <= 64,
+// FOUR CTAs per SM; 256 columns and 96 KB above, two CTAs per SM.
 //
-// Compute warps: two thread groups of 128 (warps 0-3, warps 4-7) split the keys of every tile: group g owns keys
-// [64g, 64g + 64) of the tile for row tid % 128 -- its own reference maximum and denominator, its own half of P and
-// its own output row O_g, which stays in tensor memory for the whole segment: the products P_g . V_g accumulate there.
-// The reference maximum of a row only moves when a tile's maximum exceeds it by more than 2^8 (then the row of O_g
-// and the denominator are rescaled, a tensor-memory load / store); otherwise probabilities are taken against the old
-// reference.  P replaces the scores in tensor memory (two bf16 per column) and is the A operand of P . V from there.
-// The two groups never exchange anything inside a segment; at its end they exchange their (maximum, denominator)
-// pairs through shared memory and each writes half of the columns of the merged output row, reading both O_g.
-// Lane 0 of the issuing warp requests every tile (TMA) and issues every product: issuing blocks while the tensor
-// cores' queue is full, so that thread does nothing else, and a commit covers everything issued before it, so
-// "S of step t + 1 is complete" also tells the compute warps that P.V of step t is (O_g is up to date).
+// The output row O stays in tensor memory for the whole loop: the products P . V accumulate there.  The reference
+// maximum of a row only moves when a step's maximum exceeds it by more than 2^8 (then the row of O and the
+// denominator are rescaled, a tensor-memory load / store); otherwise probabilities are taken against the old reference
+// and may reach 2^8, which bf16 and the fp32 sums hold without loss.  P replaces the scores in tensor memory (two bf16
+// per column) and is the A operand of P . V from there.  Steps where the rule is plain (inside the key range, below
+// the causal diagonal, unmasked) take ONE pass: probabilities against the old reference with no search for the step's
+// maximum; the sum of the row's 64 probabilities, which the denominator needs anyway, tells whether that was safe (at
+// most 2^14: no score exceeded the reference by more than 14); if not, in any row of the warp, the warp redoes the step
+// with the two-pass rule before anything was stored.
+// Lane 0 of the issuing warp issues every product and lane 0 of the loading warp makes every TMA request (a request
+// costs its thread a few hundred clocks and the tile takes a microsecond or two to arrive).  A commit covers
+// everything issued before it, so "S of step t + 1 is complete" also tells the compute warps that P . V of step t is.
 //
-// Per step t:  compute: wait S_t -> [first step of the second segment: write out the first] -> P = exp2(S - m) over S
-//                       -> 8 arrivals on bar_p
-//              issuer:  wait bar_p -> P.V of step t into O_g -> S_{t+1} -> request K_{t+2}, V_{t+1}
-// Hand-overs are mbarriers with bounded waits only; the second CTA on the SM fills the gaps that remain.
-// Shared memory: 2 x Q, 2 x K, 2 x V (DC boxes each, DC = ceil(head_dim / 64)), barriers, (maximum, denominator) pairs.
-// TMEM: columns [0, 128) S / P; then one block of OCOLS columns per group for O_g.
-constexpr int FWD_COMPUTE_WARPS = 8;
-constexpr int FWD_THREADS = 32 * (FWD_COMPUTE_WARPS + 2);  // + the issuing warp and the loading warp
+// Per step t:  compute: wait S_t -> P = exp2(S - m) over S -> 4 arrivals on bar_p
+//              issuer:  wait bar_p -> P . V of step t into O -> S_{t+1}
+//              loader:  wait S_t -> request K_{t+2}, V_{t+1}
+// Hand-overs are mbarriers with bounded waits only.
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
-constexpr uint32_t FWD_TAIL_BYTES = 128 + 4096;  // barriers and the TMEM slot; 2 segments x 2 groups x 128 x (m, l)
-
-__device__ __forceinline__ void compute_warps_sync() {  // the 256 compute threads, not the issuing warp
-  asm volatile("bar.sync 1, 256;" ::: "memory");
-}
-__device__ __forceinline__ bool compute_warps_all(bool pred) {  // same barrier, AND of the predicate
-  uint32_t r;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.and.pred q, 1, 256, p;\n\t"
-      "selp.b32 %0, 1, 0, q;\n\t"
-      "}\n"
-      : "=r"(r)
-      : "r"(static_cast<uint32_t>(pred))
-      : "memory");
-  return r != 0;
-}
-
-template <int DPAD, bool DROP>
-__global__ void __launch_bounds__(FWD_THREADS, DPAD <= 64 ? 2 : 1)
-attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                     const __grid_constant__ CUtensorMap tmV, const Params p) {
-  constexpr int OCOLS = DPAD <= 64 ? 64 : 128;
-  constexpr uint32_t TMEM_COLS = DPAD <= 64 ? 256 : 512;
-  extern __shared__ uint8_t smem_raw[];
-  const Smem sm = align_smem(smem_raw);
-  const int DC = (p.d + 63) >> 6;
-  const uint32_t tile_bytes = DC * BOX_BYTES;
-  const uint32_t sQ0 = sm.base, sK0 = sQ0 + 2 * tile_bytes, sV0 = sK0 + 2 * tile_bytes;
-  const uint32_t bar0 = sV0 + 2 * tile_bytes;
-  const uint32_t bar_q0 = bar0 /* 2 */, bar_k0 = bar0 + 16 /* 2 */, bar_v0 = bar0 + 32 /* 2 */, bar_s = bar0 + 48;
-  const uint32_t bar_o = bar0 + 56, bar_p = bar0 + 64, tmem_slot = bar0 + 72;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(sm.gen + 6 * tile_bytes + 72);
-  float2* ml_all = reinterpret_cast<float2*>(sm.gen + 6 * tile_bytes + 128);  // [segment][group][row]
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int grp = (warp >> 2) & 1, row = tid & 127;
-  const bool issuer = warp == FWD_COMPUTE_WARPS, loader = warp == FWD_COMPUTE_WARPS + 1;
-  const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + TILE - 1) / TILE;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int off = p.Skv - p.Sq;
-  auto key_tiles = [&](int qt) {
-    if (!p.causal) return nkv_all;
-    const int last_q = min(qt * TILE + TILE - 1, p.Sq - 1);
-    const int last_k = last_q + off;  // largest key any row of the tile may see
-    return last_k < 0 ? 0 : min(nkv_all, last_k / TILE + 1);
-  };
-  const int qt_first = nq - 1 - static_cast<int>(blockIdx.x), qt_second = static_cast<int>(blockIdx.x);
-  const int nseg = qt_second < qt_first ? 2 : 1;  // the middle tile of an odd count is alone
-  const int n0 = key_tiles(qt_first), n1 = nseg == 2 ? key_tiles(qt_second) : 0;
-  const int steps = n0 + n1;
-  const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
-
-  if (tid == 0) {
-    for (int i = 0; i < 9; ++i) mbar_init(bar0 + 8 * i, i == 8 ? FWD_COMPUTE_WARPS : 1);
-    fence_mbar_init();
-    prefetch_tmap(&tmQ);
-    prefetch_tmap(&tmK);
-    prefetch_tmap(&tmV);
-  }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t t_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
-  const uint32_t t_out = t_row + 128 + grp * OCOLS;
-  bool ok = true;
-
-  if (issuer) {
-    if (lane == 0 && steps > 0) {
-      const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      const uint32_t idesc_o = make_idesc_bf16(128, p.d, false, true);
-      constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
-      constexpr uint64_t mn_major_hi = make_smem_desc_hi(BOX_BYTES, 1024);
-      // S_t = Q . K^T, one 128-column product per 16 columns of the head (a narrower N would re-read the same
-      // 128 x 16 block of Q once more per instruction, and the operand feed is what bounds these products)
-      auto issue_s = [&](int t) {
-        const uint32_t sQ = sQ0 + (t < n0 ? 0u : tile_bytes);
-        const uint32_t sK = sK0 + (t & 1) * tile_bytes;
-        const int ksteps = p.d >> 4;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          if (ks < ksteps) {
-            const uint32_t o = static_cast<uint32_t>(ks >> 2) * BOX_BYTES + static_cast<uint32_t>(ks & 3) * 32u;
-            umma_bf16(tmem, make_smem_desc(sQ + o, k_major_hi), make_smem_desc(sK + o, k_major_hi), idesc_s,
-                      ks > 0 ? 1u : 0u);
-          }
-        }
-        umma_commit(bar_s);
-      };
-      bool go = mbar_wait_bounded(n0 > 0 ? bar_q0 : bar_q0 + 8, 0, limit) && mbar_wait_bounded(bar_k0, 0, limit);
-      if (go) {
-        tc_fence_after();
-        issue_s(0);
-      }
-      for (int t = 0; t < steps && go; ++t) {
-        go = mbar_wait_bounded(bar_p, t & 1, limit);  // P_t is in tensor memory, S_t has been read, O_g rescaled
-        if (go) go = mbar_wait_bounded(bar_v0 + 8 * (t & 1), (t >> 1) & 1, limit);
-        if (!go) break;
-        tc_fence_after();
-        const uint32_t sV = sV0 + (t & 1) * tile_bytes;
-        const bool first = t == 0 || t == n0;  // of its segment: O_g starts from zero
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {  // O_g += P_g . V_g over the group's 64 keys, the two chains interleaved
-#pragma unroll
-          for (int g = 0; g < 2; ++g)
-            umma_bf16_tmem_a(tmem + 128 + g * OCOLS, tmem + g * 64 + ks * 8,
-                             make_smem_desc(sV + (g * 4 + ks) * 2048u, mn_major_hi), idesc_o, (!first || ks > 0) ? 1u : 0u);
-        }
-        if (t + 1 < steps) {
-          go = mbar_wait_bounded(bar_k0 + 8 * ((t + 1) & 1), ((t + 1) >> 1) & 1, limit);  // requested a step ago
-          if (go && t + 1 == n0) go = mbar_wait_bounded(bar_q0 + 8, 0, limit);            // requested at the start
-          if (!go) break;
-          issue_s(t + 1);  // executes behind the products above, which read P_t from the columns it overwrites
-        } else {
-          umma_commit(bar_o);  // the last product: the output rows are complete
-        }
-      }
-      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_MMA);
-    }
-    __syncwarp();
-  } else if (loader) {
-    // Lane 0 requests every tile as soon as its buffer is free: a request costs the requesting thread a few hundred
-    // clocks and the tile takes a microsecond or two to arrive, so neither belongs on the issuing thread's path.
-    if (lane == 0 && steps > 0) {
-      auto load_tile = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int row0) {
-        mbar_arrive_expect_tx(bar, tile_bytes);
-        for (int c = 0; c < DC; ++c) tma_load_4d(dst + c * BOX_BYTES, m, bar, c * 64, h, row0, b);
-      };
-      auto key_row = [&](int t) { return (t < n0 ? t : t - n0) * TILE; };
-      if (n0 > 0) load_tile(&tmQ, sQ0, bar_q0, qt_first * TILE);
-      load_tile(&tmK, sK0, bar_k0, key_row(0));
-      load_tile(&tmV, sV0, bar_v0, key_row(0));
-      if (steps > 1) load_tile(&tmK, sK0 + tile_bytes, bar_k0 + 8, key_row(1));
-      if (n1 > 0) load_tile(&tmQ, sQ0 + tile_bytes, bar_q0 + 8, qt_second * TILE);
-      bool go = true;
-      for (int t = 0; t + 1 < steps && go; ++t) {
-        // S_t complete: K_t is free; a commit covers everything issued before it, so P.V of step t - 1 is complete
-        // too and the other V buffer is free.  (This thread cannot fall two steps behind: S_{t+2} needs the K
-        // requested here.)
-        go = mbar_wait_bounded(bar_s, t & 1, limit);
-        if (!go) break;
-        if (t + 2 < steps) load_tile(&tmK, sK0 + (t & 1) * tile_bytes, bar_k0 + 8 * (t & 1), key_row(t + 2));
-        load_tile(&tmV, sV0 + ((t + 1) & 1) * tile_bytes, bar_v0 + 8 * ((t + 1) & 1), key_row(t + 1));
-      }
-      if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_PRODUCER);
-    }
-    __syncwarp();
-  } else {
-    const float scale_log2 = p.scale * LOG2E;
-    const bool drop_aligned = ((p.Skv | static_cast<int>(p.elem_offset)) & 3) == 0;  // uniform: every chunk starts a Philox group
-    auto wait_warp = [&](uint32_t bar, uint32_t parity) {  // the whole warp continues or the whole warp leaves
-      return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, limit)) != 0;
-    };
-    float m_run = -INFINITY, l_run = 0.f;
-    // End of a segment: the two groups' partial states of a row are merged; group g writes columns
-    // [g DPAD / 2, (g + 1) DPAD / 2) of the output, reading both O_0 and O_1 (same lanes of tensor memory).
-    auto write_out = [&](int seg, bool have_rows) {
-      float2* ml = ml_all + seg * 256;
-      ml[grp * 128 + row] = make_float2(m_run, l_run);
-      compute_warps_sync();
-      const float2 other = ml[(grp ^ 1) * 128 + row];
-      const float m_all = fmaxf(m_run, other.x);
-      const float m_use = m_all == -INFINITY ? 0.f : m_all;
-      const float w_own = exp2f(m_run - m_use), w_other = exp2f(other.x - m_use);
-      const float l_all = l_run * w_own + other.y * w_other;
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      const float f_own = w_own * inv, f_other = w_other * inv;
-      const int q_row = (seg == 0 ? qt_first : qt_second) * TILE + row;
-      bf16* dst = p.out + (static_cast<int64_t>(b) * p.Sq + q_row) * p.ld_out + static_cast<int64_t>(h) * p.d;
-#pragma unroll
-      for (int c = 0; c < DPAD / 32; ++c) {
-        const int col = grp * (DPAD / 2) + c * 16;
-        uint32_t own[16], oth[16];
-        if (have_rows) {  // uniform
-          tmem_ld_32x16(t_row + 128 + grp * OCOLS + col, own);
-          tmem_ld_32x16(t_row + 128 + (grp ^ 1) * OCOLS + col, oth);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int x = 0; x < 16; ++x) own[x] = oth[x] = 0u;
-        }
-        if (q_row < p.Sq && col < p.d) {
-          uint4 w[2];
-          uint32_t* wp = reinterpret_cast<uint32_t*>(w);
-#pragma unroll
-          for (int x = 0; x < 8; ++x)
-            wp[x] = pack_bf16x2(__uint_as_float(own[2 * x]) * f_own + __uint_as_float(oth[2 * x]) * f_other,
-                                __uint_as_float(own[2 * x + 1]) * f_own + __uint_as_float(oth[2 * x + 1]) * f_other);
-          *reinterpret_cast<uint4*>(dst + col) = w[0];
-          *reinterpret_cast<uint4*>(dst + col + 8) = w[1];
-        }
-      }
-      // rows that saw no key at all get +inf so that the backward pass turns their probabilities into zeros
-      if (grp == 0 && q_row < p.Sq)
-        p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + q_row] = l_all > 0.f ? m_all + log2f(l_all) : INFINITY;
-      m_run = -INFINITY;
-      l_run = 0.f;
-    };
-    if (n0 == 0) write_out(0, false);  // a first segment whose rows see no key (more queries than keys, causal)
-    bool mid_done = !(n0 > 0 && n1 > 0);  // the first segment is written out from inside the loop
-    for (int t = 0; t < steps; ++t) {
-      // S_t complete; a commit covers everything issued before it, so P.V of step t - 1 is complete too
-      ok = wait_warp(bar_s, t & 1);
-      if (!ok) break;
-      tc_fence_after();
-      const int seg = t < n0 ? 0 : 1, j = t - seg * n0, qt = seg == 0 ? qt_first : qt_second;
-      if (seg == 1 && j == 0 && n0 > 0) {
-        write_out(0, true);
-        mid_done = true;
-      }
-      const int q_row = qt * TILE + row;
-      const int q_clamped = min(q_row, p.Sq - 1);
-      const float* mask_row = p.mask == nullptr ? nullptr
-                                                : p.mask + b * p.mask_sb + h * p.mask_sh + q_clamped * p.mask_sq;
-      const int k_limit_row = p.causal ? min(p.Skv, q_row + off + 1) : p.Skv;
-      const uint64_t drop_row = p.elem_offset + ((static_cast<uint64_t>(b) * p.H + h) * p.Sq + q_clamped) * p.Skv;
-      const int k0 = j * TILE + grp * 64;
-      // whole tile inside the key range, below the causal diagonal for every row and unmasked: no per-element rule
-      const bool plain = p.mask == nullptr && j * TILE + TILE <= p.Skv && scale_log2 > 0.f &&
-                         (!p.causal || j * TILE + TILE - 1 <= qt * TILE + off);
-      float row_sum = 0.f;
-      // One pass where the rule is plain and the row has a reference maximum: probabilities against the OLD reference,
-      // no search for the tile's maximum.  The sum of the group's 64 probabilities tells whether that was safe: at most
-      // 2^14 means that no score exceeded the reference by more than 14 (bf16 and the fp32 sums hold 2^14 without loss);
-      // anything else (a larger sum, inf, NaN) in any row of the warp sends the whole warp through the two passes
-      // below.  Nothing has been stored by then: P goes over the scores only after the check.
-      bool fast = DROP ? false : (plain && j > 0 && __all_sync(0xffffffffu, m_run > -INFINITY) != 0);
-      if (fast) {
-        uint32_t packed[2][16];
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t acc[32];
-          tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-          tmem_ld_wait();
-#pragma unroll
-          for (int x = 0; x < 32; x += 2) {
-            const float e0 = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_run));
-            const float e1 = fast_exp2(fmaf(__uint_as_float(acc[x + 1]), scale_log2, -m_run));
-            part[(x >> 1) & 3] += e0 + e1;
-            packed[c][x >> 1] = pack_bf16x2(e0, e1);
-          }
-        }
-        const float sum = (part[0] + part[1]) + (part[2] + part[3]);
-        fast = __all_sync(0xffffffffu, sum <= 16384.f) != 0;
-        if (fast) {
-          tmem_st_32x16(t_row + grp * 64, packed[0]);
-          tmem_st_32x16(t_row + grp * 64 + 16, packed[1]);
-          row_sum = sum;
-        }
-      }
-      if (!fast) {
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t acc[32];
-          tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-          tmem_ld_wait();
-          if (plain) {
-#pragma unroll
-            for (int x = 0; x < 32; ++x) mx = fmaxf(mx, __uint_as_float(acc[x]));
-          } else {
-            float v[32];
-            score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
-#pragma unroll
-            for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
-          }
-        }
-        if (plain) mx *= scale_log2;  // the scale is positive: the maximum commutes with it
-        // the reference maximum moves only when this tile exceeds it by more than the threshold (always on the first
-        // tile that has a finite score); the decision is taken per warp, the tensor-memory accesses are warp-collective
-        const bool move = mx > m_run + RESCALE_THRESHOLD || (m_run == -INFINITY && mx > -INFINITY);
-        if (__any_sync(0xffffffffu, move)) {
-          const float m_new = move ? mx : m_run;
-          const float alpha = (move && m_run > -INFINITY) ? fast_exp2(m_run - m_new) : 1.f;
-          if (j > 0) {  // rows of O_g that exist already (uniform)
-#pragma unroll
-            for (int c = 0; c < DPAD / 32; ++c) {
-              uint32_t acc[32];
-              tmem_ld_32x32(t_out + c * 32, acc);
-              tmem_ld_wait();
-#pragma unroll
-              for (int x = 0; x < 32; ++x) acc[x] = __float_as_uint(__uint_as_float(acc[x]) * alpha);
-              tmem_st_32x32(t_out + c * 32, acc);
-            }
-            tmem_st_wait();
-          }
-          l_run *= alpha;
-          m_run = m_new;
-        }
-        const float m_use = m_run == -INFINITY ? 0.f : m_run;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t acc[32];
-          float v[32];
-          tmem_ld_32x32(t_row + grp * 64 + c * 32, acc);
-          tmem_ld_wait();
-          if (plain) {
-#pragma unroll
-            for (int x = 0; x < 32; ++x) v[x] = fast_exp2(fmaf(__uint_as_float(acc[x]), scale_log2, -m_use));
-          } else {
-            score_chunk(acc, v, scale_log2, mask_row, k0 + c * 32, p.Skv, k_limit_row);
-#pragma unroll
-            for (int x = 0; x < 32; ++x) v[x] = fast_exp2(v[x] - m_use);
-          }
-#pragma unroll
-          for (int x = 0; x < 32; ++x) row_sum += v[x];
-          if constexpr (DROP) {  // the denominator sums all probabilities, P . V only the kept ones
-            float f[32];
-            dropout_factors(f, drop_row + static_cast<uint64_t>(k0 + c * 32), drop_aligned, p.seed, p.drop_threshold, p.inv_keep);
-#pragma unroll
-            for (int x = 0; x < 32; ++x) v[x] *= f[x];
-          }
-          // P as the A operand in tensor memory: two bf16 per column, over the score columns this group has read already
-          uint32_t packed[16];
-#pragma unroll
-          for (int x = 0; x < 16; ++x) packed[x] = pack_bf16x2(v[2 * x], v[2 * x + 1]);
-          tmem_st_32x16(t_row + grp * 64 + c * 16, packed);
-        }
-      }
-      l_run += row_sum;
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p);
-    }
-    if (ok && steps > 0) ok = wait_warp(bar_o, 0);  // the last P.V
-    if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_EPILOGUE);
-    // the merge has a barrier among the compute warps: if a wait ran out in any of them, all skip it (a warp that
-    // left the loop before the barrier inside it makes up for that one first, so that the counts agree)
-    if (!mid_done) compute_warps_sync();
-    ok = compute_warps_all(ok);
-    if (ok) {
-      tc_fence_after();
-      if (nseg == 1) {
-        if (n0 > 0) write_out(0, true);
-      } else if (n1 > 0) {
-        write_out(1, true);
-      } else {
-        if (n0 > 0) write_out(0, true);
-        write_out(1, false);
-      }
-    }
-  }
-
-  if (__syncthreads_and(ok) == 0) {  // a wait ran out: leave time for what is in flight before tensor memory goes back
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000LL) {
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
-}
-
-// ------------------------------------------------------------------------------------------------------------
-// Forward for head_dim <= 64, 64 keys per step: FOUR CTAs per SM.  grid = (query tiles, heads, batch), late (long)
-// query tiles first.  One step of a CTA is a chain of hand-overs (scores complete -> exponentials -> arrive -> issue ->
-// commit) whose latencies a CTA cannot hide from itself; what hides them is more CTAs per SM.  Half as many keys per
-// step halves everything a CTA holds: 128 TMEM columns (64 S / P, 64 O), 48 KB of shared memory (Q, 2 x K, 2 x V of
-// 64 rows), 4 compute warps (one thread per query row, all 64 keys of the step) + the issuing warp + the loading warp.
-// The rules are those of the kernel above: O stays in tensor memory and is rescaled only when the reference maximum
-// moves (by more than 2^8); P goes over the scores as the tensor-memory A operand of P . V; plain tiles take one pass
-// against the old reference, checked by the row sum; all hand-overs are mbarriers with bounded waits.
 constexpr int KSTEP = 64;
-constexpr int FWD64_COMPUTE_WARPS = 4;
-constexpr int FWD64_THREADS = 32 * (FWD64_COMPUTE_WARPS + 2);
+constexpr int FWD_COMPUTE_WARPS = 4;
+constexpr int FWD_THREADS = 32 * (FWD_COMPUTE_WARPS + 2);
 constexpr uint32_t KV_BOX_BYTES = KSTEP * 128;  // 64 rows of 128 bytes
 
 template <int DPAD, bool DROP>
-__global__ void __launch_bounds__(FWD64_THREADS, 4)
-attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(FWD_THREADS, DPAD <= 64 ? 4 : 2)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const Params p) {
-  static_assert(DPAD <= 64, "one 64-column box per tile");
-  constexpr uint32_t TMEM_COLS = 128, COL_O = 64;
+  constexpr uint32_t TMEM_COLS = DPAD <= 64 ? 128 : 256, COL_O = 64;
+  constexpr uint32_t DC = DPAD <= 64 ? 1 : 2;  // 64-column boxes per tile
+  constexpr uint32_t Q_BYTES = DC * BOX_BYTES, KV_BYTES = DC * KV_BOX_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = align_smem(smem_raw);
-  const uint32_t sQ = sm.base, sK0 = sQ + BOX_BYTES, sV0 = sK0 + 2 * KV_BOX_BYTES;
-  const uint32_t bar0 = sV0 + 2 * KV_BOX_BYTES;
+  const uint32_t sQ = sm.base, sK0 = sQ + Q_BYTES, sV0 = sK0 + 2 * KV_BYTES;
+  const uint32_t bar0 = sV0 + 2 * KV_BYTES;
   const uint32_t bar_q = bar0, bar_k0 = bar0 + 8 /* 2 */, bar_v0 = bar0 + 24 /* 2 */, bar_s = bar0 + 40;
   const uint32_t bar_o = bar0 + 48, bar_p = bar0 + 56, tmem_slot = bar0 + 64;
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(sm.gen + BOX_BYTES + 4 * KV_BOX_BYTES + 64);
+      reinterpret_cast<volatile uint32_t*>(sm.gen + Q_BYTES + 4 * KV_BYTES + 64);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = tid & 127;
-  const bool issuer = warp == FWD64_COMPUTE_WARPS, loader = warp == FWD64_COMPUTE_WARPS + 1;
+  const bool issuer = warp == FWD_COMPUTE_WARPS, loader = warp == FWD_COMPUTE_WARPS + 1;
   const int nq = (p.Sq + TILE - 1) / TILE, nkv_all = (p.Skv + KSTEP - 1) / KSTEP;
   const int qt = nq - 1 - static_cast<int>(blockIdx.x);
   const int h = blockIdx.y, b = blockIdx.z;
@@ -610,7 +238,7 @@ attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const long long limit = p.wait_limit > 0 ? p.wait_limit : WAIT_LIMIT_CYCLES;
 
   if (tid == 0) {
-    for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8 * i, i == 7 ? FWD64_COMPUTE_WARPS : 1);
+    for (int i = 0; i < 8; ++i) mbar_init(bar0 + 8 * i, i == 7 ? FWD_COMPUTE_WARPS : 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
@@ -635,12 +263,13 @@ attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       constexpr uint64_t k_major_hi = make_smem_desc_hi(16, 1024);
       constexpr uint64_t mn_major_hi = make_smem_desc_hi(KV_BOX_BYTES, 1024);
       auto issue_s = [&](int t) {  // S_t = Q . K_t^T: 64 columns, one product per 16 columns of the head
-        const uint32_t sK = sK0 + (t & 1) * KV_BOX_BYTES;
+        const uint32_t sK = sK0 + (t & 1) * KV_BYTES;
         const int ksteps = p.d >> 4;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < 4 * static_cast<int>(DC); ++ks) {
           if (ks < ksteps)
-            umma_bf16(tmem, make_smem_desc(sQ + ks * 32u, k_major_hi), make_smem_desc(sK + ks * 32u, k_major_hi), idesc_s,
+            umma_bf16(tmem, make_smem_desc(sQ + (ks >> 2) * BOX_BYTES + (ks & 3) * 32u, k_major_hi),
+                      make_smem_desc(sK + (ks >> 2) * KV_BOX_BYTES + (ks & 3) * 32u, k_major_hi), idesc_s,
                       ks > 0 ? 1u : 0u);
         }
         umma_commit(bar_s);
@@ -655,7 +284,7 @@ attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (go) go = mbar_wait_bounded(bar_v0 + 8 * (t & 1), (t >> 1) & 1, limit);
         if (!go) break;
         tc_fence_after();
-        const uint32_t sV = sV0 + (t & 1) * KV_BOX_BYTES;
+        const uint32_t sV = sV0 + (t & 1) * KV_BYTES;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)  // O += P . V_t over the 64 keys
           umma_bf16_tmem_a(tmem + COL_O, tmem + ks * 8, make_smem_desc(sV + ks * 2048u, mn_major_hi), idesc_o,
@@ -674,14 +303,14 @@ attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   } else if (loader) {
     if (lane == 0 && steps > 0) {
       auto load_kv = [&](const CUtensorMap* m, uint32_t dst, uint32_t bar, int t) {
-        mbar_arrive_expect_tx(bar, KV_BOX_BYTES);
-        tma_load_4d(dst, m, bar, 0, h, t * KSTEP, b);
+        mbar_arrive_expect_tx(bar, KV_BYTES);
+        for (uint32_t c = 0; c < DC; ++c) tma_load_4d(dst + c * KV_BOX_BYTES, m, bar, c * 64, h, t * KSTEP, b);
       };
-      mbar_arrive_expect_tx(bar_q, BOX_BYTES);
-      tma_load_4d(sQ, &tmQ, bar_q, 0, h, qt * TILE, b);
+      mbar_arrive_expect_tx(bar_q, Q_BYTES);
+      for (uint32_t c = 0; c < DC; ++c) tma_load_4d(sQ + c * BOX_BYTES, &tmQ, bar_q, c * 64, h, qt * TILE, b);
       load_kv(&tmK, sK0, bar_k0, 0);
       load_kv(&tmV, sV0, bar_v0, 0);
-      if (steps > 1) load_kv(&tmK, sK0 + KV_BOX_BYTES, bar_k0 + 8, 1);
+      if (steps > 1) load_kv(&tmK, sK0 + KV_BYTES, bar_k0 + 8, 1);
       bool go = true;
       for (int t = 0; t + 1 < steps && go; ++t) {
         // S_t complete: K_t is free; a commit covers everything issued before it, so P.V of step t - 1 is complete
@@ -689,8 +318,8 @@ attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         // requested here.)
         go = mbar_wait_bounded(bar_s, t & 1, limit);
         if (!go) break;
-        if (t + 2 < steps) load_kv(&tmK, sK0 + (t & 1) * KV_BOX_BYTES, bar_k0 + 8 * (t & 1), t + 2);
-        load_kv(&tmV, sV0 + ((t + 1) & 1) * KV_BOX_BYTES, bar_v0 + 8 * ((t + 1) & 1), t + 1);
+        if (t + 2 < steps) load_kv(&tmK, sK0 + (t & 1) * KV_BYTES, bar_k0 + 8 * (t & 1), t + 2);
+        load_kv(&tmV, sV0 + ((t + 1) & 1) * KV_BYTES, bar_v0 + 8 * ((t + 1) & 1), t + 1);
       }
       if (!go && p.status != nullptr) atomicCAS(p.status, 0, LEANFFN_DEV_TIMEOUT_PRODUCER);
     }
@@ -718,7 +347,7 @@ attention_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const bool plain = p.mask == nullptr && k0 + KSTEP <= p.Skv && scale_log2 > 0.f &&
                          (!p.causal || k0 + KSTEP - 1 <= qt * TILE + off);
       float row_sum = 0.f;
-      // one pass against the OLD reference maximum where the rule is plain, checked by the row sum (see the kernel above)
+      // one pass against the OLD reference maximum where the rule is plain, checked by the row sum
       bool fast = DROP ? false : (plain && t > 0 && __all_sync(0xffffffffu, m_run > -INFINITY) != 0);
       if (fast) {
         uint32_t packed[2][16];
@@ -1478,47 +1107,29 @@ extern "C" int32_t leanffn_attention_forward(const leanffn_attention_desc* d, vo
   const int32_t v = attn::validate(d, false);
   if (v != LEANFFN_OK) return v;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool narrow = d->head_dim <= 64;  // 64 keys per step, four CTAs per SM
   CUtensorMap tq, tk, tv;
   if (!make_tmap_bf16_heads(&tq, d->q, d->batch, d->q_len, d->heads, d->head_dim, d->ld_q) ||
-      !make_tmap_bf16_heads(&tk, d->k, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_k, narrow ? attn::KSTEP : 128) ||
-      !make_tmap_bf16_heads(&tv, d->v, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_v, narrow ? attn::KSTEP : 128))
+      !make_tmap_bf16_heads(&tk, d->k, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_k, attn::KSTEP) ||
+      !make_tmap_bf16_heads(&tv, d->v, d->batch, d->kv_len, d->heads, d->head_dim, d->ld_v, attn::KSTEP))
     return LEANFFN_ERR_DRIVER;
   const attn::Params p = attn::make_params(d);
   cudaError_t e;
-  if (narrow) {
-    const size_t smem64 = attn::BOX_BYTES + 4 * attn::KV_BOX_BYTES + 128 + 1024;
-    const dim3 grid64((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
-#define ATTN_FWD64(DPAD)                                                             \
-  {                                                                                  \
-    auto kern = p.drop_threshold != 0u ? attn::attention_fwd64_kernel<DPAD, true>    \
-                                       : attn::attention_fwd64_kernel<DPAD, false>;  \
-    e = attn::set_smem(kern, smem64);                                                \
-    if (e == cudaSuccess) {                                                          \
-      kern<<<grid64, attn::FWD64_THREADS, smem64, st>>>(tq, tk, tv, p);              \
-      e = cudaGetLastError();                                                        \
-    }                                                                                \
-  }
-    if (d->head_dim <= 32) ATTN_FWD64(32)
-    else ATTN_FWD64(64)
-#undef ATTN_FWD64
-    return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
-  }
   const int dc = (d->head_dim + 63) / 64;
-  const size_t smem = 6 * dc * attn::BOX_BYTES + attn::FWD_TAIL_BYTES + 1024;
-  const int q_tiles = (d->q_len + attn::TILE - 1) / attn::TILE;
-  const dim3 grid((q_tiles + 1) / 2, d->heads, d->batch);  // a CTA takes query tiles x and q_tiles - 1 - x
+  const size_t smem = dc * (attn::BOX_BYTES + 4 * attn::KV_BOX_BYTES) + 128 + 1024;
+  const dim3 grid((d->q_len + attn::TILE - 1) / attn::TILE, d->heads, d->batch);
 #define ATTN_FWD(DPAD)                                                             \
   {                                                                                \
     auto kern = p.drop_threshold != 0u ? attn::attention_fwd_kernel<DPAD, true>    \
                                        : attn::attention_fwd_kernel<DPAD, false>;  \
     e = attn::set_smem(kern, smem);                                                \
     if (e == cudaSuccess) {                                                        \
-      kern<<<grid, attn::FWD_THREADS, smem, st>>>(tq, tk, tv, p);                      \
+      kern<<<grid, attn::FWD_THREADS, smem, st>>>(tq, tk, tv, p);                  \
       e = cudaGetLastError();                                                      \
     }                                                                              \
   }
-  if (d->head_dim <= 96) ATTN_FWD(96)  // head sizes up to 64 took the 64-key kernel above
+  if (d->head_dim <= 32) ATTN_FWD(32)
+  else if (d->head_dim <= 64) ATTN_FWD(64)
+  else if (d->head_dim <= 96) ATTN_FWD(96)
   else ATTN_FWD(128)
 #undef ATTN_FWD
   return e == cudaSuccess ? LEANFFN_OK : 1000 + static_cast<int32_t>(e);
